@@ -1,0 +1,880 @@
+// libapk_b200.so: host side of the C ABI declared in include/allpaka_b200.h.
+//
+// Plain CUDA runtime; no PyTorch, no CPU compute fallback.  One context = one
+// GPU.  Weights are addressed by host pointer inside attached mappings, as the
+// reference CUDA backend does (crates/allpaka-backend/src/gpu/cuda/runtime/
+// select.rs:80-84, device.rs:588-621), and live on the device as the tiled
+// stream described in kernels.cuh.
+#include "../../include/allpaka_b200.h"
+#include "kernels.cuh"
+
+#include <dlfcn.h>
+
+#include <algorithm>
+#include <chrono>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <mutex>
+#include <string>
+#include <tuple>
+#include <vector>
+
+using namespace apk;
+
+namespace {
+
+thread_local std::string g_last_error;
+
+int fail(int code, const char *fmt, ...) {
+    char buf[512];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    g_last_error = buf;
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                          \
+    do {                                                                                        \
+        cudaError_t e__ = (expr);                                                               \
+        if (e__ != cudaSuccess)                                                                 \
+            return fail(e__ == cudaErrorMemoryAllocation ? APK_ERR_OOM : APK_ERR_CUDA,          \
+                        "%s: %s (%s:%d)", #expr, cudaGetErrorString(e__), __FILE__, __LINE__); \
+    } while (0)
+
+#define APK_TRY(expr)          \
+    do {                       \
+        int rc__ = (expr);     \
+        if (rc__) return rc__; \
+    } while (0)
+
+uint64_t now_ns() {
+    return (uint64_t)std::chrono::duration_cast<std::chrono::nanoseconds>(
+               std::chrono::steady_clock::now().time_since_epoch())
+        .count();
+}
+
+bool block_geom(uint32_t ty, uint32_t *be, uint32_t *bb) {
+    // crates/allpaka-dtype/src/lib.rs:79-108
+    if (ty == APK_TY_Q8_0) { *be = 32; *bb = 34; return true; }
+    if (ty == APK_TY_Q4_K) { *be = 256; *bb = 144; return true; }
+    return false;
+}
+
+// A device buffer that only ever grows (never while a graph that uses it exists).
+struct DevBuf {
+    void *p = nullptr;
+    size_t cap = 0;
+    int ensure(size_t bytes, bool zero = false) {
+        if (bytes <= cap) return APK_OK;
+        if (p) cudaFree(p);
+        p = nullptr;
+        cap = 0;
+        const size_t want = std::max(bytes, (size_t)4096);
+        CUDA_TRY(cudaMalloc(&p, want));
+        cap = want;
+        if (zero) CUDA_TRY(cudaMemset(p, 0, want));
+        return APK_OK;
+    }
+    void release() {
+        if (p) cudaFree(p);
+        p = nullptr;
+        cap = 0;
+    }
+    template <class T> T *as() const { return reinterpret_cast<T *>(p); }
+};
+
+// One source of rows for a device matrix: rows [row0, row0+rows) and 32-element
+// blocks starting at kblk0 of the host matrix at `w`; segment row r lands at
+// destination row (r / group) * stride + offset + r % group.
+struct Segment {
+    const void *w;
+    uint32_t n_in_full;
+    uint32_t row0, rows;
+    uint32_t kblk0;
+    int group, stride, offset;
+};
+
+struct DevMatrix {
+    uint32_t ty = 0;
+    uint32_t n_out = 0, n_in = 0;  // of the device matrix (after sharding / fusing)
+    int nb = 0, n_tiles = 0, KS = 0;
+    uint32_t tile_bytes = 0;
+    size_t bytes = 0;
+    uint8_t *d = nullptr;
+    std::vector<std::pair<const uint8_t *, size_t>> host_spans;  // for detach
+    ~DevMatrix() {
+        if (d) cudaFree(d);
+    }
+};
+
+// (kind, p0, p1, p2, ty, n_out, n_in, shard kind, shard index * 64 + world)
+typedef std::tuple<int, const void *, const void *, const void *, uint32_t, uint32_t, uint32_t, int, int> MatKey;
+enum { KIND_PLAIN = 0, KIND_QKV = 1, KIND_GATEUP = 2 };
+enum { SHARD_NONE = 0, SHARD_ROWS = 1, SHARD_K = 2 };
+
+// ---- NCCL through dlopen: only tensor-parallel runs need the library ---------
+struct Nccl {
+    void *h = nullptr;
+    struct uid_t { char internal[128]; };
+    int (*GetUniqueId)(uid_t *) = nullptr;
+    int (*CommInitRank)(void **, int, uid_t, int) = nullptr;
+    int (*CommDestroy)(void *) = nullptr;
+    int (*AllReduce)(const void *, void *, size_t, int, int, void *, cudaStream_t) = nullptr;
+    int (*AllGather)(const void *, void *, size_t, int, void *, cudaStream_t) = nullptr;
+    const char *(*GetErrorString)(int) = nullptr;
+    bool load() {
+        if (h) return true;
+        h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+        if (!h) return false;
+        GetUniqueId = (decltype(GetUniqueId))dlsym(h, "ncclGetUniqueId");
+        CommInitRank = (decltype(CommInitRank))dlsym(h, "ncclCommInitRank");
+        CommDestroy = (decltype(CommDestroy))dlsym(h, "ncclCommDestroy");
+        AllReduce = (decltype(AllReduce))dlsym(h, "ncclAllReduce");
+        AllGather = (decltype(AllGather))dlsym(h, "ncclAllGather");
+        GetErrorString = (decltype(GetErrorString))dlsym(h, "ncclGetErrorString");
+        return GetUniqueId && CommInitRank && CommDestroy && AllReduce && AllGather && GetErrorString;
+    }
+};
+Nccl g_nccl;
+constexpr int NCCL_FLOAT32 = 7;  // ncclFloat32
+constexpr int NCCL_SUM = 0;      // ncclSum
+
+struct PlanLayer {
+    DevMatrix *qkv = nullptr, *wo = nullptr, *gateup = nullptr, *down = nullptr;
+    const float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;  // device
+};
+
+struct Plan {
+    // identity of the request this plan was built for
+    const apk_token_layer *layers_key = nullptr;
+    uint32_t n_layers = 0;
+    const void *output_key = nullptr;
+    uint32_t hidden = 0, head_dim = 0, n_heads = 0, n_kv_heads = 0, rot_dim = 0, vocab = 0, ffn = 0;
+    float eps = 0;
+    // local (per-rank) shapes
+    uint32_t nq_l = 0, nkv_l = 0, ffn_l = 0, vocab_l = 0;
+    std::vector<PlanLayer> L;
+    DevMatrix *head = nullptr;
+    const float *out_norm = nullptr;
+    DevBuf norms, xin, x[2], qkv, yp, act_h, act_q, act_d, logits, logits_all, amax, rope;
+    cudaGraphExec_t exec[APK_MAX_M + 1][2] = {};  // [m][argmax]
+    int launches[APK_MAX_M + 1][2] = {};
+    ~Plan() {
+        for (auto &row : exec)
+            for (auto &e : row)
+                if (e) cudaGraphExecDestroy(e);
+        for (DevBuf *b : {&norms, &xin, &x[0], &x[1], &qkv, &yp, &act_h, &act_q, &act_d, &logits, &logits_all, &amax, &rope})
+            b->release();
+    }
+};
+
+}  // namespace
+
+struct apk_ctx {
+    std::mutex mu;
+    int device = 0;
+    int n_sm = 0;
+    int smem_optin = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    std::map<std::pair<const uint8_t *, size_t>, int> attached;  // (base,len) -> refcount
+    std::map<MatKey, std::unique_ptr<DevMatrix>> mats;
+    DevBuf staging;             // raw GGUF rows on their way to the repack
+    DevBuf partials, counters;  // stream-K fix-up scratch
+    int *d_err = nullptr;       // device error word
+    int *h_err = nullptr;       // pinned mirror
+    DevBuf x_dev, y_dev, act_a, act_b, misc, dump;
+    apk_stats_t st{};
+    int rank = 0, world = 1;
+    void *comm = nullptr;
+    std::unique_ptr<Plan> plan;
+};
+
+namespace {
+
+// ------------------------------------------------------------ kernel table
+
+typedef void (*MvKernel)(const MvParams);
+
+template <int TY, bool DUMP>
+MvKernel pick_m(int m) {
+    switch (m) {
+        case 1: return matvec_streamk_kernel<TY, 1, DUMP>;
+        case 2: return matvec_streamk_kernel<TY, 2, DUMP>;
+        case 3: return matvec_streamk_kernel<TY, 3, DUMP>;
+        case 4: return matvec_streamk_kernel<TY, 4, DUMP>;
+        case 5: return matvec_streamk_kernel<TY, 5, DUMP>;
+        case 6: return matvec_streamk_kernel<TY, 6, DUMP>;
+        case 7: return matvec_streamk_kernel<TY, 7, DUMP>;
+        case 8: return matvec_streamk_kernel<TY, 8, DUMP>;
+        case 10: return matvec_streamk_kernel<TY, 10, DUMP>;
+        case 12: return matvec_streamk_kernel<TY, 12, DUMP>;
+        case 14: return matvec_streamk_kernel<TY, 14, DUMP>;
+        case 16: return matvec_streamk_kernel<TY, 16, DUMP>;
+        default: return nullptr;
+    }
+}
+
+MvKernel pick_kernel(uint32_t ty, int m_eff, bool dump) {
+    if (ty == APK_TY_Q8_0) return dump ? pick_m<TY_Q8_0, true>(m_eff) : pick_m<TY_Q8_0, false>(m_eff);
+    if (ty == APK_TY_Q4_K) return dump ? pick_m<TY_Q4_K, true>(m_eff) : pick_m<TY_Q4_K, false>(m_eff);
+    return nullptr;
+}
+
+int mv_smem_bytes(int m_eff, int n_stages, int act_rec) {
+    return 256 + 2 * m_eff * TILE_ROWS * 4 + n_stages * (STAGE_W_BYTES + ((act_rec + 127) & ~127));
+}
+
+int init_kernel_attrs(apk_ctx *c) {
+    static const int ms[] = {1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 14, 16};
+    for (uint32_t ty : {APK_TY_Q8_0, APK_TY_Q4_K})
+        for (int m : ms)
+            for (int dump = 0; dump < 2; ++dump) {
+                MvKernel k = pick_kernel(ty, m, dump != 0);
+                CUDA_TRY(cudaFuncSetAttribute((const void *)k, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              c->smem_optin));
+            }
+    return APK_OK;
+}
+
+int ke_of(uint32_t ty) { return ty == APK_TY_Q8_0 ? 256 : 512; }
+
+// --------------------------------------------------------------- matrices
+
+bool inside_attached(apk_ctx *c, const void *p, size_t len) {
+    const uint8_t *b = (const uint8_t *)p;
+    for (auto &kv : c->attached) {
+        const uint8_t *base = kv.first.first;
+        if (b >= base && b + len <= base + kv.first.second) return true;
+    }
+    return false;
+}
+
+size_t host_bytes(uint32_t ty, uint32_t n_out, uint32_t n_in) {
+    uint32_t be, bb;
+    if (!block_geom(ty, &be, &bb)) return 0;
+    return (size_t)n_out * (n_in / be) * bb;
+}
+
+// Build a device matrix of n_out x n_in from row segments of host matrices.
+int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const std::vector<Segment> &segs,
+                 std::unique_ptr<DevMatrix> *out) {
+    uint32_t be, bb;
+    if (!block_geom(ty, &be, &bb)) return fail(APK_DECLINE_UNSUPPORTED_TYPE, "ggml type %u has no kernel", ty);
+    if (n_in == 0 || n_out == 0 || n_in % be)
+        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "row length %u is not whole %u-element blocks", n_in, be);
+    auto m = std::make_unique<DevMatrix>();
+    m->ty = ty;
+    m->n_out = n_out;
+    m->n_in = n_in;
+    m->nb = (int)(n_in / 32);
+    m->n_tiles = (int)((n_out + TILE_ROWS - 1) / TILE_ROWS);
+    const int kt = ty == APK_TY_Q8_0 ? Q8_KT : Q4_KT_SB * 8;
+    m->KS = (m->nb + kt - 1) / kt;
+    m->tile_bytes = ty == APK_TY_Q8_0 ? (uint32_t)m->nb * Q8_BLOCK_UNIT : (uint32_t)(m->nb / 8) * Q4_SB_UNIT;
+    m->bytes = (size_t)m->n_tiles * m->tile_bytes;
+    CUDA_TRY(cudaMalloc((void **)&m->d, m->bytes));
+    CUDA_TRY(cudaMemsetAsync(m->d, 0, m->bytes, c->stream));
+    APK_TRY(c->counters.ensure((size_t)m->n_tiles * sizeof(int), true));
+
+    const size_t seg_row_bytes = (size_t)n_in / be * bb;
+    for (const Segment &s : segs) {
+        const size_t full_row_bytes = (size_t)s.n_in_full / be * bb;
+        const uint8_t *src =
+            (const uint8_t *)s.w + (size_t)s.row0 * full_row_bytes + (size_t)s.kblk0 * 32 / be * bb;
+        m->host_spans.emplace_back((const uint8_t *)s.w + (size_t)s.row0 * full_row_bytes,
+                                   (size_t)s.rows * full_row_bytes);
+        // upload in slabs of whole rows through the staging buffer
+        const size_t slab_rows = std::max<size_t>(1, ((size_t)256 << 20) / seg_row_bytes);
+        APK_TRY(c->staging.ensure(std::min<size_t>(slab_rows, s.rows) * seg_row_bytes));
+        for (size_t r0 = 0; r0 < s.rows; r0 += slab_rows) {
+            const size_t nr = std::min<size_t>(slab_rows, s.rows - r0);
+            CUDA_TRY(cudaMemcpy2DAsync(c->staging.p, seg_row_bytes, src + r0 * full_row_bytes, full_row_bytes,
+                                       seg_row_bytes, nr, cudaMemcpyHostToDevice, c->stream));
+            RepackParams rp;
+            rp.src = c->staging.as<uint8_t>();
+            rp.src_row_bytes = seg_row_bytes;
+            rp.src_rows = (int)nr;
+            rp.row_base = (int)r0;
+            rp.nb = m->nb;
+            rp.dst = m->d;
+            rp.dst_tile_bytes = m->tile_bytes;
+            rp.group = s.group;
+            rp.stride = s.stride;
+            rp.offset = s.offset;
+            const size_t total = ty == APK_TY_Q8_0 ? nr * (size_t)m->nb : nr * (size_t)(m->nb / 8) * 9;
+            const int threads = 256;
+            const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+            if (ty == APK_TY_Q8_0)
+                repack_q8_0_kernel<<<blocks, threads, 0, c->stream>>>(rp);
+            else
+                repack_q4_k_kernel<<<blocks, threads, 0, c->stream>>>(rp);
+            CUDA_TRY(cudaGetLastError());
+            c->st.launches++;
+            CUDA_TRY(cudaStreamSynchronize(c->stream));  // staging is reused by the next slab
+        }
+    }
+    c->st.weight_bytes += m->bytes;
+    *out = std::move(m);
+    return APK_OK;
+}
+
+int check_host_matrix(apk_ctx *c, const char *what, const void *w, uint32_t ty, uint32_t n_out, uint32_t n_in) {
+    uint32_t be, bb;
+    if (!block_geom(ty, &be, &bb))
+        return fail(APK_DECLINE_UNSUPPORTED_TYPE, "%s: tensor has unsupported type %u", what, ty);
+    if (!w || n_out == 0 || n_in == 0) return fail(APK_ERR_INVALID_ARG, "%s: null or empty matrix", what);
+    if (n_in % be)
+        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "%s: row length %u is not whole %u-element blocks", what, n_in, be);
+    if (!inside_attached(c, w, host_bytes(ty, n_out, n_in)))
+        return fail(APK_DECLINE_FOREIGN_MEMORY, "%s: weights are outside attached mappings", what);
+    return APK_OK;
+}
+
+int shard_tag(apk_ctx *c, int kind) { return kind == SHARD_NONE ? 0 : c->rank * 64 + c->world; }
+
+// A single host matrix, whole or sharded for this rank.
+int resolve_plain(apk_ctx *c, const char *what, const void *w, uint32_t ty, uint32_t n_out, uint32_t n_in, int shard,
+                  DevMatrix **out) {
+    if (c->world == 1) shard = SHARD_NONE;
+    MatKey key(KIND_PLAIN, w, nullptr, nullptr, ty, n_out, n_in, shard, shard_tag(c, shard));
+    auto it = c->mats.find(key);
+    if (it != c->mats.end()) { *out = it->second.get(); return APK_OK; }
+    APK_TRY(check_host_matrix(c, what, w, ty, n_out, n_in));
+    uint32_t be, bb;
+    block_geom(ty, &be, &bb);
+    Segment s{w, n_in, 0, n_out, 0, 1 << 30, 0, 0};
+    uint32_t dn_out = n_out, dn_in = n_in;
+    if (shard == SHARD_ROWS) {
+        if (n_out % c->world) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "%s: %u rows do not split over %d ranks", what, n_out, c->world);
+        dn_out = n_out / c->world;
+        s.row0 = c->rank * dn_out;
+        s.rows = dn_out;
+    } else if (shard == SHARD_K) {
+        if (n_in % (c->world * be)) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "%s: row length %u does not split over %d ranks in %u-element blocks", what, n_in, c->world, be);
+        dn_in = n_in / c->world;
+        s.kblk0 = c->rank * (dn_in / 32);
+    }
+    std::unique_ptr<DevMatrix> m;
+    APK_TRY(build_matrix(c, ty, dn_out, dn_in, {s}, &m));
+    *out = m.get();
+    c->mats[key] = std::move(m);
+    return APK_OK;
+}
+
+// wq | wk | wv as one matrix whose tiles are whole heads (head_dim 128); with
+// tensor parallelism this rank's Q heads, then its K heads, then its V heads.
+int resolve_qkv(apk_ctx *c, uint32_t ty, const void *wq, const void *wk, const void *wv, uint32_t hidden,
+                uint32_t n_q, uint32_t n_kv, DevMatrix **out) {
+    MatKey key(KIND_QKV, wq, wk, wv, ty, n_q + 2 * n_kv, hidden, SHARD_ROWS, shard_tag(c, SHARD_ROWS));
+    auto it = c->mats.find(key);
+    if (it != c->mats.end()) { *out = it->second.get(); return APK_OK; }
+    APK_TRY(check_host_matrix(c, "attn wq", wq, ty, n_q, hidden));
+    APK_TRY(check_host_matrix(c, "attn wk", wk, ty, n_kv, hidden));
+    APK_TRY(check_host_matrix(c, "attn wv", wv, ty, n_kv, hidden));
+    if ((n_q / TILE_ROWS) % c->world || (n_kv / TILE_ROWS) % c->world)
+        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "attention heads (%u q, %u kv) do not split over %d ranks",
+                    n_q / TILE_ROWS, n_kv / TILE_ROWS, c->world);
+    const uint32_t ql = n_q / c->world, kl = n_kv / c->world;
+    std::vector<Segment> segs = {
+        {wq, hidden, c->rank * ql, ql, 0, 1 << 30, 0, 0},
+        {wk, hidden, c->rank * kl, kl, 0, 1 << 30, 0, (int)ql},
+        {wv, hidden, c->rank * kl, kl, 0, 1 << 30, 0, (int)(ql + kl)},
+    };
+    std::unique_ptr<DevMatrix> m;
+    APK_TRY(build_matrix(c, ty, ql + 2 * kl, hidden, segs, &m));
+    *out = m.get();
+    c->mats[key] = std::move(m);
+    return APK_OK;
+}
+
+// gate and up interleaved in groups of 64 rows so one 128-row tile holds 64
+// gate rows and the 64 matching up rows (the SwiGLU epilogue is then tile-local).
+int resolve_gateup(apk_ctx *c, uint32_t ty, const void *gate, const void *up, uint32_t hidden, uint32_t ffn,
+                   DevMatrix **out, uint32_t *ffn_local) {
+    MatKey key(KIND_GATEUP, gate, up, nullptr, ty, ffn, hidden, SHARD_ROWS, shard_tag(c, SHARD_ROWS));
+    if (ffn % (c->world * 32))
+        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "ffn width %u does not split over %d ranks in 32-row blocks", ffn, c->world);
+    const uint32_t fl = ffn / c->world;
+    *ffn_local = fl;
+    auto it = c->mats.find(key);
+    if (it != c->mats.end()) { *out = it->second.get(); return APK_OK; }
+    APK_TRY(check_host_matrix(c, "ffn gate", gate, ty, ffn, hidden));
+    APK_TRY(check_host_matrix(c, "ffn up", up, ty, ffn, hidden));
+    std::vector<Segment> segs = {
+        {gate, hidden, c->rank * fl, fl, 0, 64, 128, 0},
+        {up, hidden, c->rank * fl, fl, 0, 64, 128, 64},
+    };
+    const uint32_t tiles = (fl + 63) / 64;
+    std::unique_ptr<DevMatrix> m;
+    APK_TRY(build_matrix(c, ty, tiles * TILE_ROWS, hidden, segs, &m));
+    *out = m.get();
+    c->mats[key] = std::move(m);
+    return APK_OK;
+}
+
+// --------------------------------------------------------------- launches
+
+ActLayout act_layout(void *base, uint32_t consumer_ty, int m_eff) {
+    ActLayout L;
+    L.base = (uint8_t *)base;
+    L.ke = ke_of(consumer_ty);
+    L.m_eff = m_eff;
+    return L;
+}
+
+size_t act_bytes(uint32_t consumer_ty, int m_eff, uint32_t n_in) {
+    ActLayout L = act_layout(nullptr, consumer_ty, m_eff);
+    return L.total_bytes((int)n_in) + 256;
+}
+
+struct ActMode {
+    int two_level;
+    int m_eff;
+};
+
+ActMode resolve_mode(uint32_t act_mode, uint32_t m) {
+    // QuantMat::matmul: m == 1 -> Q8 activations, m > 1 -> f32 dots (quantmat/mod.rs:142-169)
+    const bool f32 = act_mode == APK_ACT_F32 || (act_mode == APK_ACT_AUTO && m > 1);
+    return ActMode{f32 ? 1 : 0, (int)(f32 ? 2 * m : m)};
+}
+
+// x [m][n] (f32 or bf16) -> prepared activations for a consumer matrix of type `cty`.
+int launch_prep(apk_ctx *c, const void *x, int x_is_bf16, int ldx, const float *add, int ldadd, float *xout,
+                int ldxout, const float *gamma, float eps, float *hout, int ldh, uint32_t n, uint32_t m,
+                uint32_t cty, ActMode mode, void *act_base) {
+    PrepParams p;
+    p.x = x; p.x_is_bf16 = x_is_bf16; p.ldx = ldx;
+    p.add = add; p.ldadd = ldadd;
+    p.xout = xout; p.ldxout = ldxout;
+    p.gamma = gamma; p.eps = eps;
+    p.hout = hout; p.ldh = ldh;
+    p.n = (int)n; p.m = (int)m;
+    p.out = act_layout(act_base, cty, mode.m_eff);
+    p.two_level = mode.two_level;
+    p.need_sum = cty == APK_TY_Q4_K;
+    dim3 grid((n / 32 + 7) / 8, m);
+    prep_acts_kernel<<<grid, 256, 0, c->stream>>>(p);
+    CUDA_TRY(cudaGetLastError());
+    c->st.launches++;
+    return APK_OK;
+}
+
+int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool dump = false) {
+    MvKernel k = pick_kernel(W->ty, mode.m_eff, dump);
+    if (!k) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "no kernel for %d activation rows", mode.m_eff);
+    p.W = W->d;
+    p.ty = (int)W->ty;
+    p.n_out = (int)W->n_out;
+    p.nb = W->nb;
+    p.n_tiles = W->n_tiles;
+    p.KS = W->KS;
+    p.tile_bytes = W->tile_bytes;
+    p.two_level = mode.two_level;
+    p.m_out = mode.two_level ? mode.m_eff / 2 : mode.m_eff;
+    p.partials = c->partials.as<float>();
+    p.counters = c->counters.as<int>();
+    p.err = c->d_err;
+    const int act_rec = p.act.rec_bytes();
+    int ns = 6;
+    while (ns > 2 && mv_smem_bytes(mode.m_eff, ns, act_rec) > c->smem_optin) --ns;
+    const int smem = mv_smem_bytes(mode.m_eff, ns, act_rec);
+    if (smem > c->smem_optin) return fail(APK_DECLINE_MISSING_CAPABILITY, "kernel needs %d bytes of shared memory", smem);
+    p.n_stages = ns;
+    const long long U = (long long)W->n_tiles * W->KS;
+    const int grid = (int)std::min<long long>(c->n_sm, U);
+    k<<<grid, MV_THREADS, smem, c->stream>>>(p);
+    CUDA_TRY(cudaGetLastError());
+    c->st.launches++;
+    return APK_OK;
+}
+
+MvParams mv_store(const ActLayout &act, float *y, int ldy) {
+    MvParams p{};
+    p.act = act;
+    p.epi = EPI_STORE;
+    p.y = y;
+    p.ldy = ldy;
+    return p;
+}
+
+// Wait for the stream, then surface any error word a kernel left behind.
+int finish(apk_ctx *c) {
+    const uint64_t t0 = now_ns();
+    cudaError_t e = cudaMemcpyAsync(c->h_err, c->d_err, sizeof(int), cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    c->st.wait_ns += now_ns() - t0;
+    if (e != cudaSuccess) return fail(APK_ERR_CUDA, "stream: %s", cudaGetErrorString(e));
+    if (*c->h_err != 0) {
+        const int w = *c->h_err;
+        cudaMemsetAsync(c->d_err, 0, sizeof(int), c->stream);
+        cudaStreamSynchronize(c->stream);
+        return fail(APK_ERR_TIMEOUT, "device-side wait expired (%s)",
+                    w == ERRW_PRODUCER_TIMEOUT ? "copy producer" : "tile consumer");
+    }
+    return APK_OK;
+}
+
+int check_m(uint32_t m) {
+    if (m == 0 || m > APK_MAX_M) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "m = %u is outside 1..%u", m, APK_MAX_M);
+    return APK_OK;
+}
+
+// One matvec on device buffers (x already in x_dev): prep + kernel -> y (device).
+int run_matvec_dev(apk_ctx *c, DevMatrix *W, const float *x_dev, uint32_t m, uint32_t act_mode, float *y_dev,
+                   bool reuse_act, int32_t *dump) {
+    const ActMode mode = resolve_mode(act_mode, m);
+    if (!reuse_act) {
+        APK_TRY(c->act_a.ensure(act_bytes(W->ty, mode.m_eff, W->n_in)));
+        APK_TRY(launch_prep(c, x_dev, 0, (int)W->n_in, nullptr, 0, nullptr, 0, nullptr, 0.f, nullptr, 0, W->n_in, m,
+                            W->ty, mode, c->act_a.p));
+    }
+    MvParams p = mv_store(act_layout(c->act_a.p, W->ty, mode.m_eff), y_dev, (int)W->n_out);
+    p.dump = dump;
+    return launch_matvec(c, W, p, mode, dump != nullptr);
+}
+
+}  // namespace
+
+// =========================================================== the C ABI
+
+extern "C" {
+
+int apk_init(apk_ctx **out, int device) {
+    if (!out) return fail(APK_ERR_INVALID_ARG, "apk_init: null out pointer");
+    *out = nullptr;
+    int n_dev = 0;
+    if (cudaGetDeviceCount(&n_dev) != cudaSuccess || n_dev == 0)
+        return fail(APK_DECLINE_NO_DEVICE, "no accelerator device");
+    if (device < 0) {
+        const char *lr = getenv("LOCAL_RANK");
+        device = lr ? atoi(lr) % n_dev : 0;
+    }
+    if (device >= n_dev) return fail(APK_ERR_INVALID_ARG, "device %d of %d", device, n_dev);
+    CUDA_TRY(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, device));
+    if (prop.major != 10)
+        return fail(APK_DECLINE_MISSING_CAPABILITY, "device is sm_%d%d; this library is built for sm_100a only",
+                    prop.major, prop.minor);
+    auto c = std::make_unique<apk_ctx>();
+    c->device = device;
+    c->n_sm = prop.multiProcessorCount;
+    c->smem_optin = (int)prop.sharedMemPerBlockOptin;
+    CUDA_TRY(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    CUDA_TRY(cudaEventCreate(&c->ev0));
+    CUDA_TRY(cudaEventCreate(&c->ev1));
+    CUDA_TRY(cudaMalloc((void **)&c->d_err, sizeof(int)));
+    CUDA_TRY(cudaMemset(c->d_err, 0, sizeof(int)));
+    CUDA_TRY(cudaMallocHost((void **)&c->h_err, sizeof(int)));
+    *c->h_err = 0;
+    APK_TRY(c->partials.ensure((size_t)c->n_sm * 2 * MAX_M_EFF * TILE_ROWS * sizeof(float), true));
+    APK_TRY(c->counters.ensure(65536 * sizeof(int), true));
+    APK_TRY(init_kernel_attrs(c.get()));
+    *out = c.release();
+    return APK_OK;
+}
+
+void apk_shutdown(apk_ctx *c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    if (c->stream) cudaStreamSynchronize(c->stream);
+    c->plan.reset();
+    c->mats.clear();
+    if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
+    for (DevBuf *b : {&c->staging, &c->partials, &c->counters, &c->x_dev, &c->y_dev, &c->act_a, &c->act_b, &c->misc, &c->dump})
+        b->release();
+    if (c->d_err) cudaFree(c->d_err);
+    if (c->h_err) cudaFreeHost(c->h_err);
+    if (c->ev0) cudaEventDestroy(c->ev0);
+    if (c->ev1) cudaEventDestroy(c->ev1);
+    if (c->stream) cudaStreamDestroy(c->stream);
+    delete c;
+}
+
+int apk_attach(apk_ctx *c, const void *host_base, size_t len) {
+    if (!c || !host_base || len == 0) return fail(APK_ERR_INVALID_ARG, "attach: null or empty mapping");
+    std::lock_guard<std::mutex> g(c->mu);
+    c->attached[{(const uint8_t *)host_base, len}]++;
+    return APK_OK;
+}
+
+int apk_detach(apk_ctx *c, const void *host_base, size_t len) {
+    if (!c || !host_base) return fail(APK_ERR_INVALID_ARG, "detach: null mapping");
+    std::lock_guard<std::mutex> g(c->mu);
+    auto it = c->attached.find({(const uint8_t *)host_base, len});
+    if (it == c->attached.end()) return fail(APK_DECLINE_INVALID_STATE, "detach: mapping was never attached");
+    if (--it->second > 0) return APK_OK;
+    c->attached.erase(it);
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    c->plan.reset();  // a plan may point at matrices about to go
+    const uint8_t *b = (const uint8_t *)host_base;
+    for (auto mi = c->mats.begin(); mi != c->mats.end();) {
+        bool hit = false;
+        for (auto &sp : mi->second->host_spans)
+            if (sp.first < b + len && sp.first + sp.second > b) hit = true;
+        if (hit) {
+            c->st.weight_bytes -= mi->second->bytes;
+            mi = c->mats.erase(mi);
+        } else {
+            ++mi;
+        }
+    }
+    return APK_OK;
+}
+
+int apk_is_attached(apk_ctx *c) {
+    if (!c) return 0;
+    std::lock_guard<std::mutex> g(c->mu);
+    return c->attached.empty() ? 0 : 1;
+}
+
+int apk_register_matrix(apk_ctx *c, const void *w, uint32_t ty, uint32_t n_out, uint32_t n_in) {
+    if (!c) return fail(APK_ERR_INVALID_ARG, "null context");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    DevMatrix *m;
+    return resolve_plain(c, "register", w, ty, n_out, n_in, SHARD_NONE, &m);
+}
+
+int apk_matvec_batch(apk_ctx *c, const apk_matvec_req *reqs, uint32_t n_reqs, uint32_t act_mode,
+                     float *const *ys) {
+    if (!c || (n_reqs && (!reqs || !ys))) return fail(APK_ERR_INVALID_ARG, "matvec_batch: null argument");
+    if (n_reqs == 0) return APK_OK;
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    const uint64_t t0 = now_ns();
+    size_t y_total = 0, x_max = 0;
+    std::vector<DevMatrix *> mats(n_reqs);
+    for (uint32_t i = 0; i < n_reqs; ++i) {
+        const apk_matvec_req &r = reqs[i];
+        APK_TRY(check_m(r.m));
+        if (!r.x || !ys[i]) return fail(APK_ERR_INVALID_ARG, "matvec: null x or y");
+        APK_TRY(resolve_plain(c, "matvec", r.w, r.ty, r.n_out, r.n_in, SHARD_NONE, &mats[i]));
+        y_total += (size_t)r.m * r.n_out;
+        x_max = std::max(x_max, (size_t)r.m * r.n_in);
+    }
+    APK_TRY(c->x_dev.ensure(x_max * sizeof(float)));
+    APK_TRY(c->y_dev.ensure(y_total * sizeof(float)));
+    size_t y_off = 0;
+    const float *last_x = nullptr;
+    uint32_t last_m = 0, last_n = 0, last_ty = 0;
+    std::vector<size_t> offs(n_reqs);
+    for (uint32_t i = 0; i < n_reqs; ++i) {
+        const apk_matvec_req &r = reqs[i];
+        // items that share x share one activation quantisation (quantmat/mod.rs:372-388)
+        const bool same = last_x == r.x && last_m == r.m && last_n == r.n_in && ke_of(last_ty) == ke_of(r.ty) &&
+                          (last_ty == APK_TY_Q4_K) == (r.ty == APK_TY_Q4_K);
+        if (!same)
+            CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, r.x, (size_t)r.m * r.n_in * sizeof(float), cudaMemcpyHostToDevice,
+                                     c->stream));
+        offs[i] = y_off;
+        APK_TRY(run_matvec_dev(c, mats[i], c->x_dev.as<float>(), r.m, act_mode, c->y_dev.as<float>() + y_off, same,
+                               nullptr));
+        y_off += (size_t)r.m * r.n_out;
+        last_x = r.x; last_m = r.m; last_n = r.n_in; last_ty = r.ty;
+    }
+    for (uint32_t i = 0; i < n_reqs; ++i)
+        CUDA_TRY(cudaMemcpyAsync(ys[i], c->y_dev.as<float>() + offs[i],
+                                 (size_t)reqs[i].m * reqs[i].n_out * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+    c->st.encode_ns += now_ns() - t0;
+    c->st.calls++;
+    return finish(c);
+}
+
+int apk_matvec(apk_ctx *c, const void *w, uint32_t ty, uint32_t n_in, uint32_t n_out, const float *x, uint32_t m,
+               uint32_t act_mode, float *y) {
+    apk_matvec_req r{ty, w, n_in, n_out, x, m};
+    float *ys[1] = {y};
+    return apk_matvec_batch(c, &r, 1, act_mode, ys);
+}
+
+int apk_debug_block_dots(apk_ctx *c, const void *w, uint32_t ty, uint32_t n_in, uint32_t n_out, const float *x,
+                         uint32_t m, int32_t *dots) {
+    if (!c || !x || !dots) return fail(APK_ERR_INVALID_ARG, "block_dots: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    APK_TRY(check_m(m));
+    DevMatrix *W;
+    APK_TRY(resolve_plain(c, "block_dots", w, ty, n_out, n_in, SHARD_NONE, &W));
+    const size_t nd = (size_t)m * n_out * (n_in / 32);
+    APK_TRY(c->x_dev.ensure((size_t)m * n_in * sizeof(float)));
+    APK_TRY(c->y_dev.ensure((size_t)m * n_out * sizeof(float)));
+    APK_TRY(c->dump.ensure(nd * sizeof(int32_t)));
+    CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, x, (size_t)m * n_in * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    CUDA_TRY(cudaMemsetAsync(c->dump.p, 0xff, nd * sizeof(int32_t), c->stream));
+    APK_TRY(run_matvec_dev(c, W, c->x_dev.as<float>(), m, APK_ACT_Q8, c->y_dev.as<float>(), false,
+                           c->dump.as<int32_t>()));
+    CUDA_TRY(cudaMemcpyAsync(dots, c->dump.p, nd * sizeof(int32_t), cudaMemcpyDeviceToHost, c->stream));
+    c->st.calls++;
+    return finish(c);
+}
+
+int apk_debug_q8_acts(apk_ctx *c, const float *x, uint32_t n, const float *gamma, float eps, float *d, float *sum,
+                      int8_t *q) {
+    if (!c || !x || !d || !sum || !q) return fail(APK_ERR_INVALID_ARG, "q8_acts: null argument");
+    if (n == 0 || n % 32) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "q8_acts: %u is not whole 32-element blocks", n);
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    const ActMode mode{0, 1};
+    const size_t ab = act_bytes(APK_TY_Q4_K, 1, n);
+    APK_TRY(c->x_dev.ensure((size_t)n * sizeof(float)));
+    APK_TRY(c->misc.ensure((size_t)n * sizeof(float)));
+    APK_TRY(c->act_a.ensure(ab));
+    CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, x, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    if (gamma) CUDA_TRY(cudaMemcpyAsync(c->misc.p, gamma, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    CUDA_TRY(cudaMemsetAsync(c->act_a.p, 0, ab, c->stream));
+    // the Q4_K flavour of the record carries the block sums as well
+    APK_TRY(launch_prep(c, c->x_dev.p, 0, (int)n, nullptr, 0, nullptr, 0, gamma ? c->misc.as<float>() : nullptr, eps,
+                        nullptr, 0, n, 1, APK_TY_Q4_K, mode, c->act_a.p));
+    std::vector<uint8_t> host(ab);
+    CUDA_TRY(cudaMemcpyAsync(host.data(), c->act_a.p, ab, cudaMemcpyDeviceToHost, c->stream));
+    c->st.calls++;
+    APK_TRY(finish(c));
+    const int ke = 512, kt = 16, rec = ke + ke / 4;
+    for (uint32_t b = 0; b < n / 32; ++b) {
+        const uint8_t *r = host.data() + (size_t)(b / kt) * rec;
+        const int bl = (int)(b % kt);
+        memcpy(q + (size_t)b * 32, r + bl * 32, 32);
+        memcpy(&d[b], r + ke + bl * 4, 4);
+        memcpy(&sum[b], r + ke + kt * 4 + bl * 4, 4);
+    }
+    return APK_OK;
+}
+
+int apk_ffn(apk_ctx *c, const apk_ffn_req *r, float *y) {
+    if (!c || !r || !y || !r->x) return fail(APK_ERR_INVALID_ARG, "ffn: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    const uint64_t t0 = now_ns();
+    APK_TRY(check_m(r->m));
+    if (r->gate_ty != r->up_ty)
+        return fail(APK_DECLINE_UNSUPPORTED_TYPE, "ffn: gate (%u) and up (%u) must share a type", r->gate_ty, r->up_ty);
+    if (c->world != 1) return fail(APK_DECLINE_INVALID_STATE, "ffn: stand-alone FFN runs on an unsharded context");
+    DevMatrix *GU, *D;
+    uint32_t fl;
+    APK_TRY(resolve_gateup(c, r->gate_ty, r->gate_w, r->up_w, r->hidden, r->ffn, &GU, &fl));
+    APK_TRY(resolve_plain(c, "ffn down", r->down_w, r->down_ty, r->hidden, r->ffn, SHARD_NONE, &D));
+    const uint32_t m = r->m;
+    const ActMode q8{0, (int)m};
+    const ActMode dmode = resolve_mode(APK_ACT_AUTO, m);  // w_down.matmul(&gate, m): model/moe.rs:128
+    APK_TRY(c->x_dev.ensure((size_t)m * r->hidden * sizeof(float)));
+    APK_TRY(c->y_dev.ensure((size_t)m * r->hidden * sizeof(float)));
+    APK_TRY(c->act_a.ensure(act_bytes(GU->ty, q8.m_eff, r->hidden)));
+    APK_TRY(c->act_b.ensure(act_bytes(D->ty, dmode.m_eff, r->ffn)));
+    CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, r->x, (size_t)m * r->hidden * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    APK_TRY(launch_prep(c, c->x_dev.p, 0, (int)r->hidden, nullptr, 0, nullptr, 0, nullptr, 0.f, nullptr, 0, r->hidden,
+                        m, GU->ty, q8, c->act_a.p));
+    MvParams p{};
+    p.act = act_layout(c->act_a.p, GU->ty, q8.m_eff);
+    p.epi = EPI_SWIGLU;
+    p.act_next = act_layout(c->act_b.p, D->ty, dmode.m_eff);
+    p.next_two_level = dmode.two_level;
+    p.next_need_sum = D->ty == APK_TY_Q4_K;
+    p.ffn = (int)r->ffn;
+    APK_TRY(launch_matvec(c, GU, p, q8));
+    APK_TRY(launch_matvec(c, D, mv_store(act_layout(c->act_b.p, D->ty, dmode.m_eff), c->y_dev.as<float>(), (int)r->hidden), dmode));
+    CUDA_TRY(cudaMemcpyAsync(y, c->y_dev.p, (size_t)m * r->hidden * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+    c->st.encode_ns += now_ns() - t0;
+    c->st.calls++;
+    return finish(c);
+}
+
+int apk_attn_in(apk_ctx *c, const apk_attn_in_req *r, float *q, float *k, float *v) {
+    if (!c || !r || !q || !k || !v || !r->x || !r->rope) return fail(APK_ERR_INVALID_ARG, "attn_in: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    const uint64_t t0 = now_ns();
+    APK_TRY(check_m(r->m));
+    if (r->head_dim != TILE_ROWS)
+        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "attn_in: head_dim %u (the fused epilogue is written for 128)", r->head_dim);
+    if (r->rot_dim > r->head_dim || r->rot_dim % 2)
+        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "attn_in: rot_dim %u", r->rot_dim);
+    if (c->world != 1) return fail(APK_DECLINE_INVALID_STATE, "attn_in: stand-alone call runs on an unsharded context");
+    const uint32_t m = r->m, H = r->hidden, nq = r->n_heads * r->head_dim, nkv = r->n_kv_heads * r->head_dim;
+    const uint32_t half = r->rot_dim / 2, ld = nq + 2 * nkv;
+    DevMatrix *W;
+    APK_TRY(resolve_qkv(c, r->ty, r->wq, r->wk, r->wv, H, nq, nkv, &W));
+    const ActMode q8{0, (int)m};
+    APK_TRY(c->x_dev.ensure((size_t)m * H * sizeof(float)));
+    APK_TRY(c->y_dev.ensure((size_t)m * ld * sizeof(float)));
+    APK_TRY(c->act_a.ensure(act_bytes(W->ty, q8.m_eff, H)));
+    // misc: gamma[H] | q_norm[128] | k_norm[128] | rope[m][half][2]
+    const size_t o_qn = H, o_kn = H + 128, o_rope = H + 256;
+    APK_TRY(c->misc.ensure((o_rope + (size_t)m * half * 2) * sizeof(float)));
+    float *misc = c->misc.as<float>();
+    CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, r->x, (size_t)m * H * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    if (r->gamma) CUDA_TRY(cudaMemcpyAsync(misc, r->gamma, H * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    if (r->q_norm) CUDA_TRY(cudaMemcpyAsync(misc + o_qn, r->q_norm, 128 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    if (r->k_norm) CUDA_TRY(cudaMemcpyAsync(misc + o_kn, r->k_norm, 128 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    if (half) CUDA_TRY(cudaMemcpyAsync(misc + o_rope, r->rope, (size_t)m * half * 2 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    APK_TRY(launch_prep(c, c->x_dev.p, 0, (int)H, nullptr, 0, nullptr, 0, r->gamma ? misc : nullptr, r->eps, nullptr, 0,
+                        H, m, W->ty, q8, c->act_a.p));
+    MvParams p{};
+    p.act = act_layout(c->act_a.p, W->ty, q8.m_eff);
+    p.epi = EPI_QKV_ROPE;
+    p.y = c->y_dev.as<float>();
+    p.ldy = (int)ld;
+    p.n_q_tiles = (int)r->n_heads;
+    p.n_k_tiles = (int)r->n_kv_heads;
+    p.q_norm = r->q_norm ? misc + o_qn : nullptr;
+    p.k_norm = r->k_norm ? misc + o_kn : nullptr;
+    p.eps = r->eps;
+    p.rope = misc + o_rope;
+    p.half = (int)half;
+    APK_TRY(launch_matvec(c, W, p, q8));
+    const float *yd = c->y_dev.as<float>();
+    CUDA_TRY(cudaMemcpy2DAsync(q, nq * sizeof(float), yd, ld * sizeof(float), nq * sizeof(float), m, cudaMemcpyDeviceToHost, c->stream));
+    CUDA_TRY(cudaMemcpy2DAsync(k, nkv * sizeof(float), yd + nq, ld * sizeof(float), nkv * sizeof(float), m, cudaMemcpyDeviceToHost, c->stream));
+    CUDA_TRY(cudaMemcpy2DAsync(v, nkv * sizeof(float), yd + nq + nkv, ld * sizeof(float), nkv * sizeof(float), m, cudaMemcpyDeviceToHost, c->stream));
+    c->st.encode_ns += now_ns() - t0;
+    c->st.calls++;
+    return finish(c);
+}
+
+void apk_stats(apk_ctx *c, apk_stats_t *out) {
+    if (!c || !out) return;
+    std::lock_guard<std::mutex> g(c->mu);
+    *out = c->st;
+}
+
+const char *apk_last_error(apk_ctx *) { return g_last_error.c_str(); }
+
+int apk_dist_unique_id(void *id_out) {
+    if (!id_out) return fail(APK_ERR_INVALID_ARG, "null id buffer");
+    if (!g_nccl.load()) return fail(APK_ERR_NCCL, "libnccl.so.2 could not be loaded: %s", dlerror());
+    Nccl::uid_t id;
+    const int rc = g_nccl.GetUniqueId(&id);
+    if (rc) return fail(APK_ERR_NCCL, "ncclGetUniqueId: %s", g_nccl.GetErrorString(rc));
+    memcpy(id_out, &id, sizeof id);
+    return APK_OK;
+}
+
+int apk_dist_init(apk_ctx *c, int rank, int world, const void *unique_id) {
+    if (!c || !unique_id || world < 1 || rank < 0 || rank >= world)
+        return fail(APK_ERR_INVALID_ARG, "dist_init: bad rank %d / world %d", rank, world);
+    std::lock_guard<std::mutex> g(c->mu);
+    if (!c->mats.empty()) return fail(APK_DECLINE_INVALID_STATE, "dist_init must precede the first weight upload");
+    CUDA_TRY(cudaSetDevice(c->device));
+    if (world > 1) {
+        if (!g_nccl.load()) return fail(APK_ERR_NCCL, "libnccl.so.2 could not be loaded");
+        Nccl::uid_t id;
+        memcpy(&id, unique_id, sizeof id);
+        const int rc = g_nccl.CommInitRank(&c->comm, world, id, rank);
+        if (rc) return fail(APK_ERR_NCCL, "ncclCommInitRank: %s", g_nccl.GetErrorString(rc));
+    }
+    c->rank = rank;
+    c->world = world;
+    return APK_OK;
+}
+
+}  // extern "C"
+
+#include "decode.inl"

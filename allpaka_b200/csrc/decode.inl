@@ -1,0 +1,349 @@
+// Whole-token decode: the per-layer call order of the reference
+// (crates/allpaka-model/src/model/decode.rs:435-591, 755-777; finish_hidden
+// 594-602) as one captured CUDA graph, replayed per token.  Included at the end
+// of apk_b200.cu (same translation unit).
+//
+// Per layer (m tokens, all on the GPU):
+//   prep    h = rmsnorm(x, attn_norm) -> Q8 blocks
+//   matvec  [Q|K|V] rows, epilogue: per-head norm + NeoX RoPE          -> qkv
+//   prep    attention-core stand-in: the roped Q slice is the core's output
+//   matvec  wo, epilogue x += .           (tensor parallel: partial sums -> all-reduce,
+//                                          the add moves into the next prep)
+//   prep    h = rmsnorm(x, ffn_norm) -> Q8 blocks
+//   matvec  gate/up interleaved, epilogue swiglu -> blocks for `down`
+//   matvec  down, epilogue x += .
+// then rmsnorm(x, output_norm) + LM head (+ argmax).
+
+namespace {
+
+__global__ void __launch_bounds__(1024) argmax_rows_kernel(const float *logits, int vocab_l, int world, int m,
+                                                           uint32_t *out) {
+    // logits laid out [rank][m][vocab_l]; token = blockIdx.x.  Ties go to the
+    // higher index, as the CPU greedy pick does (model/decode.rs:604-608).
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int tok = blockIdx.x;
+    float best = -INFINITY;
+    int bi = -1;
+    const int vocab = vocab_l * world;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const int r = i / vocab_l, j = i % vocab_l;
+        const float v = logits[((size_t)r * m + tok) * vocab_l + j];
+        if (v > best || (v == best && i > bi) || bi < 0) { best = v; bi = i; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (oi >= 0 && (bi < 0 || ov > best || (ov == best && oi > bi))) { best = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        best = sv[threadIdx.x];
+        bi = si[threadIdx.x];
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (oi >= 0 && (bi < 0 || ov > best || (ov == best && oi > bi))) { best = ov; bi = oi; }
+        }
+        if (threadIdx.x == 0) out[tok] = (uint32_t)(bi < 0 ? 0 : bi);
+    }
+}
+
+int decline_decode(apk_ctx *c, int code, const char *fmt, ...) {
+    char buf[400];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof buf, fmt, ap);
+    va_end(ap);
+    c->st.decode_declines++;
+    return fail(code, "stage=backend-decode reason=%s", buf);
+}
+
+bool plan_matches(const Plan *p, const apk_token_req *r) {
+    return p && p->layers_key == r->layers && p->n_layers == r->n_layers && p->output_key == r->output.w &&
+           p->hidden == r->hidden && p->head_dim == r->head_dim && p->n_heads == r->n_heads &&
+           p->n_kv_heads == r->n_kv_heads && p->rot_dim == r->rot_dim && p->vocab == r->output.n_out &&
+           p->eps == r->eps;
+}
+
+int nccl_allreduce(apk_ctx *c, float *buf, size_t n) {
+    const int rc = g_nccl.AllReduce(buf, buf, n, NCCL_FLOAT32, NCCL_SUM, c->comm, c->stream);
+    if (rc) return fail(APK_ERR_NCCL, "ncclAllReduce: %s", g_nccl.GetErrorString(rc));
+    return APK_OK;
+}
+
+int build_plan(apk_ctx *c, const apk_token_req *r) {
+    c->plan.reset();
+    auto P = std::make_unique<Plan>();
+    const uint32_t H = r->hidden, nq = r->n_heads * r->head_dim, nkv = r->n_kv_heads * r->head_dim;
+    if (r->n_layers == 0 || !r->layers || !r->output.w || !r->output_norm)
+        return decline_decode(c, APK_ERR_INVALID_ARG, "empty layer list or missing output head");
+    if (r->head_dim != TILE_ROWS) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "head_dim %u (fused QKV epilogue is written for 128)", r->head_dim);
+    if (r->rot_dim > r->head_dim || r->rot_dim % 2) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "rot_dim %u", r->rot_dim);
+    const uint32_t ffn = r->layers[0].gate.n_out;
+    P->layers_key = r->layers; P->n_layers = r->n_layers; P->output_key = r->output.w;
+    P->hidden = H; P->head_dim = r->head_dim; P->n_heads = r->n_heads; P->n_kv_heads = r->n_kv_heads;
+    P->rot_dim = r->rot_dim; P->vocab = r->output.n_out; P->eps = r->eps; P->ffn = ffn;
+    if (P->vocab % c->world) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "vocab %u does not split over %d ranks", P->vocab, c->world);
+    P->nq_l = nq / c->world; P->nkv_l = nkv / c->world; P->vocab_l = P->vocab / c->world;
+
+    // norm weights: one device array
+    const size_t per_layer = 2 * (size_t)H + 2 * 128;
+    std::vector<float> norms(per_layer * r->n_layers + H, 0.f);
+    for (uint32_t l = 0; l < r->n_layers; ++l) {
+        const apk_token_layer &tl = r->layers[l];
+        if (!tl.attn_norm || !tl.ffn_norm) return decline_decode(c, APK_ERR_INVALID_ARG, "layer %u: missing norm weights", l);
+        float *b = norms.data() + per_layer * l;
+        memcpy(b, tl.attn_norm, H * sizeof(float));
+        memcpy(b + H, tl.ffn_norm, H * sizeof(float));
+        if (tl.q_norm) memcpy(b + 2 * H, tl.q_norm, 128 * sizeof(float));
+        if (tl.k_norm) memcpy(b + 2 * H + 128, tl.k_norm, 128 * sizeof(float));
+    }
+    memcpy(norms.data() + per_layer * r->n_layers, r->output_norm, H * sizeof(float));
+    APK_TRY(P->norms.ensure(norms.size() * sizeof(float)));
+    CUDA_TRY(cudaMemcpy(P->norms.p, norms.data(), norms.size() * sizeof(float), cudaMemcpyHostToDevice));
+
+    P->L.resize(r->n_layers);
+    uint32_t max_ty_q4 = 0;
+    for (uint32_t l = 0; l < r->n_layers; ++l) {
+        const apk_token_layer &tl = r->layers[l];
+        PlanLayer &pl = P->L[l];
+        if (tl.wq.ty != tl.wk.ty || tl.wq.ty != tl.wv.ty)
+            return decline_decode(c, APK_DECLINE_UNSUPPORTED_TYPE, "layer %u: wq/wk/wv types differ", l);
+        if (tl.gate.ty != tl.up.ty) return decline_decode(c, APK_DECLINE_UNSUPPORTED_TYPE, "layer %u: gate/up types differ", l);
+        if (tl.wq.n_out != nq || tl.wk.n_out != nkv || tl.wv.n_out != nkv || tl.wo.n_out != H || tl.gate.n_out != ffn ||
+            tl.up.n_out != ffn || tl.down.n_out != H)
+            return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "layer %u: projection shapes disagree with the request", l);
+        int rc;
+        if ((rc = resolve_qkv(c, tl.wq.ty, tl.wq.w, tl.wk.w, tl.wv.w, H, nq, nkv, &pl.qkv))) { c->st.decode_declines++; return rc; }
+        if ((rc = resolve_plain(c, "attn wo", tl.wo.w, tl.wo.ty, H, nq, SHARD_K, &pl.wo))) { c->st.decode_declines++; return rc; }
+        if ((rc = resolve_gateup(c, tl.gate.ty, tl.gate.w, tl.up.w, H, ffn, &pl.gateup, &P->ffn_l))) { c->st.decode_declines++; return rc; }
+        if ((rc = resolve_plain(c, "ffn down", tl.down.w, tl.down.ty, H, ffn, SHARD_K, &pl.down))) { c->st.decode_declines++; return rc; }
+        const float *b = P->norms.as<float>() + per_layer * l;
+        pl.attn_norm = b;
+        pl.ffn_norm = b + H;
+        pl.q_norm = tl.q_norm ? b + 2 * H : nullptr;
+        pl.k_norm = tl.k_norm ? b + 2 * H + 128 : nullptr;
+        if (tl.wq.ty == APK_TY_Q4_K || tl.wo.ty == APK_TY_Q4_K || tl.gate.ty == APK_TY_Q4_K || tl.down.ty == APK_TY_Q4_K)
+            max_ty_q4 = 1;
+    }
+    {
+        int rc;
+        if ((rc = resolve_plain(c, "output", r->output.w, r->output.ty, P->vocab, H, SHARD_ROWS, &P->head))) { c->st.decode_declines++; return rc; }
+    }
+    P->out_norm = P->norms.as<float>() + per_layer * r->n_layers;
+
+    const uint32_t M = APK_MAX_M, ldq = P->nq_l + 2 * P->nkv_l;
+    const uint32_t big = APK_TY_Q4_K;  // the larger record flavour bounds every buffer
+    (void)max_ty_q4;
+    APK_TRY(P->xin.ensure((size_t)M * H * 4));
+    APK_TRY(P->x[0].ensure((size_t)M * H * 4));
+    APK_TRY(P->x[1].ensure((size_t)M * H * 4));
+    APK_TRY(P->qkv.ensure((size_t)M * ldq * 4));
+    APK_TRY(P->yp.ensure((size_t)M * H * 4));
+    APK_TRY(P->act_h.ensure(act_bytes(big, 2 * M, H)));
+    APK_TRY(P->act_q.ensure(act_bytes(big, 2 * M, P->nq_l)));
+    APK_TRY(P->act_d.ensure(act_bytes(big, 2 * M, P->ffn_l)));
+    APK_TRY(P->logits.ensure((size_t)M * P->vocab_l * 4));
+    if (c->world > 1) APK_TRY(P->logits_all.ensure((size_t)M * P->vocab * 4));
+    APK_TRY(P->amax.ensure(M * sizeof(uint32_t)));
+    APK_TRY(P->rope.ensure((size_t)M * (r->rot_dim / 2 + 1) * 2 * 4));
+    c->plan = std::move(P);
+    return APK_OK;
+}
+
+// Enqueue one token's work on the stream (called under capture).
+int enqueue_token(apk_ctx *c, Plan *P, uint32_t m, int argmax, int *n_launches) {
+    const uint32_t H = P->hidden, ldq = P->nq_l + 2 * P->nkv_l;
+    const uint64_t l0 = c->st.launches;
+    const bool tp = c->world > 1;
+    const ActMode q8{0, (int)m};
+    const ActMode autom = resolve_mode(APK_ACT_AUTO, m);
+    int cur = 0;
+    CUDA_TRY(cudaMemcpyAsync(P->x[0].p, P->xin.p, (size_t)m * H * 4, cudaMemcpyDeviceToDevice, c->stream));
+    bool pending_add = false;  // tensor parallel: yp holds a combined delta not yet added to x
+    auto prep_norm = [&](const float *gamma, uint32_t cty, ActMode mode) -> int {
+        float *xc = P->x[cur].as<float>();
+        if (pending_add) {
+            float *xn = P->x[cur ^ 1].as<float>();
+            APK_TRY(launch_prep(c, xc, 0, (int)H, P->yp.as<float>(), (int)H, xn, (int)H, gamma, P->eps, nullptr, 0, H, m,
+                                cty, mode, P->act_h.p));
+            cur ^= 1;
+            pending_add = false;
+            return APK_OK;
+        }
+        return launch_prep(c, xc, 0, (int)H, nullptr, 0, nullptr, 0, gamma, P->eps, nullptr, 0, H, m, cty, mode, P->act_h.p);
+    };
+    auto residual_matvec = [&](DevMatrix *W, const ActLayout &act, ActMode mode) -> int {
+        MvParams p{};
+        p.act = act;
+        if (tp) {
+            p.epi = EPI_STORE;
+            p.y = P->yp.as<float>();
+            p.ldy = (int)H;
+            APK_TRY(launch_matvec(c, W, p, mode));
+            APK_TRY(nccl_allreduce(c, P->yp.as<float>(), (size_t)m * H));
+            pending_add = true;
+        } else {
+            p.epi = EPI_ADD;
+            p.y = P->x[cur].as<float>();
+            p.ldy = (int)H;
+            p.resid = P->x[cur].as<float>();
+            p.ldr = (int)H;
+            APK_TRY(launch_matvec(c, W, p, mode));
+        }
+        return APK_OK;
+    };
+    for (uint32_t l = 0; l < P->n_layers; ++l) {
+        PlanLayer &L = P->L[l];
+        APK_TRY(prep_norm(L.attn_norm, L.qkv->ty, q8));
+        {
+            MvParams p{};
+            p.act = act_layout(P->act_h.p, L.qkv->ty, q8.m_eff);
+            p.epi = EPI_QKV_ROPE;
+            p.y = P->qkv.as<float>();
+            p.ldy = (int)ldq;
+            p.n_q_tiles = (int)(P->nq_l / TILE_ROWS);
+            p.n_k_tiles = (int)(P->nkv_l / TILE_ROWS);
+            p.q_norm = L.q_norm;
+            p.k_norm = L.k_norm;
+            p.eps = P->eps;
+            p.rope = P->rope.as<float>();
+            p.half = (int)(P->rot_dim / 2);
+            APK_TRY(launch_matvec(c, L.qkv, p, q8));
+        }
+        // attention core stand-in: its output is the roped Q slice; wo.matmul(attn_out, m)
+        APK_TRY(launch_prep(c, P->qkv.p, 0, (int)ldq, nullptr, 0, nullptr, 0, nullptr, 0.f, nullptr, 0, P->nq_l, m,
+                            L.wo->ty, autom, P->act_q.p));
+        APK_TRY(residual_matvec(L.wo, act_layout(P->act_q.p, L.wo->ty, autom.m_eff), autom));
+        APK_TRY(prep_norm(L.ffn_norm, L.gateup->ty, q8));
+        {
+            MvParams p{};
+            p.act = act_layout(P->act_h.p, L.gateup->ty, q8.m_eff);
+            p.epi = EPI_SWIGLU;
+            p.act_next = act_layout(P->act_d.p, L.down->ty, autom.m_eff);
+            p.next_two_level = autom.two_level;
+            p.next_need_sum = L.down->ty == APK_TY_Q4_K;
+            p.ffn = (int)P->ffn_l;
+            APK_TRY(launch_matvec(c, L.gateup, p, q8));
+        }
+        APK_TRY(residual_matvec(L.down, act_layout(P->act_d.p, L.down->ty, autom.m_eff), autom));
+    }
+    // finish_hidden: rmsnorm + output.matmul(x, m) (QuantMat::matmul: Q8 at m == 1, f32 dots above)
+    APK_TRY(prep_norm(P->out_norm, P->head->ty, autom));
+    APK_TRY(launch_matvec(c, P->head, mv_store(act_layout(P->act_h.p, P->head->ty, autom.m_eff), P->logits.as<float>(), (int)P->vocab_l), autom));
+    const float *lg = P->logits.as<float>();
+    if (tp) {
+        const int rc = g_nccl.AllGather(P->logits.p, P->logits_all.p, (size_t)m * P->vocab_l, NCCL_FLOAT32, c->comm, c->stream);
+        if (rc) return fail(APK_ERR_NCCL, "ncclAllGather: %s", g_nccl.GetErrorString(rc));
+        lg = P->logits_all.as<float>();
+    }
+    if (argmax) {
+        argmax_rows_kernel<<<m, 1024, 0, c->stream>>>(lg, (int)P->vocab_l, c->world, (int)m, P->amax.as<uint32_t>());
+        CUDA_TRY(cudaGetLastError());
+        c->st.launches++;
+    }
+    *n_launches = (int)(c->st.launches - l0);
+    return APK_OK;
+}
+
+int ensure_graph(apk_ctx *c, const apk_token_req *r) {
+    if (!plan_matches(c->plan.get(), r)) APK_TRY(build_plan(c, r));
+    Plan *P = c->plan.get();
+    const int am = r->argmax ? 1 : 0;
+    if (P->exec[r->m][am]) return APK_OK;
+    cudaGraph_t graph = nullptr;
+    const uint64_t launches_before = c->st.launches;
+    CUDA_TRY(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    int n_launch = 0;
+    const int rc = enqueue_token(c, P, r->m, am, &n_launch);
+    const cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+    c->st.launches = launches_before;  // capture launched nothing
+    if (rc) {
+        if (graph) cudaGraphDestroy(graph);
+        return rc;
+    }
+    if (e != cudaSuccess) return fail(APK_ERR_CUDA, "graph capture: %s", cudaGetErrorString(e));
+    const cudaError_t ie = cudaGraphInstantiate(&P->exec[r->m][am], graph, 0);
+    cudaGraphDestroy(graph);
+    if (ie != cudaSuccess) return fail(APK_ERR_CUDA, "graph instantiate: %s", cudaGetErrorString(ie));
+    P->launches[r->m][am] = n_launch;
+    return APK_OK;
+}
+
+int validate_token_req(apk_ctx *c, const apk_token_req *r) {
+    if (!r) return fail(APK_ERR_INVALID_ARG, "decode: null request");
+    c->st.decode_attempts++;
+    if (r->m == 0 || r->m > APK_MAX_M) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "m = %u is outside 1..8", r->m);
+    if (r->attn_core != APK_ATTN_IDENTITY)
+        return decline_decode(c, APK_DECLINE_MISSING_CAPABILITY, "only the identity attention core is built into this library");
+    if (!r->x || (r->rot_dim && !r->rope)) return decline_decode(c, APK_ERR_INVALID_ARG, "missing input rows or rope table");
+    return APK_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int apk_decode_token(apk_ctx *c, const apk_token_req *r, apk_token_out *out) {
+    if (!c || !out) return fail(APK_ERR_INVALID_ARG, "decode: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    APK_TRY(validate_token_req(c, r));
+    if (r->argmax ? !out->argmax : !out->logits) return decline_decode(c, APK_ERR_INVALID_ARG, "missing output buffer");
+    const uint64_t t0 = now_ns();
+    APK_TRY(ensure_graph(c, r));
+    Plan *P = c->plan.get();
+    const uint32_t m = r->m, H = P->hidden;
+    CUDA_TRY(cudaMemcpyAsync(P->xin.p, r->x, (size_t)m * H * 4, cudaMemcpyHostToDevice, c->stream));
+    if (r->rot_dim)
+        CUDA_TRY(cudaMemcpyAsync(P->rope.p, r->rope, (size_t)m * (r->rot_dim / 2) * 2 * 4, cudaMemcpyHostToDevice, c->stream));
+    CUDA_TRY(cudaGraphLaunch(P->exec[m][r->argmax ? 1 : 0], c->stream));
+    c->st.launches += P->launches[m][r->argmax ? 1 : 0];
+    std::vector<float> gathered;
+    if (r->argmax) {
+        CUDA_TRY(cudaMemcpyAsync(out->argmax, P->amax.p, m * sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
+    } else if (c->world == 1 || m == 1) {
+        const void *src = c->world == 1 ? P->logits.p : P->logits_all.p;
+        CUDA_TRY(cudaMemcpyAsync(out->logits, src, (size_t)m * P->vocab * 4, cudaMemcpyDeviceToHost, c->stream));
+    } else {
+        gathered.resize((size_t)m * P->vocab);
+        CUDA_TRY(cudaMemcpyAsync(gathered.data(), P->logits_all.p, gathered.size() * 4, cudaMemcpyDeviceToHost, c->stream));
+    }
+    c->st.encode_ns += now_ns() - t0;
+    c->st.calls++;
+    APK_TRY(finish(c));
+    if (!gathered.empty())  // [rank][m][vocab_l] -> [m][vocab]
+        for (int rk = 0; rk < c->world; ++rk)
+            for (uint32_t i = 0; i < m; ++i)
+                memcpy(out->logits + (size_t)i * P->vocab + (size_t)rk * P->vocab_l,
+                       gathered.data() + ((size_t)rk * m + i) * P->vocab_l, (size_t)P->vocab_l * 4);
+    c->st.decode_successes++;
+    return APK_OK;
+}
+
+int apk_decode_replay(apk_ctx *c, const apk_token_req *r, uint32_t iters, float *elapsed_ms) {
+    if (!c || !elapsed_ms) return fail(APK_ERR_INVALID_ARG, "replay: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    APK_TRY(validate_token_req(c, r));
+    APK_TRY(ensure_graph(c, r));
+    Plan *P = c->plan.get();
+    const int am = r->argmax ? 1 : 0;
+    CUDA_TRY(cudaMemcpyAsync(P->xin.p, r->x, (size_t)r->m * P->hidden * 4, cudaMemcpyHostToDevice, c->stream));
+    if (r->rot_dim)
+        CUDA_TRY(cudaMemcpyAsync(P->rope.p, r->rope, (size_t)r->m * (r->rot_dim / 2) * 2 * 4, cudaMemcpyHostToDevice, c->stream));
+    CUDA_TRY(cudaStreamSynchronize(c->stream));
+    CUDA_TRY(cudaEventRecord(c->ev0, c->stream));
+    for (uint32_t i = 0; i < iters; ++i) CUDA_TRY(cudaGraphLaunch(P->exec[r->m][am], c->stream));
+    CUDA_TRY(cudaEventRecord(c->ev1, c->stream));
+    c->st.launches += (uint64_t)iters * P->launches[r->m][am];
+    c->st.calls++;
+    APK_TRY(finish(c));
+    CUDA_TRY(cudaEventElapsedTime(elapsed_ms, c->ev0, c->ev1));
+    c->st.decode_successes++;
+    return APK_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,718 @@
+// Device code of the B200 decode dequant-matvec path.
+//
+// Data layout in HBM ("tiled stream").  A [n_out, n_in] matrix is cut into
+// tiles of 128 output rows; a tile's K extent is cut into K-steps of 256
+// elements (Q8_0: 8 blocks) or 512 elements (Q4_K: 2 super-blocks).  One
+// (tile, K-step) "unit" is ONE contiguous span of at most 36 KiB that a single
+// bulk async copy (cp.async.bulk + mbarrier complete_tx) brings into shared
+// memory.  Inside a unit the 16-byte chunks are ordered [chunk][row group of
+// 32][lane], so lane l of a warp reads row (group*32 + l) with conflict-free
+// 16-byte shared loads and every activation load is a warp-wide broadcast.
+// The repack is a pure permutation of the GGUF blocks (zero rows pad the last
+// tile): the int8 / 4-bit quants and the f16 scales are untouched.
+//
+//   Q8_0 unit with kb blocks:  quants  [b][half][rg][lane][16 B]   kb*4096 B
+//                              scales  [b][row 0..127] f16         kb*256  B
+//   Q4_K unit with ns super-blocks: [sb][chunk 0..8][rg][lane][16 B], chunk 0
+//        = {d, dmin, scales[12]}, chunks 1..8 = qs[16*(c-1) ..]   ns*18432 B
+//
+// Work split ("stream-K"): the flat unit sequence of the whole matrix is cut
+// into equal contiguous ranges, one per CTA (one CTA per SM), so every SM
+// streams the same number of bytes regardless of n_out.  A tile whose units
+// straddle CTAs is finished by the last CTA to arrive, which sums the
+// partials in a fixed order (deterministic; no float atomics, no waiting).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace apk {
+
+constexpr int TILE_ROWS = 128;
+constexpr int Q8_KT = 8;             // Q8_0 blocks per K-step (256 elements)
+constexpr int Q8_BLOCK_UNIT = 4352;  // 128 rows * 34 B
+constexpr int Q4_SB_UNIT = 18432;    // 128 rows * 144 B
+constexpr int Q4_KT_SB = 2;          // Q4_K super-blocks per K-step (512 elements)
+constexpr int STAGE_W_BYTES = 36864; // max(8*4352, 2*18432)
+constexpr int N_CONSUMER_WARPS = 8;
+constexpr int N_CONSUMERS = N_CONSUMER_WARPS * 32;
+constexpr int MV_THREADS = N_CONSUMERS + 32;
+constexpr int MAX_M_EFF = 16;
+constexpr int MAX_STAGES = 8;
+constexpr int TY_Q8_0 = 8;
+constexpr int TY_Q4_K = 12;
+
+// Error words written by kernels (never a trap): which bounded wait gave up.
+constexpr int ERRW_PRODUCER_TIMEOUT = 1;
+constexpr int ERRW_CONSUMER_TIMEOUT = 2;
+
+// Spin budget of one mbarrier wait, in SM clock cycles (~2 s).
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+
+enum Epilogue : int {
+    EPI_STORE = 0,   // y[m][row] = v
+    EPI_ADD = 1,     // y[m][row] = resid[m][row] + v   (residual stream update)
+    EPI_QKV_ROPE = 2,// tile = one head: optional per-head RMSNorm, NeoX RoPE on Q and K heads
+    EPI_SWIGLU = 3,  // tile = 64 gate rows + 64 up rows: act = silu(g)*u, optionally packed for `down`
+};
+
+// Prepared activations as the matvec kernel streams them: per K-step of `ke`
+// elements one record {q[m_eff][ke] i8, d[m_eff][ke/32] f32, sum[m_eff][ke/32] f32}.
+struct ActLayout {
+    uint8_t *base;
+    int ke;        // elements per K-step: 256 (Q8_0 consumer) or 512 (Q4_K consumer)
+    int m_eff;     // rows in the record (2 per token in two-level mode)
+    __host__ __device__ int rec_bytes() const { return m_eff * (ke + ke / 4); }
+    __host__ __device__ size_t total_bytes(int n_in) const {
+        return (size_t)((n_in + ke - 1) / ke) * rec_bytes();
+    }
+};
+
+struct MvParams {
+    const uint8_t *W;   // tiled stream
+    ActLayout act;      // prepared activations (m_eff rows)
+    int ty;
+    int n_out, nb;      // real rows; 32-element blocks per row
+    int n_tiles, KS;    // tiles; K-steps per tile
+    uint32_t tile_bytes;
+    int n_stages;
+    int m_out;          // tokens written by the epilogue (m_eff, or m_eff/2 in two-level mode)
+    int two_level;
+    float *partials;    // [gridDim.x][2][MAX_M_EFF][128]
+    int *counters;      // [n_tiles], zero between launches
+    int *err;           // error word
+    int32_t *dump;      // optional [m_eff][n_out][nb] int32 block dots
+    // epilogue
+    int epi;
+    float *y; int ldy;
+    const float *resid; int ldr;
+    // EPI_QKV_ROPE
+    int n_q_tiles, n_k_tiles;          // tiles (heads) that are Q, then K; the rest are V
+    const float *q_norm, *k_norm;      // optional [128]
+    float eps;
+    const float *rope; int half;       // [m][half][2] (sin, cos)
+    // EPI_SWIGLU
+    float *act_f32; int ld_act;        // optional f32 swiglu rows [m][ffn]
+    ActLayout act_next;                // optional packed activations for the down projection
+    int next_two_level, next_need_sum;
+    int ffn;                           // real ffn rows (gate rows)
+};
+
+// ------------------------------------------------------------------ PTX glue
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fence_mbar_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Wait for a phase with a cycle budget.  false = gave up (caller records it).
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    }
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+// 1-D bulk async copy global -> shared, completion counted on an mbarrier.
+// dst, src 16-byte aligned; bytes a multiple of 16.
+__device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t bytes, uint64_t *bar,
+                                         uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(dst)),
+        "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(N_CONSUMERS) : "memory"); }
+
+__device__ __forceinline__ int dot32(const int4 &w0, const int4 &w1, const int4 &x0, const int4 &x1) {
+    int s = __dp4a(w0.x, x0.x, 0);
+    s = __dp4a(w0.y, x0.y, s);
+    s = __dp4a(w0.z, x0.z, s);
+    s = __dp4a(w0.w, x0.w, s);
+    s = __dp4a(w1.x, x1.x, s);
+    s = __dp4a(w1.y, x1.y, s);
+    s = __dp4a(w1.z, x1.z, s);
+    s = __dp4a(w1.w, x1.w, s);
+    return s;
+}
+
+// ----------------------------------------------------- activation quantiser
+//
+// One warp quantises one 32-element block; lane = element.  Arithmetic of
+// Q8Acts::from_f32 (crates/allpaka-backend/src/quantmat/q8_acts.rs:26-63):
+// d = amax/127 (0 when amax is not finite), id = 1/d (IEEE division),
+// q = round-half-away(v*id) saturated to i8, sum = sequential f32 sum.
+struct QBlock { float d; float sum; int q; };
+
+__device__ __forceinline__ QBlock quantize_block(float v, bool need_sum) {
+    float amax = fabsf(v);
+    if (amax != amax) amax = 0.0f;  // f32::max drops a NaN operand
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const bool fin = amax <= 3.402823466e+38f;
+    const float db = fin ? __fdiv_rn(amax, 127.0f) : 0.0f;
+    const float id = (db > 0.0f) ? __fdiv_rn(1.0f, db) : 0.0f;
+    float r = roundf(__fmul_rn(v, id));
+    int q;
+    if (r != r) q = 0;
+    else q = (int)fminf(fmaxf(r, -128.0f), 127.0f);
+    float s = 0.0f;
+    if (need_sum) {
+        // xs.iter().sum::<f32>(): strictly left to right
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s = __fadd_rn(s, __shfl_sync(0xffffffffu, v, i));
+    }
+    QBlock o;
+    o.d = db; o.sum = s; o.q = q;
+    return o;
+}
+
+// Store one quantised block (lane = element) into a prepared-activation buffer.
+__device__ __forceinline__ void store_act_block(const ActLayout &L, int row, int k_block, int lane,
+                                                const QBlock &qb) {
+    const int kt = L.ke >> 5;
+    const int ks = k_block / kt, bl = k_block - ks * kt;
+    uint8_t *rec = L.base + (size_t)ks * L.rec_bytes();
+    rec[row * L.ke + bl * 32 + lane] = (uint8_t)(int8_t)qb.q;
+    if (lane == 0) {
+        float *d = reinterpret_cast<float *>(rec + L.m_eff * L.ke);
+        d[row * kt + bl] = qb.d;
+        d[L.m_eff * kt + row * kt + bl] = qb.sum;
+    }
+}
+
+// Quantise value v (lane = element) of token m, block k_block, in Q8 mode
+// (one row per token) or two-level mode (rows 2m = value, 2m+1 = residual:
+// x = d1*q1 + d2*q2 to ~2^-15 of the block maximum, which is how the f32
+// activation call sites of the reference are served by the integer kernels).
+__device__ __forceinline__ void quantize_store(const ActLayout &L, int two_level, int need_sum, int m,
+                                               int k_block, int lane, float v) {
+    QBlock q1 = quantize_block(v, need_sum && !two_level);
+    if (!two_level) {
+        store_act_block(L, m, k_block, lane, q1);
+        return;
+    }
+    // residual is exact in one fused operation
+    const float r = __fmaf_rn(-q1.d, (float)q1.q, v);
+    QBlock q2 = quantize_block(r, false);
+    if (need_sum) {
+        // the min term needs sum(x) once: carry the exact block sum on the first row
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s = __fadd_rn(s, __shfl_sync(0xffffffffu, v, i));
+        q1.sum = s;
+        q2.sum = 0.0f;
+    }
+    store_act_block(L, 2 * m, k_block, lane, q1);
+    store_act_block(L, 2 * m + 1, k_block, lane, q2);
+}
+
+struct PrepParams {
+    const void *x; int x_is_bf16; int ldx;   // [m][n] activations
+    const float *add; int ldadd;             // optional addend (residual / combined partial sums)
+    float *xout; int ldxout;                 // optional: store x + add
+    const float *gamma; float eps;           // optional RMSNorm weight
+    float *hout; int ldh;                    // optional: store the normed f32 row
+    int n, m;
+    ActLayout out;
+    int two_level, need_sum;
+};
+
+__device__ __forceinline__ float load_x(const PrepParams &p, int m, int i) {
+    float v = p.x_is_bf16
+                  ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.x)[(size_t)m * p.ldx + i])
+                  : reinterpret_cast<const float *>(p.x)[(size_t)m * p.ldx + i];
+    if (p.add) v = __fadd_rn(v, p.add[(size_t)m * p.ldadd + i]);
+    return v;
+}
+
+// RMSNorm scale exactly as ops::rmsnorm_into does it (crates/allpaka-backend/
+// src/ops/norm.rs:193-198): f64 sum of squares, f64 1/sqrt(mean + eps).  The
+// f64 sum order differs from the reference's 8-lane walk; the difference is
+// confined to the last bits of an f64 that is then rounded to f32.
+__device__ __forceinline__ double block_rms_scale(const PrepParams &p, int m, double *red) {
+    double ss = 0.0;
+    for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
+        const double v = (double)load_x(p, m, i);
+        ss = fma(v, v, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const int w = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    if ((threadIdx.x & 31) == 0) red[w] = ss;
+    __syncthreads();
+    double tot = 0.0;
+    for (int i = 0; i < nw; ++i) tot += red[i];
+    return 1.0 / sqrt(tot / (double)p.n + (double)p.eps);
+}
+
+// grid = (ceil(blocks / 8), m), 256 threads: each warp quantises one block.
+__global__ void __launch_bounds__(256) prep_acts_kernel(PrepParams p) {
+    __shared__ double red[8];
+    const int m = blockIdx.y;
+    double scale = 1.0;
+    if (p.gamma) scale = block_rms_scale(p, m, red);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int blk = blockIdx.x * 8 + warp;
+    if (blk * 32 >= p.n) return;
+    const int i = blk * 32 + lane;
+    float v = load_x(p, m, i);
+    if (p.xout) p.xout[(size_t)m * p.ldxout + i] = v;
+    if (p.gamma) v = __fmul_rn((float)((double)v * scale), p.gamma[i]);
+    if (p.hout) p.hout[(size_t)m * p.ldh + i] = v;
+    quantize_store(p.out, p.two_level, p.need_sum, m, blk, lane, v);
+}
+
+// ------------------------------------------------------------------ repack
+
+struct RepackParams {
+    const uint8_t *src;      // raw GGUF rows (device staging copy)
+    size_t src_row_bytes;    // bytes from one staged row to the next
+    int src_rows;            // rows in the staging copy
+    int row_base;            // segment-relative index of the staging copy's first row
+    int nb;                  // 32-element blocks per (sharded) row
+    uint8_t *dst;            // tiled stream of the destination matrix
+    uint32_t dst_tile_bytes;
+    // destination row of source row r: (r / group) * stride + offset + r % group
+    int group, stride, offset;
+};
+
+__device__ __forceinline__ int map_row(const RepackParams &p, int r) {
+    r += p.row_base;
+    return (r / p.group) * p.stride + p.offset + (r % p.group);
+}
+
+// One thread per (row, block): 34 unaligned source bytes -> two 16-byte chunks + scale.
+__global__ void repack_q8_0_kernel(RepackParams p) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)p.src_rows * p.nb;
+    if (idx >= total) return;
+    const int r = (int)(idx / p.nb), b = (int)(idx % p.nb);
+    const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)b * 34;
+    const int dr = map_row(p, r);
+    const int tile = dr / TILE_ROWS, rt = dr % TILE_ROWS, rg = rt >> 5, lane = rt & 31;
+    const int ks = b / Q8_KT, bl = b % Q8_KT;
+    const int kb = min(Q8_KT, p.nb - ks * Q8_KT);
+    uint8_t *unit = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)ks * Q8_KT * Q8_BLOCK_UNIT;
+    uint32_t w[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        w[i] = (uint32_t)s[2 + 4 * i] | ((uint32_t)s[3 + 4 * i] << 8) | ((uint32_t)s[4 + 4 * i] << 16) |
+               ((uint32_t)s[5 + 4 * i] << 24);
+    uint4 *q0 = reinterpret_cast<uint4 *>(unit + ((bl * 2 + 0) * 4 + rg) * 512 + lane * 16);
+    uint4 *q1 = reinterpret_cast<uint4 *>(unit + ((bl * 2 + 1) * 4 + rg) * 512 + lane * 16);
+    *q0 = make_uint4(w[0], w[1], w[2], w[3]);
+    *q1 = make_uint4(w[4], w[5], w[6], w[7]);
+    uint16_t *sc = reinterpret_cast<uint16_t *>(unit + kb * 4096 + (bl * 128 + rt) * 2);
+    *sc = (uint16_t)(s[0] | (s[1] << 8));
+}
+
+// One thread per (row, super-block, chunk): 16 source bytes (16-byte aligned
+// whenever the staged row is) -> one chunk.
+__global__ void repack_q4_k_kernel(RepackParams p) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int nsb = p.nb / 8;
+    const size_t total = (size_t)p.src_rows * nsb * 9;
+    if (idx >= total) return;
+    const int c = (int)(idx % 9);
+    const size_t rb = idx / 9;
+    const int sb = (int)(rb % nsb), r = (int)(rb / nsb);
+    const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)sb * 144 + c * 16;
+    const int dr = map_row(p, r);
+    const int tile = dr / TILE_ROWS, rt = dr % TILE_ROWS, rg = rt >> 5, lane = rt & 31;
+    const int ks = sb / Q4_KT_SB, sl = sb % Q4_KT_SB;
+    uint8_t *unit = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)ks * Q4_KT_SB * Q4_SB_UNIT;
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+        w[i] = (uint32_t)s[4 * i] | ((uint32_t)s[4 * i + 1] << 8) | ((uint32_t)s[4 * i + 2] << 16) |
+               ((uint32_t)s[4 * i + 3] << 24);
+    *reinterpret_cast<uint4 *>(unit + sl * Q4_SB_UNIT + (c * 4 + rg) * 512 + lane * 16) =
+        make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// ------------------------------------------------------------ the matvec
+
+__device__ __forceinline__ void scale_min_k4_dev(int j, uint32_t s0, uint32_t s1, uint32_t s2, float &sc,
+                                                 float &mn) {
+    // crates/allpaka-dtype/src/lib.rs:382-390 on the 12 packed bytes as three LE words
+    auto byte = [&](int i) -> uint32_t {
+        const uint32_t w = i < 4 ? s0 : (i < 8 ? s1 : s2);
+        return (w >> (8 * (i & 3))) & 0xffu;
+    };
+    if (j < 4) {
+        sc = (float)(byte(j) & 63u);
+        mn = (float)(byte(j + 4) & 63u);
+    } else {
+        sc = (float)((byte(j + 4) & 0xfu) | ((byte(j - 4) >> 6) << 4));
+        mn = (float)((byte(j + 4) >> 4) | ((byte(j) >> 6) << 4));
+    }
+}
+
+// Shared memory map of the matvec kernel (dynamic, 128-byte aligned base):
+//   [0, 8*MAX_STAGES)        full barriers
+//   [.., 16*MAX_STAGES)      empty barriers
+//   [128 ..)                 flags: s_last
+//   [256 ..)                 red[2][M][128] f32  (K-half partials; red[0] doubles as the tile result)
+//   [..]                     stages: n_stages * (STAGE_W_BYTES + act record)
+template <int M>
+struct MvSmem {
+    static constexpr int RED_OFF = 256;
+    static constexpr int RED_BYTES = 2 * M * TILE_ROWS * 4;
+    static constexpr int STAGE_OFF = RED_OFF + RED_BYTES;
+    __host__ __device__ static int stage_bytes(int act_rec) { return STAGE_W_BYTES + ((act_rec + 127) & ~127); }
+    __host__ __device__ static int total(int n_stages, int act_rec) {
+        return STAGE_OFF + n_stages * stage_bytes(act_rec);
+    }
+};
+
+template <int M>
+__device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float *out /*[M][128] smem*/,
+                                              int tid);
+
+template <int TY, int M, bool DUMP>
+__global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvParams p) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *full = reinterpret_cast<uint64_t *>(smem);
+    uint64_t *empty = full + MAX_STAGES;
+    int *s_flags = reinterpret_cast<int *>(smem + 128);
+    float *red = reinterpret_cast<float *>(smem + MvSmem<M>::RED_OFF);
+    const int act_rec = p.act.rec_bytes();
+    const int stage_bytes = MvSmem<M>::stage_bytes(act_rec);
+    uint8_t *stages = smem + MvSmem<M>::STAGE_OFF;
+    const int NS = p.n_stages;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], N_CONSUMER_WARPS);
+        }
+        fence_mbar_init();
+    }
+    __syncthreads();
+
+    // this CTA's contiguous range of the flat unit sequence
+    const long long U = (long long)p.n_tiles * p.KS;
+    const long long G = gridDim.x;
+    const long long u_begin = (long long)blockIdx.x * U / G;
+    const long long u_end = (long long)(blockIdx.x + 1) * U / G;
+    const int kt = (TY == TY_Q8_0) ? Q8_KT : Q4_KT_SB * 8;  // 32-element blocks per full K-step
+
+    if (warp == N_CONSUMER_WARPS) {
+        // ------------------------------------------------ producer (one lane)
+        if (lane == 0) {
+            const uint64_t pol_w = l2_policy_evict_first();
+            const uint64_t pol_a = l2_policy_evict_last();
+            int it = 0;
+            for (long long u = u_begin; u < u_end; ++u, ++it) {
+                const int s = it % NS;
+                const uint32_t ph = (uint32_t)((it / NS) & 1);
+                if (!mbar_wait_bounded(&empty[s], ph ^ 1u)) {
+                    atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
+                    break;
+                }
+                const int t = (int)(u / p.KS), ks = (int)(u % p.KS);
+                const int kb = min(kt, p.nb - ks * kt);
+                uint32_t wbytes, woff;
+                if (TY == TY_Q8_0) {
+                    wbytes = (uint32_t)kb * Q8_BLOCK_UNIT;
+                    woff = (uint32_t)ks * Q8_KT * Q8_BLOCK_UNIT;
+                } else {
+                    wbytes = (uint32_t)(kb / 8) * Q4_SB_UNIT;
+                    woff = (uint32_t)ks * Q4_KT_SB * Q4_SB_UNIT;
+                }
+                uint8_t *st = stages + (size_t)s * stage_bytes;
+                mbar_arrive_expect_tx(&full[s], wbytes + (uint32_t)act_rec);
+                bulk_g2s(st, p.W + (size_t)t * p.tile_bytes + woff, wbytes, &full[s], pol_w);
+                bulk_g2s(st + STAGE_W_BYTES, p.act.base + (size_t)ks * act_rec, (uint32_t)act_rec, &full[s],
+                         pol_a);
+            }
+            // Every copy issued above lands before this lane leaves: wait (bounded)
+            // for the stages still in flight so no bulk write outlives the CTA.
+            const int pending = it < NS ? it : NS;
+            for (int j = it - pending; j < it; ++j) {
+                const int s = j % NS;
+                (void)mbar_wait_bounded(&full[s], (uint32_t)((j / NS) & 1));
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------- consumers
+    const int rg = warp & 3;   // row group of 32 rows inside the tile
+    const int kh = warp >> 2;  // which half of the K-step's blocks
+    float acc[M];
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+    bool aborted = false;
+
+    int it = 0;
+    for (long long u = u_begin; u < u_end; ++u, ++it) {
+        const int s = it % NS;
+        const uint32_t ph = (uint32_t)((it / NS) & 1);
+        const int t = (int)(u / p.KS), ks = (int)(u % p.KS);
+        if (!aborted && !mbar_wait_bounded(&full[s], ph)) {
+            aborted = true;
+            if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
+        }
+        if (!aborted) {
+            const uint8_t *sw = stages + (size_t)s * stage_bytes;
+            const uint8_t *sa = sw + STAGE_W_BYTES;
+            const int kb = min(kt, p.nb - ks * kt);
+            const float *ad = reinterpret_cast<const float *>(sa + M * p.act.ke);
+            if (TY == TY_Q8_0) {
+                for (int b = kh; b < kb; b += 2) {
+                    const int4 w0 = *reinterpret_cast<const int4 *>(sw + ((b * 2 + 0) * 4 + rg) * 512 + lane * 16);
+                    const int4 w1 = *reinterpret_cast<const int4 *>(sw + ((b * 2 + 1) * 4 + rg) * 512 + lane * 16);
+                    const float dw = __half2float(
+                        *reinterpret_cast<const __half *>(sw + kb * 4096 + (b * 128 + rg * 32 + lane) * 2));
+#pragma unroll
+                    for (int m = 0; m < M; ++m) {
+                        const int4 x0 = *reinterpret_cast<const int4 *>(sa + m * p.act.ke + b * 32);
+                        const int4 x1 = *reinterpret_cast<const int4 *>(sa + m * p.act.ke + b * 32 + 16);
+                        const int idot = dot32(w0, w1, x0, x1);
+                        const float dx = ad[m * Q8_KT + b];
+                        acc[m] = fmaf(__fmul_rn(dw, dx), (float)idot, acc[m]);
+                        if (DUMP) {
+                            const int row = t * TILE_ROWS + rg * 32 + lane;
+                            if (row < p.n_out)
+                                p.dump[((size_t)m * p.n_out + row) * p.nb + ks * Q8_KT + b] = idot;
+                        }
+                    }
+                }
+            } else {
+                const float *as = ad + M * (Q4_KT_SB * 8);
+                const int nsb = kb / 8;
+                for (int sb = kh; sb < nsb; sb += 2) {
+                    const uint8_t *base = sw + sb * Q4_SB_UNIT;
+                    const uint4 hdr = *reinterpret_cast<const uint4 *>(base + rg * 512 + lane * 16);
+                    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
+                    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+#pragma unroll
+                    for (int pr = 0; pr < 4; ++pr) {
+                        const uint4 q0 =
+                            *reinterpret_cast<const uint4 *>(base + ((1 + 2 * pr) * 4 + rg) * 512 + lane * 16);
+                        const uint4 q1 =
+                            *reinterpret_cast<const uint4 *>(base + ((2 + 2 * pr) * 4 + rg) * 512 + lane * 16);
+                        int4 lo0, lo1, hi0, hi1;
+                        lo0.x = q0.x & 0x0f0f0f0f; lo0.y = q0.y & 0x0f0f0f0f; lo0.z = q0.z & 0x0f0f0f0f; lo0.w = q0.w & 0x0f0f0f0f;
+                        lo1.x = q1.x & 0x0f0f0f0f; lo1.y = q1.y & 0x0f0f0f0f; lo1.z = q1.z & 0x0f0f0f0f; lo1.w = q1.w & 0x0f0f0f0f;
+                        hi0.x = (q0.x >> 4) & 0x0f0f0f0f; hi0.y = (q0.y >> 4) & 0x0f0f0f0f; hi0.z = (q0.z >> 4) & 0x0f0f0f0f; hi0.w = (q0.w >> 4) & 0x0f0f0f0f;
+                        hi1.x = (q1.x >> 4) & 0x0f0f0f0f; hi1.y = (q1.y >> 4) & 0x0f0f0f0f; hi1.z = (q1.z >> 4) & 0x0f0f0f0f; hi1.w = (q1.w >> 4) & 0x0f0f0f0f;
+                        float sc1, mn1, sc2, mn2;
+                        scale_min_k4_dev(2 * pr, hdr.y, hdr.z, hdr.w, sc1, mn1);
+                        scale_min_k4_dev(2 * pr + 1, hdr.y, hdr.z, hdr.w, sc2, mn2);
+                        const float dsc1 = __fmul_rn(d, sc1), dm1 = __fmul_rn(dmin, mn1);
+                        const float dsc2 = __fmul_rn(d, sc2), dm2 = __fmul_rn(dmin, mn2);
+                        const int b_lo = sb * 8 + 2 * pr, b_hi = b_lo + 1;
+#pragma unroll
+                        for (int m = 0; m < M; ++m) {
+                            const int8_t *xq = reinterpret_cast<const int8_t *>(sa) + m * p.act.ke;
+                            const int4 xl0 = *reinterpret_cast<const int4 *>(xq + b_lo * 32);
+                            const int4 xl1 = *reinterpret_cast<const int4 *>(xq + b_lo * 32 + 16);
+                            const int4 xh0 = *reinterpret_cast<const int4 *>(xq + b_hi * 32);
+                            const int4 xh1 = *reinterpret_cast<const int4 *>(xq + b_hi * 32 + 16);
+                            const int il = dot32(lo0, lo1, xl0, xl1);
+                            const int ih = dot32(hi0, hi1, xh0, xh1);
+                            const float dot_lo = __fmul_rn((float)il, ad[m * 16 + b_lo]);
+                            const float dot_hi = __fmul_rn((float)ih, ad[m * 16 + b_hi]);
+                            // total += d*sc*dot - dmin*mn*sum  (q8_acts.rs:296-297)
+                            acc[m] += __fsub_rn(__fmul_rn(dsc1, dot_lo), __fmul_rn(dm1, as[m * 16 + b_lo]));
+                            acc[m] += __fsub_rn(__fmul_rn(dsc2, dot_hi), __fmul_rn(dm2, as[m * 16 + b_hi]));
+                            if (DUMP) {
+                                const int row = t * TILE_ROWS + rg * 32 + lane;
+                                if (row < p.n_out) {
+                                    int32_t *o = p.dump + ((size_t)m * p.n_out + row) * p.nb + ks * 16;
+                                    o[b_lo] = il;
+                                    o[b_hi] = ih;
+                                }
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+
+        // ---- end of this CTA's share of tile t: combine and finish the tile
+        const bool tile_done = (ks == p.KS - 1) || (u + 1 == u_end);
+        if (!tile_done) continue;
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            red[(kh * M + m) * TILE_ROWS + rg * 32 + lane] = acc[m];
+            acc[m] = 0.0f;
+        }
+        consumer_bar();
+        for (int i = tid; i < M * TILE_ROWS; i += N_CONSUMERS) red[i] += red[M * TILE_ROWS + i];
+        const long long ua = (long long)t * p.KS, ub = ua + p.KS - 1;
+        const int c_first = (int)(((ua + 1) * G - 1) / U), c_last = (int)(((ub + 1) * G - 1) / U);
+        if (c_first != c_last) {
+            // partial tile: publish, count arrivals, the last arriver sums in CTA order
+            const int my_first_tile = (int)(u_begin / p.KS);
+            float *slot = p.partials + ((size_t)blockIdx.x * 2 + (my_first_tile == t ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
+            consumer_bar();
+            for (int i = tid; i < M * TILE_ROWS; i += N_CONSUMERS) __stcg(&slot[i], red[i]);
+            __threadfence();
+            consumer_bar();
+            if (tid == 0) {
+                const int old = atomicAdd(&p.counters[t], 1);
+                s_flags[0] = (old == c_last - c_first) ? 1 : 0;
+            }
+            consumer_bar();
+            const bool last = s_flags[0] != 0;
+            if (last) {
+                __threadfence();
+                for (int i = tid; i < M * TILE_ROWS; i += N_CONSUMERS) {
+                    float v = 0.0f;
+                    for (int c = c_first; c <= c_last; ++c) {
+                        const int cf = (int)(((long long)c * U / G) / p.KS);
+                        const float *sl = p.partials + ((size_t)c * 2 + (cf == t ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
+                        v += __ldcg(&sl[i]);
+                    }
+                    red[i] = v;
+                }
+                if (tid == 0) p.counters[t] = 0;
+            }
+            consumer_bar();
+            if (last) epilogue_tile<M>(p, t, red, tid);
+        } else {
+            consumer_bar();
+            epilogue_tile<M>(p, t, red, tid);
+        }
+        consumer_bar();  // red is reused by the next tile
+    }
+}
+
+// tile result out[m][r] (m < M rows of the activation record) -> global.
+// Called by all 256 consumer threads.
+template <int M>
+__device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float *out, int tid) {
+    const int MO = p.m_out;
+    // two-level rows 2m, 2m+1 are the two digits of token m: their sum is the dot
+    auto val = [&](int m, int r) -> float {
+        return p.two_level ? out[(2 * m) * TILE_ROWS + r] + out[(2 * m + 1) * TILE_ROWS + r]
+                           : out[m * TILE_ROWS + r];
+    };
+    const int row0 = tile * TILE_ROWS;
+    if (p.epi == EPI_STORE || p.epi == EPI_ADD) {
+        for (int i = tid; i < MO * TILE_ROWS; i += N_CONSUMERS) {
+            const int m = i / TILE_ROWS, r = i % TILE_ROWS;
+            const int row = row0 + r;
+            if (row >= p.n_out) continue;
+            float v = val(m, r);
+            if (p.epi == EPI_ADD) v = __fadd_rn(p.resid[(size_t)m * p.ldr + row], v);
+            p.y[(size_t)m * p.ldy + row] = v;
+        }
+        return;
+    }
+    if (p.epi == EPI_QKV_ROPE) {
+        // one head per tile (head_dim 128): warp w serves tokens w, w+8, ...
+        const int warp = tid >> 5, lane = tid & 31;
+        const float *nw = tile < p.n_q_tiles ? p.q_norm : (tile < p.n_q_tiles + p.n_k_tiles ? p.k_norm : nullptr);
+        const bool rot = tile < p.n_q_tiles + p.n_k_tiles;
+        for (int m = warp; m < MO; m += N_CONSUMER_WARPS) {
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = val(m, lane + 32 * j);
+            if (nw) {
+                // ops::rmsnorm on the head (model/attention.rs:134-137; ops/norm.rs:115-118)
+                double ss = 0.0;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) ss = fma((double)v[j], (double)v[j], ss);
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const double scale = 1.0 / sqrt(ss / 128.0 + (double)p.eps);
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    v[j] = __fmul_rn((float)((double)v[j] * scale), nw[lane + 32 * j]);
+            }
+            // stage the (normed) head so rotation partners can be read back
+            __syncwarp();
+            float *hs = out + (p.two_level ? 2 * m : m) * TILE_ROWS;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) hs[lane + 32 * j] = v[j];
+            __syncwarp();
+            const int half = p.half;
+            const float *tab = p.rope + (size_t)m * half * 2;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int c = lane + 32 * j;
+                float o = v[j];
+                if (rot) {
+                    // ops::rope_neox_cached_from_array (ops/rope.rs:70-81)
+                    if (c < half) {
+                        const float sn = tab[2 * c], cs = tab[2 * c + 1];
+                        o = __fsub_rn(__fmul_rn(v[j], cs), __fmul_rn(hs[c + half], sn));
+                    } else if (c < 2 * half) {
+                        const int i = c - half;
+                        const float sn = tab[2 * i], cs = tab[2 * i + 1];
+                        o = __fadd_rn(__fmul_rn(hs[i], sn), __fmul_rn(v[j], cs));
+                    }
+                }
+                const int row = row0 + c;
+                if (row < p.n_out) p.y[(size_t)m * p.ldy + row] = o;
+            }
+        }
+        return;
+    }
+    if (p.epi == EPI_SWIGLU) {
+        // rows 0..63 = gate rows [64*tile, 64*tile+64), rows 64..127 = the matching up rows.
+        // Work item = (token, 32-row half) = one activation block of the down projection.
+        const int warp = tid >> 5, lane = tid & 31;
+        for (int w = warp; w < MO * 2; w += N_CONSUMER_WARPS) {
+            const int m = w >> 1, h = w & 1;
+            const int r = h * 32 + lane;
+            const float g = val(m, r), uu = val(m, 64 + r);
+            // ops::silu / swiglu (ops/activation.rs:20-22, 116-119)
+            const float a = __fmul_rn(__fdiv_rn(g, __fadd_rn(1.0f, expf(-g))), uu);
+            const int k = tile * 64 + r;  // column of the down projection
+            const bool live = k < p.ffn;
+            if (p.act_f32 && live) p.act_f32[(size_t)m * p.ld_act + k] = a;
+            if (p.act_next.base && (tile * 64 + h * 32) < p.ffn)
+                quantize_store(p.act_next, p.next_two_level, p.next_need_sum, m, k >> 5, lane, live ? a : 0.0f);
+        }
+        return;
+    }
+}
+
+}  // namespace apk

@@ -1,0 +1,527 @@
+"""Host-side mirror of allpaka-backend's accelerator module (``crate::gpu``).
+
+Same free-function surface, names and argument meaning as the module every
+reference backend implements (crates/allpaka-backend/src/gpu/stub.rs:37-217;
+request structs gpu/types.rs:9-31, 54-80, 111-252): ``attach``, ``detach``,
+``is_attached``, ``matvec``, ``matvec_batch``, ``ffn_batch``, ``attn_block``'s
+input half, ``decode_token_checked`` / ``decode_token``, ``stats``,
+``decode_path_stats``.  A declined request returns ``None`` (Rust ``Option``);
+``decode_token_checked`` raises :class:`DecodeDecline`; hard errors raise
+:class:`GpuError`.  Everything runs through the C ABI of ``libapk_b200.so``;
+there is no CPU path here, and a missing library is an error, not a fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libapk_b200.so")
+
+# GGML type ids (crates/allpaka-dtype/src/lib.rs:61-75)
+Q8_0 = 8
+Q4_K = 12
+
+ACT_Q8, ACT_F32, ACT_AUTO = 0, 1, 2
+ATTN_IDENTITY = 1
+MAX_M = 8
+
+_DECLINE_NAMES = {
+    1: "NoDevice", 2: "UnsupportedTensorType", 3: "UnsupportedShape", 4: "ForeignMemory",
+    5: "MissingCapability", 6: "InvalidState", 7: "Backend",
+}
+
+
+class GpuError(RuntimeError):
+    """A hard failure (CUDA/NCCL error, expired device wait, invalid argument)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"apk error {code}: {message}")
+        self.code = code
+
+
+class DecodeDecline(Exception):
+    """``DecodeDecline { stage, reason }`` (gpu/types.rs:240-252)."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(message)
+        self.code = code
+        self.reason = _DECLINE_NAMES.get(code, str(code))
+
+
+class _MatvecReq(C.Structure):
+    _fields_ = [("ty", C.c_uint32), ("w", C.c_void_p), ("n_in", C.c_uint32), ("n_out", C.c_uint32),
+                ("x", C.c_void_p), ("m", C.c_uint32)]
+
+
+class _FfnReq(C.Structure):
+    _fields_ = [("gate_ty", C.c_uint32), ("gate_w", C.c_void_p), ("up_ty", C.c_uint32),
+                ("up_w", C.c_void_p), ("down_ty", C.c_uint32), ("down_w", C.c_void_p),
+                ("hidden", C.c_uint32), ("ffn", C.c_uint32), ("x", C.c_void_p), ("m", C.c_uint32)]
+
+
+class _AttnInReq(C.Structure):
+    _fields_ = [("ty", C.c_uint32), ("wq", C.c_void_p), ("wk", C.c_void_p), ("wv", C.c_void_p),
+                ("hidden", C.c_uint32), ("head_dim", C.c_uint32), ("n_heads", C.c_uint32),
+                ("n_kv_heads", C.c_uint32), ("x", C.c_void_p), ("m", C.c_uint32),
+                ("gamma", C.c_void_p), ("eps", C.c_float), ("q_norm", C.c_void_p),
+                ("k_norm", C.c_void_p), ("rope", C.c_void_p), ("rot_dim", C.c_uint32)]
+
+
+class _Mat(C.Structure):
+    _fields_ = [("ty", C.c_uint32), ("w", C.c_void_p), ("n_out", C.c_uint32)]
+
+
+class _TokenLayer(C.Structure):
+    _fields_ = [("attn_norm", C.c_void_p), ("ffn_norm", C.c_void_p),
+                ("wq", _Mat), ("wk", _Mat), ("wv", _Mat), ("wo", _Mat),
+                ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
+                ("gate", _Mat), ("up", _Mat), ("down", _Mat)]
+
+
+class _TokenReq(C.Structure):
+    _fields_ = [("layers", C.c_void_p), ("n_layers", C.c_uint32), ("output_norm", C.c_void_p),
+                ("output", _Mat), ("x", C.c_void_p), ("m", C.c_uint32), ("rope", C.c_void_p),
+                ("rot_dim", C.c_uint32), ("eps", C.c_float), ("hidden", C.c_uint32),
+                ("head_dim", C.c_uint32), ("n_heads", C.c_uint32), ("n_kv_heads", C.c_uint32),
+                ("attn_core", C.c_uint32), ("argmax", C.c_int)]
+
+
+class _TokenOut(C.Structure):
+    _fields_ = [("logits", C.c_void_p), ("argmax", C.c_void_p)]
+
+
+class _Stats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in
+                ("calls", "launches", "encode_ns", "wait_ns", "weight_bytes",
+                 "decode_attempts", "decode_successes", "decode_declines")]
+
+
+EXPORTS = (
+    "apk_init", "apk_shutdown", "apk_attach", "apk_detach", "apk_is_attached",
+    "apk_register_matrix", "apk_matvec", "apk_matvec_batch", "apk_ffn", "apk_attn_in",
+    "apk_decode_token", "apk_decode_replay", "apk_debug_block_dots", "apk_debug_q8_acts",
+    "apk_stats", "apk_last_error", "apk_dist_unique_id", "apk_dist_init",
+)
+
+_lib = None
+
+
+def load_library() -> C.CDLL:
+    """dlopen libapk_b200.so; a missing library is a hard error."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise GpuError(-1, f"{LIB_PATH} is missing: build it with `python -m allpaka_b200.build` "
+                           "(there is no CPU fallback)")
+    l = C.CDLL(LIB_PATH)
+    l.apk_init.argtypes = [C.POINTER(C.c_void_p), C.c_int]
+    l.apk_shutdown.argtypes = [C.c_void_p]
+    l.apk_shutdown.restype = None
+    l.apk_attach.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    l.apk_detach.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t]
+    l.apk_is_attached.argtypes = [C.c_void_p]
+    l.apk_register_matrix.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32]
+    l.apk_matvec.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
+                             C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
+    l.apk_matvec_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p]
+    l.apk_ffn.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+    l.apk_attn_in.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    l.apk_decode_token.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
+    l.apk_decode_replay.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(C.c_float)]
+    l.apk_debug_block_dots.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
+                                       C.c_void_p, C.c_uint32, C.c_void_p]
+    l.apk_debug_q8_acts.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_float,
+                                    C.c_void_p, C.c_void_p, C.c_void_p]
+    l.apk_stats.argtypes = [C.c_void_p, C.c_void_p]
+    l.apk_stats.restype = None
+    l.apk_last_error.argtypes = [C.c_void_p]
+    l.apk_last_error.restype = C.c_char_p
+    l.apk_dist_unique_id.argtypes = [C.c_void_p]
+    l.apk_dist_init.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
+    _lib = l
+    return l
+
+
+def _u8(a) -> np.ndarray:
+    a = np.ascontiguousarray(a)
+    return a.view(np.uint8).reshape(-1)
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _ptr(a) -> Optional[int]:
+    return None if a is None else a.ctypes.data
+
+
+@dataclass
+class MatvecReq:
+    """gpu/types.rs:9-16"""
+    ty: int
+    w: np.ndarray
+    n_in: int
+    n_out: int
+    x: np.ndarray
+    m: int
+
+
+@dataclass
+class FfnReq:
+    """gpu/types.rs:20-31"""
+    gate_ty: int
+    gate_w: np.ndarray
+    up_ty: int
+    up_w: np.ndarray
+    down_ty: int
+    down_w: np.ndarray
+    hidden: int
+    ffn: int
+    x: np.ndarray
+    m: int
+
+
+@dataclass
+class TokenLayer:
+    """gpu/types.rs:111-150, dense attention layers; matrices are (ty, bytes, n_out)."""
+    attn_norm: np.ndarray
+    ffn_norm: np.ndarray
+    wq: tuple
+    wk: tuple
+    wv: tuple
+    wo: tuple
+    gate: tuple
+    up: tuple
+    down: tuple
+    q_norm: Optional[np.ndarray] = None
+    k_norm: Optional[np.ndarray] = None
+
+
+@dataclass
+class TokenReq:
+    """gpu/types.rs:183-238, the fields the dequant-matvec path consumes."""
+    layers: Sequence[TokenLayer]
+    output_norm: np.ndarray
+    output: tuple
+    x: np.ndarray
+    m: int
+    rope: np.ndarray
+    rot_dim: int
+    eps: float
+    hidden: int
+    head_dim: int
+    n_heads: int
+    n_kv_heads: int
+    argmax: bool = False
+    attn_core: int = ATTN_IDENTITY
+
+
+class Gpu:
+    """One GPU context.  The module-level functions below forward to a
+    process-wide instance, like the reference's lazily-initialised singleton
+    (gpu/cuda/runtime/device.rs:267, 934-948)."""
+
+    def __init__(self, device: int = -1):
+        self._l = load_library()
+        h = C.c_void_p()
+        rc = self._l.apk_init(C.byref(h), device)
+        if rc != 0:
+            raise GpuError(rc, self._l.apk_last_error(None).decode())
+        self._h = h
+        self._attached = []   # keeps attached buffers alive
+        self._token_cache = {}
+
+    def close(self):
+        if self._h:
+            self._l.apk_shutdown(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- status handling ---------------------------------------------------
+    def _err(self) -> str:
+        return self._l.apk_last_error(self._h).decode(errors="replace")
+
+    def _check(self, rc: int) -> bool:
+        """True = executed, False = declined (caller returns None)."""
+        if rc == 0:
+            return True
+        if rc > 0:
+            self.last_decline = (rc, self._err())
+            return False
+        raise GpuError(rc, self._err())
+
+    # -- gpu::attach / detach / is_attached (stub.rs:37-45) ------------------
+    def attach(self, mapping: np.ndarray) -> bool:
+        m = _u8(mapping)
+        rc = self._l.apk_attach(self._h, m.ctypes.data, m.size)
+        if rc == 0:
+            self._attached.append(m)
+        return self._check(rc)
+
+    def detach(self, mapping: np.ndarray) -> None:
+        m = _u8(mapping)
+        self._check(self._l.apk_detach(self._h, m.ctypes.data, m.size))
+        self._attached = [a for a in self._attached if a.ctypes.data != m.ctypes.data or a.size != m.size]
+        self._token_cache.clear()
+
+    def is_attached(self) -> bool:
+        return bool(self._l.apk_is_attached(self._h))
+
+    def register_matrix(self, w, ty: int, n_out: int, n_in: int) -> bool:
+        w = _u8(w)
+        return self._check(self._l.apk_register_matrix(self._h, w.ctypes.data, ty, n_out, n_in))
+
+    # -- gpu::matvec (stub.rs:87-95) ----------------------------------------
+    def matvec(self, ty: int, w, n_in: int, n_out: int, x, m: int = 1,
+               act_mode: int = ACT_AUTO) -> Optional[np.ndarray]:
+        w = _u8(w)
+        x = _f32(x).reshape(-1)
+        if x.size != m * n_in:
+            raise ValueError(f"x has {x.size} values, expected {m} x {n_in}")
+        y = np.empty((m, n_out), dtype=np.float32)
+        rc = self._l.apk_matvec(self._h, w.ctypes.data, ty, n_in, n_out, x.ctypes.data, m, act_mode,
+                                y.ctypes.data)
+        return y if self._check(rc) else None
+
+    # -- gpu::matvec_batch (stub.rs:97-99) ----------------------------------
+    def matvec_batch(self, reqs: Sequence[MatvecReq], act_mode: int = ACT_Q8):
+        if not reqs:
+            return []
+        arr = (_MatvecReq * len(reqs))()
+        keep, ys = [], []
+        for i, r in enumerate(reqs):
+            w, x = _u8(r.w), _f32(r.x).reshape(-1)
+            if x.size != r.m * r.n_in:
+                raise ValueError(f"x has {x.size} values, expected {r.m} x {r.n_in}")
+            # requests that share one activation array keep sharing it here
+            for (ko, kx) in keep:
+                if ko is r.x:
+                    x = kx
+            keep.append((r.x, x))
+            y = np.empty((r.m, r.n_out), dtype=np.float32)
+            ys.append(y)
+            arr[i] = _MatvecReq(r.ty, w.ctypes.data, r.n_in, r.n_out, x.ctypes.data, r.m)
+        yp = (C.c_void_p * len(reqs))(*[y.ctypes.data for y in ys])
+        rc = self._l.apk_matvec_batch(self._h, C.addressof(arr), len(reqs), act_mode, C.addressof(yp))
+        return ys if self._check(rc) else None
+
+    # -- gpu::ffn_batch (stub.rs:101-103) -----------------------------------
+    def ffn_batch(self, reqs: Sequence[FfnReq]):
+        outs = []
+        for r in reqs:
+            x = _f32(r.x).reshape(-1)
+            if x.size != r.m * r.hidden:
+                return None  # the reference declines a mis-sized x (cuda/mod.rs:269-271)
+            g, u, d = _u8(r.gate_w), _u8(r.up_w), _u8(r.down_w)
+            req = _FfnReq(r.gate_ty, g.ctypes.data, r.up_ty, u.ctypes.data, r.down_ty, d.ctypes.data,
+                          r.hidden, r.ffn, x.ctypes.data, r.m)
+            y = np.empty((r.m, r.hidden), dtype=np.float32)
+            if not self._check(self._l.apk_ffn(self._h, C.byref(req), y.ctypes.data)):
+                return None
+            outs.append(y)
+        return outs
+
+    # -- input half of gpu::attn_block (stub.rs:146-148) ---------------------
+    def attn_in(self, ty, wq, wk, wv, hidden, head_dim, n_heads, n_kv_heads, x, m, gamma, eps, rope,
+                rot_dim=None, q_norm=None, k_norm=None):
+        wq, wk, wv = _u8(wq), _u8(wk), _u8(wv)
+        x = _f32(x).reshape(-1)
+        rope = _f32(rope).reshape(m, -1, 2)
+        rot_dim = rope.shape[1] * 2 if rot_dim is None else rot_dim
+        gamma = None if gamma is None else _f32(gamma)
+        q_norm = None if q_norm is None else _f32(q_norm)
+        k_norm = None if k_norm is None else _f32(k_norm)
+        nq, nkv = n_heads * head_dim, n_kv_heads * head_dim
+        q = np.empty((m, nq), np.float32)
+        k = np.empty((m, nkv), np.float32)
+        v = np.empty((m, nkv), np.float32)
+        req = _AttnInReq(ty, wq.ctypes.data, wk.ctypes.data, wv.ctypes.data, hidden, head_dim, n_heads,
+                         n_kv_heads, x.ctypes.data, m, _ptr(gamma), eps, _ptr(q_norm), _ptr(k_norm),
+                         rope.ctypes.data, rot_dim)
+        rc = self._l.apk_attn_in(self._h, C.byref(req), q.ctypes.data, k.ctypes.data, v.ctypes.data)
+        return (q, k, v) if self._check(rc) else None
+
+    # -- gpu::decode_token_checked / decode_token (stub.rs:150-161) ----------
+    def _token_req(self, req: TokenReq):
+        """Marshal once per distinct layer list; the C side keys its plan on the
+        layer array's address, as the reference keys on borrowed slices."""
+        key = id(req.layers)
+        ent = self._token_cache.get(key)
+        if ent is None:
+            arr = (_TokenLayer * len(req.layers))()
+            keep = []
+
+            def mat(t):
+                ty, w, n_out = t
+                w = _u8(w)
+                keep.append(w)
+                return _Mat(ty, w.ctypes.data, n_out)
+
+            def vec(a):
+                if a is None:
+                    return None
+                a = _f32(a)
+                keep.append(a)
+                return a.ctypes.data
+
+            for i, L in enumerate(req.layers):
+                arr[i] = _TokenLayer(vec(L.attn_norm), vec(L.ffn_norm), mat(L.wq), mat(L.wk), mat(L.wv),
+                                     mat(L.wo), vec(L.q_norm), vec(L.k_norm), mat(L.gate), mat(L.up),
+                                     mat(L.down))
+            on = _f32(req.output_norm)
+            keep.append(on)
+            ent = (arr, keep, on, mat(req.output), req.layers)
+            self._token_cache[key] = ent
+        arr, keep, on, out_mat, _ = ent
+        x = _f32(req.x).reshape(-1)
+        rope = _f32(req.rope).reshape(-1)
+        creq = _TokenReq(C.addressof(arr), len(req.layers), on.ctypes.data, out_mat, x.ctypes.data, req.m,
+                         rope.ctypes.data, req.rot_dim, req.eps, req.hidden, req.head_dim, req.n_heads,
+                         req.n_kv_heads, req.attn_core, 1 if req.argmax else 0)
+        return creq, (x, rope)
+
+    def decode_token_checked(self, req: TokenReq):
+        creq, keep = self._token_req(req)
+        vocab = req.output[2]
+        if req.argmax:
+            res = np.empty(req.m, dtype=np.uint32)
+            out = _TokenOut(None, res.ctypes.data)
+        else:
+            res = np.empty((req.m, vocab), dtype=np.float32)
+            out = _TokenOut(res.ctypes.data, None)
+        rc = self._l.apk_decode_token(self._h, C.byref(creq), C.byref(out))
+        if rc > 0:
+            raise DecodeDecline(rc, self._err())
+        if rc < 0:
+            raise GpuError(rc, self._err())
+        return res
+
+    def decode_token(self, req: TokenReq):
+        try:
+            return self.decode_token_checked(req)
+        except DecodeDecline:
+            return None
+
+    def decode_replay(self, req: TokenReq, iters: int) -> float:
+        """Replay the token graph `iters` times on device-resident input; returns GPU ms."""
+        creq, keep = self._token_req(req)
+        ms = C.c_float()
+        rc = self._l.apk_decode_replay(self._h, C.byref(creq), iters, C.byref(ms))
+        if rc > 0:
+            raise DecodeDecline(rc, self._err())
+        if rc < 0:
+            raise GpuError(rc, self._err())
+        return ms.value
+
+    # -- parity instrumentation ----------------------------------------------
+    def debug_block_dots(self, ty, w, n_in, n_out, x, m=1):
+        w, x = _u8(w), _f32(x).reshape(-1)
+        dots = np.empty((m, n_out, n_in // 32), dtype=np.int32)
+        rc = self._l.apk_debug_block_dots(self._h, w.ctypes.data, ty, n_in, n_out, x.ctypes.data, m,
+                                          dots.ctypes.data)
+        return dots if self._check(rc) else None
+
+    def debug_q8_acts(self, x, gamma=None, eps=0.0):
+        x = _f32(x).reshape(-1)
+        gamma = None if gamma is None else _f32(gamma)
+        d = np.empty(x.size // 32, np.float32)
+        s = np.empty(x.size // 32, np.float32)
+        q = np.empty(x.size, np.int8)
+        rc = self._l.apk_debug_q8_acts(self._h, x.ctypes.data, x.size, _ptr(gamma), eps, d.ctypes.data,
+                                       s.ctypes.data, q.ctypes.data)
+        return (d, s, q) if self._check(rc) else None
+
+    # -- gpu::stats / decode_path_stats (common.rs:24-31, types.rs:271-278) --
+    def stats_full(self) -> dict:
+        st = _Stats()
+        self._l.apk_stats(self._h, C.byref(st))
+        return {n: getattr(st, n) for n, _ in _Stats._fields_}
+
+    def stats(self):
+        s = self.stats_full()
+        return (s["calls"], s["launches"], s["encode_ns"], s["wait_ns"])
+
+    def decode_path_stats(self):
+        s = self.stats_full()
+        return {"attempts": s["decode_attempts"], "successes": s["decode_successes"],
+                "declines": s["decode_declines"]}
+
+    # -- tensor parallel group -------------------------------------------------
+    @staticmethod
+    def dist_unique_id() -> bytes:
+        l = load_library()
+        buf = C.create_string_buffer(128)
+        rc = l.apk_dist_unique_id(buf)
+        if rc != 0:
+            raise GpuError(rc, l.apk_last_error(None).decode())
+        return buf.raw
+
+    def dist_init(self, rank: int, world: int, unique_id: bytes) -> None:
+        buf = C.create_string_buffer(unique_id, 128)
+        rc = self._l.apk_dist_init(self._h, rank, world, buf)
+        if rc != 0:
+            raise GpuError(rc, self._err())
+
+
+# ---------------------------------------------------------------- module API
+_GPU: Optional[Gpu] = None
+
+
+def _gpu() -> Gpu:
+    global _GPU
+    if _GPU is None:
+        _GPU = Gpu()
+    return _GPU
+
+
+def attach(mapping) -> bool:
+    return _gpu().attach(mapping)
+
+
+def detach(mapping) -> None:
+    _gpu().detach(mapping)
+
+
+def is_attached() -> bool:
+    return _GPU is not None and _GPU.is_attached()
+
+
+def matvec(ty, w, n_in, n_out, x):
+    """gpu::matvec: one activation row, Q8 activations (m == 1)."""
+    y = _gpu().matvec(ty, w, n_in, n_out, x, 1, ACT_AUTO)
+    return None if y is None else y[0]
+
+
+def matvec_batch(reqs, act_mode=ACT_Q8):
+    return _gpu().matvec_batch(reqs, act_mode)
+
+
+def ffn_batch(reqs):
+    return _gpu().ffn_batch(reqs)
+
+
+def decode_token_checked(req):
+    return _gpu().decode_token_checked(req)
+
+
+def decode_token(req):
+    return _gpu().decode_token(req)
+
+
+def stats():
+    return _gpu().stats() if _GPU is not None else (0, 0, 0, 0)
+
+
+def decode_path_stats():
+    return _gpu().decode_path_stats()

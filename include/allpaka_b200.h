@@ -1,0 +1,236 @@
+/*
+ * allpaka_b200.h -- C ABI of libapk_b200.so, the sm_100a decode dequant-matvec
+ * path for the allpaka engine.
+ *
+ * Every entry point is what an `allpaka-b200-sys` FFI crate binds so that
+ * allpaka-backend's accelerator module (`crate::gpu::*`, the free-function
+ * surface every backend implements: crates/allpaka-backend/src/gpu/mod.rs:9-26,
+ * spelled out by gpu/stub.rs:37-217) can forward to it.  Conventions follow the
+ * engine's existing native shim (third_party/allpaka_ggml/allpaka_ggml.h:16-152):
+ * `extern "C"`, plain pointers and sizes, int status, no callbacks, no
+ * unwinding, nothing allocated here is freed by the caller.
+ *
+ * Ownership: all pointer arguments are borrowed HOST memory, valid only for the
+ * call.  Weights are identified by their host address inside an attached
+ * mapping, exactly like the reference CUDA backend (gpu/cuda/runtime/
+ * select.rs:80-84); the library keeps a repacked device copy until the mapping
+ * is detached.  There is no CPU fallback: a supported request either runs on
+ * the GPU or returns an error.
+ *
+ * Threading: one internal mutex per context; calls may come from any thread and
+ * are serialised (the reference: one process-wide Mutex<CudaGpu>,
+ * gpu/cuda/runtime/device.rs:267, 944-948).
+ */
+#ifndef ALLPAKA_B200_H
+#define ALLPAKA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes -------------------------------------------------------
+ * 0 = executed.  1..7 = declined, nothing happened; the values are the
+ * variants of allpaka-backend's DeclineReason (src/accel.rs:10-36).
+ * Negative = a hard error; the context stays usable unless stated. */
+#define APK_OK 0
+#define APK_DECLINE_NO_DEVICE 1
+#define APK_DECLINE_UNSUPPORTED_TYPE 2
+#define APK_DECLINE_UNSUPPORTED_SHAPE 3
+#define APK_DECLINE_FOREIGN_MEMORY 4
+#define APK_DECLINE_MISSING_CAPABILITY 5
+#define APK_DECLINE_INVALID_STATE 6
+#define APK_DECLINE_BACKEND 7
+#define APK_ERR_INVALID_ARG (-1)
+#define APK_ERR_CUDA (-2)
+#define APK_ERR_TIMEOUT (-3) /* a bounded device-side wait expired */
+#define APK_ERR_NCCL (-4)
+#define APK_ERR_OOM (-5)
+
+/* GGML type ids (crates/allpaka-dtype/src/lib.rs:61-75). */
+#define APK_TY_Q8_0 8u
+#define APK_TY_Q4_K 12u
+
+/* How activations meet the integer weights.  The reference picks this by call
+ * site, not by dtype (crates/allpaka-backend/src/quantmat/mod.rs):
+ *   APK_ACT_Q8   Q8Acts::from_f32 per row + int32 block dots: every m == 1
+ *                matvec (mod.rs:224-267) and every matmul_many item at any m
+ *                (mod.rs:314-419).  Block dots are bit-exact.
+ *   APK_ACT_F32  f32 row dots: QuantMat::matmul with m > 1 (mod.rs:156-213).
+ *                Computed here with two-level int8 activations (error ~2e-5
+ *                relative, far inside the 2e-3 bar).
+ *   APK_ACT_AUTO what QuantMat::matmul does: m == 1 -> Q8, m > 1 -> F32. */
+#define APK_ACT_Q8 0u
+#define APK_ACT_F32 1u
+#define APK_ACT_AUTO 2u
+
+#define APK_MAX_M 8u /* speculative verify batches are m = K+1 <= 8 (model/decode.rs:140-225) */
+
+typedef struct apk_ctx apk_ctx;
+
+/* One context = one GPU (one process per GPU; ranks of a tensor-parallel
+ * group each own one).  device < 0 picks LOCAL_RANK or 0.
+ * Replaces the lazy GPU singleton, gpu/cuda/runtime/device.rs:934-948. */
+int apk_init(apk_ctx **out, int device);
+void apk_shutdown(apk_ctx *ctx);
+
+/* gpu::attach / detach / is_attached (stub.rs:37-45; cuda/mod.rs:41-66).
+ * Attach is refcounted per (base,len) and uploads nothing; matrices inside the
+ * range are repacked and uploaded at their first use or by
+ * apk_register_matrix.  Detach at refcount 0 frees every device copy whose
+ * host bytes lie in the range. */
+int apk_attach(apk_ctx *ctx, const void *host_base, size_t len);
+int apk_detach(apk_ctx *ctx, const void *host_base, size_t len);
+int apk_is_attached(apk_ctx *ctx);
+
+/* Optional eager form of what the first matvec does lazily: repack the
+ * [n_out, n_in] matrix at w (raw GGUF blocks, crates/allpaka-backend/src/
+ * quantmat/mod.rs:39-65 geometry rules) into the tiled device stream. */
+int apk_register_matrix(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_out, uint32_t n_in);
+
+/* gpu::matvec (stub.rs:87-95) and one item of gpu::matvec_batch
+ * (stub.rs:97-99, MatvecReq gpu/types.rs:9-16): y[m][n_out] = x[m][n_in] . W^T. */
+int apk_matvec(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_in, uint32_t n_out,
+               const float *x, uint32_t m, uint32_t act_mode, float *y);
+
+typedef struct {
+    uint32_t ty;
+    const void *w;
+    uint32_t n_in, n_out;
+    const float *x; /* m * n_in */
+    uint32_t m;
+} apk_matvec_req; /* MatvecReq, gpu/types.rs:9-16 */
+
+/* gpu::matvec_batch (stub.rs:97-99): several matmuls, one submission.  Items
+ * that share x (QKV, gate/up) share one activation quantisation, as the CPU
+ * path does (quantmat/mod.rs:372-388).  act_mode applies to every item
+ * (matmul_many -> APK_ACT_Q8; a single matmul -> APK_ACT_AUTO). */
+int apk_matvec_batch(apk_ctx *ctx, const apk_matvec_req *reqs, uint32_t n_reqs, uint32_t act_mode,
+                     float *const *ys);
+
+typedef struct {
+    uint32_t gate_ty; const void *gate_w;
+    uint32_t up_ty; const void *up_w;
+    uint32_t down_ty; const void *down_w;
+    uint32_t hidden, ffn;
+    const float *x; /* m * hidden */
+    uint32_t m;
+} apk_ffn_req; /* FfnReq, gpu/types.rs:20-31 */
+
+/* One item of gpu::ffn_batch (stub.rs:101-103): y = swiglu(x.G^T, x.U^T).D^T.
+ * gate/up: Q8 activations (matmul_many); down: Q8 at m == 1, F32 at m > 1
+ * (model/moe.rs:120-128).  y is m * hidden. */
+int apk_ffn(apk_ctx *ctx, const apk_ffn_req *req, float *y);
+
+typedef struct {
+    uint32_t ty; /* wq, wk, wv share a type */
+    const void *wq, *wk, *wv;
+    uint32_t hidden, head_dim, n_heads, n_kv_heads;
+    const float *x;      /* m * hidden (the layer input; normed here when gamma != NULL) */
+    uint32_t m;
+    const float *gamma;  /* attn_norm weight [hidden] or NULL */
+    float eps;
+    const float *q_norm; /* per-head norms [head_dim] or NULL */
+    const float *k_norm;
+    const float *rope;   /* (sin, cos) pairs: m rows of rot_dim/2 entries */
+    uint32_t rot_dim;    /* <= head_dim; NeoX split-half pairing */
+} apk_attn_in_req;
+
+/* The input half of gpu::attn_block (stub.rs:146-148, AttnBlockReq
+ * gpu/types.rs:54-80): RMSNorm -> fused Q/K/V matvec -> per-head norm -> NeoX
+ * RoPE, the part of the block that is dequant-matvec work
+ * (model/decode.rs:478, 548-552; model/attention.rs:131-165).
+ * q is m * n_heads*head_dim, k and v are m * n_kv_heads*head_dim. */
+int apk_attn_in(apk_ctx *ctx, const apk_attn_in_req *req, float *q, float *k, float *v);
+
+typedef struct {
+    uint32_t ty;
+    const void *w;
+    uint32_t n_out;
+} apk_mat; /* the (GgmlType, bytes, n_out) descriptor tuple, quantmat/mod.rs:499-502 */
+
+typedef struct {
+    const float *attn_norm, *ffn_norm; /* hidden floats each */
+    apk_mat wq, wk, wv, wo;
+    const float *q_norm, *k_norm;      /* optional, head_dim floats */
+    apk_mat gate, up, down;            /* TokenFfn::Dense */
+} apk_token_layer; /* TokenLayer, gpu/types.rs:111-150 (dense attention layers) */
+
+#define APK_ATTN_IDENTITY 1u /* attention core = identity on the roped Q slice */
+
+typedef struct {
+    const apk_token_layer *layers;
+    uint32_t n_layers;
+    const float *output_norm; /* hidden floats */
+    apk_mat output;           /* LM head, n_out = vocab */
+    const float *x;           /* m * hidden input rows */
+    uint32_t m;               /* 1 = decode, 2..8 = speculative verify */
+    const float *rope;        /* m rows of rot_dim/2 (sin,cos) pairs */
+    uint32_t rot_dim;
+    float eps;
+    uint32_t hidden, head_dim, n_heads, n_kv_heads;
+    uint32_t attn_core;       /* APK_ATTN_IDENTITY; a KV-cache attention core is not part of this library */
+    int argmax;               /* 1: return the greedy token per row instead of logits */
+} apk_token_req; /* TokenReq, gpu/types.rs:183-238 */
+
+typedef struct {
+    float *logits;    /* m * vocab, written when argmax == 0 */
+    uint32_t *argmax; /* m ids, written when argmax == 1 */
+} apk_token_out; /* TokenOut, gpu/types.rs:240-252 */
+
+/* gpu::decode_token_checked (stub.rs:150-157): the whole token as one
+ * submission (a replayed CUDA graph).  Layer weights are resolved, fused
+ * (Q|K|V rows, gate/up row interleave) and uploaded at the first call that
+ * names them. */
+int apk_decode_token(apk_ctx *ctx, const apk_token_req *req, apk_token_out *out);
+
+/* Same work with the m*hidden input already in device memory and the result
+ * left there: what a caller that keeps the residual stream on the GPU between
+ * tokens uses, and what the benchmark times as the device-resident number.
+ * `iters` back-to-back replays; returns the elapsed GPU time of all of them
+ * (CUDA events on the launching stream). */
+int apk_decode_replay(apk_ctx *ctx, const apk_token_req *req, uint32_t iters, float *elapsed_ms);
+
+/* Parity instrumentation: the int32 dot of every 32-element block,
+ * dots[(i*n_out + j)*(n_in/32) + b], for Q8-activation mode.  For Q4_K block
+ * b = 8*superblock + sub-block. */
+int apk_debug_block_dots(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_in, uint32_t n_out,
+                         const float *x, uint32_t m, int32_t *dots);
+
+/* Parity instrumentation: the Q8 activation blocks the kernels consume
+ * (Q8Acts::from_f32 semantics, quantmat/q8_acts.rs:26-63), optionally after
+ * the fused RMSNorm (gamma != NULL).  d and sum are n/32 floats, q n bytes. */
+int apk_debug_q8_acts(apk_ctx *ctx, const float *x, uint32_t n, const float *gamma, float eps,
+                      float *d, float *sum, int8_t *q);
+
+typedef struct {
+    uint64_t calls;      /* entry-point submissions (gpu::stats().0, gpu/common.rs:24-31) */
+    uint64_t launches;   /* kernels launched by this library (".1 dispatches") */
+    uint64_t encode_ns;  /* host time spent building submissions */
+    uint64_t wait_ns;    /* host time blocked on the GPU */
+    uint64_t weight_bytes;   /* repacked device bytes resident */
+    uint64_t decode_attempts, decode_successes, decode_declines; /* DecodePathStats, gpu/types.rs:258-285 */
+} apk_stats_t;
+
+void apk_stats(apk_ctx *ctx, apk_stats_t *out);
+
+/* Human-readable reason for the last non-zero status on this thread
+ * (gpu::init_error, stub.rs:51-53; DecodeDecline{stage,reason} gpu/types.rs:247-252). */
+const char *apk_last_error(apk_ctx *ctx);
+
+/* ---- tensor parallelism over one NVLink domain ----------------------------
+ * No counterpart in the reference (its only multi-device scheme is layer
+ * pipelining over TCP, crates/allpaka-model/src/pipeline.rs).  Every rank
+ * calls the same entry points with the same host tensors; each uploads only
+ * its shard (column-parallel Q|K|V and gate/up, row-parallel wo and down) and
+ * the partial sums are combined across ranks after wo and down. */
+#define APK_UNIQUE_ID_BYTES 128
+int apk_dist_unique_id(void *id_out /* APK_UNIQUE_ID_BYTES */);
+int apk_dist_init(apk_ctx *ctx, int rank, int world, const void *unique_id);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
