@@ -166,6 +166,8 @@ def test_matvec_batch_shares_one_activation_quantisation(gpu, orc):
     r = attach(gpu, *ws)
     x = synth.normal_f32((3, hidden), 33)
     reqs = [MatvecReq(Q8_0, v, hidden, n, x, 3) for v, n in zip(r.views, (512, 128, 128))]
+    for v, n in zip(r.views, (512, 128, 128)):
+        assert gpu.register_matrix(v, Q8_0, n, hidden)  # uploads happen here, not in the count below
     calls0 = gpu.stats()[1]
     ys = gpu.matvec_batch(reqs)
     assert gpu.stats()[1] - calls0 == 4  # one activation pass, three matvecs
