@@ -194,6 +194,8 @@ struct apk_ctx {
     int rank = 0, world = 1;
     void *comm = nullptr;
     std::unique_ptr<Plan> plan;
+    // host address -> device-resident raw GGUF bytes written by apk_debug_synth_matrix
+    std::map<const uint8_t *, std::pair<uint8_t *, size_t>> raw_dev;
 };
 
 namespace {
@@ -262,6 +264,15 @@ size_t host_bytes(uint32_t ty, uint32_t n_out, uint32_t n_in) {
     return (size_t)n_out * (n_in / be) * bb;
 }
 
+// Device-resident stand-in for host bytes [p, p+len), if a generator put one there.
+const uint8_t *raw_lookup(apk_ctx *c, const uint8_t *p, size_t len) {
+    auto it = c->raw_dev.upper_bound(p);
+    if (it == c->raw_dev.begin()) return nullptr;
+    --it;
+    if (p >= it->first && p + len <= it->first + it->second.second) return it->second.first + (p - it->first);
+    return nullptr;
+}
+
 // Build a device matrix of n_out x n_in from row segments of host matrices.
 int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const std::vector<Segment> &segs,
                  std::unique_ptr<DevMatrix> *out) {
@@ -295,8 +306,14 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
         APK_TRY(c->staging.ensure(std::min<size_t>(slab_rows, s.rows) * seg_row_bytes));
         for (size_t r0 = 0; r0 < s.rows; r0 += slab_rows) {
             const size_t nr = std::min<size_t>(slab_rows, s.rows - r0);
-            CUDA_TRY(cudaMemcpy2DAsync(c->staging.p, seg_row_bytes, src + r0 * full_row_bytes, full_row_bytes,
-                                       seg_row_bytes, nr, cudaMemcpyHostToDevice, c->stream));
+            const uint8_t *from = src + r0 * full_row_bytes;
+            cudaMemcpyKind kind = cudaMemcpyHostToDevice;
+            if (const uint8_t *dev = raw_lookup(c, from, (nr - 1) * full_row_bytes + seg_row_bytes)) {
+                from = dev;
+                kind = cudaMemcpyDeviceToDevice;
+            }
+            CUDA_TRY(cudaMemcpy2DAsync(c->staging.p, seg_row_bytes, from, full_row_bytes, seg_row_bytes, nr, kind,
+                                       c->stream));
             RepackParams rp;
             rp.src = c->staging.as<uint8_t>();
             rp.src_row_bytes = seg_row_bytes;
@@ -587,6 +604,8 @@ void apk_shutdown(apk_ctx *c) {
     if (c->stream) cudaStreamSynchronize(c->stream);
     c->plan.reset();
     c->mats.clear();
+    for (auto &kv : c->raw_dev) cudaFree(kv.second.first);
+    c->raw_dev.clear();
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
     for (DevBuf *b : {&c->staging, &c->partials, &c->counters, &c->x_dev, &c->y_dev, &c->act_a, &c->act_b, &c->misc, &c->dump})
         b->release();
@@ -837,6 +856,48 @@ int apk_attn_in(apk_ctx *c, const apk_attn_in_req *r, float *q, float *k, float 
     c->st.encode_ns += now_ns() - t0;
     c->st.calls++;
     return finish(c);
+}
+
+int apk_debug_synth_matrix(apk_ctx *c, void *w, uint32_t ty, uint32_t n_out, uint32_t n_in, uint64_t seed,
+                           int write_host) {
+    if (!c || !w) return fail(APK_ERR_INVALID_ARG, "synth: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    APK_TRY(check_host_matrix(c, "synth", w, ty, n_out, n_in));
+    const size_t bytes = host_bytes(ty, n_out, n_in);
+    const size_t n_blocks = bytes / (ty == APK_TY_Q8_0 ? 34 : 144);
+    uint8_t *d = nullptr;
+    CUDA_TRY(cudaMalloc((void **)&d, bytes));
+    const unsigned blocks = (unsigned)((n_blocks + 255) / 256);
+    if (ty == APK_TY_Q8_0)
+        synth_q8_0_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
+    else
+        synth_q4_k_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
+    c->st.launches++;
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess && write_host) e = cudaMemcpyAsync(w, d, bytes, cudaMemcpyDeviceToHost, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) {
+        cudaFree(d);
+        return fail(APK_ERR_CUDA, "synth: %s", cudaGetErrorString(e));
+    }
+    auto old = c->raw_dev.find((const uint8_t *)w);
+    if (old != c->raw_dev.end()) {
+        cudaFree(old->second.first);
+        c->raw_dev.erase(old);
+    }
+    c->raw_dev[(const uint8_t *)w] = {d, bytes};
+    return APK_OK;
+}
+
+int apk_debug_synth_release(apk_ctx *c) {
+    if (!c) return fail(APK_ERR_INVALID_ARG, "null context");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    CUDA_TRY(cudaStreamSynchronize(c->stream));
+    for (auto &kv : c->raw_dev) cudaFree(kv.second.first);
+    c->raw_dev.clear();
+    return APK_OK;
 }
 
 void apk_stats(apk_ctx *c, apk_stats_t *out) {

@@ -105,7 +105,6 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
     CUDA_TRY(cudaMemcpy(P->norms.p, norms.data(), norms.size() * sizeof(float), cudaMemcpyHostToDevice));
 
     P->L.resize(r->n_layers);
-    uint32_t max_ty_q4 = 0;
     for (uint32_t l = 0; l < r->n_layers; ++l) {
         const apk_token_layer &tl = r->layers[l];
         PlanLayer &pl = P->L[l];
@@ -125,8 +124,6 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
         pl.ffn_norm = b + H;
         pl.q_norm = tl.q_norm ? b + 2 * H : nullptr;
         pl.k_norm = tl.k_norm ? b + 2 * H + 128 : nullptr;
-        if (tl.wq.ty == APK_TY_Q4_K || tl.wo.ty == APK_TY_Q4_K || tl.gate.ty == APK_TY_Q4_K || tl.down.ty == APK_TY_Q4_K)
-            max_ty_q4 = 1;
     }
     {
         int rc;
@@ -136,7 +133,6 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
 
     const uint32_t M = APK_MAX_M, ldq = P->nq_l + 2 * P->nkv_l;
     const uint32_t big = APK_TY_Q4_K;  // the larger record flavour bounds every buffer
-    (void)max_ty_q4;
     APK_TRY(P->xin.ensure((size_t)M * H * 4));
     APK_TRY(P->x[0].ensure((size_t)M * H * 4));
     APK_TRY(P->x[1].ensure((size_t)M * H * 4));
@@ -320,6 +316,74 @@ int apk_decode_token(apk_ctx *c, const apk_token_req *r, apk_token_out *out) {
                 memcpy(out->logits + (size_t)i * P->vocab + (size_t)rk * P->vocab_l,
                        gathered.data() + ((size_t)rk * m + i) * P->vocab_l, (size_t)P->vocab_l * 4);
     c->st.decode_successes++;
+    return APK_OK;
+}
+
+int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float *ms, double *bytes) {
+    if (!c || !ms || !bytes || reps == 0) return fail(APK_ERR_INVALID_ARG, "profile: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    APK_TRY(validate_token_req(c, r));
+    APK_TRY(ensure_graph(c, r));
+    Plan *P = c->plan.get();
+    const uint32_t m = r->m, H = P->hidden, ldq = P->nq_l + 2 * P->nkv_l;
+    // one real token first, so every activation buffer the kernels read holds sane data
+    CUDA_TRY(cudaMemcpyAsync(P->xin.p, r->x, (size_t)m * H * 4, cudaMemcpyHostToDevice, c->stream));
+    if (r->rot_dim)
+        CUDA_TRY(cudaMemcpyAsync(P->rope.p, r->rope, (size_t)m * (r->rot_dim / 2) * 2 * 4, cudaMemcpyHostToDevice, c->stream));
+    CUDA_TRY(cudaGraphLaunch(P->exec[m][r->argmax ? 1 : 0], c->stream));
+    APK_TRY(finish(c));
+    const ActMode q8{0, (int)m};
+    const ActMode autom = resolve_mode(APK_ACT_AUTO, m);
+    auto orig_bytes = [](const DevMatrix *W) {
+        return (double)W->n_out * (W->n_in / (W->ty == APK_TY_Q8_0 ? 32 : 256)) * (W->ty == APK_TY_Q8_0 ? 34 : 144);
+    };
+    for (int kind = 0; kind < 5; ++kind) {
+        const uint32_t n_launch = kind == 4 ? 1 : P->n_layers;
+        CUDA_TRY(cudaEventRecord(c->ev0, c->stream));
+        for (uint32_t rep = 0; rep < reps; ++rep)
+            for (uint32_t l = 0; l < n_launch; ++l) {
+                PlanLayer &L = P->L[l];
+                MvParams p{};
+                if (kind == 0) {
+                    p.act = act_layout(P->act_h.p, L.qkv->ty, q8.m_eff);
+                    p.epi = EPI_QKV_ROPE;
+                    p.y = P->qkv.as<float>(); p.ldy = (int)ldq;
+                    p.n_q_tiles = (int)(P->nq_l / TILE_ROWS); p.n_k_tiles = (int)(P->nkv_l / TILE_ROWS);
+                    p.q_norm = L.q_norm; p.k_norm = L.k_norm; p.eps = P->eps;
+                    p.rope = P->rope.as<float>(); p.half = (int)(P->rot_dim / 2);
+                    APK_TRY(launch_matvec(c, L.qkv, p, q8));
+                } else if (kind == 1) {
+                    APK_TRY(launch_matvec(c, L.wo, mv_store(act_layout(P->act_q.p, L.wo->ty, autom.m_eff), P->yp.as<float>(), (int)H), autom));
+                } else if (kind == 2) {
+                    p.act = act_layout(P->act_h.p, L.gateup->ty, q8.m_eff);
+                    p.epi = EPI_SWIGLU;
+                    p.act_next = act_layout(P->act_d.p, L.down->ty, autom.m_eff);
+                    p.next_two_level = autom.two_level;
+                    p.next_need_sum = L.down->ty == APK_TY_Q4_K;
+                    p.ffn = (int)P->ffn_l;
+                    APK_TRY(launch_matvec(c, L.gateup, p, q8));
+                } else if (kind == 3) {
+                    APK_TRY(launch_matvec(c, L.down, mv_store(act_layout(P->act_d.p, L.down->ty, autom.m_eff), P->yp.as<float>(), (int)H), autom));
+                } else {
+                    APK_TRY(launch_matvec(c, P->head, mv_store(act_layout(P->act_h.p, P->head->ty, autom.m_eff), P->logits.as<float>(), (int)P->vocab_l), autom));
+                }
+            }
+        CUDA_TRY(cudaEventRecord(c->ev1, c->stream));
+        APK_TRY(finish(c));
+        float t = 0.f;
+        CUDA_TRY(cudaEventElapsedTime(&t, c->ev0, c->ev1));
+        ms[kind] = t / (float)(reps * n_launch);
+        const PlanLayer &L0 = P->L[0];
+        const DevMatrix *W = kind == 0 ? L0.qkv : kind == 1 ? L0.wo : kind == 2 ? L0.gateup : kind == 3 ? L0.down : P->head;
+        // weights as stored in the GGUF file (padding rows of the tiled stream are not counted)
+        double wb = orig_bytes(W);
+        if (kind == 2) wb = 2.0 * (double)P->ffn_l * (H / 32) * (W->ty == APK_TY_Q8_0 ? 34 : 144 / 8.0);
+        const double in_b = (double)m * W->n_in * 4.0;
+        const double out_b = kind == 2 ? (double)m * P->ffn_l * 4.0 : (double)m * W->n_out * 4.0;
+        bytes[kind] = wb + in_b + out_b;
+    }
+    c->st.calls++;
     return APK_OK;
 }
 

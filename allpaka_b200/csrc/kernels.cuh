@@ -369,6 +369,59 @@ __global__ void repack_q4_k_kernel(RepackParams p) {
         make_uint4(w[0], w[1], w[2], w[3]);
 }
 
+// ------------------------------------------------- synthetic weights (bench)
+//
+// Counter-based generator for benchmark tensors: raw GGUF blocks are produced
+// on the device so a multi-gigabyte synthetic model needs no host generation.
+// Q8_0: quants uniform in [-127,127], scale f16(|N(0,0.02)|/127).
+// Q4_K: nibbles, 6-bit scales and mins uniform, d and dmin f16(|N(0,0.002)|).
+__device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
+    x += 0x9E3779B97F4A7C15ull;
+    x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+    x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+    return x ^ (x >> 31);
+}
+__device__ __forceinline__ float absnormal(uint64_t h, float sigma) {
+    const float u1 = ((float)(uint32_t)(h >> 40) + 1.0f) * (1.0f / 16777217.0f);
+    const float u2 = (float)(uint32_t)(h & 0xffffffu) * (1.0f / 16777216.0f);
+    return fabsf(sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2)) * sigma;
+}
+// one thread per block of the raw row-major GGUF layout
+__global__ void synth_q8_0_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    uint8_t *o = dst + b * 34;
+    const uint64_t base = splitmix64(seed) ^ (b * 0x9E3779B97F4A7C15ull);
+    const __half d = __float2half_rn(absnormal(splitmix64(base ^ 0x51ull), 0.02f) / 127.0f);
+    const unsigned short db = __half_as_ushort(d);
+    o[0] = (uint8_t)(db & 0xff);
+    o[1] = (uint8_t)(db >> 8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint64_t h = splitmix64(base + (uint64_t)i + 1);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const uint32_t u16 = (uint32_t)(h >> (16 * j)) & 0xffffu;
+            o[2 + i * 4 + j] = (uint8_t)(int8_t)((int)((u16 * 255u) >> 16) - 127);
+        }
+    }
+}
+__global__ void synth_q4_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    uint8_t *o = dst + b * 144;
+    const uint64_t base = splitmix64(seed) ^ (b * 0x9E3779B97F4A7C15ull);
+    const unsigned short d = __half_as_ushort(__float2half_rn(absnormal(splitmix64(base ^ 0x51ull), 0.002f)));
+    const unsigned short dm = __half_as_ushort(__float2half_rn(absnormal(splitmix64(base ^ 0x52ull), 0.002f)));
+    o[0] = (uint8_t)(d & 0xff); o[1] = (uint8_t)(d >> 8);
+    o[2] = (uint8_t)(dm & 0xff); o[3] = (uint8_t)(dm >> 8);
+    for (int i = 0; i < 140 / 4; ++i) {
+        const uint32_t h = (uint32_t)splitmix64(base + (uint64_t)i + 1);
+        o[4 + i * 4 + 0] = (uint8_t)h; o[4 + i * 4 + 1] = (uint8_t)(h >> 8);
+        o[4 + i * 4 + 2] = (uint8_t)(h >> 16); o[4 + i * 4 + 3] = (uint8_t)(h >> 24);
+    }
+}
+
 // ------------------------------------------------------------ the matvec
 
 __device__ __forceinline__ void scale_min_k4_dev(int j, uint32_t s0, uint32_t s1, uint32_t s2, float &sc,

@@ -106,6 +106,7 @@ EXPORTS = (
     "apk_register_matrix", "apk_matvec", "apk_matvec_batch", "apk_ffn", "apk_attn_in",
     "apk_decode_token", "apk_decode_replay", "apk_debug_block_dots", "apk_debug_q8_acts",
     "apk_stats", "apk_last_error", "apk_dist_unique_id", "apk_dist_init",
+    "apk_debug_synth_matrix", "apk_debug_synth_release", "apk_decode_profile",
 )
 
 _lib = None
@@ -138,6 +139,10 @@ def load_library() -> C.CDLL:
                                        C.c_void_p, C.c_uint32, C.c_void_p]
     l.apk_debug_q8_acts.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_float,
                                     C.c_void_p, C.c_void_p, C.c_void_p]
+    l.apk_debug_synth_matrix.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
+                                         C.c_uint64, C.c_int]
+    l.apk_debug_synth_release.argtypes = [C.c_void_p]
+    l.apk_decode_profile.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
     l.apk_stats.argtypes = [C.c_void_p, C.c_void_p]
     l.apk_stats.restype = None
     l.apk_last_error.argtypes = [C.c_void_p]
@@ -441,6 +446,31 @@ class Gpu:
         rc = self._l.apk_debug_q8_acts(self._h, x.ctypes.data, x.size, _ptr(gamma), eps, d.ctypes.data,
                                        s.ctypes.data, q.ctypes.data)
         return (d, s, q) if self._check(rc) else None
+
+    # -- benchmark utilities --------------------------------------------------
+    def synth_matrix(self, w: np.ndarray, ty: int, n_out: int, n_in: int, seed: int,
+                     write_host: bool = False) -> None:
+        """Fill the matrix whose host bytes are `w` from the on-device generator."""
+        rc = self._l.apk_debug_synth_matrix(self._h, w.ctypes.data, ty, n_out, n_in, seed,
+                                            1 if write_host else 0)
+        if rc != 0:
+            raise GpuError(rc, self._err())
+
+    def synth_release(self) -> None:
+        rc = self._l.apk_debug_synth_release(self._h)
+        if rc != 0:
+            raise GpuError(rc, self._err())
+
+    def decode_profile(self, req: "TokenReq", reps: int = 1):
+        """Per-launch GPU ms and algorithmic bytes of the five matvec kinds of a token."""
+        creq, keep = self._token_req(req)
+        ms = np.zeros(5, np.float32)
+        by = np.zeros(5, np.float64)
+        rc = self._l.apk_decode_profile(self._h, C.byref(creq), reps, ms.ctypes.data, by.ctypes.data)
+        if rc != 0:
+            raise GpuError(rc, self._err())
+        names = ("qkv", "wo", "gate_up", "down", "lm_head")
+        return {n: {"ms": float(t), "bytes": float(b)} for n, t, b in zip(names, ms, by)}
 
     # -- gpu::stats / decode_path_stats (common.rs:24-31, types.rs:271-278) --
     def stats_full(self) -> dict:

@@ -205,6 +205,25 @@ int apk_debug_block_dots(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_in
 int apk_debug_q8_acts(apk_ctx *ctx, const float *x, uint32_t n, const float *gamma, float eps,
                       float *d, float *sum, int8_t *q);
 
+/* Benchmark utility: a seeded synthetic tensor without host-side generation.
+ * The raw GGUF blocks of the [n_out, n_in] matrix whose host address is w are
+ * produced by a counter-based generator on the device and kept there as the
+ * stand-in for the host bytes: later uploads of (parts of) that host range
+ * copy from it instead of from w.  With write_host != 0 the same bytes are
+ * also stored to w, so a CPU reference can read them.  w must lie inside an
+ * attached mapping.  apk_debug_synth_release drops the stand-ins once every
+ * matrix that needs them has been uploaded. */
+int apk_debug_synth_matrix(apk_ctx *ctx, void *w, uint32_t ty, uint32_t n_out, uint32_t n_in, uint64_t seed,
+                           int write_host);
+int apk_debug_synth_release(apk_ctx *ctx);
+
+/* Benchmark utility: average GPU time of each matvec kernel launch of one
+ * token, by kind, with the kernels launched back to back over all layers
+ * between one CUDA-event pair per kind (no graph).  ms[0..4] = Q|K|V, wo,
+ * gate/up, down, LM head (per launch); bytes[0..4] = algorithmic bytes of one
+ * such launch (original GGUF weight bytes + activations in + results out). */
+int apk_decode_profile(apk_ctx *ctx, const apk_token_req *req, uint32_t reps, float *ms, double *bytes);
+
 typedef struct {
     uint64_t calls;      /* entry-point submissions (gpu::stats().0, gpu/common.rs:24-31) */
     uint64_t launches;   /* kernels launched by this library (".1 dispatches") */
