@@ -736,6 +736,37 @@ int apk_debug_block_dots(apk_ctx *c, const void *w, uint32_t ty, uint32_t n_in, 
     return finish(c);
 }
 
+int apk_debug_matvec_timeline(apk_ctx *c, const void *w, uint32_t ty, uint32_t n_in, uint32_t n_out, const float *x,
+                              uint32_t m, uint64_t *stamps, uint32_t max_ctas, uint32_t *n_ctas) {
+    if (!c || !x || !stamps || !n_ctas) return fail(APK_ERR_INVALID_ARG, "timeline: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    APK_TRY(check_m(m));
+    DevMatrix *W;
+    APK_TRY(resolve_plain(c, "timeline", w, ty, n_out, n_in, SHARD_NONE, &W));
+    const long long U = (long long)W->n_tiles * W->KS;
+    const uint32_t grid = (uint32_t)std::min<long long>(c->n_sm, U);
+    if (grid > max_ctas) return fail(APK_ERR_INVALID_ARG, "timeline: room for %u CTAs, need %u", max_ctas, grid);
+    *n_ctas = grid;
+    const ActMode mode{0, (int)m};
+    APK_TRY(c->x_dev.ensure((size_t)m * n_in * sizeof(float)));
+    APK_TRY(c->y_dev.ensure((size_t)m * n_out * sizeof(float)));
+    APK_TRY(c->dump.ensure((size_t)grid * 8 * sizeof(uint64_t)));
+    APK_TRY(c->act_a.ensure(act_bytes(W->ty, mode.m_eff, W->n_in)));
+    CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, x, (size_t)m * n_in * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    APK_TRY(launch_prep(c, c->x_dev.p, 0, (int)n_in, nullptr, 0, nullptr, 0, nullptr, 0.f, nullptr, 0, n_in, m, W->ty,
+                        mode, c->act_a.p));
+    MvParams p = mv_store(act_layout(c->act_a.p, W->ty, mode.m_eff), c->y_dev.as<float>(), (int)n_out);
+    for (int rep = 0; rep < 3; ++rep) {  // the last of three launches is the one reported (warm)
+        CUDA_TRY(cudaMemsetAsync(c->dump.p, 0, (size_t)grid * 8 * sizeof(uint64_t), c->stream));
+        p.timeline = c->dump.as<unsigned long long>();
+        APK_TRY(launch_matvec(c, W, p, mode));
+    }
+    CUDA_TRY(cudaMemcpyAsync(stamps, c->dump.p, (size_t)grid * 8 * sizeof(uint64_t), cudaMemcpyDeviceToHost, c->stream));
+    c->st.calls++;
+    return finish(c);
+}
+
 int apk_debug_q8_acts(apk_ctx *c, const float *x, uint32_t n, const float *gamma, float eps, float *d, float *sum,
                       int8_t *q) {
     if (!c || !x || !d || !sum || !q) return fail(APK_ERR_INVALID_ARG, "q8_acts: null argument");

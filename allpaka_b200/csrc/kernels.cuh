@@ -84,6 +84,7 @@ struct MvParams {
     int *counters;      // [n_tiles], zero between launches
     int *err;           // error word
     int32_t *dump;      // optional [m_eff][n_out][nb] int32 block dots
+    unsigned long long *timeline;  // optional [gridDim.x][8] globaltimer stamps (trace)
     // epilogue
     int epi;
     float *y; int ldy;
@@ -159,6 +160,11 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
         "[%0], [%1], %2, [%3], %4;" ::"r"(smem_u32(dst)),
         "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
+}
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
 }
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(N_CONSUMERS) : "memory"); }
 
@@ -474,6 +480,8 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     const int NS = p.n_stages;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    unsigned long long *tl = p.timeline ? p.timeline + (size_t)blockIdx.x * 8 : nullptr;
+    if (tl && tid == 0) tl[0] = globaltimer_ns();
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full[s], 1);
@@ -546,6 +554,11 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         if (!aborted && !mbar_wait_bounded(&full[s], ph)) {
             aborted = true;
             if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
+        }
+        if (tl && tid == 0) {
+            if (it == 0) tl[1] = globaltimer_ns();   // first unit landed
+            if (it == 1) tl[2] = globaltimer_ns();
+            if (u + 1 == u_end) tl[3] = globaltimer_ns();  // last unit landed
         }
         if (!aborted) {
             const uint8_t *sw = stages + (size_t)s * stage_bytes;
@@ -673,6 +686,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             epilogue_tile<M>(p, t, red, tid);
         }
         consumer_bar();  // red is reused by the next tile
+        if (tl && tid == 0) tl[4 + (u + 1 == u_end ? 1 : 0)] = globaltimer_ns();  // a flush / the final flush done
     }
 }
 

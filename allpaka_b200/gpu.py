@@ -107,6 +107,7 @@ EXPORTS = (
     "apk_decode_token", "apk_decode_replay", "apk_debug_block_dots", "apk_debug_q8_acts",
     "apk_stats", "apk_last_error", "apk_dist_unique_id", "apk_dist_init",
     "apk_debug_synth_matrix", "apk_debug_synth_release", "apk_decode_profile",
+    "apk_debug_matvec_timeline",
 )
 
 _lib = None
@@ -142,6 +143,8 @@ def load_library() -> C.CDLL:
     l.apk_debug_synth_matrix.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
                                          C.c_uint64, C.c_int]
     l.apk_debug_synth_release.argtypes = [C.c_void_p]
+    l.apk_debug_matvec_timeline.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
+                                            C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
     l.apk_decode_profile.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
     l.apk_stats.argtypes = [C.c_void_p, C.c_void_p]
     l.apk_stats.restype = None
@@ -446,6 +449,15 @@ class Gpu:
         rc = self._l.apk_debug_q8_acts(self._h, x.ctypes.data, x.size, _ptr(gamma), eps, d.ctypes.data,
                                        s.ctypes.data, q.ctypes.data)
         return (d, s, q) if self._check(rc) else None
+
+    def debug_matvec_timeline(self, ty, w, n_in, n_out, x, m=1):
+        """Per-CTA global-timer stamps (ns) of one matvec launch; see the C header."""
+        w, x = _u8(w), _f32(x).reshape(-1)
+        stamps = np.zeros((512, 8), dtype=np.uint64)
+        n = C.c_uint32()
+        rc = self._l.apk_debug_matvec_timeline(self._h, w.ctypes.data, ty, n_in, n_out, x.ctypes.data, m,
+                                               stamps.ctypes.data, 512, C.byref(n))
+        return stamps[: n.value] if self._check(rc) else None
 
     # -- benchmark utilities --------------------------------------------------
     def synth_matrix(self, w: np.ndarray, ty: int, n_out: int, n_in: int, seed: int,

@@ -205,6 +205,13 @@ int apk_debug_block_dots(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_in
 int apk_debug_q8_acts(apk_ctx *ctx, const float *x, uint32_t n, const float *gamma, float eps,
                       float *d, float *sum, int8_t *q);
 
+/* Trace: per-CTA timestamps (GPU global timer, ns) of one matvec launch on
+ * activations already quantised: stamps[cta][8] = {kernel entry, first unit in
+ * shared memory, second unit, last unit, a tile finished, last tile finished,
+ * 0, 0}.  n_ctas receives the grid size. */
+int apk_debug_matvec_timeline(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_in, uint32_t n_out,
+                              const float *x, uint32_t m, uint64_t *stamps, uint32_t max_ctas, uint32_t *n_ctas);
+
 /* Benchmark utility: a seeded synthetic tensor without host-side generation.
  * The raw GGUF blocks of the [n_out, n_in] matrix whose host address is w are
  * produced by a counter-based generator on the device and kept there as the
