@@ -354,6 +354,30 @@ int check_host_matrix(apk_ctx *c, const char *what, const void *w, uint32_t ty, 
     return APK_OK;
 }
 
+int shard_plan(uint32_t kind, uint32_t ty, uint32_t n_out, uint32_t n_in, uint32_t row_granule, int rank, int world,
+               uint32_t out[4]) {
+    uint32_t be, bb;
+    if (!block_geom(ty, &be, &bb)) return fail(APK_DECLINE_UNSUPPORTED_TYPE, "ggml type %u has no kernel", ty);
+    if (world < 1 || rank < 0 || rank >= world) return fail(APK_ERR_INVALID_ARG, "rank %d of %d", rank, world);
+    out[0] = 0; out[1] = n_out; out[2] = 0; out[3] = n_in;
+    if (world == 1 || kind == SHARD_NONE) return APK_OK;
+    if (row_granule == 0) row_granule = 1;
+    if (kind == SHARD_ROWS) {
+        if (n_out % ((uint32_t)world * row_granule))
+            return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "%u rows do not split over %d ranks in bands of %u", n_out, world, row_granule);
+        out[1] = n_out / world;
+        out[0] = rank * out[1];
+    } else if (kind == SHARD_K) {
+        if (n_in % ((uint32_t)world * be))
+            return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "row length %u does not split over %d ranks in %u-element blocks", n_in, world, be);
+        out[3] = n_in / world;
+        out[2] = rank * out[3];
+    } else {
+        return fail(APK_ERR_INVALID_ARG, "unknown shard kind %u", kind);
+    }
+    return APK_OK;
+}
+
 int shard_tag(apk_ctx *c, int kind) { return kind == SHARD_NONE ? 0 : c->rank * 64 + c->world; }
 
 // A single host matrix, whole or sharded for this rank.
@@ -366,18 +390,10 @@ int resolve_plain(apk_ctx *c, const char *what, const void *w, uint32_t ty, uint
     APK_TRY(check_host_matrix(c, what, w, ty, n_out, n_in));
     uint32_t be, bb;
     block_geom(ty, &be, &bb);
-    Segment s{w, n_in, 0, n_out, 0, 1 << 30, 0, 0};
-    uint32_t dn_out = n_out, dn_in = n_in;
-    if (shard == SHARD_ROWS) {
-        if (n_out % c->world) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "%s: %u rows do not split over %d ranks", what, n_out, c->world);
-        dn_out = n_out / c->world;
-        s.row0 = c->rank * dn_out;
-        s.rows = dn_out;
-    } else if (shard == SHARD_K) {
-        if (n_in % (c->world * be)) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "%s: row length %u does not split over %d ranks in %u-element blocks", what, n_in, c->world, be);
-        dn_in = n_in / c->world;
-        s.kblk0 = c->rank * (dn_in / 32);
-    }
+    uint32_t sl[4];
+    APK_TRY(shard_plan((uint32_t)shard, ty, n_out, n_in, 1, c->rank, c->world, sl));
+    Segment s{w, n_in, sl[0], sl[1], sl[2] / 32, 1 << 30, 0, 0};
+    const uint32_t dn_out = sl[1], dn_in = sl[3];
     std::unique_ptr<DevMatrix> m;
     APK_TRY(build_matrix(c, ty, dn_out, dn_in, {s}, &m));
     *out = m.get();
@@ -395,14 +411,14 @@ int resolve_qkv(apk_ctx *c, uint32_t ty, const void *wq, const void *wk, const v
     APK_TRY(check_host_matrix(c, "attn wq", wq, ty, n_q, hidden));
     APK_TRY(check_host_matrix(c, "attn wk", wk, ty, n_kv, hidden));
     APK_TRY(check_host_matrix(c, "attn wv", wv, ty, n_kv, hidden));
-    if ((n_q / TILE_ROWS) % c->world || (n_kv / TILE_ROWS) % c->world)
-        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "attention heads (%u q, %u kv) do not split over %d ranks",
-                    n_q / TILE_ROWS, n_kv / TILE_ROWS, c->world);
-    const uint32_t ql = n_q / c->world, kl = n_kv / c->world;
+    uint32_t sq[4], sk[4];
+    APK_TRY(shard_plan(SHARD_ROWS, ty, n_q, hidden, TILE_ROWS, c->rank, c->world, sq));
+    APK_TRY(shard_plan(SHARD_ROWS, ty, n_kv, hidden, TILE_ROWS, c->rank, c->world, sk));
+    const uint32_t ql = sq[1], kl = sk[1];
     std::vector<Segment> segs = {
-        {wq, hidden, c->rank * ql, ql, 0, 1 << 30, 0, 0},
-        {wk, hidden, c->rank * kl, kl, 0, 1 << 30, 0, (int)ql},
-        {wv, hidden, c->rank * kl, kl, 0, 1 << 30, 0, (int)(ql + kl)},
+        {wq, hidden, sq[0], ql, 0, 1 << 30, 0, 0},
+        {wk, hidden, sk[0], kl, 0, 1 << 30, 0, (int)ql},
+        {wv, hidden, sk[0], kl, 0, 1 << 30, 0, (int)(ql + kl)},
     };
     std::unique_ptr<DevMatrix> m;
     APK_TRY(build_matrix(c, ty, ql + 2 * kl, hidden, segs, &m));
@@ -416,17 +432,18 @@ int resolve_qkv(apk_ctx *c, uint32_t ty, const void *wq, const void *wk, const v
 int resolve_gateup(apk_ctx *c, uint32_t ty, const void *gate, const void *up, uint32_t hidden, uint32_t ffn,
                    DevMatrix **out, uint32_t *ffn_local) {
     MatKey key(KIND_GATEUP, gate, up, nullptr, ty, ffn, hidden, SHARD_ROWS, shard_tag(c, SHARD_ROWS));
-    if (ffn % (c->world * 32))
-        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "ffn width %u does not split over %d ranks in 32-row blocks", ffn, c->world);
-    const uint32_t fl = ffn / c->world;
+    // the band of ffn rows is also the band of `down` columns: split on 32-row (block) boundaries
+    uint32_t sf[4];
+    APK_TRY(shard_plan(SHARD_ROWS, ty, ffn, hidden, 32, c->rank, c->world, sf));
+    const uint32_t fl = sf[1];
     *ffn_local = fl;
     auto it = c->mats.find(key);
     if (it != c->mats.end()) { *out = it->second.get(); return APK_OK; }
     APK_TRY(check_host_matrix(c, "ffn gate", gate, ty, ffn, hidden));
     APK_TRY(check_host_matrix(c, "ffn up", up, ty, ffn, hidden));
     std::vector<Segment> segs = {
-        {gate, hidden, c->rank * fl, fl, 0, 64, 128, 0},
-        {up, hidden, c->rank * fl, fl, 0, 64, 128, 64},
+        {gate, hidden, sf[0], fl, 0, 64, 128, 0},
+        {up, hidden, sf[0], fl, 0, 64, 128, 64},
     };
     const uint32_t tiles = (fl + 63) / 64;
     std::unique_ptr<DevMatrix> m;
@@ -938,6 +955,12 @@ void apk_stats(apk_ctx *c, apk_stats_t *out) {
 }
 
 const char *apk_last_error(apk_ctx *) { return g_last_error.c_str(); }
+
+int apk_shard_plan(uint32_t kind, uint32_t ty, uint32_t n_out, uint32_t n_in, uint32_t row_granule, int rank, int world,
+                   uint32_t out[4]) {
+    if (!out) return fail(APK_ERR_INVALID_ARG, "shard_plan: null out");
+    return shard_plan(kind, ty, n_out, n_in, row_granule, rank, world, out);
+}
 
 int apk_dist_unique_id(void *id_out) {
     if (!id_out) return fail(APK_ERR_INVALID_ARG, "null id buffer");

@@ -107,7 +107,7 @@ EXPORTS = (
     "apk_decode_token", "apk_decode_replay", "apk_debug_block_dots", "apk_debug_q8_acts",
     "apk_stats", "apk_last_error", "apk_dist_unique_id", "apk_dist_init",
     "apk_debug_synth_matrix", "apk_debug_synth_release", "apk_decode_profile",
-    "apk_debug_matvec_timeline",
+    "apk_debug_matvec_timeline", "apk_shard_plan",
 )
 
 _lib = None
@@ -150,6 +150,8 @@ def load_library() -> C.CDLL:
     l.apk_stats.restype = None
     l.apk_last_error.argtypes = [C.c_void_p]
     l.apk_last_error.restype = C.c_char_p
+    l.apk_shard_plan.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, C.c_int,
+                                 C.c_void_p]
     l.apk_dist_unique_id.argtypes = [C.c_void_p]
     l.apk_dist_init.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
     _lib = l
@@ -514,6 +516,21 @@ class Gpu:
         rc = self._l.apk_dist_init(self._h, rank, world, buf)
         if rc != 0:
             raise GpuError(rc, self._err())
+
+
+SHARD_ROWS, SHARD_K = 1, 2
+
+
+def shard_plan(kind: int, ty: int, n_out: int, n_in: int, rank: int, world: int, row_granule: int = 1):
+    """(first row, rows, first column, columns) of the slice `rank` holds; None when
+    the matrix does not divide.  Host arithmetic only: works without a GPU."""
+    out = (C.c_uint32 * 4)()
+    rc = load_library().apk_shard_plan(kind, ty, n_out, n_in, row_granule, rank, world, out)
+    if rc > 0:
+        return None
+    if rc < 0:
+        raise GpuError(rc, load_library().apk_last_error(None).decode())
+    return tuple(int(v) for v in out)
 
 
 # ---------------------------------------------------------------- module API

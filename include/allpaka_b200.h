@@ -252,6 +252,15 @@ const char *apk_last_error(apk_ctx *ctx);
  * calls the same entry points with the same host tensors; each uploads only
  * its shard (column-parallel Q|K|V and gate/up, row-parallel wo and down) and
  * the partial sums are combined across ranks after wo and down. */
+#define APK_SHARD_ROWS 1u /* column-parallel: a contiguous band of output rows (whole 128-row heads for Q|K|V) */
+#define APK_SHARD_K 2u    /* row-parallel: a contiguous band of input columns, on quantisation-block boundaries */
+/* The slice of an [n_out, n_in] matrix that `rank` of `world` holds: out[0..3] =
+ * {first row, rows, first column, columns}.  `row_granule` is 1, or 128 when rows
+ * are attention heads.  Pure host arithmetic (no GPU needed); the uploads use
+ * exactly this function.  Returns APK_DECLINE_UNSUPPORTED_SHAPE when the
+ * matrix does not divide. */
+int apk_shard_plan(uint32_t kind, uint32_t ty, uint32_t n_out, uint32_t n_in, uint32_t row_granule, int rank,
+                   int world, uint32_t out[4]);
 #define APK_UNIQUE_ID_BYTES 128
 int apk_dist_unique_id(void *id_out /* APK_UNIQUE_ID_BYTES */);
 int apk_dist_init(apk_ctx *ctx, int rank, int world, const void *unique_id);
