@@ -192,6 +192,7 @@ struct apk_ctx {
     DevBuf x_dev, y_dev, act_a, act_b, misc, dump;
     apk_stats_t st{};
     int rank = 0, world = 1;
+    bool use_pdl = true;        // ALLPAKA_B200_PDL=0 turns programmatic dependent launch off
     void *comm = nullptr;
     std::unique_ptr<Plan> plan;
     // host address -> device-resident raw GGUF bytes written by apk_debug_synth_matrix
@@ -227,10 +228,6 @@ MvKernel pick_kernel(uint32_t ty, int m_eff, bool dump) {
     if (ty == APK_TY_Q8_0) return dump ? pick_m<TY_Q8_0, true>(m_eff) : pick_m<TY_Q8_0, false>(m_eff);
     if (ty == APK_TY_Q4_K) return dump ? pick_m<TY_Q4_K, true>(m_eff) : pick_m<TY_Q4_K, false>(m_eff);
     return nullptr;
-}
-
-int mv_smem_bytes(int m_eff, int n_stages, int act_rec) {
-    return 256 + 2 * m_eff * TILE_ROWS * 4 + n_stages * (STAGE_W_BYTES + ((act_rec + 127) & ~127));
 }
 
 int init_kernel_attrs(apk_ctx *c) {
@@ -455,6 +452,23 @@ int resolve_gateup(apk_ctx *c, uint32_t ty, const void *gate, const void *up, ui
 
 // --------------------------------------------------------------- launches
 
+// Launch with (optionally) a programmatic dependency on the previous kernel in
+// the stream: the kernel may start early and calls griddepcontrol.wait itself.
+template <class... Args>
+cudaError_t launch_ex(apk_ctx *c, void (*kernel)(Args...), dim3 grid, dim3 block, size_t smem, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = c->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+
 ActLayout act_layout(void *base, uint32_t consumer_ty, int m_eff) {
     ActLayout L;
     L.base = (uint8_t *)base;
@@ -494,12 +508,21 @@ int launch_prep(apk_ctx *c, const void *x, int x_is_bf16, int ldx, const float *
     p.two_level = mode.two_level;
     p.need_sum = cty == APK_TY_Q4_K;
     dim3 grid((n / 32 + 7) / 8, m);
-    prep_acts_kernel<<<grid, 256, 0, c->stream>>>(p);
-    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(launch_ex(c, prep_acts_kernel, grid, dim3(256), 0, c->use_pdl, p, c->use_pdl ? 1 : 0));
     c->st.launches++;
     return APK_OK;
 }
 
+// Stages that fit next to the resident activations (0 = does not fit at all).
+int pick_stages(apk_ctx *c, int m_eff, int pro, int KS, int act_rec) {
+    int ns = 6;
+    while (ns > 0 && mv_smem_total(m_eff, pro, KS, act_rec, ns) > c->smem_optin) --ns;
+    return ns;
+}
+
+// p.pro on entry is the prologue the caller would like; a resident prologue that
+// does not leave room for a useful ring falls back to streaming records (the
+// caller must then have prepared them: see want_resident()).
 int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool dump = false) {
     MvKernel k = pick_kernel(W->ty, mode.m_eff, dump);
     if (!k) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "no kernel for %d activation rows", mode.m_eff);
@@ -515,18 +538,56 @@ int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool
     p.partials = c->partials.as<float>();
     p.counters = c->counters.as<int>();
     p.err = c->d_err;
+    p.pdl = c->use_pdl ? 1 : 0;
     const int act_rec = p.act.rec_bytes();
-    int ns = 6;
-    while (ns > 2 && mv_smem_bytes(mode.m_eff, ns, act_rec) > c->smem_optin) --ns;
-    const int smem = mv_smem_bytes(mode.m_eff, ns, act_rec);
-    if (smem > c->smem_optin) return fail(APK_DECLINE_MISSING_CAPABILITY, "kernel needs %d bytes of shared memory", smem);
+    const int ns = pick_stages(c, mode.m_eff, p.pro, W->KS, act_rec);
+    if (ns < 2) return fail(APK_DECLINE_MISSING_CAPABILITY, "activations of %d rows x %u do not fit in shared memory", mode.m_eff, W->n_in);
     p.n_stages = ns;
+    const int smem = mv_smem_total(mode.m_eff, p.pro, W->KS, act_rec, ns);
     const long long U = (long long)W->n_tiles * W->KS;
     const int grid = (int)std::min<long long>(c->n_sm, U);
-    k<<<grid, MV_THREADS, smem, c->stream>>>(p);
-    CUDA_TRY(cudaGetLastError());
+    CUDA_TRY(launch_ex(c, k, dim3(grid), dim3(MV_THREADS), (size_t)smem, c->use_pdl, (const MvParams)p));
     c->st.launches++;
     return APK_OK;
+}
+
+// Can the whole activation buffer of this matvec live in shared memory with a ring of >= 4 stages?
+bool want_resident(apk_ctx *c, const DevMatrix *W, int m_eff) {
+    ActLayout L = act_layout(nullptr, W->ty, m_eff);
+    return pick_stages(c, m_eff, PRO_LOAD, W->KS, L.rec_bytes()) >= 4;
+}
+
+// Activation source for a matvec on x (device, f32 or bf16): at one token the
+// kernel quantises in its own prologue (with the optional RMSNorm); otherwise
+// the separate pass writes records that are then loaded whole or streamed.
+int stage_acts(apk_ctx *c, const DevMatrix *W, const void *x, int x_is_bf16, int ldx, const float *add, int ldadd,
+               float *xout, int ldxout, const float *gamma, float eps, uint32_t m, ActMode mode, void *act_buf,
+               MvParams *p) {
+    p->act = act_layout(act_buf, W->ty, mode.m_eff);
+    if (m == 1 && W->n_in <= (uint32_t)(N_CONSUMERS * PRO_CH) && want_resident(c, W, mode.m_eff)) {
+        p->pro = PRO_QUANT;
+        PrepParams &pp = p->prep;
+        pp.x = x; pp.x_is_bf16 = x_is_bf16; pp.ldx = ldx;
+        pp.add = add; pp.ldadd = ldadd;
+        pp.xout = xout; pp.ldxout = ldxout;
+        pp.gamma = gamma; pp.eps = eps;
+        pp.hout = nullptr; pp.ldh = 0;
+        pp.n = (int)W->n_in; pp.m = (int)m;
+        pp.out = p->act;
+        pp.two_level = mode.two_level;
+        pp.need_sum = W->ty == APK_TY_Q4_K;
+        return APK_OK;
+    }
+    APK_TRY(launch_prep(c, x, x_is_bf16, ldx, add, ldadd, xout, ldxout, gamma, eps, nullptr, 0, W->n_in, m, W->ty, mode,
+                        act_buf));
+    p->pro = want_resident(c, W, mode.m_eff) ? PRO_LOAD : PRO_STREAM;
+    return APK_OK;
+}
+
+// Activation source for records an earlier epilogue already wrote.
+void use_records(apk_ctx *c, const DevMatrix *W, ActMode mode, void *act_buf, MvParams *p) {
+    p->act = act_layout(act_buf, W->ty, mode.m_eff);
+    p->pro = want_resident(c, W, mode.m_eff) ? PRO_LOAD : PRO_STREAM;
 }
 
 MvParams mv_store(const ActLayout &act, float *y, int ldy) {
@@ -560,16 +621,16 @@ int check_m(uint32_t m) {
     return APK_OK;
 }
 
-// One matvec on device buffers (x already in x_dev): prep + kernel -> y (device).
+// One matvec on device buffers (x already in x_dev): activations + kernel -> y (device).
 int run_matvec_dev(apk_ctx *c, DevMatrix *W, const float *x_dev, uint32_t m, uint32_t act_mode, float *y_dev,
                    bool reuse_act, int32_t *dump) {
     const ActMode mode = resolve_mode(act_mode, m);
-    if (!reuse_act) {
-        APK_TRY(c->act_a.ensure(act_bytes(W->ty, mode.m_eff, W->n_in)));
-        APK_TRY(launch_prep(c, x_dev, 0, (int)W->n_in, nullptr, 0, nullptr, 0, nullptr, 0.f, nullptr, 0, W->n_in, m,
-                            W->ty, mode, c->act_a.p));
-    }
-    MvParams p = mv_store(act_layout(c->act_a.p, W->ty, mode.m_eff), y_dev, (int)W->n_out);
+    MvParams p = mv_store(ActLayout{}, y_dev, (int)W->n_out);
+    APK_TRY(c->act_a.ensure(act_bytes(W->ty, mode.m_eff, W->n_in)));
+    if (reuse_act && m > 1)
+        use_records(c, W, mode, c->act_a.p, &p);
+    else
+        APK_TRY(stage_acts(c, W, x_dev, 0, (int)W->n_in, nullptr, 0, nullptr, 0, nullptr, 0.f, m, mode, c->act_a.p, &p));
     p.dump = dump;
     return launch_matvec(c, W, p, mode, dump != nullptr);
 }
@@ -611,6 +672,7 @@ int apk_init(apk_ctx **out, int device) {
     APK_TRY(c->partials.ensure((size_t)c->n_sm * 2 * MAX_M_EFF * TILE_ROWS * sizeof(float), true));
     APK_TRY(c->counters.ensure(65536 * sizeof(int), true));
     APK_TRY(init_kernel_attrs(c.get()));
+    if (const char *e = getenv("ALLPAKA_B200_PDL")) c->use_pdl = atoi(e) != 0;
     *out = c.release();
     return APK_OK;
 }
@@ -771,14 +833,13 @@ int apk_debug_matvec_timeline(apk_ctx *c, const void *w, uint32_t ty, uint32_t n
     APK_TRY(c->dump.ensure((size_t)grid * 8 * sizeof(uint64_t)));
     APK_TRY(c->act_a.ensure(act_bytes(W->ty, mode.m_eff, W->n_in)));
     CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, x, (size_t)m * n_in * sizeof(float), cudaMemcpyHostToDevice, c->stream));
-    APK_TRY(launch_prep(c, c->x_dev.p, 0, (int)n_in, nullptr, 0, nullptr, 0, nullptr, 0.f, nullptr, 0, n_in, m, W->ty,
-                        mode, c->act_a.p));
-    MvParams p = mv_store(act_layout(c->act_a.p, W->ty, mode.m_eff), c->y_dev.as<float>(), (int)n_out);
-    for (int rep = 0; rep < 3; ++rep) {  // the last of three launches is the one reported (warm)
-        CUDA_TRY(cudaMemsetAsync(c->dump.p, 0, (size_t)grid * 8 * sizeof(uint64_t), c->stream));
-        p.timeline = c->dump.as<unsigned long long>();
-        APK_TRY(launch_matvec(c, W, p, mode));
-    }
+    MvParams p = mv_store(ActLayout{}, c->y_dev.as<float>(), (int)n_out);
+    APK_TRY(stage_acts(c, W, c->x_dev.p, 0, (int)n_in, nullptr, 0, nullptr, 0, nullptr, 0.f, m, mode, c->act_a.p, &p));
+    // Four launches back to back (programmatic dependencies chain them like the layers of
+    // a token); every launch rewrites all stamps, so the last one is what is reported.
+    CUDA_TRY(cudaMemsetAsync(c->dump.p, 0, (size_t)grid * 8 * sizeof(uint64_t), c->stream));
+    p.timeline = c->dump.as<unsigned long long>();
+    for (int rep = 0; rep < 4; ++rep) APK_TRY(launch_matvec(c, W, p, mode));
     CUDA_TRY(cudaMemcpyAsync(stamps, c->dump.p, (size_t)grid * 8 * sizeof(uint64_t), cudaMemcpyDeviceToHost, c->stream));
     c->st.calls++;
     return finish(c);
@@ -837,17 +898,17 @@ int apk_ffn(apk_ctx *c, const apk_ffn_req *r, float *y) {
     APK_TRY(c->act_a.ensure(act_bytes(GU->ty, q8.m_eff, r->hidden)));
     APK_TRY(c->act_b.ensure(act_bytes(D->ty, dmode.m_eff, r->ffn)));
     CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, r->x, (size_t)m * r->hidden * sizeof(float), cudaMemcpyHostToDevice, c->stream));
-    APK_TRY(launch_prep(c, c->x_dev.p, 0, (int)r->hidden, nullptr, 0, nullptr, 0, nullptr, 0.f, nullptr, 0, r->hidden,
-                        m, GU->ty, q8, c->act_a.p));
     MvParams p{};
-    p.act = act_layout(c->act_a.p, GU->ty, q8.m_eff);
+    APK_TRY(stage_acts(c, GU, c->x_dev.p, 0, (int)r->hidden, nullptr, 0, nullptr, 0, nullptr, 0.f, m, q8, c->act_a.p, &p));
     p.epi = EPI_SWIGLU;
     p.act_next = act_layout(c->act_b.p, D->ty, dmode.m_eff);
     p.next_two_level = dmode.two_level;
     p.next_need_sum = D->ty == APK_TY_Q4_K;
     p.ffn = (int)r->ffn;
     APK_TRY(launch_matvec(c, GU, p, q8));
-    APK_TRY(launch_matvec(c, D, mv_store(act_layout(c->act_b.p, D->ty, dmode.m_eff), c->y_dev.as<float>(), (int)r->hidden), dmode));
+    MvParams pd = mv_store(ActLayout{}, c->y_dev.as<float>(), (int)r->hidden);
+    use_records(c, D, dmode, c->act_b.p, &pd);
+    APK_TRY(launch_matvec(c, D, pd, dmode));
     CUDA_TRY(cudaMemcpyAsync(y, c->y_dev.p, (size_t)m * r->hidden * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
     c->st.encode_ns += now_ns() - t0;
     c->st.calls++;
@@ -882,10 +943,9 @@ int apk_attn_in(apk_ctx *c, const apk_attn_in_req *r, float *q, float *k, float 
     if (r->q_norm) CUDA_TRY(cudaMemcpyAsync(misc + o_qn, r->q_norm, 128 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
     if (r->k_norm) CUDA_TRY(cudaMemcpyAsync(misc + o_kn, r->k_norm, 128 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
     if (half) CUDA_TRY(cudaMemcpyAsync(misc + o_rope, r->rope, (size_t)m * half * 2 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
-    APK_TRY(launch_prep(c, c->x_dev.p, 0, (int)H, nullptr, 0, nullptr, 0, r->gamma ? misc : nullptr, r->eps, nullptr, 0,
-                        H, m, W->ty, q8, c->act_a.p));
     MvParams p{};
-    p.act = act_layout(c->act_a.p, W->ty, q8.m_eff);
+    APK_TRY(stage_acts(c, W, c->x_dev.p, 0, (int)H, nullptr, 0, nullptr, 0, r->gamma ? misc : nullptr, r->eps, m, q8,
+                       c->act_a.p, &p));
     p.epi = EPI_QKV_ROPE;
     p.y = c->y_dev.as<float>();
     p.ldy = (int)ld;

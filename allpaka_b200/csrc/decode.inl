@@ -149,88 +149,107 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
     return APK_OK;
 }
 
-// Enqueue one token's work on the stream (called under capture).
-int enqueue_token(apk_ctx *c, Plan *P, uint32_t m, int argmax, int *n_launches) {
-    const uint32_t H = P->hidden, ldq = P->nq_l + 2 * P->nkv_l;
-    const uint64_t l0 = c->st.launches;
-    const bool tp = c->world > 1;
-    const ActMode q8{0, (int)m};
-    const ActMode autom = resolve_mode(APK_ACT_AUTO, m);
+// The four matvecs of a layer and the head, as launches on the context stream.
+// `for_profile` replays one kind in isolation (activations already in place).
+struct TokenLaunch {
+    apk_ctx *c;
+    Plan *P;
+    uint32_t m;
+    ActMode q8, autom;
     int cur = 0;
-    CUDA_TRY(cudaMemcpyAsync(P->x[0].p, P->xin.p, (size_t)m * H * 4, cudaMemcpyDeviceToDevice, c->stream));
     bool pending_add = false;  // tensor parallel: yp holds a combined delta not yet added to x
-    auto prep_norm = [&](const float *gamma, uint32_t cty, ActMode mode) -> int {
+
+    TokenLaunch(apk_ctx *c_, Plan *P_, uint32_t m_) : c(c_), P(P_), m(m_), q8{0, (int)m_}, autom(resolve_mode(APK_ACT_AUTO, m_)) {}
+
+    // activations of a matvec that reads the residual stream through an RMSNorm
+    int normed_input(const DevMatrix *W, const float *gamma, ActMode mode, MvParams *p, bool advance) {
+        const uint32_t H = P->hidden;
         float *xc = P->x[cur].as<float>();
         if (pending_add) {
             float *xn = P->x[cur ^ 1].as<float>();
-            APK_TRY(launch_prep(c, xc, 0, (int)H, P->yp.as<float>(), (int)H, xn, (int)H, gamma, P->eps, nullptr, 0, H, m,
-                                cty, mode, P->act_h.p));
-            cur ^= 1;
-            pending_add = false;
+            APK_TRY(stage_acts(c, W, xc, 0, (int)H, P->yp.as<float>(), (int)H, xn, (int)H, gamma, P->eps, m, mode, P->act_h.p, p));
+            if (advance) { cur ^= 1; pending_add = false; }
             return APK_OK;
         }
-        return launch_prep(c, xc, 0, (int)H, nullptr, 0, nullptr, 0, gamma, P->eps, nullptr, 0, H, m, cty, mode, P->act_h.p);
-    };
-    auto residual_matvec = [&](DevMatrix *W, const ActLayout &act, ActMode mode) -> int {
+        return stage_acts(c, W, xc, 0, (int)H, nullptr, 0, nullptr, 0, gamma, P->eps, m, mode, P->act_h.p, p);
+    }
+    int qkv(PlanLayer &L, bool advance = true) {
         MvParams p{};
-        p.act = act;
-        if (tp) {
+        APK_TRY(normed_input(L.qkv, L.attn_norm, q8, &p, advance));
+        p.epi = EPI_QKV_ROPE;
+        p.y = P->qkv.as<float>();
+        p.ldy = (int)(P->nq_l + 2 * P->nkv_l);
+        p.n_q_tiles = (int)(P->nq_l / TILE_ROWS);
+        p.n_k_tiles = (int)(P->nkv_l / TILE_ROWS);
+        p.q_norm = L.q_norm;
+        p.k_norm = L.k_norm;
+        p.eps = P->eps;
+        p.rope = P->rope.as<float>();
+        p.half = (int)(P->rot_dim / 2);
+        // attention core stand-in (identity): the roped Q slice, packed here, is wo's input
+        p.q_next = act_layout(P->act_q.p, L.wo->ty, autom.m_eff);
+        p.q_next_two_level = autom.two_level;
+        p.q_next_need_sum = L.wo->ty == APK_TY_Q4_K;
+        return launch_matvec(c, L.qkv, p, q8);
+    }
+    int residual(DevMatrix *W, void *records) {
+        const uint32_t H = P->hidden;
+        MvParams p{};
+        use_records(c, W, autom, records, &p);
+        if (c->world > 1) {
             p.epi = EPI_STORE;
             p.y = P->yp.as<float>();
             p.ldy = (int)H;
-            APK_TRY(launch_matvec(c, W, p, mode));
+            APK_TRY(launch_matvec(c, W, p, autom));
             APK_TRY(nccl_allreduce(c, P->yp.as<float>(), (size_t)m * H));
             pending_add = true;
-        } else {
-            p.epi = EPI_ADD;
-            p.y = P->x[cur].as<float>();
-            p.ldy = (int)H;
-            p.resid = P->x[cur].as<float>();
-            p.ldr = (int)H;
-            APK_TRY(launch_matvec(c, W, p, mode));
+            return APK_OK;
         }
-        return APK_OK;
-    };
+        p.epi = EPI_ADD;
+        p.y = P->x[cur].as<float>();
+        p.ldy = (int)H;
+        p.resid = P->x[cur].as<float>();
+        p.ldr = (int)H;
+        return launch_matvec(c, W, p, autom);
+    }
+    int wo(PlanLayer &L) { return residual(L.wo, P->act_q.p); }
+    int gateup(PlanLayer &L, bool advance = true) {
+        MvParams p{};
+        APK_TRY(normed_input(L.gateup, L.ffn_norm, q8, &p, advance));
+        p.epi = EPI_SWIGLU;
+        p.act_next = act_layout(P->act_d.p, L.down->ty, autom.m_eff);
+        p.next_two_level = autom.two_level;
+        p.next_need_sum = L.down->ty == APK_TY_Q4_K;
+        p.ffn = (int)P->ffn_l;
+        return launch_matvec(c, L.gateup, p, q8);
+    }
+    int down(PlanLayer &L) { return residual(L.down, P->act_d.p); }
+    int head(bool advance = true) {
+        // finish_hidden: rmsnorm + output.matmul(x, m) (QuantMat::matmul: Q8 at m == 1, f32 dots above)
+        MvParams p{};
+        APK_TRY(normed_input(P->head, P->out_norm, autom, &p, advance));
+        p.epi = EPI_STORE;
+        p.y = P->logits.as<float>();
+        p.ldy = (int)P->vocab_l;
+        return launch_matvec(c, P->head, p, autom);
+    }
+};
+
+// Enqueue one token's work on the stream (called under capture).
+int enqueue_token(apk_ctx *c, Plan *P, uint32_t m, int argmax, int *n_launches) {
+    const uint64_t l0 = c->st.launches;
+    TokenLaunch T(c, P, m);
+    CUDA_TRY(cudaMemcpyAsync(P->x[0].p, P->xin.p, (size_t)m * P->hidden * 4, cudaMemcpyDeviceToDevice, c->stream));
     for (uint32_t l = 0; l < P->n_layers; ++l) {
         PlanLayer &L = P->L[l];
-        APK_TRY(prep_norm(L.attn_norm, L.qkv->ty, q8));
-        {
-            MvParams p{};
-            p.act = act_layout(P->act_h.p, L.qkv->ty, q8.m_eff);
-            p.epi = EPI_QKV_ROPE;
-            p.y = P->qkv.as<float>();
-            p.ldy = (int)ldq;
-            p.n_q_tiles = (int)(P->nq_l / TILE_ROWS);
-            p.n_k_tiles = (int)(P->nkv_l / TILE_ROWS);
-            p.q_norm = L.q_norm;
-            p.k_norm = L.k_norm;
-            p.eps = P->eps;
-            p.rope = P->rope.as<float>();
-            p.half = (int)(P->rot_dim / 2);
-            APK_TRY(launch_matvec(c, L.qkv, p, q8));
-        }
-        // attention core stand-in: its output is the roped Q slice; wo.matmul(attn_out, m)
-        APK_TRY(launch_prep(c, P->qkv.p, 0, (int)ldq, nullptr, 0, nullptr, 0, nullptr, 0.f, nullptr, 0, P->nq_l, m,
-                            L.wo->ty, autom, P->act_q.p));
-        APK_TRY(residual_matvec(L.wo, act_layout(P->act_q.p, L.wo->ty, autom.m_eff), autom));
-        APK_TRY(prep_norm(L.ffn_norm, L.gateup->ty, q8));
-        {
-            MvParams p{};
-            p.act = act_layout(P->act_h.p, L.gateup->ty, q8.m_eff);
-            p.epi = EPI_SWIGLU;
-            p.act_next = act_layout(P->act_d.p, L.down->ty, autom.m_eff);
-            p.next_two_level = autom.two_level;
-            p.next_need_sum = L.down->ty == APK_TY_Q4_K;
-            p.ffn = (int)P->ffn_l;
-            APK_TRY(launch_matvec(c, L.gateup, p, q8));
-        }
-        APK_TRY(residual_matvec(L.down, act_layout(P->act_d.p, L.down->ty, autom.m_eff), autom));
+        APK_TRY(T.qkv(L));
+        APK_TRY(T.wo(L));
+        APK_TRY(T.gateup(L));
+        APK_TRY(T.down(L));
     }
-    // finish_hidden: rmsnorm + output.matmul(x, m) (QuantMat::matmul: Q8 at m == 1, f32 dots above)
-    APK_TRY(prep_norm(P->out_norm, P->head->ty, autom));
-    APK_TRY(launch_matvec(c, P->head, mv_store(act_layout(P->act_h.p, P->head->ty, autom.m_eff), P->logits.as<float>(), (int)P->vocab_l), autom));
+    APK_TRY(T.head());
     const float *lg = P->logits.as<float>();
-    if (tp) {
+    if (c->world > 1) {
         const int rc = g_nccl.AllGather(P->logits.p, P->logits_all.p, (size_t)m * P->vocab_l, NCCL_FLOAT32, c->comm, c->stream);
         if (rc) return fail(APK_ERR_NCCL, "ncclAllGather: %s", g_nccl.GetErrorString(rc));
         lg = P->logits_all.as<float>();
@@ -326,15 +345,13 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
     APK_TRY(validate_token_req(c, r));
     APK_TRY(ensure_graph(c, r));
     Plan *P = c->plan.get();
-    const uint32_t m = r->m, H = P->hidden, ldq = P->nq_l + 2 * P->nkv_l;
+    const uint32_t m = r->m, H = P->hidden;
     // one real token first, so every activation buffer the kernels read holds sane data
     CUDA_TRY(cudaMemcpyAsync(P->xin.p, r->x, (size_t)m * H * 4, cudaMemcpyHostToDevice, c->stream));
     if (r->rot_dim)
         CUDA_TRY(cudaMemcpyAsync(P->rope.p, r->rope, (size_t)m * (r->rot_dim / 2) * 2 * 4, cudaMemcpyHostToDevice, c->stream));
     CUDA_TRY(cudaGraphLaunch(P->exec[m][r->argmax ? 1 : 0], c->stream));
     APK_TRY(finish(c));
-    const ActMode q8{0, (int)m};
-    const ActMode autom = resolve_mode(APK_ACT_AUTO, m);
     auto orig_bytes = [](const DevMatrix *W) {
         return (double)W->n_out * (W->n_in / (W->ty == APK_TY_Q8_0 ? 32 : 256)) * (W->ty == APK_TY_Q8_0 ? 34 : 144);
     };
@@ -344,30 +361,12 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
         for (uint32_t rep = 0; rep < reps; ++rep)
             for (uint32_t l = 0; l < n_launch; ++l) {
                 PlanLayer &L = P->L[l];
-                MvParams p{};
-                if (kind == 0) {
-                    p.act = act_layout(P->act_h.p, L.qkv->ty, q8.m_eff);
-                    p.epi = EPI_QKV_ROPE;
-                    p.y = P->qkv.as<float>(); p.ldy = (int)ldq;
-                    p.n_q_tiles = (int)(P->nq_l / TILE_ROWS); p.n_k_tiles = (int)(P->nkv_l / TILE_ROWS);
-                    p.q_norm = L.q_norm; p.k_norm = L.k_norm; p.eps = P->eps;
-                    p.rope = P->rope.as<float>(); p.half = (int)(P->rot_dim / 2);
-                    APK_TRY(launch_matvec(c, L.qkv, p, q8));
-                } else if (kind == 1) {
-                    APK_TRY(launch_matvec(c, L.wo, mv_store(act_layout(P->act_q.p, L.wo->ty, autom.m_eff), P->yp.as<float>(), (int)H), autom));
-                } else if (kind == 2) {
-                    p.act = act_layout(P->act_h.p, L.gateup->ty, q8.m_eff);
-                    p.epi = EPI_SWIGLU;
-                    p.act_next = act_layout(P->act_d.p, L.down->ty, autom.m_eff);
-                    p.next_two_level = autom.two_level;
-                    p.next_need_sum = L.down->ty == APK_TY_Q4_K;
-                    p.ffn = (int)P->ffn_l;
-                    APK_TRY(launch_matvec(c, L.gateup, p, q8));
-                } else if (kind == 3) {
-                    APK_TRY(launch_matvec(c, L.down, mv_store(act_layout(P->act_d.p, L.down->ty, autom.m_eff), P->yp.as<float>(), (int)H), autom));
-                } else {
-                    APK_TRY(launch_matvec(c, P->head, mv_store(act_layout(P->act_h.p, P->head->ty, autom.m_eff), P->logits.as<float>(), (int)P->vocab_l), autom));
-                }
+                TokenLaunch T(c, P, m);  // fresh state: reads x[0], never flips buffers
+                if (kind == 0) APK_TRY(T.qkv(L, false));
+                else if (kind == 1) APK_TRY(T.wo(L));
+                else if (kind == 2) APK_TRY(T.gateup(L, false));
+                else if (kind == 3) APK_TRY(T.down(L));
+                else APK_TRY(T.head(false));
             }
         CUDA_TRY(cudaEventRecord(c->ev1, c->stream));
         APK_TRY(finish(c));

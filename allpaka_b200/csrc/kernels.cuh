@@ -70,6 +70,24 @@ struct ActLayout {
     }
 };
 
+struct PrepParams {
+    const void *x; int x_is_bf16; int ldx;   // [m][n] activations
+    const float *add; int ldadd;             // optional addend (residual / combined partial sums)
+    float *xout; int ldxout;                 // optional: store x + add
+    const float *gamma; float eps;           // optional RMSNorm weight
+    float *hout; int ldh;                    // optional: store the normed f32 row
+    int n, m;
+    ActLayout out;
+    int two_level, need_sum;
+};
+
+// How the kernel gets its activations.
+enum Prologue : int {
+    PRO_STREAM = 0,  // prepared records streamed with every unit (any m, any K)
+    PRO_LOAD = 1,    // the whole prepared buffer bulk-loaded once into shared memory
+    PRO_QUANT = 2,   // x (f32/bf16) [+ addend] -> optional RMSNorm -> Q8 blocks, computed in the CTA
+};
+
 struct MvParams {
     const uint8_t *W;   // tiled stream
     ActLayout act;      // prepared activations (m_eff rows)
@@ -80,6 +98,9 @@ struct MvParams {
     int n_stages;
     int m_out;          // tokens written by the epilogue (m_eff, or m_eff/2 in two-level mode)
     int two_level;
+    int pro;            // Prologue
+    PrepParams prep;    // PRO_QUANT inputs (prep.out is ignored: blocks go to shared memory)
+    int pdl;            // launched with a programmatic dependency on the previous kernel
     float *partials;    // [gridDim.x][2][MAX_M_EFF][128]
     int *counters;      // [n_tiles], zero between launches
     int *err;           // error word
@@ -94,6 +115,8 @@ struct MvParams {
     const float *q_norm, *k_norm;      // optional [128]
     float eps;
     const float *rope; int half;       // [m][half][2] (sin, cos)
+    ActLayout q_next;                  // optional: roped Q heads packed as the next matvec's activations
+    int q_next_two_level, q_next_need_sum;
     // EPI_SWIGLU
     float *act_f32; int ld_act;        // optional f32 swiglu rows [m][ffn]
     ActLayout act_next;                // optional packed activations for the down projection
@@ -161,6 +184,10 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
         "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
         : "memory");
 }
+// Programmatic dependent launch: let the next kernel in the stream start its
+// independent work (weight prefetch) early / wait for the previous kernel's results.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ unsigned long long globaltimer_ns() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -191,11 +218,11 @@ struct QBlock { float d; float sum; int q; };
 __device__ __forceinline__ QBlock quantize_block(float v, bool need_sum) {
     float amax = fabsf(v);
     if (amax != amax) amax = 0.0f;  // f32::max drops a NaN operand
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    // non-negative floats order like their bit patterns: one warp-wide integer max
+    amax = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(amax)));
     const bool fin = amax <= 3.402823466e+38f;
     const float db = fin ? __fdiv_rn(amax, 127.0f) : 0.0f;
-    const float id = (db > 0.0f) ? __fdiv_rn(1.0f, db) : 0.0f;
+    const float id = (db > 0.0f) ? __frcp_rn(db) : 0.0f;  // IEEE 1.0/db
     float r = roundf(__fmul_rn(v, id));
     int q;
     if (r != r) q = 0;
@@ -251,17 +278,6 @@ __device__ __forceinline__ void quantize_store(const ActLayout &L, int two_level
     store_act_block(L, 2 * m + 1, k_block, lane, q2);
 }
 
-struct PrepParams {
-    const void *x; int x_is_bf16; int ldx;   // [m][n] activations
-    const float *add; int ldadd;             // optional addend (residual / combined partial sums)
-    float *xout; int ldxout;                 // optional: store x + add
-    const float *gamma; float eps;           // optional RMSNorm weight
-    float *hout; int ldh;                    // optional: store the normed f32 row
-    int n, m;
-    ActLayout out;
-    int two_level, need_sum;
-};
-
 __device__ __forceinline__ float load_x(const PrepParams &p, int m, int i) {
     float v = p.x_is_bf16
                   ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.x)[(size_t)m * p.ldx + i])
@@ -291,8 +307,12 @@ __device__ __forceinline__ double block_rms_scale(const PrepParams &p, int m, do
 }
 
 // grid = (ceil(blocks / 8), m), 256 threads: each warp quantises one block.
-__global__ void __launch_bounds__(256) prep_acts_kernel(PrepParams p) {
+__global__ void __launch_bounds__(256) prep_acts_kernel(PrepParams p, int pdl) {
     __shared__ double red[8];
+    if (pdl) {
+        pdl_launch_dependents();
+        pdl_wait();
+    }
     const int m = blockIdx.y;
     double scale = 1.0;
     if (p.gamma) scale = block_rms_scale(p, m, red);
@@ -447,19 +467,47 @@ __device__ __forceinline__ void scale_min_k4_dev(int j, uint32_t s0, uint32_t s1
 }
 
 // Shared memory map of the matvec kernel (dynamic, 128-byte aligned base):
-//   [0, 8*MAX_STAGES)        full barriers
-//   [.., 16*MAX_STAGES)      empty barriers
-//   [128 ..)                 flags: s_last
-//   [256 ..)                 red[2][M][128] f32  (K-half partials; red[0] doubles as the tile result)
-//   [..]                     stages: n_stages * (STAGE_W_BYTES + act record)
+//   [0, 64)      full barriers       [64, 128) empty barriers
+//   [128, 136)   flags               [136, 144) barrier of the resident-activation load
+//   [256 ..)     red[2][M][128] f32  (K-half partials; red[0] doubles as the tile result)
+//   [..]         resident activation records (PRO_LOAD / PRO_QUANT), all K-steps
+//   [..]         stages: n_stages * (STAGE_W_BYTES [+ one activation record when streaming])
 template <int M>
 struct MvSmem {
     static constexpr int RED_OFF = 256;
     static constexpr int RED_BYTES = 2 * M * TILE_ROWS * 4;
-    static constexpr int STAGE_OFF = RED_OFF + RED_BYTES;
-    __host__ __device__ static int stage_bytes(int act_rec) { return STAGE_W_BYTES + ((act_rec + 127) & ~127); }
-    __host__ __device__ static int total(int n_stages, int act_rec) {
-        return STAGE_OFF + n_stages * stage_bytes(act_rec);
+    static constexpr int RES_OFF = RED_OFF + RED_BYTES;
+};
+__host__ __device__ inline int mv_resident_bytes(int pro, int KS, int act_rec) {
+    return pro == PRO_STREAM ? 0 : ((KS * act_rec + 127) & ~127);
+}
+__host__ __device__ inline int mv_stage_bytes(int pro, int act_rec) {
+    return STAGE_W_BYTES + (pro == PRO_STREAM ? ((act_rec + 127) & ~127) : 0);
+}
+__host__ __device__ inline int mv_smem_total(int m_eff, int pro, int KS, int act_rec, int n_stages) {
+    return 256 + 2 * m_eff * TILE_ROWS * 4 + mv_resident_bytes(pro, KS, act_rec) + n_stages * mv_stage_bytes(pro, act_rec);
+}
+
+// The order in which a CTA walks its range [u_begin, u_end) of the flat unit
+// sequence: the tile pieces it shares with neighbours first (tail piece, then
+// head piece), whole tiles after.  A shared tile's cross-CTA hand-off (publish,
+// count, last arriver sums) then overlaps the streaming of the whole tiles
+// instead of sitting at the very end of the kernel.
+struct UnitOrder {
+    long long u_begin, u_end;
+    int n_total, len_tail, len_head;
+    __device__ UnitOrder(long long ub, long long ue, int KS) : u_begin(ub), u_end(ue) {
+        n_total = (int)(ue - ub);
+        const long long t_first = ub / KS, t_last = (ue - 1) / KS;
+        const long long h_end = (t_first + 1) * (long long)KS < ue ? (t_first + 1) * (long long)KS : ue;
+        const bool head_partial = (ub % KS) != 0 || (h_end - ub) < KS;
+        len_head = head_partial ? (int)(h_end - ub) : 0;
+        len_tail = (t_last > t_first && (ue % KS) != 0) ? (int)(ue - t_last * (long long)KS) : 0;
+    }
+    __device__ __forceinline__ long long at(int it) const {
+        if (it < len_tail) return u_end - len_tail + it;
+        if (it < len_tail + len_head) return u_begin + (it - len_tail);
+        return u_begin + it - len_tail;  // = u_begin + len_head + (it - len_tail - len_head)
     }
 };
 
@@ -467,16 +515,125 @@ template <int M>
 __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float *out /*[M][128] smem*/,
                                               int tid);
 
+// In-CTA activation prologue (PRO_QUANT): the 256 consumer threads turn one row
+// x (n <= 256 * PRO_CH elements) into Q8 blocks in shared memory, after the
+// optional RMSNorm.
+//  * Every global load of the row (x, addend, norm weight) is issued up front:
+//    ONE memory round trip (the memory system is busy with the weight prefetch).
+//  * The per-block scalar chain (max, IEEE divide, reciprocal) is the slow part,
+//    so it runs one block per THREAD over a padded f32 copy of the row in shared
+//    memory (`hs`, one pad word per block: conflict-free), all blocks at once;
+//    the per-element rounding then runs from registers.
+// Arithmetic is Q8Acts::from_f32 (quantmat/q8_acts.rs:26-63) exactly, including
+// the left-to-right f32 block sum.  `hs` is the ring's last stage buffer, which
+// the producer leaves alone until pro_bar completes.
+constexpr int PRO_CH = 20;
+
+template <int M>
+__device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, float *hs, float *red, int tid) {
+    const PrepParams &pp = p.prep;
+    const int warp = tid >> 5, lane = tid & 31;
+    const int n = pp.n, nb = n >> 5;
+    const int ke = p.act.ke, kt_shift = ke == 256 ? 3 : 4, kt = 1 << kt_shift;
+    const int rec_bytes = M * (ke + ke / 4);
+    float *idv = hs + n + nb;  // reciprocal scale per block
+    float *dv = idv + nb;      // scale per block
+    double *dred = reinterpret_cast<double *>(red);
+    float v[PRO_CH], a[PRO_CH], g[PRO_CH];
+    const float *xf = reinterpret_cast<const float *>(pp.x);
+    const __nv_bfloat16 *xb = reinterpret_cast<const __nv_bfloat16 *>(pp.x);
+#pragma unroll
+    for (int j = 0; j < PRO_CH; ++j) {
+        const int i = j * N_CONSUMERS + tid;
+        const bool in = i < n;
+        v[j] = !in ? 0.0f : (pp.x_is_bf16 ? __bfloat162float(xb[i]) : xf[i]);
+        a[j] = (in && pp.add) ? pp.add[i] : 0.0f;
+        g[j] = (in && pp.gamma) ? pp.gamma[i] : 1.0f;
+    }
+    if (pp.add) {
+#pragma unroll
+        for (int j = 0; j < PRO_CH; ++j) v[j] = __fadd_rn(v[j], a[j]);
+    }
+    double scale = 1.0;
+    if (pp.gamma) {
+        // ops::rmsnorm_into (ops/norm.rs:193-198): f64 sum of squares, f64 1/sqrt(mean + eps)
+        double ss = 0.0;
+#pragma unroll
+        for (int j = 0; j < PRO_CH; ++j) ss = fma((double)v[j], (double)v[j], ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) dred[warp] = ss;
+        consumer_bar();
+        double tot = 0.0;
+#pragma unroll
+        for (int i = 0; i < N_CONSUMER_WARPS; ++i) tot += dred[i];
+        scale = 1.0 / sqrt(tot / (double)n + (double)pp.eps);
+    }
+    if (p.timeline && tid == 0) p.timeline[(size_t)blockIdx.x * 8 + 7] = globaltimer_ns();  // row loaded
+#pragma unroll
+    for (int j = 0; j < PRO_CH; ++j) {
+        const int i = j * N_CONSUMERS + tid;
+        if (i < n) {
+            if (pp.xout && blockIdx.x == 0) pp.xout[i] = v[j];
+            if (pp.gamma) v[j] = __fmul_rn((float)((double)v[j] * scale), g[j]);
+            hs[i + (i >> 5)] = v[j];
+        }
+    }
+    const int levels = pp.two_level ? 2 : 1;
+#pragma unroll 1
+    for (int lv = 0; lv < levels; ++lv) {
+        const int row = lv;  // one token: rows 0 (value) and 1 (residual)
+        consumer_bar();
+        for (int b = tid; b < nb; b += N_CONSUMERS) {
+            const float *hb = hs + b * 33;
+            float amax = 0.0f, sum = 0.0f;
+            const bool want_sum = pp.need_sum && lv == 0;
+#pragma unroll 8
+            for (int k = 0; k < 32; ++k) {
+                const float t = hb[k];
+                amax = fmaxf(amax, fabsf(t));          // f32::max drops a NaN operand, like fmaxf
+                if (want_sum) sum = __fadd_rn(sum, t);  // strictly left to right
+            }
+            const bool fin = amax <= 3.402823466e+38f;
+            const float db = fin ? __fdiv_rn(amax, 127.0f) : 0.0f;
+            const float id = (db > 0.0f) ? __frcp_rn(db) : 0.0f;  // IEEE 1.0/db
+            idv[b] = id;
+            dv[b] = db;
+            float *d = reinterpret_cast<float *>(res + (size_t)(b >> kt_shift) * rec_bytes + M * ke);
+            d[row * kt + (b & (kt - 1))] = db;
+            d[M * kt + row * kt + (b & (kt - 1))] = sum;
+        }
+        consumer_bar();
+        // elements straight from the shared copy; a short rolled loop (this code runs
+        // once per CTA: its size is paid in cold instruction fetches)
+#pragma unroll 4
+        for (int i = tid; i < n; i += N_CONSUMERS) {
+            const int b = i >> 5;
+            const float x = hs[i + b];
+            const float r = roundf(__fmul_rn(x, idv[b]));
+            const int q = (r != r) ? 0 : (int)fminf(fmaxf(r, -128.0f), 127.0f);
+            res[(size_t)(b >> kt_shift) * rec_bytes + row * ke + (b & (kt - 1)) * 32 + lane] = (uint8_t)(int8_t)q;
+            // residual for the second digit, exact in one fused operation (own slot: no hazard)
+            if (lv + 1 < levels) hs[i + b] = __fmaf_rn(-dv[b], (float)q, x);
+        }
+    }
+    consumer_bar();
+}
+
 template <int TY, int M, bool DUMP>
 __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvParams p) {
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + MAX_STAGES;
     int *s_flags = reinterpret_cast<int *>(smem + 128);
+    uint64_t *acts_bar = reinterpret_cast<uint64_t *>(smem + 136);
+    uint64_t *pro_bar = reinterpret_cast<uint64_t *>(smem + 144);  // PRO_QUANT scratch (last stage) released
     float *red = reinterpret_cast<float *>(smem + MvSmem<M>::RED_OFF);
     const int act_rec = p.act.rec_bytes();
-    const int stage_bytes = MvSmem<M>::stage_bytes(act_rec);
-    uint8_t *stages = smem + MvSmem<M>::STAGE_OFF;
+    const bool streaming = p.pro == PRO_STREAM;
+    uint8_t *res = smem + MvSmem<M>::RES_OFF;
+    const int stage_bytes = mv_stage_bytes(p.pro, act_rec);
+    uint8_t *stages = res + mv_resident_bytes(p.pro, p.KS, act_rec);
     const int NS = p.n_stages;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -487,15 +644,18 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], N_CONSUMER_WARPS);
         }
+        mbar_init(acts_bar, 1);
+        mbar_init(pro_bar, N_CONSUMER_WARPS);
         fence_mbar_init();
     }
     __syncthreads();
+    if (p.pdl) pdl_launch_dependents();
 
     // this CTA's contiguous range of the flat unit sequence
     const long long U = (long long)p.n_tiles * p.KS;
     const long long G = gridDim.x;
-    const long long u_begin = (long long)blockIdx.x * U / G;
-    const long long u_end = (long long)(blockIdx.x + 1) * U / G;
+    const UnitOrder order((long long)blockIdx.x * U / G, (long long)(blockIdx.x + 1) * U / G, p.KS);
+    const int n_total = order.n_total;
     const int kt = (TY == TY_Q8_0) ? Q8_KT : Q4_KT_SB * 8;  // 32-element blocks per full K-step
 
     if (warp == N_CONSUMER_WARPS) {
@@ -503,14 +663,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         if (lane == 0) {
             const uint64_t pol_w = l2_policy_evict_first();
             const uint64_t pol_a = l2_policy_evict_last();
-            int it = 0;
-            for (long long u = u_begin; u < u_end; ++u, ++it) {
+            auto issue_weights = [&](int it) {
+                const long long u = order.at(it);
                 const int s = it % NS;
-                const uint32_t ph = (uint32_t)((it / NS) & 1);
-                if (!mbar_wait_bounded(&empty[s], ph ^ 1u)) {
-                    atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
-                    break;
-                }
                 const int t = (int)(u / p.KS), ks = (int)(u % p.KS);
                 const int kb = min(kt, p.nb - ks * kt);
                 uint32_t wbytes, woff;
@@ -521,19 +676,46 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     wbytes = (uint32_t)(kb / 8) * Q4_SB_UNIT;
                     woff = (uint32_t)ks * Q4_KT_SB * Q4_SB_UNIT;
                 }
-                uint8_t *st = stages + (size_t)s * stage_bytes;
-                mbar_arrive_expect_tx(&full[s], wbytes + (uint32_t)act_rec);
-                bulk_g2s(st, p.W + (size_t)t * p.tile_bytes + woff, wbytes, &full[s], pol_w);
-                bulk_g2s(st + STAGE_W_BYTES, p.act.base + (size_t)ks * act_rec, (uint32_t)act_rec, &full[s],
-                         pol_a);
+                mbar_arrive_expect_tx(&full[s], wbytes + (streaming ? (uint32_t)act_rec : 0u));
+                bulk_g2s(stages + (size_t)s * stage_bytes, p.W + (size_t)t * p.tile_bytes + woff, wbytes, &full[s], pol_w);
+            };
+            auto issue_acts = [&](int it) {
+                const int s = it % NS;
+                const int ks = (int)(order.at(it) % p.KS);
+                bulk_g2s(stages + (size_t)s * stage_bytes + STAGE_W_BYTES, p.act.base + (size_t)ks * act_rec,
+                         (uint32_t)act_rec, &full[s], pol_a);
+            };
+            // Weights depend on nothing: fill the ring before waiting for the previous kernel.
+            // (The in-CTA prologue borrows the last stage buffer as scratch until pro_bar.)
+            const int ring0 = p.pro == PRO_QUANT ? NS - 1 : NS;
+            const int pre = n_total < ring0 ? n_total : ring0;
+            for (int it = 0; it < pre; ++it) issue_weights(it);
+            if (p.pdl) pdl_wait();
+            if (p.pro == PRO_QUANT && !mbar_wait_bounded(pro_bar, 0u)) atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
+            if (p.pro == PRO_LOAD) {
+                const uint32_t bytes = (uint32_t)(p.KS * act_rec);
+                mbar_arrive_expect_tx(acts_bar, bytes);
+                for (uint32_t o = 0; o < bytes; o += 32768u)
+                    bulk_g2s(res + o, p.act.base + o, min(32768u, bytes - o), acts_bar, pol_a);
+            }
+            if (streaming)
+                for (int it = 0; it < pre; ++it) issue_acts(it);
+            int it = pre;
+            for (; it < n_total; ++it) {
+                const int s = it % NS;
+                const uint32_t ph = (uint32_t)((it / NS) & 1);
+                if (!mbar_wait_bounded(&empty[s], ph ^ 1u)) {
+                    atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
+                    break;
+                }
+                issue_weights(it);
+                if (streaming) issue_acts(it);
             }
             // Every copy issued above lands before this lane leaves: wait (bounded)
             // for the stages still in flight so no bulk write outlives the CTA.
             const int pending = it < NS ? it : NS;
-            for (int j = it - pending; j < it; ++j) {
-                const int s = j % NS;
-                (void)mbar_wait_bounded(&full[s], (uint32_t)((j / NS) & 1));
-            }
+            for (int j = it - pending; j < it; ++j) (void)mbar_wait_bounded(&full[j % NS], (uint32_t)((j / NS) & 1));
+            if (p.pro == PRO_LOAD) (void)mbar_wait_bounded(acts_bar, 0u);
         }
         return;
     }
@@ -546,42 +728,109 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     for (int m = 0; m < M; ++m) acc[m] = 0.0f;
     bool aborted = false;
 
-    int it = 0;
-    for (long long u = u_begin; u < u_end; ++u, ++it) {
-        const int s = it % NS;
-        const uint32_t ph = (uint32_t)((it / NS) & 1);
-        const int t = (int)(u / p.KS), ks = (int)(u % p.KS);
+    if (p.pdl) pdl_wait();
+    if (tl && tid == 0) tl[2] = globaltimer_ns();  // dependency satisfied
+    if (p.pro == PRO_QUANT) {
+        prologue_quant<M>(p, res, reinterpret_cast<float *>(stages + (size_t)(NS - 1) * stage_bytes), red, tid);
+        // generic-proxy accesses to the scratch are done; the bulk-copy engine may overwrite it
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pro_bar);
+    } else if (p.pro == PRO_LOAD) {
+        if (!mbar_wait_bounded(acts_bar, 0u)) {
+            aborted = true;
+            if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
+        }
+    }
+    if (tl && tid == 0) tl[6] = globaltimer_ns();  // activations ready
+
+    const int my_first_tile = (int)(order.u_begin / p.KS);
+    // (tile, K-step) of the walk, kept incrementally: the order has one jump
+    // (after the tail piece) and otherwise advances by one unit.
+    int t, ks;
+    {
+        const long long u0 = order.at(0);
+        t = (int)(u0 / p.KS);
+        ks = (int)(u0 % p.KS);
+    }
+    int s = 0;
+    uint32_t ph = 0;
+    for (int it = 0; it < n_total; ++it) {
+        // where the next unit lies (decides whether this one closes its tile)
+        int t_next = t, ks_next = ks + 1;
+        if (it + 1 == order.len_tail) {
+            t_next = (int)(order.u_begin / p.KS);
+            ks_next = (int)(order.u_begin % p.KS);
+        } else if (ks_next == p.KS) {
+            ks_next = 0;
+            t_next = t + 1;
+        }
         if (!aborted && !mbar_wait_bounded(&full[s], ph)) {
             aborted = true;
             if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
         }
         if (tl && tid == 0) {
             if (it == 0) tl[1] = globaltimer_ns();   // first unit landed
-            if (it == 1) tl[2] = globaltimer_ns();
-            if (u + 1 == u_end) tl[3] = globaltimer_ns();  // last unit landed
+            if (it + 1 == n_total) tl[3] = globaltimer_ns();  // last unit landed
         }
         if (!aborted) {
             const uint8_t *sw = stages + (size_t)s * stage_bytes;
-            const uint8_t *sa = sw + STAGE_W_BYTES;
+            const uint8_t *sa = streaming ? sw + STAGE_W_BYTES : res + (size_t)ks * act_rec;
             const int kb = min(kt, p.nb - ks * kt);
             const float *ad = reinterpret_cast<const float *>(sa + M * p.act.ke);
             if (TY == TY_Q8_0) {
-                for (int b = kh; b < kb; b += 2) {
-                    const int4 w0 = *reinterpret_cast<const int4 *>(sw + ((b * 2 + 0) * 4 + rg) * 512 + lane * 16);
-                    const int4 w1 = *reinterpret_cast<const int4 *>(sw + ((b * 2 + 1) * 4 + rg) * 512 + lane * 16);
-                    const float dw = __half2float(
-                        *reinterpret_cast<const __half *>(sw + kb * 4096 + (b * 128 + rg * 32 + lane) * 2));
+                // lane = row: two 16-byte chunks + one f16 scale per block; activations are
+                // warp-wide broadcasts.  This warp takes blocks kh, kh+2, kh+4, kh+6.
+                const uint8_t *wq = sw + (kh * 8 + rg) * 512 + lane * 16;            // + j*8192 (+2048 second half)
+                const uint8_t *ws = sw + kb * 4096 + (kh * 128 + rg * 32 + lane) * 2;  // + j*512
+                const uint8_t *xa = sa + kh * 32;                                      // + m*ke + j*64
+                const float *xd = ad + kh;                                             // + m*8 + 2*j
+                if (kb == Q8_KT) {
+                    int4 w0[4], w1[4];
+                    float dw[4];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        w0[j] = *reinterpret_cast<const int4 *>(wq + j * 8192);
+                        w1[j] = *reinterpret_cast<const int4 *>(wq + j * 8192 + 2048);
+                        dw[j] = __half2float(*reinterpret_cast<const __half *>(ws + j * 512));
+                    }
 #pragma unroll
                     for (int m = 0; m < M; ++m) {
-                        const int4 x0 = *reinterpret_cast<const int4 *>(sa + m * p.act.ke + b * 32);
-                        const int4 x1 = *reinterpret_cast<const int4 *>(sa + m * p.act.ke + b * 32 + 16);
-                        const int idot = dot32(w0, w1, x0, x1);
-                        const float dx = ad[m * Q8_KT + b];
-                        acc[m] = fmaf(__fmul_rn(dw, dx), (float)idot, acc[m]);
-                        if (DUMP) {
-                            const int row = t * TILE_ROWS + rg * 32 + lane;
-                            if (row < p.n_out)
-                                p.dump[((size_t)m * p.n_out + row) * p.nb + ks * Q8_KT + b] = idot;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int4 x0 = *reinterpret_cast<const int4 *>(xa + m * p.act.ke + j * 64);
+                            const int4 x1 = *reinterpret_cast<const int4 *>(xa + m * p.act.ke + j * 64 + 16);
+                            // two independent dp4a chains per block
+                            int d0 = __dp4a(w0[j].x, x0.x, 0), d1 = __dp4a(w1[j].x, x1.x, 0);
+                            d0 = __dp4a(w0[j].y, x0.y, d0); d1 = __dp4a(w1[j].y, x1.y, d1);
+                            d0 = __dp4a(w0[j].z, x0.z, d0); d1 = __dp4a(w1[j].z, x1.z, d1);
+                            d0 = __dp4a(w0[j].w, x0.w, d0); d1 = __dp4a(w1[j].w, x1.w, d1);
+                            const int idot = d0 + d1;
+                            acc[m] = fmaf(__fmul_rn(dw[j], xd[m * Q8_KT + 2 * j]), (float)idot, acc[m]);
+                            if (DUMP) {
+                                const int row = t * TILE_ROWS + rg * 32 + lane;
+                                if (row < p.n_out)
+                                    p.dump[((size_t)m * p.n_out + row) * p.nb + ks * Q8_KT + kh + 2 * j] = idot;
+                            }
+                        }
+                    }
+                } else {
+                    for (int b = kh; b < kb; b += 2) {
+                        const int4 w0 = *reinterpret_cast<const int4 *>(sw + ((b * 2 + 0) * 4 + rg) * 512 + lane * 16);
+                        const int4 w1 = *reinterpret_cast<const int4 *>(sw + ((b * 2 + 1) * 4 + rg) * 512 + lane * 16);
+                        const float dwb = __half2float(
+                            *reinterpret_cast<const __half *>(sw + kb * 4096 + (b * 128 + rg * 32 + lane) * 2));
+#pragma unroll
+                        for (int m = 0; m < M; ++m) {
+                            const int4 x0 = *reinterpret_cast<const int4 *>(sa + m * p.act.ke + b * 32);
+                            const int4 x1 = *reinterpret_cast<const int4 *>(sa + m * p.act.ke + b * 32 + 16);
+                            const int idot = dot32(w0, w1, x0, x1);
+                            acc[m] = fmaf(__fmul_rn(dwb, ad[m * Q8_KT + b]), (float)idot, acc[m]);
+                            if (DUMP) {
+                                const int row = t * TILE_ROWS + rg * 32 + lane;
+                                if (row < p.n_out)
+                                    p.dump[((size_t)m * p.n_out + row) * p.nb + ks * Q8_KT + b] = idot;
+                            }
                         }
                     }
                 }
@@ -641,7 +890,14 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         }
 
         // ---- end of this CTA's share of tile t: combine and finish the tile
-        const bool tile_done = (ks == p.KS - 1) || (u + 1 == u_end);
+        const bool tile_done = (it + 1 == n_total) || t_next != t;
+        const int t_cur = t;
+        t = t_next;
+        ks = ks_next;
+        if (++s == NS) {
+            s = 0;
+            ph ^= 1u;
+        }
         if (!tile_done) continue;
 #pragma unroll
         for (int m = 0; m < M; ++m) {
@@ -650,18 +906,16 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         }
         consumer_bar();
         for (int i = tid; i < M * TILE_ROWS; i += N_CONSUMERS) red[i] += red[M * TILE_ROWS + i];
-        const long long ua = (long long)t * p.KS, ub = ua + p.KS - 1;
+        const long long ua = (long long)t_cur * p.KS, ub = ua + p.KS - 1;
         const int c_first = (int)(((ua + 1) * G - 1) / U), c_last = (int)(((ub + 1) * G - 1) / U);
         if (c_first != c_last) {
-            // partial tile: publish, count arrivals, the last arriver sums in CTA order
-            const int my_first_tile = (int)(u_begin / p.KS);
-            float *slot = p.partials + ((size_t)blockIdx.x * 2 + (my_first_tile == t ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
-            consumer_bar();
+            // shared tile: publish, count arrivals, the last arriver sums in CTA order
+            float *slot = p.partials + ((size_t)blockIdx.x * 2 + (my_first_tile == t_cur ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
             for (int i = tid; i < M * TILE_ROWS; i += N_CONSUMERS) __stcg(&slot[i], red[i]);
             __threadfence();
             consumer_bar();
             if (tid == 0) {
-                const int old = atomicAdd(&p.counters[t], 1);
+                const int old = atomicAdd(&p.counters[t_cur], 1);
                 s_flags[0] = (old == c_last - c_first) ? 1 : 0;
             }
             consumer_bar();
@@ -672,21 +926,21 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     float v = 0.0f;
                     for (int c = c_first; c <= c_last; ++c) {
                         const int cf = (int)(((long long)c * U / G) / p.KS);
-                        const float *sl = p.partials + ((size_t)c * 2 + (cf == t ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
+                        const float *sl = p.partials + ((size_t)c * 2 + (cf == t_cur ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
                         v += __ldcg(&sl[i]);
                     }
                     red[i] = v;
                 }
-                if (tid == 0) p.counters[t] = 0;
+                if (tid == 0) p.counters[t_cur] = 0;
+                consumer_bar();
+                epilogue_tile<M>(p, t_cur, red, tid);
             }
-            consumer_bar();
-            if (last) epilogue_tile<M>(p, t, red, tid);
         } else {
             consumer_bar();
-            epilogue_tile<M>(p, t, red, tid);
+            epilogue_tile<M>(p, t_cur, red, tid);
         }
         consumer_bar();  // red is reused by the next tile
-        if (tl && tid == 0) tl[4 + (u + 1 == u_end ? 1 : 0)] = globaltimer_ns();  // a flush / the final flush done
+        if (tl && tid == 0) tl[4 + (it + 1 == n_total ? 1 : 0)] = globaltimer_ns();  // a tile / the last tile done
     }
 }
 
@@ -758,6 +1012,9 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
                 }
                 const int row = row0 + c;
                 if (row < p.n_out) p.y[(size_t)m * p.ldy + row] = o;
+                // identity attention core: the roped Q head is what the output projection consumes
+                if (p.q_next.base && tile < p.n_q_tiles)
+                    quantize_store(p.q_next, p.q_next_two_level, p.q_next_need_sum, m, tile * 4 + j, lane, o);
             }
         }
         return;
