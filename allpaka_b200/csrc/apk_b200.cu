@@ -564,7 +564,7 @@ int stage_acts(apk_ctx *c, const DevMatrix *W, const void *x, int x_is_bf16, int
                float *xout, int ldxout, const float *gamma, float eps, uint32_t m, ActMode mode, void *act_buf,
                MvParams *p) {
     p->act = act_layout(act_buf, W->ty, mode.m_eff);
-    if (m == 1 && W->n_in <= (uint32_t)(N_CONSUMERS * PRO_CH) && want_resident(c, W, mode.m_eff)) {
+    if (m == 1 && W->n_in <= (uint32_t)(N_CONSUMERS * PRO_CH) && ((uintptr_t)x & 15) == 0 && want_resident(c, W, mode.m_eff)) {
         p->pro = PRO_QUANT;
         PrepParams &pp = p->prep;
         pp.x = x; pp.x_is_bf16 = x_is_bf16; pp.ldx = ldx;

@@ -518,19 +518,36 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
 // In-CTA activation prologue (PRO_QUANT): the 256 consumer threads turn one row
 // x (n <= 256 * PRO_CH elements) into Q8 blocks in shared memory, after the
 // optional RMSNorm.
-//  * Every global load of the row (x, addend, norm weight) is issued up front:
-//    ONE memory round trip (the memory system is busy with the weight prefetch).
+//  * The norm weight does not depend on the previous kernel: it is loaded into
+//    registers BEFORE the dependency wait (prologue_gamma).
+//  * The row itself arrives by one bulk async copy issued by the producer lane
+//    right after the wait (raw f32/bf16 in the scratch buffer).
 //  * The per-block scalar chain (max, IEEE divide, reciprocal) is the slow part,
 //    so it runs one block per THREAD over a padded f32 copy of the row in shared
 //    memory (`hs`, one pad word per block: conflict-free), all blocks at once;
-//    the per-element rounding then runs from registers.
+//    rounding then runs four elements per thread with one packed 32-bit store.
 // Arithmetic is Q8Acts::from_f32 (quantmat/q8_acts.rs:26-63) exactly, including
-// the left-to-right f32 block sum.  `hs` is the ring's last stage buffer, which
-// the producer leaves alone until pro_bar completes.
+// the left-to-right f32 block sum.  The scratch is the ring's last stage buffer,
+// which the producer leaves alone until pro_bar completes.
 constexpr int PRO_CH = 20;
 
+__device__ __forceinline__ void prologue_gamma(const MvParams &p, int tid, float (&g)[PRO_CH]) {
+    const PrepParams &pp = p.prep;
+#pragma unroll
+    for (int j = 0; j < PRO_CH; ++j) {
+        const int i = j * N_CONSUMERS + tid;
+        g[j] = (pp.gamma && i < pp.n) ? pp.gamma[i] : 1.0f;
+    }
+}
+
+__device__ __forceinline__ int q8_round(float x, float id) {
+    const float r = roundf(__fmul_rn(x, id));  // half away from zero, like f32::round
+    return (r != r) ? 0 : (int)fminf(fmaxf(r, -128.0f), 127.0f);
+}
+
 template <int M>
-__device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, float *hs, float *red, int tid) {
+__device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, float *hs, float *red, int tid,
+                                               const float (&g)[PRO_CH]) {
     const PrepParams &pp = p.prep;
     const int warp = tid >> 5, lane = tid & 31;
     const int n = pp.n, nb = n >> 5;
@@ -539,20 +556,23 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
     float *idv = hs + n + nb;  // reciprocal scale per block
     float *dv = idv + nb;      // scale per block
     double *dred = reinterpret_cast<double *>(red);
-    float v[PRO_CH], a[PRO_CH], g[PRO_CH];
-    const float *xf = reinterpret_cast<const float *>(pp.x);
-    const __nv_bfloat16 *xb = reinterpret_cast<const __nv_bfloat16 *>(pp.x);
+    float v[PRO_CH];
+    // the raw row sits at the start of the scratch (bulk copy); the addend, if any, is read from global
+    {
+        const float *xf = hs;
+        const __nv_bfloat16 *xb = reinterpret_cast<const __nv_bfloat16 *>(hs);
 #pragma unroll
-    for (int j = 0; j < PRO_CH; ++j) {
-        const int i = j * N_CONSUMERS + tid;
-        const bool in = i < n;
-        v[j] = !in ? 0.0f : (pp.x_is_bf16 ? __bfloat162float(xb[i]) : xf[i]);
-        a[j] = (in && pp.add) ? pp.add[i] : 0.0f;
-        g[j] = (in && pp.gamma) ? pp.gamma[i] : 1.0f;
-    }
-    if (pp.add) {
+        for (int j = 0; j < PRO_CH; ++j) {
+            const int i = j * N_CONSUMERS + tid;
+            v[j] = i >= n ? 0.0f : (pp.x_is_bf16 ? __bfloat162float(xb[i]) : xf[i]);
+        }
+        if (pp.add) {
 #pragma unroll
-        for (int j = 0; j < PRO_CH; ++j) v[j] = __fadd_rn(v[j], a[j]);
+            for (int j = 0; j < PRO_CH; ++j) {
+                const int i = j * N_CONSUMERS + tid;
+                if (i < n) v[j] = __fadd_rn(v[j], pp.add[i]);
+            }
+        }
     }
     double scale = 1.0;
     if (pp.gamma) {
@@ -568,8 +588,10 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
 #pragma unroll
         for (int i = 0; i < N_CONSUMER_WARPS; ++i) tot += dred[i];
         scale = 1.0 / sqrt(tot / (double)n + (double)pp.eps);
+    } else {
+        consumer_bar();  // everyone has read the raw row before the padded copy overwrites it
     }
-    if (p.timeline && tid == 0) p.timeline[(size_t)blockIdx.x * 8 + 7] = globaltimer_ns();  // row loaded
+    if (p.timeline && tid == 0) p.timeline[(size_t)blockIdx.x * 8 + 7] = globaltimer_ns();  // row in registers
 #pragma unroll
     for (int j = 0; j < PRO_CH; ++j) {
         const int i = j * N_CONSUMERS + tid;
@@ -604,17 +626,25 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
             d[M * kt + row * kt + (b & (kt - 1))] = sum;
         }
         consumer_bar();
-        // elements straight from the shared copy; a short rolled loop (this code runs
-        // once per CTA: its size is paid in cold instruction fetches)
-#pragma unroll 4
-        for (int i = tid; i < n; i += N_CONSUMERS) {
+        // four consecutive elements per thread, one packed store
+#pragma unroll 2
+        for (int i = 4 * tid; i < n; i += 4 * N_CONSUMERS) {
             const int b = i >> 5;
-            const float x = hs[i + b];
-            const float r = roundf(__fmul_rn(x, idv[b]));
-            const int q = (r != r) ? 0 : (int)fminf(fmaxf(r, -128.0f), 127.0f);
-            res[(size_t)(b >> kt_shift) * rec_bytes + row * ke + (b & (kt - 1)) * 32 + lane] = (uint8_t)(int8_t)q;
-            // residual for the second digit, exact in one fused operation (own slot: no hazard)
-            if (lv + 1 < levels) hs[i + b] = __fmaf_rn(-dv[b], (float)q, x);
+            float *h4 = hs + i + b;
+            const float id = idv[b];
+            const float x0 = h4[0], x1 = h4[1], x2 = h4[2], x3 = h4[3];
+            const int q0 = q8_round(x0, id), q1 = q8_round(x1, id), q2 = q8_round(x2, id), q3 = q8_round(x3, id);
+            const uint32_t packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
+                                    ((uint32_t)(q3 & 0xff) << 24);
+            *reinterpret_cast<uint32_t *>(res + (size_t)(b >> kt_shift) * rec_bytes + row * ke + (b & (kt - 1)) * 32 + (i & 31)) = packed;
+            if (lv + 1 < levels) {
+                // residual for the second digit, exact in one fused operation (own slots: no hazard)
+                const float d1 = dv[b];
+                h4[0] = __fmaf_rn(-d1, (float)q0, x0);
+                h4[1] = __fmaf_rn(-d1, (float)q1, x1);
+                h4[2] = __fmaf_rn(-d1, (float)q2, x2);
+                h4[3] = __fmaf_rn(-d1, (float)q3, x3);
+            }
         }
     }
     consumer_bar();
@@ -691,7 +721,13 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             const int pre = n_total < ring0 ? n_total : ring0;
             for (int it = 0; it < pre; ++it) issue_weights(it);
             if (p.pdl) pdl_wait();
-            if (p.pro == PRO_QUANT && !mbar_wait_bounded(pro_bar, 0u)) atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
+            if (p.pro == PRO_QUANT) {
+                // the activation row, raw, into the scratch stage; then hands off until the prologue is done
+                const uint32_t bytes = (uint32_t)p.prep.n * (p.prep.x_is_bf16 ? 2u : 4u);
+                mbar_arrive_expect_tx(acts_bar, bytes);
+                bulk_g2s(stages + (size_t)(NS - 1) * stage_bytes, p.prep.x, bytes, acts_bar, pol_a);
+                if (!mbar_wait_bounded(pro_bar, 0u)) atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
+            }
             if (p.pro == PRO_LOAD) {
                 const uint32_t bytes = (uint32_t)(p.KS * act_rec);
                 mbar_arrive_expect_tx(acts_bar, bytes);
@@ -715,7 +751,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             // for the stages still in flight so no bulk write outlives the CTA.
             const int pending = it < NS ? it : NS;
             for (int j = it - pending; j < it; ++j) (void)mbar_wait_bounded(&full[j % NS], (uint32_t)((j / NS) & 1));
-            if (p.pro == PRO_LOAD) (void)mbar_wait_bounded(acts_bar, 0u);
+            if (p.pro != PRO_STREAM) (void)mbar_wait_bounded(acts_bar, 0u);
         }
         return;
     }
@@ -728,19 +764,21 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     for (int m = 0; m < M; ++m) acc[m] = 0.0f;
     bool aborted = false;
 
+    float gam[PRO_CH];
+    if (p.pro == PRO_QUANT) prologue_gamma(p, tid, gam);  // independent of the previous kernel
     if (p.pdl) pdl_wait();
     if (tl && tid == 0) tl[2] = globaltimer_ns();  // dependency satisfied
+    if (p.pro != PRO_STREAM && !mbar_wait_bounded(acts_bar, 0u)) {
+        aborted = true;
+        if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
+    }
     if (p.pro == PRO_QUANT) {
-        prologue_quant<M>(p, res, reinterpret_cast<float *>(stages + (size_t)(NS - 1) * stage_bytes), red, tid);
+        if (tl && tid == 0) tl[4] = globaltimer_ns();  // raw row landed
+        prologue_quant<M>(p, res, reinterpret_cast<float *>(stages + (size_t)(NS - 1) * stage_bytes), red, tid, gam);
         // generic-proxy accesses to the scratch are done; the bulk-copy engine may overwrite it
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(pro_bar);
-    } else if (p.pro == PRO_LOAD) {
-        if (!mbar_wait_bounded(acts_bar, 0u)) {
-            aborted = true;
-            if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
-        }
     }
     if (tl && tid == 0) tl[6] = globaltimer_ns();  // activations ready
 
@@ -940,7 +978,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             epilogue_tile<M>(p, t_cur, red, tid);
         }
         consumer_bar();  // red is reused by the next tile
-        if (tl && tid == 0) tl[4 + (it + 1 == n_total ? 1 : 0)] = globaltimer_ns();  // a tile / the last tile done
+        if (tl && tid == 0 && it + 1 == n_total) tl[5] = globaltimer_ns();  // the last tile done
     }
 }
 
