@@ -517,26 +517,30 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
 
 // In-CTA activation prologue (PRO_QUANT): the 256 consumer threads turn one row
 // x (n <= 256 * PRO_CH elements) into Q8 blocks in shared memory, after the
-// optional RMSNorm.
-//  * The norm weight does not depend on the previous kernel: it is loaded into
-//    registers BEFORE the dependency wait (prologue_gamma).
+// optional RMSNorm, entirely in registers.
+//  * The norm weight does not depend on the previous kernel: it is loaded
+//    BEFORE the dependency wait (prologue_gamma).
 //  * The row itself arrives by one bulk async copy issued by the producer lane
-//    right after the wait (raw f32/bf16 in the scratch buffer).
-//  * The per-block scalar chain (max, IEEE divide, reciprocal) is the slow part,
-//    so it runs one block per THREAD over a padded f32 copy of the row in shared
-//    memory (`hs`, one pad word per block: conflict-free), all blocks at once;
-//    rounding then runs four elements per thread with one packed 32-bit store.
-// Arithmetic is Q8Acts::from_f32 (quantmat/q8_acts.rs:26-63) exactly, including
-// the left-to-right f32 block sum.  The scratch is the ring's last stage buffer,
-// which the producer leaves alone until pro_bar completes.
-constexpr int PRO_CH = 20;
+//    right after the wait (raw f32/bf16 in the scratch buffer = last ring stage,
+//    which the producer leaves alone until pro_bar completes).
+//  * Thread t owns elements 4t..4t+3 of every 1024-element chunk j, so the 8
+//    lanes t&~7 .. t|7 hold one 32-element block: block maximum = 3 shuffles,
+//    then the IEEE divide / reciprocal, rounding and one packed 32-bit store,
+//    the PRO_J chunks being independent chains that overlap.
+// Arithmetic is Q8Acts::from_f32 (quantmat/q8_acts.rs:26-63) exactly; the
+// left-to-right f32 block sum (needed by Q4_K consumers only) is done one block
+// per thread over a padded copy of the row.
+constexpr int PRO_CH = 20;          // elements per thread
+constexpr int PRO_J = PRO_CH / 4;   // 1024-element chunks
 
 __device__ __forceinline__ void prologue_gamma(const MvParams &p, int tid, float (&g)[PRO_CH]) {
     const PrepParams &pp = p.prep;
 #pragma unroll
-    for (int j = 0; j < PRO_CH; ++j) {
-        const int i = j * N_CONSUMERS + tid;
-        g[j] = (pp.gamma && i < pp.n) ? pp.gamma[i] : 1.0f;
+    for (int j = 0; j < PRO_J; ++j) {
+        const int e = 4 * tid + 1024 * j;
+        float4 w = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
+        if (pp.gamma && e < pp.n) w = *reinterpret_cast<const float4 *>(pp.gamma + e);
+        g[4 * j] = w.x; g[4 * j + 1] = w.y; g[4 * j + 2] = w.z; g[4 * j + 3] = w.w;
     }
 }
 
@@ -553,28 +557,28 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
     const int n = pp.n, nb = n >> 5;
     const int ke = p.act.ke, kt_shift = ke == 256 ? 3 : 4, kt = 1 << kt_shift;
     const int rec_bytes = M * (ke + ke / 4);
-    float *idv = hs + n + nb;  // reciprocal scale per block
-    float *dv = idv + nb;      // scale per block
     double *dred = reinterpret_cast<double *>(red);
     float v[PRO_CH];
-    // the raw row sits at the start of the scratch (bulk copy); the addend, if any, is read from global
-    {
-        const float *xf = hs;
-        const __nv_bfloat16 *xb = reinterpret_cast<const __nv_bfloat16 *>(hs);
 #pragma unroll
-        for (int j = 0; j < PRO_CH; ++j) {
-            const int i = j * N_CONSUMERS + tid;
-            v[j] = i >= n ? 0.0f : (pp.x_is_bf16 ? __bfloat162float(xb[i]) : xf[i]);
-        }
-        if (pp.add) {
-#pragma unroll
-            for (int j = 0; j < PRO_CH; ++j) {
-                const int i = j * N_CONSUMERS + tid;
-                if (i < n) v[j] = __fadd_rn(v[j], pp.add[i]);
+    for (int j = 0; j < PRO_J; ++j) {
+        const int e = 4 * tid + 1024 * j;
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (e < n) {
+            if (pp.x_is_bf16) {
+                const uint2 r = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __nv_bfloat16 *>(hs) + e);
+                x.x = __uint_as_float(r.x << 16); x.y = __uint_as_float(r.x & 0xffff0000u);
+                x.z = __uint_as_float(r.y << 16); x.w = __uint_as_float(r.y & 0xffff0000u);
+            } else {
+                x = *reinterpret_cast<const float4 *>(hs + e);
             }
+            if (pp.add) {
+                const float4 a = *reinterpret_cast<const float4 *>(pp.add + e);
+                x.x = __fadd_rn(x.x, a.x); x.y = __fadd_rn(x.y, a.y); x.z = __fadd_rn(x.z, a.z); x.w = __fadd_rn(x.w, a.w);
+            }
+            if (pp.xout && blockIdx.x == 0) *reinterpret_cast<float4 *>(pp.xout + e) = x;
         }
+        v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
     }
-    double scale = 1.0;
     if (pp.gamma) {
         // ops::rmsnorm_into (ops/norm.rs:193-198): f64 sum of squares, f64 1/sqrt(mean + eps)
         double ss = 0.0;
@@ -587,63 +591,69 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
         double tot = 0.0;
 #pragma unroll
         for (int i = 0; i < N_CONSUMER_WARPS; ++i) tot += dred[i];
-        scale = 1.0 / sqrt(tot / (double)n + (double)pp.eps);
-    } else {
-        consumer_bar();  // everyone has read the raw row before the padded copy overwrites it
-    }
-    if (p.timeline && tid == 0) p.timeline[(size_t)blockIdx.x * 8 + 7] = globaltimer_ns();  // row in registers
+        const double scale = 1.0 / sqrt(tot / (double)n + (double)pp.eps);
 #pragma unroll
-    for (int j = 0; j < PRO_CH; ++j) {
-        const int i = j * N_CONSUMERS + tid;
-        if (i < n) {
-            if (pp.xout && blockIdx.x == 0) pp.xout[i] = v[j];
-            if (pp.gamma) v[j] = __fmul_rn((float)((double)v[j] * scale), g[j]);
-            hs[i + (i >> 5)] = v[j];
-        }
+        for (int j = 0; j < PRO_CH; ++j) v[j] = __fmul_rn((float)((double)v[j] * scale), g[j]);
     }
-    const int levels = pp.two_level ? 2 : 1;
-#pragma unroll 1
-    for (int lv = 0; lv < levels; ++lv) {
-        const int row = lv;  // one token: rows 0 (value) and 1 (residual)
+    if (p.timeline && tid == 0) p.timeline[(size_t)blockIdx.x * 8 + 7] = globaltimer_ns();  // row normalised
+    if (pp.need_sum) {
+        // exact sequential block sums: padded copy of the row, one block per thread
+        consumer_bar();  // everyone has read the raw row
+#pragma unroll
+        for (int j = 0; j < PRO_J; ++j) {
+            const int e = 4 * tid + 1024 * j;
+            if (e < n) {
+                float *h4 = hs + e + (e >> 5);
+                h4[0] = v[4 * j]; h4[1] = v[4 * j + 1]; h4[2] = v[4 * j + 2]; h4[3] = v[4 * j + 3];
+            }
+        }
         consumer_bar();
         for (int b = tid; b < nb; b += N_CONSUMERS) {
             const float *hb = hs + b * 33;
-            float amax = 0.0f, sum = 0.0f;
-            const bool want_sum = pp.need_sum && lv == 0;
+            float sum = 0.0f;
 #pragma unroll 8
-            for (int k = 0; k < 32; ++k) {
-                const float t = hb[k];
-                amax = fmaxf(amax, fabsf(t));          // f32::max drops a NaN operand, like fmaxf
-                if (want_sum) sum = __fadd_rn(sum, t);  // strictly left to right
-            }
-            const bool fin = amax <= 3.402823466e+38f;
-            const float db = fin ? __fdiv_rn(amax, 127.0f) : 0.0f;
-            const float id = (db > 0.0f) ? __frcp_rn(db) : 0.0f;  // IEEE 1.0/db
-            idv[b] = id;
-            dv[b] = db;
+            for (int k = 0; k < 32; ++k) sum = __fadd_rn(sum, hb[k]);  // strictly left to right
             float *d = reinterpret_cast<float *>(res + (size_t)(b >> kt_shift) * rec_bytes + M * ke);
-            d[row * kt + (b & (kt - 1))] = db;
-            d[M * kt + row * kt + (b & (kt - 1))] = sum;
+            d[M * kt + (b & (kt - 1))] = sum;           // row 0 carries sum(x)
+            if (pp.two_level) d[M * kt + kt + (b & (kt - 1))] = 0.0f;  // the residual row adds nothing to the min term
         }
-        consumer_bar();
-        // four consecutive elements per thread, one packed store
-#pragma unroll 2
-        for (int i = 4 * tid; i < n; i += 4 * N_CONSUMERS) {
-            const int b = i >> 5;
-            float *h4 = hs + i + b;
-            const float id = idv[b];
-            const float x0 = h4[0], x1 = h4[1], x2 = h4[2], x3 = h4[3];
-            const int q0 = q8_round(x0, id), q1 = q8_round(x1, id), q2 = q8_round(x2, id), q3 = q8_round(x3, id);
-            const uint32_t packed = (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) |
-                                    ((uint32_t)(q3 & 0xff) << 24);
-            *reinterpret_cast<uint32_t *>(res + (size_t)(b >> kt_shift) * rec_bytes + row * ke + (b & (kt - 1)) * 32 + (i & 31)) = packed;
-            if (lv + 1 < levels) {
-                // residual for the second digit, exact in one fused operation (own slots: no hazard)
-                const float d1 = dv[b];
-                h4[0] = __fmaf_rn(-d1, (float)q0, x0);
-                h4[1] = __fmaf_rn(-d1, (float)q1, x1);
-                h4[2] = __fmaf_rn(-d1, (float)q2, x2);
-                h4[3] = __fmaf_rn(-d1, (float)q3, x3);
+    }
+    const int levels = pp.two_level ? 2 : 1;
+#pragma unroll
+    for (int lv = 0; lv < 2; ++lv) {
+        if (lv < levels) {
+#pragma unroll
+            for (int j = 0; j < PRO_J; ++j) {
+                const int e = 4 * tid + 1024 * j;
+                const int b = e >> 5;
+                float amax = fmaxf(fmaxf(fabsf(v[4 * j]), fabsf(v[4 * j + 1])), fmaxf(fabsf(v[4 * j + 2]), fabsf(v[4 * j + 3])));
+                if (amax != amax) amax = 0.0f;  // all four NaN: f32::max drops NaN operands
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+                const bool fin = amax <= 3.402823466e+38f;
+                const float db = fin ? __fdiv_rn(amax, 127.0f) : 0.0f;
+                const float id = (db > 0.0f) ? __frcp_rn(db) : 0.0f;  // IEEE 1.0/db
+                const int q0 = q8_round(v[4 * j], id), q1 = q8_round(v[4 * j + 1], id);
+                const int q2 = q8_round(v[4 * j + 2], id), q3 = q8_round(v[4 * j + 3], id);
+                if (e < n) {
+                    uint8_t *rec = res + (size_t)(b >> kt_shift) * rec_bytes;
+                    const int bl = b & (kt - 1);
+                    *reinterpret_cast<uint32_t *>(rec + lv * ke + bl * 32 + (e & 31)) =
+                        (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+                    if ((tid & 7) == 0) {
+                        float *d = reinterpret_cast<float *>(rec + M * ke);
+                        d[lv * kt + bl] = db;
+                        if (!pp.need_sum) d[M * kt + lv * kt + bl] = 0.0f;
+                    }
+                }
+                if (lv + 1 < levels) {
+                    // residual for the second digit, exact in one fused operation
+                    v[4 * j] = __fmaf_rn(-db, (float)q0, v[4 * j]);
+                    v[4 * j + 1] = __fmaf_rn(-db, (float)q1, v[4 * j + 1]);
+                    v[4 * j + 2] = __fmaf_rn(-db, (float)q2, v[4 * j + 2]);
+                    v[4 * j + 3] = __fmaf_rn(-db, (float)q3, v[4 * j + 3]);
+                }
             }
         }
     }
