@@ -164,6 +164,20 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
     }
 }
+// Same, for the producer lane: it has nothing else to do, so it backs off between
+// polls instead of competing with the consumer warps for issue slots.
+__device__ __forceinline__ bool mbar_wait_bounded_relaxed(uint64_t *bar, uint32_t parity) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i) {
+            if (mbar_try_wait(bar, parity)) return true;
+            __nanosleep(40);
+        }
+        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+    }
+}
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t p;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
@@ -213,6 +227,16 @@ __device__ __forceinline__ int dot32(const int4 &w0, const int4 &w1, const int4 
 // Q8Acts::from_f32 (crates/allpaka-backend/src/quantmat/q8_acts.rs:26-63):
 // d = amax/127 (0 when amax is not finite), id = 1/d (IEEE division),
 // q = round-half-away(v*id) saturated to i8, sum = sequential f32 sum.
+// q = round-half-away-from-zero(x * id) saturated to i8, i.e. `(x * id).round() as i8`
+// (quantmat/q8_acts.rs:57).  For |r| <= 129 (always: |x * id| <= 127 up to rounding),
+// trunc(r + copysign(0.5, r)) with |r| < 0.5 -> 0 equals roundf(r) for every f32
+// (checked exhaustively); NaN converts to 0 like the Rust cast.
+__device__ __forceinline__ int q8_round(float x, float id) {
+    const float r = __fmul_rn(x, id);
+    const int q = __float2int_rz(__fadd_rn(r, copysignf(0.5f, r)));
+    return fabsf(r) < 0.5f ? 0 : max(-128, min(127, q));
+}
+
 struct QBlock { float d; float sum; int q; };
 
 __device__ __forceinline__ QBlock quantize_block(float v, bool need_sum) {
@@ -223,10 +247,7 @@ __device__ __forceinline__ QBlock quantize_block(float v, bool need_sum) {
     const bool fin = amax <= 3.402823466e+38f;
     const float db = fin ? __fdiv_rn(amax, 127.0f) : 0.0f;
     const float id = (db > 0.0f) ? __frcp_rn(db) : 0.0f;  // IEEE 1.0/db
-    float r = roundf(__fmul_rn(v, id));
-    int q;
-    if (r != r) q = 0;
-    else q = (int)fminf(fmaxf(r, -128.0f), 127.0f);
+    const int q = q8_round(v, id);
     float s = 0.0f;
     if (need_sum) {
         // xs.iter().sum::<f32>(): strictly left to right
@@ -544,11 +565,6 @@ __device__ __forceinline__ void prologue_gamma(const MvParams &p, int tid, float
     }
 }
 
-__device__ __forceinline__ int q8_round(float x, float id) {
-    const float r = roundf(__fmul_rn(x, id));  // half away from zero, like f32::round
-    return (r != r) ? 0 : (int)fminf(fmaxf(r, -128.0f), 127.0f);
-}
-
 template <int M>
 __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, float *hs, float *red, int tid,
                                                const float (&g)[PRO_CH]) {
@@ -736,7 +752,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 const uint32_t bytes = (uint32_t)p.prep.n * (p.prep.x_is_bf16 ? 2u : 4u);
                 mbar_arrive_expect_tx(acts_bar, bytes);
                 bulk_g2s(stages + (size_t)(NS - 1) * stage_bytes, p.prep.x, bytes, acts_bar, pol_a);
-                if (!mbar_wait_bounded(pro_bar, 0u)) atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
+                if (!mbar_wait_bounded_relaxed(pro_bar, 0u)) atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
             }
             if (p.pro == PRO_LOAD) {
                 const uint32_t bytes = (uint32_t)(p.KS * act_rec);
@@ -750,7 +766,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             for (; it < n_total; ++it) {
                 const int s = it % NS;
                 const uint32_t ph = (uint32_t)((it / NS) & 1);
-                if (!mbar_wait_bounded(&empty[s], ph ^ 1u)) {
+                if (!mbar_wait_bounded_relaxed(&empty[s], ph ^ 1u)) {
                     atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
                     break;
                 }
