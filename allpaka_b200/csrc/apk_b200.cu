@@ -27,15 +27,13 @@ using namespace apk;
 
 namespace {
 
-thread_local std::string g_last_error;
+thread_local char g_last_error[512] = "";  // fixed storage: reporting an error never touches the heap
 
 int fail(int code, const char *fmt, ...) {
-    char buf[512];
     va_list ap;
     va_start(ap, fmt);
-    vsnprintf(buf, sizeof buf, fmt, ap);
+    vsnprintf(g_last_error, sizeof g_last_error, fmt, ap);
     va_end(ap);
-    g_last_error = buf;
     return code;
 }
 
@@ -1014,7 +1012,7 @@ void apk_stats(apk_ctx *c, apk_stats_t *out) {
     *out = c->st;
 }
 
-const char *apk_last_error(apk_ctx *) { return g_last_error.c_str(); }
+const char *apk_last_error(apk_ctx *) { return g_last_error; }
 
 int apk_shard_plan(uint32_t kind, uint32_t ty, uint32_t n_out, uint32_t n_in, uint32_t row_granule, int rank, int world,
                    uint32_t out[4]) {
