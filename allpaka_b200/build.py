@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libapk_b200.so")
 SOURCES = ["apk_b200.cu"]
-DEPS = ["apk_b200.cu", "decode.inl", "kernels.cuh", os.path.join("..", "..", "include", "allpaka_b200.h")]
+DEPS = ["apk_b200.cu", "decode.inl", "noalloc.inl", "kernels.cuh", os.path.join("..", "..", "include", "allpaka_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

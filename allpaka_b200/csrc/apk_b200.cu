@@ -193,6 +193,7 @@ struct apk_ctx {
     bool use_pdl = true;        // ALLPAKA_B200_PDL=0 turns programmatic dependent launch off
     void *comm = nullptr;
     std::unique_ptr<Plan> plan;
+    unsigned char *noalloc_ptr = nullptr;  // device address of the built-in scratch array (apk_matvec_noalloc)
     // host address -> device-resident raw GGUF bytes written by apk_debug_synth_matrix
     std::map<const uint8_t *, std::pair<uint8_t *, size_t>> raw_dev;
 };
@@ -1051,3 +1052,4 @@ int apk_dist_init(apk_ctx *c, int rank, int world, const void *unique_id) {
 }  // extern "C"
 
 #include "decode.inl"
+#include "noalloc.inl"

@@ -107,7 +107,7 @@ EXPORTS = (
     "apk_decode_token", "apk_decode_replay", "apk_debug_block_dots", "apk_debug_q8_acts",
     "apk_stats", "apk_last_error", "apk_dist_unique_id", "apk_dist_init",
     "apk_debug_synth_matrix", "apk_debug_synth_release", "apk_decode_profile",
-    "apk_debug_matvec_timeline", "apk_shard_plan",
+    "apk_debug_matvec_timeline", "apk_shard_plan", "apk_matvec_noalloc",
 )
 
 _lib = None
@@ -145,6 +145,8 @@ def load_library() -> C.CDLL:
     l.apk_debug_synth_release.argtypes = [C.c_void_p]
     l.apk_debug_matvec_timeline.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
                                             C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
+    l.apk_matvec_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
+                                     C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_int]
     l.apk_decode_profile.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
     l.apk_stats.argtypes = [C.c_void_p, C.c_void_p]
     l.apk_stats.restype = None
@@ -451,6 +453,17 @@ class Gpu:
         rc = self._l.apk_debug_q8_acts(self._h, x.ctypes.data, x.size, _ptr(gamma), eps, d.ctypes.data,
                                        s.ctypes.data, q.ctypes.data)
         return (d, s, q) if self._check(rc) else None
+
+    def matvec_noalloc(self, ty: int, w, n_in: int, n_out: int, x_dev: int, m: int, y_dev: int,
+                       stream: int = 0, act_mode: int = ACT_AUTO, wait: bool = True) -> bool:
+        """apk_matvec_noalloc: for callers that may not allocate device memory here (VRAM fully
+        budgeted, or a latency-bounded loop that cannot afford the stall).  `w` must already be resident;
+        `x_dev`, `y_dev` and `stream` are raw device pointers / a cudaStream_t handle owned by the
+        caller.  True = executed, False = declined (see ``last_decline``)."""
+        w = _u8(w)
+        rc = self._l.apk_matvec_noalloc(self._h, w.ctypes.data, ty, n_in, n_out, x_dev, m, act_mode, y_dev,
+                                        stream, 1 if wait else 0)
+        return self._check(rc)
 
     def debug_matvec_timeline(self, ty, w, n_in, n_out, x, m=1):
         """Per-CTA global-timer stamps (ns) of one matvec launch; see the C header."""

@@ -205,6 +205,37 @@ int apk_debug_block_dots(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_in
 int apk_debug_q8_acts(apk_ctx *ctx, const float *x, uint32_t n, const float *gamma, float eps,
                       float *d, float *sum, int8_t *q);
 
+/* A matvec that allocates nothing.  It has no counterpart in the reference.
+ *
+ * For callers that cannot call cudaMalloc at this point: every byte of device
+ * memory was budgeted and handed out at start-up (a late allocation would
+ * simply fail), or the call sits in a latency-bounded decode loop where the
+ * device-wide stall of an allocation is not acceptable.  They own x and y already; the kernel's
+ * private scratch (stream-K partial sums, tile arrival counters, error word,
+ * quantised-activation records) lives in a fixed ~3.3 MB array inside the
+ * library's device image, which every GPU that loads the library holds until
+ * the process exits.
+ *
+ *   w        host address of a matrix that is ALREADY resident (apk_register_matrix or any
+ *            earlier call); otherwise APK_DECLINE_INVALID_STATE, because uploading would allocate
+ *   x_dev    device pointer, m * n_in floats;  y_dev  device pointer, m * n_out floats
+ *   stream   the CUDA stream (cudaStream_t) to enqueue on; wait != 0 also synchronises it and
+ *            reports an expired device-side wait
+ * Limits: n_in <= APK_NOALLOC_MAX_N_IN, n_out <= APK_NOALLOC_MAX_N_OUT, m <= APK_MAX_M, at most 160
+ * SMs; larger requests are declined with APK_DECLINE_UNSUPPORTED_SHAPE / _MISSING_CAPABILITY.
+ * No cudaMalloc, cudaFree or other allocating call is made, on any path.
+ *
+ * The first call on a device resolves the array's device address
+ * (cudaGetSymbolAddress); make that first call before starting a stream capture.
+ * All calls share the one array and it keeps the last call's contents (the
+ * counters and the error word are cleared at the start of every call): two calls
+ * whose kernels overlap on the GPU, on different streams or contexts of the
+ * same device, race.  Results are identical to apk_matvec's. */
+#define APK_NOALLOC_MAX_N_IN 32768u
+#define APK_NOALLOC_MAX_N_OUT 524288u
+int apk_matvec_noalloc(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_in, uint32_t n_out, const float *x_dev,
+                       uint32_t m, uint32_t act_mode, float *y_dev, void *stream, int wait);
+
 /* Trace: per-CTA timestamps (GPU global timer, ns) of one matvec launch on
  * activations already quantised: stamps[cta][8] = {kernel entry, first unit in
  * shared memory, second unit, last unit, a tile finished, last tile finished,
