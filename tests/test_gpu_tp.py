@@ -1,0 +1,87 @@
+"""Tensor-parallel decode on 2 GPUs against the single-device oracle (needs >= 2 GPUs; skipped otherwise).
+
+Two child processes, one GPU each, join an NCCL group through the library
+(apk_dist_init), upload only their shards and decode the same token; rank 0's
+logits must match the CPU oracle of the unsharded model."""
+import os
+import socket
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, ty, m, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from allpaka_b200 import gpu as G
+    from allpaka_b200 import synth
+    from oracle import oracle as orc
+    from tests.util import Region, make_layer, oracle_decode, oracle_logits, rel_l2, rope_table
+
+    g = G.Gpu(rank)
+    ids = [G.Gpu.dist_unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(ids, src=0)
+    g.dist_init(rank, world, ids[0])
+    hidden, nh, nkv, ffn, vocab, hd = 1024, 8, 2, 2048, 1536, 128
+    nq, nk = nh * hd, nkv * hd
+    layers = [make_layer(ty, hidden, nq, nk, ffn, 300 + 100 * l, True) for l in range(2)]
+    head = synth.matrix(ty, vocab, hidden, 999)
+    names = ("wq", "wk", "wv", "wo", "gate", "up", "down")
+    r = Region([L[n] for L in layers for n in names] + [head])
+    assert g.attach(r.buf)
+    tls = []
+    for li, L in enumerate(layers):
+        v = dict(zip(names, r.views[li * 7:(li + 1) * 7]))
+        tls.append(G.TokenLayer(L["attn_norm"], L["ffn_norm"], (ty, v["wq"], nq), (ty, v["wk"], nk), (ty, v["wv"], nk),
+                                (ty, v["wo"], hidden), (ty, v["gate"], ffn), (ty, v["up"], ffn), (ty, v["down"], hidden),
+                                L["q_norm"], L["k_norm"]))
+    out_norm = synth.gamma(hidden, 998)
+    x = synth.normal_f32((m, hidden), 997)
+    rope = rope_table(orc, np.arange(m) + 4000, hd, hd)
+    req = G.TokenReq(tls, out_norm, (ty, r.views[-1], vocab), x, m, rope, hd, 1e-6, hidden, hd, nh, nkv)
+    logits = g.decode_token_checked(req)
+    again = g.decode_token_checked(req)
+    req.argmax = True
+    ids_ = g.decode_token_checked(req)
+    if rank == 0:
+        xo = oracle_decode(orc, ty, layers, hidden, nq, nk, hd, ffn, 1e-6, rope, x, m)
+        want = oracle_logits(orc, ty, head, vocab, hidden, xo, out_norm, 1e-6, m)
+        out_q.put((rel_l2(logits, want), bool(np.array_equal(logits, again)),
+                   [int(i) for i in ids_] == [int(np.flatnonzero(row == row.max())[-1]) for row in logits]))
+    dist.barrier()
+    g.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("ty,m", [(8, 1), (8, 3), (12, 1)])
+def test_two_gpu_decode_matches_the_unsharded_oracle(ty, m):
+    import torch
+    import torch.multiprocessing as mp
+
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, ty, m, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    err, same, argmax_ok = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert err <= 2e-3, err
+    assert same and argmax_ok
