@@ -635,41 +635,54 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
         }
     }
     const int levels = pp.two_level ? 2 : 1;
+    // Stage by stage across the PRO_J chunks (not chunk by chunk): the warp shuffles
+    // order the instruction stream, so independent work has to sit side by side for
+    // the chains of the five blocks to overlap.
 #pragma unroll
     for (int lv = 0; lv < 2; ++lv) {
         if (lv < levels) {
+            float amax[PRO_J], db[PRO_J], id[PRO_J];
+            int q[PRO_CH];
+#pragma unroll
+            for (int j = 0; j < PRO_J; ++j) {
+                amax[j] = fmaxf(fmaxf(fabsf(v[4 * j]), fabsf(v[4 * j + 1])), fmaxf(fabsf(v[4 * j + 2]), fabsf(v[4 * j + 3])));
+                if (amax[j] != amax[j]) amax[j] = 0.0f;  // all four NaN: f32::max drops NaN operands
+            }
+#pragma unroll
+            for (int o = 1; o <= 4; o <<= 1) {
+                float t[PRO_J];
+#pragma unroll
+                for (int j = 0; j < PRO_J; ++j) t[j] = __shfl_xor_sync(0xffffffffu, amax[j], o);
+#pragma unroll
+                for (int j = 0; j < PRO_J; ++j) amax[j] = fmaxf(amax[j], t[j]);
+            }
+#pragma unroll
+            for (int j = 0; j < PRO_J; ++j) db[j] = amax[j] <= 3.402823466e+38f ? __fdiv_rn(amax[j], 127.0f) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < PRO_J; ++j) id[j] = (db[j] > 0.0f) ? __frcp_rn(db[j]) : 0.0f;  // IEEE 1.0/db
+#pragma unroll
+            for (int k = 0; k < PRO_CH; ++k) q[k] = q8_round(v[k], id[k >> 2]);
 #pragma unroll
             for (int j = 0; j < PRO_J; ++j) {
                 const int e = 4 * tid + 1024 * j;
                 const int b = e >> 5;
-                float amax = fmaxf(fmaxf(fabsf(v[4 * j]), fabsf(v[4 * j + 1])), fmaxf(fabsf(v[4 * j + 2]), fabsf(v[4 * j + 3])));
-                if (amax != amax) amax = 0.0f;  // all four NaN: f32::max drops NaN operands
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-                amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
-                const bool fin = amax <= 3.402823466e+38f;
-                const float db = fin ? __fdiv_rn(amax, 127.0f) : 0.0f;
-                const float id = (db > 0.0f) ? __frcp_rn(db) : 0.0f;  // IEEE 1.0/db
-                const int q0 = q8_round(v[4 * j], id), q1 = q8_round(v[4 * j + 1], id);
-                const int q2 = q8_round(v[4 * j + 2], id), q3 = q8_round(v[4 * j + 3], id);
                 if (e < n) {
                     uint8_t *rec = res + (size_t)(b >> kt_shift) * rec_bytes;
                     const int bl = b & (kt - 1);
                     *reinterpret_cast<uint32_t *>(rec + lv * ke + bl * 32 + (e & 31)) =
-                        (uint32_t)(q0 & 0xff) | ((uint32_t)(q1 & 0xff) << 8) | ((uint32_t)(q2 & 0xff) << 16) | ((uint32_t)(q3 & 0xff) << 24);
+                        (uint32_t)(q[4 * j] & 0xff) | ((uint32_t)(q[4 * j + 1] & 0xff) << 8) |
+                        ((uint32_t)(q[4 * j + 2] & 0xff) << 16) | ((uint32_t)(q[4 * j + 3] & 0xff) << 24);
                     if ((tid & 7) == 0) {
                         float *d = reinterpret_cast<float *>(rec + M * ke);
-                        d[lv * kt + bl] = db;
+                        d[lv * kt + bl] = db[j];
                         if (!pp.need_sum) d[M * kt + lv * kt + bl] = 0.0f;
                     }
                 }
-                if (lv + 1 < levels) {
-                    // residual for the second digit, exact in one fused operation
-                    v[4 * j] = __fmaf_rn(-db, (float)q0, v[4 * j]);
-                    v[4 * j + 1] = __fmaf_rn(-db, (float)q1, v[4 * j + 1]);
-                    v[4 * j + 2] = __fmaf_rn(-db, (float)q2, v[4 * j + 2]);
-                    v[4 * j + 3] = __fmaf_rn(-db, (float)q3, v[4 * j + 3]);
-                }
+            }
+            if (lv + 1 < levels) {
+                // residual for the second digit, exact in one fused operation
+#pragma unroll
+                for (int k = 0; k < PRO_CH; ++k) v[k] = __fmaf_rn(-db[k >> 2], (float)q[k], v[k]);
             }
         }
     }
