@@ -193,6 +193,9 @@ struct apk_ctx {
     bool use_pdl = true;        // ALLPAKA_B200_PDL=0 turns programmatic dependent launch off
     void *comm = nullptr;
     std::unique_ptr<Plan> plan;
+    float *xch_local = nullptr;     // this rank's exchange buffer (apk_dist_p2p_export)
+    XchPeers xch{};                 // every rank's buffer, peer-mapped
+    bool p2p_ready = false;
     unsigned char *noalloc_ptr = nullptr;  // device address of the built-in scratch array (apk_matvec_noalloc)
     // host address -> device-resident raw GGUF bytes written by apk_debug_synth_matrix
     std::map<const uint8_t *, std::pair<uint8_t *, size_t>> raw_dev;
@@ -610,7 +613,7 @@ int finish(apk_ctx *c) {
         cudaMemsetAsync(c->d_err, 0, sizeof(int), c->stream);
         cudaStreamSynchronize(c->stream);
         return fail(APK_ERR_TIMEOUT, "device-side wait expired (%s)",
-                    w == ERRW_PRODUCER_TIMEOUT ? "copy producer" : "tile consumer");
+                    w == ERRW_PRODUCER_TIMEOUT ? "copy producer" : w == ERRW_PEER_TIMEOUT ? "a peer rank never announced its partial sums" : "tile consumer");
     }
     return APK_OK;
 }
@@ -684,6 +687,10 @@ void apk_shutdown(apk_ctx *c) {
     c->mats.clear();
     for (auto &kv : c->raw_dev) cudaFree(kv.second.first);
     c->raw_dev.clear();
+    if (c->p2p_ready)
+        for (int r = 0; r < c->world; ++r)
+            if (r != c->rank && c->xch.slots[r]) cudaIpcCloseMemHandle(c->xch.slots[r]);
+    if (c->xch_local) cudaFree(c->xch_local);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
     for (DevBuf *b : {&c->staging, &c->partials, &c->counters, &c->x_dev, &c->y_dev, &c->act_a, &c->act_b, &c->misc, &c->dump})
         b->release();
@@ -1019,6 +1026,43 @@ int apk_shard_plan(uint32_t kind, uint32_t ty, uint32_t n_out, uint32_t n_in, ui
                    uint32_t out[4]) {
     if (!out) return fail(APK_ERR_INVALID_ARG, "shard_plan: null out");
     return shard_plan(kind, ty, n_out, n_in, row_granule, rank, world, out);
+}
+
+int apk_dist_p2p_export(apk_ctx *c, void *handle_out) {
+    if (!c || !handle_out) return fail(APK_ERR_INVALID_ARG, "p2p_export: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    if (c->world > XCH_MAX_RANKS) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "p2p exchange is built for at most %d ranks", XCH_MAX_RANKS);
+    if (!c->xch_local) {
+        CUDA_TRY(cudaMalloc((void **)&c->xch_local, XCH_BYTES));
+        CUDA_TRY(cudaMemset(c->xch_local, 0, XCH_BYTES));
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == APK_IPC_HANDLE_BYTES, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    CUDA_TRY(cudaIpcGetMemHandle(&h, c->xch_local));
+    memcpy(handle_out, &h, sizeof h);
+    return APK_OK;
+}
+
+int apk_dist_p2p_open(apk_ctx *c, const void *handles) {
+    if (!c || !handles) return fail(APK_ERR_INVALID_ARG, "p2p_open: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    if (!c->xch_local) return fail(APK_DECLINE_INVALID_STATE, "p2p_open before p2p_export");
+    if (c->p2p_ready) return APK_OK;
+    c->xch.rank = c->rank;
+    c->xch.world = c->world;
+    for (int r = 0; r < c->world; ++r) {
+        if (r == c->rank) { c->xch.slots[r] = c->xch_local; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const uint8_t *)handles + (size_t)r * APK_IPC_HANDLE_BYTES, sizeof h);
+        void *ptr = nullptr;
+        CUDA_TRY(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        c->xch.slots[r] = (float *)ptr;
+    }
+    c->plan.reset();  // graphs captured with NCCL reductions are rebuilt
+    c->p2p_ready = true;
+    return APK_OK;
 }
 
 int apk_dist_unique_id(void *id_out) {

@@ -85,6 +85,8 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
     P->layers_key = r->layers; P->n_layers = r->n_layers; P->output_key = r->output.w;
     P->hidden = H; P->head_dim = r->head_dim; P->n_heads = r->n_heads; P->n_kv_heads = r->n_kv_heads;
     P->rot_dim = r->rot_dim; P->vocab = r->output.n_out; P->eps = r->eps; P->ffn = ffn;
+    if (c->p2p_ready && ((size_t)APK_MAX_M * H > (size_t)XCH_ROW_FLOATS || H % 4))
+        return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "hidden %u exceeds the peer exchange buffer", H);
     if (P->vocab % c->world) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "vocab %u does not split over %d ranks", P->vocab, c->world);
     P->nq_l = nq / c->world; P->nkv_l = nkv / c->world; P->vocab_l = P->vocab / c->world;
 
@@ -196,6 +198,25 @@ struct TokenLaunch {
         const uint32_t H = P->hidden;
         MvParams p{};
         use_records(c, W, autom, records, &p);
+        if (c->world > 1 && c->p2p_ready) {
+            // partial sums straight into every rank's exchange buffer; a small kernel adds them
+            p.epi = EPI_PEERS;
+            p.xch = c->xch;
+            p.xch_row = (int)H;
+            APK_TRY(launch_matvec(c, W, p, autom));
+            XchReduceParams rp{};
+            rp.xch = c->xch;
+            rp.x = P->x[cur].as<float>(); rp.ldx = (int)H;
+            rp.xout = P->x[cur ^ 1].as<float>(); rp.ldxout = (int)H;
+            rp.n = (int)H; rp.m = (int)m;
+            rp.err = c->d_err;
+            rp.pdl = c->use_pdl ? 1 : 0;
+            const unsigned grid = (unsigned)(((size_t)m * H + 1023) / 1024);
+            CUDA_TRY(launch_ex(c, xch_reduce_kernel, dim3(grid), dim3(256), 0, c->use_pdl, rp));
+            c->st.launches++;
+            cur ^= 1;
+            return APK_OK;
+        }
         if (c->world > 1) {
             p.epi = EPI_STORE;
             p.y = P->yp.as<float>();

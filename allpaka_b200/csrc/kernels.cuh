@@ -47,6 +47,7 @@ constexpr int TY_Q4_K = 12;
 // Error words written by kernels (never a trap): which bounded wait gave up.
 constexpr int ERRW_PRODUCER_TIMEOUT = 1;
 constexpr int ERRW_CONSUMER_TIMEOUT = 2;
+constexpr int ERRW_PEER_TIMEOUT = 3;
 
 // Spin budget of one mbarrier wait, in SM clock cycles (~2 s).
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
@@ -56,7 +57,29 @@ enum Epilogue : int {
     EPI_ADD = 1,     // y[m][row] = resid[m][row] + v   (residual stream update)
     EPI_QKV_ROPE = 2,// tile = one head: optional per-head RMSNorm, NeoX RoPE on Q and K heads
     EPI_SWIGLU = 3,  // tile = 64 gate rows + 64 up rows: act = silu(g)*u, optionally packed for `down`
+    EPI_PEERS = 4,   // tensor parallel: this rank's partial sums stored straight into every rank's exchange buffer
 };
+
+// One-shot exchange of row-parallel partial sums between the ranks of a
+// tensor-parallel group over peer-mapped memory (plain stores across NVLink; no
+// multicast).  Every rank owns one buffer, laid out
+//   slots [2 parity][APK_XCH_MAX_RANKS][XCH_ROW_FLOATS] f32 | flags[APK_XCH_MAX_RANKS] u32 | epoch u32 | done u32 | dead u32
+// Rank s writes its partial vector into slot (parity, s) of EVERY rank's buffer
+// (the matvec epilogue), then raises flags[s] = epoch on every rank; a rank
+// adds the slots 0..world-1 in rank order once all its flags show the epoch.
+constexpr int XCH_MAX_RANKS = 8;
+constexpr int XCH_ROW_FLOATS = 8 * 16384;  // m * hidden floats per slot
+constexpr size_t XCH_SLOTS_BYTES = (size_t)2 * XCH_MAX_RANKS * XCH_ROW_FLOATS * sizeof(float);
+constexpr size_t XCH_BYTES = XCH_SLOTS_BYTES + 256;
+
+struct XchPeers {
+    float *slots[XCH_MAX_RANKS];  // peer-mapped base of each rank's buffer (own included)
+    int rank, world;
+};
+__host__ __device__ inline uint32_t *xch_flags(float *base) { return reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(base) + XCH_SLOTS_BYTES); }
+__host__ __device__ inline uint32_t *xch_epoch(float *base) { return xch_flags(base) + XCH_MAX_RANKS; }
+__host__ __device__ inline uint32_t *xch_done(float *base) { return xch_flags(base) + XCH_MAX_RANKS + 1; }
+__host__ __device__ inline uint32_t *xch_dead(float *base) { return xch_flags(base) + XCH_MAX_RANKS + 2; }
 
 // Prepared activations as the matvec kernel streams them: per K-step of `ke`
 // elements one record {q[m_eff][ke] i8, d[m_eff][ke/32] f32, sum[m_eff][ke/32] f32}.
@@ -117,6 +140,8 @@ struct MvParams {
     const float *rope; int half;       // [m][half][2] (sin, cos)
     ActLayout q_next;                  // optional: roped Q heads packed as the next matvec's activations
     int q_next_two_level, q_next_need_sum;
+    // EPI_PEERS
+    XchPeers xch; int xch_row;         // floats per token row in a slot (= hidden)
     // EPI_SWIGLU
     float *act_f32; int ld_act;        // optional f32 swiglu rows [m][ffn]
     ActLayout act_next;                // optional packed activations for the down projection
@@ -346,6 +371,89 @@ __global__ void __launch_bounds__(256) prep_acts_kernel(PrepParams p, int pdl) {
     if (p.gamma) v = __fmul_rn((float)((double)v * scale), p.gamma[i]);
     if (p.hout) p.hout[(size_t)m * p.ldh + i] = v;
     quantize_store(p.out, p.two_level, p.need_sum, m, blk, lane, v);
+}
+
+// ------------------------------------------------- tensor-parallel exchange
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+struct XchReduceParams {
+    XchPeers xch;
+    const float *x; int ldx;   // residual stream in  [m][n]
+    float *xout; int ldxout;   // residual stream out [m][n] = x + sum over ranks of the partial vectors
+    int n, m;
+    int *err;
+    int pdl;
+};
+
+// grid = ceil(m*n / 1024), 256 threads, four floats per thread.  Runs after the
+// row-parallel matvec of this rank (programmatic dependency): announces this
+// rank's slot to every peer, waits (bounded) until every rank's slot for the
+// same epoch has been announced here, then adds the slots in rank order.
+__global__ void __launch_bounds__(256) xch_reduce_kernel(XchReduceParams p) {
+    if (p.pdl) {
+        pdl_launch_dependents();
+        pdl_wait();  // this rank's matvec (and its peer stores) is complete
+    }
+    float *mine = p.xch.slots[p.xch.rank];
+    const uint32_t e = __ldcg(xch_epoch(mine)) + 1u;
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    if (blockIdx.x == 0 && threadIdx.x < p.xch.world)
+        st_release_sys(xch_flags(p.xch.slots[threadIdx.x]) + p.xch.rank, e);
+    __syncthreads();
+    if (threadIdx.x < p.xch.world) {
+        const uint32_t *f = xch_flags(mine) + threadIdx.x;
+        volatile uint32_t *dead = xch_dead(mine);
+        const long long t0 = clock64();
+        bool ok = false;
+        while (!*dead) {
+            if ((int32_t)(ld_acquire_sys(f) - e) >= 0) { ok = true; break; }
+            if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
+            __nanosleep(20);
+        }
+        if (!ok) {
+            // a peer never announced: record it, stop waiting for good, finish normally
+            s_ok = 0;
+            *dead = 1u;
+            atomicExch(p.err, ERRW_PEER_TIMEOUT);
+        }
+    }
+    __syncthreads();
+    const uint32_t parity = e & 1u;
+    const size_t total = (size_t)p.m * p.n;
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i < total && s_ok) {
+        const int m = (int)(i / p.n), col = (int)(i % p.n);
+        float4 acc = *reinterpret_cast<const float4 *>(p.x + (size_t)m * p.ldx + col);
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < p.xch.world; ++r) {  // fixed order: run-to-run identical
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(
+                mine + ((size_t)parity * XCH_MAX_RANKS + r) * XCH_ROW_FLOATS + (size_t)m * p.n + col));
+            sum.x = __fadd_rn(sum.x, v.x); sum.y = __fadd_rn(sum.y, v.y);
+            sum.z = __fadd_rn(sum.z, v.z); sum.w = __fadd_rn(sum.w, v.w);
+        }
+        acc.x = __fadd_rn(acc.x, sum.x); acc.y = __fadd_rn(acc.y, sum.y);
+        acc.z = __fadd_rn(acc.z, sum.z); acc.w = __fadd_rn(acc.w, sum.w);
+        *reinterpret_cast<float4 *>(p.xout + (size_t)m * p.ldxout + col) = acc;
+    }
+    // the last CTA out advances the epoch (every CTA has read it by then)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        const uint32_t old = atomicAdd(xch_done(mine), 1u);
+        if (old == gridDim.x - 1) {
+            *xch_done(mine) = 0u;
+            *xch_epoch(mine) = e;
+        }
+    }
 }
 
 // ------------------------------------------------------------------ repack
@@ -1041,6 +1149,24 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
             if (p.epi == EPI_ADD) v = __fadd_rn(p.resid[(size_t)m * p.ldr + row], v);
             p.y[(size_t)m * p.ldy + row] = v;
         }
+        return;
+    }
+    if (p.epi == EPI_PEERS) {
+        // the exchange in flight is epoch + 1 (the epoch word only moves between kernels)
+        const uint32_t parity = (__ldcg(xch_epoch(p.xch.slots[p.xch.rank])) + 1u) & 1u;
+        const size_t slot = ((size_t)parity * XCH_MAX_RANKS + p.xch.rank) * XCH_ROW_FLOATS;
+        for (int i = tid; i < MO * TILE_ROWS; i += N_CONSUMERS) {
+            const int m = i / TILE_ROWS, r = i % TILE_ROWS;
+            const int row = row0 + r;
+            if (row >= p.n_out) continue;
+            const float v = val(m, r);
+            for (int k = 0; k < p.xch.world; ++k) {
+                const int dst = (p.xch.rank + k) % p.xch.world;  // start with the local copy, spread the links
+                p.xch.slots[dst][slot + (size_t)m * p.xch_row + row] = v;
+            }
+        }
+        // No fence here: the flag that publishes these stores is raised by a kernel that runs
+        // after this grid has completed (st.release.sys, cumulative over what it has observed).
         return;
     }
     if (p.epi == EPI_QKV_ROPE) {

@@ -108,6 +108,7 @@ EXPORTS = (
     "apk_stats", "apk_last_error", "apk_dist_unique_id", "apk_dist_init",
     "apk_debug_synth_matrix", "apk_debug_synth_release", "apk_decode_profile",
     "apk_debug_matvec_timeline", "apk_shard_plan", "apk_matvec_noalloc",
+    "apk_dist_p2p_export", "apk_dist_p2p_open",
 )
 
 _lib = None
@@ -154,6 +155,8 @@ def load_library() -> C.CDLL:
     l.apk_last_error.restype = C.c_char_p
     l.apk_shard_plan.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_int, C.c_int,
                                  C.c_void_p]
+    l.apk_dist_p2p_export.argtypes = [C.c_void_p, C.c_void_p]
+    l.apk_dist_p2p_open.argtypes = [C.c_void_p, C.c_void_p]
     l.apk_dist_unique_id.argtypes = [C.c_void_p]
     l.apk_dist_init.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p]
     _lib = l
@@ -523,6 +526,21 @@ class Gpu:
         if rc != 0:
             raise GpuError(rc, l.apk_last_error(None).decode())
         return buf.raw
+
+    def p2p_export(self) -> bytes:
+        """This rank's exchange-buffer handle (64 bytes) for the peer-memory reductions."""
+        buf = C.create_string_buffer(64)
+        rc = self._l.apk_dist_p2p_export(self._h, buf)
+        if rc != 0:
+            raise GpuError(rc, self._err())
+        return buf.raw
+
+    def p2p_open(self, handles: Sequence[bytes]) -> None:
+        """Open every rank's handle (rank order); reductions then go over peer memory."""
+        blob = C.create_string_buffer(b"".join(handles), 64 * len(handles))
+        rc = self._l.apk_dist_p2p_open(self._h, blob)
+        if rc != 0:
+            raise GpuError(rc, self._err())
 
     def dist_init(self, rank: int, world: int, unique_id: bytes) -> None:
         buf = C.create_string_buffer(unique_id, 128)

@@ -285,6 +285,10 @@ def run_ours(args, rank, world, local_rank):
         ids = [G.Gpu.dist_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
         g.dist_init(rank, world, ids[0])
+        if args.tp_exchange == "p2p":
+            handles = [None] * world
+            dist.all_gather_object(handles, g.p2p_export())
+            g.p2p_open(handles)
     n_layers = args.layers
     want_cpu = rank == 0 and world == 1 and not args.no_cpu_baseline
     t_setup = time.perf_counter()
@@ -376,7 +380,7 @@ def run_ours(args, rank, world, local_rank):
             "dtype": "int8 x int8 -> int32, f32 scales", "data": "synthetic",
             "config": {"workload": f"qwen3-32b-shaped decode step, {n_layers} layers + lm_head, Q8_0, batch 1",
                        "weights_gb": token_bytes(n_layers) / 1e9, "l2": "inputs larger than L2 (33.98 GB streamed per step)",
-                       "parallelism": "tp%d" % world if world > 1 else "single gpu",
+                       "parallelism": ("tp%d, %s reductions" % (world, args.tp_exchange)) if world > 1 else "single gpu",
                        "attention_core": "identity on the roped Q slice"},
             "hbm_gbs": token_bytes(n_layers) / (ms_per_step * 1e-3) / 1e9,
             "e2e": {"value": e2e_val, "unit": "tok/s", "h2d_bytes_per_step": HIDDEN * 4 + rope_bytes,
@@ -403,6 +407,8 @@ def main():
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="fewer layers only for quick checks")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU-baseline work")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tp-exchange", default="p2p", choices=["p2p", "nccl"],
+                    help="how the two per-layer reductions cross GPUs: peer-memory stores or NCCL all-reduce")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -292,6 +292,16 @@ const char *apk_last_error(apk_ctx *ctx);
  * matrix does not divide. */
 int apk_shard_plan(uint32_t kind, uint32_t ty, uint32_t n_out, uint32_t n_in, uint32_t row_granule, int rank,
                    int world, uint32_t out[4]);
+/* Optional low-latency exchange for the two per-layer reductions: each rank
+ * exports one device buffer (CUDA IPC handle, APK_IPC_HANDLE_BYTES), the host
+ * gathers the handles of all ranks in rank order and every rank opens them.
+ * From then on the row-parallel matvecs store their partial sums straight into
+ * every rank's buffer over NVLink and a small kernel adds them in rank order
+ * (bounded waits on per-rank flags), instead of an NCCL all-reduce.  At most 8
+ * ranks, m * hidden <= 131072. */
+#define APK_IPC_HANDLE_BYTES 64
+int apk_dist_p2p_export(apk_ctx *ctx, void *handle_out);
+int apk_dist_p2p_open(apk_ctx *ctx, const void *handles /* world * APK_IPC_HANDLE_BYTES */);
 #define APK_UNIQUE_ID_BYTES 128
 int apk_dist_unique_id(void *id_out /* APK_UNIQUE_ID_BYTES */);
 int apk_dist_init(apk_ctx *ctx, int rank, int world, const void *unique_id);

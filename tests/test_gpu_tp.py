@@ -20,7 +20,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, ty, m, out_q):
+def _worker(rank, world, port, ty, m, exchange, out_q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
                       LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -35,6 +35,10 @@ def _worker(rank, world, port, ty, m, out_q):
     ids = [G.Gpu.dist_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(ids, src=0)
     g.dist_init(rank, world, ids[0])
+    if exchange == "p2p":
+        handles = [None] * world
+        dist.all_gather_object(handles, g.p2p_export())
+        g.p2p_open(handles)
     hidden, nh, nkv, ffn, vocab, hd = 1024, 8, 2, 2048, 1536, 128
     nq, nk = nh * hd, nkv * hd
     layers = [make_layer(ty, hidden, nq, nk, ffn, 300 + 100 * l, True) for l in range(2)]
@@ -66,8 +70,9 @@ def _worker(rank, world, port, ty, m, out_q):
     dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("exchange", ["nccl", "p2p"])
 @pytest.mark.parametrize("ty,m", [(8, 1), (8, 3), (12, 1)])
-def test_two_gpu_decode_matches_the_unsharded_oracle(ty, m):
+def test_two_gpu_decode_matches_the_unsharded_oracle(ty, m, exchange):
     import torch
     import torch.multiprocessing as mp
 
@@ -76,7 +81,7 @@ def test_two_gpu_decode_matches_the_unsharded_oracle(ty, m):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, ty, m, q)) for r in range(2)]
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, ty, m, exchange, q)) for r in range(2)]
     for p in procs:
         p.start()
     err, same, argmax_ok = q.get(timeout=300)
