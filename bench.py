@@ -42,6 +42,10 @@ def q8_bytes(n_out, n_in):
     return n_out * (n_in // 32) * 34
 
 
+def ty_bytes(ty, n_out, n_in):
+    return q8_bytes(n_out, n_in) if ty == Q8_0 else n_out * (n_in // 256) * 144
+
+
 def layer_tensors(hidden, nq, nkv, ffn):
     return [("wq", nq, hidden), ("wk", nkv, hidden), ("wv", nkv, hidden), ("wo", hidden, nq),
             ("gate", ffn, hidden), ("up", ffn, hidden), ("down", hidden, ffn)]
@@ -132,7 +136,7 @@ def dist_setup(world):
     return dist
 
 
-def build_model(g, n_layers, write_host_layers, rank):
+def build_model(g, n_layers, write_host_layers, rank, ty=Q8_0, m=1, head=True):
     """Reserve a host mapping for the whole model, attach it, and fill the
     tensors from the on-device generator (seeds 2000 + 8*layer + k)."""
     from allpaka_b200 import gpu as G
@@ -140,15 +144,16 @@ def build_model(g, n_layers, write_host_layers, rank):
 
     nq, nkv = N_HEADS * HEAD_DIM, N_KV * HEAD_DIM
     specs = layer_tensors(HIDDEN, nq, nkv, FFN)
+    vocab = VOCAB if head else 1024
     off, offsets = 0, []
     for _ in range(n_layers):
         lo = {}
         for name, n_out, n_in in specs:
             lo[name] = off
-            off += (q8_bytes(n_out, n_in) + 255) // 256 * 256
+            off += (ty_bytes(ty, n_out, n_in) + 255) // 256 * 256
         offsets.append(lo)
     head_off = off
-    off += (q8_bytes(VOCAB, HIDDEN) + 255) // 256 * 256
+    off += (ty_bytes(ty, vocab, HIDDEN) + 255) // 256 * 256
     mm = mmap.mmap(-1, off, flags=mmap.MAP_PRIVATE | mmap.MAP_ANONYMOUS | getattr(mmap, "MAP_NORESERVE", 0))
     region = np.frombuffer(mm, dtype=np.uint8)
     assert g.attach(region)
@@ -156,25 +161,25 @@ def build_model(g, n_layers, write_host_layers, rank):
     for l in range(n_layers):
         views = {}
         for k, (name, n_out, n_in) in enumerate(specs):
-            v = region[offsets[l][name]: offsets[l][name] + q8_bytes(n_out, n_in)]
-            g.synth_matrix(v, Q8_0, n_out, n_in, 2000 + 8 * l + k, write_host=(l in write_host_layers))
+            v = region[offsets[l][name]: offsets[l][name] + ty_bytes(ty, n_out, n_in)]
+            g.synth_matrix(v, ty, n_out, n_in, 2000 + 8 * l + k, write_host=(l in write_host_layers))
             views[name] = v
         an, fn = synth.gamma(HIDDEN, 5000 + 2 * l), synth.gamma(HIDDEN, 5001 + 2 * l)
-        layers.append(G.TokenLayer(an, fn, (Q8_0, views["wq"], nq), (Q8_0, views["wk"], nkv),
-                                   (Q8_0, views["wv"], nkv), (Q8_0, views["wo"], HIDDEN),
-                                   (Q8_0, views["gate"], FFN), (Q8_0, views["up"], FFN),
-                                   (Q8_0, views["down"], HIDDEN)))
+        layers.append(G.TokenLayer(an, fn, (ty, views["wq"], nq), (ty, views["wk"], nkv),
+                                   (ty, views["wv"], nkv), (ty, views["wo"], HIDDEN),
+                                   (ty, views["gate"], FFN), (ty, views["up"], FFN),
+                                   (ty, views["down"], HIDDEN)))
         if l in write_host_layers:
             host[l] = dict(views, attn_norm=an, ffn_norm=fn)
-    head = region[head_off: head_off + q8_bytes(VOCAB, HIDDEN)]
-    g.synth_matrix(head, Q8_0, VOCAB, HIDDEN, 1999, write_host=bool(write_host_layers))
+    hd = region[head_off: head_off + ty_bytes(ty, vocab, HIDDEN)]
+    g.synth_matrix(hd, ty, vocab, HIDDEN, 1999, write_host=bool(write_host_layers))
     out_norm = synth.gamma(HIDDEN, 4999)
-    x = synth.normal_f32((1, HIDDEN), 4242)
-    pos = int(np.random.default_rng(4243).integers(0, 32768))
-    rope = rope_table(pos, HEAD_DIM, ROPE_BASE)
-    req = G.TokenReq(layers, out_norm, (Q8_0, head, VOCAB), x, 1, rope, HEAD_DIM, EPS, HIDDEN, HEAD_DIM,
+    x = synth.normal_f32((m, HIDDEN), 4242)
+    pos0 = int(np.random.default_rng(4243).integers(0, 32768 - 8))
+    rope = np.concatenate([rope_table(pos0 + i, HEAD_DIM, ROPE_BASE) for i in range(m)])
+    req = G.TokenReq(layers, out_norm, (ty, hd, vocab), x, m, rope, HEAD_DIM, EPS, HIDDEN, HEAD_DIM,
                      N_HEADS, N_KV)
-    return req, host, head, out_norm, (mm, region)
+    return req, host, hd, out_norm, (mm, region)
 
 
 def token_bytes(n_layers, world=1):
