@@ -324,7 +324,7 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
             rp.group = s.group;
             rp.stride = s.stride;
             rp.offset = s.offset;
-            const size_t total = ty == APK_TY_Q8_0 ? nr * (size_t)m->nb : nr * (size_t)(m->nb / 8) * 9;
+            const size_t total = ty == APK_TY_Q8_0 ? nr * (size_t)m->nb : nr * (size_t)(m->nb / 8);
             const int threads = 256;
             const unsigned blocks = (unsigned)((total + threads - 1) / threads);
             if (ty == APK_TY_Q8_0)
@@ -872,13 +872,15 @@ int apk_debug_q8_acts(apk_ctx *c, const float *x, uint32_t n, const float *gamma
     CUDA_TRY(cudaMemcpyAsync(host.data(), c->act_a.p, ab, cudaMemcpyDeviceToHost, c->stream));
     c->st.calls++;
     APK_TRY(finish(c));
-    const int ke = 512, kt = 16, rec = ke + ke / 4;
+    // one-row record of the Q4_K flavour: q [block][half][16], d [block][2], sum [block][2]
+    const ActLayout L = act_layout(nullptr, APK_TY_Q4_K, 1);
+    const int kt = L.kt(), mp = L.mp(), rec = L.rec_bytes();
     for (uint32_t b = 0; b < n / 32; ++b) {
         const uint8_t *r = host.data() + (size_t)(b / kt) * rec;
         const int bl = (int)(b % kt);
         memcpy(q + (size_t)b * 32, r + bl * 32, 32);
-        memcpy(&d[b], r + ke + bl * 4, 4);
-        memcpy(&sum[b], r + ke + kt * 4 + bl * 4, 4);
+        memcpy(&d[b], r + L.q_bytes() + (bl * mp) * 4, 4);
+        memcpy(&sum[b], r + L.q_bytes() + (kt * mp + bl * mp) * 4, 4);
     }
     return APK_OK;
 }

@@ -5,16 +5,22 @@
 // elements (Q8_0: 8 blocks) or 512 elements (Q4_K: 2 super-blocks).  One
 // (tile, K-step) "unit" is ONE contiguous span of at most 36 KiB that a single
 // bulk async copy (cp.async.bulk + mbarrier complete_tx) brings into shared
-// memory.  Inside a unit the 16-byte chunks are ordered [chunk][row group of
-// 32][lane], so lane l of a warp reads row (group*32 + l) with conflict-free
-// 16-byte shared loads and every activation load is a warp-wide broadcast.
-// The repack is a pure permutation of the GGUF blocks (zero rows pad the last
-// tile): the int8 / 4-bit quants and the f16 scales are untouched.
+// memory.  Inside a unit the bytes sit in the order the tensor-core fragments
+// want them, so a warp feeds `mma.sync.m16n8k32.s8` (16 rows x one 32-element
+// block x up to 8 activation rows -> int32 block dots) with conflict-free
+// 16-byte shared loads and no shuffles.  The repack is a pure permutation of
+// the GGUF blocks (zero rows pad the last tile; Q4_K's packed 6-bit scale/min
+// fields are split into bytes): quants and f16 scales are untouched.
 //
-//   Q8_0 unit with kb blocks:  quants  [b][half][rg][lane][16 B]   kb*4096 B
-//                              scales  [b][row 0..127] f16         kb*256  B
-//   Q4_K unit with ns super-blocks: [sb][chunk 0..8][rg][lane][16 B], chunk 0
-//        = {d, dmin, scales[12]}, chunks 1..8 = qs[16*(c-1) ..]   ns*18432 B
+//   Q8_0 unit with kb blocks:  quants [b][row group 0..3][16-row half][lane][16 B], i.e. the
+//                              A fragments of mma.m16n8k32 (lane = 4*g + t holds rows g, g+8
+//                              and k bytes 4t.., 16+4t..), kb*4096 B; then the f16 scales
+//                              [b][row group][g][rows g, g+8, g+16, g+24], kb*256 B
+//   Q4_K unit with ns super-blocks: per super-block and row group, the nibble bytes in the
+//        same fragment order (one 16-byte chunk per pair, 16-row half and lane: masking
+//        gives the low-nibble sub-block, shifting the high one), 4096 B, then the header
+//        with the 6-bit scales and mins already split out into bytes: {d, dmin} f16 pairs
+//        [g][4 rows], scales [g][half of the sub-blocks][4 rows][4], mins likewise, 640 B
 //
 // Work split ("stream-K"): the flat unit sequence of the whole matrix is cut
 // into equal contiguous ranges, one per CTA (one CTA per SM), so every SM
@@ -33,10 +39,12 @@ namespace apk {
 constexpr int TILE_ROWS = 128;
 constexpr int Q8_KT = 8;             // Q8_0 blocks per K-step (256 elements)
 constexpr int Q8_BLOCK_UNIT = 4352;  // 128 rows * 34 B
-constexpr int Q4_SB_UNIT = 18432;    // 128 rows * 144 B
+constexpr int Q4_SB_RG = 4736;       // one row group of a super-block: 4096 B nibbles + 640 B header
+constexpr int Q4_SB_UNIT = 4 * Q4_SB_RG;  // 128 rows: 18944 B (18432 B of GGUF blocks + split scale bytes)
 constexpr int Q4_KT_SB = 2;          // Q4_K super-blocks per K-step (512 elements)
-constexpr int STAGE_W_BYTES = 36864; // max(8*4352, 2*18432)
-constexpr int N_CONSUMER_WARPS = 8;
+constexpr int STAGE_W_BYTES = 37888; // max(8*4352, 2*18944)
+constexpr int N_CONSUMER_WARPS = 16; // 4 row groups x 4 quarters of a K-step
+constexpr int K_SPLIT = 4;
 constexpr int N_CONSUMERS = N_CONSUMER_WARPS * 32;
 constexpr int MV_THREADS = N_CONSUMERS + 32;
 constexpr int MAX_M_EFF = 16;
@@ -81,13 +89,19 @@ __host__ __device__ inline uint32_t *xch_epoch(float *base) { return xch_flags(b
 __host__ __device__ inline uint32_t *xch_done(float *base) { return xch_flags(base) + XCH_MAX_RANKS + 1; }
 __host__ __device__ inline uint32_t *xch_dead(float *base) { return xch_flags(base) + XCH_MAX_RANKS + 2; }
 
-// Prepared activations as the matvec kernel streams them: per K-step of `ke`
-// elements one record {q[m_eff][ke] i8, d[m_eff][ke/32] f32, sum[m_eff][ke/32] f32}.
+// Prepared activations as the matvec kernel consumes them: per K-step of `ke`
+// elements (kt = ke/32 blocks) one record
+//   q   [block][16-element half][row 0..m_eff-1][16 B]   int8, the B fragments of the mma
+//   d   [block][mp] f32      (mp = m_eff rounded up to even)
+//   sum [block][mp] f32
 struct ActLayout {
     uint8_t *base;
     int ke;        // elements per K-step: 256 (Q8_0 consumer) or 512 (Q4_K consumer)
     int m_eff;     // rows in the record (2 per token in two-level mode)
-    __host__ __device__ int rec_bytes() const { return m_eff * (ke + ke / 4); }
+    __host__ __device__ int kt() const { return ke >> 5; }
+    __host__ __device__ int mp() const { return (m_eff + 1) & ~1; }
+    __host__ __device__ int q_bytes() const { return ke * m_eff; }
+    __host__ __device__ int rec_bytes() const { return ke * m_eff + kt() * mp() * 8; }
     __host__ __device__ size_t total_bytes(int n_in) const {
         return (size_t)((n_in + ke - 1) / ke) * rec_bytes();
     }
@@ -234,6 +248,15 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 }
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(N_CONSUMERS) : "memory"); }
 
+// D[16 rows x 8 cols] = A[16 x 32] . B[32 x 8], int8 operands, int32 result: one
+// 32-element quantisation block of 16 weight rows against up to 8 activation rows.
+__device__ __forceinline__ void mma_block_s8(int (&d)[4], const uint4 &a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+        : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1), "r"(0));
+}
+
 __device__ __forceinline__ int dot32(const int4 &w0, const int4 &w1, const int4 &x0, const int4 &x1) {
     int s = __dp4a(w0.x, x0.x, 0);
     s = __dp4a(w0.y, x0.y, s);
@@ -287,14 +310,14 @@ __device__ __forceinline__ QBlock quantize_block(float v, bool need_sum) {
 // Store one quantised block (lane = element) into a prepared-activation buffer.
 __device__ __forceinline__ void store_act_block(const ActLayout &L, int row, int k_block, int lane,
                                                 const QBlock &qb) {
-    const int kt = L.ke >> 5;
+    const int kt = L.kt();
     const int ks = k_block / kt, bl = k_block - ks * kt;
     uint8_t *rec = L.base + (size_t)ks * L.rec_bytes();
-    rec[row * L.ke + bl * 32 + lane] = (uint8_t)(int8_t)qb.q;
+    rec[((bl * 2 + (lane >> 4)) * L.m_eff + row) * 16 + (lane & 15)] = (uint8_t)(int8_t)qb.q;
     if (lane == 0) {
-        float *d = reinterpret_cast<float *>(rec + L.m_eff * L.ke);
-        d[row * kt + bl] = qb.d;
-        d[L.m_eff * kt + row * kt + bl] = qb.sum;
+        float *d = reinterpret_cast<float *>(rec + L.q_bytes());
+        d[bl * L.mp() + row] = qb.d;
+        d[kt * L.mp() + bl * L.mp() + row] = qb.sum;
     }
 }
 
@@ -475,7 +498,19 @@ __device__ __forceinline__ int map_row(const RepackParams &p, int r) {
     return (r / p.group) * p.stride + p.offset + (r % p.group);
 }
 
-// One thread per (row, block): 34 unaligned source bytes -> two 16-byte chunks + scale.
+// Where the fragment order puts things.  A tile row r (0..127) is row group
+// rg = r/32, 16-row half h16 = (r%32)/16, fragment row g = r%8, upper = (r%16)/8
+// (rows g and g+8 of a 16-row mma tile share a lane).  Within a 32-byte block,
+// k-word w (bytes 4w..4w+3) belongs to lane column t = w%4 and k-half w/4; the
+// A-fragment register index is 2*(w/4) + upper.
+__device__ __forceinline__ void frag_pos(int r, int &rg, int &h16, int &g, int &upper) {
+    rg = r >> 5;
+    h16 = (r >> 4) & 1;
+    g = r & 7;
+    upper = (r >> 3) & 1;
+}
+
+// One thread per (row, block): 34 unaligned source bytes -> eight fragment words + scale.
 __global__ void repack_q8_0_kernel(RepackParams p) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t total = (size_t)p.src_rows * p.nb;
@@ -483,45 +518,70 @@ __global__ void repack_q8_0_kernel(RepackParams p) {
     const int r = (int)(idx / p.nb), b = (int)(idx % p.nb);
     const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)b * 34;
     const int dr = map_row(p, r);
-    const int tile = dr / TILE_ROWS, rt = dr % TILE_ROWS, rg = rt >> 5, lane = rt & 31;
+    const int tile = dr / TILE_ROWS, rt = dr % TILE_ROWS;
+    int rg, h16, g, upper;
+    frag_pos(rt, rg, h16, g, upper);
     const int ks = b / Q8_KT, bl = b % Q8_KT;
     const int kb = min(Q8_KT, p.nb - ks * Q8_KT);
     uint8_t *unit = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)ks * Q8_KT * Q8_BLOCK_UNIT;
-    uint32_t w[8];
+    uint8_t *frag = unit + (size_t)(((bl * 4 + rg) * 2 + h16) * 32) * 16;
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-        w[i] = (uint32_t)s[2 + 4 * i] | ((uint32_t)s[3 + 4 * i] << 8) | ((uint32_t)s[4 + 4 * i] << 16) |
-               ((uint32_t)s[5 + 4 * i] << 24);
-    uint4 *q0 = reinterpret_cast<uint4 *>(unit + ((bl * 2 + 0) * 4 + rg) * 512 + lane * 16);
-    uint4 *q1 = reinterpret_cast<uint4 *>(unit + ((bl * 2 + 1) * 4 + rg) * 512 + lane * 16);
-    *q0 = make_uint4(w[0], w[1], w[2], w[3]);
-    *q1 = make_uint4(w[4], w[5], w[6], w[7]);
-    uint16_t *sc = reinterpret_cast<uint16_t *>(unit + kb * 4096 + (bl * 128 + rt) * 2);
+    for (int w = 0; w < 8; ++w) {
+        const uint32_t v = (uint32_t)s[2 + 4 * w] | ((uint32_t)s[3 + 4 * w] << 8) | ((uint32_t)s[4 + 4 * w] << 16) |
+                           ((uint32_t)s[5 + 4 * w] << 24);
+        const int lane = g * 4 + (w & 3), reg = 2 * (w >> 2) + upper;
+        *reinterpret_cast<uint32_t *>(frag + lane * 16 + reg * 4) = v;
+    }
+    uint16_t *sc = reinterpret_cast<uint16_t *>(unit + kb * 4096 + ((bl * 4 + rg) * 8 + g) * 8 + (h16 * 2 + upper) * 2);
     *sc = (uint16_t)(s[0] | (s[1] << 8));
 }
 
-// One thread per (row, super-block, chunk): 16 source bytes (16-byte aligned
-// whenever the staged row is) -> one chunk.
+// One thread per (row, super-block): 144 source bytes -> nibble fragments + split header.
 __global__ void repack_q4_k_kernel(RepackParams p) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int nsb = p.nb / 8;
-    const size_t total = (size_t)p.src_rows * nsb * 9;
+    const size_t total = (size_t)p.src_rows * nsb;
     if (idx >= total) return;
-    const int c = (int)(idx % 9);
-    const size_t rb = idx / 9;
-    const int sb = (int)(rb % nsb), r = (int)(rb / nsb);
-    const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)sb * 144 + c * 16;
+    const int sb = (int)(idx % nsb), r = (int)(idx / nsb);
+    const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)sb * 144;
     const int dr = map_row(p, r);
-    const int tile = dr / TILE_ROWS, rt = dr % TILE_ROWS, rg = rt >> 5, lane = rt & 31;
+    const int tile = dr / TILE_ROWS, rt = dr % TILE_ROWS;
+    int rg, h16, g, upper;
+    frag_pos(rt, rg, h16, g, upper);
     const int ks = sb / Q4_KT_SB, sl = sb % Q4_KT_SB;
-    uint8_t *unit = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)ks * Q4_KT_SB * Q4_SB_UNIT;
-    uint32_t w[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-        w[i] = (uint32_t)s[4 * i] | ((uint32_t)s[4 * i + 1] << 8) | ((uint32_t)s[4 * i + 2] << 16) |
-               ((uint32_t)s[4 * i + 3] << 24);
-    *reinterpret_cast<uint4 *>(unit + sl * Q4_SB_UNIT + (c * 4 + rg) * 512 + lane * 16) =
-        make_uint4(w[0], w[1], w[2], w[3]);
+    uint8_t *base = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)ks * Q4_KT_SB * Q4_SB_UNIT +
+                    (size_t)sl * Q4_SB_UNIT + (size_t)rg * Q4_SB_RG;
+    // nibble bytes: pair pr holds qs[32*pr .. 32*pr+31]; word w of the pair -> lane column w%4, k-half w/4
+    const uint8_t *qs = s + 16;
+#pragma unroll 4
+    for (int pr = 0; pr < 4; ++pr) {
+        uint8_t *frag = base + (size_t)((pr * 2 + h16) * 32) * 16;
+        for (int w = 0; w < 8; ++w) {
+            const uint8_t *q = qs + pr * 32 + 4 * w;
+            const uint32_t v = (uint32_t)q[0] | ((uint32_t)q[1] << 8) | ((uint32_t)q[2] << 16) | ((uint32_t)q[3] << 24);
+            const int lane = g * 4 + (w & 3), reg = 2 * (w >> 2) + upper;
+            *reinterpret_cast<uint32_t *>(frag + lane * 16 + reg * 4) = v;
+        }
+    }
+    // header: {d, dmin} [g][4 rows] | scales [g][j half][4 rows][4] | mins likewise
+    uint8_t *hdr = base + 4096;
+    const int row4 = h16 * 2 + upper;  // which of rows g, g+8, g+16, g+24
+    *reinterpret_cast<uint32_t *>(hdr + (g * 4 + row4) * 4) =
+        (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
+    const uint8_t *pk = s + 4;
+    for (int j = 0; j < 8; ++j) {
+        // scale_min_k4 (crates/allpaka-dtype/src/lib.rs:382-390), kept as integers
+        uint8_t sc, mn;
+        if (j < 4) {
+            sc = pk[j] & 63;
+            mn = pk[j + 4] & 63;
+        } else {
+            sc = (uint8_t)((pk[j + 4] & 0xf) | ((pk[j - 4] >> 6) << 4));
+            mn = (uint8_t)((pk[j + 4] >> 4) | ((pk[j] >> 6) << 4));
+        }
+        hdr[128 + ((g * 2 + (j >> 2)) * 4 + row4) * 4 + (j & 3)] = sc;
+        hdr[384 + ((g * 2 + (j >> 2)) * 4 + row4) * 4 + (j & 3)] = mn;
+    }
 }
 
 // ------------------------------------------------- synthetic weights (bench)
@@ -598,13 +658,13 @@ __device__ __forceinline__ void scale_min_k4_dev(int j, uint32_t s0, uint32_t s1
 // Shared memory map of the matvec kernel (dynamic, 128-byte aligned base):
 //   [0, 64)      full barriers       [64, 128) empty barriers
 //   [128, 136)   flags               [136, 144) barrier of the resident-activation load
-//   [256 ..)     red[2][M][128] f32  (K-half partials; red[0] doubles as the tile result)
+//   [256 ..)     red[4][M][128] f32  (K-quarter partials; red[0] doubles as the tile result)
 //   [..]         resident activation records (PRO_LOAD / PRO_QUANT), all K-steps
 //   [..]         stages: n_stages * (STAGE_W_BYTES [+ one activation record when streaming])
 template <int M>
 struct MvSmem {
     static constexpr int RED_OFF = 256;
-    static constexpr int RED_BYTES = 2 * M * TILE_ROWS * 4;
+    static constexpr int RED_BYTES = K_SPLIT * M * TILE_ROWS * 4;
     static constexpr int RES_OFF = RED_OFF + RED_BYTES;
 };
 __host__ __device__ inline int mv_resident_bytes(int pro, int KS, int act_rec) {
@@ -614,7 +674,7 @@ __host__ __device__ inline int mv_stage_bytes(int pro, int act_rec) {
     return STAGE_W_BYTES + (pro == PRO_STREAM ? ((act_rec + 127) & ~127) : 0);
 }
 __host__ __device__ inline int mv_smem_total(int m_eff, int pro, int KS, int act_rec, int n_stages) {
-    return 256 + 2 * m_eff * TILE_ROWS * 4 + mv_resident_bytes(pro, KS, act_rec) + n_stages * mv_stage_bytes(pro, act_rec);
+    return 256 + K_SPLIT * m_eff * TILE_ROWS * 4 + mv_resident_bytes(pro, KS, act_rec) + n_stages * mv_stage_bytes(pro, act_rec);
 }
 
 // The order in which a CTA walks its range [u_begin, u_end) of the flat unit
@@ -652,21 +712,23 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
 //  * The row itself arrives by one bulk async copy issued by the producer lane
 //    right after the wait (raw f32/bf16 in the scratch buffer = last ring stage,
 //    which the producer leaves alone until pro_bar completes).
-//  * Thread t owns elements 4t..4t+3 of every 1024-element chunk j, so the 8
+//  * Thread t owns elements 4t..4t+3 of every 2048-element chunk j, so the 8
 //    lanes t&~7 .. t|7 hold one 32-element block: block maximum = 3 shuffles,
 //    then the IEEE divide / reciprocal, rounding and one packed 32-bit store,
 //    the PRO_J chunks being independent chains that overlap.
 // Arithmetic is Q8Acts::from_f32 (quantmat/q8_acts.rs:26-63) exactly; the
 // left-to-right f32 block sum (needed by Q4_K consumers only) is done one block
 // per thread over a padded copy of the row.
-constexpr int PRO_CH = 20;          // elements per thread
-constexpr int PRO_J = PRO_CH / 4;   // 1024-element chunks
+constexpr int PRO_J = 3;            // chunks of 4 * N_CONSUMERS = 2048 elements
+constexpr int PRO_CH = 4 * PRO_J;   // elements per thread
+constexpr int PRO_CHUNK = 4 * N_CONSUMERS;
+constexpr int PRO_MAX_N = PRO_J * PRO_CHUNK;  // longest row the in-CTA prologue takes (6144)
 
 __device__ __forceinline__ void prologue_gamma(const MvParams &p, int tid, float (&g)[PRO_CH]) {
     const PrepParams &pp = p.prep;
 #pragma unroll
     for (int j = 0; j < PRO_J; ++j) {
-        const int e = 4 * tid + 1024 * j;
+        const int e = 4 * tid + PRO_CHUNK * j;
         float4 w = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
         if (pp.gamma && e < pp.n) w = *reinterpret_cast<const float4 *>(pp.gamma + e);
         g[4 * j] = w.x; g[4 * j + 1] = w.y; g[4 * j + 2] = w.z; g[4 * j + 3] = w.w;
@@ -679,13 +741,16 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
     const PrepParams &pp = p.prep;
     const int warp = tid >> 5, lane = tid & 31;
     const int n = pp.n, nb = n >> 5;
-    const int ke = p.act.ke, kt_shift = ke == 256 ? 3 : 4, kt = 1 << kt_shift;
-    const int rec_bytes = M * (ke + ke / 4);
+    ActLayout L = p.act;
+    L.base = res;
+    L.m_eff = M;
+    const int ke = L.ke, kt_shift = ke == 256 ? 3 : 4, kt = 1 << kt_shift, mp = L.mp();
+    const int rec_bytes = L.rec_bytes(), q_bytes = L.q_bytes();
     double *dred = reinterpret_cast<double *>(red);
     float v[PRO_CH];
 #pragma unroll
     for (int j = 0; j < PRO_J; ++j) {
-        const int e = 4 * tid + 1024 * j;
+        const int e = 4 * tid + PRO_CHUNK * j;
         float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
         if (e < n) {
             if (pp.x_is_bf16) {
@@ -725,7 +790,7 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
         consumer_bar();  // everyone has read the raw row
 #pragma unroll
         for (int j = 0; j < PRO_J; ++j) {
-            const int e = 4 * tid + 1024 * j;
+            const int e = 4 * tid + PRO_CHUNK * j;
             if (e < n) {
                 float *h4 = hs + e + (e >> 5);
                 h4[0] = v[4 * j]; h4[1] = v[4 * j + 1]; h4[2] = v[4 * j + 2]; h4[3] = v[4 * j + 3];
@@ -737,9 +802,9 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
             float sum = 0.0f;
 #pragma unroll 8
             for (int k = 0; k < 32; ++k) sum = __fadd_rn(sum, hb[k]);  // strictly left to right
-            float *d = reinterpret_cast<float *>(res + (size_t)(b >> kt_shift) * rec_bytes + M * ke);
-            d[M * kt + (b & (kt - 1))] = sum;           // row 0 carries sum(x)
-            if (pp.two_level) d[M * kt + kt + (b & (kt - 1))] = 0.0f;  // the residual row adds nothing to the min term
+            float *d = reinterpret_cast<float *>(res + (size_t)(b >> kt_shift) * rec_bytes + q_bytes);
+            d[kt * mp + (b & (kt - 1)) * mp] = sum;           // row 0 carries sum(x)
+            if (pp.two_level) d[kt * mp + (b & (kt - 1)) * mp + 1] = 0.0f;  // the residual row adds nothing to the min term
         }
     }
     const int levels = pp.two_level ? 2 : 1;
@@ -772,18 +837,18 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
             for (int k = 0; k < PRO_CH; ++k) q[k] = q8_round(v[k], id[k >> 2]);
 #pragma unroll
             for (int j = 0; j < PRO_J; ++j) {
-                const int e = 4 * tid + 1024 * j;
+                const int e = 4 * tid + PRO_CHUNK * j;
                 const int b = e >> 5;
                 if (e < n) {
                     uint8_t *rec = res + (size_t)(b >> kt_shift) * rec_bytes;
                     const int bl = b & (kt - 1);
-                    *reinterpret_cast<uint32_t *>(rec + lv * ke + bl * 32 + (e & 31)) =
+                    *reinterpret_cast<uint32_t *>(rec + ((bl * 2 + ((e >> 4) & 1)) * M + lv) * 16 + (e & 15)) =
                         (uint32_t)(q[4 * j] & 0xff) | ((uint32_t)(q[4 * j + 1] & 0xff) << 8) |
                         ((uint32_t)(q[4 * j + 2] & 0xff) << 16) | ((uint32_t)(q[4 * j + 3] & 0xff) << 24);
                     if ((tid & 7) == 0) {
-                        float *d = reinterpret_cast<float *>(rec + M * ke);
-                        d[lv * kt + bl] = db[j];
-                        if (!pp.need_sum) d[M * kt + lv * kt + bl] = 0.0f;
+                        float *d = reinterpret_cast<float *>(rec + q_bytes);
+                        d[bl * mp + lv] = db[j];
+                        if (!pp.need_sum) d[kt * mp + bl * mp + lv] = 0.0f;
                     }
                 }
             }
@@ -904,11 +969,20 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     }
 
     // ---------------------------------------------------------- consumers
-    const int rg = warp & 3;   // row group of 32 rows inside the tile
-    const int kh = warp >> 2;  // which half of the K-step's blocks
-    float acc[M];
+    // Warp = (row group of 32 rows, quarter of the K-step).  Lane = 4*lg + lt: fragment rows
+    // lg, lg+8 of each 16-row half, activation rows (tokens) 2*lt, 2*lt+1 of each group of 8.
+    const int rg = warp & 3;
+    const int kq = warp >> 2;
+    const int lg = lane >> 2, lt = lane & 3;
+    constexpr int NG = (M + 7) / 8;   // groups of 8 activation rows
+    constexpr int MP = (M + 1) & ~1;  // row stride of the d / sum arrays
+    float acc[2][NG][4];              // [16-row half][group][rows g,g / g+8,g+8 x tokens 2t,2t+1]
 #pragma unroll
-    for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < NG; ++j)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) acc[h][j][i] = 0.0f;
     bool aborted = false;
 
     float gam[PRO_CH];
@@ -962,112 +1036,143 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             const uint8_t *sw = stages + (size_t)s * stage_bytes;
             const uint8_t *sa = streaming ? sw + STAGE_W_BYTES : res + (size_t)ks * act_rec;
             const int kb = min(kt, p.nb - ks * kt);
-            const float *ad = reinterpret_cast<const float *>(sa + M * p.act.ke);
+            const float *ad = reinterpret_cast<const float *>(sa + M * p.act.ke);  // d[block][MP], then sum[block][MP]
+            const float *as = ad + kt * MP;
+            // B fragments of activation block b, group j: token 8j+lg, k bytes 4*lt.. (b0) and 16+4*lt.. (b1)
+            auto load_b = [&](int b, int j, uint32_t &b0, uint32_t &b1) {
+                const int tok = 8 * j + lg;
+                b0 = 0u;
+                b1 = 0u;
+                if (tok < M) {
+                    b0 = *reinterpret_cast<const uint32_t *>(sa + ((b * 2 + 0) * M + tok) * 16 + 4 * lt);
+                    b1 = *reinterpret_cast<const uint32_t *>(sa + ((b * 2 + 1) * M + tok) * 16 + 4 * lt);
+                }
+            };
+            // parity instrumentation: the int32 block dots of fragment (h16, group j), global block gb
+            auto dump4 = [&](const int (&d)[4], int h16, int j, int gb) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int row = t * TILE_ROWS + rg * 32 + h16 * 16 + lg + (i >> 1) * 8;
+                    const int tok = 8 * j + 2 * lt + (i & 1);
+                    if (tok < M && row < p.n_out) p.dump[((size_t)tok * p.n_out + row) * p.nb + gb] = d[i];
+                }
+            };
             if (TY == TY_Q8_0) {
-                // lane = row: two 16-byte chunks + one f16 scale per block; activations are
-                // warp-wide broadcasts.  This warp takes blocks kh, kh+2, kh+4, kh+6.
-                const uint8_t *wq = sw + (kh * 8 + rg) * 512 + lane * 16;            // + j*8192 (+2048 second half)
-                const uint8_t *ws = sw + kb * 4096 + (kh * 128 + rg * 32 + lane) * 2;  // + j*512
-                const uint8_t *xa = sa + kh * 32;                                      // + m*ke + j*64
-                const float *xd = ad + kh;                                             // + m*8 + 2*j
-                if (kb == Q8_KT) {
-                    int4 w0[4], w1[4];
+                // this warp: blocks kq, kq+4 of the K-step
+                for (int b = kq; b < kb; b += K_SPLIT) {
+                    const uint4 a0 = *reinterpret_cast<const uint4 *>(sw + (((b * 4 + rg) * 2 + 0) * 32 + lane) * 16);
+                    const uint4 a1 = *reinterpret_cast<const uint4 *>(sw + (((b * 4 + rg) * 2 + 1) * 32 + lane) * 16);
+                    // f16 scales of rows lg, lg+8, lg+16, lg+24 of this row group
+                    const uint2 sc = *reinterpret_cast<const uint2 *>(sw + kb * 4096 + ((b * 4 + rg) * 8 + lg) * 8);
                     float dw[4];
+                    dw[0] = __half2float(__ushort_as_half((unsigned short)(sc.x & 0xffffu)));
+                    dw[1] = __half2float(__ushort_as_half((unsigned short)(sc.x >> 16)));
+                    dw[2] = __half2float(__ushort_as_half((unsigned short)(sc.y & 0xffffu)));
+                    dw[3] = __half2float(__ushort_as_half((unsigned short)(sc.y >> 16)));
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        w0[j] = *reinterpret_cast<const int4 *>(wq + j * 8192);
-                        w1[j] = *reinterpret_cast<const int4 *>(wq + j * 8192 + 2048);
-                        dw[j] = __half2float(*reinterpret_cast<const __half *>(ws + j * 512));
-                    }
-#pragma unroll
-                    for (int m = 0; m < M; ++m) {
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const int4 x0 = *reinterpret_cast<const int4 *>(xa + m * p.act.ke + j * 64);
-                            const int4 x1 = *reinterpret_cast<const int4 *>(xa + m * p.act.ke + j * 64 + 16);
-                            // two independent dp4a chains per block
-                            int d0 = __dp4a(w0[j].x, x0.x, 0), d1 = __dp4a(w1[j].x, x1.x, 0);
-                            d0 = __dp4a(w0[j].y, x0.y, d0); d1 = __dp4a(w1[j].y, x1.y, d1);
-                            d0 = __dp4a(w0[j].z, x0.z, d0); d1 = __dp4a(w1[j].z, x1.z, d1);
-                            d0 = __dp4a(w0[j].w, x0.w, d0); d1 = __dp4a(w1[j].w, x1.w, d1);
-                            const int idot = d0 + d1;
-                            acc[m] = fmaf(__fmul_rn(dw[j], xd[m * Q8_KT + 2 * j]), (float)idot, acc[m]);
-                            if (DUMP) {
-                                const int row = t * TILE_ROWS + rg * 32 + lane;
-                                if (row < p.n_out)
-                                    p.dump[((size_t)m * p.n_out + row) * p.nb + ks * Q8_KT + kh + 2 * j] = idot;
-                            }
-                        }
-                    }
-                } else {
-                    for (int b = kh; b < kb; b += 2) {
-                        const int4 w0 = *reinterpret_cast<const int4 *>(sw + ((b * 2 + 0) * 4 + rg) * 512 + lane * 16);
-                        const int4 w1 = *reinterpret_cast<const int4 *>(sw + ((b * 2 + 1) * 4 + rg) * 512 + lane * 16);
-                        const float dwb = __half2float(
-                            *reinterpret_cast<const __half *>(sw + kb * 4096 + (b * 128 + rg * 32 + lane) * 2));
-#pragma unroll
-                        for (int m = 0; m < M; ++m) {
-                            const int4 x0 = *reinterpret_cast<const int4 *>(sa + m * p.act.ke + b * 32);
-                            const int4 x1 = *reinterpret_cast<const int4 *>(sa + m * p.act.ke + b * 32 + 16);
-                            const int idot = dot32(w0, w1, x0, x1);
-                            acc[m] = fmaf(__fmul_rn(dwb, ad[m * Q8_KT + b]), (float)idot, acc[m]);
-                            if (DUMP) {
-                                const int row = t * TILE_ROWS + rg * 32 + lane;
-                                if (row < p.n_out)
-                                    p.dump[((size_t)m * p.n_out + row) * p.nb + ks * Q8_KT + b] = idot;
-                            }
+                    for (int j = 0; j < NG; ++j) {
+                        uint32_t b0, b1;
+                        load_b(b, j, b0, b1);
+                        int d0[4], d1[4];
+                        mma_block_s8(d0, a0, b0, b1);
+                        mma_block_s8(d1, a1, b0, b1);
+                        const int tok = 8 * j + 2 * lt;
+                        const float dx0 = tok < M ? ad[b * MP + tok] : 0.0f;
+                        const float dx1 = tok + 1 < M ? ad[b * MP + tok + 1] : 0.0f;
+                        // total += d_w * d_x * dot (q8_acts.rs:93), per (row, token)
+                        acc[0][j][0] = fmaf(__fmul_rn(dw[0], dx0), (float)d0[0], acc[0][j][0]);
+                        acc[0][j][1] = fmaf(__fmul_rn(dw[0], dx1), (float)d0[1], acc[0][j][1]);
+                        acc[0][j][2] = fmaf(__fmul_rn(dw[1], dx0), (float)d0[2], acc[0][j][2]);
+                        acc[0][j][3] = fmaf(__fmul_rn(dw[1], dx1), (float)d0[3], acc[0][j][3]);
+                        acc[1][j][0] = fmaf(__fmul_rn(dw[2], dx0), (float)d1[0], acc[1][j][0]);
+                        acc[1][j][1] = fmaf(__fmul_rn(dw[2], dx1), (float)d1[1], acc[1][j][1]);
+                        acc[1][j][2] = fmaf(__fmul_rn(dw[3], dx0), (float)d1[2], acc[1][j][2]);
+                        acc[1][j][3] = fmaf(__fmul_rn(dw[3], dx1), (float)d1[3], acc[1][j][3]);
+                        if (DUMP) {
+                            dump4(d0, 0, j, ks * Q8_KT + b);
+                            dump4(d1, 1, j, ks * Q8_KT + b);
                         }
                     }
                 }
             } else {
-                const float *as = ad + M * (Q4_KT_SB * 8);
-                const int nsb = kb / 8;
-                for (int sb = kh; sb < nsb; sb += 2) {
-                    const uint8_t *base = sw + sb * Q4_SB_UNIT;
-                    const uint4 hdr = *reinterpret_cast<const uint4 *>(base + rg * 512 + lane * 16);
-                    const float d = __half2float(__ushort_as_half((unsigned short)(hdr.x & 0xffffu)));
-                    const float dmin = __half2float(__ushort_as_half((unsigned short)(hdr.x >> 16)));
+                // this warp: super-block kq/2 of the K-step, sub-blocks 4*(kq&1) .. +3 (pairs 2*(kq&1), +1)
+                const int sb = kq >> 1, jh = kq & 1;
+                if (sb * 8 < kb) {
+                    const uint8_t *base = sw + sb * Q4_SB_UNIT + rg * Q4_SB_RG;
+                    const uint8_t *hdr = base + 4096;
+                    const uint4 dd = *reinterpret_cast<const uint4 *>(hdr + lg * 16);                   // {d, dmin} of 4 rows
+                    const uint4 scw = *reinterpret_cast<const uint4 *>(hdr + 128 + (lg * 2 + jh) * 16);  // 4 scales x 4 rows
+                    const uint4 mnw = *reinterpret_cast<const uint4 *>(hdr + 384 + (lg * 2 + jh) * 16);  // 4 mins x 4 rows
+                    const uint32_t ddw[4] = {dd.x, dd.y, dd.z, dd.w};
+                    const uint32_t scr[4] = {scw.x, scw.y, scw.z, scw.w};
+                    const uint32_t mnr[4] = {mnw.x, mnw.y, mnw.z, mnw.w};
+                    float U[2][NG][4], V[2][NG][4];  // sum_j sc_j * (dot_j * dx_j), sum_j mn_j * sum_j
 #pragma unroll
-                    for (int pr = 0; pr < 4; ++pr) {
-                        const uint4 q0 =
-                            *reinterpret_cast<const uint4 *>(base + ((1 + 2 * pr) * 4 + rg) * 512 + lane * 16);
-                        const uint4 q1 =
-                            *reinterpret_cast<const uint4 *>(base + ((2 + 2 * pr) * 4 + rg) * 512 + lane * 16);
-                        int4 lo0, lo1, hi0, hi1;
-                        lo0.x = q0.x & 0x0f0f0f0f; lo0.y = q0.y & 0x0f0f0f0f; lo0.z = q0.z & 0x0f0f0f0f; lo0.w = q0.w & 0x0f0f0f0f;
-                        lo1.x = q1.x & 0x0f0f0f0f; lo1.y = q1.y & 0x0f0f0f0f; lo1.z = q1.z & 0x0f0f0f0f; lo1.w = q1.w & 0x0f0f0f0f;
-                        hi0.x = (q0.x >> 4) & 0x0f0f0f0f; hi0.y = (q0.y >> 4) & 0x0f0f0f0f; hi0.z = (q0.z >> 4) & 0x0f0f0f0f; hi0.w = (q0.w >> 4) & 0x0f0f0f0f;
-                        hi1.x = (q1.x >> 4) & 0x0f0f0f0f; hi1.y = (q1.y >> 4) & 0x0f0f0f0f; hi1.z = (q1.z >> 4) & 0x0f0f0f0f; hi1.w = (q1.w >> 4) & 0x0f0f0f0f;
-                        float sc1, mn1, sc2, mn2;
-                        scale_min_k4_dev(2 * pr, hdr.y, hdr.z, hdr.w, sc1, mn1);
-                        scale_min_k4_dev(2 * pr + 1, hdr.y, hdr.z, hdr.w, sc2, mn2);
-                        const float dsc1 = __fmul_rn(d, sc1), dm1 = __fmul_rn(dmin, mn1);
-                        const float dsc2 = __fmul_rn(d, sc2), dm2 = __fmul_rn(dmin, mn2);
-                        const int b_lo = sb * 8 + 2 * pr, b_hi = b_lo + 1;
+                    for (int h = 0; h < 2; ++h)
 #pragma unroll
-                        for (int m = 0; m < M; ++m) {
-                            const int8_t *xq = reinterpret_cast<const int8_t *>(sa) + m * p.act.ke;
-                            const int4 xl0 = *reinterpret_cast<const int4 *>(xq + b_lo * 32);
-                            const int4 xl1 = *reinterpret_cast<const int4 *>(xq + b_lo * 32 + 16);
-                            const int4 xh0 = *reinterpret_cast<const int4 *>(xq + b_hi * 32);
-                            const int4 xh1 = *reinterpret_cast<const int4 *>(xq + b_hi * 32 + 16);
-                            const int il = dot32(lo0, lo1, xl0, xl1);
-                            const int ih = dot32(hi0, hi1, xh0, xh1);
-                            const float dot_lo = __fmul_rn((float)il, ad[m * 16 + b_lo]);
-                            const float dot_hi = __fmul_rn((float)ih, ad[m * 16 + b_hi]);
-                            // total += d*sc*dot - dmin*mn*sum  (q8_acts.rs:296-297)
-                            acc[m] += __fsub_rn(__fmul_rn(dsc1, dot_lo), __fmul_rn(dm1, as[m * 16 + b_lo]));
-                            acc[m] += __fsub_rn(__fmul_rn(dsc2, dot_hi), __fmul_rn(dm2, as[m * 16 + b_hi]));
-                            if (DUMP) {
-                                const int row = t * TILE_ROWS + rg * 32 + lane;
-                                if (row < p.n_out) {
-                                    int32_t *o = p.dump + ((size_t)m * p.n_out + row) * p.nb + ks * 16;
-                                    o[b_lo] = il;
-                                    o[b_hi] = ih;
+                        for (int j = 0; j < NG; ++j)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) U[h][j][i] = V[h][j][i] = 0.0f;
+#pragma unroll
+                    for (int pi = 0; pi < 2; ++pi) {
+                        const int pr = 2 * jh + pi;
+                        uint4 lo[2], hi[2];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            const uint4 q = *reinterpret_cast<const uint4 *>(base + ((pr * 2 + h) * 32 + lane) * 16);
+                            lo[h] = make_uint4(q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu);
+                            hi[h] = make_uint4((q.x >> 4) & 0x0f0f0f0fu, (q.y >> 4) & 0x0f0f0f0fu, (q.z >> 4) & 0x0f0f0f0fu,
+                                               (q.w >> 4) & 0x0f0f0f0fu);
+                        }
+#pragma unroll
+                        for (int nib = 0; nib < 2; ++nib) {
+                            const int jj = 2 * pi + nib;         // sub-block within this warp's four
+                            const int b = sb * 8 + 2 * pr + nib;  // activation block within the K-step
+                            float scf[4], mnf[4];
+#pragma unroll
+                            for (int r4 = 0; r4 < 4; ++r4) {
+                                scf[r4] = (float)((scr[r4] >> (8 * jj)) & 0xffu);
+                                mnf[r4] = (float)((mnr[r4] >> (8 * jj)) & 0xffu);
+                            }
+#pragma unroll
+                            for (int j = 0; j < NG; ++j) {
+                                uint32_t b0, b1;
+                                load_b(b, j, b0, b1);
+                                int d0[4], d1[4];
+                                mma_block_s8(d0, nib ? hi[0] : lo[0], b0, b1);
+                                mma_block_s8(d1, nib ? hi[1] : lo[1], b0, b1);
+                                const int tok = 8 * j + 2 * lt;
+                                const float dx0 = tok < M ? ad[b * MP + tok] : 0.0f;
+                                const float dx1 = tok + 1 < M ? ad[b * MP + tok + 1] : 0.0f;
+                                const float sx0 = tok < M ? as[b * MP + tok] : 0.0f;
+                                const float sx1 = tok + 1 < M ? as[b * MP + tok + 1] : 0.0f;
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const float dx = (i & 1) ? dx1 : dx0, sx = (i & 1) ? sx1 : sx0;
+                                    U[0][j][i] = fmaf(scf[i >> 1], __fmul_rn((float)d0[i], dx), U[0][j][i]);
+                                    U[1][j][i] = fmaf(scf[2 + (i >> 1)], __fmul_rn((float)d1[i], dx), U[1][j][i]);
+                                    V[0][j][i] = fmaf(mnf[i >> 1], sx, V[0][j][i]);
+                                    V[1][j][i] = fmaf(mnf[2 + (i >> 1)], sx, V[1][j][i]);
+                                }
+                                if (DUMP) {
+                                    dump4(d0, 0, j, ks * 16 + b);
+                                    dump4(d1, 1, j, ks * 16 + b);
                                 }
                             }
                         }
                     }
+                    // total += d * sum(sc*dot*dx) - dmin * sum(mn*sum)  (q8_acts.rs:296-297, regrouped per super-block)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h)
+#pragma unroll
+                        for (int j = 0; j < NG; ++j)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const uint32_t w = ddw[2 * h + (i >> 1)];
+                                const float d = __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
+                                const float dmin = __half2float(__ushort_as_half((unsigned short)(w >> 16)));
+                                acc[h][j][i] += __fsub_rn(__fmul_rn(d, U[h][j][i]), __fmul_rn(dmin, V[h][j][i]));
+                            }
                 }
             }
             __syncwarp();
@@ -1085,12 +1190,18 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         }
         if (!tile_done) continue;
 #pragma unroll
-        for (int m = 0; m < M; ++m) {
-            red[(kh * M + m) * TILE_ROWS + rg * 32 + lane] = acc[m];
-            acc[m] = 0.0f;
-        }
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int j = 0; j < NG; ++j)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int tok = 8 * j + 2 * lt + (i & 1);
+                    if (tok < M) red[(kq * M + tok) * TILE_ROWS + rg * 32 + h * 16 + lg + (i >> 1) * 8] = acc[h][j][i];
+                    acc[h][j][i] = 0.0f;
+                }
         consumer_bar();
-        for (int i = tid; i < M * TILE_ROWS; i += N_CONSUMERS) red[i] += red[M * TILE_ROWS + i];
+        for (int i = tid; i < M * TILE_ROWS; i += N_CONSUMERS)
+            red[i] = (red[i] + red[M * TILE_ROWS + i]) + (red[2 * M * TILE_ROWS + i] + red[3 * M * TILE_ROWS + i]);
         const long long ua = (long long)t_cur * p.KS, ub = ua + p.KS - 1;
         const int c_first = (int)(((ua + 1) * G - 1) / U), c_last = (int)(((ub + 1) * G - 1) / U);
         if (c_first != c_last) {
