@@ -516,9 +516,9 @@ int launch_prep(apk_ctx *c, const void *x, int x_is_bf16, int ldx, const float *
 }
 
 // Stages that fit next to the resident activations (0 = does not fit at all).
-int pick_stages(apk_ctx *c, int m_eff, int pro, int KS, int act_rec) {
+int pick_stages(apk_ctx *c, int ty, int m_eff, int pro, int KS, int act_rec) {
     int ns = 6;
-    while (ns > 0 && mv_smem_total(m_eff, pro, KS, act_rec, ns) > c->smem_optin) --ns;
+    while (ns > 0 && mv_smem_total(ty, m_eff, pro, KS, act_rec, ns) > c->smem_optin) --ns;
     return ns;
 }
 
@@ -542,10 +542,10 @@ int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool
     p.err = c->d_err;
     p.pdl = c->use_pdl ? 1 : 0;
     const int act_rec = p.act.rec_bytes();
-    const int ns = pick_stages(c, mode.m_eff, p.pro, W->KS, act_rec);
+    const int ns = pick_stages(c, (int)W->ty, mode.m_eff, p.pro, W->KS, act_rec);
     if (ns < 2) return fail(APK_DECLINE_MISSING_CAPABILITY, "activations of %d rows x %u do not fit in shared memory", mode.m_eff, W->n_in);
     p.n_stages = ns;
-    const int smem = mv_smem_total(mode.m_eff, p.pro, W->KS, act_rec, ns);
+    const int smem = mv_smem_total((int)W->ty, mode.m_eff, p.pro, W->KS, act_rec, ns);
     const long long U = (long long)W->n_tiles * W->KS;
     const int grid = (int)std::min<long long>(c->n_sm, U);
     CUDA_TRY(launch_ex(c, k, dim3(grid), dim3(MV_THREADS), (size_t)smem, c->use_pdl, (const MvParams)p));
@@ -556,7 +556,7 @@ int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool
 // Can the whole activation buffer of this matvec live in shared memory with a ring of >= 4 stages?
 bool want_resident(apk_ctx *c, const DevMatrix *W, int m_eff) {
     ActLayout L = act_layout(nullptr, W->ty, m_eff);
-    return pick_stages(c, m_eff, PRO_LOAD, W->KS, L.rec_bytes()) >= 4;
+    return pick_stages(c, (int)W->ty, m_eff, PRO_LOAD, W->KS, L.rec_bytes()) >= 4;
 }
 
 // Activation source for a matvec on x (device, f32 or bf16): at one token the

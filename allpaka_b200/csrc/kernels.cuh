@@ -42,7 +42,7 @@ constexpr int Q8_BLOCK_UNIT = 4352;  // 128 rows * 34 B
 constexpr int Q4_SB_RG = 4736;       // one row group of a super-block: 4096 B nibbles + 640 B header
 constexpr int Q4_SB_UNIT = 4 * Q4_SB_RG;  // 128 rows: 18944 B (18432 B of GGUF blocks + split scale bytes)
 constexpr int Q4_KT_SB = 2;          // Q4_K super-blocks per K-step (512 elements)
-constexpr int STAGE_W_BYTES = 37888; // max(8*4352, 2*18944)
+__host__ __device__ constexpr int stage_w_bytes(int ty) { return ty == 8 ? 8 * 4352 : 2 * 18944; }  // one full K-step of weights
 constexpr int N_CONSUMER_WARPS = 16; // 4 row groups x 4 quarters of a K-step
 constexpr int K_SPLIT = 4;
 constexpr int N_CONSUMERS = N_CONSUMER_WARPS * 32;
@@ -660,7 +660,7 @@ __device__ __forceinline__ void scale_min_k4_dev(int j, uint32_t s0, uint32_t s1
 //   [128, 136)   flags               [136, 144) barrier of the resident-activation load
 //   [256 ..)     red[4][M][128] f32  (K-quarter partials; red[0] doubles as the tile result)
 //   [..]         resident activation records (PRO_LOAD / PRO_QUANT), all K-steps
-//   [..]         stages: n_stages * (STAGE_W_BYTES [+ one activation record when streaming])
+//   [..]         stages: n_stages * (one K-step of weights [+ one activation record when streaming])
 template <int M>
 struct MvSmem {
     static constexpr int RED_OFF = 256;
@@ -670,11 +670,11 @@ struct MvSmem {
 __host__ __device__ inline int mv_resident_bytes(int pro, int KS, int act_rec) {
     return pro == PRO_STREAM ? 0 : ((KS * act_rec + 127) & ~127);
 }
-__host__ __device__ inline int mv_stage_bytes(int pro, int act_rec) {
-    return STAGE_W_BYTES + (pro == PRO_STREAM ? ((act_rec + 127) & ~127) : 0);
+__host__ __device__ inline int mv_stage_bytes(int ty, int pro, int act_rec) {
+    return stage_w_bytes(ty) + (pro == PRO_STREAM ? ((act_rec + 127) & ~127) : 0);
 }
-__host__ __device__ inline int mv_smem_total(int m_eff, int pro, int KS, int act_rec, int n_stages) {
-    return 256 + K_SPLIT * m_eff * TILE_ROWS * 4 + mv_resident_bytes(pro, KS, act_rec) + n_stages * mv_stage_bytes(pro, act_rec);
+__host__ __device__ inline int mv_smem_total(int ty, int m_eff, int pro, int KS, int act_rec, int n_stages) {
+    return 256 + K_SPLIT * m_eff * TILE_ROWS * 4 + mv_resident_bytes(pro, KS, act_rec) + n_stages * mv_stage_bytes(ty, pro, act_rec);
 }
 
 // The order in which a CTA walks its range [u_begin, u_end) of the flat unit
@@ -874,7 +874,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     const int act_rec = p.act.rec_bytes();
     const bool streaming = p.pro == PRO_STREAM;
     uint8_t *res = smem + MvSmem<M>::RES_OFF;
-    const int stage_bytes = mv_stage_bytes(p.pro, act_rec);
+    const int stage_bytes = mv_stage_bytes(TY, p.pro, act_rec);
     uint8_t *stages = res + mv_resident_bytes(p.pro, p.KS, act_rec);
     const int NS = p.n_stages;
 
@@ -924,7 +924,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             auto issue_acts = [&](int it) {
                 const int s = it % NS;
                 const int ks = (int)(order.at(it) % p.KS);
-                bulk_g2s(stages + (size_t)s * stage_bytes + STAGE_W_BYTES, p.act.base + (size_t)ks * act_rec,
+                bulk_g2s(stages + (size_t)s * stage_bytes + stage_w_bytes(TY), p.act.base + (size_t)ks * act_rec,
                          (uint32_t)act_rec, &full[s], pol_a);
             };
             // Weights depend on nothing: fill the ring before waiting for the previous kernel.
@@ -1034,7 +1034,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         }
         if (!aborted) {
             const uint8_t *sw = stages + (size_t)s * stage_bytes;
-            const uint8_t *sa = streaming ? sw + STAGE_W_BYTES : res + (size_t)ks * act_rec;
+            const uint8_t *sa = streaming ? sw + stage_w_bytes(TY) : res + (size_t)ks * act_rec;
             const int kb = min(kt, p.nb - ks * kt);
             const float *ad = reinterpret_cast<const float *>(sa + M * p.act.ke);  // d[block][MP], then sum[block][MP]
             const float *as = ad + kt * MP;
@@ -1058,41 +1058,54 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 }
             };
             if (TY == TY_Q8_0) {
-                // this warp: blocks kq, kq+4 of the K-step
-                for (int b = kq; b < kb; b += K_SPLIT) {
-                    const uint4 a0 = *reinterpret_cast<const uint4 *>(sw + (((b * 4 + rg) * 2 + 0) * 32 + lane) * 16);
-                    const uint4 a1 = *reinterpret_cast<const uint4 *>(sw + (((b * 4 + rg) * 2 + 1) * 32 + lane) * 16);
-                    // f16 scales of rows lg, lg+8, lg+16, lg+24 of this row group
-                    const uint2 sc = *reinterpret_cast<const uint2 *>(sw + kb * 4096 + ((b * 4 + rg) * 8 + lg) * 8);
-                    float dw[4];
-                    dw[0] = __half2float(__ushort_as_half((unsigned short)(sc.x & 0xffffu)));
-                    dw[1] = __half2float(__ushort_as_half((unsigned short)(sc.x >> 16)));
-                    dw[2] = __half2float(__ushort_as_half((unsigned short)(sc.y & 0xffffu)));
-                    dw[3] = __half2float(__ushort_as_half((unsigned short)(sc.y >> 16)));
+                // this warp: blocks kq, kq+4 of the K-step.  Activation rows past M are clamped to
+                // row M-1: their results are computed but never stored, which keeps predicates
+                // out of the loop.
+                const uint8_t *wa = sw + rg * 1024 + lane * 16;           // + b*4096 (+512 for the upper 16 rows)
+                const uint8_t *ws = sw + kb * 4096 + (rg * 8 + lg) * 8;   // + b*256
+                auto block = [&](int b) {
+                    const uint4 a0 = *reinterpret_cast<const uint4 *>(wa + b * 4096);
+                    const uint4 a1 = *reinterpret_cast<const uint4 *>(wa + b * 4096 + 512);
+                    const uint2 sc = *reinterpret_cast<const uint2 *>(ws + b * 256);
+                    const __half2 s01 = *reinterpret_cast<const __half2 *>(&sc.x);
+                    const __half2 s23 = *reinterpret_cast<const __half2 *>(&sc.y);
+                    const float2 f01 = __half22float2(s01), f23 = __half22float2(s23);
+                    const uint8_t *xb = sa + b * (32 * M);
+                    const float *xd = ad + b * MP;
 #pragma unroll
                     for (int j = 0; j < NG; ++j) {
-                        uint32_t b0, b1;
-                        load_b(b, j, b0, b1);
+                        const int tb = min(8 * j + lg, M - 1);      // B-fragment row
+                        const int t0 = min(8 * j + 2 * lt, M - 1);  // result columns
+                        const int t1 = min(8 * j + 2 * lt + 1, M - 1);
+                        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xb + tb * 16 + 4 * lt);
+                        const uint32_t b1 = *reinterpret_cast<const uint32_t *>(xb + 16 * M + tb * 16 + 4 * lt);
                         int d0[4], d1[4];
                         mma_block_s8(d0, a0, b0, b1);
                         mma_block_s8(d1, a1, b0, b1);
-                        const int tok = 8 * j + 2 * lt;
-                        const float dx0 = tok < M ? ad[b * MP + tok] : 0.0f;
-                        const float dx1 = tok + 1 < M ? ad[b * MP + tok + 1] : 0.0f;
+                        const float dx0 = xd[t0];
                         // total += d_w * d_x * dot (q8_acts.rs:93), per (row, token)
-                        acc[0][j][0] = fmaf(__fmul_rn(dw[0], dx0), (float)d0[0], acc[0][j][0]);
-                        acc[0][j][1] = fmaf(__fmul_rn(dw[0], dx1), (float)d0[1], acc[0][j][1]);
-                        acc[0][j][2] = fmaf(__fmul_rn(dw[1], dx0), (float)d0[2], acc[0][j][2]);
-                        acc[0][j][3] = fmaf(__fmul_rn(dw[1], dx1), (float)d0[3], acc[0][j][3]);
-                        acc[1][j][0] = fmaf(__fmul_rn(dw[2], dx0), (float)d1[0], acc[1][j][0]);
-                        acc[1][j][1] = fmaf(__fmul_rn(dw[2], dx1), (float)d1[1], acc[1][j][1]);
-                        acc[1][j][2] = fmaf(__fmul_rn(dw[3], dx0), (float)d1[2], acc[1][j][2]);
-                        acc[1][j][3] = fmaf(__fmul_rn(dw[3], dx1), (float)d1[3], acc[1][j][3]);
+                        acc[0][j][0] = fmaf(__fmul_rn(f01.x, dx0), (float)d0[0], acc[0][j][0]);
+                        acc[0][j][2] = fmaf(__fmul_rn(f01.y, dx0), (float)d0[2], acc[0][j][2]);
+                        acc[1][j][0] = fmaf(__fmul_rn(f23.x, dx0), (float)d1[0], acc[1][j][0]);
+                        acc[1][j][2] = fmaf(__fmul_rn(f23.y, dx0), (float)d1[2], acc[1][j][2]);
+                        if (M > 1) {  // a single activation row never has an odd column
+                            const float dx1 = xd[t1];
+                            acc[0][j][1] = fmaf(__fmul_rn(f01.x, dx1), (float)d0[1], acc[0][j][1]);
+                            acc[0][j][3] = fmaf(__fmul_rn(f01.y, dx1), (float)d0[3], acc[0][j][3]);
+                            acc[1][j][1] = fmaf(__fmul_rn(f23.x, dx1), (float)d1[1], acc[1][j][1]);
+                            acc[1][j][3] = fmaf(__fmul_rn(f23.y, dx1), (float)d1[3], acc[1][j][3]);
+                        }
                         if (DUMP) {
                             dump4(d0, 0, j, ks * Q8_KT + b);
                             dump4(d1, 1, j, ks * Q8_KT + b);
                         }
                     }
+                };
+                if (kb == Q8_KT) {
+                    block(kq);
+                    block(kq + K_SPLIT);
+                } else {
+                    for (int b = kq; b < kb; b += K_SPLIT) block(b);
                 }
             } else {
                 // this warp: super-block kq/2 of the K-step, sub-blocks 4*(kq&1) .. +3 (pairs 2*(kq&1), +1)

@@ -118,10 +118,10 @@ extern "C" int apk_matvec_noalloc(apk_ctx *c, const void *w, uint32_t ty, uint32
     p.y = y_dev;
     p.ldy = (int)n_out;
     const int act_rec = p.act.rec_bytes();
-    const int ns = pick_stages(c, mode.m_eff, p.pro, W->KS, act_rec);
+    const int ns = pick_stages(c, (int)W->ty, mode.m_eff, p.pro, W->KS, act_rec);
     if (ns < 2) return fail(APK_DECLINE_MISSING_CAPABILITY, "activations do not fit in shared memory");
     p.n_stages = ns;
-    const int smem = mv_smem_total(mode.m_eff, p.pro, W->KS, act_rec, ns);
+    const int smem = mv_smem_total((int)W->ty, mode.m_eff, p.pro, W->KS, act_rec, ns);
     const long long U = (long long)W->n_tiles * W->KS;
     const int grid = (int)std::min<long long>(c->n_sm, U);
     k<<<grid, MV_THREADS, smem, st>>>(p);
