@@ -1038,16 +1038,6 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             const int kb = min(kt, p.nb - ks * kt);
             const float *ad = reinterpret_cast<const float *>(sa + M * p.act.ke);  // d[block][MP], then sum[block][MP]
             const float *as = ad + kt * MP;
-            // B fragments of activation block b, group j: token 8j+lg, k bytes 4*lt.. (b0) and 16+4*lt.. (b1)
-            auto load_b = [&](int b, int j, uint32_t &b0, uint32_t &b1) {
-                const int tok = 8 * j + lg;
-                b0 = 0u;
-                b1 = 0u;
-                if (tok < M) {
-                    b0 = *reinterpret_cast<const uint32_t *>(sa + ((b * 2 + 0) * M + tok) * 16 + 4 * lt);
-                    b1 = *reinterpret_cast<const uint32_t *>(sa + ((b * 2 + 1) * M + tok) * 16 + 4 * lt);
-                }
-            };
             // parity instrumentation: the int32 block dots of fragment (h16, group j), global block gb
             auto dump4 = [&](const int (&d)[4], int h16, int j, int gb) {
 #pragma unroll
@@ -1147,20 +1137,22 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                                 scf[r4] = (float)((scr[r4] >> (8 * jj)) & 0xffu);
                                 mnf[r4] = (float)((mnr[r4] >> (8 * jj)) & 0xffu);
                             }
+                            const uint8_t *xb = sa + b * (32 * M);
 #pragma unroll
                             for (int j = 0; j < NG; ++j) {
-                                uint32_t b0, b1;
-                                load_b(b, j, b0, b1);
+                                // rows past M are clamped to row M-1: computed, never stored
+                                const int tb = min(8 * j + lg, M - 1);
+                                const int t0 = min(8 * j + 2 * lt, M - 1), t1 = min(8 * j + 2 * lt + 1, M - 1);
+                                const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xb + tb * 16 + 4 * lt);
+                                const uint32_t b1 = *reinterpret_cast<const uint32_t *>(xb + 16 * M + tb * 16 + 4 * lt);
                                 int d0[4], d1[4];
                                 mma_block_s8(d0, nib ? hi[0] : lo[0], b0, b1);
                                 mma_block_s8(d1, nib ? hi[1] : lo[1], b0, b1);
-                                const int tok = 8 * j + 2 * lt;
-                                const float dx0 = tok < M ? ad[b * MP + tok] : 0.0f;
-                                const float dx1 = tok + 1 < M ? ad[b * MP + tok + 1] : 0.0f;
-                                const float sx0 = tok < M ? as[b * MP + tok] : 0.0f;
-                                const float sx1 = tok + 1 < M ? as[b * MP + tok + 1] : 0.0f;
+                                const float dx0 = ad[b * MP + t0], dx1 = ad[b * MP + t1];
+                                const float sx0 = as[b * MP + t0], sx1 = as[b * MP + t1];
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
+                                    if (M == 1 && (i & 1)) continue;  // a single activation row has no odd column
                                     const float dx = (i & 1) ? dx1 : dx0, sx = (i & 1) ? sx1 : sx0;
                                     U[0][j][i] = fmaf(scf[i >> 1], __fmul_rn((float)d0[i], dx), U[0][j][i]);
                                     U[1][j][i] = fmaf(scf[2 + (i >> 1)], __fmul_rn((float)d1[i], dx), U[1][j][i]);
