@@ -1331,9 +1331,23 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
                 }
                 const int row = row0 + c;
                 if (row < p.n_out) p.y[(size_t)m * p.ldy + row] = o;
-                // identity attention core: the roped Q head is what the output projection consumes
-                if (p.q_next.base && tile < p.n_q_tiles)
-                    quantize_store(p.q_next, p.q_next_two_level, p.q_next_need_sum, m, tile * 4 + j, lane, o);
+                v[j] = o;
+            }
+            if (p.q_next.base && tile < p.n_q_tiles) {
+                // keep the roped head in shared memory for the packing pass below
+                __syncwarp();
+#pragma unroll
+                for (int j = 0; j < 4; ++j) hs[lane + 32 * j] = v[j];
+            }
+        }
+        // identity attention core: the roped Q head is what the output projection consumes.
+        // One warp per (token, 32-element block): the four blocks of a head go in parallel.
+        if (p.q_next.base && tile < p.n_q_tiles) {
+            consumer_bar();
+            for (int w = warp; w < MO * 4; w += N_CONSUMER_WARPS) {
+                const int m = w >> 2, j = w & 3;
+                const float *hs = out + (p.two_level ? 2 * m : m) * TILE_ROWS;
+                quantize_store(p.q_next, p.q_next_two_level, p.q_next_need_sum, m, tile * 4 + j, lane, hs[lane + 32 * j]);
             }
         }
         return;
