@@ -548,6 +548,7 @@ int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool
     const int smem = mv_smem_total((int)W->ty, mode.m_eff, p.pro, W->KS, act_rec, ns);
     const long long U = (long long)W->n_tiles * W->KS;
     const int grid = (int)std::min<long long>(c->n_sm, U);
+    if ((U + 1) * grid >= (1LL << 31)) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "matrix too large for 32-bit unit arithmetic");
     CUDA_TRY(launch_ex(c, k, dim3(grid), dim3(MV_THREADS), (size_t)smem, c->use_pdl, (const MvParams)p));
     c->st.launches++;
     return APK_OK;

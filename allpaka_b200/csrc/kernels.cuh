@@ -682,18 +682,19 @@ __host__ __device__ inline int mv_smem_total(int ty, int m_eff, int pro, int KS,
 // head piece), whole tiles after.  A shared tile's cross-CTA hand-off (publish,
 // count, last arriver sums) then overlaps the streaming of the whole tiles
 // instead of sitting at the very end of the kernel.
+// (All unit arithmetic is 32-bit: the host checks tiles * K-steps * grid < 2^31.)
 struct UnitOrder {
-    long long u_begin, u_end;
+    uint32_t u_begin, u_end;
     int n_total, len_tail, len_head;
-    __device__ UnitOrder(long long ub, long long ue, int KS) : u_begin(ub), u_end(ue) {
+    __device__ UnitOrder(uint32_t ub, uint32_t ue, uint32_t KS) : u_begin(ub), u_end(ue) {
         n_total = (int)(ue - ub);
-        const long long t_first = ub / KS, t_last = (ue - 1) / KS;
-        const long long h_end = (t_first + 1) * (long long)KS < ue ? (t_first + 1) * (long long)KS : ue;
+        const uint32_t t_first = ub / KS, t_last = (ue - 1) / KS;
+        const uint32_t h_end = (t_first + 1) * KS < ue ? (t_first + 1) * KS : ue;
         const bool head_partial = (ub % KS) != 0 || (h_end - ub) < KS;
         len_head = head_partial ? (int)(h_end - ub) : 0;
-        len_tail = (t_last > t_first && (ue % KS) != 0) ? (int)(ue - t_last * (long long)KS) : 0;
+        len_tail = (t_last > t_first && (ue % KS) != 0) ? (int)(ue - t_last * KS) : 0;
     }
-    __device__ __forceinline__ long long at(int it) const {
+    __device__ __forceinline__ uint32_t at(int it) const {
         if (it < len_tail) return u_end - len_tail + it;
         if (it < len_tail + len_head) return u_begin + (it - len_tail);
         return u_begin + it - len_tail;  // = u_begin + len_head + (it - len_tail - len_head)
@@ -894,9 +895,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     if (p.pdl) pdl_launch_dependents();
 
     // this CTA's contiguous range of the flat unit sequence
-    const long long U = (long long)p.n_tiles * p.KS;
-    const long long G = gridDim.x;
-    const UnitOrder order((long long)blockIdx.x * U / G, (long long)(blockIdx.x + 1) * U / G, p.KS);
+    const uint32_t U = (uint32_t)p.n_tiles * (uint32_t)p.KS;
+    const uint32_t G = gridDim.x;
+    const UnitOrder order(blockIdx.x * U / G, (blockIdx.x + 1) * U / G, (uint32_t)p.KS);
     const int n_total = order.n_total;
     const int kt = (TY == TY_Q8_0) ? Q8_KT : Q4_KT_SB * 8;  // 32-element blocks per full K-step
 
@@ -906,7 +907,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             const uint64_t pol_w = l2_policy_evict_first();
             const uint64_t pol_a = l2_policy_evict_last();
             auto issue_weights = [&](int it) {
-                const long long u = order.at(it);
+                const uint32_t u = order.at(it);
                 const int s = it % NS;
                 const int t = (int)(u / p.KS), ks = (int)(u % p.KS);
                 const int kb = min(kt, p.nb - ks * kt);
@@ -1008,7 +1009,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     // (after the tail piece) and otherwise advances by one unit.
     int t, ks;
     {
-        const long long u0 = order.at(0);
+        const uint32_t u0 = order.at(0);
         t = (int)(u0 / p.KS);
         ks = (int)(u0 % p.KS);
     }
@@ -1207,7 +1208,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         consumer_bar();
         for (int i = tid; i < M * TILE_ROWS; i += N_CONSUMERS)
             red[i] = (red[i] + red[M * TILE_ROWS + i]) + (red[2 * M * TILE_ROWS + i] + red[3 * M * TILE_ROWS + i]);
-        const long long ua = (long long)t_cur * p.KS, ub = ua + p.KS - 1;
+        const uint32_t ua = (uint32_t)t_cur * (uint32_t)p.KS, ub = ua + (uint32_t)p.KS - 1;
         const int c_first = (int)(((ua + 1) * G - 1) / U), c_last = (int)(((ub + 1) * G - 1) / U);
         if (c_first != c_last) {
             // shared tile: publish, count arrivals, the last arriver sums in CTA order
@@ -1223,13 +1224,18 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             const bool last = s_flags[0] != 0;
             if (last) {
                 __threadfence();
+                // where each contributor left its piece (head piece -> slot 0, else slot 1)
+                int *slot_tab = reinterpret_cast<int *>(red + M * TILE_ROWS);  // quarters 1..3 of red are free now
+                if (tid <= c_last - c_first) {
+                    const int c = c_first + tid;
+                    const int cf = (int)(((uint32_t)c * U / G) / (uint32_t)p.KS);
+                    slot_tab[tid] = (c * 2 + (cf == t_cur ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
+                }
+                consumer_bar();
+                const int nparts = c_last - c_first + 1;
                 for (int i = tid; i < M * TILE_ROWS; i += N_CONSUMERS) {
                     float v = 0.0f;
-                    for (int c = c_first; c <= c_last; ++c) {
-                        const int cf = (int)(((long long)c * U / G) / p.KS);
-                        const float *sl = p.partials + ((size_t)c * 2 + (cf == t_cur ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
-                        v += __ldcg(&sl[i]);
-                    }
+                    for (int k = 0; k < nparts; ++k) v += __ldcg(p.partials + slot_tab[k] + i);  // CTA order
                     red[i] = v;
                 }
                 if (tid == 0) p.counters[t_cur] = 0;
