@@ -188,6 +188,8 @@ struct apk_ctx {
     int *d_err = nullptr;       // device error word
     int *h_err = nullptr;       // pinned mirror
     DevBuf x_dev, y_dev, act_a, act_b, misc, dump;
+    unsigned long long *trace = nullptr;  // when set: every matvec launch stamps its own [n_sm][8] slab
+    uint32_t trace_idx = 0, trace_cap = 0;
     apk_stats_t st{};
     int rank = 0, world = 1;
     bool use_pdl = true;        // ALLPAKA_B200_PDL=0 turns programmatic dependent launch off
@@ -197,6 +199,8 @@ struct apk_ctx {
     XchPeers xch{};                 // every rank's buffer, peer-mapped
     bool p2p_ready = false;
     unsigned char *noalloc_ptr = nullptr;  // device address of the built-in scratch array (apk_matvec_noalloc)
+    int inflight = 3;            // K-steps of weights a CTA keeps outstanding (ALLPAKA_B200_INFLIGHT overrides, for tuning)
+    bool noalloc_dirty = false;  // the last no-allocation call was not seen to end cleanly
     // host address -> device-resident raw GGUF bytes written by apk_debug_synth_matrix
     std::map<const uint8_t *, std::pair<uint8_t *, size_t>> raw_dev;
 };
@@ -537,10 +541,12 @@ int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool
     p.tile_bytes = W->tile_bytes;
     p.two_level = mode.two_level;
     p.m_out = mode.two_level ? mode.m_eff / 2 : mode.m_eff;
-    p.partials = c->partials.as<float>();
+    p.partials = c->partials.as<unsigned long long>();
     p.counters = c->counters.as<int>();
     p.err = c->d_err;
     p.pdl = c->use_pdl ? 1 : 0;
+    p.inflight = c->inflight;
+    if (c->trace && c->trace_idx < c->trace_cap) p.timeline = c->trace + (size_t)(c->trace_idx++) * c->n_sm * 8;
     const int act_rec = p.act.rec_bytes();
     const int ns = pick_stages(c, (int)W->ty, mode.m_eff, p.pro, W->KS, act_rec);
     if (ns < 2) return fail(APK_DECLINE_MISSING_CAPABILITY, "activations of %d rows x %u do not fit in shared memory", mode.m_eff, W->n_in);
@@ -612,9 +618,14 @@ int finish(apk_ctx *c) {
     if (*c->h_err != 0) {
         const int w = *c->h_err;
         cudaMemsetAsync(c->d_err, 0, sizeof(int), c->stream);
+        // a kernel that gave up may have left tagged partial sums behind
+        if (c->partials.p) cudaMemsetAsync(c->partials.p, 0, c->partials.cap, c->stream);
         cudaStreamSynchronize(c->stream);
         return fail(APK_ERR_TIMEOUT, "device-side wait expired (%s)",
-                    w == ERRW_PRODUCER_TIMEOUT ? "copy producer" : w == ERRW_PEER_TIMEOUT ? "a peer rank never announced its partial sums" : "tile consumer");
+                    w == ERRW_PRODUCER_TIMEOUT ? "copy producer"
+                    : w == ERRW_PEER_TIMEOUT   ? "a peer rank never announced its partial sums"
+                    : w == ERRW_FINISHER_TIMEOUT ? "a tile piece of another CTA never arrived"
+                                                 : "tile consumer");
     }
     return APK_OK;
 }
@@ -672,10 +683,11 @@ int apk_init(apk_ctx **out, int device) {
     CUDA_TRY(cudaMemset(c->d_err, 0, sizeof(int)));
     CUDA_TRY(cudaMallocHost((void **)&c->h_err, sizeof(int)));
     *c->h_err = 0;
-    APK_TRY(c->partials.ensure((size_t)c->n_sm * 2 * MAX_M_EFF * TILE_ROWS * sizeof(float), true));
+    APK_TRY(c->partials.ensure((size_t)c->n_sm * 2 * MAX_M_EFF * TILE_ROWS * sizeof(unsigned long long), true));
     APK_TRY(c->counters.ensure(65536 * sizeof(int), true));
     APK_TRY(init_kernel_attrs(c.get()));
     if (const char *e = getenv("ALLPAKA_B200_PDL")) c->use_pdl = atoi(e) != 0;
+    if (const char *e = getenv("ALLPAKA_B200_INFLIGHT")) c->inflight = std::max(1, std::min(atoi(e), MAX_STAGES));
     *out = c.release();
     return APK_OK;
 }

@@ -407,6 +407,35 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
     return APK_OK;
 }
 
+int apk_debug_token_timeline(apk_ctx *c, const apk_token_req *r, uint64_t *stamps, uint32_t max_launches,
+                             uint32_t *n_launches, uint32_t *n_ctas) {
+    if (!c || !stamps || !n_launches || !n_ctas || max_launches == 0) return fail(APK_ERR_INVALID_ARG, "timeline: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    APK_TRY(validate_token_req(c, r));
+    APK_TRY(ensure_graph(c, r));
+    Plan *P = c->plan.get();
+    const size_t words = (size_t)max_launches * c->n_sm * 8;
+    APK_TRY(c->dump.ensure(words * sizeof(uint64_t)));
+    CUDA_TRY(cudaMemcpyAsync(P->xin.p, r->x, (size_t)r->m * P->hidden * 4, cudaMemcpyHostToDevice, c->stream));
+    if (r->rot_dim)
+        CUDA_TRY(cudaMemcpyAsync(P->rope.p, r->rope, (size_t)r->m * (r->rot_dim / 2) * 2 * 4, cudaMemcpyHostToDevice, c->stream));
+    CUDA_TRY(cudaMemsetAsync(c->dump.p, 0, words * sizeof(uint64_t), c->stream));
+    int nl = 0;
+    APK_TRY(enqueue_token(c, P, r->m, 0, &nl));  // untraced pass first: caches and clocks warm
+    c->trace = c->dump.as<unsigned long long>();
+    c->trace_idx = 0;
+    c->trace_cap = max_launches;
+    const int rc = enqueue_token(c, P, r->m, 0, &nl);
+    c->trace = nullptr;
+    *n_launches = c->trace_idx;
+    *n_ctas = (uint32_t)c->n_sm;
+    if (rc) return rc;
+    CUDA_TRY(cudaMemcpyAsync(stamps, c->dump.p, words * sizeof(uint64_t), cudaMemcpyDeviceToHost, c->stream));
+    c->st.calls++;
+    return finish(c);
+}
+
 int apk_decode_replay(apk_ctx *c, const apk_token_req *r, uint32_t iters, float *elapsed_ms) {
     if (!c || !elapsed_ms) return fail(APK_ERR_INVALID_ARG, "replay: null argument");
     std::lock_guard<std::mutex> g(c->mu);

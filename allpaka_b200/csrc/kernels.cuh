@@ -46,7 +46,9 @@ __host__ __device__ constexpr int stage_w_bytes(int ty) { return ty == 8 ? 8 * 4
 constexpr int N_CONSUMER_WARPS = 16; // 4 row groups x 4 quarters of a K-step
 constexpr int K_SPLIT = 4;
 constexpr int N_CONSUMERS = N_CONSUMER_WARPS * 32;
-constexpr int MV_THREADS = N_CONSUMERS + 32;
+constexpr int N_FINISH_WARPS = 2;     // close tiles (cross-CTA hand-off, epilogue) while the consumers stream on
+constexpr int N_FINISHERS = N_FINISH_WARPS * 32;
+constexpr int MV_THREADS = N_CONSUMERS + 32 + N_FINISHERS;  // consumers | producer warp | finisher warps
 constexpr int MAX_M_EFF = 16;
 constexpr int MAX_STAGES = 8;
 constexpr int TY_Q8_0 = 8;
@@ -56,6 +58,7 @@ constexpr int TY_Q4_K = 12;
 constexpr int ERRW_PRODUCER_TIMEOUT = 1;
 constexpr int ERRW_CONSUMER_TIMEOUT = 2;
 constexpr int ERRW_PEER_TIMEOUT = 3;
+constexpr int ERRW_FINISHER_TIMEOUT = 4;
 
 // Spin budget of one mbarrier wait, in SM clock cycles (~2 s).
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
@@ -138,10 +141,11 @@ struct MvParams {
     int pro;            // Prologue
     PrepParams prep;    // PRO_QUANT inputs (prep.out is ignored: blocks go to shared memory)
     int pdl;            // launched with a programmatic dependency on the previous kernel
-    float *partials;    // [gridDim.x][2][MAX_M_EFF][128]
+    unsigned long long *partials;  // [gridDim.x][2][MAX_M_EFF][128] tagged partial sums (see part_store)
     int *counters;      // [n_tiles], zero between launches
     int *err;           // error word
     int32_t *dump;      // optional [m_eff][n_out][nb] int32 block dots
+    int inflight;       // K-steps of weights one CTA keeps in flight at a time (>= 1)
     unsigned long long *timeline;  // optional [gridDim.x][8] globaltimer stamps (trace)
     // epilogue
     int epi;
@@ -217,6 +221,24 @@ __device__ __forceinline__ bool mbar_wait_bounded_relaxed(uint64_t *bar, uint32_
         if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
     }
 }
+// Partial sums of a tile shared by several CTAs travel as one 64-bit word per
+// element: the f32 value below a "valid" tag.  A naturally aligned 64-bit scalar
+// access is single-copy atomic, so a reader that sees the tag has the value: no
+// fence, no counter, no second round trip.  The reader clears what it has read,
+// so every word is back to zero when the kernel ends.
+constexpr unsigned long long PART_VALID = 1ull << 32;
+__device__ __forceinline__ void part_store(unsigned long long *p, float v) {
+    const unsigned long long w = PART_VALID | (unsigned long long)__float_as_uint(v);
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
+}
+__device__ __forceinline__ void part_clear(unsigned long long *p) {
+    asm volatile("st.relaxed.gpu.global.b64 [%0], %1;" ::"l"(p), "l"(0ull) : "memory");
+}
+__device__ __forceinline__ unsigned long long part_load(const unsigned long long *p) {
+    unsigned long long w;
+    asm volatile("ld.relaxed.gpu.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+    return w;
+}
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t p;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
@@ -247,6 +269,7 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
     return t;
 }
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(N_CONSUMERS) : "memory"); }
+__device__ __forceinline__ void finisher_bar() { asm volatile("bar.sync 2, %0;" ::"n"(N_FINISHERS) : "memory"); }
 
 // D[16 rows x 8 cols] = A[16 x 32] . B[32 x 8], int8 operands, int32 result: one
 // 32-element quantisation block of 16 weight rows against up to 8 activation rows.
@@ -657,15 +680,21 @@ __device__ __forceinline__ void scale_min_k4_dev(int j, uint32_t s0, uint32_t s1
 
 // Shared memory map of the matvec kernel (dynamic, 128-byte aligned base):
 //   [0, 64)      full barriers       [64, 128) empty barriers
-//   [128, 136)   flags               [136, 144) barrier of the resident-activation load
-//   [256 ..)     red[4][M][128] f32  (K-quarter partials; red[0] doubles as the tile result)
+//   [128, 136)   barrier of the resident-activation load    [136, 144) prologue scratch released
+//   [144, 152)   red full (consumers -> finishers)          [152, 160) red empty (finishers -> consumers)
+//   [160, 192)   flags: tile and last-tile mark of the hand-off, finisher-local words
+//   [256 ..)     red[4][M][128] f32  K-quarter partials of the tile the consumers just left
+//   [..]         fin[M][128] f32     the finishers' working copy (tile result), then the slot table
 //   [..]         resident activation records (PRO_LOAD / PRO_QUANT), all K-steps
 //   [..]         stages: n_stages * (one K-step of weights [+ one activation record when streaming])
+constexpr int SLOT_TAB_BYTES = 640;  // one int per CTA that can share a tile (grids of up to 160 CTAs)
 template <int M>
 struct MvSmem {
     static constexpr int RED_OFF = 256;
     static constexpr int RED_BYTES = K_SPLIT * M * TILE_ROWS * 4;
-    static constexpr int RES_OFF = RED_OFF + RED_BYTES;
+    static constexpr int FIN_OFF = RED_OFF + RED_BYTES;
+    static constexpr int SLOT_OFF = FIN_OFF + M * TILE_ROWS * 4;
+    static constexpr int RES_OFF = SLOT_OFF + SLOT_TAB_BYTES;
 };
 __host__ __device__ inline int mv_resident_bytes(int pro, int KS, int act_rec) {
     return pro == PRO_STREAM ? 0 : ((KS * act_rec + 127) & ~127);
@@ -674,7 +703,7 @@ __host__ __device__ inline int mv_stage_bytes(int ty, int pro, int act_rec) {
     return stage_w_bytes(ty) + (pro == PRO_STREAM ? ((act_rec + 127) & ~127) : 0);
 }
 __host__ __device__ inline int mv_smem_total(int ty, int m_eff, int pro, int KS, int act_rec, int n_stages) {
-    return 256 + K_SPLIT * m_eff * TILE_ROWS * 4 + mv_resident_bytes(pro, KS, act_rec) + n_stages * mv_stage_bytes(ty, pro, act_rec);
+    return 256 + (K_SPLIT + 1) * m_eff * TILE_ROWS * 4 + SLOT_TAB_BYTES + mv_resident_bytes(pro, KS, act_rec) + n_stages * mv_stage_bytes(ty, pro, act_rec);
 }
 
 // The order in which a CTA walks its range [u_begin, u_end) of the flat unit
@@ -703,7 +732,8 @@ struct UnitOrder {
 
 template <int M>
 __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float *out /*[M][128] smem*/,
-                                              int tid);
+                                              int tid, const float *pre);
+constexpr int EPI_PRE = 2;  // residual values a finisher thread fetches ahead of the EPI_ADD epilogue
 
 // In-CTA activation prologue (PRO_QUANT): the 256 consumer threads turn one row
 // x (n <= 256 * PRO_CH elements) into Q8 blocks in shared memory, after the
@@ -868,9 +898,11 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     extern __shared__ __align__(128) uint8_t smem[];
     uint64_t *full = reinterpret_cast<uint64_t *>(smem);
     uint64_t *empty = full + MAX_STAGES;
-    int *s_flags = reinterpret_cast<int *>(smem + 128);
-    uint64_t *acts_bar = reinterpret_cast<uint64_t *>(smem + 136);
-    uint64_t *pro_bar = reinterpret_cast<uint64_t *>(smem + 144);  // PRO_QUANT scratch (last stage) released
+    uint64_t *acts_bar = reinterpret_cast<uint64_t *>(smem + 128);
+    uint64_t *pro_bar = reinterpret_cast<uint64_t *>(smem + 136);  // PRO_QUANT scratch (last stage) released
+    uint64_t *red_full = reinterpret_cast<uint64_t *>(smem + 144);   // a tile's K-quarter partials are in red
+    uint64_t *red_empty = reinterpret_cast<uint64_t *>(smem + 152);  // the finishers have taken them
+    int *s_flags = reinterpret_cast<int *>(smem + 160);
     float *red = reinterpret_cast<float *>(smem + MvSmem<M>::RED_OFF);
     const int act_rec = p.act.rec_bytes();
     const bool streaming = p.pro == PRO_STREAM;
@@ -889,6 +921,8 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         }
         mbar_init(acts_bar, 1);
         mbar_init(pro_bar, N_CONSUMER_WARPS);
+        mbar_init(red_full, N_CONSUMER_WARPS);
+        mbar_init(red_empty, 1);
         fence_mbar_init();
     }
     __syncthreads();
@@ -930,9 +964,25 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             };
             // Weights depend on nothing: fill the ring before waiting for the previous kernel.
             // (The in-CTA prologue borrows the last stage buffer as scratch until pro_bar.)
-            const int ring0 = p.pro == PRO_QUANT ? NS - 1 : NS;
+            // Only `inflight` K-steps are outstanding at a time: a K-step or two per SM already
+            // saturate HBM, and everything beyond that just queues in the memory system, in
+            // front of the small latency-critical loads (activation rows, tile pieces of other
+            // CTAs) of the kernel that is finishing on the other SMs.
+            const int D = p.inflight < NS - 1 ? p.inflight : NS - 1;  // D < NS: the stage asked about has not been re-armed since
+            bool stuck = false;
+            auto landed = [&](int j) {  // K-step j of this CTA's walk is in shared memory
+                if (j >= 0 && !stuck && !mbar_wait_bounded_relaxed(&full[j % NS], (uint32_t)((j / NS) & 1))) {
+                    stuck = true;
+                    atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
+                }
+            };
+            int ring0 = p.pro == PRO_QUANT ? NS - 1 : NS;
+            if (streaming && ring0 > D) ring0 = D;  // a streamed stage completes only with its activation record
             const int pre = n_total < ring0 ? n_total : ring0;
-            for (int it = 0; it < pre; ++it) issue_weights(it);
+            for (int it = 0; it < pre; ++it) {
+                landed(it - D);
+                issue_weights(it);
+            }
             if (p.pdl) pdl_wait();
             if (p.pro == PRO_QUANT) {
                 // the activation row, raw, into the scratch stage; then hands off until the prologue is done
@@ -953,10 +1003,11 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             for (; it < n_total; ++it) {
                 const int s = it % NS;
                 const uint32_t ph = (uint32_t)((it / NS) & 1);
-                if (!mbar_wait_bounded_relaxed(&empty[s], ph ^ 1u)) {
+                if (stuck || !mbar_wait_bounded_relaxed(&empty[s], ph ^ 1u)) {
                     atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
                     break;
                 }
+                landed(it - D);
                 issue_weights(it);
                 if (streaming) issue_acts(it);
             }
@@ -966,6 +1017,102 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             for (int j = it - pending; j < it; ++j) (void)mbar_wait_bounded(&full[j % NS], (uint32_t)((j / NS) & 1));
             if (p.pro != PRO_STREAM) (void)mbar_wait_bounded(acts_bar, 0u);
         }
+        return;
+    }
+
+    if (warp > N_CONSUMER_WARPS) {
+        // ------------------------------------------------------- finishers
+        // Take each tile (or tile piece) the consumers leave in red, and close it: add the
+        // four K-quarters; for a tile shared with other CTAs publish the partial sum, count
+        // arrivals, and if this CTA is the last to arrive add all pieces in CTA order; run
+        // the epilogue.  None of this stalls the consumers, who are already on the next tile.
+        const int ftid = tid - (N_CONSUMERS + 32);
+        float *fin = reinterpret_cast<float *>(smem + MvSmem<M>::FIN_OFF);
+        int *slot_tab = reinterpret_cast<int *>(smem + MvSmem<M>::SLOT_OFF);
+        const int my_first_tile = (int)(order.u_begin / (uint32_t)p.KS);
+        for (uint32_t n = 0;; ++n) {
+            // one thread waits (bounded) and tells the others, so all of them leave together
+            if (ftid == 0) {
+                const bool ok = mbar_wait_bounded(red_full, n & 1u);
+                if (!ok) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
+                s_flags[2] = ok ? 1 : 0;
+            }
+            finisher_bar();
+            if (s_flags[2] == 0) break;
+            const int t_cur = s_flags[0];
+            const bool final_tile = s_flags[1] != 0;
+            for (int i = ftid; i < M * TILE_ROWS; i += N_FINISHERS)
+                fin[i] = (red[i] + red[M * TILE_ROWS + i]) + (red[2 * M * TILE_ROWS + i] + red[3 * M * TILE_ROWS + i]);
+            finisher_bar();  // red and the flags have been read
+            if (ftid == 0) mbar_arrive(red_empty);
+            const uint32_t ua = (uint32_t)t_cur * (uint32_t)p.KS, ub = ua + (uint32_t)p.KS - 1;
+            const int c_first = (int)(((ua + 1) * G - 1) / U), c_last = (int)(((ub + 1) * G - 1) / U);
+            if (c_first != c_last && (int)blockIdx.x != c_last) {
+                // a piece of a tile that a later CTA closes: publish and move on
+                unsigned long long *slot =
+                    p.partials + ((size_t)blockIdx.x * 2 + (my_first_tile == t_cur ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
+                for (int i = ftid; i < M * TILE_ROWS; i += N_FINISHERS) part_store(&slot[i], fin[i]);
+            } else {
+                // EPI_ADD: the residual is known since the dependency resolved; fetch it now so
+                // that its round trip overlaps the wait for the other pieces
+                float pre[EPI_PRE];
+                const bool use_pre = p.epi == EPI_ADD && M * TILE_ROWS <= EPI_PRE * N_FINISHERS && !p.two_level;
+                if (use_pre) {
+#pragma unroll
+                    for (int j = 0; j < EPI_PRE; ++j) {
+                        const int i = ftid + j * N_FINISHERS;
+                        const int m = i / TILE_ROWS, row = t_cur * TILE_ROWS + i % TILE_ROWS;
+                        pre[j] = (i < M * TILE_ROWS && row < p.n_out) ? p.resid[(size_t)m * p.ldr + row] : 0.0f;
+                    }
+                }
+                if (c_first != c_last) {
+                    // This CTA holds the last units of the tile: it adds the pieces of CTAs
+                    // c_first .. c_last-1 (lower block indices, so they were scheduled no later
+                    // than this one) in CTA order, then its own.  Where each left its piece:
+                    // head piece -> slot 0, else slot 1.
+                    const int nparts = c_last - c_first;
+                    for (int k = ftid; k < nparts; k += N_FINISHERS) {
+                        const int c = c_first + k;
+                        const int cf = (int)(((uint32_t)c * U / G) / (uint32_t)p.KS);
+                        slot_tab[k] = (c * 2 + (cf == t_cur ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
+                    }
+                    finisher_bar();
+                    const long long t_wait = clock64();
+                    bool gave_up = false;
+                    for (int i = ftid; i < M * TILE_ROWS; i += N_FINISHERS) {
+                        float v = 0.0f;
+                        for (int k0 = 0; k0 < nparts; k0 += 8) {
+                            // eight pieces per round trip; poll until every tag is there (bounded)
+                            unsigned long long w[8];
+                            for (;;) {
+                                bool all = true;
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    w[j] = (k0 + j < nparts) ? part_load(p.partials + slot_tab[k0 + j] + i) : PART_VALID;
+                                    all = all && (w[j] & PART_VALID) != 0;
+                                }
+                                if (all || gave_up) break;
+                                if (clock64() - t_wait > WAIT_LIMIT_CYCLES) gave_up = true;
+                            }
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                if (k0 + j < nparts) {
+                                    v += __uint_as_float((uint32_t)w[j]);
+                                    part_clear(p.partials + slot_tab[k0 + j] + i);
+                                }
+                        }
+                        fin[i] = v + fin[i];
+                    }
+                    if (gave_up) atomicExch(p.err, ERRW_FINISHER_TIMEOUT);
+                    finisher_bar();
+                }
+                if (tl && ftid == 0 && final_tile && p.pro != PRO_QUANT) tl[7] = globaltimer_ns();  // pieces added
+                epilogue_tile<M>(p, t_cur, fin, ftid, use_pre ? pre : nullptr);
+            }
+            finisher_bar();  // fin, the slot table and the flags are reused by the next tile
+            if (final_tile) break;
+        }
+        if (tl && ftid == 0) tl[5] = globaltimer_ns();  // the last tile done
         return;
     }
 
@@ -1004,7 +1151,6 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     }
     if (tl && tid == 0) tl[6] = globaltimer_ns();  // activations ready
 
-    const int my_first_tile = (int)(order.u_begin / p.KS);
     // (tile, K-step) of the walk, kept incrementally: the order has one jump
     // (after the tail piece) and otherwise advances by one unit.
     int t, ks;
@@ -1015,6 +1161,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     }
     int s = 0;
     uint32_t ph = 0;
+    uint32_t n_handoff = 0;  // tiles (or tile pieces) passed to the finishers so far
     for (int it = 0; it < n_total; ++it) {
         // where the next unit lies (decides whether this one closes its tile)
         int t_next = t, ks_next = ks + 1;
@@ -1195,6 +1342,13 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             ph ^= 1u;
         }
         if (!tile_done) continue;
+        // Hand the tile's partial sums to the finisher warps and stream on.  red is a single
+        // buffer: the finishers copy it out at once, so this wait only bites when two tiles
+        // close within a fraction of a microsecond.
+        if (n_handoff > 0 && !aborted && !mbar_wait_bounded(red_empty, (n_handoff - 1u) & 1u)) {
+            aborted = true;
+            if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
+        }
 #pragma unroll
         for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -1205,56 +1359,20 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     if (tok < M) red[(kq * M + tok) * TILE_ROWS + rg * 32 + h * 16 + lg + (i >> 1) * 8] = acc[h][j][i];
                     acc[h][j][i] = 0.0f;
                 }
-        consumer_bar();
-        for (int i = tid; i < M * TILE_ROWS; i += N_CONSUMERS)
-            red[i] = (red[i] + red[M * TILE_ROWS + i]) + (red[2 * M * TILE_ROWS + i] + red[3 * M * TILE_ROWS + i]);
-        const uint32_t ua = (uint32_t)t_cur * (uint32_t)p.KS, ub = ua + (uint32_t)p.KS - 1;
-        const int c_first = (int)(((ua + 1) * G - 1) / U), c_last = (int)(((ub + 1) * G - 1) / U);
-        if (c_first != c_last) {
-            // shared tile: publish, count arrivals, the last arriver sums in CTA order
-            float *slot = p.partials + ((size_t)blockIdx.x * 2 + (my_first_tile == t_cur ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
-            for (int i = tid; i < M * TILE_ROWS; i += N_CONSUMERS) __stcg(&slot[i], red[i]);
-            __threadfence();
-            consumer_bar();
-            if (tid == 0) {
-                const int old = atomicAdd(&p.counters[t_cur], 1);
-                s_flags[0] = (old == c_last - c_first) ? 1 : 0;
-            }
-            consumer_bar();
-            const bool last = s_flags[0] != 0;
-            if (last) {
-                __threadfence();
-                // where each contributor left its piece (head piece -> slot 0, else slot 1)
-                int *slot_tab = reinterpret_cast<int *>(red + M * TILE_ROWS);  // quarters 1..3 of red are free now
-                if (tid <= c_last - c_first) {
-                    const int c = c_first + tid;
-                    const int cf = (int)(((uint32_t)c * U / G) / (uint32_t)p.KS);
-                    slot_tab[tid] = (c * 2 + (cf == t_cur ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
-                }
-                consumer_bar();
-                const int nparts = c_last - c_first + 1;
-                for (int i = tid; i < M * TILE_ROWS; i += N_CONSUMERS) {
-                    float v = 0.0f;
-                    for (int k = 0; k < nparts; ++k) v += __ldcg(p.partials + slot_tab[k] + i);  // CTA order
-                    red[i] = v;
-                }
-                if (tid == 0) p.counters[t_cur] = 0;
-                consumer_bar();
-                epilogue_tile<M>(p, t_cur, red, tid);
-            }
-        } else {
-            consumer_bar();
-            epilogue_tile<M>(p, t_cur, red, tid);
+        if (tid == 0) {
+            s_flags[0] = t_cur;
+            s_flags[1] = (it + 1 == n_total) ? 1 : 0;
         }
-        consumer_bar();  // red is reused by the next tile
-        if (tl && tid == 0 && it + 1 == n_total) tl[5] = globaltimer_ns();  // the last tile done
+        __syncwarp();
+        if (lane == 0) mbar_arrive(red_full);
+        ++n_handoff;
     }
 }
 
 // tile result out[m][r] (m < M rows of the activation record) -> global.
-// Called by all 256 consumer threads.
+// Called by all finisher threads (tid = index among them).
 template <int M>
-__device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float *out, int tid) {
+__device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float *out, int tid, const float *pre) {
     const int MO = p.m_out;
     // two-level rows 2m, 2m+1 are the two digits of token m: their sum is the dot
     auto val = [&](int m, int r) -> float {
@@ -1263,12 +1381,12 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
     };
     const int row0 = tile * TILE_ROWS;
     if (p.epi == EPI_STORE || p.epi == EPI_ADD) {
-        for (int i = tid; i < MO * TILE_ROWS; i += N_CONSUMERS) {
+        for (int i = tid, j = 0; i < MO * TILE_ROWS; i += N_FINISHERS, ++j) {
             const int m = i / TILE_ROWS, r = i % TILE_ROWS;
             const int row = row0 + r;
             if (row >= p.n_out) continue;
             float v = val(m, r);
-            if (p.epi == EPI_ADD) v = __fadd_rn(p.resid[(size_t)m * p.ldr + row], v);
+            if (p.epi == EPI_ADD) v = __fadd_rn(pre ? pre[j] : p.resid[(size_t)m * p.ldr + row], v);
             p.y[(size_t)m * p.ldy + row] = v;
         }
         return;
@@ -1277,7 +1395,7 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
         // the exchange in flight is epoch + 1 (the epoch word only moves between kernels)
         const uint32_t parity = (__ldcg(xch_epoch(p.xch.slots[p.xch.rank])) + 1u) & 1u;
         const size_t slot = ((size_t)parity * XCH_MAX_RANKS + p.xch.rank) * XCH_ROW_FLOATS;
-        for (int i = tid; i < MO * TILE_ROWS; i += N_CONSUMERS) {
+        for (int i = tid; i < MO * TILE_ROWS; i += N_FINISHERS) {
             const int m = i / TILE_ROWS, r = i % TILE_ROWS;
             const int row = row0 + r;
             if (row >= p.n_out) continue;
@@ -1296,7 +1414,7 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
         const int warp = tid >> 5, lane = tid & 31;
         const float *nw = tile < p.n_q_tiles ? p.q_norm : (tile < p.n_q_tiles + p.n_k_tiles ? p.k_norm : nullptr);
         const bool rot = tile < p.n_q_tiles + p.n_k_tiles;
-        for (int m = warp; m < MO; m += N_CONSUMER_WARPS) {
+        for (int m = warp; m < MO; m += N_FINISH_WARPS) {
             float v[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) v[j] = val(m, lane + 32 * j);
@@ -1349,8 +1467,8 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
         // identity attention core: the roped Q head is what the output projection consumes.
         // One warp per (token, 32-element block): the four blocks of a head go in parallel.
         if (p.q_next.base && tile < p.n_q_tiles) {
-            consumer_bar();
-            for (int w = warp; w < MO * 4; w += N_CONSUMER_WARPS) {
+            finisher_bar();
+            for (int w = warp; w < MO * 4; w += N_FINISH_WARPS) {
                 const int m = w >> 2, j = w & 3;
                 const float *hs = out + (p.two_level ? 2 * m : m) * TILE_ROWS;
                 quantize_store(p.q_next, p.q_next_two_level, p.q_next_need_sum, m, tile * 4 + j, lane, hs[lane + 32 * j]);
@@ -1362,7 +1480,7 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
         // rows 0..63 = gate rows [64*tile, 64*tile+64), rows 64..127 = the matching up rows.
         // Work item = (token, 32-row half) = one activation block of the down projection.
         const int warp = tid >> 5, lane = tid & 31;
-        for (int w = warp; w < MO * 2; w += N_CONSUMER_WARPS) {
+        for (int w = warp; w < MO * 2; w += N_FINISH_WARPS) {
             const int m = w >> 1, h = w & 1;
             const int r = h * 32 + lane;
             const float g = val(m, r), uu = val(m, 64 + r);

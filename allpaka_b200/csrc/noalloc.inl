@@ -18,14 +18,14 @@ namespace {
 
 constexpr uint32_t NOALLOC_MAX_CTAS = 160;       // one CTA per SM
 constexpr uint32_t NOALLOC_MAX_TILES = 4096;     // 128-row tiles -> n_out <= 524288
-constexpr size_t NOALLOC_PARTIALS_BYTES = (size_t)NOALLOC_MAX_CTAS * 2 * MAX_M_EFF * TILE_ROWS * sizeof(float);
+constexpr size_t NOALLOC_PARTIALS_BYTES = (size_t)NOALLOC_MAX_CTAS * 2 * MAX_M_EFF * TILE_ROWS * sizeof(unsigned long long);
 constexpr size_t NOALLOC_COUNTERS_BYTES = (size_t)NOALLOC_MAX_TILES * sizeof(int);
 constexpr size_t NOALLOC_ERR_BYTES = 256;
 constexpr size_t NOALLOC_ACTS_BYTES = (size_t)MAX_M_EFF * APK_NOALLOC_MAX_N_IN * 5 / 4 + 256;
 constexpr size_t NOALLOC_OFF_COUNTERS = NOALLOC_PARTIALS_BYTES;
 constexpr size_t NOALLOC_OFF_ERR = NOALLOC_OFF_COUNTERS + NOALLOC_COUNTERS_BYTES;
 constexpr size_t NOALLOC_OFF_ACTS = NOALLOC_OFF_ERR + NOALLOC_ERR_BYTES;
-constexpr size_t NOALLOC_TOTAL = NOALLOC_OFF_ACTS + NOALLOC_ACTS_BYTES;  // about 3.3 MB
+constexpr size_t NOALLOC_TOTAL = NOALLOC_OFF_ACTS + NOALLOC_ACTS_BYTES;  // about 5.9 MB
 
 // Held by every GPU that loads the library, until the process exits.  In host
 // code this name is only a stand-in for the symbol, never a device address.
@@ -67,12 +67,17 @@ extern "C" int apk_matvec_noalloc(apk_ctx *c, const void *w, uint32_t ty, uint32
     APK_TRY(noalloc_setup(c));  // first call on this device: resolves the scratch symbol
     cudaStream_t st = (cudaStream_t)stream;
     unsigned char *base = c->noalloc_ptr;
-    float *partials = reinterpret_cast<float *>(base);
+    unsigned long long *partials = reinterpret_cast<unsigned long long *>(base);
     int *counters = reinterpret_cast<int *>(base + NOALLOC_OFF_COUNTERS);
     int *err = reinterpret_cast<int *>(base + NOALLOC_OFF_ERR);
     void *acts = base + NOALLOC_OFF_ACTS;
     // The array keeps the previous call's contents: counters and the error word must start at zero.
     CUDA_TRY(cudaMemsetAsync(base + NOALLOC_OFF_COUNTERS, 0, NOALLOC_COUNTERS_BYTES + NOALLOC_ERR_BYTES, st));
+    // So must the tagged partial sums.  A kernel that ran to its end leaves them zero; only a
+    // call that was seen to end cleanly (wait != 0, no error) proves that, so after any other
+    // call the region is cleared again.
+    if (c->noalloc_dirty) CUDA_TRY(cudaMemsetAsync(base, 0, NOALLOC_PARTIALS_BYTES, st));
+    c->noalloc_dirty = true;
 
     const ActMode mode = resolve_mode(act_mode, m);
     MvKernel k = pick_kernel(W->ty, mode.m_eff, false);
@@ -114,6 +119,7 @@ extern "C" int apk_matvec_noalloc(apk_ctx *c, const void *w, uint32_t ty, uint32
     p.counters = counters;
     p.err = err;
     p.pdl = 0;
+    p.inflight = c->inflight;
     p.epi = EPI_STORE;
     p.y = y_dev;
     p.ldy = (int)n_out;
@@ -133,5 +139,6 @@ extern "C" int apk_matvec_noalloc(apk_ctx *c, const void *w, uint32_t ty, uint32
     CUDA_TRY(cudaMemcpyAsync(&herr, err, sizeof herr, cudaMemcpyDeviceToHost, st));
     CUDA_TRY(cudaStreamSynchronize(st));
     if (herr != 0) return fail(APK_ERR_TIMEOUT, "device-side wait expired (%s)", herr == ERRW_PRODUCER_TIMEOUT ? "copy producer" : "tile consumer");
+    c->noalloc_dirty = false;
     return APK_OK;
 }

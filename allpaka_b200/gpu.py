@@ -108,7 +108,7 @@ EXPORTS = (
     "apk_stats", "apk_last_error", "apk_dist_unique_id", "apk_dist_init",
     "apk_debug_synth_matrix", "apk_debug_synth_release", "apk_decode_profile",
     "apk_debug_matvec_timeline", "apk_shard_plan", "apk_matvec_noalloc",
-    "apk_dist_p2p_export", "apk_dist_p2p_open",
+    "apk_dist_p2p_export", "apk_dist_p2p_open", "apk_debug_token_timeline",
 )
 
 _lib = None
@@ -146,6 +146,7 @@ def load_library() -> C.CDLL:
     l.apk_debug_synth_release.argtypes = [C.c_void_p]
     l.apk_debug_matvec_timeline.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
                                             C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
+    l.apk_debug_token_timeline.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
     l.apk_matvec_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
                                      C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_int]
     l.apk_decode_profile.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
@@ -501,6 +502,19 @@ class Gpu:
             raise GpuError(rc, self._err())
         names = ("qkv", "wo", "gate_up", "down", "lm_head")
         return {n: {"ms": float(t), "bytes": float(b)} for n, t, b in zip(names, ms, by)}
+
+    def debug_token_timeline(self, req: "TokenReq", max_launches: int = 64):
+        """Per-launch, per-CTA global-timer stamps (ns) of one un-graphed token; see the C header."""
+        creq, keep = self._token_req(req)
+        stamps = np.zeros((max_launches, 256, 8), dtype=np.uint64)
+        nl, nc = C.c_uint32(), C.c_uint32()
+        # the library writes [launch][n_ctas][8] densely; n_ctas is only known afterwards
+        flat = stamps.reshape(-1)
+        rc = self._l.apk_debug_token_timeline(self._h, C.byref(creq), flat.ctypes.data, max_launches,
+                                              C.byref(nl), C.byref(nc))
+        if rc != 0:
+            raise GpuError(rc, self._err())
+        return flat[: max_launches * nc.value * 8].reshape(max_launches, nc.value, 8)[: nl.value]
 
     # -- gpu::stats / decode_path_stats (common.rs:24-31, types.rs:271-278) --
     def stats_full(self) -> dict:

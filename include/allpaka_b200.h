@@ -212,7 +212,7 @@ int apk_debug_q8_acts(apk_ctx *ctx, const float *x, uint32_t n, const float *gam
  * simply fail), or the call sits in a latency-bounded decode loop where the
  * device-wide stall of an allocation is not acceptable.  They own x and y already; the kernel's
  * private scratch (stream-K partial sums, tile arrival counters, error word,
- * quantised-activation records) lives in a fixed ~3.3 MB array inside the
+ * quantised-activation records) lives in a fixed ~5.9 MB array inside the
  * library's device image, which every GPU that loads the library holds until
  * the process exits.
  *
@@ -242,6 +242,14 @@ int apk_matvec_noalloc(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_in, 
  * 0, 0}.  n_ctas receives the grid size. */
 int apk_debug_matvec_timeline(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_in, uint32_t n_out,
                               const float *x, uint32_t m, uint64_t *stamps, uint32_t max_ctas, uint32_t *n_ctas);
+
+/* Trace of a whole token: the token of apk_decode_token is enqueued launch by
+ * launch (no graph) and every matvec launch writes the same eight stamps per
+ * CTA into its own slab: stamps[launch][n_ctas][8], launches in issue order
+ * (per layer Q|K|V, wo, gate/up, down; then the LM head).  At most
+ * max_launches slabs are written; n_launches receives how many were. */
+int apk_debug_token_timeline(apk_ctx *ctx, const apk_token_req *req, uint64_t *stamps, uint32_t max_launches,
+                             uint32_t *n_launches, uint32_t *n_ctas);
 
 /* Benchmark utility: a seeded synthetic tensor without host-side generation.
  * The raw GGUF blocks of the [n_out, n_in] matrix whose host address is w are
