@@ -200,6 +200,7 @@ struct apk_ctx {
     bool p2p_ready = false;
     unsigned char *noalloc_ptr = nullptr;  // device address of the built-in scratch array (apk_matvec_noalloc)
     int inflight = 3;            // K-steps of weights a CTA keeps outstanding (ALLPAKA_B200_INFLIGHT overrides, for tuning)
+    int inflight_pre = 2;        // ... while the previous kernel is still finishing (ALLPAKA_B200_INFLIGHT_PRE)
     bool noalloc_dirty = false;  // the last no-allocation call was not seen to end cleanly
     // host address -> device-resident raw GGUF bytes written by apk_debug_synth_matrix
     std::map<const uint8_t *, std::pair<uint8_t *, size_t>> raw_dev;
@@ -546,6 +547,7 @@ int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool
     p.err = c->d_err;
     p.pdl = c->use_pdl ? 1 : 0;
     p.inflight = c->inflight;
+    p.inflight_pre = c->inflight_pre;
     if (c->trace && c->trace_idx < c->trace_cap) p.timeline = c->trace + (size_t)(c->trace_idx++) * c->n_sm * 8;
     const int act_rec = p.act.rec_bytes();
     const int ns = pick_stages(c, (int)W->ty, mode.m_eff, p.pro, W->KS, act_rec);
@@ -688,6 +690,7 @@ int apk_init(apk_ctx **out, int device) {
     APK_TRY(init_kernel_attrs(c.get()));
     if (const char *e = getenv("ALLPAKA_B200_PDL")) c->use_pdl = atoi(e) != 0;
     if (const char *e = getenv("ALLPAKA_B200_INFLIGHT")) c->inflight = std::max(1, std::min(atoi(e), MAX_STAGES));
+    if (const char *e = getenv("ALLPAKA_B200_INFLIGHT_PRE")) c->inflight_pre = std::max(1, std::min(atoi(e), MAX_STAGES));
     *out = c.release();
     return APK_OK;
 }

@@ -146,6 +146,7 @@ struct MvParams {
     int *err;           // error word
     int32_t *dump;      // optional [m_eff][n_out][nb] int32 block dots
     int inflight;       // K-steps of weights one CTA keeps in flight at a time (>= 1)
+    int inflight_pre;   // the same while the previous kernel has not finished yet (>= 1)
     unsigned long long *timeline;  // optional [gridDim.x][8] globaltimer stamps (trace)
     // epilogue
     int epi;
@@ -732,7 +733,7 @@ struct UnitOrder {
 
 template <int M>
 __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float *out /*[M][128] smem*/,
-                                              int tid, const float *pre);
+                                              int tid, const float *pre, const float *rope_pre);
 constexpr int EPI_PRE = 2;  // residual values a finisher thread fetches ahead of the EPI_ADD epilogue
 
 // In-CTA activation prologue (PRO_QUANT): the 256 consumer threads turn one row
@@ -968,7 +969,10 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             // saturate HBM, and everything beyond that just queues in the memory system, in
             // front of the small latency-critical loads (activation rows, tile pieces of other
             // CTAs) of the kernel that is finishing on the other SMs.
+            // While the previous kernel is still closing its tiles the budget is smaller still
+            // (inflight_pre): there is no hurry, the dependency wait comes next.
             const int D = p.inflight < NS - 1 ? p.inflight : NS - 1;  // D < NS: the stage asked about has not been re-armed since
+            const int D0 = p.inflight_pre < D ? p.inflight_pre : D;
             bool stuck = false;
             auto landed = [&](int j) {  // K-step j of this CTA's walk is in shared memory
                 if (j >= 0 && !stuck && !mbar_wait_bounded_relaxed(&full[j % NS], (uint32_t)((j / NS) & 1))) {
@@ -977,28 +981,20 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 }
             };
             int ring0 = p.pro == PRO_QUANT ? NS - 1 : NS;
-            if (streaming && ring0 > D) ring0 = D;  // a streamed stage completes only with its activation record
+            if (streaming && ring0 > D0) ring0 = D0;  // a streamed stage completes only with its activation record
             const int pre = n_total < ring0 ? n_total : ring0;
             for (int it = 0; it < pre; ++it) {
-                landed(it - D);
+                landed(it - D0);
                 issue_weights(it);
             }
-            if (p.pdl) pdl_wait();
-            if (p.pro == PRO_QUANT) {
-                // the activation row, raw, into the scratch stage; then hands off until the prologue is done
-                const uint32_t bytes = (uint32_t)p.prep.n * (p.prep.x_is_bf16 ? 2u : 4u);
-                mbar_arrive_expect_tx(acts_bar, bytes);
-                bulk_g2s(stages + (size_t)(NS - 1) * stage_bytes, p.prep.x, bytes, acts_bar, pol_a);
-                if (!mbar_wait_bounded_relaxed(pro_bar, 0u)) atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
-            }
-            if (p.pro == PRO_LOAD) {
-                const uint32_t bytes = (uint32_t)(p.KS * act_rec);
-                mbar_arrive_expect_tx(acts_bar, bytes);
-                for (uint32_t o = 0; o < bytes; o += 32768u)
-                    bulk_g2s(res + o, p.act.base + o, min(32768u, bytes - o), acts_bar, pol_a);
-            }
-            if (streaming)
+            // (The resident activations are fetched by the first consumer thread, which is not
+            // held up by the metering above.)
+            if (streaming) {
+                if (p.pdl) pdl_wait();
                 for (int it = 0; it < pre; ++it) issue_acts(it);
+            }
+            // the in-CTA prologue borrows the last stage until it is done
+            if (p.pro == PRO_QUANT && !mbar_wait_bounded_relaxed(pro_bar, 0u)) atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
             int it = pre;
             for (; it < n_total; ++it) {
                 const int s = it % NS;
@@ -1030,6 +1026,20 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         float *fin = reinterpret_cast<float *>(smem + MvSmem<M>::FIN_OFF);
         int *slot_tab = reinterpret_cast<int *>(smem + MvSmem<M>::SLOT_OFF);
         const int my_first_tile = (int)(order.u_begin / (uint32_t)p.KS);
+        // The RoPE table comes from the host, not from the previous kernel: the sin/cos pairs
+        // lane, lane+32 of the first token this warp rotates are fetched before any tile is due.
+        float rope_pre[4] = {0.f, 0.f, 0.f, 0.f};
+        const bool has_rope_pre = p.epi == EPI_QKV_ROPE && (p.half == 32 || p.half == 64) && (ftid >> 5) < p.m_out;
+        if (has_rope_pre) {
+            const float *tab = p.rope + (size_t)(ftid >> 5) * p.half * 2;
+            const int l = ftid & 31;
+            rope_pre[0] = tab[2 * l];
+            rope_pre[1] = tab[2 * l + 1];
+            if (l + 32 < p.half) {
+                rope_pre[2] = tab[2 * (l + 32)];
+                rope_pre[3] = tab[2 * (l + 32) + 1];
+            }
+        }
         for (uint32_t n = 0;; ++n) {
             // one thread waits (bounded) and tells the others, so all of them leave together
             if (ftid == 0) {
@@ -1107,7 +1117,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     finisher_bar();
                 }
                 if (tl && ftid == 0 && final_tile && p.pro != PRO_QUANT) tl[7] = globaltimer_ns();  // pieces added
-                epilogue_tile<M>(p, t_cur, fin, ftid, use_pre ? pre : nullptr);
+                epilogue_tile<M>(p, t_cur, fin, ftid, use_pre ? pre : nullptr, has_rope_pre ? rope_pre : nullptr);
             }
             finisher_bar();  // fin, the slot table and the flags are reused by the next tile
             if (final_tile) break;
@@ -1137,6 +1147,21 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     if (p.pro == PRO_QUANT) prologue_gamma(p, tid, gam);  // independent of the previous kernel
     if (p.pdl) pdl_wait();
     if (tl && tid == 0) tl[2] = globaltimer_ns();  // dependency satisfied
+    if (tid == 0 && p.pro != PRO_STREAM) {
+        // the activations, as soon as they exist
+        const uint64_t pol_a = l2_policy_evict_last();
+        if (p.pro == PRO_QUANT) {
+            // the raw row into the scratch stage (the ring's last, which the producer leaves alone until pro_bar)
+            const uint32_t bytes = (uint32_t)p.prep.n * (p.prep.x_is_bf16 ? 2u : 4u);
+            mbar_arrive_expect_tx(acts_bar, bytes);
+            bulk_g2s(stages + (size_t)(NS - 1) * stage_bytes, p.prep.x, bytes, acts_bar, pol_a);
+        } else {
+            const uint32_t bytes = (uint32_t)(p.KS * act_rec);
+            mbar_arrive_expect_tx(acts_bar, bytes);
+            for (uint32_t o = 0; o < bytes; o += 32768u)
+                bulk_g2s(res + o, p.act.base + o, min(32768u, bytes - o), acts_bar, pol_a);
+        }
+    }
     if (p.pro != PRO_STREAM && !mbar_wait_bounded(acts_bar, 0u)) {
         aborted = true;
         if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
@@ -1372,7 +1397,8 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
 // tile result out[m][r] (m < M rows of the activation record) -> global.
 // Called by all finisher threads (tid = index among them).
 template <int M>
-__device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float *out, int tid, const float *pre) {
+__device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float *out, int tid, const float *pre,
+                                              const float *rope_pre) {
     const int MO = p.m_out;
     // two-level rows 2m, 2m+1 are the two digits of token m: their sum is the dot
     auto val = [&](int m, int r) -> float {
@@ -1443,13 +1469,18 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
                 const int c = lane + 32 * j;
                 float o = v[j];
                 if (rot) {
-                    // ops::rope_neox_cached_from_array (ops/rope.rs:70-81)
+                    // ops::rope_neox_cached_from_array (ops/rope.rs:70-81); pair i = lane or lane + 32
+                    // when half is 32 or 64, which is what the prefetched values cover
+                    const bool from_pre = rope_pre != nullptr && m == warp;
                     if (c < half) {
-                        const float sn = tab[2 * c], cs = tab[2 * c + 1];
+                        const float sn = from_pre ? (j == 0 ? rope_pre[0] : rope_pre[2]) : tab[2 * c];
+                        const float cs = from_pre ? (j == 0 ? rope_pre[1] : rope_pre[3]) : tab[2 * c + 1];
                         o = __fsub_rn(__fmul_rn(v[j], cs), __fmul_rn(hs[c + half], sn));
                     } else if (c < 2 * half) {
                         const int i = c - half;
-                        const float sn = tab[2 * i], cs = tab[2 * i + 1];
+                        const bool first = i < 32;  // pair `lane`, else pair `lane + 32`
+                        const float sn = from_pre ? (first ? rope_pre[0] : rope_pre[2]) : tab[2 * i];
+                        const float cs = from_pre ? (first ? rope_pre[1] : rope_pre[3]) : tab[2 * i + 1];
                         o = __fadd_rn(__fmul_rn(hs[i], sn), __fmul_rn(v[j], cs));
                     }
                 }

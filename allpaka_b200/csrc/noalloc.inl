@@ -120,6 +120,7 @@ extern "C" int apk_matvec_noalloc(apk_ctx *c, const void *w, uint32_t ty, uint32
     p.err = err;
     p.pdl = 0;
     p.inflight = c->inflight;
+    p.inflight_pre = c->inflight_pre;
     p.epi = EPI_STORE;
     p.y = y_dev;
     p.ldy = (int)n_out;
