@@ -46,7 +46,7 @@ __host__ __device__ constexpr int stage_w_bytes(int ty) { return ty == 8 ? 8 * 4
 constexpr int N_CONSUMER_WARPS = 16; // 4 row groups x 4 quarters of a K-step
 constexpr int K_SPLIT = 4;
 constexpr int N_CONSUMERS = N_CONSUMER_WARPS * 32;
-constexpr int N_FINISH_WARPS = 2;     // close tiles (cross-CTA hand-off, epilogue) while the consumers stream on
+constexpr int N_FINISH_WARPS = 3;     // close tiles (cross-CTA hand-off, epilogue) while the consumers stream on
 constexpr int N_FINISHERS = N_FINISH_WARPS * 32;
 constexpr int MV_THREADS = N_CONSUMERS + 32 + N_FINISHERS;  // consumers | producer warp | finisher warps
 constexpr int MAX_M_EFF = 16;
@@ -281,6 +281,14 @@ __device__ __forceinline__ void mma_block_s8(int (&d)[4], const uint4 &a, uint32
         : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1), "r"(0));
 }
 
+// The same, accumulating onto d.
+__device__ __forceinline__ void mma_block_s8_acc(int (&d)[4], const uint4 &a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+}
+
 __device__ __forceinline__ int dot32(const int4 &w0, const int4 &w1, const int4 &x0, const int4 &x1) {
     int s = __dp4a(w0.x, x0.x, 0);
     s = __dp4a(w0.y, x0.y, s);
@@ -347,7 +355,7 @@ __device__ __forceinline__ void store_act_block(const ActLayout &L, int row, int
 
 // Quantise value v (lane = element) of token m, block k_block, in Q8 mode
 // (one row per token) or two-level mode (rows 2m = value, 2m+1 = residual:
-// x = d1*q1 + d2*q2 to ~2^-15 of the block maximum, which is how the f32
+// x = d1*q1 + d2*q2, d2 = d1/256, to ~2^-16 of the block maximum, which is how the f32
 // activation call sites of the reference are served by the integer kernels).
 __device__ __forceinline__ void quantize_store(const ActLayout &L, int two_level, int need_sum, int m,
                                                int k_block, int lane, float v) {
@@ -356,9 +364,13 @@ __device__ __forceinline__ void quantize_store(const ActLayout &L, int two_level
         store_act_block(L, m, k_block, lane, q1);
         return;
     }
-    // residual is exact in one fused operation
+    // residual is exact in one fused operation; its scale is d1 / 256 exactly, so that the
+    // consumer can merge the two digits as integers: d1*dot1 + d2*dot2 = d2 * (256*dot1 + dot2)
     const float r = __fmaf_rn(-q1.d, (float)q1.q, v);
-    QBlock q2 = quantize_block(r, false);
+    QBlock q2;
+    q2.d = q1.d * 0.00390625f;
+    q2.sum = 0.0f;
+    q2.q = max(-127, min(127, q8_round(r, q2.d > 0.0f ? __frcp_rn(q2.d) : 0.0f)));
     if (need_sum) {
         // the min term needs sum(x) once: carry the exact block sum on the first row
         float s = 0.0f;
@@ -843,30 +855,43 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
     // Stage by stage across the PRO_J chunks (not chunk by chunk): the warp shuffles
     // order the instruction stream, so independent work has to sit side by side for
     // the chains of the five blocks to overlap.
+    float dprev[PRO_J];
 #pragma unroll
     for (int lv = 0; lv < 2; ++lv) {
         if (lv < levels) {
             float amax[PRO_J], db[PRO_J], id[PRO_J];
             int q[PRO_CH];
+            if (lv == 0) {
+#pragma unroll
+                for (int j = 0; j < PRO_J; ++j) {
+                    amax[j] = fmaxf(fmaxf(fabsf(v[4 * j]), fabsf(v[4 * j + 1])), fmaxf(fabsf(v[4 * j + 2]), fabsf(v[4 * j + 3])));
+                    if (amax[j] != amax[j]) amax[j] = 0.0f;  // all four NaN: f32::max drops NaN operands
+                }
+#pragma unroll
+                for (int o = 1; o <= 4; o <<= 1) {
+                    float t[PRO_J];
+#pragma unroll
+                    for (int j = 0; j < PRO_J; ++j) t[j] = __shfl_xor_sync(0xffffffffu, amax[j], o);
+#pragma unroll
+                    for (int j = 0; j < PRO_J; ++j) amax[j] = fmaxf(amax[j], t[j]);
+                }
+#pragma unroll
+                for (int j = 0; j < PRO_J; ++j) db[j] = amax[j] <= 3.402823466e+38f ? __fdiv_rn(amax[j], 127.0f) : 0.0f;
+            } else {
+                // the residual's scale is d1 / 256 exactly (see quantize_store)
+#pragma unroll
+                for (int j = 0; j < PRO_J; ++j) db[j] = dprev[j] * 0.00390625f;
+            }
 #pragma unroll
             for (int j = 0; j < PRO_J; ++j) {
-                amax[j] = fmaxf(fmaxf(fabsf(v[4 * j]), fabsf(v[4 * j + 1])), fmaxf(fabsf(v[4 * j + 2]), fabsf(v[4 * j + 3])));
-                if (amax[j] != amax[j]) amax[j] = 0.0f;  // all four NaN: f32::max drops NaN operands
+                id[j] = (db[j] > 0.0f) ? __frcp_rn(db[j]) : 0.0f;  // IEEE 1.0/db
+                dprev[j] = db[j];
             }
 #pragma unroll
-            for (int o = 1; o <= 4; o <<= 1) {
-                float t[PRO_J];
-#pragma unroll
-                for (int j = 0; j < PRO_J; ++j) t[j] = __shfl_xor_sync(0xffffffffu, amax[j], o);
-#pragma unroll
-                for (int j = 0; j < PRO_J; ++j) amax[j] = fmaxf(amax[j], t[j]);
+            for (int k = 0; k < PRO_CH; ++k) {
+                q[k] = q8_round(v[k], id[k >> 2]);
+                if (lv == 1) q[k] = max(-127, min(127, q[k]));
             }
-#pragma unroll
-            for (int j = 0; j < PRO_J; ++j) db[j] = amax[j] <= 3.402823466e+38f ? __fdiv_rn(amax[j], 127.0f) : 0.0f;
-#pragma unroll
-            for (int j = 0; j < PRO_J; ++j) id[j] = (db[j] > 0.0f) ? __frcp_rn(db[j]) : 0.0f;  // IEEE 1.0/db
-#pragma unroll
-            for (int k = 0; k < PRO_CH; ++k) q[k] = q8_round(v[k], id[k >> 2]);
 #pragma unroll
             for (int j = 0; j < PRO_J; ++j) {
                 const int e = 4 * tid + PRO_CHUNK * j;
@@ -912,13 +937,21 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     uint8_t *stages = res + mv_resident_bytes(p.pro, p.KS, act_rec);
     const int NS = p.n_stages;
 
+    // Few activation rows (M <= 4): the eight result columns of an mma are shared out among
+    // 8 / MP2 consecutive blocks x MP2 rows ("chained columns", see the consumers below); the
+    // two halves of the consumer warps then take alternate K-steps.
+    constexpr bool CH = M <= 4;
+    constexpr int MP2 = M <= 1 ? 1 : (M <= 2 ? 2 : 4);  // result columns per block
+    constexpr int BPC = 8 / MP2;                        // blocks per mma chain
+    constexpr int KQ = CH ? 2 : K_SPLIT;                // partial sums per tile row handed to the finishers
+
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     unsigned long long *tl = p.timeline ? p.timeline + (size_t)blockIdx.x * 8 : nullptr;
     if (tl && tid == 0) tl[0] = globaltimer_ns();
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full[s], 1);
-            mbar_init(&empty[s], N_CONSUMER_WARPS);
+            mbar_init(&empty[s], CH ? N_CONSUMER_WARPS / 2 : N_CONSUMER_WARPS);
         }
         mbar_init(acts_bar, 1);
         mbar_init(pro_bar, N_CONSUMER_WARPS);
@@ -981,10 +1014,11 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 }
             };
             int ring0 = p.pro == PRO_QUANT ? NS - 1 : NS;
-            if (streaming && ring0 > D0) ring0 = D0;  // a streamed stage completes only with its activation record
             const int pre = n_total < ring0 ? n_total : ring0;
             for (int it = 0; it < pre; ++it) {
-                landed(it - D0);
+                // (a streamed stage completes only with its activation record, which cannot be
+                // asked for yet: no metering there)
+                if (!streaming) landed(it - D0);
                 issue_weights(it);
             }
             // (The resident activations are fetched by the first consumer thread, which is not
@@ -1051,8 +1085,16 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             if (s_flags[2] == 0) break;
             const int t_cur = s_flags[0];
             const bool final_tile = s_flags[1] != 0;
-            for (int i = ftid; i < M * TILE_ROWS; i += N_FINISHERS)
-                fin[i] = (red[i] + red[M * TILE_ROWS + i]) + (red[2 * M * TILE_ROWS + i] + red[3 * M * TILE_ROWS + i]);
+            // Two-level activations: the consumers merged the digit pairs, everything sits in the
+            // even rows; from here on the tile has one row per token.
+            const int R = p.two_level ? M / 2 : M;
+            const int RN = R * TILE_ROWS;
+            for (int i = ftid; i < RN; i += N_FINISHERS) {
+                const int src = p.two_level ? 2 * (i / TILE_ROWS) * TILE_ROWS + i % TILE_ROWS : i;
+                float v = red[src] + red[M * TILE_ROWS + src];
+                if (KQ == 4) v += red[2 * M * TILE_ROWS + src] + red[3 * M * TILE_ROWS + src];
+                fin[i] = v;
+            }
             finisher_bar();  // red and the flags have been read
             if (ftid == 0) mbar_arrive(red_empty);
             const uint32_t ua = (uint32_t)t_cur * (uint32_t)p.KS, ub = ua + (uint32_t)p.KS - 1;
@@ -1061,18 +1103,18 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 // a piece of a tile that a later CTA closes: publish and move on
                 unsigned long long *slot =
                     p.partials + ((size_t)blockIdx.x * 2 + (my_first_tile == t_cur ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
-                for (int i = ftid; i < M * TILE_ROWS; i += N_FINISHERS) part_store(&slot[i], fin[i]);
+                for (int i = ftid; i < RN; i += N_FINISHERS) part_store(&slot[i], fin[i]);
             } else {
                 // EPI_ADD: the residual is known since the dependency resolved; fetch it now so
                 // that its round trip overlaps the wait for the other pieces
                 float pre[EPI_PRE];
-                const bool use_pre = p.epi == EPI_ADD && M * TILE_ROWS <= EPI_PRE * N_FINISHERS && !p.two_level;
+                const bool use_pre = p.epi == EPI_ADD && RN <= EPI_PRE * N_FINISHERS;
                 if (use_pre) {
 #pragma unroll
                     for (int j = 0; j < EPI_PRE; ++j) {
                         const int i = ftid + j * N_FINISHERS;
                         const int m = i / TILE_ROWS, row = t_cur * TILE_ROWS + i % TILE_ROWS;
-                        pre[j] = (i < M * TILE_ROWS && row < p.n_out) ? p.resid[(size_t)m * p.ldr + row] : 0.0f;
+                        pre[j] = (i < RN && row < p.n_out) ? p.resid[(size_t)m * p.ldr + row] : 0.0f;
                     }
                 }
                 if (c_first != c_last) {
@@ -1089,17 +1131,21 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     finisher_bar();
                     const long long t_wait = clock64();
                     bool gave_up = false;
-                    for (int i = ftid; i < M * TILE_ROWS; i += N_FINISHERS) {
-                        float v = 0.0f;
+                    for (int i = ftid; i < RN; i += 2 * N_FINISHERS) {
+                        // two elements x eight pieces per round trip; poll until every tag is there (bounded)
+                        const int i2 = i + N_FINISHERS;
+                        const bool two = i2 < RN;
+                        float v = 0.0f, v2 = 0.0f;
                         for (int k0 = 0; k0 < nparts; k0 += 8) {
-                            // eight pieces per round trip; poll until every tag is there (bounded)
-                            unsigned long long w[8];
+                            unsigned long long w[8], w2[8];
                             for (;;) {
                                 bool all = true;
 #pragma unroll
                                 for (int j = 0; j < 8; ++j) {
-                                    w[j] = (k0 + j < nparts) ? part_load(p.partials + slot_tab[k0 + j] + i) : PART_VALID;
-                                    all = all && (w[j] & PART_VALID) != 0;
+                                    const bool on = k0 + j < nparts;
+                                    w[j] = on ? part_load(p.partials + slot_tab[k0 + j] + i) : PART_VALID;
+                                    w2[j] = (on && two) ? part_load(p.partials + slot_tab[k0 + j] + i2) : PART_VALID;
+                                    all = all && (w[j] & w2[j] & PART_VALID) != 0;
                                 }
                                 if (all || gave_up) break;
                                 if (clock64() - t_wait > WAIT_LIMIT_CYCLES) gave_up = true;
@@ -1109,9 +1155,14 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                                 if (k0 + j < nparts) {
                                     v += __uint_as_float((uint32_t)w[j]);
                                     part_clear(p.partials + slot_tab[k0 + j] + i);
+                                    if (two) {
+                                        v2 += __uint_as_float((uint32_t)w2[j]);
+                                        part_clear(p.partials + slot_tab[k0 + j] + i2);
+                                    }
                                 }
                         }
                         fin[i] = v + fin[i];
+                        if (two) fin[i2] = v2 + fin[i2];
                     }
                     if (gave_up) atomicExch(p.err, ERRW_FINISHER_TIMEOUT);
                     finisher_bar();
@@ -1141,6 +1192,12 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         for (int j = 0; j < NG; ++j)
 #pragma unroll
             for (int i = 0; i < 4; ++i) acc[h][j][i] = 0.0f;
+    // chained columns: warp = (16-row half-group, parity of the K-steps it takes)
+    const int hg = warp & 7, ug = warp >> 3;
+    const int rgc = hg >> 1, h16c = hg & 1;
+    const int my_blk = lg / MP2;                          // block of a chain whose activations this lane feeds (B column lg)
+    const int my_tok = (lg % MP2) < M ? (lg % MP2) : M - 1;  // ... and which activation row (clamped)
+    float cacc[4] = {0.0f, 0.0f, 0.0f, 0.0f};             // rows lg, lg, lg+8, lg+8 x result columns 2lt, 2lt+1
     bool aborted = false;
 
     float gam[PRO_CH];
@@ -1197,15 +1254,16 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             ks_next = 0;
             t_next = t + 1;
         }
-        if (!aborted && !mbar_wait_bounded(&full[s], ph)) {
+        const bool mine = !CH || (it & 1) == ug;
+        if (mine && !aborted && !mbar_wait_bounded(&full[s], ph)) {
             aborted = true;
             if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
         }
-        if (tl && tid == 0) {
+        if (tl && mine && lane == 0 && (warp & 7) == 0) {
             if (it == 0) tl[1] = globaltimer_ns();   // first unit landed
             if (it + 1 == n_total) tl[3] = globaltimer_ns();  // last unit landed
         }
-        if (!aborted) {
+        if (mine && !aborted) {
             const uint8_t *sw = stages + (size_t)s * stage_bytes;
             const uint8_t *sa = streaming ? sw + stage_w_bytes(TY) : res + (size_t)ks * act_rec;
             const int kb = min(kt, p.nb - ks * kt);
@@ -1220,6 +1278,141 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     if (tok < M && row < p.n_out) p.dump[((size_t)tok * p.n_out + row) * p.nb + gb] = d[i];
                 }
             };
+            if constexpr (CH) {
+                // Chained columns.  One mma gives 16 rows x 8 columns, and with a single activation
+                // row seven columns would repeat the first.  Instead a chain of BPC mmas runs over BPC
+                // consecutive blocks into ONE accumulator, block i of the chain feeding only columns
+                // i*MP2 .. i*MP2+MP2-1 of the B operand (zero elsewhere): column c of the result is the
+                // block dot of block c / MP2 with activation row c % MP2.  Every lane then holds four
+                // distinct dots (rows lg, lg+8 x columns 2lt, 2lt+1) and the fp32 scaling is done once
+                // per dot instead of eight times.
+                auto dumpc = [&](const int (&d)[4], int gb0) {  // gb0: global index of the chain's first block
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int c = 2 * lt + (i & 1);
+                        const int row = t * TILE_ROWS + hg * 16 + lg + (i >> 1) * 8;
+                        const int tok = c % MP2, gb = gb0 + c / MP2;
+                        if (tok < M && gb < p.nb && row < p.n_out) p.dump[((size_t)tok * p.n_out + row) * p.nb + gb] = d[i];
+                    }
+                };
+                if (TY == TY_Q8_0) {
+                    const uint8_t *wa = sw + rgc * 1024 + h16c * 512 + lane * 16;       // + b*4096
+                    const uint8_t *ws = sw + kb * 4096 + (rgc * 8 + lg) * 8 + h16c * 4;  // + b*256: scales of rows lg, lg+8
+#pragma unroll
+                    for (int cb = 0; cb < Q8_KT; cb += BPC) {
+                        if (cb < kb) {
+                            const int xblk = cb + my_blk;
+                            uint32_t xb0 = 0u, xb1 = 0u;
+                            if (xblk < kb) {
+                                const uint8_t *xb = sa + xblk * (32 * M) + my_tok * 16 + 4 * lt;
+                                xb0 = *reinterpret_cast<const uint32_t *>(xb);
+                                xb1 = *reinterpret_cast<const uint32_t *>(xb + 16 * M);
+                            }
+                            int d[4] = {0, 0, 0, 0}, e[4] = {0, 0, 0, 0};  // two chains, so consecutive mmas do not wait on each other
+#pragma unroll
+                            for (int i = 0; i < BPC; ++i) {
+                                if (cb + i < kb) {
+                                    const uint4 a = *reinterpret_cast<const uint4 *>(wa + (cb + i) * 4096);
+                                    const uint32_t b0 = my_blk == i ? xb0 : 0u, b1 = my_blk == i ? xb1 : 0u;
+                                    if (i & 1) mma_block_s8_acc(e, a, b0, b1);
+                                    else mma_block_s8_acc(d, a, b0, b1);
+                                }
+                            }
+                            if (BPC > 1) {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) d[i] += e[i];
+                            }
+                            if (MP2 > 1 && p.two_level) {
+                                // columns 2lt, 2lt+1 are the two digits of one token of one block, d2 = d1 / 256:
+                                // merge them as integers, scale once
+                                const int c = 2 * lt;
+                                const int b = cb + c / MP2, tok = c % MP2 + 1;
+                                if (b < kb) {
+                                    const __half2 sc = *reinterpret_cast<const __half2 *>(ws + b * 256);
+                                    const float dx = ad[b * MP + tok];
+                                    cacc[0] = fmaf(__fmul_rn(__low2float(sc), dx), (float)((d[0] << 8) + d[1]), cacc[0]);
+                                    cacc[2] = fmaf(__fmul_rn(__high2float(sc), dx), (float)((d[2] << 8) + d[3]), cacc[2]);
+                                }
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const int c = 2 * lt + (i & 1);
+                                    const int b = cb + c / MP2;
+                                    const int tok = (c % MP2) < M ? (c % MP2) : M - 1;
+                                    if (b < kb) {
+                                        const __half2 sc = *reinterpret_cast<const __half2 *>(ws + b * 256);
+                                        const float dw = (i >> 1) ? __high2float(sc) : __low2float(sc);
+                                        cacc[i] = fmaf(__fmul_rn(dw, ad[b * MP + tok]), (float)d[i], cacc[i]);
+                                    }
+                                }
+                            }
+                            if (DUMP) dumpc(d, ks * Q8_KT + cb);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int sbi = 0; sbi < Q4_KT_SB; ++sbi) {
+                        if (sbi * 8 < kb) {
+                            const uint8_t *base = sw + sbi * Q4_SB_UNIT + rgc * Q4_SB_RG;
+                            const uint8_t *hdr = base + 4096;
+                            // {d, dmin} of rows lg, lg+8 of this half
+                            const uint2 dd = *reinterpret_cast<const uint2 *>(hdr + (lg * 4 + 2 * h16c) * 4);
+                            float U[4] = {0.0f, 0.0f, 0.0f, 0.0f}, V[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                            for (int ch = 0; ch < 8 / BPC; ++ch) {  // sub-blocks ch*BPC .. ch*BPC+BPC-1 of the super-block
+                                const int xs = sbi * 8 + ch * BPC + my_blk;
+                                const uint8_t *xb = sa + xs * (32 * M) + my_tok * 16 + 4 * lt;
+                                const uint32_t xb0 = *reinterpret_cast<const uint32_t *>(xb);
+                                const uint32_t xb1 = *reinterpret_cast<const uint32_t *>(xb + 16 * M);
+                                int d[4] = {0, 0, 0, 0}, e[4] = {0, 0, 0, 0};
+#pragma unroll
+                                for (int pi = 0; pi < BPC / 2; ++pi) {  // a byte holds sub-blocks 2*pr (low nibble), 2*pr+1 (high)
+                                    const int pr = ch * (BPC / 2) + pi;
+                                    const uint4 q = *reinterpret_cast<const uint4 *>(base + ((pr * 2 + h16c) * 32 + lane) * 16);
+                                    const uint4 lo = make_uint4(q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu);
+                                    const uint4 hi = make_uint4((q.x >> 4) & 0x0f0f0f0fu, (q.y >> 4) & 0x0f0f0f0fu,
+                                                                (q.z >> 4) & 0x0f0f0f0fu, (q.w >> 4) & 0x0f0f0f0fu);
+                                    mma_block_s8_acc(d, lo, my_blk == 2 * pi ? xb0 : 0u, my_blk == 2 * pi ? xb1 : 0u);
+                                    mma_block_s8_acc(e, hi, my_blk == 2 * pi + 1 ? xb0 : 0u, my_blk == 2 * pi + 1 ? xb1 : 0u);
+                                }
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) d[i] += e[i];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    const int c = 2 * lt + (i & 1);
+                                    const int sbk = ch * BPC + c / MP2;  // sub-block of the super-block
+                                    const int tok = (c % MP2) < M ? (c % MP2) : M - 1;
+                                    // 6-bit scale and min of rows lg, lg+8 (split out at repack): four sub-blocks per word
+                                    const uint2 scw = *reinterpret_cast<const uint2 *>(hdr + 128 + ((lg * 2 + (sbk >> 2)) * 4 + 2 * h16c) * 4);
+                                    const uint2 mnw = *reinterpret_cast<const uint2 *>(hdr + 384 + ((lg * 2 + (sbk >> 2)) * 4 + 2 * h16c) * 4);
+                                    const float sc = (float)((((i >> 1) ? scw.y : scw.x) >> (8 * (sbk & 3))) & 0xffu);
+                                    const float mn = (float)((((i >> 1) ? mnw.y : mnw.x) >> (8 * (sbk & 3))) & 0xffu);
+                                    const int b = sbi * 8 + sbk;
+                                    if (MP2 > 1 && p.two_level) {
+                                        // digits merged as integers (d2 = d1 / 256); odd columns carry nothing
+                                        if (!(i & 1)) {
+                                            U[i] = fmaf(sc, __fmul_rn((float)((d[i] << 8) + d[i + 1]), ad[b * MP + tok + 1]), U[i]);
+                                            V[i] = fmaf(mn, as[b * MP + tok], V[i]);
+                                        }
+                                    } else {
+                                        U[i] = fmaf(sc, __fmul_rn((float)d[i], ad[b * MP + tok]), U[i]);
+                                        V[i] = fmaf(mn, as[b * MP + tok], V[i]);
+                                    }
+                                }
+                                if (DUMP) dumpc(d, ks * 16 + sbi * 8 + ch * BPC);
+                            }
+                            // total += d * sum(sc*dot*dx) - dmin * sum(mn*sum)  (q8_acts.rs:296-297, regrouped per super-block)
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const uint32_t w = (i >> 1) ? dd.y : dd.x;
+                                const float dq = __half2float(__ushort_as_half((unsigned short)(w & 0xffffu)));
+                                const float dmin = __half2float(__ushort_as_half((unsigned short)(w >> 16)));
+                                cacc[i] += __fsub_rn(__fmul_rn(dq, U[i]), __fmul_rn(dmin, V[i]));
+                            }
+                        }
+                    }
+                }
+            } else
             if (TY == TY_Q8_0) {
                 // this warp: blocks kq, kq+4 of the K-step.  Activation rows past M are clamped to
                 // row M-1: their results are computed but never stored, which keeps predicates
@@ -1247,16 +1440,26 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                         mma_block_s8(d1, a1, b0, b1);
                         const float dx0 = xd[t0];
                         // total += d_w * d_x * dot (q8_acts.rs:93), per (row, token)
-                        acc[0][j][0] = fmaf(__fmul_rn(f01.x, dx0), (float)d0[0], acc[0][j][0]);
-                        acc[0][j][2] = fmaf(__fmul_rn(f01.y, dx0), (float)d0[2], acc[0][j][2]);
-                        acc[1][j][0] = fmaf(__fmul_rn(f23.x, dx0), (float)d1[0], acc[1][j][0]);
-                        acc[1][j][2] = fmaf(__fmul_rn(f23.y, dx0), (float)d1[2], acc[1][j][2]);
-                        if (M > 1) {  // a single activation row never has an odd column
+                        if (M > 1 && p.two_level) {
+                            // columns 2lt, 2lt+1 are the two digits of one token, d2 = d1 / 256:
+                            // merge them as integers, scale once
                             const float dx1 = xd[t1];
-                            acc[0][j][1] = fmaf(__fmul_rn(f01.x, dx1), (float)d0[1], acc[0][j][1]);
-                            acc[0][j][3] = fmaf(__fmul_rn(f01.y, dx1), (float)d0[3], acc[0][j][3]);
-                            acc[1][j][1] = fmaf(__fmul_rn(f23.x, dx1), (float)d1[1], acc[1][j][1]);
-                            acc[1][j][3] = fmaf(__fmul_rn(f23.y, dx1), (float)d1[3], acc[1][j][3]);
+                            acc[0][j][0] = fmaf(__fmul_rn(f01.x, dx1), (float)((d0[0] << 8) + d0[1]), acc[0][j][0]);
+                            acc[0][j][2] = fmaf(__fmul_rn(f01.y, dx1), (float)((d0[2] << 8) + d0[3]), acc[0][j][2]);
+                            acc[1][j][0] = fmaf(__fmul_rn(f23.x, dx1), (float)((d1[0] << 8) + d1[1]), acc[1][j][0]);
+                            acc[1][j][2] = fmaf(__fmul_rn(f23.y, dx1), (float)((d1[2] << 8) + d1[3]), acc[1][j][2]);
+                        } else {
+                            acc[0][j][0] = fmaf(__fmul_rn(f01.x, dx0), (float)d0[0], acc[0][j][0]);
+                            acc[0][j][2] = fmaf(__fmul_rn(f01.y, dx0), (float)d0[2], acc[0][j][2]);
+                            acc[1][j][0] = fmaf(__fmul_rn(f23.x, dx0), (float)d1[0], acc[1][j][0]);
+                            acc[1][j][2] = fmaf(__fmul_rn(f23.y, dx0), (float)d1[2], acc[1][j][2]);
+                            if (M > 1) {  // a single activation row never has an odd column
+                                const float dx1 = xd[t1];
+                                acc[0][j][1] = fmaf(__fmul_rn(f01.x, dx1), (float)d0[1], acc[0][j][1]);
+                                acc[0][j][3] = fmaf(__fmul_rn(f01.y, dx1), (float)d0[3], acc[0][j][3]);
+                                acc[1][j][1] = fmaf(__fmul_rn(f23.x, dx1), (float)d1[1], acc[1][j][1]);
+                                acc[1][j][3] = fmaf(__fmul_rn(f23.y, dx1), (float)d1[3], acc[1][j][3]);
+                            }
                         }
                         if (DUMP) {
                             dump4(d0, 0, j, ks * Q8_KT + b);
@@ -1323,14 +1526,25 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                                 mma_block_s8(d1, nib ? hi[1] : lo[1], b0, b1);
                                 const float dx0 = ad[b * MP + t0], dx1 = ad[b * MP + t1];
                                 const float sx0 = as[b * MP + t0], sx1 = as[b * MP + t1];
+                                if (M > 1 && p.two_level) {
+                                    // digits merged as integers (d2 = d1 / 256); the min term rides on the first digit's row
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) {
-                                    if (M == 1 && (i & 1)) continue;  // a single activation row has no odd column
-                                    const float dx = (i & 1) ? dx1 : dx0, sx = (i & 1) ? sx1 : sx0;
-                                    U[0][j][i] = fmaf(scf[i >> 1], __fmul_rn((float)d0[i], dx), U[0][j][i]);
-                                    U[1][j][i] = fmaf(scf[2 + (i >> 1)], __fmul_rn((float)d1[i], dx), U[1][j][i]);
-                                    V[0][j][i] = fmaf(mnf[i >> 1], sx, V[0][j][i]);
-                                    V[1][j][i] = fmaf(mnf[2 + (i >> 1)], sx, V[1][j][i]);
+                                    for (int i = 0; i < 4; i += 2) {
+                                        U[0][j][i] = fmaf(scf[i >> 1], __fmul_rn((float)((d0[i] << 8) + d0[i + 1]), dx1), U[0][j][i]);
+                                        U[1][j][i] = fmaf(scf[2 + (i >> 1)], __fmul_rn((float)((d1[i] << 8) + d1[i + 1]), dx1), U[1][j][i]);
+                                        V[0][j][i] = fmaf(mnf[i >> 1], sx0, V[0][j][i]);
+                                        V[1][j][i] = fmaf(mnf[2 + (i >> 1)], sx0, V[1][j][i]);
+                                    }
+                                } else {
+#pragma unroll
+                                    for (int i = 0; i < 4; ++i) {
+                                        if (M == 1 && (i & 1)) continue;  // a single activation row has no odd column
+                                        const float dx = (i & 1) ? dx1 : dx0, sx = (i & 1) ? sx1 : sx0;
+                                        U[0][j][i] = fmaf(scf[i >> 1], __fmul_rn((float)d0[i], dx), U[0][j][i]);
+                                        U[1][j][i] = fmaf(scf[2 + (i >> 1)], __fmul_rn((float)d1[i], dx), U[1][j][i]);
+                                        V[0][j][i] = fmaf(mnf[i >> 1], sx, V[0][j][i]);
+                                        V[1][j][i] = fmaf(mnf[2 + (i >> 1)], sx, V[1][j][i]);
+                                    }
                                 }
                                 if (DUMP) {
                                     dump4(d0, 0, j, ks * 16 + b);
@@ -1374,16 +1588,41 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             aborted = true;
             if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
         }
+        if constexpr (CH) {
+            // columns of the same activation row sit in different lt lanes: add them up
+            float v[4] = {cacc[0], cacc[1], cacc[2], cacc[3]};
+            if (MP2 == 1) {  // all eight columns are row 0
+                v[0] += v[1];
+                v[2] += v[3];
+            }
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int j = 0; j < NG; ++j)
+            for (int i = 0; i < 4; ++i) {
+                if (MP2 <= 2) v[i] += __shfl_xor_sync(0xffffffffu, v[i], 1);
+                v[i] += __shfl_xor_sync(0xffffffffu, v[i], 2);
+            }
+            // after that lane lt = 0 (MP2 <= 2) or lanes lt = 0, 1 (MP2 = 4) hold rows 2lt, 2lt+1
+            if (lt < (MP2 == 4 ? 2 : 1)) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const int tok = 8 * j + 2 * lt + (i & 1);
-                    if (tok < M) red[(kq * M + tok) * TILE_ROWS + rg * 32 + h * 16 + lg + (i >> 1) * 8] = acc[h][j][i];
-                    acc[h][j][i] = 0.0f;
+                    const int tok = MP2 == 1 ? 0 : (2 * lt + (i & 1)) % MP2;
+                    if ((MP2 > 1 || !(i & 1)) && tok < M)
+                        red[(ug * M + tok) * TILE_ROWS + hg * 16 + lg + (i >> 1) * 8] = v[i];
                 }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) cacc[i] = 0.0f;
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int j = 0; j < NG; ++j)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int tok = 8 * j + 2 * lt + (i & 1);
+                        if (tok < M) red[(kq * M + tok) * TILE_ROWS + rg * 32 + h * 16 + lg + (i >> 1) * 8] = acc[h][j][i];
+                        acc[h][j][i] = 0.0f;
+                    }
+        }
         if (tid == 0) {
             s_flags[0] = t_cur;
             s_flags[1] = (it + 1 == n_total) ? 1 : 0;
@@ -1400,11 +1639,8 @@ template <int M>
 __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float *out, int tid, const float *pre,
                                               const float *rope_pre) {
     const int MO = p.m_out;
-    // two-level rows 2m, 2m+1 are the two digits of token m: their sum is the dot
-    auto val = [&](int m, int r) -> float {
-        return p.two_level ? out[(2 * m) * TILE_ROWS + r] + out[(2 * m + 1) * TILE_ROWS + r]
-                           : out[m * TILE_ROWS + r];
-    };
+    // one row per token (the digit pairs of two-level activations are merged by now)
+    auto val = [&](int m, int r) -> float { return out[m * TILE_ROWS + r]; };
     const int row0 = tile * TILE_ROWS;
     if (p.epi == EPI_STORE || p.epi == EPI_ADD) {
         for (int i = tid, j = 0; i < MO * TILE_ROWS; i += N_FINISHERS, ++j) {
@@ -1458,7 +1694,7 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
             }
             // stage the (normed) head so rotation partners can be read back
             __syncwarp();
-            float *hs = out + (p.two_level ? 2 * m : m) * TILE_ROWS;
+            float *hs = out + m * TILE_ROWS;
 #pragma unroll
             for (int j = 0; j < 4; ++j) hs[lane + 32 * j] = v[j];
             __syncwarp();
@@ -1501,7 +1737,7 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
             finisher_bar();
             for (int w = warp; w < MO * 4; w += N_FINISH_WARPS) {
                 const int m = w >> 2, j = w & 3;
-                const float *hs = out + (p.two_level ? 2 * m : m) * TILE_ROWS;
+                const float *hs = out + m * TILE_ROWS;
                 quantize_store(p.q_next, p.q_next_two_level, p.q_next_need_sum, m, tile * 4 + j, lane, hs[lane + 32 * j]);
             }
         }
