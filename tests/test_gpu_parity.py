@@ -281,6 +281,20 @@ def test_decode_token_matches_oracle_layer_stack(gpu, orc, ty, m, qk_norm):
     gpu.detach(r.buf)
 
 
+@pytest.mark.parametrize("ty,m", [(Q8_0, 1), (Q8_0, 3), (Q4_K, 1)])
+def test_decode_token_tiles_shared_by_many_ctas(gpu, orc, ty, m):
+    """Shapes whose K dimension spreads one tile over up to eight CTAs (every CTA holds one unit),
+    per-head norm on: the cross-CTA hand-off, the residual epilogue and the packed Q for wo."""
+    hidden, nh, nkv, ffn, vocab = 1024, 8, 2, 2048, 1536
+    req, layers, head, out_norm, x, rope, r = build_token(gpu, orc, ty, 2, hidden, nh, nkv, ffn, vocab, m, True, 700)
+    logits = gpu.decode_token_checked(req)
+    xo = oracle_decode(orc, ty, layers, hidden, nh * 128, nkv * 128, 128, ffn, 1e-6, rope, x, m)
+    want = oracle_logits(orc, ty, head, vocab, hidden, xo, out_norm, 1e-6, m)
+    assert rel_l2(logits, want) <= TOL, rel_l2(logits, want)
+    assert np.array_equal(logits, gpu.decode_token_checked(req))
+    gpu.detach(r.buf)
+
+
 def test_decode_token_declines_what_it_does_not_build(gpu, orc):
     from allpaka_b200.gpu import DecodeDecline
 
