@@ -25,8 +25,10 @@
 // Work split ("stream-K"): the flat unit sequence of the whole matrix is cut
 // into equal contiguous ranges, one per CTA (one CTA per SM), so every SM
 // streams the same number of bytes regardless of n_out.  A tile whose units
-// straddle CTAs is finished by the last CTA to arrive, which sums the
-// partials in a fixed order (deterministic; no float atomics, no waiting).
+// straddle CTAs is finished by the CTA that holds its last units: the others
+// publish their partial sums as tagged 64-bit words, it adds them in CTA order
+// (deterministic; no float atomics; its only wait, on CTAs of lower index of
+// the same grid, is bounded).
 #pragma once
 
 #include <cuda_bf16.h>
@@ -142,7 +144,7 @@ struct MvParams {
     PrepParams prep;    // PRO_QUANT inputs (prep.out is ignored: blocks go to shared memory)
     int pdl;            // launched with a programmatic dependency on the previous kernel
     unsigned long long *partials;  // [gridDim.x][2][MAX_M_EFF][128] tagged partial sums (see part_store)
-    int *counters;      // [n_tiles], zero between launches
+    int *counters;      // [n_tiles] zeroed scratch; not used by the tagged hand-off
     int *err;           // error word
     int32_t *dump;      // optional [m_eff][n_out][nb] int32 block dots
     int inflight;       // K-steps of weights one CTA keeps in flight at a time (>= 1)
@@ -748,8 +750,8 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
                                               int tid, const float *pre, const float *rope_pre);
 constexpr int EPI_PRE = 2;  // residual values a finisher thread fetches ahead of the EPI_ADD epilogue
 
-// In-CTA activation prologue (PRO_QUANT): the 256 consumer threads turn one row
-// x (n <= 256 * PRO_CH elements) into Q8 blocks in shared memory, after the
+// In-CTA activation prologue (PRO_QUANT): the consumer threads turn one row
+// x (n <= N_CONSUMERS * PRO_CH elements) into Q8 blocks in shared memory, after the
 // optional RMSNorm, entirely in registers.
 //  * The norm weight does not depend on the previous kernel: it is loaded
 //    BEFORE the dependency wait (prologue_gamma).

@@ -228,7 +228,9 @@ int apk_debug_q8_acts(apk_ctx *ctx, const float *x, uint32_t n, const float *gam
  * The first call on a device resolves the array's device address
  * (cudaGetSymbolAddress); make that first call before starting a stream capture.
  * All calls share the one array and it keeps the last call's contents (the
- * counters and the error word are cleared at the start of every call): two calls
+ * counters and the error word are cleared at the start of every call; the
+ * tagged partial sums are left all-zero by a kernel that ran to its end and are
+ * cleared again after any call that was not seen to end cleanly): two calls
  * whose kernels overlap on the GPU, on different streams or contexts of the
  * same device, race.  Results are identical to apk_matvec's. */
 #define APK_NOALLOC_MAX_N_IN 32768u
