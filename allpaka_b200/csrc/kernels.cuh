@@ -273,6 +273,13 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
 }
 __device__ __forceinline__ void consumer_bar() { asm volatile("bar.sync 1, %0;" ::"n"(N_CONSUMERS) : "memory"); }
 __device__ __forceinline__ void finisher_bar() { asm volatile("bar.sync 2, %0;" ::"n"(N_FINISHERS) : "memory"); }
+// The threads that close a tile together: the finisher warps (barrier 2), joined for a CTA's
+// last tile by the consumer warps, which have nothing left to do by then (barrier 3).
+struct Crew {
+    int t, n, bar;  // this thread's index in the crew, crew size, named barrier
+    __device__ __forceinline__ void sync() const { asm volatile("bar.sync %0, %1;" ::"r"(bar), "r"(n) : "memory"); }
+};
+constexpr int N_CREW_ALL = N_FINISHERS + N_CONSUMERS;
 
 // D[16 rows x 8 cols] = A[16 x 32] . B[32 x 8], int8 operands, int32 result: one
 // 32-element quantisation block of 16 weight rows against up to 8 activation rows.
@@ -746,8 +753,8 @@ struct UnitOrder {
 };
 
 template <int M>
-__device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float *out /*[M][128] smem*/,
-                                              int tid, const float *pre, const float *rope_pre);
+__device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw, int tile, float *out /*[M][128] smem*/,
+                                              const float *pre, const float *rope_pre);
 constexpr int EPI_PRE = 2;  // residual values a finisher thread fetches ahead of the EPI_ADD epilogue
 
 // In-CTA activation prologue (PRO_QUANT): the consumer threads turn one row
@@ -1052,69 +1059,41 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         return;
     }
 
-    if (warp > N_CONSUMER_WARPS) {
-        // ------------------------------------------------------- finishers
-        // Take each tile (or tile piece) the consumers leave in red, and close it: add the
-        // four K-quarters; for a tile shared with other CTAs publish the partial sum, count
-        // arrivals, and if this CTA is the last to arrive add all pieces in CTA order; run
-        // the epilogue.  None of this stalls the consumers, who are already on the next tile.
-        const int ftid = tid - (N_CONSUMERS + 32);
-        float *fin = reinterpret_cast<float *>(smem + MvSmem<M>::FIN_OFF);
-        int *slot_tab = reinterpret_cast<int *>(smem + MvSmem<M>::SLOT_OFF);
-        const int my_first_tile = (int)(order.u_begin / (uint32_t)p.KS);
-        // The RoPE table comes from the host, not from the previous kernel: the sin/cos pairs
-        // lane, lane+32 of the first token this warp rotates are fetched before any tile is due.
-        float rope_pre[4] = {0.f, 0.f, 0.f, 0.f};
-        const bool has_rope_pre = p.epi == EPI_QKV_ROPE && (p.half == 32 || p.half == 64) && (ftid >> 5) < p.m_out;
-        if (has_rope_pre) {
-            const float *tab = p.rope + (size_t)(ftid >> 5) * p.half * 2;
-            const int l = ftid & 31;
-            rope_pre[0] = tab[2 * l];
-            rope_pre[1] = tab[2 * l + 1];
-            if (l + 32 < p.half) {
-                rope_pre[2] = tab[2 * (l + 32)];
-                rope_pre[3] = tab[2 * (l + 32) + 1];
-            }
-        }
-        for (uint32_t n = 0;; ++n) {
-            // one thread waits (bounded) and tells the others, so all of them leave together
-            if (ftid == 0) {
-                const bool ok = mbar_wait_bounded(red_full, n & 1u);
-                if (!ok) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
-                s_flags[2] = ok ? 1 : 0;
-            }
-            finisher_bar();
-            if (s_flags[2] == 0) break;
-            const int t_cur = s_flags[0];
-            const bool final_tile = s_flags[1] != 0;
+    // Close one tile (or tile piece) that the consumers left in red: add the K-quarters; for a tile
+    // shared with other CTAs publish the partial sum, or - in the CTA that holds the tile's last
+    // units - collect the others' and add them in CTA order; run the epilogue.
+    float *fin = reinterpret_cast<float *>(smem + MvSmem<M>::FIN_OFF);
+    int *slot_tab = reinterpret_cast<int *>(smem + MvSmem<M>::SLOT_OFF);
+    const int my_first_tile = (int)(order.u_begin / (uint32_t)p.KS);
+    auto close_tile = [&](const Crew &cw, int t_cur, bool final_tile, const float *rope_pre) {
             // Two-level activations: the consumers merged the digit pairs, everything sits in the
             // even rows; from here on the tile has one row per token.
             const int R = p.two_level ? M / 2 : M;
             const int RN = R * TILE_ROWS;
-            for (int i = ftid; i < RN; i += N_FINISHERS) {
+            for (int i = cw.t; i < RN; i += cw.n) {
                 const int src = p.two_level ? 2 * (i / TILE_ROWS) * TILE_ROWS + i % TILE_ROWS : i;
                 float v = red[src] + red[M * TILE_ROWS + src];
                 if (KQ == 4) v += red[2 * M * TILE_ROWS + src] + red[3 * M * TILE_ROWS + src];
                 fin[i] = v;
             }
-            finisher_bar();  // red and the flags have been read
-            if (ftid == 0) mbar_arrive(red_empty);
+            cw.sync();  // red and the flags have been read
+            if (cw.t == 0) mbar_arrive(red_empty);
             const uint32_t ua = (uint32_t)t_cur * (uint32_t)p.KS, ub = ua + (uint32_t)p.KS - 1;
             const int c_first = (int)(((ua + 1) * G - 1) / U), c_last = (int)(((ub + 1) * G - 1) / U);
             if (c_first != c_last && (int)blockIdx.x != c_last) {
                 // a piece of a tile that a later CTA closes: publish and move on
                 unsigned long long *slot =
                     p.partials + ((size_t)blockIdx.x * 2 + (my_first_tile == t_cur ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
-                for (int i = ftid; i < RN; i += N_FINISHERS) part_store(&slot[i], fin[i]);
+                for (int i = cw.t; i < RN; i += cw.n) part_store(&slot[i], fin[i]);
             } else {
                 // EPI_ADD: the residual is known since the dependency resolved; fetch it now so
                 // that its round trip overlaps the wait for the other pieces
                 float pre[EPI_PRE];
-                const bool use_pre = p.epi == EPI_ADD && RN <= EPI_PRE * N_FINISHERS;
+                const bool use_pre = p.epi == EPI_ADD && RN <= EPI_PRE * cw.n;
                 if (use_pre) {
 #pragma unroll
                     for (int j = 0; j < EPI_PRE; ++j) {
-                        const int i = ftid + j * N_FINISHERS;
+                        const int i = cw.t + j * cw.n;
                         const int m = i / TILE_ROWS, row = t_cur * TILE_ROWS + i % TILE_ROWS;
                         pre[j] = (i < RN && row < p.n_out) ? p.resid[(size_t)m * p.ldr + row] : 0.0f;
                     }
@@ -1125,17 +1104,17 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     // than this one) in CTA order, then its own.  Where each left its piece:
                     // head piece -> slot 0, else slot 1.
                     const int nparts = c_last - c_first;
-                    for (int k = ftid; k < nparts; k += N_FINISHERS) {
+                    for (int k = cw.t; k < nparts; k += cw.n) {
                         const int c = c_first + k;
                         const int cf = (int)(((uint32_t)c * U / G) / (uint32_t)p.KS);
                         slot_tab[k] = (c * 2 + (cf == t_cur ? 0 : 1)) * (MAX_M_EFF * TILE_ROWS);
                     }
-                    finisher_bar();
+                    cw.sync();
                     const long long t_wait = clock64();
                     bool gave_up = false;
-                    for (int i = ftid; i < RN; i += 2 * N_FINISHERS) {
+                    for (int i = cw.t; i < RN; i += 2 * cw.n) {
                         // two elements x eight pieces per round trip; poll until every tag is there (bounded)
-                        const int i2 = i + N_FINISHERS;
+                        const int i2 = i + cw.n;
                         const bool two = i2 < RN;
                         float v = 0.0f, v2 = 0.0f;
                         for (int k0 = 0; k0 < nparts; k0 += 8) {
@@ -1167,13 +1146,52 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                         if (two) fin[i2] = v2 + fin[i2];
                     }
                     if (gave_up) atomicExch(p.err, ERRW_FINISHER_TIMEOUT);
-                    finisher_bar();
+                    cw.sync();
                 }
-                if (tl && ftid == 0 && final_tile && p.pro != PRO_QUANT) tl[7] = globaltimer_ns();  // pieces added
-                epilogue_tile<M>(p, t_cur, fin, ftid, use_pre ? pre : nullptr, has_rope_pre ? rope_pre : nullptr);
+                if (tl && cw.t == 0 && final_tile && p.pro != PRO_QUANT) tl[7] = globaltimer_ns();  // pieces added
+                epilogue_tile<M>(p, cw, t_cur, fin, use_pre ? pre : nullptr, rope_pre);
             }
-            finisher_bar();  // fin, the slot table and the flags are reused by the next tile
+    };
+
+    if (warp > N_CONSUMER_WARPS) {
+        // ------------------------------------------------------- finishers
+        // Take each tile (or tile piece) the consumers leave in red, and close it: add the
+        // four K-quarters; for a tile shared with other CTAs publish the partial sum, count
+        // arrivals, and if this CTA is the last to arrive add all pieces in CTA order; run
+        // the epilogue.  None of this stalls the consumers, who are already on the next tile.
+        const int ftid = tid - (N_CONSUMERS + 32);
+        // The RoPE table comes from the host, not from the previous kernel: the sin/cos pairs
+        // lane, lane+32 of the first token this warp rotates are fetched before any tile is due.
+        float rope_pre[4] = {0.f, 0.f, 0.f, 0.f};
+        const bool has_rope_pre = p.epi == EPI_QKV_ROPE && (p.half == 32 || p.half == 64) && (ftid >> 5) < p.m_out;
+        if (has_rope_pre) {
+            const float *tab = p.rope + (size_t)(ftid >> 5) * p.half * 2;
+            const int l = ftid & 31;
+            rope_pre[0] = tab[2 * l];
+            rope_pre[1] = tab[2 * l + 1];
+            if (l + 32 < p.half) {
+                rope_pre[2] = tab[2 * (l + 32)];
+                rope_pre[3] = tab[2 * (l + 32) + 1];
+            }
+        }
+        for (uint32_t n = 0;; ++n) {
+            // one thread waits (bounded) and tells the others, so all of them leave together
+            if (ftid == 0) {
+                const bool ok = mbar_wait_bounded(red_full, n & 1u);
+                if (!ok) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
+                s_flags[2] = ok ? 1 : 0;
+            }
+            finisher_bar();
+            // (after an expired wait the error word is set and the walk goes on: every wait in
+            // this kernel is bounded, and leaving here would strand the consumers at the barrier
+            // they share with the finishers for the last tile)
+            const int t_cur = s_flags[0];
+            const bool final_tile = s_flags[1] != 0;
+            Crew cw{ftid, final_tile ? N_CREW_ALL : N_FINISHERS, final_tile ? 3 : 2};
+            if (final_tile) cw.sync();  // the consumers join for the CTA's last tile
+            close_tile(cw, t_cur, final_tile, has_rope_pre ? rope_pre : nullptr);
             if (final_tile) break;
+            finisher_bar();  // fin, the slot table and the flags are reused by the next tile
         }
         if (tl && ftid == 0) tl[5] = globaltimer_ns();  // the last tile done
         return;
@@ -1246,6 +1264,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     int s = 0;
     uint32_t ph = 0;
     uint32_t n_handoff = 0;  // tiles (or tile pieces) passed to the finishers so far
+    int t_last = 0;          // the tile of the last hand-off
     for (int it = 0; it < n_total; ++it) {
         // where the next unit lies (decides whether this one closes its tile)
         int t_next = t, ks_next = ks + 1;
@@ -1632,20 +1651,28 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         __syncwarp();
         if (lane == 0) mbar_arrive(red_full);
         ++n_handoff;
+        t_last = t_cur;
+    }
+    // Nothing left to stream: help the finishers close this CTA's last tile.
+    {
+        const Crew cw{N_FINISHERS + tid, N_CREW_ALL, 3};
+        cw.sync();
+        close_tile(cw, t_last, true, nullptr);
     }
 }
 
 // tile result out[m][r] (m < M rows of the activation record) -> global.
-// Called by all finisher threads (tid = index among them).
+// Called by all threads of the crew that closes the tile.
 template <int M>
-__device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float *out, int tid, const float *pre,
+__device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw, int tile, float *out, const float *pre,
                                               const float *rope_pre) {
+    const int tid = cw.t;
     const int MO = p.m_out;
     // one row per token (the digit pairs of two-level activations are merged by now)
     auto val = [&](int m, int r) -> float { return out[m * TILE_ROWS + r]; };
     const int row0 = tile * TILE_ROWS;
     if (p.epi == EPI_STORE || p.epi == EPI_ADD) {
-        for (int i = tid, j = 0; i < MO * TILE_ROWS; i += N_FINISHERS, ++j) {
+        for (int i = tid, j = 0; i < MO * TILE_ROWS; i += cw.n, ++j) {
             const int m = i / TILE_ROWS, r = i % TILE_ROWS;
             const int row = row0 + r;
             if (row >= p.n_out) continue;
@@ -1659,7 +1686,7 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
         // the exchange in flight is epoch + 1 (the epoch word only moves between kernels)
         const uint32_t parity = (__ldcg(xch_epoch(p.xch.slots[p.xch.rank])) + 1u) & 1u;
         const size_t slot = ((size_t)parity * XCH_MAX_RANKS + p.xch.rank) * XCH_ROW_FLOATS;
-        for (int i = tid; i < MO * TILE_ROWS; i += N_FINISHERS) {
+        for (int i = tid; i < MO * TILE_ROWS; i += cw.n) {
             const int m = i / TILE_ROWS, r = i % TILE_ROWS;
             const int row = row0 + r;
             if (row >= p.n_out) continue;
@@ -1678,7 +1705,7 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
         const int warp = tid >> 5, lane = tid & 31;
         const float *nw = tile < p.n_q_tiles ? p.q_norm : (tile < p.n_q_tiles + p.n_k_tiles ? p.k_norm : nullptr);
         const bool rot = tile < p.n_q_tiles + p.n_k_tiles;
-        for (int m = warp; m < MO; m += N_FINISH_WARPS) {
+        for (int m = warp; m < MO; m += (cw.n >> 5)) {
             float v[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) v[j] = val(m, lane + 32 * j);
@@ -1736,8 +1763,8 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
         // identity attention core: the roped Q head is what the output projection consumes.
         // One warp per (token, 32-element block): the four blocks of a head go in parallel.
         if (p.q_next.base && tile < p.n_q_tiles) {
-            finisher_bar();
-            for (int w = warp; w < MO * 4; w += N_FINISH_WARPS) {
+            cw.sync();
+            for (int w = warp; w < MO * 4; w += (cw.n >> 5)) {
                 const int m = w >> 2, j = w & 3;
                 const float *hs = out + m * TILE_ROWS;
                 quantize_store(p.q_next, p.q_next_two_level, p.q_next_need_sum, m, tile * 4 + j, lane, hs[lane + 32 * j]);
@@ -1749,7 +1776,7 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, int tile, float
         // rows 0..63 = gate rows [64*tile, 64*tile+64), rows 64..127 = the matching up rows.
         // Work item = (token, 32-row half) = one activation block of the down projection.
         const int warp = tid >> 5, lane = tid & 31;
-        for (int w = warp; w < MO * 2; w += N_FINISH_WARPS) {
+        for (int w = warp; w < MO * 2; w += (cw.n >> 5)) {
             const int m = w >> 1, h = w & 1;
             const int r = h * 32 + lane;
             const float g = val(m, r), uu = val(m, 64 + r);
