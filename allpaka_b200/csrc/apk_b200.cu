@@ -160,14 +160,14 @@ struct Plan {
     std::vector<PlanLayer> L;
     DevMatrix *head = nullptr;
     const float *out_norm = nullptr;
-    DevBuf norms, xin, x[2], qkv, yp, act_h, act_q, act_d, logits, logits_all, amax, rope;
+    DevBuf norms, xin, x[2], qkv, yp, act_h, act_q, act_d, logits, logits_all, amax, rope, sumsq;
     cudaGraphExec_t exec[APK_MAX_M + 1][2] = {};  // [m][argmax]
     int launches[APK_MAX_M + 1][2] = {};
     ~Plan() {
         for (auto &row : exec)
             for (auto &e : row)
                 if (e) cudaGraphExecDestroy(e);
-        for (DevBuf *b : {&norms, &xin, &x[0], &x[1], &qkv, &yp, &act_h, &act_q, &act_d, &logits, &logits_all, &amax, &rope})
+        for (DevBuf *b : {&norms, &xin, &x[0], &x[1], &qkv, &yp, &act_h, &act_q, &act_d, &logits, &logits_all, &amax, &rope, &sumsq})
             b->release();
     }
 };
@@ -192,6 +192,7 @@ struct apk_ctx {
     uint32_t trace_idx = 0, trace_cap = 0;
     apk_stats_t st{};
     int rank = 0, world = 1;
+    int fuse_norm = 1;          // residual epilogue quantises for the next RMSNorm: 0 never, 1 always, 2 only for m > 1 (ALLPAKA_B200_FUSE_NORM)
     bool use_pdl = true;        // ALLPAKA_B200_PDL=0 turns programmatic dependent launch off
     void *comm = nullptr;
     std::unique_ptr<Plan> plan;
@@ -689,6 +690,7 @@ int apk_init(apk_ctx **out, int device) {
     APK_TRY(c->counters.ensure(65536 * sizeof(int), true));
     APK_TRY(init_kernel_attrs(c.get()));
     if (const char *e = getenv("ALLPAKA_B200_PDL")) c->use_pdl = atoi(e) != 0;
+    if (const char *e = getenv("ALLPAKA_B200_FUSE_NORM")) c->fuse_norm = atoi(e);
     if (const char *e = getenv("ALLPAKA_B200_INFLIGHT")) c->inflight = std::max(1, std::min(atoi(e), MAX_STAGES));
     if (const char *e = getenv("ALLPAKA_B200_INFLIGHT_PRE")) c->inflight_pre = std::max(1, std::min(atoi(e), MAX_STAGES));
     *out = c.release();

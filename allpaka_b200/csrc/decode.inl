@@ -147,6 +147,7 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
     if (c->world > 1) APK_TRY(P->logits_all.ensure((size_t)M * P->vocab * 4));
     APK_TRY(P->amax.ensure(M * sizeof(uint32_t)));
     APK_TRY(P->rope.ensure((size_t)M * (r->rot_dim / 2 + 1) * 2 * 4));
+    APK_TRY(P->sumsq.ensure((size_t)M * (H / 32 + 1) * sizeof(double), true));
     c->plan = std::move(P);
     return APK_OK;
 }
@@ -160,12 +161,30 @@ struct TokenLaunch {
     ActMode q8, autom;
     int cur = 0;
     bool pending_add = false;  // tensor parallel: yp holds a combined delta not yet added to x
+    // the previous residual matvec already quantised x * gamma for this (matrix, mode): its
+    // records sit in act_h and only lack the row-wide RMSNorm scale
+    const DevMatrix *prenormed_for = nullptr;
+    int prenormed_m_eff = 0;
 
     TokenLaunch(apk_ctx *c_, Plan *P_, uint32_t m_) : c(c_), P(P_), m(m_), q8{0, (int)m_}, autom(resolve_mode(APK_ACT_AUTO, m_)) {}
 
     // activations of a matvec that reads the residual stream through an RMSNorm
+    // Can the residual epilogue in front of matvec W (through an RMSNorm) do the quantisation?
+    bool can_prenorm(const DevMatrix *W, ActMode mode) const {
+        const bool on = c->fuse_norm == 1 || (c->fuse_norm == 2 && m > 1);
+        return on && c->world == 1 && P->hidden % 32 == 0 && want_resident(c, W, mode.m_eff);
+    }
     int normed_input(const DevMatrix *W, const float *gamma, ActMode mode, MvParams *p, bool advance) {
         const uint32_t H = P->hidden;
+        if (prenormed_for == W && prenormed_m_eff == mode.m_eff) {
+            p->act = act_layout(P->act_h.p, W->ty, mode.m_eff);
+            p->pro = PRO_LOAD;
+            p->norm_sumsq = P->sumsq.as<double>();
+            p->norm_blocks = (int)(H / 32);
+            p->norm_eps = P->eps;
+            if (advance) prenormed_for = nullptr;
+            return APK_OK;
+        }
         float *xc = P->x[cur].as<float>();
         if (pending_add) {
             float *xn = P->x[cur ^ 1].as<float>();
@@ -194,7 +213,9 @@ struct TokenLaunch {
         p.q_next_need_sum = L.wo->ty == APK_TY_Q4_K;
         return launch_matvec(c, L.qkv, p, q8);
     }
-    int residual(DevMatrix *W, void *records) {
+    // next_*: the matvec that will read the updated rows through an RMSNorm (null: none)
+    int residual(DevMatrix *W, void *records, const DevMatrix *next_W = nullptr, const float *next_gamma = nullptr,
+                 ActMode next_mode = ActMode{0, 1}) {
         const uint32_t H = P->hidden;
         MvParams p{};
         use_records(c, W, autom, records, &p);
@@ -231,9 +252,18 @@ struct TokenLaunch {
         p.ldy = (int)H;
         p.resid = P->x[cur].as<float>();
         p.ldr = (int)H;
+        if (next_W && can_prenorm(next_W, next_mode)) {
+            p.nq_gamma = next_gamma;
+            p.nq_act = act_layout(P->act_h.p, next_W->ty, next_mode.m_eff);
+            p.nq_two_level = next_mode.two_level;
+            p.nq_need_sum = next_W->ty == APK_TY_Q4_K;
+            p.nq_sumsq = P->sumsq.as<double>();
+            prenormed_for = next_W;
+            prenormed_m_eff = next_mode.m_eff;
+        }
         return launch_matvec(c, W, p, autom);
     }
-    int wo(PlanLayer &L) { return residual(L.wo, P->act_q.p); }
+    int wo(PlanLayer &L) { return residual(L.wo, P->act_q.p, L.gateup, L.ffn_norm, q8); }
     int gateup(PlanLayer &L, bool advance = true) {
         MvParams p{};
         APK_TRY(normed_input(L.gateup, L.ffn_norm, q8, &p, advance));
@@ -244,7 +274,11 @@ struct TokenLaunch {
         p.ffn = (int)P->ffn_l;
         return launch_matvec(c, L.gateup, p, q8);
     }
-    int down(PlanLayer &L) { return residual(L.down, P->act_d.p); }
+    // after down comes the next layer's Q|K|V, or the output head
+    int down(PlanLayer &L, PlanLayer *next) {
+        if (next) return residual(L.down, P->act_d.p, next->qkv, next->attn_norm, q8);
+        return residual(L.down, P->act_d.p, P->head, P->out_norm, autom);
+    }
     int head(bool advance = true) {
         // finish_hidden: rmsnorm + output.matmul(x, m) (QuantMat::matmul: Q8 at m == 1, f32 dots above)
         MvParams p{};
@@ -266,7 +300,7 @@ int enqueue_token(apk_ctx *c, Plan *P, uint32_t m, int argmax, int *n_launches) 
         APK_TRY(T.qkv(L));
         APK_TRY(T.wo(L));
         APK_TRY(T.gateup(L));
-        APK_TRY(T.down(L));
+        APK_TRY(T.down(L, l + 1 < P->n_layers ? &P->L[l + 1] : nullptr));
     }
     APK_TRY(T.head());
     const float *lg = P->logits.as<float>();
@@ -383,10 +417,17 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
             for (uint32_t l = 0; l < n_launch; ++l) {
                 PlanLayer &L = P->L[l];
                 TokenLaunch T(c, P, m);  // fresh state: reads x[0], never flips buffers
+                // the launch variants of the real token: inputs that a residual epilogue prepared
+                const DevMatrix *nw = kind == 0 ? L.qkv : kind == 2 ? L.gateup : kind == 4 ? P->head : nullptr;
+                const ActMode nm = kind == 4 ? T.autom : T.q8;
+                if (nw && T.can_prenorm(nw, nm)) {
+                    T.prenormed_for = nw;
+                    T.prenormed_m_eff = nm.m_eff;
+                }
                 if (kind == 0) APK_TRY(T.qkv(L, false));
                 else if (kind == 1) APK_TRY(T.wo(L));
                 else if (kind == 2) APK_TRY(T.gateup(L, false));
-                else if (kind == 3) APK_TRY(T.down(L));
+                else if (kind == 3) APK_TRY(T.down(L, l + 1 < P->n_layers ? &P->L[l + 1] : nullptr));
                 else APK_TRY(T.head(false));
             }
         CUDA_TRY(cudaEventRecord(c->ev1, c->stream));

@@ -168,6 +168,18 @@ struct MvParams {
     ActLayout act_next;                // optional packed activations for the down projection
     int next_two_level, next_need_sum;
     int ffn;                           // real ffn rows (gate rows)
+    // EPI_ADD, optional: the updated residual rows feed an RMSNorm and a matvec next.  Each tile
+    // quantises its 128 elements times the norm weight right away (codes do not depend on the
+    // row-wide scale, scales are linear in it) and leaves the f64 sums of squares of its four
+    // blocks; the next kernel multiplies the block scales by 1/sqrt(mean + eps) (norm_sumsq).
+    const float *nq_gamma;             // [n_out] weight of the next norm; null = off
+    ActLayout nq_act;                  // the next matvec's activation records
+    int nq_two_level, nq_need_sum;
+    double *nq_sumsq;                  // [m_out][n_out / 32]
+    // PRO_LOAD, optional: records prepared that way by the previous kernel
+    const double *norm_sumsq;          // [m_out][norm_blocks]; null = records are final
+    int norm_blocks;                   // 32-element blocks per row
+    float norm_eps;
 };
 
 // ------------------------------------------------------------------ PTX glue
@@ -1239,9 +1251,39 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 bulk_g2s(res + o, p.act.base + o, min(32768u, bytes - o), acts_bar, pol_a);
         }
     }
+    float *s_scale = red;  // [m_out] row scales of the block below; red is free until the first tile closes
+    if (p.pro == PRO_LOAD && p.norm_sumsq) {
+        // Records quantised before the row-wide RMSNorm scale was known: finish them.  Warp w
+        // adds the per-block sums of squares of token w (fixed order), ops::rmsnorm_into's
+        // f64 1/sqrt(mean + eps) (ops/norm.rs:193-198); below, every block scale and block sum
+        // of that token's rows is multiplied by it.
+        for (int tok = warp; tok < p.m_out; tok += N_CONSUMER_WARPS) {
+            double ss = 0.0;
+            for (int i = lane; i < p.norm_blocks; i += 32) ss += p.norm_sumsq[(size_t)tok * p.norm_blocks + i];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) s_scale[tok] = (float)(1.0 / sqrt(ss / (double)(p.norm_blocks * 32) + (double)p.norm_eps));
+        }
+    }
     if (p.pro != PRO_STREAM && !mbar_wait_bounded(acts_bar, 0u)) {
         aborted = true;
         if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
+    }
+    if (p.pro == PRO_LOAD && p.norm_sumsq) {
+        consumer_bar();
+        const int kt_r = p.act.kt(), mp_r = p.act.mp(), qb_r = p.act.q_bytes();
+        const int per_rec = kt_r * mp_r;
+        for (int i = tid; i < p.KS * per_rec; i += N_CONSUMERS) {
+            const int ksr = i / per_rec, e = i - ksr * per_rec;
+            const int row = e % mp_r;
+            if (row < M) {
+                float *d = reinterpret_cast<float *>(res + (size_t)ksr * act_rec + qb_r);
+                const float sc = s_scale[p.two_level ? row >> 1 : row];
+                d[e] = __fmul_rn(d[e], sc);
+                d[per_rec + e] = __fmul_rn(d[per_rec + e], sc);
+            }
+        }
+        consumer_bar();
     }
     if (p.pro == PRO_QUANT) {
         if (tl && tid == 0) tl[4] = globaltimer_ns();  // raw row landed
@@ -1679,6 +1721,25 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw,
             float v = val(m, r);
             if (p.epi == EPI_ADD) v = __fadd_rn(pre ? pre[j] : p.resid[(size_t)m * p.ldr + row], v);
             p.y[(size_t)m * p.ldy + row] = v;
+            if (p.nq_gamma) out[i] = v;
+        }
+        if (p.epi == EPI_ADD && p.nq_gamma) {
+            // the next norm + quantisation, as far as this tile can take it (see MvParams)
+            cw.sync();
+            const int warp = tid >> 5, lane = tid & 31;
+            const int nblk = p.n_out >> 5;
+            for (int w = warp; w < MO * 4; w += (cw.n >> 5)) {
+                const int m = w >> 2, jb = w & 3;
+                const int row = row0 + 32 * jb + lane;
+                if (row0 + 32 * jb >= p.n_out) continue;
+                const float v = out[m * TILE_ROWS + 32 * jb + lane];
+                const float gam = p.nq_gamma[row];
+                double ss = (double)v * (double)v;
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) p.nq_sumsq[(size_t)m * nblk + (row >> 5)] = ss;
+                quantize_store(p.nq_act, p.nq_two_level, p.nq_need_sum, m, row >> 5, lane, __fmul_rn(v, gam));
+            }
         }
         return;
     }
