@@ -766,7 +766,7 @@ struct UnitOrder {
 
 template <int M>
 __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw, int tile, float *out /*[M][128] smem*/,
-                                              const float *pre, const float *rope_pre);
+                                              const float *pre, const float *rope_pre, float gam_pre);
 constexpr int EPI_PRE = 2;  // residual values a finisher thread fetches ahead of the EPI_ADD epilogue
 
 // In-CTA activation prologue (PRO_QUANT): the consumer threads turn one row
@@ -1110,6 +1110,13 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                         pre[j] = (i < RN && row < p.n_out) ? p.resid[(size_t)m * p.ldr + row] : 0.0f;
                     }
                 }
+                // likewise the weight of the next norm for the first block this warp will quantise
+                float gam_pre = 0.0f;
+                if (p.epi == EPI_ADD && p.nq_gamma) {
+                    const int w = cw.t >> 5;
+                    const int row = t_cur * TILE_ROWS + 32 * (w & 3) + (cw.t & 31);
+                    if (w < R * 4 && row < p.n_out) gam_pre = p.nq_gamma[row];
+                }
                 if (c_first != c_last) {
                     // This CTA holds the last units of the tile: it adds the pieces of CTAs
                     // c_first .. c_last-1 (lower block indices, so they were scheduled no later
@@ -1161,7 +1168,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     cw.sync();
                 }
                 if (tl && cw.t == 0 && final_tile && p.pro != PRO_QUANT) tl[7] = globaltimer_ns();  // pieces added
-                epilogue_tile<M>(p, cw, t_cur, fin, use_pre ? pre : nullptr, rope_pre);
+                epilogue_tile<M>(p, cw, t_cur, fin, use_pre ? pre : nullptr, rope_pre, gam_pre);
             }
     };
 
@@ -1707,7 +1714,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
 // Called by all threads of the crew that closes the tile.
 template <int M>
 __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw, int tile, float *out, const float *pre,
-                                              const float *rope_pre) {
+                                              const float *rope_pre, float gam_pre) {
     const int tid = cw.t;
     const int MO = p.m_out;
     // one row per token (the digit pairs of two-level activations are merged by now)
@@ -1733,7 +1740,7 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw,
                 const int row = row0 + 32 * jb + lane;
                 if (row0 + 32 * jb >= p.n_out) continue;
                 const float v = out[m * TILE_ROWS + 32 * jb + lane];
-                const float gam = p.nq_gamma[row];
+                const float gam = w == warp ? gam_pre : p.nq_gamma[row];
                 double ss = (double)v * (double)v;
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
