@@ -211,7 +211,7 @@ int apk_debug_q8_acts(apk_ctx *ctx, const float *x, uint32_t n, const float *gam
  * memory was budgeted and handed out at start-up (a late allocation would
  * simply fail), or the call sits in a latency-bounded decode loop where the
  * device-wide stall of an allocation is not acceptable.  They own x and y already; the kernel's
- * private scratch (stream-K partial sums, tile arrival counters, error word,
+ * private scratch (stream-K partial sums, error word,
  * quantised-activation records) lives in a fixed ~5.9 MB array inside the
  * library's device image, which every GPU that loads the library holds until
  * the process exits.
