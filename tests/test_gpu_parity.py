@@ -295,6 +295,41 @@ def test_decode_token_tiles_shared_by_many_ctas(gpu, orc, ty, m):
     gpu.detach(r.buf)
 
 
+@pytest.mark.parametrize("ty,m", [(Q8_0, 1), (Q8_0, 5), (Q4_K, 2)])
+def test_next_norm_started_by_the_residual_epilogue_changes_nothing(orc, ty, m, monkeypatch):
+    """The RMSNorm input of Q|K|V, gate/up and the head is quantised either by the residual epilogue
+    in front of it (default) or in the kernel's own prologue / a separate pass: same logits."""
+    from allpaka_b200 import gpu as G
+
+    out = []
+    for fuse in ("1", "0"):
+        monkeypatch.setenv("ALLPAKA_B200_FUSE_NORM", fuse)
+        g = G.Gpu(0)
+        req, layers, head, out_norm, x, rope, r = build_token(g, orc, ty, 2, 1024, 8, 2, 2048, 1536, m, True, 800)
+        out.append(g.decode_token_checked(req))
+        if fuse == "1":
+            xo = oracle_decode(orc, ty, layers, 1024, 8 * 128, 2 * 128, 128, 2048, 1e-6, rope, x, m)
+            want = oracle_logits(orc, ty, head, 1536, 1024, xo, out_norm, 1e-6, m)
+            assert rel_l2(out[0], want) <= TOL, rel_l2(out[0], want)
+        g.detach(r.buf)
+        g.close()
+    assert rel_l2(out[0], out[1]) <= 1e-4, rel_l2(out[0], out[1])
+
+
+def test_token_timeline_is_ordered(gpu, orc):
+    """Trace entry point: one slab of stamps per matvec launch, entry <= dependency <= last tile closed."""
+    req, layers, head, out_norm, x, rope, r = build_token(gpu, orc, Q8_0, 2, 512, 4, 2, 1024, 1000, 1, False, 900)
+    st = gpu.debug_token_timeline(req, 16).astype(np.int64)
+    assert st.shape[0] == 2 * 4 + 1 and st.shape[2] == 8
+    for slab in st:
+        live = slab[slab[:, 0] > 0]
+        assert len(live) > 0
+        assert np.all(live[:, 2] >= live[:, 0]) and np.all(live[:, 5] >= live[:, 2])
+    ends = [slab[:, 5].max() for slab in st]
+    assert all(b > a for a, b in zip(ends, ends[1:]))  # launches finish in issue order
+    gpu.detach(r.buf)
+
+
 def test_decode_token_declines_what_it_does_not_build(gpu, orc):
     from allpaka_b200.gpu import DecodeDecline
 
