@@ -143,6 +143,8 @@ Nccl g_nccl;
 constexpr int NCCL_FLOAT32 = 7;  // ncclFloat32
 constexpr int NCCL_SUM = 0;      // ncclSum
 
+struct RecMeta { int ke, m_eff, two_level, launch; };
+
 struct PlanLayer {
     DevMatrix *qkv = nullptr, *wo = nullptr, *gateup = nullptr, *down = nullptr;
     const float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;  // device
@@ -153,6 +155,7 @@ struct Plan {
     const apk_token_layer *layers_key = nullptr;
     uint32_t n_layers = 0;
     const void *output_key = nullptr;
+    uint64_t desc_hash = 0;  // every layer's descriptors (weight and norm pointers, types, row counts)
     uint32_t hidden = 0, head_dim = 0, n_heads = 0, n_kv_heads = 0, rot_dim = 0, vocab = 0, ffn = 0;
     float eps = 0;
     // local (per-rank) shapes
@@ -160,14 +163,14 @@ struct Plan {
     std::vector<PlanLayer> L;
     DevMatrix *head = nullptr;
     const float *out_norm = nullptr;
-    DevBuf norms, xin, x[2], qkv, yp, act_h, act_q, act_d, logits, logits_all, amax, rope, sumsq;
+    DevBuf norms, xin, x[2], qkv, yp, act_h, act_q, act_d, logits, logits_all, amax, rope, sumsq, hidden_out;
     cudaGraphExec_t exec[APK_MAX_M + 1][2] = {};  // [m][argmax]
     int launches[APK_MAX_M + 1][2] = {};
     ~Plan() {
         for (auto &row : exec)
             for (auto &e : row)
                 if (e) cudaGraphExecDestroy(e);
-        for (DevBuf *b : {&norms, &xin, &x[0], &x[1], &qkv, &yp, &act_h, &act_q, &act_d, &logits, &logits_all, &amax, &rope, &sumsq})
+        for (DevBuf *b : {&norms, &xin, &x[0], &x[1], &qkv, &yp, &act_h, &act_q, &act_d, &logits, &logits_all, &amax, &rope, &sumsq, &hidden_out})
             b->release();
     }
 };
@@ -184,7 +187,7 @@ struct apk_ctx {
     std::map<std::pair<const uint8_t *, size_t>, int> attached;  // (base,len) -> refcount
     std::map<MatKey, std::unique_ptr<DevMatrix>> mats;
     DevBuf staging;             // raw GGUF rows on their way to the repack
-    DevBuf partials, counters;  // stream-K fix-up scratch
+    DevBuf partials;            // stream-K fix-up scratch
     int *d_err = nullptr;       // device error word
     int *h_err = nullptr;       // pinned mirror
     DevBuf x_dev, y_dev, act_a, act_b, misc, dump;
@@ -192,17 +195,32 @@ struct apk_ctx {
     uint32_t trace_idx = 0, trace_cap = 0;
     apk_stats_t st{};
     int rank = 0, world = 1;
-    int fuse_norm = 1;          // residual epilogue quantises for the next RMSNorm: 0 never, 1 always, 2 only for m > 1 (ALLPAKA_B200_FUSE_NORM)
+    // How a residual matvec (wo, down) helps the RMSNorm that reads its result (ALLPAKA_B200_FUSE_NORM):
+    //  0 nothing; 1 (default) it leaves the per-block sums of squares, the reader still quantises
+    //  f32(f64(x)*scale)*gamma itself (exact); 2 it also quantises x*gamma per tile and the reader only
+    //  applies the row scale (cheaper; codes may differ by one at a .5 boundary); 3 like 2 for m > 1, like 1 at m = 1
+    int fuse_norm = 1;
+    long long wait_limit = WAIT_LIMIT_DEFAULT;  // cycle budget of the bounded device-side waits (apk_debug_set_wait_limit)
+    int next_units = 6;          // units of the next matvec a CTA pulls into L2 while it closes its last tile (ALLPAKA_B200_NEXT_PREFETCH)
+    int next_pace = 600;         // ns between two of those (ALLPAKA_B200_NEXT_PACE)
+    bool self_xch = false;       // ALLPAKA_B200_SELF_XCH=1: a single rank runs the peer-exchange path on itself (one-GPU test of it)
+    // parity instrumentation (apk_debug_token_records): one slab per matvec launch that reads the residual through a norm
+    uint8_t *rec_dump = nullptr;
+    size_t rec_slab = 0;
+    uint32_t rec_idx = 0, rec_cap = 0;
+    int32_t *dots_dump = nullptr;  // block dots of launch dots_launch
+    size_t dots_cap = 0;
+    int dots_launch = -1, launch_no = 0;
+    std::vector<RecMeta> rec_meta;
     bool use_pdl = true;        // ALLPAKA_B200_PDL=0 turns programmatic dependent launch off
     void *comm = nullptr;
     std::unique_ptr<Plan> plan;
     float *xch_local = nullptr;     // this rank's exchange buffer (apk_dist_p2p_export)
     XchPeers xch{};                 // every rank's buffer, peer-mapped
-    bool p2p_ready = false;
-    unsigned char *noalloc_ptr = nullptr;  // device address of the built-in scratch array (apk_matvec_noalloc)
+    bool p2p_open = false;       // every rank's exchange buffer is mapped here
+    bool p2p_ready = false;      // peer buffers are mapped and the peer exchange is switched on
     int inflight = 3;            // K-steps of weights a CTA keeps outstanding (ALLPAKA_B200_INFLIGHT overrides, for tuning)
     int inflight_pre = 2;        // ... while the previous kernel is still finishing (ALLPAKA_B200_INFLIGHT_PRE)
-    bool noalloc_dirty = false;  // the last no-allocation call was not seen to end cleanly
     // host address -> device-resident raw GGUF bytes written by apk_debug_synth_matrix
     std::map<const uint8_t *, std::pair<uint8_t *, size_t>> raw_dev;
 };
@@ -297,7 +315,6 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
     m->bytes = (size_t)m->n_tiles * m->tile_bytes;
     CUDA_TRY(cudaMalloc((void **)&m->d, m->bytes));
     CUDA_TRY(cudaMemsetAsync(m->d, 0, m->bytes, c->stream));
-    APK_TRY(c->counters.ensure((size_t)m->n_tiles * sizeof(int), true));
 
     const size_t seg_row_bytes = (size_t)n_in / be * bb;
     for (const Segment &s : segs) {
@@ -502,11 +519,12 @@ ActMode resolve_mode(uint32_t act_mode, uint32_t m) {
 }
 
 // x [m][n] (f32 or bf16) -> prepared activations for a consumer matrix of type `cty`.
-int launch_prep(apk_ctx *c, const void *x, int x_is_bf16, int ldx, const float *add, int ldadd, float *xout,
+int launch_prep(apk_ctx *c, const float *x, int ldx, const float *add, int ldadd, float *xout,
                 int ldxout, const float *gamma, float eps, float *hout, int ldh, uint32_t n, uint32_t m,
-                uint32_t cty, ActMode mode, void *act_base) {
-    PrepParams p;
-    p.x = x; p.x_is_bf16 = x_is_bf16; p.ldx = ldx;
+                uint32_t cty, ActMode mode, void *act_base, const double *sumsq = nullptr) {
+    PrepParams p{};
+    p.sumsq = sumsq;
+    p.x = x; p.ldx = ldx;
     p.add = add; p.ldadd = ldadd;
     p.xout = xout; p.ldxout = ldxout;
     p.gamma = gamma; p.eps = eps;
@@ -544,12 +562,19 @@ int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool
     p.two_level = mode.two_level;
     p.m_out = mode.two_level ? mode.m_eff / 2 : mode.m_eff;
     p.partials = c->partials.as<unsigned long long>();
-    p.counters = c->counters.as<int>();
     p.err = c->d_err;
+    p.wait_limit = c->wait_limit;
     p.pdl = c->use_pdl ? 1 : 0;
     p.inflight = c->inflight;
     p.inflight_pre = c->inflight_pre;
     if (c->trace && c->trace_idx < c->trace_cap) p.timeline = c->trace + (size_t)(c->trace_idx++) * c->n_sm * 8;
+    if (c->dots_dump && c->launch_no == c->dots_launch &&
+        (size_t)mode.m_eff * W->n_out * W->nb <= c->dots_cap) {
+        p.dump = c->dots_dump;
+        dump = true;
+        k = pick_kernel(W->ty, mode.m_eff, true);
+    }
+    c->launch_no++;
     const int act_rec = p.act.rec_bytes();
     const int ns = pick_stages(c, (int)W->ty, mode.m_eff, p.pro, W->KS, act_rec);
     if (ns < 2) return fail(APK_DECLINE_MISSING_CAPABILITY, "activations of %d rows x %u do not fit in shared memory", mode.m_eff, W->n_in);
@@ -572,26 +597,27 @@ bool want_resident(apk_ctx *c, const DevMatrix *W, int m_eff) {
 // Activation source for a matvec on x (device, f32 or bf16): at one token the
 // kernel quantises in its own prologue (with the optional RMSNorm); otherwise
 // the separate pass writes records that are then loaded whole or streamed.
-int stage_acts(apk_ctx *c, const DevMatrix *W, const void *x, int x_is_bf16, int ldx, const float *add, int ldadd,
+int stage_acts(apk_ctx *c, const DevMatrix *W, const float *x, int ldx, const float *add, int ldadd,
                float *xout, int ldxout, const float *gamma, float eps, uint32_t m, ActMode mode, void *act_buf,
-               MvParams *p) {
+               MvParams *p, const double *sumsq = nullptr, float *hout = nullptr) {
     p->act = act_layout(act_buf, W->ty, mode.m_eff);
     if (m == 1 && W->n_in <= (uint32_t)(N_CONSUMERS * PRO_CH) && ((uintptr_t)x & 15) == 0 && want_resident(c, W, mode.m_eff)) {
         p->pro = PRO_QUANT;
         PrepParams &pp = p->prep;
-        pp.x = x; pp.x_is_bf16 = x_is_bf16; pp.ldx = ldx;
+        pp.x = x; pp.ldx = ldx;
         pp.add = add; pp.ldadd = ldadd;
         pp.xout = xout; pp.ldxout = ldxout;
         pp.gamma = gamma; pp.eps = eps;
-        pp.hout = nullptr; pp.ldh = 0;
+        pp.hout = hout; pp.ldh = (int)W->n_in;
+        pp.sumsq = sumsq;
         pp.n = (int)W->n_in; pp.m = (int)m;
         pp.out = p->act;
         pp.two_level = mode.two_level;
         pp.need_sum = W->ty == APK_TY_Q4_K;
         return APK_OK;
     }
-    APK_TRY(launch_prep(c, x, x_is_bf16, ldx, add, ldadd, xout, ldxout, gamma, eps, nullptr, 0, W->n_in, m, W->ty, mode,
-                        act_buf));
+    APK_TRY(launch_prep(c, x, ldx, add, ldadd, xout, ldxout, gamma, eps, hout, (int)W->n_in, W->n_in, m, W->ty, mode,
+                        act_buf, sumsq));
     p->pro = want_resident(c, W, mode.m_eff) ? PRO_LOAD : PRO_STREAM;
     return APK_OK;
 }
@@ -604,6 +630,7 @@ void use_records(apk_ctx *c, const DevMatrix *W, ActMode mode, void *act_buf, Mv
 
 MvParams mv_store(const ActLayout &act, float *y, int ldy) {
     MvParams p{};
+    p.xin.index = -1;
     p.act = act;
     p.epi = EPI_STORE;
     p.y = y;
@@ -626,7 +653,7 @@ int finish(apk_ctx *c) {
         cudaStreamSynchronize(c->stream);
         return fail(APK_ERR_TIMEOUT, "device-side wait expired (%s)",
                     w == ERRW_PRODUCER_TIMEOUT ? "copy producer"
-                    : w == ERRW_PEER_TIMEOUT   ? "a peer rank never announced its partial sums"
+                    : w == ERRW_PEER_TIMEOUT   ? "a peer rank never delivered its partial sums"
                     : w == ERRW_FINISHER_TIMEOUT ? "a tile piece of another CTA never arrived"
                                                  : "tile consumer");
     }
@@ -647,9 +674,107 @@ int run_matvec_dev(apk_ctx *c, DevMatrix *W, const float *x_dev, uint32_t m, uin
     if (reuse_act && m > 1)
         use_records(c, W, mode, c->act_a.p, &p);
     else
-        APK_TRY(stage_acts(c, W, x_dev, 0, (int)W->n_in, nullptr, 0, nullptr, 0, nullptr, 0.f, m, mode, c->act_a.p, &p));
+        APK_TRY(stage_acts(c, W, x_dev, (int)W->n_in, nullptr, 0, nullptr, 0, nullptr, 0.f, m, mode, c->act_a.p, &p));
     p.dump = dump;
     return launch_matvec(c, W, p, mode, dump != nullptr);
+}
+
+
+// One item of gpu::ffn_batch, resolved (matrices resident) and enqueued on device buffers:
+// x in c->x_dev [m][hidden], y in c->y_dev.
+struct FfnOp {
+    DevMatrix *GU = nullptr, *D = nullptr;
+    uint32_t m = 0, hidden = 0, ffn = 0;
+};
+
+int ffn_resolve(apk_ctx *c, const apk_ffn_req *r, FfnOp *op) {
+    APK_TRY(check_m(r->m));
+    if (r->gate_ty != r->up_ty)
+        return fail(APK_DECLINE_UNSUPPORTED_TYPE, "ffn: gate (%u) and up (%u) must share a type", r->gate_ty, r->up_ty);
+    if (c->world != 1) return fail(APK_DECLINE_INVALID_STATE, "ffn: stand-alone FFN runs on an unsharded context");
+    uint32_t fl;
+    APK_TRY(resolve_gateup(c, r->gate_ty, r->gate_w, r->up_w, r->hidden, r->ffn, &op->GU, &fl));
+    APK_TRY(resolve_plain(c, "ffn down", r->down_w, r->down_ty, r->hidden, r->ffn, SHARD_NONE, &op->D));
+    op->m = r->m; op->hidden = r->hidden; op->ffn = r->ffn;
+    const ActMode q8{0, (int)r->m};
+    const ActMode dmode = resolve_mode(APK_ACT_AUTO, r->m);
+    APK_TRY(c->x_dev.ensure((size_t)r->m * r->hidden * sizeof(float)));
+    APK_TRY(c->y_dev.ensure((size_t)r->m * r->hidden * sizeof(float)));
+    APK_TRY(c->act_a.ensure(act_bytes(op->GU->ty, q8.m_eff, r->hidden)));
+    APK_TRY(c->act_b.ensure(act_bytes(op->D->ty, dmode.m_eff, r->ffn)));
+    return APK_OK;
+}
+
+int ffn_enqueue(apk_ctx *c, const FfnOp &op) {
+    const uint32_t m = op.m;
+    const ActMode q8{0, (int)m};
+    const ActMode dmode = resolve_mode(APK_ACT_AUTO, m);  // w_down.matmul(&gate, m): model/moe.rs:128
+    MvParams p{};
+    APK_TRY(stage_acts(c, op.GU, c->x_dev.as<float>(), (int)op.hidden, nullptr, 0, nullptr, 0, nullptr, 0.f, m, q8, c->act_a.p, &p));
+    p.epi = EPI_SWIGLU;
+    p.act_next = act_layout(c->act_b.p, op.D->ty, dmode.m_eff);
+    p.next_two_level = dmode.two_level;
+    p.next_need_sum = op.D->ty == APK_TY_Q4_K;
+    p.ffn = (int)op.ffn;
+    APK_TRY(launch_matvec(c, op.GU, p, q8));
+    MvParams pd = mv_store(ActLayout{}, c->y_dev.as<float>(), (int)op.hidden);
+    use_records(c, op.D, dmode, c->act_b.p, &pd);
+    return launch_matvec(c, op.D, pd, dmode);
+}
+
+// The input half of gpu::attn_block: x in c->x_dev, side inputs in c->misc, [q | k | v] rows in c->y_dev.
+struct AttnInOp {
+    DevMatrix *W = nullptr;
+    uint32_t m = 0, H = 0, nq = 0, nkv = 0, half = 0;
+};
+
+int attn_in_resolve(apk_ctx *c, const apk_attn_in_req *r, AttnInOp *op) {
+    APK_TRY(check_m(r->m));
+    if (r->head_dim != TILE_ROWS)
+        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "attn_in: head_dim %u (the fused epilogue is written for 128)", r->head_dim);
+    if (r->rot_dim > r->head_dim || r->rot_dim % 2)
+        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "attn_in: rot_dim %u", r->rot_dim);
+    if (c->world != 1) return fail(APK_DECLINE_INVALID_STATE, "attn_in: stand-alone call runs on an unsharded context");
+    op->m = r->m; op->H = r->hidden; op->nq = r->n_heads * r->head_dim; op->nkv = r->n_kv_heads * r->head_dim;
+    op->half = r->rot_dim / 2;
+    APK_TRY(resolve_qkv(c, r->ty, r->wq, r->wk, r->wv, op->H, op->nq, op->nkv, &op->W));
+    APK_TRY(c->x_dev.ensure((size_t)op->m * op->H * sizeof(float)));
+    APK_TRY(c->y_dev.ensure((size_t)op->m * (op->nq + 2 * op->nkv) * sizeof(float)));
+    APK_TRY(c->act_a.ensure(act_bytes(op->W->ty, (int)op->m, op->H)));
+    // misc: gamma[H] | q_norm[128] | k_norm[128] | rope[m][half][2]
+    APK_TRY(c->misc.ensure(((size_t)op->H + 256 + (size_t)op->m * op->half * 2) * sizeof(float)));
+    return APK_OK;
+}
+
+int attn_in_upload(apk_ctx *c, const apk_attn_in_req *r, const AttnInOp &op) {
+    float *misc = c->misc.as<float>();
+    const size_t H = op.H;
+    CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, r->x, (size_t)op.m * H * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    if (r->gamma) CUDA_TRY(cudaMemcpyAsync(misc, r->gamma, H * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    if (r->q_norm) CUDA_TRY(cudaMemcpyAsync(misc + H, r->q_norm, 128 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    if (r->k_norm) CUDA_TRY(cudaMemcpyAsync(misc + H + 128, r->k_norm, 128 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    if (op.half) CUDA_TRY(cudaMemcpyAsync(misc + H + 256, r->rope, (size_t)op.m * op.half * 2 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    return APK_OK;
+}
+
+int attn_in_enqueue(apk_ctx *c, const apk_attn_in_req *r, const AttnInOp &op) {
+    float *misc = c->misc.as<float>();
+    const size_t H = op.H;
+    const ActMode q8{0, (int)op.m};
+    MvParams p{};
+    APK_TRY(stage_acts(c, op.W, c->x_dev.as<float>(), (int)H, nullptr, 0, nullptr, 0, r->gamma ? misc : nullptr, r->eps, op.m, q8,
+                       c->act_a.p, &p));
+    p.epi = EPI_QKV_ROPE;
+    p.y = c->y_dev.as<float>();
+    p.ldy = (int)(op.nq + 2 * op.nkv);
+    p.n_q_tiles = (int)r->n_heads;
+    p.n_k_tiles = (int)r->n_kv_heads;
+    p.q_norm = r->q_norm ? misc + H : nullptr;
+    p.k_norm = r->k_norm ? misc + H + 128 : nullptr;
+    p.eps = r->eps;
+    p.rope = misc + H + 256;
+    p.half = (int)op.half;
+    return launch_matvec(c, op.W, p, q8);
 }
 
 }  // namespace
@@ -687,12 +812,23 @@ int apk_init(apk_ctx **out, int device) {
     CUDA_TRY(cudaMallocHost((void **)&c->h_err, sizeof(int)));
     *c->h_err = 0;
     APK_TRY(c->partials.ensure((size_t)c->n_sm * 2 * MAX_M_EFF * TILE_ROWS * sizeof(unsigned long long), true));
-    APK_TRY(c->counters.ensure(65536 * sizeof(int), true));
     APK_TRY(init_kernel_attrs(c.get()));
     if (const char *e = getenv("ALLPAKA_B200_PDL")) c->use_pdl = atoi(e) != 0;
     if (const char *e = getenv("ALLPAKA_B200_FUSE_NORM")) c->fuse_norm = atoi(e);
     if (const char *e = getenv("ALLPAKA_B200_INFLIGHT")) c->inflight = std::max(1, std::min(atoi(e), MAX_STAGES));
     if (const char *e = getenv("ALLPAKA_B200_INFLIGHT_PRE")) c->inflight_pre = std::max(1, std::min(atoi(e), MAX_STAGES));
+    if (const char *e = getenv("ALLPAKA_B200_NEXT_PREFETCH")) c->next_units = std::max(0, std::min(atoi(e), 64));
+    if (const char *e = getenv("ALLPAKA_B200_NEXT_PACE")) c->next_pace = std::max(0, std::min(atoi(e), 100000));
+    if (const char *e = getenv("ALLPAKA_B200_SELF_XCH")) c->self_xch = atoi(e) != 0;
+    if (c->self_xch) {
+        // one rank exchanging with itself: the peer-store epilogue and the collecting prologue on one GPU
+        CUDA_TRY(cudaMalloc((void **)&c->xch_local, XCH_BYTES));
+        CUDA_TRY(cudaMemset(c->xch_local, 0, XCH_BYTES));
+        c->xch.slots[0] = c->xch_local;
+        c->xch.rank = 0;
+        c->xch.world = 1;
+        c->p2p_ready = true;  // (p2p_open stays false: nothing was mapped from a peer)
+    }
     *out = c.release();
     return APK_OK;
 }
@@ -705,12 +841,12 @@ void apk_shutdown(apk_ctx *c) {
     c->mats.clear();
     for (auto &kv : c->raw_dev) cudaFree(kv.second.first);
     c->raw_dev.clear();
-    if (c->p2p_ready)
+    if (c->p2p_open)
         for (int r = 0; r < c->world; ++r)
             if (r != c->rank && c->xch.slots[r]) cudaIpcCloseMemHandle(c->xch.slots[r]);
     if (c->xch_local) cudaFree(c->xch_local);
     if (c->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(c->comm);
-    for (DevBuf *b : {&c->staging, &c->partials, &c->counters, &c->x_dev, &c->y_dev, &c->act_a, &c->act_b, &c->misc, &c->dump})
+    for (DevBuf *b : {&c->staging, &c->partials, &c->x_dev, &c->y_dev, &c->act_a, &c->act_b, &c->misc, &c->dump})
         b->release();
     if (c->d_err) cudaFree(c->d_err);
     if (c->h_err) cudaFreeHost(c->h_err);
@@ -858,7 +994,7 @@ int apk_debug_matvec_timeline(apk_ctx *c, const void *w, uint32_t ty, uint32_t n
     APK_TRY(c->act_a.ensure(act_bytes(W->ty, mode.m_eff, W->n_in)));
     CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, x, (size_t)m * n_in * sizeof(float), cudaMemcpyHostToDevice, c->stream));
     MvParams p = mv_store(ActLayout{}, c->y_dev.as<float>(), (int)n_out);
-    APK_TRY(stage_acts(c, W, c->x_dev.p, 0, (int)n_in, nullptr, 0, nullptr, 0, nullptr, 0.f, m, mode, c->act_a.p, &p));
+    APK_TRY(stage_acts(c, W, c->x_dev.as<float>(), (int)n_in, nullptr, 0, nullptr, 0, nullptr, 0.f, m, mode, c->act_a.p, &p));
     // Four launches back to back (programmatic dependencies chain them like the layers of
     // a token); every launch rewrites all stamps, so the last one is what is reported.
     CUDA_TRY(cudaMemsetAsync(c->dump.p, 0, (size_t)grid * 8 * sizeof(uint64_t), c->stream));
@@ -884,7 +1020,7 @@ int apk_debug_q8_acts(apk_ctx *c, const float *x, uint32_t n, const float *gamma
     if (gamma) CUDA_TRY(cudaMemcpyAsync(c->misc.p, gamma, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, c->stream));
     CUDA_TRY(cudaMemsetAsync(c->act_a.p, 0, ab, c->stream));
     // the Q4_K flavour of the record carries the block sums as well
-    APK_TRY(launch_prep(c, c->x_dev.p, 0, (int)n, nullptr, 0, nullptr, 0, gamma ? c->misc.as<float>() : nullptr, eps,
+    APK_TRY(launch_prep(c, c->x_dev.as<float>(), (int)n, nullptr, 0, nullptr, 0, gamma ? c->misc.as<float>() : nullptr, eps,
                         nullptr, 0, n, 1, APK_TY_Q4_K, mode, c->act_a.p));
     std::vector<uint8_t> host(ab);
     CUDA_TRY(cudaMemcpyAsync(host.data(), c->act_a.p, ab, cudaMemcpyDeviceToHost, c->stream));
@@ -908,34 +1044,11 @@ int apk_ffn(apk_ctx *c, const apk_ffn_req *r, float *y) {
     std::lock_guard<std::mutex> g(c->mu);
     CUDA_TRY(cudaSetDevice(c->device));
     const uint64_t t0 = now_ns();
-    APK_TRY(check_m(r->m));
-    if (r->gate_ty != r->up_ty)
-        return fail(APK_DECLINE_UNSUPPORTED_TYPE, "ffn: gate (%u) and up (%u) must share a type", r->gate_ty, r->up_ty);
-    if (c->world != 1) return fail(APK_DECLINE_INVALID_STATE, "ffn: stand-alone FFN runs on an unsharded context");
-    DevMatrix *GU, *D;
-    uint32_t fl;
-    APK_TRY(resolve_gateup(c, r->gate_ty, r->gate_w, r->up_w, r->hidden, r->ffn, &GU, &fl));
-    APK_TRY(resolve_plain(c, "ffn down", r->down_w, r->down_ty, r->hidden, r->ffn, SHARD_NONE, &D));
-    const uint32_t m = r->m;
-    const ActMode q8{0, (int)m};
-    const ActMode dmode = resolve_mode(APK_ACT_AUTO, m);  // w_down.matmul(&gate, m): model/moe.rs:128
-    APK_TRY(c->x_dev.ensure((size_t)m * r->hidden * sizeof(float)));
-    APK_TRY(c->y_dev.ensure((size_t)m * r->hidden * sizeof(float)));
-    APK_TRY(c->act_a.ensure(act_bytes(GU->ty, q8.m_eff, r->hidden)));
-    APK_TRY(c->act_b.ensure(act_bytes(D->ty, dmode.m_eff, r->ffn)));
-    CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, r->x, (size_t)m * r->hidden * sizeof(float), cudaMemcpyHostToDevice, c->stream));
-    MvParams p{};
-    APK_TRY(stage_acts(c, GU, c->x_dev.p, 0, (int)r->hidden, nullptr, 0, nullptr, 0, nullptr, 0.f, m, q8, c->act_a.p, &p));
-    p.epi = EPI_SWIGLU;
-    p.act_next = act_layout(c->act_b.p, D->ty, dmode.m_eff);
-    p.next_two_level = dmode.two_level;
-    p.next_need_sum = D->ty == APK_TY_Q4_K;
-    p.ffn = (int)r->ffn;
-    APK_TRY(launch_matvec(c, GU, p, q8));
-    MvParams pd = mv_store(ActLayout{}, c->y_dev.as<float>(), (int)r->hidden);
-    use_records(c, D, dmode, c->act_b.p, &pd);
-    APK_TRY(launch_matvec(c, D, pd, dmode));
-    CUDA_TRY(cudaMemcpyAsync(y, c->y_dev.p, (size_t)m * r->hidden * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+    FfnOp op;
+    APK_TRY(ffn_resolve(c, r, &op));
+    CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, r->x, (size_t)op.m * op.hidden * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    APK_TRY(ffn_enqueue(c, op));
+    CUDA_TRY(cudaMemcpyAsync(y, c->y_dev.p, (size_t)op.m * op.hidden * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
     c->st.encode_ns += now_ns() - t0;
     c->st.calls++;
     return finish(c);
@@ -946,43 +1059,11 @@ int apk_attn_in(apk_ctx *c, const apk_attn_in_req *r, float *q, float *k, float 
     std::lock_guard<std::mutex> g(c->mu);
     CUDA_TRY(cudaSetDevice(c->device));
     const uint64_t t0 = now_ns();
-    APK_TRY(check_m(r->m));
-    if (r->head_dim != TILE_ROWS)
-        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "attn_in: head_dim %u (the fused epilogue is written for 128)", r->head_dim);
-    if (r->rot_dim > r->head_dim || r->rot_dim % 2)
-        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "attn_in: rot_dim %u", r->rot_dim);
-    if (c->world != 1) return fail(APK_DECLINE_INVALID_STATE, "attn_in: stand-alone call runs on an unsharded context");
-    const uint32_t m = r->m, H = r->hidden, nq = r->n_heads * r->head_dim, nkv = r->n_kv_heads * r->head_dim;
-    const uint32_t half = r->rot_dim / 2, ld = nq + 2 * nkv;
-    DevMatrix *W;
-    APK_TRY(resolve_qkv(c, r->ty, r->wq, r->wk, r->wv, H, nq, nkv, &W));
-    const ActMode q8{0, (int)m};
-    APK_TRY(c->x_dev.ensure((size_t)m * H * sizeof(float)));
-    APK_TRY(c->y_dev.ensure((size_t)m * ld * sizeof(float)));
-    APK_TRY(c->act_a.ensure(act_bytes(W->ty, q8.m_eff, H)));
-    // misc: gamma[H] | q_norm[128] | k_norm[128] | rope[m][half][2]
-    const size_t o_qn = H, o_kn = H + 128, o_rope = H + 256;
-    APK_TRY(c->misc.ensure((o_rope + (size_t)m * half * 2) * sizeof(float)));
-    float *misc = c->misc.as<float>();
-    CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, r->x, (size_t)m * H * sizeof(float), cudaMemcpyHostToDevice, c->stream));
-    if (r->gamma) CUDA_TRY(cudaMemcpyAsync(misc, r->gamma, H * sizeof(float), cudaMemcpyHostToDevice, c->stream));
-    if (r->q_norm) CUDA_TRY(cudaMemcpyAsync(misc + o_qn, r->q_norm, 128 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
-    if (r->k_norm) CUDA_TRY(cudaMemcpyAsync(misc + o_kn, r->k_norm, 128 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
-    if (half) CUDA_TRY(cudaMemcpyAsync(misc + o_rope, r->rope, (size_t)m * half * 2 * sizeof(float), cudaMemcpyHostToDevice, c->stream));
-    MvParams p{};
-    APK_TRY(stage_acts(c, W, c->x_dev.p, 0, (int)H, nullptr, 0, nullptr, 0, r->gamma ? misc : nullptr, r->eps, m, q8,
-                       c->act_a.p, &p));
-    p.epi = EPI_QKV_ROPE;
-    p.y = c->y_dev.as<float>();
-    p.ldy = (int)ld;
-    p.n_q_tiles = (int)r->n_heads;
-    p.n_k_tiles = (int)r->n_kv_heads;
-    p.q_norm = r->q_norm ? misc + o_qn : nullptr;
-    p.k_norm = r->k_norm ? misc + o_kn : nullptr;
-    p.eps = r->eps;
-    p.rope = misc + o_rope;
-    p.half = (int)half;
-    APK_TRY(launch_matvec(c, W, p, q8));
+    AttnInOp op;
+    APK_TRY(attn_in_resolve(c, r, &op));
+    APK_TRY(attn_in_upload(c, r, op));
+    APK_TRY(attn_in_enqueue(c, r, op));
+    const uint32_t m = op.m, nq = op.nq, nkv = op.nkv, ld = nq + 2 * nkv;
     const float *yd = c->y_dev.as<float>();
     CUDA_TRY(cudaMemcpy2DAsync(q, nq * sizeof(float), yd, ld * sizeof(float), nq * sizeof(float), m, cudaMemcpyDeviceToHost, c->stream));
     CUDA_TRY(cudaMemcpy2DAsync(k, nkv * sizeof(float), yd + nq, ld * sizeof(float), nkv * sizeof(float), m, cudaMemcpyDeviceToHost, c->stream));
@@ -990,6 +1071,60 @@ int apk_attn_in(apk_ctx *c, const apk_attn_in_req *r, float *q, float *k, float 
     c->st.encode_ns += now_ns() - t0;
     c->st.calls++;
     return finish(c);
+}
+
+int apk_bench_ring(apk_ctx *c, const apk_bench_req *b, uint32_t reps, float *us_per_pass) {
+    if (!c || !b || !us_per_pass || reps == 0 || b->n_copies == 0) return fail(APK_ERR_INVALID_ARG, "bench_ring: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    const uint32_t n = b->n_copies;
+    std::vector<DevMatrix *> mats(n);
+    std::vector<FfnOp> ffns(n);
+    std::vector<AttnInOp> attns(n);
+    if (b->op == APK_BENCH_MATVEC) {
+        if (!b->mv) return fail(APK_ERR_INVALID_ARG, "bench_ring: no matvec requests");
+        for (uint32_t i = 0; i < n; ++i) {
+            const apk_matvec_req &r = b->mv[i];
+            APK_TRY(check_m(r.m));
+            if (r.m != b->mv[0].m || r.n_in != b->mv[0].n_in || r.n_out != b->mv[0].n_out)
+                return fail(APK_ERR_INVALID_ARG, "bench_ring: copies differ in shape");
+            APK_TRY(resolve_plain(c, "bench", r.w, r.ty, r.n_out, r.n_in, SHARD_NONE, &mats[i]));
+        }
+        const apk_matvec_req &r0 = b->mv[0];
+        if (!r0.x) return fail(APK_ERR_INVALID_ARG, "bench_ring: no input rows");
+        APK_TRY(c->x_dev.ensure((size_t)r0.m * r0.n_in * sizeof(float)));
+        APK_TRY(c->y_dev.ensure((size_t)r0.m * r0.n_out * sizeof(float)));
+        CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, r0.x, (size_t)r0.m * r0.n_in * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+    } else if (b->op == APK_BENCH_FFN) {
+        if (!b->ffn || !b->ffn[0].x) return fail(APK_ERR_INVALID_ARG, "bench_ring: no ffn requests");
+        for (uint32_t i = 0; i < n; ++i) APK_TRY(ffn_resolve(c, &b->ffn[i], &ffns[i]));
+        CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, b->ffn[0].x, (size_t)ffns[0].m * ffns[0].hidden * sizeof(float),
+                                 cudaMemcpyHostToDevice, c->stream));
+    } else if (b->op == APK_BENCH_ATTN_IN) {
+        if (!b->attn || !b->attn[0].x || !b->attn[0].rope) return fail(APK_ERR_INVALID_ARG, "bench_ring: no attn_in requests");
+        for (uint32_t i = 0; i < n; ++i) APK_TRY(attn_in_resolve(c, &b->attn[i], &attns[i]));
+        APK_TRY(attn_in_upload(c, &b->attn[0], attns[0]));
+    } else {
+        return fail(APK_ERR_INVALID_ARG, "bench_ring: unknown op %u", b->op);
+    }
+    auto pass = [&](uint32_t i) -> int {
+        if (b->op == APK_BENCH_MATVEC)
+            return run_matvec_dev(c, mats[i], c->x_dev.as<float>(), b->mv[0].m, b->act_mode, c->y_dev.as<float>(), false, nullptr);
+        if (b->op == APK_BENCH_FFN) return ffn_enqueue(c, ffns[i]);
+        return attn_in_enqueue(c, &b->attn[0], attns[i]);
+    };
+    for (uint32_t i = 0; i < n; ++i) APK_TRY(pass(i));  // warm: every copy once
+    APK_TRY(finish(c));
+    CUDA_TRY(cudaEventRecord(c->ev0, c->stream));
+    for (uint32_t rep = 0; rep < reps; ++rep)
+        for (uint32_t i = 0; i < n; ++i) APK_TRY(pass(i));
+    CUDA_TRY(cudaEventRecord(c->ev1, c->stream));
+    c->st.calls++;
+    APK_TRY(finish(c));
+    float ms = 0.f;
+    CUDA_TRY(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+    *us_per_pass = ms * 1e3f / (float)(reps * n);
+    return APK_OK;
 }
 
 int apk_debug_synth_matrix(apk_ctx *c, void *w, uint32_t ty, uint32_t n_out, uint32_t n_in, uint64_t seed,
@@ -1069,7 +1204,8 @@ int apk_dist_p2p_open(apk_ctx *c, const void *handles) {
     std::lock_guard<std::mutex> g(c->mu);
     CUDA_TRY(cudaSetDevice(c->device));
     if (!c->xch_local) return fail(APK_DECLINE_INVALID_STATE, "p2p_open before p2p_export");
-    if (c->p2p_ready) return APK_OK;
+    if (c->p2p_open) return APK_OK;
+    if (c->world > XCH_MAX_RANKS) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "p2p exchange is built for at most %d ranks", XCH_MAX_RANKS);
     c->xch.rank = c->rank;
     c->xch.world = c->world;
     for (int r = 0; r < c->world; ++r) {
@@ -1081,7 +1217,19 @@ int apk_dist_p2p_open(apk_ctx *c, const void *handles) {
         c->xch.slots[r] = (float *)ptr;
     }
     c->plan.reset();  // graphs captured with NCCL reductions are rebuilt
+    c->p2p_open = true;
     c->p2p_ready = true;
+    return APK_OK;
+}
+
+int apk_dist_set_exchange(apk_ctx *c, int peer_stores) {
+    if (!c) return fail(APK_ERR_INVALID_ARG, "null context");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    if (peer_stores && !c->p2p_open) return fail(APK_DECLINE_INVALID_STATE, "set_exchange: no peer buffers are open");
+    CUDA_TRY(cudaStreamSynchronize(c->stream));
+    c->p2p_ready = peer_stores != 0;
+    c->plan.reset();  // captured graphs carry the other kind of reduction
     return APK_OK;
 }
 

@@ -60,11 +60,37 @@ int decline_decode(apk_ctx *c, int code, const char *fmt, ...) {
     return fail(code, "stage=backend-decode reason=%s", buf);
 }
 
+// FNV-1a over every descriptor of the request that the plan bakes in: a caller that
+// rewrites the layer array in place, or reuses its address for another model, gets a
+// new plan instead of the old weights.
+uint64_t desc_hash(const apk_token_req *r) {
+    uint64_t h = 1469598103934665603ull;
+    auto mix = [&](uint64_t v) {
+        for (int i = 0; i < 8; ++i) {
+            h ^= (v >> (8 * i)) & 0xffu;
+            h *= 1099511628211ull;
+        }
+    };
+    auto mat = [&](const apk_mat &m) {
+        mix((uint64_t)(uintptr_t)m.w);
+        mix(((uint64_t)m.ty << 32) | m.n_out);
+    };
+    for (uint32_t l = 0; l < r->n_layers; ++l) {
+        const apk_token_layer &t = r->layers[l];
+        mix((uint64_t)(uintptr_t)t.attn_norm); mix((uint64_t)(uintptr_t)t.ffn_norm);
+        mix((uint64_t)(uintptr_t)t.q_norm); mix((uint64_t)(uintptr_t)t.k_norm);
+        mat(t.wq); mat(t.wk); mat(t.wv); mat(t.wo); mat(t.gate); mat(t.up); mat(t.down);
+    }
+    mix((uint64_t)(uintptr_t)r->output_norm);
+    mat(r->output);
+    return h;
+}
+
 bool plan_matches(const Plan *p, const apk_token_req *r) {
     return p && p->layers_key == r->layers && p->n_layers == r->n_layers && p->output_key == r->output.w &&
            p->hidden == r->hidden && p->head_dim == r->head_dim && p->n_heads == r->n_heads &&
            p->n_kv_heads == r->n_kv_heads && p->rot_dim == r->rot_dim && p->vocab == r->output.n_out &&
-           p->eps == r->eps;
+           p->eps == r->eps && p->desc_hash == desc_hash(r);
 }
 
 int nccl_allreduce(apk_ctx *c, float *buf, size_t n) {
@@ -72,6 +98,8 @@ int nccl_allreduce(apk_ctx *c, float *buf, size_t n) {
     if (rc) return fail(APK_ERR_NCCL, "ncclAllReduce: %s", g_nccl.GetErrorString(rc));
     return APK_OK;
 }
+
+bool uses_xch(const apk_ctx *c) { return c->p2p_ready && (c->world > 1 || c->self_xch); }
 
 int build_plan(apk_ctx *c, const apk_token_req *r) {
     c->plan.reset();
@@ -83,9 +111,10 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
     if (r->rot_dim > r->head_dim || r->rot_dim % 2) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "rot_dim %u", r->rot_dim);
     const uint32_t ffn = r->layers[0].gate.n_out;
     P->layers_key = r->layers; P->n_layers = r->n_layers; P->output_key = r->output.w;
+    P->desc_hash = desc_hash(r);
     P->hidden = H; P->head_dim = r->head_dim; P->n_heads = r->n_heads; P->n_kv_heads = r->n_kv_heads;
     P->rot_dim = r->rot_dim; P->vocab = r->output.n_out; P->eps = r->eps; P->ffn = ffn;
-    if (c->p2p_ready && ((size_t)APK_MAX_M * H > (size_t)XCH_ROW_FLOATS || H % 4))
+    if (uses_xch(c) && ((size_t)APK_MAX_M * H > (size_t)XCH_ROW_FLOATS || H % 4 || H > (uint32_t)XCH_MAX_TILES * TILE_ROWS))
         return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "hidden %u exceeds the peer exchange buffer", H);
     if (P->vocab % c->world) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "vocab %u does not split over %d ranks", P->vocab, c->world);
     P->nq_l = nq / c->world; P->nkv_l = nkv / c->world; P->vocab_l = P->vocab / c->world;
@@ -148,51 +177,131 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
     APK_TRY(P->amax.ensure(M * sizeof(uint32_t)));
     APK_TRY(P->rope.ensure((size_t)M * (r->rot_dim / 2 + 1) * 2 * 4));
     APK_TRY(P->sumsq.ensure((size_t)M * (H / 32 + 1) * sizeof(double), true));
+    APK_TRY(P->hidden_out.ensure((size_t)M * H * 4));
+    if (uses_xch(c)) {
+        // A new plan restarts the exchange numbering (its exchanges per token may differ): clear
+        // this rank's flags and token counter, then meet the other ranks, so that nobody's first
+        // token runs against a peer that is still uploading or still holds old flags.  (The bounded
+        // device-side waits are for a peer that died, not for one that is a few seconds behind.)
+        if (c->world > 1) APK_TRY(nccl_allreduce(c, P->yp.as<float>(), 1));  // every rank's previous token is over
+        CUDA_TRY(cudaStreamSynchronize(c->stream));
+        CUDA_TRY(cudaMemsetAsync(xch_flags(c->xch_local), 0, XCH_FLAGS_BYTES + 256, c->stream));
+    }
+    if (c->world > 1) {
+        APK_TRY(nccl_allreduce(c, P->yp.as<float>(), 1));
+        CUDA_TRY(cudaStreamSynchronize(c->stream));
+    }
     c->plan = std::move(P);
     return APK_OK;
 }
 
-// The four matvecs of a layer and the head, as launches on the context stream.
-// `for_profile` replays one kind in isolation (activations already in place).
+// The matvecs of a layer and the head, as launches on the context stream.
 struct TokenLaunch {
     apk_ctx *c;
     Plan *P;
     uint32_t m;
     ActMode q8, autom;
     int cur = 0;
-    bool pending_add = false;  // tensor parallel: yp holds a combined delta not yet added to x
+    bool pending_add = false;  // NCCL reductions: yp holds a combined delta not yet added to x
+    int pending_xch = -1;      // peer exchange: index of the exchange whose sum is not yet added to x
+    int n_xch = 0;             // exchanges launched so far in this token
+    bool first = true;         // the next matvec launch is the token's first
+    bool have_sumsq = false;   // the last residual matvec left the per-block sums of squares of x[cur]
     // the previous residual matvec already quantised x * gamma for this (matrix, mode): its
-    // records sit in act_h and only lack the row-wide RMSNorm scale
+    // records sit in act_h and only lack the row-wide RMSNorm scale (opt-in approximation)
     const DevMatrix *prenormed_for = nullptr;
     int prenormed_m_eff = 0;
 
     TokenLaunch(apk_ctx *c_, Plan *P_, uint32_t m_) : c(c_), P(P_), m(m_), q8{0, (int)m_}, autom(resolve_mode(APK_ACT_AUTO, m_)) {}
 
-    // activations of a matvec that reads the residual stream through an RMSNorm
+    int per_token() const { return 2 * (int)P->n_layers; }
     // Can the residual epilogue in front of matvec W (through an RMSNorm) do the quantisation?
     bool can_prenorm(const DevMatrix *W, ActMode mode) const {
-        const bool on = c->fuse_norm == 1 || (c->fuse_norm == 2 && m > 1);
-        return on && c->world == 1 && P->hidden % 32 == 0 && want_resident(c, W, mode.m_eff);
+        const bool on = c->fuse_norm == 2 || (c->fuse_norm == 3 && m > 1);
+        return on && W != P->head && !uses_xch(c) && c->world == 1 && P->hidden % 32 == 0 && want_resident(c, W, mode.m_eff);
     }
-    int normed_input(const DevMatrix *W, const float *gamma, ActMode mode, MvParams *p, bool advance) {
+    void set_next(MvParams *p, const DevMatrix *Wn) const {
+        if (!Wn || c->next_units <= 0) return;
+        p->next_W = Wn->d;
+        p->next_tile_bytes = Wn->tile_bytes;
+        p->next_ty = (int)Wn->ty;
+        p->next_nb = Wn->nb;
+        p->next_n_tiles = Wn->n_tiles;
+        p->next_KS = Wn->KS;
+        p->next_grid = (int)std::min<long long>(c->n_sm, (long long)Wn->n_tiles * Wn->KS);
+        p->next_units = c->next_units;
+        p->next_pace = c->next_pace;
+    }
+    int launch(const DevMatrix *W, MvParams &p, ActMode mode, const DevMatrix *Wn) {
+        if (first && uses_xch(c)) {
+            p.xch = c->xch;
+            p.tok_inc = 1;
+        }
+        first = false;
+        set_next(&p, Wn);
+        return launch_matvec(c, W, p, mode);
+    }
+    // Parity instrumentation: keep the rows this launch normalises and the records it consumes.
+    void record_hook(const float *x_in, ActMode mode, MvParams *p) {
+        if (!c->rec_dump || c->rec_idx >= c->rec_cap) return;
+        uint8_t *slab = c->rec_dump + (size_t)c->rec_idx * c->rec_slab;
+        cudaMemcpyAsync(slab, x_in, (size_t)m * P->hidden * 4, cudaMemcpyDeviceToDevice, c->stream);
+        p->act_dump = slab + (size_t)APK_MAX_M * P->hidden * 4;
+        c->rec_meta.push_back({p->act.ke, mode.m_eff, mode.two_level, c->launch_no});
+        c->rec_idx++;
+    }
+    // activations of a matvec that reads the residual stream through an RMSNorm
+    int normed_input(const DevMatrix *W, const float *gamma, ActMode mode, MvParams *p, bool advance, float *hout = nullptr) {
         const uint32_t H = P->hidden;
+        p->xin.index = -1;
         if (prenormed_for == W && prenormed_m_eff == mode.m_eff) {
             p->act = act_layout(P->act_h.p, W->ty, mode.m_eff);
             p->pro = PRO_LOAD;
             p->norm_sumsq = P->sumsq.as<double>();
             p->norm_blocks = (int)(H / 32);
             p->norm_eps = P->eps;
+            record_hook(P->x[cur].as<float>(), mode, p);
             if (advance) prenormed_for = nullptr;
             return APK_OK;
         }
         float *xc = P->x[cur].as<float>();
+        if (pending_xch >= 0) {
+            float *xn = P->x[cur ^ 1].as<float>();
+            const bool in_cta = m == 1 && H <= (uint32_t)(N_CONSUMERS * PRO_CH) && want_resident(c, W, mode.m_eff);
+            if (in_cta) {
+                // the kernel gathers the row itself: residual + rank-ordered sum of the slots
+                APK_TRY(stage_acts(c, W, xc, (int)H, nullptr, 0, xn, (int)H, gamma, P->eps, m, mode, P->act_h.p, p, nullptr, hout));
+                p->xch = c->xch;
+                p->xin = XchSeq{pending_xch, per_token()};
+                if (advance) { cur ^= 1; pending_xch = -1; }
+                return APK_OK;
+            }
+            XchReduceParams rp{};
+            rp.xch = c->xch;
+            rp.seq = XchSeq{pending_xch, per_token()};
+            rp.x = xc; rp.ldx = (int)H;
+            rp.xout = xn; rp.ldxout = (int)H;
+            rp.n = (int)H; rp.m = (int)m;
+            rp.err = c->d_err;
+            rp.pdl = c->use_pdl ? 1 : 0;
+            rp.wait_limit = c->wait_limit;
+            const unsigned grid = (unsigned)(((size_t)m * H + 1023) / 1024);
+            CUDA_TRY(launch_ex(c, xch_reduce_kernel, dim3(grid), dim3(256), 0, c->use_pdl, rp));
+            c->st.launches++;
+            if (advance) { cur ^= 1; pending_xch = -1; xc = xn; }
+            else xc = xn;
+            return stage_acts(c, W, xc, (int)H, nullptr, 0, nullptr, 0, gamma, P->eps, m, mode, P->act_h.p, p, nullptr, hout);
+        }
         if (pending_add) {
             float *xn = P->x[cur ^ 1].as<float>();
-            APK_TRY(stage_acts(c, W, xc, 0, (int)H, P->yp.as<float>(), (int)H, xn, (int)H, gamma, P->eps, m, mode, P->act_h.p, p));
+            APK_TRY(stage_acts(c, W, xc, (int)H, P->yp.as<float>(), (int)H, xn, (int)H, gamma, P->eps, m, mode, P->act_h.p, p, nullptr, hout));
             if (advance) { cur ^= 1; pending_add = false; }
             return APK_OK;
         }
-        return stage_acts(c, W, xc, 0, (int)H, nullptr, 0, nullptr, 0, gamma, P->eps, m, mode, P->act_h.p, p);
+        APK_TRY(stage_acts(c, W, xc, (int)H, nullptr, 0, nullptr, 0, gamma, P->eps, m, mode, P->act_h.p, p,
+                           have_sumsq ? P->sumsq.as<double>() : nullptr, hout));
+        record_hook(xc, mode, p);
+        return APK_OK;
     }
     int qkv(PlanLayer &L, bool advance = true) {
         MvParams p{};
@@ -211,7 +320,7 @@ struct TokenLaunch {
         p.q_next = act_layout(P->act_q.p, L.wo->ty, autom.m_eff);
         p.q_next_two_level = autom.two_level;
         p.q_next_need_sum = L.wo->ty == APK_TY_Q4_K;
-        return launch_matvec(c, L.qkv, p, q8);
+        return launch(L.qkv, p, q8, L.wo);
     }
     // next_*: the matvec that will read the updated rows through an RMSNorm (null: none)
     int residual(DevMatrix *W, void *records, const DevMatrix *next_W = nullptr, const float *next_gamma = nullptr,
@@ -219,30 +328,23 @@ struct TokenLaunch {
         const uint32_t H = P->hidden;
         MvParams p{};
         use_records(c, W, autom, records, &p);
-        if (c->world > 1 && c->p2p_ready) {
-            // partial sums straight into every rank's exchange buffer; a small kernel adds them
+        p.xin.index = -1;
+        have_sumsq = false;
+        if (uses_xch(c)) {
+            // partial sums straight into every rank's exchange buffer; the kernel that reads the
+            // residual next gathers them in its prologue
             p.epi = EPI_PEERS;
             p.xch = c->xch;
             p.xch_row = (int)H;
-            APK_TRY(launch_matvec(c, W, p, autom));
-            XchReduceParams rp{};
-            rp.xch = c->xch;
-            rp.x = P->x[cur].as<float>(); rp.ldx = (int)H;
-            rp.xout = P->x[cur ^ 1].as<float>(); rp.ldxout = (int)H;
-            rp.n = (int)H; rp.m = (int)m;
-            rp.err = c->d_err;
-            rp.pdl = c->use_pdl ? 1 : 0;
-            const unsigned grid = (unsigned)(((size_t)m * H + 1023) / 1024);
-            CUDA_TRY(launch_ex(c, xch_reduce_kernel, dim3(grid), dim3(256), 0, c->use_pdl, rp));
-            c->st.launches++;
-            cur ^= 1;
-            return APK_OK;
+            p.xout = XchSeq{n_xch, per_token()};
+            pending_xch = n_xch++;
+            return launch(W, p, autom, next_W);
         }
         if (c->world > 1) {
             p.epi = EPI_STORE;
             p.y = P->yp.as<float>();
             p.ldy = (int)H;
-            APK_TRY(launch_matvec(c, W, p, autom));
+            APK_TRY(launch(W, p, autom, nullptr));
             APK_TRY(nccl_allreduce(c, P->yp.as<float>(), (size_t)m * H));
             pending_add = true;
             return APK_OK;
@@ -252,16 +354,19 @@ struct TokenLaunch {
         p.ldy = (int)H;
         p.resid = P->x[cur].as<float>();
         p.ldr = (int)H;
-        if (next_W && can_prenorm(next_W, next_mode)) {
-            p.nq_gamma = next_gamma;
-            p.nq_act = act_layout(P->act_h.p, next_W->ty, next_mode.m_eff);
-            p.nq_two_level = next_mode.two_level;
-            p.nq_need_sum = next_W->ty == APK_TY_Q4_K;
+        if (next_W && c->fuse_norm != 0 && H % 32 == 0) {
             p.nq_sumsq = P->sumsq.as<double>();
-            prenormed_for = next_W;
-            prenormed_m_eff = next_mode.m_eff;
+            have_sumsq = true;
+            if (can_prenorm(next_W, next_mode)) {
+                p.nq_gamma = next_gamma;
+                p.nq_act = act_layout(P->act_h.p, next_W->ty, next_mode.m_eff);
+                p.nq_two_level = next_mode.two_level;
+                p.nq_need_sum = next_W->ty == APK_TY_Q4_K;
+                prenormed_for = next_W;
+                prenormed_m_eff = next_mode.m_eff;
+            }
         }
-        return launch_matvec(c, W, p, autom);
+        return launch(W, p, autom, next_W);
     }
     int wo(PlanLayer &L) { return residual(L.wo, P->act_q.p, L.gateup, L.ffn_norm, q8); }
     int gateup(PlanLayer &L, bool advance = true) {
@@ -272,7 +377,7 @@ struct TokenLaunch {
         p.next_two_level = autom.two_level;
         p.next_need_sum = L.down->ty == APK_TY_Q4_K;
         p.ffn = (int)P->ffn_l;
-        return launch_matvec(c, L.gateup, p, q8);
+        return launch(L.gateup, p, q8, L.down);
     }
     // after down comes the next layer's Q|K|V, or the output head
     int down(PlanLayer &L, PlanLayer *next) {
@@ -280,13 +385,14 @@ struct TokenLaunch {
         return residual(L.down, P->act_d.p, P->head, P->out_norm, autom);
     }
     int head(bool advance = true) {
-        // finish_hidden: rmsnorm + output.matmul(x, m) (QuantMat::matmul: Q8 at m == 1, f32 dots above)
+        // finish_hidden: rmsnorm + output.matmul(x, m) (QuantMat::matmul: Q8 at m == 1, f32 dots above);
+        // the output-normed rows are kept: TokenOut::Rows hands them to the caller
         MvParams p{};
-        APK_TRY(normed_input(P->head, P->out_norm, autom, &p, advance));
+        APK_TRY(normed_input(P->head, P->out_norm, autom, &p, advance, P->hidden_out.as<float>()));
         p.epi = EPI_STORE;
         p.y = P->logits.as<float>();
         p.ldy = (int)P->vocab_l;
-        return launch_matvec(c, P->head, p, autom);
+        return launch(P->head, p, autom, nullptr);
     }
 };
 
@@ -372,6 +478,9 @@ int apk_decode_token(apk_ctx *c, const apk_token_req *r, apk_token_out *out) {
     CUDA_TRY(cudaGraphLaunch(P->exec[m][r->argmax ? 1 : 0], c->stream));
     c->st.launches += P->launches[m][r->argmax ? 1 : 0];
     std::vector<float> gathered;
+    // TokenOut::Rows: the output-normed hidden rows next to the per-row winners (or logits)
+    if (out->hidden)
+        CUDA_TRY(cudaMemcpyAsync(out->hidden, P->hidden_out.p, (size_t)m * H * 4, cudaMemcpyDeviceToHost, c->stream));
     if (r->argmax) {
         CUDA_TRY(cudaMemcpyAsync(out->argmax, P->amax.p, m * sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
     } else if (c->world == 1 || m == 1) {
@@ -417,6 +526,16 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
             for (uint32_t l = 0; l < n_launch; ++l) {
                 PlanLayer &L = P->L[l];
                 TokenLaunch T(c, P, m);  // fresh state: reads x[0], never flips buffers
+                T.first = false;         // the token counter stays: the flags of the token above satisfy every wait
+                if (uses_xch(c)) {
+                    // as in the real token: Q|K|V, gate/up and the head gather the exchange in front of them
+                    T.n_xch = (int)(2 * l + (kind >= 2 ? 1 : 0));
+                    if (kind == 0 && l > 0) T.pending_xch = (int)(2 * l - 1);
+                    if (kind == 2) T.pending_xch = (int)(2 * l);
+                    if (kind == 4) T.pending_xch = (int)(2 * P->n_layers - 1);
+                } else if (c->world == 1 && c->fuse_norm != 0 && (kind == 0 ? l > 0 : (kind == 2 || kind == 4))) {
+                    T.have_sumsq = true;  // left in place by the token above
+                }
                 // the launch variants of the real token: inputs that a residual epilogue prepared
                 const DevMatrix *nw = kind == 0 ? L.qkv : kind == 2 ? L.gateup : kind == 4 ? P->head : nullptr;
                 const ActMode nm = kind == 4 ? T.autom : T.q8;
@@ -497,6 +616,130 @@ int apk_decode_replay(apk_ctx *c, const apk_token_req *r, uint32_t iters, float 
     APK_TRY(finish(c));
     CUDA_TRY(cudaEventElapsedTime(elapsed_ms, c->ev0, c->ev1));
     c->st.decode_successes++;
+    return APK_OK;
+}
+
+int apk_debug_set_wait_limit(apk_ctx *c, uint64_t cycles) {
+    if (!c) return fail(APK_ERR_INVALID_ARG, "null context");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    CUDA_TRY(cudaStreamSynchronize(c->stream));
+    c->wait_limit = cycles ? (long long)std::min<uint64_t>(cycles, (uint64_t)1 << 62) : WAIT_LIMIT_DEFAULT;
+    c->plan.reset();  // captured launches carry the old budget
+    return APK_OK;
+}
+
+int apk_debug_xch_timeout(apk_ctx *c) {
+    if (!c) return fail(APK_ERR_INVALID_ARG, "null context");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    // Two exchange buffers on this one GPU stand for ranks 0 and 1.  Rank 0's own tile flags are
+    // raised, "rank 1" never delivers: the collecting kernel must give up after the wait budget,
+    // leave an error word and end normally.
+    const int n = 256;
+    float *buf[2] = {nullptr, nullptr};
+    for (auto &b : buf) {
+        CUDA_TRY(cudaMalloc((void **)&b, XCH_BYTES));
+        CUDA_TRY(cudaMemsetAsync(b, 0, XCH_BYTES, c->stream));
+    }
+    APK_TRY(c->x_dev.ensure(n * sizeof(float)));
+    APK_TRY(c->y_dev.ensure(n * sizeof(float)));
+    CUDA_TRY(cudaMemsetAsync(c->x_dev.p, 0, n * sizeof(float), c->stream));
+    const uint32_t ones[3] = {1u, 1u, 1u};
+    CUDA_TRY(cudaMemcpyAsync(xch_tok(buf[0]), ones, 4, cudaMemcpyHostToDevice, c->stream));
+    CUDA_TRY(cudaMemcpyAsync(xch_flags(buf[0]), ones, 8, cudaMemcpyHostToDevice, c->stream));  // rank 0, tiles 0 and 1
+    XchReduceParams rp{};
+    rp.xch.slots[0] = buf[0];
+    rp.xch.slots[1] = buf[1];
+    rp.xch.rank = 0;
+    rp.xch.world = 2;
+    rp.seq = XchSeq{0, 1};
+    rp.x = c->x_dev.as<float>(); rp.ldx = n;
+    rp.xout = c->y_dev.as<float>(); rp.ldxout = n;
+    rp.n = n; rp.m = 1;
+    rp.err = c->d_err;
+    rp.pdl = 0;
+    rp.wait_limit = c->wait_limit;
+    xch_reduce_kernel<<<1, 256, 0, c->stream>>>(rp);
+    cudaError_t e = cudaGetLastError();
+    c->st.launches++;
+    c->st.calls++;
+    const int rc = e == cudaSuccess ? finish(c) : fail(APK_ERR_CUDA, "launch: %s", cudaGetErrorString(e));
+    cudaStreamSynchronize(c->stream);
+    for (auto &b : buf) cudaFree(b);
+    return rc;
+}
+
+int apk_debug_token_records(apk_ctx *c, const apk_token_req *r, uint32_t max_records, float *x, float *d, float *sum,
+                            int8_t *q, int32_t *meta, uint32_t *n_records, int dots_launch, int32_t *dots,
+                            size_t dots_elems) {
+    if (!c || !x || !d || !sum || !q || !meta || !n_records || max_records == 0)
+        return fail(APK_ERR_INVALID_ARG, "token_records: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    APK_TRY(validate_token_req(c, r));
+    if (c->world != 1 || uses_xch(c)) return fail(APK_DECLINE_INVALID_STATE, "token_records runs on an unsharded context");
+    APK_TRY(ensure_graph(c, r));
+    Plan *P = c->plan.get();
+    const uint32_t m = r->m, H = P->hidden, nblk = H / 32;
+    const size_t x_bytes = (size_t)APK_MAX_M * H * 4;
+    const size_t slab = (x_bytes + act_bytes(APK_TY_Q4_K, MAX_M_EFF, H) + 255) & ~(size_t)255;
+    APK_TRY(c->dump.ensure(slab * max_records));
+    if (dots && dots_elems) {
+        APK_TRY(c->misc.ensure(dots_elems * sizeof(int32_t)));
+        CUDA_TRY(cudaMemsetAsync(c->misc.p, 0xff, dots_elems * sizeof(int32_t), c->stream));
+    }
+    CUDA_TRY(cudaMemsetAsync(c->dump.p, 0, slab * max_records, c->stream));
+    CUDA_TRY(cudaMemcpyAsync(P->xin.p, r->x, (size_t)m * H * 4, cudaMemcpyHostToDevice, c->stream));
+    if (r->rot_dim)
+        CUDA_TRY(cudaMemcpyAsync(P->rope.p, r->rope, (size_t)m * (r->rot_dim / 2) * 2 * 4, cudaMemcpyHostToDevice, c->stream));
+    c->rec_dump = c->dump.as<uint8_t>();
+    c->rec_slab = slab;
+    c->rec_idx = 0;
+    c->rec_cap = max_records;
+    c->rec_meta.clear();
+    c->launch_no = 0;
+    c->dots_launch = dots && dots_elems ? dots_launch : -1;
+    c->dots_dump = dots && dots_elems ? c->misc.as<int32_t>() : nullptr;
+    c->dots_cap = dots_elems;
+    int nl = 0;
+    const int rc = enqueue_token(c, P, m, 0, &nl);
+    c->rec_dump = nullptr;
+    c->dots_dump = nullptr;
+    c->dots_launch = -1;
+    const uint32_t n = c->rec_idx;
+    *n_records = n;
+    if (rc) {
+        cudaStreamSynchronize(c->stream);
+        return rc;
+    }
+    std::vector<uint8_t> host(slab * n);
+    CUDA_TRY(cudaMemcpyAsync(host.data(), c->dump.p, host.size(), cudaMemcpyDeviceToHost, c->stream));
+    if (dots && dots_elems)
+        CUDA_TRY(cudaMemcpyAsync(dots, c->misc.p, dots_elems * sizeof(int32_t), cudaMemcpyDeviceToHost, c->stream));
+    c->st.calls++;
+    APK_TRY(finish(c));
+    // per record: x [APK_MAX_M][H] | d, sum [MAX_M_EFF][H/32] | q [MAX_M_EFF][H]; meta = {rows, two-level, launch, K-step}
+    for (uint32_t i = 0; i < n; ++i) {
+        const RecMeta &mt = c->rec_meta[i];
+        const uint8_t *sl = host.data() + slab * i;
+        memcpy(x + (size_t)i * APK_MAX_M * H, sl, (size_t)m * H * 4);
+        ActLayout L;
+        L.base = nullptr; L.ke = mt.ke; L.m_eff = mt.m_eff;
+        const int kt = L.kt(), mp = L.mp(), rec = L.rec_bytes(), qb = L.q_bytes();
+        const uint8_t *recs = sl + x_bytes;
+        for (int row = 0; row < mt.m_eff; ++row)
+            for (uint32_t b = 0; b < nblk; ++b) {
+                const uint8_t *rr = recs + (size_t)(b / kt) * rec;
+                const int bl = (int)(b % kt);
+                int8_t *qo = q + ((size_t)i * MAX_M_EFF + row) * H + (size_t)b * 32;
+                memcpy(qo, rr + ((bl * 2 + 0) * mt.m_eff + row) * 16, 16);
+                memcpy(qo + 16, rr + ((bl * 2 + 1) * mt.m_eff + row) * 16, 16);
+                memcpy(d + ((size_t)i * MAX_M_EFF + row) * nblk + b, rr + qb + (bl * mp + row) * 4, 4);
+                memcpy(sum + ((size_t)i * MAX_M_EFF + row) * nblk + b, rr + qb + (kt * mp + bl * mp + row) * 4, 4);
+            }
+        meta[4 * i] = mt.m_eff; meta[4 * i + 1] = mt.two_level; meta[4 * i + 2] = mt.launch; meta[4 * i + 3] = mt.ke;
+    }
     return APK_OK;
 }
 

@@ -62,8 +62,9 @@ constexpr int ERRW_CONSUMER_TIMEOUT = 2;
 constexpr int ERRW_PEER_TIMEOUT = 3;
 constexpr int ERRW_FINISHER_TIMEOUT = 4;
 
-// Spin budget of one mbarrier wait, in SM clock cycles (~2 s).
-constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+// Default spin budget of one bounded wait, in SM clock cycles (~2 s).  Kernels take the
+// budget as a parameter so that a test can make a wait run out in a millisecond.
+constexpr long long WAIT_LIMIT_DEFAULT = 4000000000LL;
 
 enum Epilogue : int {
     EPI_STORE = 0,   // y[m][row] = v
@@ -76,23 +77,34 @@ enum Epilogue : int {
 // One-shot exchange of row-parallel partial sums between the ranks of a
 // tensor-parallel group over peer-mapped memory (plain stores across NVLink; no
 // multicast).  Every rank owns one buffer, laid out
-//   slots [2 parity][APK_XCH_MAX_RANKS][XCH_ROW_FLOATS] f32 | flags[APK_XCH_MAX_RANKS] u32 | epoch u32 | done u32 | dead u32
-// Rank s writes its partial vector into slot (parity, s) of EVERY rank's buffer
-// (the matvec epilogue), then raises flags[s] = epoch on every rank; a rank
-// adds the slots 0..world-1 in rank order once all its flags show the epoch.
+//   slots [2 parity][XCH_MAX_RANKS][XCH_ROW_FLOATS] f32 | flags[XCH_MAX_RANKS][XCH_MAX_TILES] u32 | tok u32
+// Exchanges are numbered e = 1, 2, ... for the life of the group (every rank runs the
+// same sequence).  The CTA of rank s that closes a 128-row tile of the row-parallel matvec
+// stores the tile's partial rows into slot (e & 1, s) of EVERY rank's buffer and then sets
+// flags[s][tile] = e there (release, system scope).  The kernel that consumes the sum
+// waits (bounded) until all world * tiles flags of its own buffer have reached e and adds
+// the slots in rank order 0..world-1: deterministic, one NVLink hop, no extra launch.
+// Two parities suffice: a rank can run at most one exchange ahead of the slowest one,
+// because passing exchange e + 1 needs every rank's flags for e + 1.
+// `tok` counts decoded tokens; e = (tok - 1) * exchanges per token + index in the token + 1.
 constexpr int XCH_MAX_RANKS = 8;
 constexpr int XCH_ROW_FLOATS = 8 * 16384;  // m * hidden floats per slot
+constexpr int XCH_MAX_TILES = 128;         // hidden <= 16384
 constexpr size_t XCH_SLOTS_BYTES = (size_t)2 * XCH_MAX_RANKS * XCH_ROW_FLOATS * sizeof(float);
-constexpr size_t XCH_BYTES = XCH_SLOTS_BYTES + 256;
+constexpr size_t XCH_FLAGS_BYTES = (size_t)XCH_MAX_RANKS * XCH_MAX_TILES * sizeof(uint32_t);
+constexpr size_t XCH_BYTES = XCH_SLOTS_BYTES + XCH_FLAGS_BYTES + 256;
 
 struct XchPeers {
     float *slots[XCH_MAX_RANKS];  // peer-mapped base of each rank's buffer (own included)
     int rank, world;
 };
 __host__ __device__ inline uint32_t *xch_flags(float *base) { return reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(base) + XCH_SLOTS_BYTES); }
-__host__ __device__ inline uint32_t *xch_epoch(float *base) { return xch_flags(base) + XCH_MAX_RANKS; }
-__host__ __device__ inline uint32_t *xch_done(float *base) { return xch_flags(base) + XCH_MAX_RANKS + 1; }
-__host__ __device__ inline uint32_t *xch_dead(float *base) { return xch_flags(base) + XCH_MAX_RANKS + 2; }
+__host__ __device__ inline uint32_t *xch_tok(float *base) { return xch_flags(base) + XCH_MAX_RANKS * XCH_MAX_TILES; }
+// Where a kernel stands in the exchange sequence of its token.
+struct XchSeq {
+    int index = -1;     // exchange index within the token (0-based); -1 = this launch takes no part
+    int per_token = 0;  // exchanges per token
+};
 
 // Prepared activations as the matvec kernel consumes them: per K-step of `ke`
 // elements (kt = ke/32 blocks) one record
@@ -113,7 +125,7 @@ struct ActLayout {
 };
 
 struct PrepParams {
-    const void *x; int x_is_bf16; int ldx;   // [m][n] activations
+    const float *x; int ldx;                 // [m][n] activations
     const float *add; int ldadd;             // optional addend (residual / combined partial sums)
     float *xout; int ldxout;                 // optional: store x + add
     const float *gamma; float eps;           // optional RMSNorm weight
@@ -121,6 +133,9 @@ struct PrepParams {
     int n, m;
     ActLayout out;
     int two_level, need_sum;
+    // optional: f64 sums of squares of the 32-element blocks of x, [m][n / 32], left by the
+    // kernel that produced x; the RMSNorm then adds those instead of re-reading the row
+    const double *sumsq;
 };
 
 // How the kernel gets its activations.
@@ -144,12 +159,21 @@ struct MvParams {
     PrepParams prep;    // PRO_QUANT inputs (prep.out is ignored: blocks go to shared memory)
     int pdl;            // launched with a programmatic dependency on the previous kernel
     unsigned long long *partials;  // [gridDim.x][2][MAX_M_EFF][128] tagged partial sums (see part_store)
-    int *counters;      // [n_tiles] zeroed scratch; not used by the tagged hand-off
     int *err;           // error word
+    long long wait_limit;  // cycle budget of every bounded wait in this launch
     int32_t *dump;      // optional [m_eff][n_out][nb] int32 block dots
+    uint8_t *act_dump;  // optional: CTA 0 copies its resident activation records here (parity instrumentation)
     int inflight;       // K-steps of weights one CTA keeps in flight at a time (>= 1)
     int inflight_pre;   // the same while the previous kernel has not finished yet (>= 1)
     unsigned long long *timeline;  // optional [gridDim.x][8] globaltimer stamps (trace)
+    // The matvec that follows this one in the stream (optional).  Once a CTA has asked for all
+    // of its own units, HBM would idle while tiles are closed and the next kernel starts: the
+    // producer lane uses that time to pull the first units of the next kernel's CTA of the same
+    // index into L2, so that its ring fills from L2 instead of from DRAM.
+    const uint8_t *next_W;
+    uint32_t next_tile_bytes;
+    int next_ty, next_nb, next_n_tiles, next_KS, next_grid;
+    int next_units, next_pace;         // how many units at most; nanoseconds between two of them
     // epilogue
     int epi;
     float *y; int ldy;
@@ -161,17 +185,26 @@ struct MvParams {
     const float *rope; int half;       // [m][half][2] (sin, cos)
     ActLayout q_next;                  // optional: roped Q heads packed as the next matvec's activations
     int q_next_two_level, q_next_need_sum;
-    // EPI_PEERS
+    // Tensor-parallel exchange (see XchPeers).  xout: EPI_PEERS, this launch feeds exchange
+    // xout.index.  xin: PRO_QUANT, the input row is prep.x + the rank-ordered sum of exchange
+    // xin.index (CTA 0 stores it to prep.xout).  tok_inc: CTA 0 advances the token counter
+    // (set on the first launch of a token, which takes part in no exchange).
     XchPeers xch; int xch_row;         // floats per token row in a slot (= hidden)
+    XchSeq xin, xout;
+    int tok_inc;
     // EPI_SWIGLU
     float *act_f32; int ld_act;        // optional f32 swiglu rows [m][ffn]
     ActLayout act_next;                // optional packed activations for the down projection
     int next_two_level, next_need_sum;
     int ffn;                           // real ffn rows (gate rows)
-    // EPI_ADD, optional: the updated residual rows feed an RMSNorm and a matvec next.  Each tile
-    // quantises its 128 elements times the norm weight right away (codes do not depend on the
-    // row-wide scale, scales are linear in it) and leaves the f64 sums of squares of its four
-    // blocks; the next kernel multiplies the block scales by 1/sqrt(mean + eps) (norm_sumsq).
+    // EPI_ADD, optional: the updated residual rows feed an RMSNorm and a matvec next.
+    //  nq_sumsq: each tile leaves the f64 sums of squares of its four blocks, [m_out][n_out / 32];
+    //    the next kernel adds them up instead of reducing the row again (exact: the quantisation
+    //    itself happens there, on f32(f64(x) * scale) * gamma as ops::rmsnorm_into orders it).
+    //  nq_gamma (with nq_sumsq): the tile also quantises its 128 elements times the norm weight
+    //    right away, before the row-wide scale exists, and the next kernel multiplies the block
+    //    scales by 1/sqrt(mean + eps) (norm_sumsq).  Cheaper, but codes can differ from the exact
+    //    order by one where v/d lands on a .5 boundary: an opt-in approximation.
     const float *nq_gamma;             // [n_out] weight of the next norm; null = off
     ActLayout nq_act;                  // the next matvec's activation records
     int nq_two_level, nq_need_sum;
@@ -212,19 +245,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 // Wait for a phase with a cycle budget.  false = gave up (caller records it).
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t *bar, uint32_t parity, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
 #pragma unroll 1
         for (int i = 0; i < 256; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+        if (clock64() - t0 > limit) return false;
     }
 }
 // Same, for the producer lane: it has nothing else to do, so it backs off between
 // polls instead of competing with the consumer warps for issue slots.
-__device__ __forceinline__ bool mbar_wait_bounded_relaxed(uint64_t *bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_bounded_relaxed(uint64_t *bar, uint32_t parity, long long limit) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
@@ -233,7 +266,7 @@ __device__ __forceinline__ bool mbar_wait_bounded_relaxed(uint64_t *bar, uint32_
             if (mbar_try_wait(bar, parity)) return true;
             __nanosleep(40);
         }
-        if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+        if (clock64() - t0 > limit) return false;
     }
 }
 // Partial sums of a tile shared by several CTAs travel as one 64-bit word per
@@ -308,18 +341,6 @@ __device__ __forceinline__ void mma_block_s8_acc(int (&d)[4], const uint4 &a, ui
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
         : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
-}
-
-__device__ __forceinline__ int dot32(const int4 &w0, const int4 &w1, const int4 &x0, const int4 &x1) {
-    int s = __dp4a(w0.x, x0.x, 0);
-    s = __dp4a(w0.y, x0.y, s);
-    s = __dp4a(w0.z, x0.z, s);
-    s = __dp4a(w0.w, x0.w, s);
-    s = __dp4a(w1.x, x1.x, s);
-    s = __dp4a(w1.y, x1.y, s);
-    s = __dp4a(w1.z, x1.z, s);
-    s = __dp4a(w1.w, x1.w, s);
-    return s;
 }
 
 // ----------------------------------------------------- activation quantiser
@@ -405,11 +426,20 @@ __device__ __forceinline__ void quantize_store(const ActLayout &L, int two_level
 }
 
 __device__ __forceinline__ float load_x(const PrepParams &p, int m, int i) {
-    float v = p.x_is_bf16
-                  ? __bfloat162float(reinterpret_cast<const __nv_bfloat16 *>(p.x)[(size_t)m * p.ldx + i])
-                  : reinterpret_cast<const float *>(p.x)[(size_t)m * p.ldx + i];
+    float v = p.x[(size_t)m * p.ldx + i];
     if (p.add) v = __fadd_rn(v, p.add[(size_t)m * p.ldadd + i]);
     return v;
+}
+
+// The sum of squares of a row from the per-block f64 sums its producer left: lane-strided
+// partial sums, then a butterfly.  One fixed order, used by every kernel that takes the
+// hand-off, so they all get the same scale.
+__device__ __forceinline__ double sumsq_total(const double *sq, int nblk, int lane) {
+    double ss = 0.0;
+    for (int i = lane; i < nblk; i += 32) ss += sq[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    return ss;
 }
 
 // RMSNorm scale exactly as ops::rmsnorm_into does it (crates/allpaka-backend/
@@ -417,6 +447,10 @@ __device__ __forceinline__ float load_x(const PrepParams &p, int m, int i) {
 // f64 sum order differs from the reference's 8-lane walk; the difference is
 // confined to the last bits of an f64 that is then rounded to f32.
 __device__ __forceinline__ double block_rms_scale(const PrepParams &p, int m, double *red) {
+    if (p.sumsq) {
+        const double tot = sumsq_total(p.sumsq + (size_t)m * (p.n >> 5), p.n >> 5, threadIdx.x & 31);
+        return 1.0 / sqrt(tot / (double)p.n + (double)p.eps);
+    }
     double ss = 0.0;
     for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
         const double v = (double)load_x(p, m, i);
@@ -463,76 +497,77 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+// Number of the exchange a launch takes part in (see XchPeers).
+__device__ __forceinline__ uint32_t xch_number(float *mine, const XchSeq &s) {
+    return (__ldcg(xch_tok(mine)) - 1u) * (uint32_t)s.per_token + (uint32_t)s.index + 1u;
+}
+// Thread t of nthreads waits (bounded) until its share of this rank's world * n_tiles flags
+// has reached exchange e.  false = the budget ran out.  The caller follows with a barrier of
+// the same threads before any of them reads the slots.
+__device__ __forceinline__ bool xch_wait_flags(float *mine, int world, int n_tiles, uint32_t e, int t, int nthreads,
+                                               long long limit) {
+    const long long t0 = clock64();
+    for (int i = t; i < world * n_tiles; i += nthreads) {
+        const uint32_t *f = xch_flags(mine) + (i / n_tiles) * XCH_MAX_TILES + i % n_tiles;
+        while ((int32_t)(ld_acquire_sys(f) - e) < 0) {
+            if (clock64() - t0 > limit) return false;
+            __nanosleep(20);
+        }
+    }
+    return true;
+}
+// x[i..i+3] + (slot 0 + slot 1 + ...)[i..i+3] in rank order: the one summation order of an exchange.
+__device__ __forceinline__ float4 xch_sum4(const float *x, const float *mine, uint32_t e, int world, size_t off) {
+    float4 acc = __ldcg(reinterpret_cast<const float4 *>(x));
+    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float *s0 = mine + (size_t)(e & 1u) * XCH_MAX_RANKS * XCH_ROW_FLOATS + off;
+    for (int r = 0; r < world; ++r) {
+        const float4 v = __ldcg(reinterpret_cast<const float4 *>(s0 + (size_t)r * XCH_ROW_FLOATS));
+        sum.x = __fadd_rn(sum.x, v.x); sum.y = __fadd_rn(sum.y, v.y);
+        sum.z = __fadd_rn(sum.z, v.z); sum.w = __fadd_rn(sum.w, v.w);
+    }
+    acc.x = __fadd_rn(acc.x, sum.x); acc.y = __fadd_rn(acc.y, sum.y);
+    acc.z = __fadd_rn(acc.z, sum.z); acc.w = __fadd_rn(acc.w, sum.w);
+    return acc;
+}
 
 struct XchReduceParams {
     XchPeers xch;
+    XchSeq seq;                // which exchange to collect
     const float *x; int ldx;   // residual stream in  [m][n]
     float *xout; int ldxout;   // residual stream out [m][n] = x + sum over ranks of the partial vectors
     int n, m;
     int *err;
     int pdl;
+    long long wait_limit;
 };
 
-// grid = ceil(m*n / 1024), 256 threads, four floats per thread.  Runs after the
-// row-parallel matvec of this rank (programmatic dependency): announces this
-// rank's slot to every peer, waits (bounded) until every rank's slot for the
-// same epoch has been announced here, then adds the slots in rank order.
+// Stand-alone form of the collecting side (batches of m > 1 rows, whose activations are
+// quantised by a separate pass): grid = ceil(m*n / 1024), 256 threads, four floats per
+// thread.  Waits (bounded) for every rank's tile flags of the exchange, then adds the slots
+// in rank order onto the residual rows.
 __global__ void __launch_bounds__(256) xch_reduce_kernel(XchReduceParams p) {
     if (p.pdl) {
         pdl_launch_dependents();
         pdl_wait();  // this rank's matvec (and its peer stores) is complete
     }
     float *mine = p.xch.slots[p.xch.rank];
-    const uint32_t e = __ldcg(xch_epoch(mine)) + 1u;
+    const uint32_t e = xch_number(mine, p.seq);
     __shared__ int s_ok;
     if (threadIdx.x == 0) s_ok = 1;
-    if (blockIdx.x == 0 && threadIdx.x < p.xch.world)
-        st_release_sys(xch_flags(p.xch.slots[threadIdx.x]) + p.xch.rank, e);
     __syncthreads();
-    if (threadIdx.x < p.xch.world) {
-        const uint32_t *f = xch_flags(mine) + threadIdx.x;
-        volatile uint32_t *dead = xch_dead(mine);
-        const long long t0 = clock64();
-        bool ok = false;
-        while (!*dead) {
-            if ((int32_t)(ld_acquire_sys(f) - e) >= 0) { ok = true; break; }
-            if (clock64() - t0 > WAIT_LIMIT_CYCLES) break;
-            __nanosleep(20);
-        }
-        if (!ok) {
-            // a peer never announced: record it, stop waiting for good, finish normally
-            s_ok = 0;
-            *dead = 1u;
-            atomicExch(p.err, ERRW_PEER_TIMEOUT);
-        }
+    if (!xch_wait_flags(mine, p.xch.world, (p.n + TILE_ROWS - 1) / TILE_ROWS, e, threadIdx.x, blockDim.x, p.wait_limit)) {
+        // a peer never delivered: record it and finish normally
+        s_ok = 0;
+        atomicExch(p.err, ERRW_PEER_TIMEOUT);
     }
     __syncthreads();
-    const uint32_t parity = e & 1u;
     const size_t total = (size_t)p.m * p.n;
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (i < total && s_ok) {
         const int m = (int)(i / p.n), col = (int)(i % p.n);
-        float4 acc = *reinterpret_cast<const float4 *>(p.x + (size_t)m * p.ldx + col);
-        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < p.xch.world; ++r) {  // fixed order: run-to-run identical
-            const float4 v = __ldcg(reinterpret_cast<const float4 *>(
-                mine + ((size_t)parity * XCH_MAX_RANKS + r) * XCH_ROW_FLOATS + (size_t)m * p.n + col));
-            sum.x = __fadd_rn(sum.x, v.x); sum.y = __fadd_rn(sum.y, v.y);
-            sum.z = __fadd_rn(sum.z, v.z); sum.w = __fadd_rn(sum.w, v.w);
-        }
-        acc.x = __fadd_rn(acc.x, sum.x); acc.y = __fadd_rn(acc.y, sum.y);
-        acc.z = __fadd_rn(acc.z, sum.z); acc.w = __fadd_rn(acc.w, sum.w);
+        const float4 acc = xch_sum4(p.x + (size_t)m * p.ldx + col, mine, e, p.xch.world, (size_t)m * p.n + col);
         *reinterpret_cast<float4 *>(p.xout + (size_t)m * p.ldxout + col) = acc;
-    }
-    // the last CTA out advances the epoch (every CTA has read it by then)
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence();
-        const uint32_t old = atomicAdd(xch_done(mine), 1u);
-        if (old == gridDim.x - 1) {
-            *xch_done(mine) = 0u;
-            *xch_epoch(mine) = e;
-        }
     }
 }
 
@@ -696,22 +731,6 @@ __global__ void synth_q4_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) 
 
 // ------------------------------------------------------------ the matvec
 
-__device__ __forceinline__ void scale_min_k4_dev(int j, uint32_t s0, uint32_t s1, uint32_t s2, float &sc,
-                                                 float &mn) {
-    // crates/allpaka-dtype/src/lib.rs:382-390 on the 12 packed bytes as three LE words
-    auto byte = [&](int i) -> uint32_t {
-        const uint32_t w = i < 4 ? s0 : (i < 8 ? s1 : s2);
-        return (w >> (8 * (i & 3))) & 0xffu;
-    };
-    if (j < 4) {
-        sc = (float)(byte(j) & 63u);
-        mn = (float)(byte(j + 4) & 63u);
-    } else {
-        sc = (float)((byte(j + 4) & 0xfu) | ((byte(j - 4) >> 6) << 4));
-        mn = (float)((byte(j + 4) >> 4) | ((byte(j) >> 6) << 4));
-    }
-}
-
 // Shared memory map of the matvec kernel (dynamic, 128-byte aligned base):
 //   [0, 64)      full barriers       [64, 128) empty barriers
 //   [128, 136)   barrier of the resident-activation load    [136, 144) prologue scratch released
@@ -802,7 +821,7 @@ __device__ __forceinline__ void prologue_gamma(const MvParams &p, int tid, float
 
 template <int M>
 __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, float *hs, float *red, int tid,
-                                               const float (&g)[PRO_CH]) {
+                                               const float (&g)[PRO_CH], double ssq_in) {
     const PrepParams &pp = p.prep;
     const int warp = tid >> 5, lane = tid & 31;
     const int n = pp.n, nb = n >> 5;
@@ -813,41 +832,68 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
     const int rec_bytes = L.rec_bytes(), q_bytes = L.q_bytes();
     double *dred = reinterpret_cast<double *>(red);
     float v[PRO_CH];
+    if (p.xin.index >= 0) {
+        // Tensor parallel: the row is the residual plus the partial sums every rank stored
+        // into this rank's exchange buffer.  Wait (bounded) for their tile flags, then add
+        // the slots in rank order; CTA 0 keeps the new residual row.
+        float *mine = p.xch.slots[p.xch.rank];
+        const uint32_t e = xch_number(mine, p.xin);
+        if (!xch_wait_flags(mine, p.xch.world, (n + TILE_ROWS - 1) / TILE_ROWS, e, tid, N_CONSUMERS, p.wait_limit))
+            atomicExch(p.err, ERRW_PEER_TIMEOUT);  // goes on with what is there; the host reports the error
+        consumer_bar();
 #pragma unroll
-    for (int j = 0; j < PRO_J; ++j) {
-        const int e = 4 * tid + PRO_CHUNK * j;
-        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (e < n) {
-            if (pp.x_is_bf16) {
-                const uint2 r = *reinterpret_cast<const uint2 *>(reinterpret_cast<const __nv_bfloat16 *>(hs) + e);
-                x.x = __uint_as_float(r.x << 16); x.y = __uint_as_float(r.x & 0xffff0000u);
-                x.z = __uint_as_float(r.y << 16); x.w = __uint_as_float(r.y & 0xffff0000u);
-            } else {
-                x = *reinterpret_cast<const float4 *>(hs + e);
+        for (int j = 0; j < PRO_J; ++j) {
+            const int el = 4 * tid + PRO_CHUNK * j;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (el < n) {
+                x = xch_sum4(pp.x + el, mine, e, p.xch.world, (size_t)el);
+                if (pp.xout && blockIdx.x == 0) *reinterpret_cast<float4 *>(pp.xout + el) = x;
             }
-            if (pp.add) {
-                const float4 a = *reinterpret_cast<const float4 *>(pp.add + e);
-                x.x = __fadd_rn(x.x, a.x); x.y = __fadd_rn(x.y, a.y); x.z = __fadd_rn(x.z, a.z); x.w = __fadd_rn(x.w, a.w);
-            }
-            if (pp.xout && blockIdx.x == 0) *reinterpret_cast<float4 *>(pp.xout + e) = x;
+            v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
         }
-        v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+    } else {
+#pragma unroll
+        for (int j = 0; j < PRO_J; ++j) {
+            const int e = 4 * tid + PRO_CHUNK * j;
+            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (e < n) {
+                x = *reinterpret_cast<const float4 *>(hs + e);
+                if (pp.add) {
+                    const float4 a = *reinterpret_cast<const float4 *>(pp.add + e);
+                    x.x = __fadd_rn(x.x, a.x); x.y = __fadd_rn(x.y, a.y); x.z = __fadd_rn(x.z, a.z); x.w = __fadd_rn(x.w, a.w);
+                }
+                if (pp.xout && blockIdx.x == 0) *reinterpret_cast<float4 *>(pp.xout + e) = x;
+            }
+            v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
+        }
     }
     if (pp.gamma) {
         // ops::rmsnorm_into (ops/norm.rs:193-198): f64 sum of squares, f64 1/sqrt(mean + eps)
-        double ss = 0.0;
+        double tot;
+        if (pp.sumsq) {
+            tot = ssq_in;  // the producer of the row left the per-block sums (added up by the caller)
+        } else {
+            double ss = 0.0;
 #pragma unroll
-        for (int j = 0; j < PRO_CH; ++j) ss = fma((double)v[j], (double)v[j], ss);
+            for (int j = 0; j < PRO_CH; ++j) ss = fma((double)v[j], (double)v[j], ss);
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-        if (lane == 0) dred[warp] = ss;
-        consumer_bar();
-        double tot = 0.0;
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) dred[warp] = ss;
+            consumer_bar();
+            tot = 0.0;
 #pragma unroll
-        for (int i = 0; i < N_CONSUMER_WARPS; ++i) tot += dred[i];
+            for (int i = 0; i < N_CONSUMER_WARPS; ++i) tot += dred[i];
+        }
         const double scale = 1.0 / sqrt(tot / (double)n + (double)pp.eps);
 #pragma unroll
         for (int j = 0; j < PRO_CH; ++j) v[j] = __fmul_rn((float)((double)v[j] * scale), g[j]);
+        if (pp.hout && blockIdx.x == 0) {
+#pragma unroll
+            for (int j = 0; j < PRO_J; ++j) {
+                const int e = 4 * tid + PRO_CHUNK * j;
+                if (e < n) *reinterpret_cast<float4 *>(pp.hout + e) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+        }
     }
     if (p.timeline && tid == 0) p.timeline[(size_t)blockIdx.x * 8 + 7] = globaltimer_ns();  // row normalised
     if (pp.need_sum) {
@@ -969,6 +1015,12 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     unsigned long long *tl = p.timeline ? p.timeline + (size_t)blockIdx.x * 8 : nullptr;
     if (tl && tid == 0) tl[0] = globaltimer_ns();
+    // the resident activations arrive by bulk copy, except when the prologue gathers the row
+    // from the exchange slots itself
+    const bool acts_copy = p.pro == PRO_LOAD || (p.pro == PRO_QUANT && p.xin.index < 0);
+    // first launch of a token in a tensor-parallel group: advance the token counter that numbers
+    // the exchanges (single writer; later launches read it after this grid has completed)
+    if (p.tok_inc && blockIdx.x == 0 && tid == 0) *xch_tok(p.xch.slots[p.xch.rank]) += 1u;
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full[s], 1);
@@ -978,6 +1030,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         mbar_init(pro_bar, N_CONSUMER_WARPS);
         mbar_init(red_full, N_CONSUMER_WARPS);
         mbar_init(red_empty, 1);
+        s_flags[3] = 0;  // set once this CTA's last tile is closed
         fence_mbar_init();
     }
     __syncthreads();
@@ -1029,7 +1082,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             const int D0 = p.inflight_pre < D ? p.inflight_pre : D;
             bool stuck = false;
             auto landed = [&](int j) {  // K-step j of this CTA's walk is in shared memory
-                if (j >= 0 && !stuck && !mbar_wait_bounded_relaxed(&full[j % NS], (uint32_t)((j / NS) & 1))) {
+                if (j >= 0 && !stuck && !mbar_wait_bounded_relaxed(&full[j % NS], (uint32_t)((j / NS) & 1), p.wait_limit)) {
                     stuck = true;
                     atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
                 }
@@ -1049,12 +1102,12 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 for (int it = 0; it < pre; ++it) issue_acts(it);
             }
             // the in-CTA prologue borrows the last stage until it is done
-            if (p.pro == PRO_QUANT && !mbar_wait_bounded_relaxed(pro_bar, 0u)) atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
+            if (p.pro == PRO_QUANT && !mbar_wait_bounded_relaxed(pro_bar, 0u, p.wait_limit)) atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
             int it = pre;
             for (; it < n_total; ++it) {
                 const int s = it % NS;
                 const uint32_t ph = (uint32_t)((it / NS) & 1);
-                if (stuck || !mbar_wait_bounded_relaxed(&empty[s], ph ^ 1u)) {
+                if (stuck || !mbar_wait_bounded_relaxed(&empty[s], ph ^ 1u, p.wait_limit)) {
                     atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
                     break;
                 }
@@ -1062,11 +1115,34 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 issue_weights(it);
                 if (streaming) issue_acts(it);
             }
+            // All of this CTA's units are on their way.  While its last tile is closed and the next
+            // kernel starts up HBM would idle: pull the first units of the next matvec's CTA of the
+            // same index into L2, one unit per `next_pace` ns (about the rate at which an SM's share
+            // of HBM delivers them, so that nothing queues in front of the closing crews' small
+            // loads), until the CTA's last tile is closed.  Fire and forget: nothing waits for these.
+            if (p.next_W && (int)blockIdx.x < p.next_grid && it == n_total) {
+                const uint32_t Un = (uint32_t)p.next_n_tiles * (uint32_t)p.next_KS, Gn = (uint32_t)p.next_grid;
+                const UnitOrder nxt(blockIdx.x * Un / Gn, (blockIdx.x + 1) * Un / Gn, (uint32_t)p.next_KS);
+                const int cnt = nxt.n_total < p.next_units ? nxt.n_total : p.next_units;
+                const int nkt = p.next_ty == TY_Q8_0 ? Q8_KT : Q4_KT_SB * 8;
+                volatile int *done = s_flags + 3;
+                for (int j = 0; j < cnt && !*done; ++j) {
+                    const uint32_t u = nxt.at(j);
+                    const int nks = (int)(u % p.next_KS);
+                    const int kb = min(nkt, p.next_nb - nks * nkt);
+                    const uint32_t bytes = p.next_ty == TY_Q8_0 ? (uint32_t)kb * Q8_BLOCK_UNIT : (uint32_t)(kb / 8) * Q4_SB_UNIT;
+                    const uint32_t off = p.next_ty == TY_Q8_0 ? (uint32_t)nks * Q8_KT * Q8_BLOCK_UNIT
+                                                              : (uint32_t)nks * Q4_KT_SB * Q4_SB_UNIT;
+                    const uint8_t *src = p.next_W + (size_t)(u / p.next_KS) * p.next_tile_bytes + off;
+                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+                    if (p.next_pace > 0) __nanosleep(p.next_pace);
+                }
+            }
             // Every copy issued above lands before this lane leaves: wait (bounded)
             // for the stages still in flight so no bulk write outlives the CTA.
             const int pending = it < NS ? it : NS;
-            for (int j = it - pending; j < it; ++j) (void)mbar_wait_bounded(&full[j % NS], (uint32_t)((j / NS) & 1));
-            if (p.pro != PRO_STREAM) (void)mbar_wait_bounded(acts_bar, 0u);
+            for (int j = it - pending; j < it; ++j) (void)mbar_wait_bounded(&full[j % NS], (uint32_t)((j / NS) & 1), p.wait_limit);
+            if (acts_copy) (void)mbar_wait_bounded(acts_bar, 0u, p.wait_limit);
         }
         return;
     }
@@ -1148,7 +1224,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                                     all = all && (w[j] & w2[j] & PART_VALID) != 0;
                                 }
                                 if (all || gave_up) break;
-                                if (clock64() - t_wait > WAIT_LIMIT_CYCLES) gave_up = true;
+                                if (clock64() - t_wait > p.wait_limit) gave_up = true;
                             }
 #pragma unroll
                             for (int j = 0; j < 8; ++j)
@@ -1170,6 +1246,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 if (tl && cw.t == 0 && final_tile && p.pro != PRO_QUANT) tl[7] = globaltimer_ns();  // pieces added
                 epilogue_tile<M>(p, cw, t_cur, fin, use_pre ? pre : nullptr, rope_pre, gam_pre);
             }
+            if (final_tile && cw.t == 0) *reinterpret_cast<volatile int *>(s_flags + 3) = 1;
     };
 
     if (warp > N_CONSUMER_WARPS) {
@@ -1196,7 +1273,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         for (uint32_t n = 0;; ++n) {
             // one thread waits (bounded) and tells the others, so all of them leave together
             if (ftid == 0) {
-                const bool ok = mbar_wait_bounded(red_full, n & 1u);
+                const bool ok = mbar_wait_bounded(red_full, n & 1u, p.wait_limit);
                 if (!ok) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
                 s_flags[2] = ok ? 1 : 0;
             }
@@ -1243,12 +1320,12 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     if (p.pro == PRO_QUANT) prologue_gamma(p, tid, gam);  // independent of the previous kernel
     if (p.pdl) pdl_wait();
     if (tl && tid == 0) tl[2] = globaltimer_ns();  // dependency satisfied
-    if (tid == 0 && p.pro != PRO_STREAM) {
+    if (tid == 0 && acts_copy) {
         // the activations, as soon as they exist
         const uint64_t pol_a = l2_policy_evict_last();
         if (p.pro == PRO_QUANT) {
             // the raw row into the scratch stage (the ring's last, which the producer leaves alone until pro_bar)
-            const uint32_t bytes = (uint32_t)p.prep.n * (p.prep.x_is_bf16 ? 2u : 4u);
+            const uint32_t bytes = (uint32_t)p.prep.n * 4u;
             mbar_arrive_expect_tx(acts_bar, bytes);
             bulk_g2s(stages + (size_t)(NS - 1) * stage_bytes, p.prep.x, bytes, acts_bar, pol_a);
         } else {
@@ -1265,14 +1342,15 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         // f64 1/sqrt(mean + eps) (ops/norm.rs:193-198); below, every block scale and block sum
         // of that token's rows is multiplied by it.
         for (int tok = warp; tok < p.m_out; tok += N_CONSUMER_WARPS) {
-            double ss = 0.0;
-            for (int i = lane; i < p.norm_blocks; i += 32) ss += p.norm_sumsq[(size_t)tok * p.norm_blocks + i];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const double ss = sumsq_total(p.norm_sumsq + (size_t)tok * p.norm_blocks, p.norm_blocks, lane);
             if (lane == 0) s_scale[tok] = (float)(1.0 / sqrt(ss / (double)(p.norm_blocks * 32) + (double)p.norm_eps));
         }
     }
-    if (p.pro != PRO_STREAM && !mbar_wait_bounded(acts_bar, 0u)) {
+    // the row's sum of squares, when its producer left the per-block sums: the loads fly
+    // while the row itself is on its way
+    double ssq_in = 0.0;
+    if (p.pro == PRO_QUANT && p.prep.gamma && p.prep.sumsq) ssq_in = sumsq_total(p.prep.sumsq, p.prep.n >> 5, lane);
+    if (acts_copy && !mbar_wait_bounded(acts_bar, 0u, p.wait_limit)) {
         aborted = true;
         if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
     }
@@ -1294,13 +1372,19 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     }
     if (p.pro == PRO_QUANT) {
         if (tl && tid == 0) tl[4] = globaltimer_ns();  // raw row landed
-        prologue_quant<M>(p, res, reinterpret_cast<float *>(stages + (size_t)(NS - 1) * stage_bytes), red, tid, gam);
+        prologue_quant<M>(p, res, reinterpret_cast<float *>(stages + (size_t)(NS - 1) * stage_bytes), red, tid, gam, ssq_in);
         // generic-proxy accesses to the scratch are done; the bulk-copy engine may overwrite it
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(pro_bar);
     }
     if (tl && tid == 0) tl[6] = globaltimer_ns();  // activations ready
+    if (p.act_dump && blockIdx.x == 0 && p.pro != PRO_STREAM) {
+        // parity instrumentation: the records exactly as the mma loop is about to read them
+        const uint32_t *src = reinterpret_cast<const uint32_t *>(res);
+        uint32_t *dst = reinterpret_cast<uint32_t *>(p.act_dump);
+        for (int i = tid; i < (p.KS * act_rec) >> 2; i += N_CONSUMERS) dst[i] = src[i];
+    }
 
     // (tile, K-step) of the walk, kept incrementally: the order has one jump
     // (after the tail piece) and otherwise advances by one unit.
@@ -1325,7 +1409,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             t_next = t + 1;
         }
         const bool mine = !CH || (it & 1) == ug;
-        if (mine && !aborted && !mbar_wait_bounded(&full[s], ph)) {
+        if (mine && !aborted && !mbar_wait_bounded(&full[s], ph, p.wait_limit)) {
             aborted = true;
             if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
         }
@@ -1654,7 +1738,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         // Hand the tile's partial sums to the finisher warps and stream on.  red is a single
         // buffer: the finishers copy it out at once, so this wait only bites when two tiles
         // close within a fraction of a microsecond.
-        if (n_handoff > 0 && !aborted && !mbar_wait_bounded(red_empty, (n_handoff - 1u) & 1u)) {
+        if (n_handoff > 0 && !aborted && !mbar_wait_bounded(red_empty, (n_handoff - 1u) & 1u, p.wait_limit)) {
             aborted = true;
             if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
         }
@@ -1728,10 +1812,10 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw,
             float v = val(m, r);
             if (p.epi == EPI_ADD) v = __fadd_rn(pre ? pre[j] : p.resid[(size_t)m * p.ldr + row], v);
             p.y[(size_t)m * p.ldy + row] = v;
-            if (p.nq_gamma) out[i] = v;
+            if (p.nq_sumsq) out[i] = v;
         }
-        if (p.epi == EPI_ADD && p.nq_gamma) {
-            // the next norm + quantisation, as far as this tile can take it (see MvParams)
+        if (p.epi == EPI_ADD && p.nq_sumsq) {
+            // the start of the next RMSNorm, as far as this tile can take it (see MvParams)
             cw.sync();
             const int warp = tid >> 5, lane = tid & 31;
             const int nblk = p.n_out >> 5;
@@ -1740,20 +1824,22 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw,
                 const int row = row0 + 32 * jb + lane;
                 if (row0 + 32 * jb >= p.n_out) continue;
                 const float v = out[m * TILE_ROWS + 32 * jb + lane];
-                const float gam = w == warp ? gam_pre : p.nq_gamma[row];
                 double ss = (double)v * (double)v;
 #pragma unroll
                 for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
                 if (lane == 0) p.nq_sumsq[(size_t)m * nblk + (row >> 5)] = ss;
-                quantize_store(p.nq_act, p.nq_two_level, p.nq_need_sum, m, row >> 5, lane, __fmul_rn(v, gam));
+                if (p.nq_gamma) {
+                    const float gam = w == warp ? gam_pre : p.nq_gamma[row];
+                    quantize_store(p.nq_act, p.nq_two_level, p.nq_need_sum, m, row >> 5, lane, __fmul_rn(v, gam));
+                }
             }
         }
         return;
     }
     if (p.epi == EPI_PEERS) {
-        // the exchange in flight is epoch + 1 (the epoch word only moves between kernels)
-        const uint32_t parity = (__ldcg(xch_epoch(p.xch.slots[p.xch.rank])) + 1u) & 1u;
-        const size_t slot = ((size_t)parity * XCH_MAX_RANKS + p.xch.rank) * XCH_ROW_FLOATS;
+        float *mine = p.xch.slots[p.xch.rank];
+        const uint32_t e = xch_number(mine, p.xout);
+        const size_t slot = ((size_t)(e & 1u) * XCH_MAX_RANKS + p.xch.rank) * XCH_ROW_FLOATS;
         for (int i = tid; i < MO * TILE_ROWS; i += cw.n) {
             const int m = i / TILE_ROWS, r = i % TILE_ROWS;
             const int row = row0 + r;
@@ -1764,8 +1850,13 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw,
                 p.xch.slots[dst][slot + (size_t)m * p.xch_row + row] = v;
             }
         }
-        // No fence here: the flag that publishes these stores is raised by a kernel that runs
-        // after this grid has completed (st.release.sys, cumulative over what it has observed).
+        // Publish the tile: the crew's stores are ordered before the barrier, the flag stores
+        // after it are releases at system scope (cumulative over what the barrier ordered).
+        cw.sync();
+        if (tid < p.xch.world) {
+            asm volatile("fence.acq_rel.sys;" ::: "memory");
+            st_release_sys(xch_flags(p.xch.slots[tid]) + p.xch.rank * XCH_MAX_TILES + tile, e);
+        }
         return;
     }
     if (p.epi == EPI_QKV_ROPE) {

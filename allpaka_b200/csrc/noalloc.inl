@@ -7,8 +7,8 @@
 // or fail outright: a latency-bounded decode thread, a process whose allocator
 // has been frozen after start-up.  Such a caller owns the
 // input and output buffers already; what it cannot supply is the kernel's
-// private scratch (stream-K partial sums, per-tile arrival counters, the error
-// word, and the quantised-activation records).  Here that scratch is a fixed
+// private scratch (stream-K partial sums, the error word, and the
+// quantised-activation records).  Here that scratch is a fixed
 // array in the library's own device image.
 //
 // Included at the end of apk_b200.cu: same translation unit as the kernels, so
@@ -17,13 +17,10 @@
 namespace {
 
 constexpr uint32_t NOALLOC_MAX_CTAS = 160;       // one CTA per SM
-constexpr uint32_t NOALLOC_MAX_TILES = 4096;     // 128-row tiles -> n_out <= 524288
 constexpr size_t NOALLOC_PARTIALS_BYTES = (size_t)NOALLOC_MAX_CTAS * 2 * MAX_M_EFF * TILE_ROWS * sizeof(unsigned long long);
-constexpr size_t NOALLOC_COUNTERS_BYTES = (size_t)NOALLOC_MAX_TILES * sizeof(int);
 constexpr size_t NOALLOC_ERR_BYTES = 256;
 constexpr size_t NOALLOC_ACTS_BYTES = (size_t)MAX_M_EFF * APK_NOALLOC_MAX_N_IN * 5 / 4 + 256;
-constexpr size_t NOALLOC_OFF_COUNTERS = NOALLOC_PARTIALS_BYTES;
-constexpr size_t NOALLOC_OFF_ERR = NOALLOC_OFF_COUNTERS + NOALLOC_COUNTERS_BYTES;
+constexpr size_t NOALLOC_OFF_ERR = NOALLOC_PARTIALS_BYTES;
 constexpr size_t NOALLOC_OFF_ACTS = NOALLOC_OFF_ERR + NOALLOC_ERR_BYTES;
 constexpr size_t NOALLOC_TOTAL = NOALLOC_OFF_ACTS + NOALLOC_ACTS_BYTES;  // about 5.9 MB
 
@@ -31,14 +28,29 @@ constexpr size_t NOALLOC_TOTAL = NOALLOC_OFF_ACTS + NOALLOC_ACTS_BYTES;  // abou
 // code this name is only a stand-in for the symbol, never a device address.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_TOTAL];
 
+// The array exists once per DEVICE, not per context: its address and whether its last
+// user was seen to leave it clean are kept per device, under one lock, so that contexts
+// sharing a GPU see each other's calls.
+constexpr int NOALLOC_MAX_DEVICES = 64;
+struct NoallocDev {
+    unsigned char *ptr = nullptr;
+    bool dirty = true;  // until a call is seen to end cleanly the tagged partial sums are cleared first
+};
+NoallocDev g_noalloc_dev[NOALLOC_MAX_DEVICES];
+std::mutex g_noalloc_mu;
+
 // Device address of the array on the context's device (that device is current).
-int noalloc_setup(apk_ctx *c) {
-    if (c->noalloc_ptr) return APK_OK;
-    void *ptr = nullptr;
-    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
-    if (e != cudaSuccess || !ptr)
-        return fail(APK_ERR_CUDA, "cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
-    c->noalloc_ptr = (unsigned char *)ptr;
+int noalloc_setup(apk_ctx *c, NoallocDev **out) {
+    if (c->device < 0 || c->device >= NOALLOC_MAX_DEVICES) return fail(APK_ERR_INVALID_ARG, "device %d", c->device);
+    NoallocDev *d = &g_noalloc_dev[c->device];
+    if (!d->ptr) {
+        void *ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || !ptr)
+            return fail(APK_ERR_CUDA, "cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+        d->ptr = (unsigned char *)ptr;
+    }
+    *out = d;
     return APK_OK;
 }
 
@@ -64,20 +76,21 @@ extern "C" int apk_matvec_noalloc(apk_ctx *c, const void *w, uint32_t ty, uint32
         return fail(APK_DECLINE_INVALID_STATE,
                     "matvec_noalloc: matrix is not resident; call apk_register_matrix first (this entry point never allocates)");
     const DevMatrix *W = it->second.get();
-    APK_TRY(noalloc_setup(c));  // first call on this device: resolves the scratch symbol
+    std::lock_guard<std::mutex> gdev(g_noalloc_mu);
+    NoallocDev *dev = nullptr;
+    APK_TRY(noalloc_setup(c, &dev));  // first call on this device: resolves the scratch symbol
     cudaStream_t st = (cudaStream_t)stream;
-    unsigned char *base = c->noalloc_ptr;
+    unsigned char *base = dev->ptr;
     unsigned long long *partials = reinterpret_cast<unsigned long long *>(base);
-    int *counters = reinterpret_cast<int *>(base + NOALLOC_OFF_COUNTERS);
     int *err = reinterpret_cast<int *>(base + NOALLOC_OFF_ERR);
     void *acts = base + NOALLOC_OFF_ACTS;
-    // The array keeps the previous call's contents: counters and the error word must start at zero.
-    CUDA_TRY(cudaMemsetAsync(base + NOALLOC_OFF_COUNTERS, 0, NOALLOC_COUNTERS_BYTES + NOALLOC_ERR_BYTES, st));
+    // The array keeps the previous call's contents: the error word must start at zero.
+    CUDA_TRY(cudaMemsetAsync(err, 0, NOALLOC_ERR_BYTES, st));
     // So must the tagged partial sums.  A kernel that ran to its end leaves them zero; only a
     // call that was seen to end cleanly (wait != 0, no error) proves that, so after any other
-    // call the region is cleared again.
-    if (c->noalloc_dirty) CUDA_TRY(cudaMemsetAsync(base, 0, NOALLOC_PARTIALS_BYTES, st));
-    c->noalloc_dirty = true;
+    // call on this device, from whichever context, the region is cleared again.
+    if (dev->dirty) CUDA_TRY(cudaMemsetAsync(base, 0, NOALLOC_PARTIALS_BYTES, st));
+    dev->dirty = true;
 
     const ActMode mode = resolve_mode(act_mode, m);
     MvKernel k = pick_kernel(W->ty, mode.m_eff, false);
@@ -89,7 +102,7 @@ extern "C" int apk_matvec_noalloc(apk_ctx *c, const void *w, uint32_t ty, uint32
     if (in_cta) {
         p.pro = PRO_QUANT;
         PrepParams &pp = p.prep;
-        pp.x = x_dev; pp.x_is_bf16 = 0; pp.ldx = (int)n_in;
+        pp.x = x_dev; pp.ldx = (int)n_in;
         pp.n = (int)n_in; pp.m = 1;
         pp.out = p.act;
         pp.two_level = mode.two_level;
@@ -116,8 +129,9 @@ extern "C" int apk_matvec_noalloc(apk_ctx *c, const void *w, uint32_t ty, uint32
     p.two_level = mode.two_level;
     p.m_out = mode.two_level ? mode.m_eff / 2 : mode.m_eff;
     p.partials = partials;
-    p.counters = counters;
     p.err = err;
+    p.wait_limit = c->wait_limit;
+    p.xin.index = -1;
     p.pdl = 0;
     p.inflight = c->inflight;
     p.inflight_pre = c->inflight_pre;
@@ -139,7 +153,11 @@ extern "C" int apk_matvec_noalloc(apk_ctx *c, const void *w, uint32_t ty, uint32
     int herr = 0;  // plain stack word: a synchronous copy needs no pinned staging of ours
     CUDA_TRY(cudaMemcpyAsync(&herr, err, sizeof herr, cudaMemcpyDeviceToHost, st));
     CUDA_TRY(cudaStreamSynchronize(st));
-    if (herr != 0) return fail(APK_ERR_TIMEOUT, "device-side wait expired (%s)", herr == ERRW_PRODUCER_TIMEOUT ? "copy producer" : "tile consumer");
-    c->noalloc_dirty = false;
+    if (herr != 0)
+        return fail(APK_ERR_TIMEOUT, "device-side wait expired (%s)",
+                    herr == ERRW_PRODUCER_TIMEOUT   ? "copy producer"
+                    : herr == ERRW_FINISHER_TIMEOUT ? "a tile piece of another CTA never arrived"
+                                                    : "tile consumer");
+    dev->dirty = false;
     return APK_OK;
 }

@@ -92,7 +92,12 @@ class _TokenReq(C.Structure):
 
 
 class _TokenOut(C.Structure):
-    _fields_ = [("logits", C.c_void_p), ("argmax", C.c_void_p)]
+    _fields_ = [("logits", C.c_void_p), ("argmax", C.c_void_p), ("hidden", C.c_void_p)]
+
+
+class _BenchReq(C.Structure):
+    _fields_ = [("op", C.c_uint32), ("n_copies", C.c_uint32), ("mv", C.c_void_p), ("attn", C.c_void_p),
+                ("ffn", C.c_void_p), ("act_mode", C.c_uint32)]
 
 
 class _Stats(C.Structure):
@@ -109,6 +114,8 @@ EXPORTS = (
     "apk_debug_synth_matrix", "apk_debug_synth_release", "apk_decode_profile",
     "apk_debug_matvec_timeline", "apk_shard_plan", "apk_matvec_noalloc",
     "apk_dist_p2p_export", "apk_dist_p2p_open", "apk_debug_token_timeline",
+    "apk_debug_token_records", "apk_debug_set_wait_limit", "apk_debug_xch_timeout",
+    "apk_bench_ring", "apk_dist_set_exchange",
 )
 
 _lib = None
@@ -147,6 +154,12 @@ def load_library() -> C.CDLL:
     l.apk_debug_matvec_timeline.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
                                             C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p]
     l.apk_debug_token_timeline.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
+    l.apk_debug_token_records.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p, C.c_void_p,
+                                          C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_size_t]
+    l.apk_debug_set_wait_limit.argtypes = [C.c_void_p, C.c_uint64]
+    l.apk_debug_xch_timeout.argtypes = [C.c_void_p]
+    l.apk_bench_ring.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(C.c_float)]
+    l.apk_dist_set_exchange.argtypes = [C.c_void_p, C.c_int]
     l.apk_matvec_noalloc.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p,
                                      C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p, C.c_int]
     l.apk_decode_profile.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
@@ -217,6 +230,14 @@ class TokenLayer:
     down: tuple
     q_norm: Optional[np.ndarray] = None
     k_norm: Optional[np.ndarray] = None
+
+
+@dataclass
+class TokenRows:
+    """``TokenOut::Rows { argmax, hidden }`` (gpu/types.rs:228-238): the greedy winner of every
+    row and the output-normed hidden rows, what ``verify_tokens`` consumes (model/decode.rs:212-217)."""
+    argmax: np.ndarray
+    hidden: np.ndarray
 
 
 @dataclass
@@ -407,21 +428,28 @@ class Gpu:
                          req.n_kv_heads, req.attn_core, 1 if req.argmax else 0)
         return creq, (x, rope)
 
-    def decode_token_checked(self, req: TokenReq):
+    def decode_token_checked(self, req: TokenReq, want_hidden: bool = False):
+        """``TokenOut``: logits (argmax off), the winner ids (argmax on, m == 1), or
+        :class:`TokenRows` (argmax on and m > 1, as the reference returns for a verify batch).
+        With ``want_hidden`` the output-normed rows come along in every form: ``(result, hidden)``."""
         creq, keep = self._token_req(req)
         vocab = req.output[2]
+        rows = want_hidden or (req.argmax and req.m > 1)
+        hidden = np.empty((req.m, req.hidden), dtype=np.float32) if rows else None
         if req.argmax:
             res = np.empty(req.m, dtype=np.uint32)
-            out = _TokenOut(None, res.ctypes.data)
+            out = _TokenOut(None, res.ctypes.data, _ptr(hidden))
         else:
             res = np.empty((req.m, vocab), dtype=np.float32)
-            out = _TokenOut(res.ctypes.data, None)
+            out = _TokenOut(res.ctypes.data, None, _ptr(hidden))
         rc = self._l.apk_decode_token(self._h, C.byref(creq), C.byref(out))
         if rc > 0:
             raise DecodeDecline(rc, self._err())
         if rc < 0:
             raise GpuError(rc, self._err())
-        return res
+        if req.argmax and req.m > 1:
+            return TokenRows(res, hidden)
+        return (res, hidden) if want_hidden else res
 
     def decode_token(self, req: TokenReq):
         try:
@@ -458,6 +486,43 @@ class Gpu:
                                        s.ctypes.data, q.ctypes.data)
         return (d, s, q) if self._check(rc) else None
 
+    def debug_token_records(self, req: TokenReq, max_records: int = 512, dots_launch: int = -1,
+                            dots_shape=None):
+        """What every RMSNorm-fed matvec of one token worked on: a list of dicts with the residual
+        rows ``x`` it normalised and the activation records ``d``, ``sum``, ``q`` it consumed
+        (rows = tokens, or digit pairs in two-level mode), plus, for matvec launch number
+        ``dots_launch``, its int32 block dots (``dots_shape`` = (rows, device rows, blocks))."""
+        creq, keep = self._token_req(req)
+        H, nb = req.hidden, req.hidden // 32
+        x = np.zeros((max_records, MAX_M, H), np.float32)
+        d = np.zeros((max_records, 16, nb), np.float32)
+        s = np.zeros((max_records, 16, nb), np.float32)
+        q = np.zeros((max_records, 16, H), np.int8)
+        meta = np.zeros((max_records, 4), np.int32)
+        n = C.c_uint32()
+        dots = np.empty(dots_shape, np.int32) if dots_shape is not None else None
+        rc = self._l.apk_debug_token_records(self._h, C.byref(creq), max_records, x.ctypes.data, d.ctypes.data,
+                                             s.ctypes.data, q.ctypes.data, meta.ctypes.data, C.byref(n), dots_launch,
+                                             _ptr(dots), 0 if dots is None else dots.size)
+        if rc != 0:
+            raise GpuError(rc, self._err())
+        recs = []
+        for i in range(n.value):
+            rows, two, launch, ke = (int(v) for v in meta[i])
+            recs.append({"x": x[i, :req.m], "d": d[i, :rows], "sum": s[i, :rows], "q": q[i, :rows],
+                         "rows": rows, "two_level": bool(two), "launch": launch, "ke": ke})
+        return (recs, dots) if dots is not None else recs
+
+    def debug_set_wait_limit(self, cycles: int) -> None:
+        """Cycle budget of the bounded device-side waits (0 = default)."""
+        rc = self._l.apk_debug_set_wait_limit(self._h, cycles)
+        if rc != 0:
+            raise GpuError(rc, self._err())
+
+    def debug_xch_timeout(self) -> int:
+        """Run the exchange-collecting kernel against a peer that never delivers; returns the status."""
+        return self._l.apk_debug_xch_timeout(self._h)
+
     def matvec_noalloc(self, ty: int, w, n_in: int, n_out: int, x_dev: int, m: int, y_dev: int,
                        stream: int = 0, act_mode: int = ACT_AUTO, wait: bool = True) -> bool:
         """apk_matvec_noalloc: for callers that may not allocate device memory here (VRAM fully
@@ -491,6 +556,49 @@ class Gpu:
         rc = self._l.apk_debug_synth_release(self._h)
         if rc != 0:
             raise GpuError(rc, self._err())
+
+    def bench_ring(self, op: str, copies: Sequence, reps: int = 20, act_mode: int = ACT_AUTO) -> float:
+        """Microseconds per pass of one operator over a ring of distinct weight copies (device-resident
+        inputs, launches chained back to back).  ``op`` = "matvec" (copies: MatvecReq), "attn_in"
+        (copies: dicts with the arguments of :meth:`attn_in`) or "ffn" (copies: FfnReq)."""
+        keep = []
+        n = len(copies)
+        br = _BenchReq(0, n, None, None, None, act_mode)
+        if op == "matvec":
+            arr = (_MatvecReq * n)()
+            for i, r in enumerate(copies):
+                w, x = _u8(r.w), _f32(r.x).reshape(-1)
+                keep += [w, x]
+                arr[i] = _MatvecReq(r.ty, w.ctypes.data, r.n_in, r.n_out, x.ctypes.data, r.m)
+            br.op, br.mv = 0, C.addressof(arr)
+        elif op == "attn_in":
+            arr = (_AttnInReq * n)()
+            for i, a in enumerate(copies):
+                wq, wk, wv = _u8(a["wq"]), _u8(a["wk"]), _u8(a["wv"])
+                x, rope = _f32(a["x"]).reshape(-1), _f32(a["rope"]).reshape(-1)
+                gam = None if a.get("gamma") is None else _f32(a["gamma"])
+                qn = None if a.get("q_norm") is None else _f32(a["q_norm"])
+                kn = None if a.get("k_norm") is None else _f32(a["k_norm"])
+                keep += [wq, wk, wv, x, rope, gam, qn, kn]
+                arr[i] = _AttnInReq(a["ty"], wq.ctypes.data, wk.ctypes.data, wv.ctypes.data, a["hidden"], a["head_dim"],
+                                    a["n_heads"], a["n_kv_heads"], x.ctypes.data, a["m"], _ptr(gam), a["eps"], _ptr(qn),
+                                    _ptr(kn), rope.ctypes.data, a["rot_dim"])
+            br.op, br.attn = 1, C.addressof(arr)
+        elif op == "ffn":
+            arr = (_FfnReq * n)()
+            for i, r in enumerate(copies):
+                g, u, d, x = _u8(r.gate_w), _u8(r.up_w), _u8(r.down_w), _f32(r.x).reshape(-1)
+                keep += [g, u, d, x]
+                arr[i] = _FfnReq(r.gate_ty, g.ctypes.data, r.up_ty, u.ctypes.data, r.down_ty, d.ctypes.data, r.hidden,
+                                 r.ffn, x.ctypes.data, r.m)
+            br.op, br.ffn = 2, C.addressof(arr)
+        else:
+            raise ValueError(op)
+        us = C.c_float()
+        rc = self._l.apk_bench_ring(self._h, C.byref(br), reps, C.byref(us))
+        if rc != 0:
+            raise GpuError(rc, self._err())
+        return us.value
 
     def decode_profile(self, req: "TokenReq", reps: int = 1):
         """Per-launch GPU ms and algorithmic bytes of the five matvec kinds of a token."""
@@ -553,6 +661,12 @@ class Gpu:
         """Open every rank's handle (rank order); reductions then go over peer memory."""
         blob = C.create_string_buffer(b"".join(handles), 64 * len(handles))
         rc = self._l.apk_dist_p2p_open(self._h, blob)
+        if rc != 0:
+            raise GpuError(rc, self._err())
+
+    def dist_set_exchange(self, peer_stores: bool) -> None:
+        """Per-layer reductions through the peer-store exchange (True) or NCCL all-reduce (False)."""
+        rc = self._l.apk_dist_set_exchange(self._h, 1 if peer_stores else 0)
         if rc != 0:
             raise GpuError(rc, self._err())
 

@@ -175,15 +175,23 @@ typedef struct {
     int argmax;               /* 1: return the greedy token per row instead of logits */
 } apk_token_req; /* TokenReq, gpu/types.rs:183-238 */
 
+/* TokenOut, gpu/types.rs:228-238.  Logits(Vec<f32>): logits set, argmax == 0.
+ * Argmax(u32): argmax set, argmax == 1, m == 1.  Rows { argmax, hidden }, what
+ * the speculative verify consumes (model/decode.rs:212-217): argmax and hidden
+ * both set, argmax == 1, any m.  `hidden` may accompany either form. */
 typedef struct {
     float *logits;    /* m * vocab, written when argmax == 0 */
-    uint32_t *argmax; /* m ids, written when argmax == 1 */
-} apk_token_out; /* TokenOut, gpu/types.rs:240-252 */
+    uint32_t *argmax; /* m ids, written when argmax == 1 (ties go to the higher id, model/decode.rs:604-608) */
+    float *hidden;    /* optional, m * hidden: the output-normed rows (rmsnorm(x, output_norm), the LM head's input) */
+} apk_token_out;
 
 /* gpu::decode_token_checked (stub.rs:150-157): the whole token as one
  * submission (a replayed CUDA graph).  Layer weights are resolved, fused
  * (Q|K|V rows, gate/up row interleave) and uploaded at the first call that
- * names them. */
+ * names them.  The plan built then is keyed on every descriptor of the request
+ * (layer array address, each weight and norm pointer, types, row counts); the
+ * norm weights are copied at that point, so the borrowed tensors must keep
+ * their contents until the mapping is detached. */
 int apk_decode_token(apk_ctx *ctx, const apk_token_req *req, apk_token_out *out);
 
 /* Same work with the m*hidden input already in device memory and the result
@@ -204,6 +212,34 @@ int apk_debug_block_dots(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_in
  * the fused RMSNorm (gamma != NULL).  d and sum are n/32 floats, q n bytes. */
 int apk_debug_q8_acts(apk_ctx *ctx, const float *x, uint32_t n, const float *gamma, float eps,
                       float *d, float *sum, int8_t *q);
+
+/* Parity instrumentation for the whole-token path: the token of apk_decode_token
+ * is enqueued launch by launch and every matvec that reads the residual stream
+ * through an RMSNorm (Q|K|V, gate/up, LM head) hands back what it worked on:
+ * record i = the m residual rows it normalised, x[(i*8 + row)*hidden ..], and
+ * the activation records its tensor-core loop consumed, unpacked to
+ * d, sum [(i*16 + r)*(hidden/32) ..] and q [(i*16 + r)*hidden ..] for r < rows;
+ * meta[4i..] = {rows, two-level flag, index of the launch in the token, K-step}.
+ * With dots != NULL the int32 block dots of matvec launch number dots_launch
+ * (0-based in issue order; layout [rows][device rows of that matrix][n_in/32])
+ * are written too, if they fit dots_elems.  Single-GPU contexts only. */
+int apk_debug_token_records(apk_ctx *ctx, const apk_token_req *req, uint32_t max_records, float *x, float *d,
+                            float *sum, int8_t *q, int32_t *meta, uint32_t *n_records, int dots_launch,
+                            int32_t *dots, size_t dots_elems);
+
+/* Every wait inside a kernel (on a copy, on another CTA's tile piece, on a
+ * peer rank's partial sums) gives up after a cycle budget, records which wait
+ * it was and lets the kernel end; the call then returns APK_ERR_TIMEOUT and
+ * the context stays usable.  This sets the budget in SM clock cycles (0
+ * restores the default of 4e9, about two seconds), for tests that make a wait
+ * run out on purpose. */
+int apk_debug_set_wait_limit(apk_ctx *ctx, uint64_t cycles);
+
+/* Test of that path which needs one GPU only: the kernel that collects a
+ * tensor-parallel exchange is run against a second local buffer standing for a
+ * peer that never delivers.  Returns what the call that hit it would return
+ * (APK_ERR_TIMEOUT once the budget has run out). */
+int apk_debug_xch_timeout(apk_ctx *ctx);
 
 /* A matvec that allocates nothing.  It has no counterpart in the reference.
  *
@@ -227,12 +263,14 @@ int apk_debug_q8_acts(apk_ctx *ctx, const float *x, uint32_t n, const float *gam
  *
  * The first call on a device resolves the array's device address
  * (cudaGetSymbolAddress); make that first call before starting a stream capture.
- * All calls share the one array and it keeps the last call's contents (the
- * counters and the error word are cleared at the start of every call; the
- * tagged partial sums are left all-zero by a kernel that ran to its end and are
- * cleared again after any call that was not seen to end cleanly): two calls
- * whose kernels overlap on the GPU, on different streams or contexts of the
- * same device, race.  Results are identical to apk_matvec's. */
+ * All calls on a device share the one array, from whichever context, and it
+ * keeps the last call's contents (the error word is cleared at the start of
+ * every call; the tagged partial sums are left all-zero by a kernel that ran to
+ * its end and are cleared again after any call on that device that was not
+ * seen to end cleanly): two calls whose kernels overlap on the GPU, on
+ * different streams or contexts of the same device, race.  With wait == 0
+ * nobody reads the error word, so an expired device-side wait of that call
+ * goes unreported.  Results are identical to apk_matvec's. */
 #define APK_NOALLOC_MAX_N_IN 32768u
 #define APK_NOALLOC_MAX_N_OUT 524288u
 int apk_matvec_noalloc(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_in, uint32_t n_out, const float *x_dev,
@@ -272,6 +310,27 @@ int apk_debug_synth_release(apk_ctx *ctx);
  * such launch (original GGUF weight bytes + activations in + results out). */
 int apk_decode_profile(apk_ctx *ctx, const apk_token_req *req, uint32_t reps, float *ms, double *bytes);
 
+/* Benchmark utility: one operator timed over a ring of distinct weight copies,
+ * inputs resident on the device, launches chained back to back like the layers
+ * of a token, one CUDA-event pair on the launching stream around reps * n_copies
+ * passes (after one untimed pass over every copy).  A ring larger than L2
+ * measures HBM-cold; a single copy measures L2-hot.  Ops: a plain matvec
+ * (mv[i], x of mv[0]), the input half of the attention block (attn[i]: RMSNorm
+ * -> Q|K|V -> per-head norm -> RoPE; x, norm weights and RoPE table of attn[0]),
+ * or one FFN (ffn[i]; x of ffn[0]).  Copies must share one shape. */
+#define APK_BENCH_MATVEC 0u
+#define APK_BENCH_ATTN_IN 1u
+#define APK_BENCH_FFN 2u
+typedef struct {
+    uint32_t op;
+    uint32_t n_copies;
+    const apk_matvec_req *mv;
+    const apk_attn_in_req *attn;
+    const apk_ffn_req *ffn;
+    uint32_t act_mode; /* matvec only */
+} apk_bench_req;
+int apk_bench_ring(apk_ctx *ctx, const apk_bench_req *req, uint32_t reps, float *us_per_pass);
+
 typedef struct {
     uint64_t calls;      /* entry-point submissions (gpu::stats().0, gpu/common.rs:24-31) */
     uint64_t launches;   /* kernels launched by this library (".1 dispatches") */
@@ -305,13 +364,19 @@ int apk_shard_plan(uint32_t kind, uint32_t ty, uint32_t n_out, uint32_t n_in, ui
 /* Optional low-latency exchange for the two per-layer reductions: each rank
  * exports one device buffer (CUDA IPC handle, APK_IPC_HANDLE_BYTES), the host
  * gathers the handles of all ranks in rank order and every rank opens them.
- * From then on the row-parallel matvecs store their partial sums straight into
- * every rank's buffer over NVLink and a small kernel adds them in rank order
- * (bounded waits on per-rank flags), instead of an NCCL all-reduce.  At most 8
- * ranks, m * hidden <= 131072. */
+ * From then on the CTA that closes a tile of a row-parallel matvec stores its
+ * partial sums straight into every rank's buffer over NVLink and raises a
+ * per-tile flag there; the next matvec gathers them in its own prologue
+ * (bounded wait on the flags, sum in rank order, residual add, RMSNorm,
+ * quantisation): four launches per layer, no NCCL all-reduce.  At most 8
+ * ranks, hidden <= 16384, m * hidden <= 131072.  Every rank must issue the
+ * same sequence of decode calls. */
 #define APK_IPC_HANDLE_BYTES 64
 int apk_dist_p2p_export(apk_ctx *ctx, void *handle_out);
 int apk_dist_p2p_open(apk_ctx *ctx, const void *handles /* world * APK_IPC_HANDLE_BYTES */);
+/* Switch between the peer-store exchange (1; needs apk_dist_p2p_open) and NCCL
+ * all-reduce (0) for the per-layer reductions.  Every rank must make the same call. */
+int apk_dist_set_exchange(apk_ctx *ctx, int peer_stores);
 #define APK_UNIQUE_ID_BYTES 128
 int apk_dist_unique_id(void *id_out /* APK_UNIQUE_ID_BYTES */);
 int apk_dist_init(apk_ctx *ctx, int rank, int world, const void *unique_id);

@@ -215,7 +215,11 @@ def test_config3_ffn_swiglu_down(gpu, orc, m):
     _, x = synth.normal_bf16((m, hidden), 1013)
     got = gpu.ffn_batch([FfnReq(Q8_0, r.views[0], Q8_0, r.views[1], Q8_0, r.views[2], hidden, ffn, x, m)])[0]
     want = orc.ffn(Q8_0, g, Q8_0, u, Q8_0, d, hidden, ffn, x, m)
-    assert rel_l2(got, want) <= TOL, rel_l2(got, want)
+    err = rel_l2(got, want)
+    print(f"config 3, m = {m}: rel-L2 {err:.2e}")
+    # m = 1: Q8 activations everywhere, same arithmetic as the oracle; m = 6: `down` takes f32 rows in the
+    # reference and two-level int8 rows here (about 2^-16 of a block maximum per element)
+    assert err <= (1e-5 if m == 1 else 1e-4), err
     gpu.detach(r.buf)
 
 
@@ -275,6 +279,7 @@ def test_decode_token_matches_oracle_layer_stack(gpu, orc, ty, m, qk_norm):
     assert np.array_equal(logits, again)
     req.argmax = True
     ids = gpu.decode_token_checked(req)
+    ids = ids.argmax if m > 1 else ids  # a verify batch answers with TokenOut::Rows
     assert list(ids) == [int(np.flatnonzero(row == row.max())[-1]) for row in logits]
     st = gpu.decode_path_stats()
     assert st["successes"] >= 3 and st["attempts"] >= st["successes"]
@@ -297,12 +302,13 @@ def test_decode_token_tiles_shared_by_many_ctas(gpu, orc, ty, m):
 
 @pytest.mark.parametrize("ty,m", [(Q8_0, 1), (Q8_0, 5), (Q4_K, 2)])
 def test_next_norm_started_by_the_residual_epilogue_changes_nothing(orc, ty, m, monkeypatch):
-    """The RMSNorm input of Q|K|V, gate/up and the head is quantised either by the residual epilogue
-    in front of it (default) or in the kernel's own prologue / a separate pass: same logits."""
+    """The RMSNorm in front of Q|K|V, gate/up and the head either adds up the per-block sums of squares
+    that the residual epilogue left (default), reduces the row itself (0), or takes records that the
+    residual epilogue already quantised before the row scale existed (2, opt-in approximation): same logits."""
     from allpaka_b200 import gpu as G
 
     out = []
-    for fuse in ("1", "0"):
+    for fuse in ("1", "0", "2"):
         monkeypatch.setenv("ALLPAKA_B200_FUSE_NORM", fuse)
         g = G.Gpu(0)
         req, layers, head, out_norm, x, rope, r = build_token(g, orc, ty, 2, 1024, 8, 2, 2048, 1536, m, True, 800)
@@ -313,7 +319,8 @@ def test_next_norm_started_by_the_residual_epilogue_changes_nothing(orc, ty, m, 
             assert rel_l2(out[0], want) <= TOL, rel_l2(out[0], want)
         g.detach(r.buf)
         g.close()
-    assert rel_l2(out[0], out[1]) <= 1e-4, rel_l2(out[0], out[1])
+    assert rel_l2(out[0], out[1]) <= 1e-6, rel_l2(out[0], out[1])
+    assert rel_l2(out[0], out[2]) <= 1e-3, rel_l2(out[0], out[2])
 
 
 def test_token_timeline_is_ordered(gpu, orc):

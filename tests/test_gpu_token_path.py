@@ -1,0 +1,333 @@
+"""The whole-token path against the oracle, looked at from the inside (run with -m gpu on a B200).
+
+What the default decode graph hands to its tensor-core loops must be what the reference
+computes on the same residual rows: Q8 codes and block scales of
+``Q8Acts::from_f32(rmsnorm_into(x, gamma))`` bit for bit (ops/norm.rs:193-198, then
+quantmat/q8_acts.rs:26-63), hence bit-exact int32 block dots.  Chained over layers the f32
+additions upstream run in another order than the reference's strictly sequential ones, so a
+residual value may differ in its last bit, and where such a value sits within an ulp of a .5
+rounding boundary one code flips: the tests below therefore check every operator on the GPU's
+own intermediate rows (the per-operator bar) and record the chained figure over many seeds.
+"""
+import numpy as np
+import pytest
+
+from allpaka_b200 import synth
+from tests.util import (Q4_K, Q8_0, Region, make_layer, oracle_decode, oracle_logits, rel_l2,
+                        rope_table)
+
+pytestmark = pytest.mark.gpu
+
+
+def fresh_gpu(monkeypatch=None, **env):
+    from allpaka_b200 import gpu as G
+
+    if monkeypatch is not None:
+        for k, v in env.items():
+            monkeypatch.setenv(k, str(v))
+    return G.Gpu(0)
+
+
+def build_token(g, orc, ty, n_layers, hidden, nh, nkv, ffn, vocab, m, qk_norm, seed, x_seed=None):
+    from allpaka_b200.gpu import TokenLayer, TokenReq
+
+    hd = 128
+    nq, nk = nh * hd, nkv * hd
+    layers = [make_layer(ty, hidden, nq, nk, ffn, seed + 100 * l, qk_norm) for l in range(n_layers)]
+    head = synth.matrix(ty, vocab, hidden, seed + 9000)
+    names = ("wq", "wk", "wv", "wo", "gate", "up", "down")
+    r = Region([L[n] for L in layers for n in names] + [head])
+    assert g.attach(r.buf)
+    tls = []
+    for li, L in enumerate(layers):
+        v = dict(zip(names, r.views[li * 7:(li + 1) * 7]))
+        tls.append(TokenLayer(L["attn_norm"], L["ffn_norm"], (ty, v["wq"], nq), (ty, v["wk"], nk),
+                              (ty, v["wv"], nk), (ty, v["wo"], hidden), (ty, v["gate"], ffn),
+                              (ty, v["up"], ffn), (ty, v["down"], hidden), L.get("q_norm"), L.get("k_norm")))
+    out_norm = synth.gamma(hidden, seed + 9001)
+    x = synth.normal_f32((m, hidden), seed + 9002 if x_seed is None else x_seed)
+    rope = rope_table(orc, np.arange(m) + 1234, hd, hd)
+    req = TokenReq(tls, out_norm, (ty, r.views[-1], vocab), x, m, rope, hd, 1e-6, hidden, hd, nh, nkv)
+    return req, layers, head, out_norm, x, rope, r
+
+
+def synth_stack(g, n_layers, hidden, nh, nkv, ffn, vocab, m, seed):
+    """A deep full-width stack whose weights exist on the device only (seeded on-device
+    generator): the oracle side of the test needs the rows and the norm weights, not the matrices."""
+    import mmap
+
+    from allpaka_b200.gpu import TokenLayer, TokenReq
+
+    hd = 128
+    nq, nk = nh * hd, nkv * hd
+    specs = [("wq", nq, hidden), ("wk", nk, hidden), ("wv", nk, hidden), ("wo", hidden, nq),
+             ("gate", ffn, hidden), ("up", ffn, hidden), ("down", hidden, ffn)]
+    nbytes = lambda o, i: o * (i // 32) * 34
+    total = n_layers * sum((nbytes(o, i) + 255) // 256 * 256 for _, o, i in specs) + nbytes(vocab, hidden) + 256
+    mm = mmap.mmap(-1, total, flags=mmap.MAP_PRIVATE | mmap.MAP_ANONYMOUS | getattr(mmap, "MAP_NORESERVE", 0))
+    region = np.frombuffer(mm, dtype=np.uint8)
+    assert g.attach(region)
+    off, tls, gammas = 0, [], []
+    for l in range(n_layers):
+        v = {}
+        for k, (name, o, i) in enumerate(specs):
+            v[name] = region[off: off + nbytes(o, i)]
+            g.synth_matrix(v[name], Q8_0, o, i, seed + 8 * l + k)
+            off += (nbytes(o, i) + 255) // 256 * 256
+        an, fn = synth.gamma(hidden, seed + 5000 + 2 * l), synth.gamma(hidden, seed + 5001 + 2 * l)
+        gammas += [an, fn]
+        tls.append(TokenLayer(an, fn, (Q8_0, v["wq"], nq), (Q8_0, v["wk"], nk), (Q8_0, v["wv"], nk),
+                              (Q8_0, v["wo"], hidden), (Q8_0, v["gate"], ffn), (Q8_0, v["up"], ffn),
+                              (Q8_0, v["down"], hidden)))
+    hdw = region[off: off + nbytes(vocab, hidden)]
+    g.synth_matrix(hdw, Q8_0, vocab, hidden, seed + 7)
+    out_norm = synth.gamma(hidden, seed + 4999)
+    gammas.append(out_norm)
+    x = synth.normal_f32((m, hidden), seed + 4242)
+    rope = np.stack([np.stack([np.sin(np.arange(hd // 2, dtype=np.float32) * (p + 1) * 0.01),
+                               np.cos(np.arange(hd // 2, dtype=np.float32) * (p + 1) * 0.01)], axis=1)
+                     for p in range(m)]).astype(np.float32)
+    req = TokenReq(tls, out_norm, (Q8_0, hdw, vocab), x, m, rope, hd, 1e-6, hidden, hd, nh, nkv)
+    return req, gammas, (mm, region)
+
+
+def count_flips(orc, recs, gammas, eps=1e-6):
+    """Compare every Q8-mode record with Q8Acts::from_f32(rmsnorm_into(x)) on the GPU's own rows."""
+    rows = flips = bad_d = 0
+    for rec, gam in zip(recs, gammas):
+        if rec["two_level"]:
+            continue
+        for t in range(rec["rows"]):
+            h = orc.rmsnorm_into(rec["x"][t], gam, eps)
+            od, _, oq = orc.q8acts(h)
+            flips += int(np.count_nonzero(rec["q"][t] != oq))
+            bad_d += int(np.count_nonzero(rec["d"][t].view(np.uint32) != od.view(np.uint32)))
+            rows += 1
+    return rows, flips, bad_d
+
+
+def test_default_token_path_hands_the_reference_blocks_to_every_matvec(orc):
+    """hidden 5120, 100 layers: 201 normalised rows of the benchmark's value distribution as they come
+    out of the running residual stream; codes and block scales bit for bit."""
+    g = fresh_gpu()
+    req, gammas, keep = synth_stack(g, 100, 5120, 8, 2, 1024, 1024, 1, 31000)
+    g.decode_replay(req, 1)
+    g.synth_release()
+    recs = g.debug_token_records(req, 256)
+    assert len(recs) == 201
+    rows, flips, bad_d = count_flips(orc, recs, gammas)
+    print(f"token path, exact norm hand-off: {rows} rows, {flips} flipped codes, {bad_d} block scales off")
+    assert rows == 201 and flips == 0 and bad_d == 0
+    g.close()
+
+
+@pytest.mark.parametrize("mode", ["0", "2"])
+def test_other_norm_modes(orc, monkeypatch, mode):
+    """Mode 0 (every kernel reduces the row itself) is exact as well.  Mode 2 (the residual epilogue
+    quantises x * gamma before the row scale exists) is the opt-in approximation: its flips are counted
+    and bounded, never assumed to be zero."""
+    g = fresh_gpu(monkeypatch, ALLPAKA_B200_FUSE_NORM=mode)
+    req, gammas, keep = synth_stack(g, 24, 5120, 8, 2, 1024, 1024, 1, 32000)
+    g.decode_replay(req, 1)
+    g.synth_release()
+    recs = g.debug_token_records(req, 64)
+    rows, flips, bad_d = count_flips(orc, recs, gammas)
+    print(f"norm mode {mode}: {rows} rows, {flips} flipped codes, {bad_d} block scales off")
+    assert rows == 49
+    if mode == "0":
+        assert flips == 0 and bad_d == 0
+    else:
+        assert flips <= 4 * rows  # about one code per row at worst, each off by one
+    g.close()
+
+
+def test_verify_batch_records_are_bit_exact(orc):
+    """m = 3: Q|K|V and gate/up take Q8 rows (matmul_many), quantised by the separate pass."""
+    g = fresh_gpu()
+    req, gammas, keep = synth_stack(g, 6, 5120, 8, 2, 1024, 1024, 3, 33000)
+    g.decode_replay(req, 1)
+    g.synth_release()
+    recs = g.debug_token_records(req, 32)
+    q8 = [(r, gm) for r, gm in zip(recs, gammas) if not r["two_level"]]
+    assert len(q8) == 12  # the head takes f32-activation rows at m > 1
+    rows, flips, bad_d = count_flips(orc, [r for r, _ in q8], [gm for _, gm in q8])
+    assert rows == 36 and flips == 0 and bad_d == 0
+    g.close()
+
+
+@pytest.mark.parametrize("ty", [Q8_0, Q4_K])
+def test_block_dots_inside_the_token_are_bit_exact(orc, ty):
+    """The int32 block dots of the second layer's Q|K|V launch (its input has been through a whole
+    layer of the fused path) against dot_i8 on the oracle's quantisation of the same row."""
+    g = fresh_gpu()
+    hidden, nh, nkv, ffn, vocab = 1024, 8, 2, 2048, 1536
+    req, layers, head, out_norm, x, rope, r = build_token(g, orc, ty, 2, hidden, nh, nkv, ffn, vocab, 1, True, 4100)
+    n_dev = (nh + 2 * nkv) * 128
+    recs, dots = g.debug_token_records(req, 16, dots_launch=4, dots_shape=(1, n_dev, hidden // 32))
+    rec = next(rc for rc in recs if rc["launch"] == 4)
+    L = layers[1]
+    h = orc.rmsnorm_into(rec["x"][0], L["attn_norm"], 1e-6)
+    od, osum, oq = orc.q8acts(h)
+    assert np.array_equal(rec["q"][0], oq) and np.array_equal(rec["d"][0].view(np.uint32), od.view(np.uint32))
+    if ty == Q4_K:  # the min term multiplies the exact f32 block sums
+        assert np.array_equal(rec["sum"][0].view(np.uint32), osum.view(np.uint32))
+    want = np.concatenate([orc.block_dots(ty, L[n], rows, hidden, oq, 1)
+                           for n, rows in (("wq", nh * 128), ("wk", nkv * 128), ("wv", nkv * 128))], axis=1)
+    assert np.array_equal(dots, want)
+    g.detach(r.buf)
+    g.close()
+
+
+def oracle_trace(orc, ty, layers, hidden, n_q, n_kv, hd, ffn, eps, rope, x, m):
+    """The reference's layer order, keeping the residual rows in front of every norm."""
+    x = np.array(x, dtype=np.float32).reshape(m, hidden).copy()
+    rows = []
+    for L in layers:
+        rows.append(x.copy())
+        q, _, _ = orc.attn_in(ty, L["wq"], L["wk"], L["wv"], hidden, n_q, n_kv, hd, x, m, L["attn_norm"], eps, rope,
+                              L.get("q_norm"), L.get("k_norm"))
+        x = x + orc.matmul(ty, L["wo"], hidden, n_q, q, m)
+        rows.append(x.copy())
+        h = np.stack([orc.rmsnorm_into(x[i], L["ffn_norm"], eps) for i in range(m)])
+        x = x + orc.ffn(ty, L["gate"], ty, L["up"], ty, L["down"], hidden, ffn, h, m)
+    rows.append(x.copy())
+    return rows
+
+
+@pytest.mark.parametrize("ty,m", [(Q8_0, 1), (Q8_0, 4), (Q4_K, 1)])
+def test_every_operator_on_the_gpus_own_rows_over_many_seeds(orc, ty, m):
+    """16 input seeds, none picked.  Per operator (attention half, FFN half, head), the oracle is fed
+    the row the GPU had at that point and must agree with the GPU's next row to 1e-5.  The chained
+    figure against the oracle's own chain is recorded; where it exceeds the 2e-3 bar the cause has to
+    be a flipped Q8 code on rows that agree to rounding (a .5 knife-edge), not an operator that is off."""
+    g = fresh_gpu()
+    hidden, nh, nkv, ffn, vocab, hd = 1024, 8, 2, 2048, 1536, 128
+    nq, nk = nh * hd, nkv * hd
+    chained, worst_op = [], 0.0
+    req, layers, head, out_norm, x0, rope, r = build_token(g, orc, ty, 2, hidden, nh, nkv, ffn, vocab, m, True, 300)
+    for seed in range(16):
+        x = synth.normal_f32((m, hidden), 990 + seed)
+        req.x = x
+        logits = g.decode_token_checked(req)
+        recs = g.debug_token_records(req, 16)
+        assert len(recs) == 5
+        xs = [rc["x"] for rc in recs]  # in front of: Q|K|V 0, gate/up 0, Q|K|V 1, gate/up 1, head
+        assert np.array_equal(xs[0], x)
+        for l, L in enumerate(layers):
+            q, _, _ = orc.attn_in(ty, L["wq"], L["wk"], L["wv"], hidden, nq, nk, hd, xs[2 * l], m, L["attn_norm"],
+                                  1e-6, rope, L["q_norm"], L["k_norm"])
+            want = xs[2 * l] + orc.matmul(ty, L["wo"], hidden, nq, q, m)
+            worst_op = max(worst_op, rel_l2(xs[2 * l + 1], want))
+            h = np.stack([orc.rmsnorm_into(xs[2 * l + 1][i], L["ffn_norm"], 1e-6) for i in range(m)])
+            want = xs[2 * l + 1] + orc.ffn(ty, L["gate"], ty, L["up"], ty, L["down"], hidden, ffn, h, m)
+            worst_op = max(worst_op, rel_l2(xs[2 * l + 2], want))
+        worst_op = max(worst_op, rel_l2(logits, oracle_logits(orc, ty, head, vocab, hidden, xs[4], out_norm, 1e-6, m)))
+        trace = oracle_trace(orc, ty, layers, hidden, nq, nk, hd, ffn, 1e-6, rope, x, m)
+        want = oracle_logits(orc, ty, head, vocab, hidden, trace[-1], out_norm, 1e-6, m)
+        err = rel_l2(logits, want)
+        chained.append(err)
+        if err > 2e-3:
+            # find the first norm input where the GPU's codes and the oracle chain's codes part
+            gams = [layers[0]["attn_norm"], layers[0]["ffn_norm"], layers[1]["attn_norm"], layers[1]["ffn_norm"]]
+            explained = False
+            for k in range(4):
+                if recs[k]["two_level"]:
+                    continue
+                for t in range(m):
+                    _, _, oq = orc.q8acts(orc.rmsnorm_into(trace[k][t], gams[k], 1e-6))
+                    if np.any(recs[k]["q"][t] != oq):
+                        assert rel_l2(xs[k][t], trace[k][t]) < 1e-6  # same rows to rounding, different code
+                        assert np.max(np.abs(recs[k]["q"][t].astype(int) - oq.astype(int))) == 1
+                        explained = True
+                if explained:
+                    break
+            assert explained, (seed, err)
+    print(f"{'Q8_0' if ty == Q8_0 else 'Q4_K'} m={m}: per-operator worst {worst_op:.2e}; chained over 16 seeds "
+          f"median {np.median(chained):.2e} max {np.max(chained):.2e}, {sum(e > 2e-3 for e in chained)} above 2e-3")
+    assert worst_op <= (1e-5 if m == 1 else 1e-4)
+    g.detach(r.buf)
+    g.close()
+
+
+@pytest.mark.parametrize("m", [2, 5, 8])
+def test_verify_rows_argmax_and_normed_hidden(orc, m):
+    """TokenOut::Rows: per-row greedy winner and the output-normed hidden rows in one call."""
+    from allpaka_b200.gpu import TokenRows
+
+    g = fresh_gpu()
+    hidden, nh, nkv, ffn, vocab = 512, 4, 2, 1024, 1000
+    req, layers, head, out_norm, x, rope, r = build_token(g, orc, Q8_0, 2, hidden, nh, nkv, ffn, vocab, m, False, 5200)
+    logits = g.decode_token_checked(req)
+    req.argmax = True
+    out = g.decode_token_checked(req)
+    assert isinstance(out, TokenRows) and out.argmax.shape == (m,) and out.hidden.shape == (m, hidden)
+    assert list(out.argmax) == [int(np.flatnonzero(row == row.max())[-1]) for row in logits]
+    recs = g.debug_token_records(req, 16)
+    x_last = recs[-1]["x"]  # the residual rows in front of the output norm
+    want_h = np.stack([orc.rmsnorm(x_last[i], out_norm, 1e-6) for i in range(m)])
+    assert rel_l2(out.hidden, want_h) <= 1e-6
+    xo = oracle_decode(orc, Q8_0, layers, hidden, nh * 128, nkv * 128, 128, ffn, 1e-6, rope, x, m)
+    want = oracle_logits(orc, Q8_0, head, vocab, hidden, xo, out_norm, 1e-6, m)
+    assert rel_l2(logits, want) <= 2e-3
+    assert list(out.argmax) == [int(np.argmax(row)) for row in want]
+    h_chain = np.stack([orc.rmsnorm(xo[i], out_norm, 1e-6) for i in range(m)])
+    assert rel_l2(out.hidden, h_chain) <= 2e-3
+    # m == 1 keeps its plain forms; the hidden row comes along when asked for
+    req1, *_r, r1 = build_token(g, orc, Q8_0, 1, hidden, nh, nkv, ffn, vocab, 1, False, 5300)
+    logits1, hidden1 = g.decode_token_checked(req1, want_hidden=True)
+    assert logits1.shape == (1, vocab)
+    x1 = g.debug_token_records(req1, 8)[-1]["x"]
+    assert rel_l2(hidden1[0], orc.rmsnorm(x1[0], req1.output_norm, 1e-6)) <= 1e-6
+    g.detach(r.buf)
+    g.detach(r1.buf)
+    g.close()
+
+
+def test_an_expired_device_wait_is_reported_and_the_context_lives_on(orc):
+    """A bounded wait that runs out by construction (a peer's flags that nothing raises), with the
+    budget cut to about a millisecond: the call reports APK_ERR_TIMEOUT, nothing hangs or faults, and
+    the next ordinary matvec on the same context is right."""
+    import time
+
+    g = fresh_gpu()
+    w = synth.q8_0_matrix(700, 2048, 61)
+    r = Region([w])
+    assert g.attach(r.buf)
+    x = synth.normal_f32((1, 2048), 62)
+    before = g.matvec(Q8_0, r.views[0], 2048, 700, x, 1)
+    g.debug_set_wait_limit(2_000_000)
+    t0 = time.perf_counter()
+    rc = g.debug_xch_timeout()
+    dt = time.perf_counter() - t0
+    assert rc == -3, (rc, g._err())
+    assert "peer" in g._err()
+    assert dt < 1.0
+    g.debug_set_wait_limit(0)
+    after = g.matvec(Q8_0, r.views[0], 2048, 700, x, 1)
+    assert np.array_equal(before, after)
+    assert rel_l2(after, orc.matmul(Q8_0, w, 700, 2048, x, 1)) <= 1e-5
+    g.detach(r.buf)
+    g.close()
+
+
+@pytest.mark.parametrize("ty,m", [(Q8_0, 1), (Q8_0, 3), (Q4_K, 1)])
+def test_peer_exchange_path_on_one_gpu(orc, monkeypatch, ty, m):
+    """One rank exchanging with itself: wo and down store their rows into the exchange slots and
+    raise the tile flags, the next matvec gathers them in its prologue (m = 1) or the collecting
+    kernel does (m > 1).  Same logits as the ordinary single-GPU path, twice (two tokens: both slot parities)."""
+    hidden, nh, nkv, ffn, vocab = 1024, 8, 2, 2048, 1536
+    outs = []
+    for self_xch in ("0", "1"):
+        g = fresh_gpu(monkeypatch, ALLPAKA_B200_SELF_XCH=self_xch)
+        req, layers, head, out_norm, x, rope, r = build_token(g, orc, ty, 3, hidden, nh, nkv, ffn, vocab, m, True, 6100)
+        a = g.decode_token_checked(req)
+        b = g.decode_token_checked(req)
+        assert np.array_equal(a, b)
+        outs.append(a)
+        if self_xch == "1":
+            xo = oracle_decode(orc, ty, layers, hidden, nh * 128, nkv * 128, 128, ffn, 1e-6, rope, x, m)
+            want = oracle_logits(orc, ty, head, vocab, hidden, xo, out_norm, 1e-6, m)
+            assert rel_l2(a, want) <= 2e-3
+        g.detach(r.buf)
+        g.close()
+    assert rel_l2(outs[1], outs[0]) <= 1e-6

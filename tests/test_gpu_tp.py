@@ -53,22 +53,30 @@ def _worker(rank, world, port, ty, m, exchange, out_q):
                                 (ty, v["wo"], hidden), (ty, v["gate"], ffn), (ty, v["up"], ffn), (ty, v["down"], hidden),
                                 L["q_norm"], L["k_norm"]))
     out_norm = synth.gamma(hidden, 998)
-    # Input seed: Q8 activation codes are round(v / d).  When some v / d lands within an f32 ulp of a
-    # .5 boundary, the order of the f32 additions upstream (strictly sequential in the oracle, per
-    # lane and tree-wise on the GPU) decides the code, and one flipped code moves the logits by
-    # ~7e-4 per layer from there on.  Seed 997 has such an element at this shape; 996 has none.
-    x = synth.normal_f32((m, hidden), 996)
+    # Four input seeds, none picked.  Chained over layers the f32 additions run in another order
+    # than the oracle's (per rank, then across ranks), so a residual value may differ in its last
+    # bit; where it sits within an ulp of a .5 rounding boundary one Q8 code flips and moves the
+    # logits by ~7e-4 per layer from there on (the single-GPU tests trace such cases to the code).
+    # Per seed the figure is recorded; the median must be at rounding level and at most one seed
+    # may sit above the chained bar.
     rope = rope_table(orc, np.arange(m) + 4000, hd, hd)
-    req = G.TokenReq(tls, out_norm, (ty, r.views[-1], vocab), x, m, rope, hd, 1e-6, hidden, hd, nh, nkv)
-    logits = g.decode_token_checked(req)
-    again = g.decode_token_checked(req)
-    req.argmax = True
-    ids_ = g.decode_token_checked(req)
+    errs, same, argmax_ok = [], True, True
+    for seed in (996, 997, 998, 999):
+        x = synth.normal_f32((m, hidden), seed)
+        req = G.TokenReq(tls, out_norm, (ty, r.views[-1], vocab), x, m, rope, hd, 1e-6, hidden, hd, nh, nkv)
+        logits = g.decode_token_checked(req)
+        again = g.decode_token_checked(req)
+        req.argmax = True
+        ids_ = g.decode_token_checked(req)
+        ids_ = ids_.argmax if m > 1 else ids_
+        if rank == 0:
+            xo = oracle_decode(orc, ty, layers, hidden, nq, nk, hd, ffn, 1e-6, rope, x, m)
+            want = oracle_logits(orc, ty, head, vocab, hidden, xo, out_norm, 1e-6, m)
+            errs.append(rel_l2(logits, want))
+            same = same and bool(np.array_equal(logits, again))
+            argmax_ok = argmax_ok and [int(i) for i in ids_] == [int(np.flatnonzero(row == row.max())[-1]) for row in logits]
     if rank == 0:
-        xo = oracle_decode(orc, ty, layers, hidden, nq, nk, hd, ffn, 1e-6, rope, x, m)
-        want = oracle_logits(orc, ty, head, vocab, hidden, xo, out_norm, 1e-6, m)
-        out_q.put((rel_l2(logits, want), bool(np.array_equal(logits, again)),
-                   [int(i) for i in ids_] == [int(np.flatnonzero(row == row.max())[-1]) for row in logits]))
+        out_q.put((errs, same, argmax_ok))
     dist.barrier()
     g.close()
     dist.destroy_process_group()
@@ -88,9 +96,11 @@ def test_two_gpu_decode_matches_the_unsharded_oracle(ty, m, exchange):
     procs = [ctx.Process(target=_worker, args=(r, 2, port, ty, m, exchange, q)) for r in range(2)]
     for p in procs:
         p.start()
-    err, same, argmax_ok = q.get(timeout=300)
+    errs, same, argmax_ok = q.get(timeout=300)
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    assert err <= 2e-3, err
+    print(f"tp2 {exchange} ty={ty} m={m}: chained rel-L2 per seed {['%.1e' % e for e in errs]}")
+    assert np.median(errs) <= 1e-4, errs
+    assert sum(e > 2e-3 for e in errs) <= 1, errs
     assert same and argmax_ok

@@ -67,6 +67,43 @@ def test_noalloc_matches_the_allocating_entry_point_twice(gpu, orc, ty, n_out, n
     gpu.detach(r.buf)
 
 
+def test_noalloc_unwaited_call_then_another_and_no_allocation(gpu, orc):
+    """wait=False leaves the call unobserved: the next call on the device clears the tagged partial
+    sums first and is right all the same.  Neither call changes the amount of free device memory."""
+    import torch
+
+    n_out, n_in = 700, 5120
+    w = synth.q8_0_matrix(n_out, n_in, 91)
+    r = Region([w])
+    assert gpu.attach(r.buf)
+    assert gpu.register_matrix(r.views[0], Q8_0, n_out, n_in)
+    x = synth.normal_f32((1, n_in), 92)
+    xd = torch.from_numpy(x).cuda()
+    yd = torch.zeros((1, n_out), device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+    assert gpu.matvec_noalloc(Q8_0, r.views[0], n_in, n_out, xd.data_ptr(), 1, yd.data_ptr(), stream)  # symbol resolved
+    torch.cuda.synchronize()
+    free0 = torch.cuda.mem_get_info()[0]
+    assert gpu.matvec_noalloc(Q8_0, r.views[0], n_in, n_out, xd.data_ptr(), 1, yd.data_ptr(), stream, wait=False)
+    assert gpu.matvec_noalloc(Q8_0, r.views[0], n_in, n_out, xd.data_ptr(), 1, yd.data_ptr(), stream, wait=True)
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free0
+    assert rel_l2(yd.cpu().numpy(), orc.matmul(Q8_0, w, n_out, n_in, x, 1)) <= 1e-5
+    # a second context on the same device shares the one array and its state
+    from allpaka_b200 import gpu as G
+
+    g2 = G.Gpu(0)
+    assert g2.attach(r.buf) and g2.register_matrix(r.views[0], Q8_0, n_out, n_in)
+    yd.zero_()
+    assert gpu.matvec_noalloc(Q8_0, r.views[0], n_in, n_out, xd.data_ptr(), 1, yd.data_ptr(), stream, wait=False)
+    torch.cuda.synchronize()
+    assert g2.matvec_noalloc(Q8_0, r.views[0], n_in, n_out, xd.data_ptr(), 1, yd.data_ptr(), stream)
+    assert rel_l2(yd.cpu().numpy(), orc.matmul(Q8_0, w, n_out, n_in, x, 1)) <= 1e-5
+    g2.detach(r.buf)
+    g2.close()
+    gpu.detach(r.buf)
+
+
 def test_noalloc_rejects_sizes_beyond_its_scratch(gpu):
     w = synth.q8_0_matrix(4, 64, 1)
     r = Region([w])
