@@ -201,8 +201,6 @@ struct apk_ctx {
     //  applies the row scale (cheaper; codes may differ by one at a .5 boundary); 3 like 2 for m > 1, like 1 at m = 1
     int fuse_norm = 1;
     long long wait_limit = WAIT_LIMIT_DEFAULT;  // cycle budget of the bounded device-side waits (apk_debug_set_wait_limit)
-    int next_units = 6;          // units of the next matvec a CTA pulls into L2 while it closes its last tile (ALLPAKA_B200_NEXT_PREFETCH)
-    int next_pace = 600;         // ns between two of those (ALLPAKA_B200_NEXT_PACE)
     bool self_xch = false;       // ALLPAKA_B200_SELF_XCH=1: a single rank runs the peer-exchange path on itself (one-GPU test of it)
     // parity instrumentation (apk_debug_token_records): one slab per matvec launch that reads the residual through a norm
     uint8_t *rec_dump = nullptr;
@@ -817,8 +815,6 @@ int apk_init(apk_ctx **out, int device) {
     if (const char *e = getenv("ALLPAKA_B200_FUSE_NORM")) c->fuse_norm = atoi(e);
     if (const char *e = getenv("ALLPAKA_B200_INFLIGHT")) c->inflight = std::max(1, std::min(atoi(e), MAX_STAGES));
     if (const char *e = getenv("ALLPAKA_B200_INFLIGHT_PRE")) c->inflight_pre = std::max(1, std::min(atoi(e), MAX_STAGES));
-    if (const char *e = getenv("ALLPAKA_B200_NEXT_PREFETCH")) c->next_units = std::max(0, std::min(atoi(e), 64));
-    if (const char *e = getenv("ALLPAKA_B200_NEXT_PACE")) c->next_pace = std::max(0, std::min(atoi(e), 100000));
     if (const char *e = getenv("ALLPAKA_B200_SELF_XCH")) c->self_xch = atoi(e) != 0;
     if (c->self_xch) {
         // one rank exchanging with itself: the peer-store epilogue and the collecting prologue on one GPU

@@ -220,25 +220,13 @@ struct TokenLaunch {
         const bool on = c->fuse_norm == 2 || (c->fuse_norm == 3 && m > 1);
         return on && W != P->head && !uses_xch(c) && c->world == 1 && P->hidden % 32 == 0 && want_resident(c, W, mode.m_eff);
     }
-    void set_next(MvParams *p, const DevMatrix *Wn) const {
-        if (!Wn || c->next_units <= 0) return;
-        p->next_W = Wn->d;
-        p->next_tile_bytes = Wn->tile_bytes;
-        p->next_ty = (int)Wn->ty;
-        p->next_nb = Wn->nb;
-        p->next_n_tiles = Wn->n_tiles;
-        p->next_KS = Wn->KS;
-        p->next_grid = (int)std::min<long long>(c->n_sm, (long long)Wn->n_tiles * Wn->KS);
-        p->next_units = c->next_units;
-        p->next_pace = c->next_pace;
-    }
     int launch(const DevMatrix *W, MvParams &p, ActMode mode, const DevMatrix *Wn) {
         if (first && uses_xch(c)) {
             p.xch = c->xch;
             p.tok_inc = 1;
         }
         first = false;
-        set_next(&p, Wn);
+        (void)Wn;
         return launch_matvec(c, W, p, mode);
     }
     // Parity instrumentation: keep the rows this launch normalises and the records it consumes.

@@ -166,14 +166,6 @@ struct MvParams {
     int inflight;       // K-steps of weights one CTA keeps in flight at a time (>= 1)
     int inflight_pre;   // the same while the previous kernel has not finished yet (>= 1)
     unsigned long long *timeline;  // optional [gridDim.x][8] globaltimer stamps (trace)
-    // The matvec that follows this one in the stream (optional).  Once a CTA has asked for all
-    // of its own units, HBM would idle while tiles are closed and the next kernel starts: the
-    // producer lane uses that time to pull the first units of the next kernel's CTA of the same
-    // index into L2, so that its ring fills from L2 instead of from DRAM.
-    const uint8_t *next_W;
-    uint32_t next_tile_bytes;
-    int next_ty, next_nb, next_n_tiles, next_KS, next_grid;
-    int next_units, next_pace;         // how many units at most; nanoseconds between two of them
     // epilogue
     int epi;
     float *y; int ldy;
@@ -793,9 +785,10 @@ constexpr int EPI_PRE = 2;  // residual values a finisher thread fetches ahead o
 // optional RMSNorm, entirely in registers.
 //  * The norm weight does not depend on the previous kernel: it is loaded
 //    BEFORE the dependency wait (prologue_gamma).
-//  * The row itself arrives by one bulk async copy issued by the producer lane
-//    right after the wait (raw f32/bf16 in the scratch buffer = last ring stage,
-//    which the producer leaves alone until pro_bar completes).
+//  * The row itself is read by the consumer threads with plain 16-byte loads right
+//    after the wait (they return sooner than a copy staged through shared memory).
+//    The last ring stage stays free until pro_bar completes: the exact block sums
+//    of the Q4_K flavour use it as scratch.
 //  * Thread t owns elements 4t..4t+3 of every 2048-element chunk j, so the 8
 //    lanes t&~7 .. t|7 hold one 32-element block: block maximum = 3 shuffles,
 //    then the IEEE divide / reciprocal, rounding and one packed 32-bit store,
@@ -821,7 +814,7 @@ __device__ __forceinline__ void prologue_gamma(const MvParams &p, int tid, float
 
 template <int M>
 __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, float *hs, float *red, int tid,
-                                               const float (&g)[PRO_CH], double ssq_in) {
+                                               const float (&g)[PRO_CH], double ssq_in, const float4 (&xr)[PRO_J]) {
     const PrepParams &pp = p.prep;
     const int warp = tid >> 5, lane = tid & 31;
     const int n = pp.n, nb = n >> 5;
@@ -855,11 +848,10 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
 #pragma unroll
         for (int j = 0; j < PRO_J; ++j) {
             const int e = 4 * tid + PRO_CHUNK * j;
-            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+            float4 x = xr[j];  // loaded by the caller right after the dependency resolved
             if (e < n) {
-                x = *reinterpret_cast<const float4 *>(hs + e);
                 if (pp.add) {
-                    const float4 a = *reinterpret_cast<const float4 *>(pp.add + e);
+                    const float4 a = __ldcg(reinterpret_cast<const float4 *>(pp.add + e));
                     x.x = __fadd_rn(x.x, a.x); x.y = __fadd_rn(x.y, a.y); x.z = __fadd_rn(x.z, a.z); x.w = __fadd_rn(x.w, a.w);
                 }
                 if (pp.xout && blockIdx.x == 0) *reinterpret_cast<float4 *>(pp.xout + e) = x;
@@ -884,7 +876,11 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
 #pragma unroll
             for (int i = 0; i < N_CONSUMER_WARPS; ++i) tot += dred[i];
         }
-        const double scale = 1.0 / sqrt(tot / (double)n + (double)pp.eps);
+        // one lane per warp does the f64 division and square root (the double-precision pipe is
+        // narrow: 512 threads doing it side by side cost more than the broadcast)
+        double scale = 0.0;
+        if (lane == 0) scale = 1.0 / sqrt(tot / (double)n + (double)pp.eps);
+        scale = __shfl_sync(0xffffffffu, scale, 0);
 #pragma unroll
         for (int j = 0; j < PRO_CH; ++j) v[j] = __fmul_rn((float)((double)v[j] * scale), g[j]);
         if (pp.hout && blockIdx.x == 0) {
@@ -1015,9 +1011,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     unsigned long long *tl = p.timeline ? p.timeline + (size_t)blockIdx.x * 8 : nullptr;
     if (tl && tid == 0) tl[0] = globaltimer_ns();
-    // the resident activations arrive by bulk copy, except when the prologue gathers the row
-    // from the exchange slots itself
-    const bool acts_copy = p.pro == PRO_LOAD || (p.pro == PRO_QUANT && p.xin.index < 0);
+    // prepared records arrive by bulk copy; a row still to be quantised is read straight into
+    // registers by the consumer threads (plain loads return sooner than a copy through shared memory)
+    const bool acts_copy = p.pro == PRO_LOAD;
     // first launch of a token in a tensor-parallel group: advance the token counter that numbers
     // the exchanges (single writer; later launches read it after this grid has completed)
     if (p.tok_inc && blockIdx.x == 0 && tid == 0) *xch_tok(p.xch.slots[p.xch.rank]) += 1u;
@@ -1030,7 +1026,6 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         mbar_init(pro_bar, N_CONSUMER_WARPS);
         mbar_init(red_full, N_CONSUMER_WARPS);
         mbar_init(red_empty, 1);
-        s_flags[3] = 0;  // set once this CTA's last tile is closed
         fence_mbar_init();
     }
     __syncthreads();
@@ -1087,7 +1082,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
                 }
             };
-            int ring0 = p.pro == PRO_QUANT ? NS - 1 : NS;
+            // (the in-CTA prologue of a Q4_K consumer uses the last stage as scratch for its exact block sums)
+            const bool scratch = p.pro == PRO_QUANT && p.prep.need_sum;
+            int ring0 = scratch ? NS - 1 : NS;
             const int pre = n_total < ring0 ? n_total : ring0;
             for (int it = 0; it < pre; ++it) {
                 // (a streamed stage completes only with its activation record, which cannot be
@@ -1102,7 +1099,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 for (int it = 0; it < pre; ++it) issue_acts(it);
             }
             // the in-CTA prologue borrows the last stage until it is done
-            if (p.pro == PRO_QUANT && !mbar_wait_bounded_relaxed(pro_bar, 0u, p.wait_limit)) atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
+            if (scratch && !mbar_wait_bounded_relaxed(pro_bar, 0u, p.wait_limit)) atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
             int it = pre;
             for (; it < n_total; ++it) {
                 const int s = it % NS;
@@ -1114,29 +1111,6 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 landed(it - D);
                 issue_weights(it);
                 if (streaming) issue_acts(it);
-            }
-            // All of this CTA's units are on their way.  While its last tile is closed and the next
-            // kernel starts up HBM would idle: pull the first units of the next matvec's CTA of the
-            // same index into L2, one unit per `next_pace` ns (about the rate at which an SM's share
-            // of HBM delivers them, so that nothing queues in front of the closing crews' small
-            // loads), until the CTA's last tile is closed.  Fire and forget: nothing waits for these.
-            if (p.next_W && (int)blockIdx.x < p.next_grid && it == n_total) {
-                const uint32_t Un = (uint32_t)p.next_n_tiles * (uint32_t)p.next_KS, Gn = (uint32_t)p.next_grid;
-                const UnitOrder nxt(blockIdx.x * Un / Gn, (blockIdx.x + 1) * Un / Gn, (uint32_t)p.next_KS);
-                const int cnt = nxt.n_total < p.next_units ? nxt.n_total : p.next_units;
-                const int nkt = p.next_ty == TY_Q8_0 ? Q8_KT : Q4_KT_SB * 8;
-                volatile int *done = s_flags + 3;
-                for (int j = 0; j < cnt && !*done; ++j) {
-                    const uint32_t u = nxt.at(j);
-                    const int nks = (int)(u % p.next_KS);
-                    const int kb = min(nkt, p.next_nb - nks * nkt);
-                    const uint32_t bytes = p.next_ty == TY_Q8_0 ? (uint32_t)kb * Q8_BLOCK_UNIT : (uint32_t)(kb / 8) * Q4_SB_UNIT;
-                    const uint32_t off = p.next_ty == TY_Q8_0 ? (uint32_t)nks * Q8_KT * Q8_BLOCK_UNIT
-                                                              : (uint32_t)nks * Q4_KT_SB * Q4_SB_UNIT;
-                    const uint8_t *src = p.next_W + (size_t)(u / p.next_KS) * p.next_tile_bytes + off;
-                    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-                    if (p.next_pace > 0) __nanosleep(p.next_pace);
-                }
             }
             // Every copy issued above lands before this lane leaves: wait (bounded)
             // for the stages still in flight so no bulk write outlives the CTA.
@@ -1246,7 +1220,6 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 if (tl && cw.t == 0 && final_tile && p.pro != PRO_QUANT) tl[7] = globaltimer_ns();  // pieces added
                 epilogue_tile<M>(p, cw, t_cur, fin, use_pre ? pre : nullptr, rope_pre, gam_pre);
             }
-            if (final_tile && cw.t == 0) *reinterpret_cast<volatile int *>(s_flags + 3) = 1;
     };
 
     if (warp > N_CONSUMER_WARPS) {
@@ -1323,17 +1296,17 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     if (tid == 0 && acts_copy) {
         // the activations, as soon as they exist
         const uint64_t pol_a = l2_policy_evict_last();
-        if (p.pro == PRO_QUANT) {
-            // the raw row into the scratch stage (the ring's last, which the producer leaves alone until pro_bar)
-            const uint32_t bytes = (uint32_t)p.prep.n * 4u;
-            mbar_arrive_expect_tx(acts_bar, bytes);
-            bulk_g2s(stages + (size_t)(NS - 1) * stage_bytes, p.prep.x, bytes, acts_bar, pol_a);
-        } else {
-            const uint32_t bytes = (uint32_t)(p.KS * act_rec);
-            mbar_arrive_expect_tx(acts_bar, bytes);
-            for (uint32_t o = 0; o < bytes; o += 32768u)
-                bulk_g2s(res + o, p.act.base + o, min(32768u, bytes - o), acts_bar, pol_a);
-        }
+        const uint32_t bytes = (uint32_t)(p.KS * act_rec);
+        mbar_arrive_expect_tx(acts_bar, bytes);
+        for (uint32_t o = 0; o < bytes; o += 32768u)
+            bulk_g2s(res + o, p.act.base + o, min(32768u, bytes - o), acts_bar, pol_a);
+    }
+    float4 xr[PRO_J];
+#pragma unroll
+    for (int j = 0; j < PRO_J; ++j) {
+        const int e = 4 * tid + PRO_CHUNK * j;
+        xr[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (p.pro == PRO_QUANT && p.xin.index < 0 && e < p.prep.n) xr[j] = __ldcg(reinterpret_cast<const float4 *>(p.prep.x + e));
     }
     float *s_scale = red;  // [m_out] row scales of the block below; red is free until the first tile closes
     if (p.pro == PRO_LOAD && p.norm_sumsq) {
@@ -1371,8 +1344,8 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         consumer_bar();
     }
     if (p.pro == PRO_QUANT) {
-        if (tl && tid == 0) tl[4] = globaltimer_ns();  // raw row landed
-        prologue_quant<M>(p, res, reinterpret_cast<float *>(stages + (size_t)(NS - 1) * stage_bytes), red, tid, gam, ssq_in);
+        if (tl && tid == 0) tl[4] = globaltimer_ns();  // raw row requested
+        prologue_quant<M>(p, res, reinterpret_cast<float *>(stages + (size_t)(NS - 1) * stage_bytes), red, tid, gam, ssq_in, xr);
         // generic-proxy accesses to the scratch are done; the bulk-copy engine may overwrite it
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
