@@ -572,6 +572,7 @@ int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool
         dump = true;
         k = pick_kernel(W->ty, mode.m_eff, true);
     }
+    p.launch_id = c->launch_no;
     c->launch_no++;
     const int act_rec = p.act.rec_bytes();
     const int ns = pick_stages(c, (int)W->ty, mode.m_eff, p.pro, W->KS, act_rec);
@@ -649,11 +650,13 @@ int finish(apk_ctx *c) {
         // a kernel that gave up may have left tagged partial sums behind
         if (c->partials.p) cudaMemsetAsync(c->partials.p, 0, c->partials.cap, c->stream);
         cudaStreamSynchronize(c->stream);
-        return fail(APK_ERR_TIMEOUT, "device-side wait expired (%s)",
-                    w == ERRW_PRODUCER_TIMEOUT ? "copy producer"
-                    : w == ERRW_PEER_TIMEOUT   ? "a peer rank never delivered its partial sums"
-                    : w == ERRW_FINISHER_TIMEOUT ? "a tile piece of another CTA never arrived"
-                                                 : "tile consumer");
+        const int kind = w & 15;
+        return fail(APK_ERR_TIMEOUT, "device-side wait expired (%s; site %d, launch %d)",
+                    kind == ERRW_PRODUCER_TIMEOUT ? "copy producer"
+                    : kind == ERRW_PEER_TIMEOUT   ? "a peer rank never delivered its partial sums"
+                    : kind == ERRW_FINISHER_TIMEOUT ? "a tile piece of another CTA never arrived"
+                                                    : "tile consumer",
+                    (w >> 4) & 15, w >> 8);
     }
     return APK_OK;
 }

@@ -387,6 +387,7 @@ struct TokenLaunch {
 // Enqueue one token's work on the stream (called under capture).
 int enqueue_token(apk_ctx *c, Plan *P, uint32_t m, int argmax, int *n_launches) {
     const uint64_t l0 = c->st.launches;
+    c->launch_no = 0;  // launches are numbered within the token (error reports, parity instrumentation)
     TokenLaunch T(c, P, m);
     CUDA_TRY(cudaMemcpyAsync(P->x[0].p, P->xin.p, (size_t)m * P->hidden * 4, cudaMemcpyDeviceToDevice, c->stream));
     for (uint32_t l = 0; l < P->n_layers; ++l) {

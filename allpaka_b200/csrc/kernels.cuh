@@ -56,7 +56,11 @@ constexpr int MAX_STAGES = 8;
 constexpr int TY_Q8_0 = 8;
 constexpr int TY_Q4_K = 12;
 
-// Error words written by kernels (never a trap): which bounded wait gave up.
+// Error words written by kernels (never a trap): which bounded wait gave up.  The matvec kernel
+// records kind | site << 4 | launch number << 8 (the first one to give up wins): sites 1-3 the
+// copy producer (a landed stage, the prologue scratch, an empty stage), 5 another CTA's tile
+// piece, 6 the finishers waiting for a hand-off, 8-10 the consumers (activation records, a full
+// stage, the hand-off buffer).
 constexpr int ERRW_PRODUCER_TIMEOUT = 1;
 constexpr int ERRW_CONSUMER_TIMEOUT = 2;
 constexpr int ERRW_PEER_TIMEOUT = 3;
@@ -124,6 +128,9 @@ struct ActLayout {
     }
 };
 
+struct MvParams;
+__device__ __forceinline__ void note_timeout(const MvParams &p, int kind, int site);
+
 struct PrepParams {
     const float *x; int ldx;                 // [m][n] activations
     const float *add; int ldadd;             // optional addend (residual / combined partial sums)
@@ -160,6 +167,7 @@ struct MvParams {
     int pdl;            // launched with a programmatic dependency on the previous kernel
     unsigned long long *partials;  // [gridDim.x][2][MAX_M_EFF][128] tagged partial sums (see part_store)
     int *err;           // error word
+    int launch_id;      // number of this launch within its submission (goes into the error word)
     long long wait_limit;  // cycle budget of every bounded wait in this launch
     int32_t *dump;      // optional [m_eff][n_out][nb] int32 block dots
     uint8_t *act_dump;  // optional: CTA 0 copies its resident activation records here (parity instrumentation)
@@ -206,6 +214,10 @@ struct MvParams {
     int norm_blocks;                   // 32-element blocks per row
     float norm_eps;
 };
+
+__device__ __forceinline__ void note_timeout(const MvParams &p, int kind, int site) {
+    atomicCAS(p.err, 0, kind | (site << 4) | (p.launch_id << 8));
+}
 
 // ------------------------------------------------------------------ PTX glue
 
@@ -668,6 +680,101 @@ __global__ void repack_q4_k_kernel(RepackParams p) {
     }
 }
 
+// ------------------------------------------------------ token ends (embedding row, greedy chain)
+//
+// The embedding row of a token, dequantised straight out of the tiled stream (the LM head of a
+// model with tied embeddings is the same resident matrix): x[i] = d * q for Q8_0
+// (crates/allpaka-gguf/src/dequant.rs:93-126), d*sc*q - dmin*mn for Q4_K (dequant.rs:211-231),
+// with the reference's operation order (two roundings, no fused multiply-add).
+struct EmbedParams {
+    const uint8_t *W;         // tiled stream of the [vocab, hidden] table
+    int ty, nb, n_rows;       // nb: 32-element blocks per row
+    uint32_t tile_bytes;
+    const uint32_t *token_dev;  // the token id lives on the device (greedy chain) ...
+    uint32_t token;             // ... or comes with the launch
+    float *x;                 // [hidden]
+    int *err;
+};
+
+__global__ void __launch_bounds__(256) embed_row_kernel(EmbedParams p) {
+    uint32_t tok = p.token_dev ? *p.token_dev : p.token;
+    if (tok >= (uint32_t)p.n_rows) tok = (uint32_t)p.n_rows - 1;  // (the host checks ids it can see; a chained id is an argmax over n_rows)
+    const int tile = (int)(tok / TILE_ROWS), rt = (int)(tok % TILE_ROWS);
+    int rg, h16, g, upper;
+    frag_pos(rt, rg, h16, g, upper);
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p.ty == TY_Q8_0) {
+        const int b = idx >> 3, w = idx & 7;
+        if (b >= p.nb) return;
+        const int ks = b / Q8_KT, bl = b % Q8_KT;
+        const int kb = min(Q8_KT, p.nb - ks * Q8_KT);
+        const uint8_t *unit = p.W + (size_t)tile * p.tile_bytes + (size_t)ks * Q8_KT * Q8_BLOCK_UNIT;
+        const uint8_t *frag = unit + (size_t)(((bl * 4 + rg) * 2 + h16) * 32) * 16;
+        const int lane = g * 4 + (w & 3), reg = 2 * (w >> 2) + upper;
+        const uint32_t v = *reinterpret_cast<const uint32_t *>(frag + lane * 16 + reg * 4);
+        const float d = __half2float(*reinterpret_cast<const __half *>(unit + kb * 4096 + ((bl * 4 + rg) * 8 + g) * 8 + (h16 * 2 + upper) * 2));
+        float4 o;
+        o.x = __fmul_rn(d, (float)(int8_t)(v & 0xffu));
+        o.y = __fmul_rn(d, (float)(int8_t)((v >> 8) & 0xffu));
+        o.z = __fmul_rn(d, (float)(int8_t)((v >> 16) & 0xffu));
+        o.w = __fmul_rn(d, (float)(int8_t)(v >> 24));
+        *reinterpret_cast<float4 *>(p.x + b * 32 + 4 * w) = o;
+    } else {
+        // one thread per (super-block, pair of sub-blocks, 4-byte word of nibbles)
+        const int sb = idx >> 5, pr = (idx >> 3) & 3, w = idx & 7;
+        if (sb >= p.nb / 8) return;
+        const int ks = sb / Q4_KT_SB, sl = sb % Q4_KT_SB;
+        const uint8_t *base = p.W + (size_t)tile * p.tile_bytes + (size_t)ks * Q4_KT_SB * Q4_SB_UNIT + (size_t)sl * Q4_SB_UNIT +
+                              (size_t)rg * Q4_SB_RG;
+        const uint8_t *frag = base + (size_t)((pr * 2 + h16) * 32) * 16;
+        const int lane = g * 4 + (w & 3), reg = 2 * (w >> 2) + upper;
+        const uint32_t v = *reinterpret_cast<const uint32_t *>(frag + lane * 16 + reg * 4);
+        const uint8_t *hdr = base + 4096;
+        const int row4 = h16 * 2 + upper;
+        const uint32_t dd = *reinterpret_cast<const uint32_t *>(hdr + (g * 4 + row4) * 4);
+        const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xffffu)));
+        const float dmin = __half2float(__ushort_as_half((unsigned short)(dd >> 16)));
+        const int j1 = 2 * pr, j2 = 2 * pr + 1;
+        const float sc1 = (float)hdr[128 + ((g * 2 + (j1 >> 2)) * 4 + row4) * 4 + (j1 & 3)];
+        const float mn1 = (float)hdr[384 + ((g * 2 + (j1 >> 2)) * 4 + row4) * 4 + (j1 & 3)];
+        const float sc2 = (float)hdr[128 + ((g * 2 + (j2 >> 2)) * 4 + row4) * 4 + (j2 & 3)];
+        const float mn2 = (float)hdr[384 + ((g * 2 + (j2 >> 2)) * 4 + row4) * 4 + (j2 & 3)];
+        const float d_sc1 = __fmul_rn(d, sc1), dm1 = __fmul_rn(dmin, mn1);
+        const float d_sc2 = __fmul_rn(d, sc2), dm2 = __fmul_rn(dmin, mn2);
+        float *o = p.x + sb * 256 + pr * 64 + 4 * w;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const uint32_t byte = (v >> (8 * k)) & 0xffu;
+            o[k] = __fsub_rn(__fmul_rn(d_sc1, (float)(byte & 0xfu)), dm1);
+            o[32 + k] = __fsub_rn(__fmul_rn(d_sc2, (float)(byte >> 4)), dm2);
+        }
+    }
+}
+
+// One step of the greedy chain, after the token's graph: keep the winner, make it the next
+// input token, and put the next position's RoPE row in place.  One CTA.
+struct ChainParams {
+    const uint32_t *amax;  // the step's greedy winner
+    uint32_t *token;       // next input token
+    uint32_t *hist;        // [steps] winners so far
+    uint32_t *step;        // steps done
+    const float *rope_tab; // [steps][row] (sin, cos) rows, one per position
+    float *rope;           // the row the token graph reads
+    int row;               // floats per row
+    int n_steps;
+};
+__global__ void __launch_bounds__(128) chain_advance_kernel(ChainParams p) {
+    const uint32_t s = *p.step;
+    if (threadIdx.x == 0) {
+        p.hist[s] = *p.amax;
+        *p.token = *p.amax;
+    }
+    if (s + 1 < (uint32_t)p.n_steps)
+        for (int i = threadIdx.x; i < p.row; i += blockDim.x) p.rope[i] = p.rope_tab[(size_t)(s + 1) * p.row + i];
+    __syncthreads();
+    if (threadIdx.x == 0) *p.step = s + 1;
+}
+
 // ------------------------------------------------- synthetic weights (bench)
 //
 // Counter-based generator for benchmark tensors: raw GGUF blocks are produced
@@ -1079,7 +1186,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             auto landed = [&](int j) {  // K-step j of this CTA's walk is in shared memory
                 if (j >= 0 && !stuck && !mbar_wait_bounded_relaxed(&full[j % NS], (uint32_t)((j / NS) & 1), p.wait_limit)) {
                     stuck = true;
-                    atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
+                    note_timeout(p, ERRW_PRODUCER_TIMEOUT, 1);
                 }
             };
             // (the in-CTA prologue of a Q4_K consumer uses the last stage as scratch for its exact block sums)
@@ -1099,13 +1206,13 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 for (int it = 0; it < pre; ++it) issue_acts(it);
             }
             // the in-CTA prologue borrows the last stage until it is done
-            if (scratch && !mbar_wait_bounded_relaxed(pro_bar, 0u, p.wait_limit)) atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
+            if (scratch && !mbar_wait_bounded_relaxed(pro_bar, 0u, p.wait_limit)) note_timeout(p, ERRW_PRODUCER_TIMEOUT, 2);
             int it = pre;
             for (; it < n_total; ++it) {
                 const int s = it % NS;
                 const uint32_t ph = (uint32_t)((it / NS) & 1);
                 if (stuck || !mbar_wait_bounded_relaxed(&empty[s], ph ^ 1u, p.wait_limit)) {
-                    atomicExch(p.err, ERRW_PRODUCER_TIMEOUT);
+                    note_timeout(p, ERRW_PRODUCER_TIMEOUT, 3);
                     break;
                 }
                 landed(it - D);
@@ -1214,7 +1321,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                         fin[i] = v + fin[i];
                         if (two) fin[i2] = v2 + fin[i2];
                     }
-                    if (gave_up) atomicExch(p.err, ERRW_FINISHER_TIMEOUT);
+                    if (gave_up) note_timeout(p, ERRW_FINISHER_TIMEOUT, 5);
                     cw.sync();
                 }
                 if (tl && cw.t == 0 && final_tile && p.pro != PRO_QUANT) tl[7] = globaltimer_ns();  // pieces added
@@ -1247,7 +1354,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             // one thread waits (bounded) and tells the others, so all of them leave together
             if (ftid == 0) {
                 const bool ok = mbar_wait_bounded(red_full, n & 1u, p.wait_limit);
-                if (!ok) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
+                if (!ok) note_timeout(p, ERRW_CONSUMER_TIMEOUT, 6);
                 s_flags[2] = ok ? 1 : 0;
             }
             finisher_bar();
@@ -1325,7 +1432,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     if (p.pro == PRO_QUANT && p.prep.gamma && p.prep.sumsq) ssq_in = sumsq_total(p.prep.sumsq, p.prep.n >> 5, lane);
     if (acts_copy && !mbar_wait_bounded(acts_bar, 0u, p.wait_limit)) {
         aborted = true;
-        if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
+        if (lane == 0) note_timeout(p, ERRW_CONSUMER_TIMEOUT, 8);
     }
     if (p.pro == PRO_LOAD && p.norm_sumsq) {
         consumer_bar();
@@ -1384,7 +1491,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         const bool mine = !CH || (it & 1) == ug;
         if (mine && !aborted && !mbar_wait_bounded(&full[s], ph, p.wait_limit)) {
             aborted = true;
-            if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
+            if (lane == 0) note_timeout(p, ERRW_CONSUMER_TIMEOUT, 9);
         }
         if (tl && mine && lane == 0 && (warp & 7) == 0) {
             if (it == 0) tl[1] = globaltimer_ns();   // first unit landed
@@ -1713,7 +1820,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         // close within a fraction of a microsecond.
         if (n_handoff > 0 && !aborted && !mbar_wait_bounded(red_empty, (n_handoff - 1u) & 1u, p.wait_limit)) {
             aborted = true;
-            if (lane == 0) atomicExch(p.err, ERRW_CONSUMER_TIMEOUT);
+            if (lane == 0) note_timeout(p, ERRW_CONSUMER_TIMEOUT, 10);
         }
         if constexpr (CH) {
             // columns of the same activation row sit in different lt lanes: add them up

@@ -155,8 +155,8 @@ extern "C" int apk_matvec_noalloc(apk_ctx *c, const void *w, uint32_t ty, uint32
     CUDA_TRY(cudaStreamSynchronize(st));
     if (herr != 0)
         return fail(APK_ERR_TIMEOUT, "device-side wait expired (%s)",
-                    herr == ERRW_PRODUCER_TIMEOUT   ? "copy producer"
-                    : herr == ERRW_FINISHER_TIMEOUT ? "a tile piece of another CTA never arrived"
+                    (herr & 15) == ERRW_PRODUCER_TIMEOUT   ? "copy producer"
+                    : (herr & 15) == ERRW_FINISHER_TIMEOUT ? "a tile piece of another CTA never arrived"
                                                     : "tile consumer");
     dev->dirty = false;
     return APK_OK;

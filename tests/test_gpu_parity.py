@@ -330,7 +330,7 @@ def test_token_timeline_is_ordered(gpu, orc):
     st = gpu.debug_token_timeline(req, 16).astype(np.int64)
     assert st.shape[0] == 2 * 4 + 1 and st.shape[2] == 8
     for slab in st:
-        live = slab[slab[:, 0] > 0]
+        live = slab[(slab[:, 0] > 0) & (slab[:, 2] > 0)]  # CTAs that got work (a late one finds no chunk left and leaves at once)
         assert len(live) > 0
         assert np.all(live[:, 2] >= live[:, 0]) and np.all(live[:, 5] >= live[:, 2])
     ends = [slab[:, 5].max() for slab in st]

@@ -33,6 +33,7 @@ CASES = [
     (Q8_0, 256, 25600, 2, 1),    # f32-activation mode, long rows (records streamed)
     (Q4_K, 513, 2048, 1, 2),
     (Q4_K, 130, 1024, 4, 1),
+    (Q8_0, 16384, 5120, 1, 2),
 ]
 
 
