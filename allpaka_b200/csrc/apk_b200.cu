@@ -145,6 +145,19 @@ constexpr int NCCL_SUM = 0;      // ncclSum
 
 struct RecMeta { int ke, m_eff, two_level, launch; };
 
+}  // namespace
+
+// The f16 KV cache of a session (this rank's kv heads): K slabs of every layer, then the V slabs.
+struct apk_kv {
+    uint32_t n_layers = 0, kv_dim = 0, capacity = 0;  // kv_dim: this rank's
+    __half *base = nullptr;
+    size_t layer_stride() const { return (size_t)kv_dim * capacity; }
+    __half *k(uint32_t layer) const { return base + layer_stride() * layer; }
+    __half *v(uint32_t layer) const { return base + layer_stride() * (n_layers + layer); }
+};
+
+namespace {
+
 struct PlanLayer {
     DevMatrix *qkv = nullptr, *wo = nullptr, *gateup = nullptr, *down = nullptr;
     const float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;  // device
@@ -158,19 +171,25 @@ struct Plan {
     uint64_t desc_hash = 0;  // every layer's descriptors (weight and norm pointers, types, row counts)
     uint32_t hidden = 0, head_dim = 0, n_heads = 0, n_kv_heads = 0, rot_dim = 0, vocab = 0, ffn = 0;
     float eps = 0;
+    uint32_t attn_core = 0;
+    const apk_kv *kv = nullptr;
+    float scale = 0;
     // local (per-rank) shapes
     uint32_t nq_l = 0, nkv_l = 0, ffn_l = 0, vocab_l = 0;
     std::vector<PlanLayer> L;
     DevMatrix *head = nullptr;
+    DevMatrix *embd = nullptr;  // token embedding table (unsharded), when the request names one
     const float *out_norm = nullptr;
     DevBuf norms, xin, x[2], qkv, yp, act_h, act_q, act_d, logits, logits_all, amax, rope, sumsq, hidden_out;
+    DevBuf chain;  // greedy chain state: token | step | hist[] | rope rows
+    DevBuf pos, attn_part, attn_out;  // cache position of row 0; split partials and f32 rows of the attention core
     cudaGraphExec_t exec[APK_MAX_M + 1][2] = {};  // [m][argmax]
     int launches[APK_MAX_M + 1][2] = {};
     ~Plan() {
         for (auto &row : exec)
             for (auto &e : row)
                 if (e) cudaGraphExecDestroy(e);
-        for (DevBuf *b : {&norms, &xin, &x[0], &x[1], &qkv, &yp, &act_h, &act_q, &act_d, &logits, &logits_all, &amax, &rope, &sumsq, &hidden_out})
+        for (DevBuf *b : {&norms, &xin, &x[0], &x[1], &qkv, &yp, &act_h, &act_q, &act_d, &logits, &logits_all, &amax, &rope, &sumsq, &hidden_out, &chain, &pos, &attn_part, &attn_out})
             b->release();
     }
 };
@@ -559,7 +578,7 @@ int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool
     p.tile_bytes = W->tile_bytes;
     p.two_level = mode.two_level;
     p.m_out = mode.two_level ? mode.m_eff / 2 : mode.m_eff;
-    p.partials = c->partials.as<unsigned long long>();
+    p.partials = c->partials.as<unsigned long long>() + (size_t)(c->launch_no & 1) * c->n_sm * 2 * MAX_M_EFF * TILE_ROWS;
     p.err = c->d_err;
     p.wait_limit = c->wait_limit;
     p.pdl = c->use_pdl ? 1 : 0;
@@ -812,7 +831,9 @@ int apk_init(apk_ctx **out, int device) {
     CUDA_TRY(cudaMemset(c->d_err, 0, sizeof(int)));
     CUDA_TRY(cudaMallocHost((void **)&c->h_err, sizeof(int)));
     *c->h_err = 0;
-    APK_TRY(c->partials.ensure((size_t)c->n_sm * 2 * MAX_M_EFF * TILE_ROWS * sizeof(unsigned long long), true));
+    // two copies, used by alternate launches: a launch that takes its input from the peer exchange
+    // starts before the launch in front of it has drained
+    APK_TRY(c->partials.ensure(2 * (size_t)c->n_sm * 2 * MAX_M_EFF * TILE_ROWS * sizeof(unsigned long long), true));
     APK_TRY(init_kernel_attrs(c.get()));
     if (const char *e = getenv("ALLPAKA_B200_PDL")) c->use_pdl = atoi(e) != 0;
     if (const char *e = getenv("ALLPAKA_B200_FUSE_NORM")) c->fuse_norm = atoi(e);

@@ -83,11 +83,13 @@ uint64_t desc_hash(const apk_token_req *r) {
     }
     mix((uint64_t)(uintptr_t)r->output_norm);
     mat(r->output);
+    mat(r->embd);
     return h;
 }
 
 bool plan_matches(const Plan *p, const apk_token_req *r) {
-    return p && p->layers_key == r->layers && p->n_layers == r->n_layers && p->output_key == r->output.w &&
+    return p && p->attn_core == r->attn_core && p->kv == r->kv && p->scale == r->scale &&
+           p->layers_key == r->layers && p->n_layers == r->n_layers && p->output_key == r->output.w &&
            p->hidden == r->hidden && p->head_dim == r->head_dim && p->n_heads == r->n_heads &&
            p->n_kv_heads == r->n_kv_heads && p->rot_dim == r->rot_dim && p->vocab == r->output.n_out &&
            p->eps == r->eps && p->desc_hash == desc_hash(r);
@@ -100,6 +102,36 @@ int nccl_allreduce(apk_ctx *c, float *buf, size_t n) {
 }
 
 bool uses_xch(const apk_ctx *c) { return c->p2p_ready && (c->world > 1 || c->self_xch); }
+
+// Position splits of the attention core: fixed per cache (the launch shape is captured), about
+// 256 positions per CTA at full capacity.
+int attn_splits(uint32_t capacity) { return (int)std::max<uint32_t>(1, std::min<uint32_t>(32, (capacity + 255) / 256)); }
+
+// q [m][ldq] -> attention over one layer of the cache -> optional f32 rows, optional records for wo.
+int launch_attention(apk_ctx *c, const apk_kv *kv, uint32_t layer, const float *q, int ldq, uint32_t m, uint32_t n_heads_l,
+                     const uint32_t *pos_dev, uint32_t pos, float scale, float *part, float *out, int ldo,
+                     const ActLayout *next, int next_two_level, int next_need_sum) {
+    AttnParams ap{};
+    ap.q = q; ap.ldq = ldq;
+    ap.kc = kv->k(layer); ap.vc = kv->v(layer);
+    ap.kv_dim = (int)kv->kv_dim;
+    ap.n_kv_heads = (int)(kv->kv_dim / TILE_ROWS);
+    ap.group = (int)(n_heads_l / (kv->kv_dim / TILE_ROWS));
+    ap.pos_dev = pos_dev; ap.pos = pos;
+    ap.m = (int)m;
+    ap.n_splits = attn_splits(kv->capacity);
+    ap.scale = scale;
+    ap.part = part;
+    ap.out = out; ap.ldo = ldo;
+    if (next) ap.next = *next;
+    ap.next_two_level = next_two_level;
+    ap.next_need_sum = next_need_sum;
+    const int pdl = c->use_pdl ? 1 : 0;
+    CUDA_TRY(launch_ex(c, attn_split_kernel, dim3(ap.n_kv_heads, ap.n_splits, m), dim3(ATT_WARPS * 32), 0, c->use_pdl, ap, pdl));
+    CUDA_TRY(launch_ex(c, attn_combine_kernel, dim3(n_heads_l, m), dim3(TILE_ROWS), 0, c->use_pdl, ap, pdl));
+    c->st.launches += 2;
+    return APK_OK;
+}
 
 int build_plan(apk_ctx *c, const apk_token_req *r) {
     c->plan.reset();
@@ -114,7 +146,8 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
     P->desc_hash = desc_hash(r);
     P->hidden = H; P->head_dim = r->head_dim; P->n_heads = r->n_heads; P->n_kv_heads = r->n_kv_heads;
     P->rot_dim = r->rot_dim; P->vocab = r->output.n_out; P->eps = r->eps; P->ffn = ffn;
-    if (uses_xch(c) && ((size_t)APK_MAX_M * H > (size_t)XCH_ROW_FLOATS || H % 4 || H > (uint32_t)XCH_MAX_TILES * TILE_ROWS))
+    P->attn_core = r->attn_core; P->kv = r->kv; P->scale = r->scale;
+    if (uses_xch(c) && ((size_t)APK_MAX_M * H > (size_t)XCH_ROW_FLOATS || H % 4))
         return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "hidden %u exceeds the peer exchange buffer", H);
     if (P->vocab % c->world) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "vocab %u does not split over %d ranks", P->vocab, c->world);
     P->nq_l = nq / c->world; P->nkv_l = nkv / c->world; P->vocab_l = P->vocab / c->world;
@@ -161,6 +194,12 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
         if ((rc = resolve_plain(c, "output", r->output.w, r->output.ty, P->vocab, H, SHARD_ROWS, &P->head))) { c->st.decode_declines++; return rc; }
     }
     P->out_norm = P->norms.as<float>() + per_layer * r->n_layers;
+    if (r->embd.w) {
+        // the embedding table stays whole on every rank (a row is looked up, not multiplied); at one
+        // rank a tied LM head resolves to the same resident matrix
+        int rc;
+        if ((rc = resolve_plain(c, "token embedding", r->embd.w, r->embd.ty, r->embd.n_out, H, SHARD_NONE, &P->embd))) { c->st.decode_declines++; return rc; }
+    }
 
     const uint32_t M = APK_MAX_M, ldq = P->nq_l + 2 * P->nkv_l;
     const uint32_t big = APK_TY_Q4_K;  // the larger record flavour bounds every buffer
@@ -178,14 +217,23 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
     APK_TRY(P->rope.ensure((size_t)M * (r->rot_dim / 2 + 1) * 2 * 4));
     APK_TRY(P->sumsq.ensure((size_t)M * (H / 32 + 1) * sizeof(double), true));
     APK_TRY(P->hidden_out.ensure((size_t)M * H * 4));
+    APK_TRY(P->pos.ensure(256, true));
+    if (r->attn_core == APK_ATTN_CAUSAL) {
+        if (nq % c->world || nkv % c->world || (nq / nkv) * nkv != nq)
+            return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "heads do not split over the ranks");
+        if (!r->kv || r->kv->n_layers < r->n_layers || r->kv->kv_dim != P->nkv_l)
+            return decline_decode(c, APK_ERR_INVALID_ARG, "the KV cache does not fit the request (layers, kv_dim)");
+        APK_TRY(P->attn_part.ensure((size_t)M * (P->nq_l / TILE_ROWS) * attn_splits(r->kv->capacity) * ATT_PART * 4));
+        APK_TRY(P->attn_out.ensure((size_t)M * P->nq_l * 4));
+    }
     if (uses_xch(c)) {
         // A new plan restarts the exchange numbering (its exchanges per token may differ): clear
-        // this rank's flags and token counter, then meet the other ranks, so that nobody's first
-        // token runs against a peer that is still uploading or still holds old flags.  (The bounded
+        // this rank's tagged words and token counter, then meet the other ranks, so that nobody's
+        // first token runs against a peer that is still uploading or against old tags.  (The bounded
         // device-side waits are for a peer that died, not for one that is a few seconds behind.)
         if (c->world > 1) APK_TRY(nccl_allreduce(c, P->yp.as<float>(), 1));  // every rank's previous token is over
         CUDA_TRY(cudaStreamSynchronize(c->stream));
-        CUDA_TRY(cudaMemsetAsync(xch_flags(c->xch_local), 0, XCH_FLAGS_BYTES + 256, c->stream));
+        CUDA_TRY(cudaMemsetAsync(c->xch_local, 0, XCH_BYTES, c->stream));
     }
     if (c->world > 1) {
         APK_TRY(nccl_allreduce(c, P->yp.as<float>(), 1));
@@ -206,6 +254,7 @@ struct TokenLaunch {
     int pending_xch = -1;      // peer exchange: index of the exchange whose sum is not yet added to x
     int n_xch = 0;             // exchanges launched so far in this token
     bool first = true;         // the next matvec launch is the token's first
+    bool in_token = true;      // launches follow the token's order (false: one kind replayed in isolation)
     bool have_sumsq = false;   // the last residual matvec left the per-block sums of squares of x[cur]
     // the previous residual matvec already quantised x * gamma for this (matrix, mode): its
     // records sit in act_h and only lack the row-wide RMSNorm scale (opt-in approximation)
@@ -261,6 +310,7 @@ struct TokenLaunch {
                 APK_TRY(stage_acts(c, W, xc, (int)H, nullptr, 0, xn, (int)H, gamma, P->eps, m, mode, P->act_h.p, p, nullptr, hout));
                 p->xch = c->xch;
                 p->xin = XchSeq{pending_xch, per_token()};
+                p->xin_late = in_token ? 1 : 0;
                 if (advance) { cur ^= 1; pending_xch = -1; }
                 return APK_OK;
             }
@@ -291,7 +341,7 @@ struct TokenLaunch {
         record_hook(xc, mode, p);
         return APK_OK;
     }
-    int qkv(PlanLayer &L, bool advance = true) {
+    int qkv(PlanLayer &L, bool advance = true, uint32_t layer = 0) {
         MvParams p{};
         APK_TRY(normed_input(L.qkv, L.attn_norm, q8, &p, advance));
         p.epi = EPI_QKV_ROPE;
@@ -304,11 +354,26 @@ struct TokenLaunch {
         p.eps = P->eps;
         p.rope = P->rope.as<float>();
         p.half = (int)(P->rot_dim / 2);
-        // attention core stand-in (identity): the roped Q slice, packed here, is wo's input
-        p.q_next = act_layout(P->act_q.p, L.wo->ty, autom.m_eff);
-        p.q_next_two_level = autom.two_level;
-        p.q_next_need_sum = L.wo->ty == APK_TY_Q4_K;
+        if (P->attn_core == APK_ATTN_CAUSAL) {
+            // K (roped) and V rows go into the f16 cache at the rows' positions; the attention core reads them there
+            p.kv_k = P->kv->k(layer);
+            p.kv_v = P->kv->v(layer);
+            p.kv_dim = (int)P->kv->kv_dim;
+            p.pos_dev = P->pos.as<uint32_t>();
+        } else {
+            // attention core stand-in (identity): the roped Q slice, packed here, is wo's input
+            p.q_next = act_layout(P->act_q.p, L.wo->ty, autom.m_eff);
+            p.q_next_two_level = autom.two_level;
+            p.q_next_need_sum = L.wo->ty == APK_TY_Q4_K;
+        }
         return launch(L.qkv, p, q8, L.wo);
+    }
+    // the attention core over the cache: its result, packed, is wo's input
+    int attention(PlanLayer &L, uint32_t layer) {
+        const ActLayout next = act_layout(P->act_q.p, L.wo->ty, autom.m_eff);
+        return launch_attention(c, P->kv, layer, P->qkv.as<float>(), (int)(P->nq_l + 2 * P->nkv_l), m, P->nq_l / TILE_ROWS,
+                                P->pos.as<uint32_t>(), 0u, P->scale, P->attn_part.as<float>(), P->attn_out.as<float>(),
+                                (int)P->nq_l, &next, autom.two_level, L.wo->ty == APK_TY_Q4_K);
     }
     // next_*: the matvec that will read the updated rows through an RMSNorm (null: none)
     int residual(DevMatrix *W, void *records, const DevMatrix *next_W = nullptr, const float *next_gamma = nullptr,
@@ -384,6 +449,27 @@ struct TokenLaunch {
     }
 };
 
+// x <- embedding row of a token (id on the device, or given).
+int launch_embed(apk_ctx *c, Plan *P, const uint32_t *token_dev, uint32_t token, float *x) {
+    const DevMatrix *E = P->embd;
+    if (!E) return fail(APK_ERR_INVALID_ARG, "the request names no embedding table");
+    EmbedParams ep{};
+    ep.W = E->d;
+    ep.ty = (int)E->ty;
+    ep.nb = E->nb;
+    ep.n_rows = (int)E->n_out;
+    ep.tile_bytes = E->tile_bytes;
+    ep.token_dev = token_dev;
+    ep.token = token;
+    ep.x = x;
+    ep.err = c->d_err;
+    const int threads = E->ty == APK_TY_Q8_0 ? E->nb * 8 : (E->nb / 8) * 32;
+    embed_row_kernel<<<(threads + 255) / 256, 256, 0, c->stream>>>(ep);
+    CUDA_TRY(cudaGetLastError());
+    c->st.launches++;
+    return APK_OK;
+}
+
 // Enqueue one token's work on the stream (called under capture).
 int enqueue_token(apk_ctx *c, Plan *P, uint32_t m, int argmax, int *n_launches) {
     const uint64_t l0 = c->st.launches;
@@ -392,7 +478,8 @@ int enqueue_token(apk_ctx *c, Plan *P, uint32_t m, int argmax, int *n_launches) 
     CUDA_TRY(cudaMemcpyAsync(P->x[0].p, P->xin.p, (size_t)m * P->hidden * 4, cudaMemcpyDeviceToDevice, c->stream));
     for (uint32_t l = 0; l < P->n_layers; ++l) {
         PlanLayer &L = P->L[l];
-        APK_TRY(T.qkv(L));
+        APK_TRY(T.qkv(L, true, l));
+        if (P->attn_core == APK_ATTN_CAUSAL) APK_TRY(T.attention(L, l));
         APK_TRY(T.wo(L));
         APK_TRY(T.gateup(L));
         APK_TRY(T.down(L, l + 1 < P->n_layers ? &P->L[l + 1] : nullptr));
@@ -441,9 +528,12 @@ int validate_token_req(apk_ctx *c, const apk_token_req *r) {
     if (!r) return fail(APK_ERR_INVALID_ARG, "decode: null request");
     c->st.decode_attempts++;
     if (r->m == 0 || r->m > APK_MAX_M) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "m = %u is outside 1..8", r->m);
-    if (r->attn_core != APK_ATTN_IDENTITY)
-        return decline_decode(c, APK_DECLINE_MISSING_CAPABILITY, "only the identity attention core is built into this library");
-    if (!r->x || (r->rot_dim && !r->rope)) return decline_decode(c, APK_ERR_INVALID_ARG, "missing input rows or rope table");
+    if (r->attn_core != APK_ATTN_IDENTITY && r->attn_core != APK_ATTN_CAUSAL)
+        return decline_decode(c, APK_DECLINE_MISSING_CAPABILITY, "attention core %u is not built into this library", r->attn_core);
+    if (r->attn_core == APK_ATTN_CAUSAL && (!r->kv || (uint64_t)r->pos + r->m > r->kv->capacity))
+        return decline_decode(c, APK_ERR_INVALID_ARG, "no KV cache, or positions %u..%u past its capacity", r->pos, r->pos + r->m - 1);
+    const bool by_token = r->use_token && r->embd.w && r->m == 1;
+    if ((!r->x && !by_token) || (r->rot_dim && !r->rope)) return decline_decode(c, APK_ERR_INVALID_ARG, "missing input rows or rope table");
     return APK_OK;
 }
 
@@ -457,13 +547,20 @@ int apk_decode_token(apk_ctx *c, const apk_token_req *r, apk_token_out *out) {
     CUDA_TRY(cudaSetDevice(c->device));
     APK_TRY(validate_token_req(c, r));
     if (r->argmax ? !out->argmax : !out->logits) return decline_decode(c, APK_ERR_INVALID_ARG, "missing output buffer");
+    const bool by_token = r->use_token && r->embd.w && r->m == 1;
+    if (by_token && r->token_id >= r->embd.n_out)
+        return decline_decode(c, APK_ERR_INVALID_ARG, "token %u out of vocabulary %u", r->token_id, r->embd.n_out);
     const uint64_t t0 = now_ns();
     APK_TRY(ensure_graph(c, r));
     Plan *P = c->plan.get();
     const uint32_t m = r->m, H = P->hidden;
-    CUDA_TRY(cudaMemcpyAsync(P->xin.p, r->x, (size_t)m * H * 4, cudaMemcpyHostToDevice, c->stream));
+    if (by_token)
+        APK_TRY(launch_embed(c, P, nullptr, r->token_id, P->xin.as<float>()));
+    else
+        CUDA_TRY(cudaMemcpyAsync(P->xin.p, r->x, (size_t)m * H * 4, cudaMemcpyHostToDevice, c->stream));
     if (r->rot_dim)
         CUDA_TRY(cudaMemcpyAsync(P->rope.p, r->rope, (size_t)m * (r->rot_dim / 2) * 2 * 4, cudaMemcpyHostToDevice, c->stream));
+    CUDA_TRY(cudaMemcpyAsync(P->pos.p, &r->pos, sizeof(uint32_t), cudaMemcpyHostToDevice, c->stream));
     CUDA_TRY(cudaGraphLaunch(P->exec[m][r->argmax ? 1 : 0], c->stream));
     c->st.launches += P->launches[m][r->argmax ? 1 : 0];
     std::vector<float> gathered;
@@ -496,8 +593,10 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
     std::lock_guard<std::mutex> g(c->mu);
     CUDA_TRY(cudaSetDevice(c->device));
     APK_TRY(validate_token_req(c, r));
+    if (!r->x) return fail(APK_ERR_INVALID_ARG, "this entry point takes its input rows from x");
     APK_TRY(ensure_graph(c, r));
     Plan *P = c->plan.get();
+    CUDA_TRY(cudaMemcpyAsync(P->pos.p, &r->pos, sizeof(uint32_t), cudaMemcpyHostToDevice, c->stream));
     const uint32_t m = r->m, H = P->hidden;
     // one real token first, so every activation buffer the kernels read holds sane data
     CUDA_TRY(cudaMemcpyAsync(P->xin.p, r->x, (size_t)m * H * 4, cudaMemcpyHostToDevice, c->stream));
@@ -515,7 +614,8 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
             for (uint32_t l = 0; l < n_launch; ++l) {
                 PlanLayer &L = P->L[l];
                 TokenLaunch T(c, P, m);  // fresh state: reads x[0], never flips buffers
-                T.first = false;         // the token counter stays: the flags of the token above satisfy every wait
+                T.first = false;         // the token counter stays: the words of the token above satisfy every wait
+                T.in_token = false;
                 if (uses_xch(c)) {
                     // as in the real token: Q|K|V, gate/up and the head gather the exchange in front of them
                     T.n_xch = (int)(2 * l + (kind >= 2 ? 1 : 0));
@@ -532,7 +632,7 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
                     T.prenormed_for = nw;
                     T.prenormed_m_eff = nm.m_eff;
                 }
-                if (kind == 0) APK_TRY(T.qkv(L, false));
+                if (kind == 0) APK_TRY(T.qkv(L, false, l));
                 else if (kind == 1) APK_TRY(T.wo(L));
                 else if (kind == 2) APK_TRY(T.gateup(L, false));
                 else if (kind == 3) APK_TRY(T.down(L, l + 1 < P->n_layers ? &P->L[l + 1] : nullptr));
@@ -562,8 +662,10 @@ int apk_debug_token_timeline(apk_ctx *c, const apk_token_req *r, uint64_t *stamp
     std::lock_guard<std::mutex> g(c->mu);
     CUDA_TRY(cudaSetDevice(c->device));
     APK_TRY(validate_token_req(c, r));
+    if (!r->x) return fail(APK_ERR_INVALID_ARG, "this entry point takes its input rows from x");
     APK_TRY(ensure_graph(c, r));
     Plan *P = c->plan.get();
+    CUDA_TRY(cudaMemcpyAsync(P->pos.p, &r->pos, sizeof(uint32_t), cudaMemcpyHostToDevice, c->stream));
     const size_t words = (size_t)max_launches * c->n_sm * 8;
     APK_TRY(c->dump.ensure(words * sizeof(uint64_t)));
     CUDA_TRY(cudaMemcpyAsync(P->xin.p, r->x, (size_t)r->m * P->hidden * 4, cudaMemcpyHostToDevice, c->stream));
@@ -590,8 +692,10 @@ int apk_decode_replay(apk_ctx *c, const apk_token_req *r, uint32_t iters, float 
     std::lock_guard<std::mutex> g(c->mu);
     CUDA_TRY(cudaSetDevice(c->device));
     APK_TRY(validate_token_req(c, r));
+    if (!r->x) return fail(APK_ERR_INVALID_ARG, "this entry point takes its input rows from x");
     APK_TRY(ensure_graph(c, r));
     Plan *P = c->plan.get();
+    CUDA_TRY(cudaMemcpyAsync(P->pos.p, &r->pos, sizeof(uint32_t), cudaMemcpyHostToDevice, c->stream));
     const int am = r->argmax ? 1 : 0;
     CUDA_TRY(cudaMemcpyAsync(P->xin.p, r->x, (size_t)r->m * P->hidden * 4, cudaMemcpyHostToDevice, c->stream));
     if (r->rot_dim)
@@ -622,9 +726,9 @@ int apk_debug_xch_timeout(apk_ctx *c) {
     if (!c) return fail(APK_ERR_INVALID_ARG, "null context");
     std::lock_guard<std::mutex> g(c->mu);
     CUDA_TRY(cudaSetDevice(c->device));
-    // Two exchange buffers on this one GPU stand for ranks 0 and 1.  Rank 0's own tile flags are
-    // raised, "rank 1" never delivers: the collecting kernel must give up after the wait budget,
-    // leave an error word and end normally.
+    // Two exchange buffers on this one GPU stand for ranks 0 and 1.  Rank 0's own words carry the
+    // exchange's tag, "rank 1" never delivers: the collecting kernel must give up after the wait
+    // budget, leave an error word and end normally.
     const int n = 256;
     float *buf[2] = {nullptr, nullptr};
     for (auto &b : buf) {
@@ -634,9 +738,11 @@ int apk_debug_xch_timeout(apk_ctx *c) {
     APK_TRY(c->x_dev.ensure(n * sizeof(float)));
     APK_TRY(c->y_dev.ensure(n * sizeof(float)));
     CUDA_TRY(cudaMemsetAsync(c->x_dev.p, 0, n * sizeof(float), c->stream));
-    const uint32_t ones[3] = {1u, 1u, 1u};
-    CUDA_TRY(cudaMemcpyAsync(xch_tok(buf[0]), ones, 4, cudaMemcpyHostToDevice, c->stream));
-    CUDA_TRY(cudaMemcpyAsync(xch_flags(buf[0]), ones, 8, cudaMemcpyHostToDevice, c->stream));  // rank 0, tiles 0 and 1
+    const uint32_t one = 1u;
+    CUDA_TRY(cudaMemcpyAsync(xch_tok(buf[0]), &one, 4, cudaMemcpyHostToDevice, c->stream));
+    std::vector<unsigned long long> own(n, 1ull << 32);  // rank 0's words of exchange 1 (parity 1): tag 1, value 0
+    CUDA_TRY(cudaMemcpyAsync(xch_words(buf[0]) + (size_t)1 * XCH_MAX_RANKS * XCH_ROW_FLOATS, own.data(), n * 8,
+                             cudaMemcpyHostToDevice, c->stream));
     XchReduceParams rp{};
     rp.xch.slots[0] = buf[0];
     rp.xch.slots[1] = buf[1];
@@ -667,9 +773,11 @@ int apk_debug_token_records(apk_ctx *c, const apk_token_req *r, uint32_t max_rec
     std::lock_guard<std::mutex> g(c->mu);
     CUDA_TRY(cudaSetDevice(c->device));
     APK_TRY(validate_token_req(c, r));
+    if (!r->x) return fail(APK_ERR_INVALID_ARG, "this entry point takes its input rows from x");
     if (c->world != 1 || uses_xch(c)) return fail(APK_DECLINE_INVALID_STATE, "token_records runs on an unsharded context");
     APK_TRY(ensure_graph(c, r));
     Plan *P = c->plan.get();
+    CUDA_TRY(cudaMemcpyAsync(P->pos.p, &r->pos, sizeof(uint32_t), cudaMemcpyHostToDevice, c->stream));
     const uint32_t m = r->m, H = P->hidden, nblk = H / 32;
     const size_t x_bytes = (size_t)APK_MAX_M * H * 4;
     const size_t slab = (x_bytes + act_bytes(APK_TY_Q4_K, MAX_M_EFF, H) + 255) & ~(size_t)255;
@@ -730,6 +838,145 @@ int apk_debug_token_records(apk_ctx *c, const apk_token_req *r, uint32_t max_rec
         meta[4 * i] = mt.m_eff; meta[4 * i + 1] = mt.two_level; meta[4 * i + 2] = mt.launch; meta[4 * i + 3] = mt.ke;
     }
     return APK_OK;
+}
+
+int apk_decode_greedy(apk_ctx *c, const apk_token_req *r, uint32_t n_tokens, const float *rope, uint32_t *tokens_out) {
+    if (!c || !r || !tokens_out || (r->rot_dim && !rope)) return fail(APK_ERR_INVALID_ARG, "greedy: null argument");
+    if (n_tokens == 0) return APK_OK;
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    apk_token_req q = *r;  // the chain is argmax decode by token id, whatever the caller left in those fields
+    q.argmax = 1;
+    q.use_token = 1;
+    q.rope = rope;
+    APK_TRY(validate_token_req(c, &q));
+    if (q.m != 1 || !q.embd.w) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "the greedy chain takes one row and an embedding table");
+    if (q.token_id >= q.embd.n_out) return decline_decode(c, APK_ERR_INVALID_ARG, "token %u out of vocabulary %u", q.token_id, q.embd.n_out);
+    if (n_tokens > 65536) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "at most 65536 chained tokens per call");
+    const uint64_t t0 = now_ns();
+    APK_TRY(ensure_graph(c, &q));
+    Plan *P = c->plan.get();
+    const int row = (int)(q.rot_dim / 2) * 2;
+    // chain state: token | step | hist[n] | rope rows [n][row]
+    const size_t hist_off = 64, rope_off = (hist_off + (size_t)n_tokens * 4 + 255) & ~(size_t)255;
+    const size_t need = rope_off + (size_t)n_tokens * std::max(row, 1) * 4;
+    if (need > P->chain.cap) {
+        CUDA_TRY(cudaStreamSynchronize(c->stream));
+        APK_TRY(P->chain.ensure(need));
+    }
+    uint8_t *base = P->chain.as<uint8_t>();
+    uint32_t *d_token = reinterpret_cast<uint32_t *>(base), *d_step = d_token + 1;
+    uint32_t *d_hist = reinterpret_cast<uint32_t *>(base + hist_off);
+    float *d_rope = reinterpret_cast<float *>(base + rope_off);
+    const uint32_t init[2] = {q.token_id, 0u};
+    CUDA_TRY(cudaMemcpyAsync(d_token, init, sizeof init, cudaMemcpyHostToDevice, c->stream));
+    if (q.attn_core == APK_ATTN_CAUSAL && (uint64_t)q.pos + n_tokens > q.kv->capacity)
+        return decline_decode(c, APK_ERR_INVALID_ARG, "the chain runs past the KV cache's capacity");
+    CUDA_TRY(cudaMemcpyAsync(P->pos.p, &q.pos, sizeof(uint32_t), cudaMemcpyHostToDevice, c->stream));
+    if (row) {
+        CUDA_TRY(cudaMemcpyAsync(d_rope, rope, (size_t)n_tokens * row * 4, cudaMemcpyHostToDevice, c->stream));
+        CUDA_TRY(cudaMemcpyAsync(P->rope.p, d_rope, (size_t)row * 4, cudaMemcpyDeviceToDevice, c->stream));
+    }
+    ChainParams cp{};
+    cp.amax = P->amax.as<uint32_t>();
+    cp.token = d_token;
+    cp.hist = d_hist;
+    cp.step = d_step;
+    cp.rope_tab = d_rope;
+    cp.rope = P->rope.as<float>();
+    cp.row = row;
+    cp.n_steps = (int)n_tokens;
+    cp.pos = P->pos.as<uint32_t>();
+    for (uint32_t i = 0; i < n_tokens; ++i) {
+        APK_TRY(launch_embed(c, P, d_token, 0u, P->xin.as<float>()));
+        CUDA_TRY(cudaGraphLaunch(P->exec[1][1], c->stream));
+        chain_advance_kernel<<<1, 128, 0, c->stream>>>(cp);
+        CUDA_TRY(cudaGetLastError());
+        c->st.launches += P->launches[1][1] + 1;
+    }
+    CUDA_TRY(cudaMemcpyAsync(tokens_out, d_hist, (size_t)n_tokens * 4, cudaMemcpyDeviceToHost, c->stream));
+    c->st.encode_ns += now_ns() - t0;
+    c->st.calls++;
+    c->st.decode_attempts += n_tokens - 1;
+    APK_TRY(finish(c));
+    c->st.decode_successes += n_tokens;
+    return APK_OK;
+}
+
+int apk_kv_create(apk_ctx *c, uint32_t n_layers, uint32_t kv_dim, uint32_t capacity, apk_kv **out) {
+    if (!c || !out || n_layers == 0 || capacity == 0) return fail(APK_ERR_INVALID_ARG, "kv_create: null or empty");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    if (kv_dim == 0 || kv_dim % (TILE_ROWS * (uint32_t)c->world))
+        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "kv_dim %u is not whole 128-wide heads per rank", kv_dim);
+    auto kv = std::make_unique<apk_kv>();
+    kv->n_layers = n_layers;
+    kv->kv_dim = kv_dim / (uint32_t)c->world;
+    kv->capacity = capacity;
+    const size_t bytes = 2 * kv->layer_stride() * n_layers * sizeof(__half);
+    CUDA_TRY(cudaMalloc((void **)&kv->base, bytes));
+    CUDA_TRY(cudaMemsetAsync(kv->base, 0, bytes, c->stream));
+    CUDA_TRY(cudaStreamSynchronize(c->stream));
+    *out = kv.release();
+    return APK_OK;
+}
+
+void apk_kv_destroy(apk_ctx *c, apk_kv *kv) {
+    if (!c || !kv) return;
+    std::lock_guard<std::mutex> g(c->mu);
+    cudaSetDevice(c->device);
+    cudaStreamSynchronize(c->stream);
+    if (c->plan && c->plan->kv == kv) c->plan.reset();  // its graphs point into the cache
+    if (kv->base) cudaFree(kv->base);
+    delete kv;
+}
+
+static int kv_rows(apk_ctx *c, const apk_kv *kv, uint32_t layer, uint32_t pos0, uint32_t n_pos, uint16_t *k, uint16_t *v, bool write) {
+    if (!c || !kv || !k || !v) return fail(APK_ERR_INVALID_ARG, "kv rows: null argument");
+    if (layer >= kv->n_layers || (uint64_t)pos0 + n_pos > kv->capacity) return fail(APK_ERR_INVALID_ARG, "kv rows: layer or positions out of range");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    const size_t bytes = (size_t)n_pos * kv->kv_dim * sizeof(__half);
+    __half *kd = kv->k(layer) + (size_t)pos0 * kv->kv_dim, *vd = kv->v(layer) + (size_t)pos0 * kv->kv_dim;
+    if (write) {
+        CUDA_TRY(cudaMemcpyAsync(kd, k, bytes, cudaMemcpyHostToDevice, c->stream));
+        CUDA_TRY(cudaMemcpyAsync(vd, v, bytes, cudaMemcpyHostToDevice, c->stream));
+    } else {
+        CUDA_TRY(cudaMemcpyAsync(k, kd, bytes, cudaMemcpyDeviceToHost, c->stream));
+        CUDA_TRY(cudaMemcpyAsync(v, vd, bytes, cudaMemcpyDeviceToHost, c->stream));
+    }
+    CUDA_TRY(cudaStreamSynchronize(c->stream));
+    return APK_OK;
+}
+
+int apk_kv_read(apk_ctx *c, const apk_kv *kv, uint32_t layer, uint32_t pos0, uint32_t n_pos, uint16_t *k, uint16_t *v) {
+    return kv_rows(c, kv, layer, pos0, n_pos, k, v, false);
+}
+
+int apk_kv_write(apk_ctx *c, apk_kv *kv, uint32_t layer, uint32_t pos0, uint32_t n_pos, const uint16_t *k, const uint16_t *v) {
+    return kv_rows(c, kv, layer, pos0, n_pos, const_cast<uint16_t *>(k), const_cast<uint16_t *>(v), true);
+}
+
+int apk_attend(apk_ctx *c, const apk_kv *kv, uint32_t layer, const float *q, uint32_t m, uint32_t n_heads, uint32_t pos,
+               float scale, float *out) {
+    if (!c || !kv || !q || !out) return fail(APK_ERR_INVALID_ARG, "attend: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    APK_TRY(check_m(m));
+    if (c->world != 1) return fail(APK_DECLINE_INVALID_STATE, "attend: stand-alone call runs on an unsharded context");
+    const uint32_t n_kv = kv->kv_dim / TILE_ROWS;
+    if (layer >= kv->n_layers || n_heads == 0 || n_heads % n_kv || (uint64_t)pos + m > kv->capacity)
+        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "attend: layer %u, %u heads over %u kv heads, positions to %u", layer, n_heads, n_kv, pos + m - 1);
+    const size_t qn = (size_t)m * n_heads * TILE_ROWS;
+    APK_TRY(c->x_dev.ensure(qn * 4));
+    APK_TRY(c->y_dev.ensure(qn * 4));
+    APK_TRY(c->misc.ensure((size_t)m * n_heads * attn_splits(kv->capacity) * ATT_PART * 4));
+    CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, q, qn * 4, cudaMemcpyHostToDevice, c->stream));
+    APK_TRY(launch_attention(c, kv, layer, c->x_dev.as<float>(), (int)(n_heads * TILE_ROWS), m, n_heads, nullptr, pos, scale,
+                             c->misc.as<float>(), c->y_dev.as<float>(), (int)(n_heads * TILE_ROWS), nullptr, 0, 0));
+    CUDA_TRY(cudaMemcpyAsync(out, c->y_dev.p, qn * 4, cudaMemcpyDeviceToHost, c->stream));
+    c->st.calls++;
+    return finish(c);
 }
 
 }  // extern "C"

@@ -81,29 +81,29 @@ enum Epilogue : int {
 // One-shot exchange of row-parallel partial sums between the ranks of a
 // tensor-parallel group over peer-mapped memory (plain stores across NVLink; no
 // multicast).  Every rank owns one buffer, laid out
-//   slots [2 parity][XCH_MAX_RANKS][XCH_ROW_FLOATS] f32 | flags[XCH_MAX_RANKS][XCH_MAX_TILES] u32 | tok u32
+//   slots [2 parity][XCH_MAX_RANKS][XCH_ROW_FLOATS] 64-bit words | tok u32
 // Exchanges are numbered e = 1, 2, ... for the life of the group (every rank runs the
 // same sequence).  The CTA of rank s that closes a 128-row tile of the row-parallel matvec
-// stores the tile's partial rows into slot (e & 1, s) of EVERY rank's buffer and then sets
-// flags[s][tile] = e there (release, system scope).  The kernel that consumes the sum
-// waits (bounded) until all world * tiles flags of its own buffer have reached e and adds
-// the slots in rank order 0..world-1: deterministic, one NVLink hop, no extra launch.
-// Two parities suffice: a rank can run at most one exchange ahead of the slowest one,
-// because passing exchange e + 1 needs every rank's flags for e + 1.
+// stores the tile's partial sums into slot (e & 1, s) of EVERY rank's buffer, each value as
+// one 64-bit word {e, f32}: a naturally aligned 64-bit access is single-copy atomic, so a
+// reader that sees tag e has the value -- no fence, no flag, no second round trip, and the
+// storing CTA leaves at once.  The kernel that consumes the sum polls the words of its own
+// buffer (bounded) until all world slots carry tag e and adds them in rank order 0..world-1:
+// deterministic, one NVLink hop, no extra launch.  Old words carry older tags, so nothing is
+// ever cleared.  Two parities suffice: a rank can run at most one exchange ahead of the
+// slowest one, because passing exchange e + 1 needs every rank's words for e + 1.
 // `tok` counts decoded tokens; e = (tok - 1) * exchanges per token + index in the token + 1.
 constexpr int XCH_MAX_RANKS = 8;
-constexpr int XCH_ROW_FLOATS = 8 * 16384;  // m * hidden floats per slot
-constexpr int XCH_MAX_TILES = 128;         // hidden <= 16384
-constexpr size_t XCH_SLOTS_BYTES = (size_t)2 * XCH_MAX_RANKS * XCH_ROW_FLOATS * sizeof(float);
-constexpr size_t XCH_FLAGS_BYTES = (size_t)XCH_MAX_RANKS * XCH_MAX_TILES * sizeof(uint32_t);
-constexpr size_t XCH_BYTES = XCH_SLOTS_BYTES + XCH_FLAGS_BYTES + 256;
+constexpr int XCH_ROW_FLOATS = 8 * 16384;  // m * hidden values per slot
+constexpr size_t XCH_SLOTS_BYTES = (size_t)2 * XCH_MAX_RANKS * XCH_ROW_FLOATS * sizeof(unsigned long long);
+constexpr size_t XCH_BYTES = XCH_SLOTS_BYTES + 256;
 
 struct XchPeers {
     float *slots[XCH_MAX_RANKS];  // peer-mapped base of each rank's buffer (own included)
     int rank, world;
 };
-__host__ __device__ inline uint32_t *xch_flags(float *base) { return reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(base) + XCH_SLOTS_BYTES); }
-__host__ __device__ inline uint32_t *xch_tok(float *base) { return xch_flags(base) + XCH_MAX_RANKS * XCH_MAX_TILES; }
+__host__ __device__ inline unsigned long long *xch_words(float *base) { return reinterpret_cast<unsigned long long *>(base); }
+__host__ __device__ inline uint32_t *xch_tok(float *base) { return reinterpret_cast<uint32_t *>(reinterpret_cast<uint8_t *>(base) + XCH_SLOTS_BYTES); }
 // Where a kernel stands in the exchange sequence of its token.
 struct XchSeq {
     int index = -1;     // exchange index within the token (0-based); -1 = this launch takes no part
@@ -185,12 +185,17 @@ struct MvParams {
     const float *rope; int half;       // [m][half][2] (sin, cos)
     ActLayout q_next;                  // optional: roped Q heads packed as the next matvec's activations
     int q_next_two_level, q_next_need_sum;
+    __half *kv_k, *kv_v;               // optional: this layer's f16 cache slabs [capacity][kv_dim]; K and V rows go there too
+    int kv_dim;                        // (this rank's) kv heads * 128
+    const uint32_t *pos_dev; uint32_t pos;  // cache position of row 0: on the device (greedy chain) or with the launch
     // Tensor-parallel exchange (see XchPeers).  xout: EPI_PEERS, this launch feeds exchange
     // xout.index.  xin: PRO_QUANT, the input row is prep.x + the rank-ordered sum of exchange
     // xin.index (CTA 0 stores it to prep.xout).  tok_inc: CTA 0 advances the token counter
     // (set on the first launch of a token, which takes part in no exchange).
     XchPeers xch; int xch_row;         // floats per token row in a slot (= hidden)
     XchSeq xin, xout;
+    int xin_late;   // xin: start on the tagged words alone, make up for the dependency wait at the end (token order only:
+                    // the launch in front must be a row-parallel matvec that did wait for its own predecessor)
     int tok_inc;
     // EPI_SWIGLU
     float *act_f32; int ld_act;        // optional f32 swiglu rows [m][ffn]
@@ -493,45 +498,42 @@ __global__ void __launch_bounds__(256) prep_acts_kernel(PrepParams p, int pdl) {
 
 // ------------------------------------------------- tensor-parallel exchange
 
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 // Number of the exchange a launch takes part in (see XchPeers).
 __device__ __forceinline__ uint32_t xch_number(float *mine, const XchSeq &s) {
     return (__ldcg(xch_tok(mine)) - 1u) * (uint32_t)s.per_token + (uint32_t)s.index + 1u;
 }
-// Thread t of nthreads waits (bounded) until its share of this rank's world * n_tiles flags
-// has reached exchange e.  false = the budget ran out.  The caller follows with a barrier of
-// the same threads before any of them reads the slots.
-__device__ __forceinline__ bool xch_wait_flags(float *mine, int world, int n_tiles, uint32_t e, int t, int nthreads,
-                                               long long limit) {
-    const long long t0 = clock64();
-    for (int i = t; i < world * n_tiles; i += nthreads) {
-        const uint32_t *f = xch_flags(mine) + (i / n_tiles) * XCH_MAX_TILES + i % n_tiles;
-        while ((int32_t)(ld_acquire_sys(f) - e) < 0) {
-            if (clock64() - t0 > limit) return false;
-            __nanosleep(20);
-        }
-    }
-    return true;
+__device__ __forceinline__ void st_relaxed_sys_b64(unsigned long long *p, unsigned long long v) {
+    asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-// x[i..i+3] + (slot 0 + slot 1 + ...)[i..i+3] in rank order: the one summation order of an exchange.
-__device__ __forceinline__ float4 xch_sum4(const float *x, const float *mine, uint32_t e, int world, size_t off) {
-    float4 acc = __ldcg(reinterpret_cast<const float4 *>(x));
+__device__ __forceinline__ void ld_relaxed_sys_v2b64(const unsigned long long *p, unsigned long long &a, unsigned long long &b) {
+    asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
+}
+// x[i..i+3] + (slot 0 + slot 1 + ...)[i..i+3] in rank order: the one summation order of an
+// exchange.  Polls (bounded) until the four words of every rank carry tag e; *ok = false when
+// the budget ran out (the sum then holds whatever was there).
+__device__ __forceinline__ float4 xch_gather4(const float *x, float *mine, uint32_t e, int world, size_t off, long long limit,
+                                              bool *ok) {
+    const float4 acc0 = __ldcg(reinterpret_cast<const float4 *>(x));
+    const unsigned long long *s0 = xch_words(mine) + (size_t)(e & 1u) * XCH_MAX_RANKS * XCH_ROW_FLOATS + off;
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float *s0 = mine + (size_t)(e & 1u) * XCH_MAX_RANKS * XCH_ROW_FLOATS + off;
+    const long long t0 = clock64();
     for (int r = 0; r < world; ++r) {
-        const float4 v = __ldcg(reinterpret_cast<const float4 *>(s0 + (size_t)r * XCH_ROW_FLOATS));
-        sum.x = __fadd_rn(sum.x, v.x); sum.y = __fadd_rn(sum.y, v.y);
-        sum.z = __fadd_rn(sum.z, v.z); sum.w = __fadd_rn(sum.w, v.w);
+        unsigned long long w0, w1, w2, w3;
+        for (;;) {
+            ld_relaxed_sys_v2b64(s0 + (size_t)r * XCH_ROW_FLOATS, w0, w1);
+            ld_relaxed_sys_v2b64(s0 + (size_t)r * XCH_ROW_FLOATS + 2, w2, w3);
+            if ((uint32_t)(w0 >> 32) == e && (uint32_t)(w1 >> 32) == e && (uint32_t)(w2 >> 32) == e && (uint32_t)(w3 >> 32) == e) break;
+            if (clock64() - t0 > limit) {
+                *ok = false;
+                break;
+            }
+        }
+        sum.x = __fadd_rn(sum.x, __uint_as_float((uint32_t)w0)); sum.y = __fadd_rn(sum.y, __uint_as_float((uint32_t)w1));
+        sum.z = __fadd_rn(sum.z, __uint_as_float((uint32_t)w2)); sum.w = __fadd_rn(sum.w, __uint_as_float((uint32_t)w3));
     }
-    acc.x = __fadd_rn(acc.x, sum.x); acc.y = __fadd_rn(acc.y, sum.y);
-    acc.z = __fadd_rn(acc.z, sum.z); acc.w = __fadd_rn(acc.w, sum.w);
+    float4 acc;
+    acc.x = __fadd_rn(acc0.x, sum.x); acc.y = __fadd_rn(acc0.y, sum.y);
+    acc.z = __fadd_rn(acc0.z, sum.z); acc.w = __fadd_rn(acc0.w, sum.w);
     return acc;
 }
 
@@ -548,8 +550,8 @@ struct XchReduceParams {
 
 // Stand-alone form of the collecting side (batches of m > 1 rows, whose activations are
 // quantised by a separate pass): grid = ceil(m*n / 1024), 256 threads, four floats per
-// thread.  Waits (bounded) for every rank's tile flags of the exchange, then adds the slots
-// in rank order onto the residual rows.
+// thread.  Waits (bounded) for every rank's tagged words of the exchange and adds them in
+// rank order onto the residual rows.
 __global__ void __launch_bounds__(256) xch_reduce_kernel(XchReduceParams p) {
     if (p.pdl) {
         pdl_launch_dependents();
@@ -557,20 +559,13 @@ __global__ void __launch_bounds__(256) xch_reduce_kernel(XchReduceParams p) {
     }
     float *mine = p.xch.slots[p.xch.rank];
     const uint32_t e = xch_number(mine, p.seq);
-    __shared__ int s_ok;
-    if (threadIdx.x == 0) s_ok = 1;
-    __syncthreads();
-    if (!xch_wait_flags(mine, p.xch.world, (p.n + TILE_ROWS - 1) / TILE_ROWS, e, threadIdx.x, blockDim.x, p.wait_limit)) {
-        // a peer never delivered: record it and finish normally
-        s_ok = 0;
-        atomicExch(p.err, ERRW_PEER_TIMEOUT);
-    }
-    __syncthreads();
     const size_t total = (size_t)p.m * p.n;
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
-    if (i < total && s_ok) {
+    if (i < total) {
         const int m = (int)(i / p.n), col = (int)(i % p.n);
-        const float4 acc = xch_sum4(p.x + (size_t)m * p.ldx + col, mine, e, p.xch.world, (size_t)m * p.n + col);
+        bool ok = true;
+        const float4 acc = xch_gather4(p.x + (size_t)m * p.ldx + col, mine, e, p.xch.world, (size_t)m * p.n + col, p.wait_limit, &ok);
+        if (!ok) atomicCAS(p.err, 0, ERRW_PEER_TIMEOUT);  // a peer never delivered: record it and finish normally
         *reinterpret_cast<float4 *>(p.xout + (size_t)m * p.ldxout + col) = acc;
     }
 }
@@ -680,6 +675,146 @@ __global__ void repack_q4_k_kernel(RepackParams p) {
     }
 }
 
+// ------------------------------------------------------ decode attention over the f16 KV cache
+//
+// What sits between the Q|K|V matvec and the output projection of a decoder layer
+// (crates/allpaka-model/src/model/attention.rs:337-399): per kv head, its GQA group of q heads
+// attends over cache positions 0..=pos with an online softmax; K and V live in the cache as f16
+// (model/kv.rs), scores and sums are f32.  HBM-bound on the cache bytes and far smaller than the
+// weight stream next to it (2 * positions * kv_dim * 2 B per layer), so plain SIMT: the positions
+// are split over CTAs, a warp walks its share one position at a time (lane = four of the 128
+// head dimensions), the splits are merged by a second small kernel that also packs the result as
+// the Q8 (or two-level) blocks the output projection consumes.
+constexpr int ATT_WARPS = 8;
+constexpr int ATT_MAX_GROUP = 8;       // q heads per kv head handled by one CTA pass
+constexpr int ATT_PART = TILE_ROWS + 2;  // floats per partial: acc[128], running max, denominator
+
+struct AttnParams {
+    const float *q; int ldq;           // [m][ldq] roped q heads (head h at column h * 128)
+    const __half *kc, *vc;             // this layer's cache slabs, [capacity][kv_dim]
+    int kv_dim, n_kv_heads, group;     // local (per rank) kv heads, q heads per kv head
+    const uint32_t *pos_dev; uint32_t pos;  // position of row 0: on the device (greedy chain) or with the launch
+    int m, n_splits;
+    float scale;
+    float *part;                       // [m][q heads][n_splits][ATT_PART]
+    // second kernel
+    float *out; int ldo;               // optional f32 rows [m][q heads * 128]
+    ActLayout next;                    // the output projection's activation records
+    int next_two_level, next_need_sum;
+};
+
+// grid (kv heads, splits, m), ATT_WARPS warps.  head_dim is 128.
+__global__ void __launch_bounds__(ATT_WARPS * 32) attn_split_kernel(AttnParams p, int pdl) {
+    if (pdl) {
+        pdl_launch_dependents();
+        pdl_wait();
+    }
+    __shared__ float sm[ATT_WARPS][ATT_MAX_GROUP][ATT_PART];
+    const int kvh = blockIdx.x, split = blockIdx.y, row = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t pos = (p.pos_dev ? *p.pos_dev : p.pos) + (uint32_t)row;  // this row sees positions 0..=pos
+    const uint32_t n_pos = pos + 1u;
+    const uint32_t per = (n_pos + (uint32_t)p.n_splits - 1u) / (uint32_t)p.n_splits;
+    const uint32_t t0 = (uint32_t)split * per, t1 = min(n_pos, t0 + per);
+    for (int g0 = 0; g0 < p.group; g0 += ATT_MAX_GROUP) {
+        const int G = min(ATT_MAX_GROUP, p.group - g0);
+        float4 q[ATT_MAX_GROUP], acc[ATT_MAX_GROUP];
+        float mx[ATT_MAX_GROUP], dn[ATT_MAX_GROUP];
+#pragma unroll
+        for (int h = 0; h < ATT_MAX_GROUP; ++h) {
+            q[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (h < G) q[h] = *reinterpret_cast<const float4 *>(p.q + (size_t)row * p.ldq + (size_t)(kvh * p.group + g0 + h) * TILE_ROWS + 4 * lane);
+            acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
+            mx[h] = -INFINITY;
+            dn[h] = 0.0f;
+        }
+        for (uint32_t t = t0 + (uint32_t)warp; t < t1; t += ATT_WARPS) {
+            const uint2 kr = *reinterpret_cast<const uint2 *>(p.kc + (size_t)t * p.kv_dim + (size_t)kvh * TILE_ROWS + 4 * lane);
+            const uint2 vr = *reinterpret_cast<const uint2 *>(p.vc + (size_t)t * p.kv_dim + (size_t)kvh * TILE_ROWS + 4 * lane);
+            const float2 k01 = __half22float2(*reinterpret_cast<const __half2 *>(&kr.x));
+            const float2 k23 = __half22float2(*reinterpret_cast<const __half2 *>(&kr.y));
+            const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&vr.x));
+            const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&vr.y));
+#pragma unroll
+            for (int h = 0; h < ATT_MAX_GROUP; ++h) {
+                if (h < G) {
+                    float s = q[h].x * k01.x + q[h].y * k01.y + q[h].z * k23.x + q[h].w * k23.y;
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                    s *= p.scale;
+                    if (s > mx[h]) {
+                        if (dn[h] > 0.0f) {
+                            const float r = expf(mx[h] - s);
+                            acc[h].x *= r; acc[h].y *= r; acc[h].z *= r; acc[h].w *= r;
+                            dn[h] *= r;
+                        }
+                        mx[h] = s;
+                    }
+                    const float pr = expf(s - mx[h]);
+                    dn[h] += pr;
+                    acc[h].x += pr * v01.x; acc[h].y += pr * v01.y; acc[h].z += pr * v23.x; acc[h].w += pr * v23.y;
+                }
+            }
+        }
+        // merge the warps' running states, head by head
+        __syncthreads();
+#pragma unroll
+        for (int h = 0; h < ATT_MAX_GROUP; ++h)
+            if (h < G) {
+                *reinterpret_cast<float4 *>(&sm[warp][h][4 * lane]) = acc[h];
+                if (lane == 0) {
+                    sm[warp][h][TILE_ROWS] = mx[h];
+                    sm[warp][h][TILE_ROWS + 1] = dn[h];
+                }
+            }
+        __syncthreads();
+        for (int h = warp; h < G; h += ATT_WARPS) {
+            float M = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, sm[w][h][TILE_ROWS]);
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            float d = 0.0f;
+#pragma unroll
+            for (int w = 0; w < ATT_WARPS; ++w) {
+                const float mw = sm[w][h][TILE_ROWS];
+                const float r = mw == -INFINITY ? 0.0f : expf(mw - M);
+                const float4 aw = *reinterpret_cast<const float4 *>(&sm[w][h][4 * lane]);
+                a.x += r * aw.x; a.y += r * aw.y; a.z += r * aw.z; a.w += r * aw.w;
+                d += r * sm[w][h][TILE_ROWS + 1];
+            }
+            float *dst = p.part + (((size_t)row * (p.n_kv_heads * p.group) + (size_t)(kvh * p.group + g0 + h)) * p.n_splits + split) * ATT_PART;
+            *reinterpret_cast<float4 *>(dst + 4 * lane) = a;
+            if (lane == 0) {
+                dst[TILE_ROWS] = M;
+                dst[TILE_ROWS + 1] = d;
+            }
+        }
+    }
+}
+
+// grid (q heads, m), 128 threads: merge the splits of one head, normalise (attention.rs:391-398),
+// keep the f32 row and pack the head's four 32-element blocks for the output projection.
+__global__ void __launch_bounds__(TILE_ROWS) attn_combine_kernel(AttnParams p, int pdl) {
+    if (pdl) {
+        pdl_launch_dependents();
+        pdl_wait();
+    }
+    const int head = blockIdx.x, row = blockIdx.y, i = threadIdx.x;
+    const float *src = p.part + ((size_t)row * (p.n_kv_heads * p.group) + head) * p.n_splits * ATT_PART;
+    float M = -INFINITY;
+    for (int s = 0; s < p.n_splits; ++s) M = fmaxf(M, src[(size_t)s * ATT_PART + TILE_ROWS]);
+    float a = 0.0f, d = 0.0f;
+    for (int s = 0; s < p.n_splits; ++s) {
+        const float ms = src[(size_t)s * ATT_PART + TILE_ROWS];
+        const float r = ms == -INFINITY ? 0.0f : expf(ms - M);
+        a += r * src[(size_t)s * ATT_PART + i];
+        d += r * src[(size_t)s * ATT_PART + TILE_ROWS + 1];
+    }
+    const float o = a * (1.0f / fmaxf(d, 1.17549435e-38f));  // denom.max(f32::MIN_POSITIVE)
+    if (p.out) p.out[(size_t)row * p.ldo + (size_t)head * TILE_ROWS + i] = o;
+    if (p.next.base) quantize_store(p.next, p.next_two_level, p.next_need_sum, row, head * 4 + (i >> 5), i & 31, o);
+}
+
 // ------------------------------------------------------ token ends (embedding row, greedy chain)
 //
 // The embedding row of a token, dequantised straight out of the tiled stream (the LM head of a
@@ -762,12 +897,14 @@ struct ChainParams {
     float *rope;           // the row the token graph reads
     int row;               // floats per row
     int n_steps;
+    uint32_t *pos;         // cache position of the next token (advanced here)
 };
 __global__ void __launch_bounds__(128) chain_advance_kernel(ChainParams p) {
     const uint32_t s = *p.step;
     if (threadIdx.x == 0) {
         p.hist[s] = *p.amax;
         *p.token = *p.amax;
+        if (p.pos) *p.pos += 1u;
     }
     if (s + 1 < (uint32_t)p.n_steps)
         for (int i = threadIdx.x; i < p.row; i += blockDim.x) p.rope[i] = p.rope_tab[(size_t)(s + 1) * p.row + i];
@@ -934,23 +1071,22 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
     float v[PRO_CH];
     if (p.xin.index >= 0) {
         // Tensor parallel: the row is the residual plus the partial sums every rank stored
-        // into this rank's exchange buffer.  Wait (bounded) for their tile flags, then add
+        // into this rank's exchange buffer as tagged words.  Poll them (bounded) and add
         // the slots in rank order; CTA 0 keeps the new residual row.
         float *mine = p.xch.slots[p.xch.rank];
         const uint32_t e = xch_number(mine, p.xin);
-        if (!xch_wait_flags(mine, p.xch.world, (n + TILE_ROWS - 1) / TILE_ROWS, e, tid, N_CONSUMERS, p.wait_limit))
-            atomicExch(p.err, ERRW_PEER_TIMEOUT);  // goes on with what is there; the host reports the error
-        consumer_bar();
+        bool ok = true;
 #pragma unroll
         for (int j = 0; j < PRO_J; ++j) {
             const int el = 4 * tid + PRO_CHUNK * j;
             float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
             if (el < n) {
-                x = xch_sum4(pp.x + el, mine, e, p.xch.world, (size_t)el);
+                x = xch_gather4(pp.x + el, mine, e, p.xch.world, (size_t)el, p.wait_limit, &ok);
                 if (pp.xout && blockIdx.x == 0) *reinterpret_cast<float4 *>(pp.xout + el) = x;
             }
             v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
         }
+        if (!ok) atomicCAS(p.err, 0, ERRW_PEER_TIMEOUT | (p.launch_id << 8));  // goes on with what is there; the host reports the error
     } else {
 #pragma unroll
         for (int j = 0; j < PRO_J; ++j) {
@@ -1398,7 +1534,12 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
 
     float gam[PRO_CH];
     if (p.pro == PRO_QUANT) prologue_gamma(p, tid, gam);  // independent of the previous kernel
-    if (p.pdl) pdl_wait();
+    // A launch whose row comes out of the exchange needs nothing else of the previous kernel:
+    // the tagged words say when the row is complete, on this rank and on the others, so it does
+    // not wait for that grid to drain (its peer stores take microseconds to be acknowledged).
+    // The wait is made up for after the last unit, when it costs nothing.
+    const bool late_dep = p.pro == PRO_QUANT && p.xin.index >= 0 && p.xin_late;
+    if (p.pdl && !late_dep) pdl_wait();
     if (tl && tid == 0) tl[2] = globaltimer_ns();  // dependency satisfied
     if (tid == 0 && acts_copy) {
         // the activations, as soon as they exist
@@ -1866,6 +2007,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         ++n_handoff;
         t_last = t_cur;
     }
+    if (p.pdl && late_dep) pdl_wait();  // keeps the chain of completions whole for the launches behind this one
     // Nothing left to stream: help the finishers close this CTA's last tile.
     {
         const Crew cw{N_FINISHERS + tid, N_CREW_ALL, 3};
@@ -1924,19 +2066,13 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw,
             const int m = i / TILE_ROWS, r = i % TILE_ROWS;
             const int row = row0 + r;
             if (row >= p.n_out) continue;
-            const float v = val(m, r);
+            const unsigned long long w = ((unsigned long long)e << 32) | (unsigned long long)__float_as_uint(val(m, r));
             for (int k = 0; k < p.xch.world; ++k) {
                 const int dst = (p.xch.rank + k) % p.xch.world;  // start with the local copy, spread the links
-                p.xch.slots[dst][slot + (size_t)m * p.xch_row + row] = v;
+                st_relaxed_sys_b64(xch_words(p.xch.slots[dst]) + slot + (size_t)m * p.xch_row + row, w);
             }
         }
-        // Publish the tile: the crew's stores are ordered before the barrier, the flag stores
-        // after it are releases at system scope (cumulative over what the barrier ordered).
-        cw.sync();
-        if (tid < p.xch.world) {
-            asm volatile("fence.acq_rel.sys;" ::: "memory");
-            st_release_sys(xch_flags(p.xch.slots[tid]) + p.xch.rank * XCH_MAX_TILES + tile, e);
-        }
+        // (nothing to publish separately: every word carries the exchange number next to its value)
         return;
     }
     if (p.epi == EPI_QKV_ROPE) {
@@ -1990,6 +2126,14 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw,
                 }
                 const int row = row0 + c;
                 if (row < p.n_out) p.y[(size_t)m * p.ldy + row] = o;
+                if (p.kv_k && tile >= p.n_q_tiles) {
+                    // K (roped) and V of this position into the f16 cache, round to nearest even
+                    // (KvCache::store_at, crates/allpaka-model/src/kv.rs:682-697)
+                    const uint32_t pos = (p.pos_dev ? *p.pos_dev : p.pos) + (uint32_t)m;
+                    const bool is_k = tile < p.n_q_tiles + p.n_k_tiles;
+                    const int col = (tile - p.n_q_tiles - (is_k ? 0 : p.n_k_tiles)) * TILE_ROWS + c;
+                    (is_k ? p.kv_k : p.kv_v)[(size_t)pos * p.kv_dim + col] = __float2half_rn(o);
+                }
                 v[j] = o;
             }
             if (p.q_next.base && tile < p.n_q_tiles) {

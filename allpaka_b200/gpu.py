@@ -28,6 +28,7 @@ Q4_K = 12
 
 ACT_Q8, ACT_F32, ACT_AUTO = 0, 1, 2
 ATTN_IDENTITY = 1
+ATTN_CAUSAL = 2
 MAX_M = 8
 
 _DECLINE_NAMES = {
@@ -88,7 +89,9 @@ class _TokenReq(C.Structure):
                 ("output", _Mat), ("x", C.c_void_p), ("m", C.c_uint32), ("rope", C.c_void_p),
                 ("rot_dim", C.c_uint32), ("eps", C.c_float), ("hidden", C.c_uint32),
                 ("head_dim", C.c_uint32), ("n_heads", C.c_uint32), ("n_kv_heads", C.c_uint32),
-                ("attn_core", C.c_uint32), ("argmax", C.c_int)]
+                ("attn_core", C.c_uint32), ("argmax", C.c_int),
+                ("embd", _Mat), ("token_id", C.c_uint32), ("use_token", C.c_int),
+                ("kv", C.c_void_p), ("pos", C.c_uint32), ("scale", C.c_float)]
 
 
 class _TokenOut(C.Structure):
@@ -115,7 +118,8 @@ EXPORTS = (
     "apk_debug_matvec_timeline", "apk_shard_plan", "apk_matvec_noalloc",
     "apk_dist_p2p_export", "apk_dist_p2p_open", "apk_debug_token_timeline",
     "apk_debug_token_records", "apk_debug_set_wait_limit", "apk_debug_xch_timeout",
-    "apk_bench_ring", "apk_dist_set_exchange",
+    "apk_bench_ring", "apk_dist_set_exchange", "apk_decode_greedy",
+    "apk_kv_create", "apk_kv_destroy", "apk_kv_read", "apk_kv_write", "apk_attend",
 )
 
 _lib = None
@@ -144,6 +148,14 @@ def load_library() -> C.CDLL:
     l.apk_attn_in.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     l.apk_decode_token.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p]
     l.apk_decode_replay.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(C.c_float)]
+    l.apk_decode_greedy.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_void_p]
+    l.apk_kv_create.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_void_p)]
+    l.apk_kv_destroy.argtypes = [C.c_void_p, C.c_void_p]
+    l.apk_kv_destroy.restype = None
+    l.apk_kv_read.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
+    l.apk_kv_write.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
+    l.apk_attend.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float,
+                             C.c_void_p]
     l.apk_debug_block_dots.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
                                        C.c_void_p, C.c_uint32, C.c_void_p]
     l.apk_debug_q8_acts.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_float,
@@ -257,6 +269,45 @@ class TokenReq:
     n_kv_heads: int
     argmax: bool = False
     attn_core: int = ATTN_IDENTITY
+    kv: Optional["KvCache"] = None    # attn_core = ATTN_CAUSAL: the session's f16 KV cache (TokenReq.cache)
+    pos: int = 0                      # cache position of row 0 (TokenReq.pos)
+    scale: float = 0.0                # 1/sqrt(head_dim) (TokenReq.scale)
+    embd: Optional[tuple] = None      # (ty, table bytes, vocab rows): TokenReq.embd
+    token_id: Optional[int] = None    # with embd and m == 1: the input row is this token's embedding row
+
+
+class KvCache:
+    """The f16 KV cache of a session on the device (``KvCache``, crates/allpaka-model/src/kv.rs): per
+    layer a K and a V slab of ``[capacity, kv_dim]`` halves.  Rows travel as uint16 (f16 bits)."""
+
+    def __init__(self, gpu: "Gpu", n_layers: int, kv_dim: int, capacity: int):
+        self._g = gpu
+        h = C.c_void_p()
+        rc = gpu._l.apk_kv_create(gpu._h, n_layers, kv_dim, capacity, C.byref(h))
+        if rc != 0:
+            raise GpuError(rc, gpu._err())
+        self._h = h
+        self.n_layers, self.kv_dim, self.capacity = n_layers, kv_dim, capacity
+
+    def read(self, layer: int, pos0: int, n_pos: int):
+        k = np.empty((n_pos, self.kv_dim), np.uint16)
+        v = np.empty((n_pos, self.kv_dim), np.uint16)
+        rc = self._g._l.apk_kv_read(self._g._h, self._h, layer, pos0, n_pos, k.ctypes.data, v.ctypes.data)
+        if rc != 0:
+            raise GpuError(rc, self._g._err())
+        return k, v
+
+    def write(self, layer: int, pos0: int, k, v) -> None:
+        k = np.ascontiguousarray(k, dtype=np.uint16).reshape(-1, self.kv_dim)
+        v = np.ascontiguousarray(v, dtype=np.uint16).reshape(-1, self.kv_dim)
+        rc = self._g._l.apk_kv_write(self._g._h, self._h, layer, pos0, k.shape[0], k.ctypes.data, v.ctypes.data)
+        if rc != 0:
+            raise GpuError(rc, self._g._err())
+
+    def close(self):
+        if self._h and self._g._h:
+            self._g._l.apk_kv_destroy(self._g._h, self._h)
+        self._h = None
 
 
 class Gpu:
@@ -418,14 +469,18 @@ class Gpu:
                                      mat(L.down))
             on = _f32(req.output_norm)
             keep.append(on)
-            ent = (arr, keep, on, mat(req.output), req.layers)
+            ent = (arr, keep, on, mat(req.output), req.layers, mat)
             self._token_cache[key] = ent
-        arr, keep, on, out_mat, _ = ent
-        x = _f32(req.x).reshape(-1)
-        rope = _f32(req.rope).reshape(-1)
-        creq = _TokenReq(C.addressof(arr), len(req.layers), on.ctypes.data, out_mat, x.ctypes.data, req.m,
-                         rope.ctypes.data, req.rot_dim, req.eps, req.hidden, req.head_dim, req.n_heads,
-                         req.n_kv_heads, req.attn_core, 1 if req.argmax else 0)
+        arr, keep, on, out_mat, _, mat = ent
+        x = None if req.x is None else _f32(req.x).reshape(-1)
+        rope = None if req.rope is None else _f32(req.rope).reshape(-1)
+        embd = mat(req.embd) if req.embd is not None else _Mat(0, None, 0)
+        use_token = req.embd is not None and req.token_id is not None
+        creq = _TokenReq(C.addressof(arr), len(req.layers), on.ctypes.data, out_mat, _ptr(x), req.m,
+                         _ptr(rope), req.rot_dim, req.eps, req.hidden, req.head_dim, req.n_heads,
+                         req.n_kv_heads, req.attn_core, 1 if req.argmax else 0, embd,
+                         int(req.token_id) if req.token_id is not None else 0, 1 if use_token else 0,
+                         req.kv._h if req.kv is not None else None, int(req.pos), float(req.scale))
         return creq, (x, rope)
 
     def decode_token_checked(self, req: TokenReq, want_hidden: bool = False):
@@ -456,6 +511,29 @@ class Gpu:
             return self.decode_token_checked(req)
         except DecodeDecline:
             return None
+
+    def decode_greedy(self, req: TokenReq, n_tokens: int, rope_rows) -> Optional[np.ndarray]:
+        """``decode_token`` with argmax followed by ``decode_greedy_continue`` (gpu/cuda/decode.rs:93-227):
+        ``n_tokens`` greedy steps from ``req.token_id`` with one synchronisation; ``rope_rows`` holds one
+        (sin, cos) row per step.  Returns the winners; None when declined."""
+        creq, keep = self._token_req(req)
+        rope = _f32(rope_rows).reshape(n_tokens, -1)
+        out = np.empty(n_tokens, dtype=np.uint32)
+        rc = self._l.apk_decode_greedy(self._h, C.byref(creq), n_tokens, rope.ctypes.data, out.ctypes.data)
+        if rc > 0:
+            self.last_decline = (rc, self._err())
+            return None
+        if rc < 0:
+            raise GpuError(rc, self._err())
+        return out
+
+    def attend(self, kv: KvCache, layer: int, q, m: int, n_heads: int, pos: int, scale: float):
+        """``gpu::attend_batch`` (AttnReq, gpu/types.rs:34-52): m query rows over one layer of the cache,
+        row i over positions 0..=pos+i.  None when declined."""
+        q = _f32(q).reshape(-1)
+        out = np.empty((m, n_heads * 128), np.float32)
+        rc = self._l.apk_attend(self._h, kv._h, layer, q.ctypes.data, m, n_heads, pos, scale, out.ctypes.data)
+        return out if self._check(rc) else None
 
     def decode_replay(self, req: TokenReq, iters: int) -> float:
         """Replay the token graph `iters` times on device-resident input; returns GPU ms."""

@@ -158,7 +158,26 @@ typedef struct {
     apk_mat gate, up, down;            /* TokenFfn::Dense */
 } apk_token_layer; /* TokenLayer, gpu/types.rs:111-150 (dense attention layers) */
 
-#define APK_ATTN_IDENTITY 1u /* attention core = identity on the roped Q slice */
+#define APK_ATTN_IDENTITY 1u /* attention core = identity on the roped Q slice (the synthetic benchmark stack) */
+#define APK_ATTN_CAUSAL 2u   /* causal GQA attention over the f16 KV cache named by the request */
+
+/* The f16 KV cache of a session on the device: per layer a K slab and a V slab of
+ * [capacity][kv_dim] halves (KvCache, crates/allpaka-model/src/kv.rs:507-535, 682-697, 815-824).
+ * kv_dim = n_kv_heads * head_dim of the whole model; a rank of a tensor-parallel group keeps its
+ * own kv heads only.  apk_kv_read / apk_kv_write move rows pos0..pos0+n_pos of one layer between
+ * the host and this rank's slabs (this rank's kv heads, f16 bits), e.g. to hand over a prefill. */
+typedef struct apk_kv apk_kv;
+int apk_kv_create(apk_ctx *ctx, uint32_t n_layers, uint32_t kv_dim, uint32_t capacity, apk_kv **out);
+void apk_kv_destroy(apk_ctx *ctx, apk_kv *kv);
+int apk_kv_read(apk_ctx *ctx, const apk_kv *kv, uint32_t layer, uint32_t pos0, uint32_t n_pos, uint16_t *k, uint16_t *v);
+int apk_kv_write(apk_ctx *ctx, apk_kv *kv, uint32_t layer, uint32_t pos0, uint32_t n_pos, const uint16_t *k,
+                 const uint16_t *v);
+
+/* gpu::attend_batch (AttnReq, gpu/types.rs:34-52): m query rows of n_heads * 128 floats attend over
+ * one layer of the cache, row i over positions 0..=pos+i, GQA group = n_heads / kv heads, scores
+ * scaled by `scale`; out is m * n_heads * 128 (model/attention.rs:337-428).  Unsharded contexts. */
+int apk_attend(apk_ctx *ctx, const apk_kv *kv, uint32_t layer, const float *q, uint32_t m, uint32_t n_heads,
+               uint32_t pos, float scale, float *out);
 
 typedef struct {
     const apk_token_layer *layers;
@@ -171,8 +190,21 @@ typedef struct {
     uint32_t rot_dim;
     float eps;
     uint32_t hidden, head_dim, n_heads, n_kv_heads;
-    uint32_t attn_core;       /* APK_ATTN_IDENTITY; a KV-cache attention core is not part of this library */
+    uint32_t attn_core;       /* APK_ATTN_IDENTITY or APK_ATTN_CAUSAL */
     int argmax;               /* 1: return the greedy token per row instead of logits */
+    /* TokenReq.embd + token_id (gpu/types.rs:187-192): when embd.w != NULL, use_token != 0 and
+     * m == 1, the input row is the embedding row of token_id, dequantised on the GPU at the head
+     * of the submission, and x is ignored.  embd = (type, table bytes, vocab rows); its row length
+     * is `hidden`.  With tied embeddings pass the LM head's bytes: the resident copy is shared. */
+    apk_mat embd;
+    uint32_t token_id;
+    int use_token;
+    /* APK_ATTN_CAUSAL (TokenReq.cache / pos / scale, gpu/types.rs:207-226): the layer's K and V rows
+     * of the m tokens are stored at positions pos..pos+m-1 of kv (f16), row i attends over
+     * 0..=pos+i.  kv must have at least n_layers layers and pos + m <= its capacity. */
+    apk_kv *kv;
+    uint32_t pos;
+    float scale;              /* 1/sqrt(head_dim) */
 } apk_token_req; /* TokenReq, gpu/types.rs:183-238 */
 
 /* TokenOut, gpu/types.rs:228-238.  Logits(Vec<f32>): logits set, argmax == 0.
@@ -193,6 +225,16 @@ typedef struct {
  * norm weights are copied at that point, so the borrowed tensors must keep
  * their contents until the mapping is detached. */
 int apk_decode_token(apk_ctx *ctx, const apk_token_req *req, apk_token_out *out);
+
+/* gpu::decode_token with argmax followed by gpu::decode_greedy_continue
+ * (gpu/cuda/decode.rs:93-227): n_tokens greedy steps with one synchronisation at the end.  Step 0
+ * embeds req->token_id; every step's winner (ties to the higher id) is embedded on the device as
+ * the next step's input, and nothing returns to the host in between.  rope holds one row of
+ * rot_dim/2 (sin, cos) pairs per step (positions pos, pos+1, ...), built by the host as for
+ * apk_decode_token; req->rope is ignored.  Needs req->embd, m == 1.  tokens_out receives the
+ * n_tokens winners. */
+int apk_decode_greedy(apk_ctx *ctx, const apk_token_req *req, uint32_t n_tokens, const float *rope,
+                      uint32_t *tokens_out);
 
 /* Same work with the m*hidden input already in device memory and the result
  * left there: what a caller that keeps the residual stream on the GPU between
@@ -365,12 +407,12 @@ int apk_shard_plan(uint32_t kind, uint32_t ty, uint32_t n_out, uint32_t n_in, ui
  * exports one device buffer (CUDA IPC handle, APK_IPC_HANDLE_BYTES), the host
  * gathers the handles of all ranks in rank order and every rank opens them.
  * From then on the CTA that closes a tile of a row-parallel matvec stores its
- * partial sums straight into every rank's buffer over NVLink and raises a
- * per-tile flag there; the next matvec gathers them in its own prologue
- * (bounded wait on the flags, sum in rank order, residual add, RMSNorm,
- * quantisation): four launches per layer, no NCCL all-reduce.  At most 8
- * ranks, hidden <= 16384, m * hidden <= 131072.  Every rank must issue the
- * same sequence of decode calls. */
+ * partial sums straight into every rank's buffer over NVLink, each value as a
+ * 64-bit word that carries the exchange's number; the next matvec polls those
+ * words in its own prologue (bounded), adds them in rank order onto the residual
+ * row, normalises and quantises: four launches per layer, no fence, no flag, no
+ * NCCL all-reduce.  At most 8 ranks, m * hidden <= 131072.  Every rank must
+ * issue the same sequence of decode calls. */
 #define APK_IPC_HANDLE_BYTES 64
 int apk_dist_p2p_export(apk_ctx *ctx, void *handle_out);
 int apk_dist_p2p_open(apk_ctx *ctx, const void *handles /* world * APK_IPC_HANDLE_BYTES */);

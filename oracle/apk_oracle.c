@@ -6,6 +6,7 @@
  */
 #include "apk_oracle.h"
 
+#include <float.h>
 #include <math.h>
 #include <pthread.h>
 #include <stdlib.h>
@@ -308,6 +309,94 @@ int orc_block_dots(uint32_t ty, const uint8_t *w, size_t n_out, size_t n_in, con
 }
 
 /* ------------------------------------------------------------- threading */
+
+/* ---------------------------------------------------------------- decode attention
+ * crates/allpaka-model/src/model/attention.rs:337-399 (attend_group), 403-428 (attend_one),
+ * 430-465 (attend_head, the test-only naive form); crates/allpaka-backend/src/ops/f16.rs scalar
+ * arms of dot (63-69) and axpy (118-121); crates/allpaka-model/src/kv.rs:682-697 (store_at). */
+void orc_kv_store(const float *row, size_t n, uint16_t *dst) {
+    for (size_t i = 0; i < n; ++i) dst[i] = orc_f32_to_f16(row[i]);
+}
+
+static float f16_dot(const float *a, const uint16_t *b, size_t n) {
+    float total = 0.0f;
+    for (size_t k = 0; k < n; ++k) total += a[k] * orc_f16_to_f32(b[k]);
+    return total;
+}
+
+void orc_attend_group(const float *q_group, const uint16_t *kcache, const uint16_t *vcache, size_t kv_dim,
+                      size_t kv_head, size_t head_dim, size_t group, size_t first, size_t pos, float scale,
+                      float *out_group) {
+    float *maxes = (float *)malloc(group * sizeof(float));
+    float *denoms = (float *)malloc(group * sizeof(float));
+    for (size_t h = 0; h < group; ++h) {
+        maxes[h] = -INFINITY;
+        denoms[h] = 0.0f;
+    }
+    for (size_t t = first; t <= pos; ++t) {
+        const uint16_t *kt = kcache + t * kv_dim + kv_head * head_dim;
+        const uint16_t *vt = vcache + t * kv_dim + kv_head * head_dim;
+        for (size_t h = 0; h < group; ++h) {
+            const float *qh = q_group + h * head_dim;
+            const float s = f16_dot(qh, kt, head_dim) * scale;
+            float *acc = out_group + h * head_dim;
+            if (s > maxes[h]) {
+                if (denoms[h] > 0.0f) {
+                    const float rescale = expf(maxes[h] - s);
+                    for (size_t i = 0; i < head_dim; ++i) acc[i] *= rescale;
+                    denoms[h] *= rescale;
+                }
+                maxes[h] = s;
+            }
+            const float p = expf(s - maxes[h]);
+            denoms[h] += p;
+            for (size_t i = 0; i < head_dim; ++i) acc[i] += p * orc_f16_to_f32(vt[i]);
+        }
+    }
+    for (size_t h = 0; h < group; ++h) {
+        const float dn = denoms[h] > FLT_MIN ? denoms[h] : FLT_MIN;  /* denom.max(f32::MIN_POSITIVE) */
+        const float inv_d = 1.0f / dn;
+        float *acc = out_group + h * head_dim;
+        for (size_t i = 0; i < head_dim; ++i) acc[i] *= inv_d;
+    }
+    free(maxes);
+    free(denoms);
+}
+
+void orc_attend_one(const float *q_row, const uint16_t *kcache, const uint16_t *vcache, size_t kv_dim,
+                    size_t n_kv_heads, size_t head_dim, size_t group, size_t first, size_t pos, float scale,
+                    float *out_row) {
+    for (size_t kvh = 0; kvh < n_kv_heads; ++kvh) {
+        const size_t at = kvh * group * head_dim;
+        orc_attend_group(q_row + at, kcache, vcache, kv_dim, kvh, head_dim, group, first, pos, scale, out_row + at);
+    }
+}
+
+void orc_attend_head(const float *qh, const uint16_t *kcache, const uint16_t *vcache, size_t kv_dim,
+                     size_t kv_head, size_t head_dim, size_t pos, float scale, float *out) {
+    float *scores = (float *)malloc((pos + 1) * sizeof(float));
+    for (size_t t = 0; t <= pos; ++t) {
+        const uint16_t *kt = kcache + t * kv_dim + kv_head * head_dim;
+        float s = 0.0f;
+        for (size_t i = 0; i < head_dim; ++i) s += qh[i] * orc_f16_to_f32(kt[i]);
+        scores[t] = s * scale;
+    }
+    /* ops::softmax (ops/activation.rs:5-16) */
+    float mx = -INFINITY;
+    for (size_t t = 0; t <= pos; ++t) mx = scores[t] > mx ? scores[t] : mx;
+    float sum = 0.0f;
+    for (size_t t = 0; t <= pos; ++t) {
+        scores[t] = expf(scores[t] - mx);
+        sum += scores[t];
+    }
+    const float inv_sum = 1.0f / sum;
+    for (size_t t = 0; t <= pos; ++t) scores[t] *= inv_sum;
+    for (size_t t = 0; t <= pos; ++t) {
+        const uint16_t *vt = vcache + t * kv_dim + kv_head * head_dim;
+        for (size_t i = 0; i < head_dim; ++i) out[i] += scores[t] * orc_f16_to_f32(vt[i]);
+    }
+    free(scores);
+}
 
 int orc_cpu_threads(void) {
     /* std::thread::available_parallelism (runtime.rs:361-365) */

@@ -130,6 +130,23 @@ int orc_decode_layers(uint32_t ty, const orc_layer *layers, size_t n_layers, siz
 int orc_lm_head(uint32_t ty, const uint8_t *w, size_t vocab, size_t hidden, const float *x,
                 const float *output_norm, float eps, float *logits, int threads);
 
+/* ---- decode attention over the f16 KV cache (model/attention.rs:337-399; model/kv.rs:682-697) */
+/* K or V row of one position into the cache: f32 -> f16, round to nearest even (kv.rs:695-696). */
+void orc_kv_store(const float *row, size_t n, uint16_t *dst);
+/* One kv head attending for its whole GQA group over positions first..=pos, online softmax in one
+ * K/V pass (attend_group, attention.rs:337-399).  kcache/vcache: this layer's [capacity][kv_dim] f16. */
+void orc_attend_group(const float *q_group, const uint16_t *kcache, const uint16_t *vcache, size_t kv_dim,
+                      size_t kv_head, size_t head_dim, size_t group, size_t first, size_t pos, float scale,
+                      float *out_group);
+/* All heads of one row (attend_one, attention.rs:403-428). */
+void orc_attend_one(const float *q_row, const uint16_t *kcache, const uint16_t *vcache, size_t kv_dim,
+                    size_t n_kv_heads, size_t head_dim, size_t group, size_t first, size_t pos, float scale,
+                    float *out_row);
+/* The naive formulation the reference pins attend_group against (attend_head, attention.rs:430-465):
+ * one q head, buffered softmax (ops/activation.rs:5-16).  out accumulates. */
+void orc_attend_head(const float *qh, const uint16_t *kcache, const uint16_t *vcache, size_t kv_dim,
+                     size_t kv_head, size_t head_dim, size_t pos, float scale, float *out);
+
 int orc_cpu_threads(void);
 
 #ifdef __cplusplus

@@ -122,6 +122,14 @@ def _declare(l):
     l.orc_decode_layers.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t,
                                     C.c_size_t, C.c_size_t, C.c_size_t, C.c_float, C.c_void_p,
                                     C.c_size_t, C.c_void_p, C.c_int]
+    l.orc_kv_store.restype = None
+    l.orc_kv_store.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
+    l.orc_attend_one.restype = None
+    l.orc_attend_one.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t,
+                                 C.c_size_t, C.c_size_t, C.c_float, C.c_void_p]
+    l.orc_attend_head.restype = None
+    l.orc_attend_head.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_size_t, C.c_size_t, C.c_size_t,
+                                  C.c_float, C.c_void_p]
     l.orc_lm_head.restype = C.c_int
     l.orc_lm_head.argtypes = [C.c_uint32, C.c_void_p, C.c_size_t, C.c_size_t, C.c_void_p,
                               C.c_void_p, C.c_float, C.c_void_p, C.c_int]
@@ -364,4 +372,33 @@ def lm_head(ty, w, vocab, hidden, x, output_norm, eps, threads=0):
     out = np.empty(vocab, dtype=np.float32)
     if lib().orc_lm_head(ty, _p(w), vocab, hidden, _p(x), _p(g), eps, _p(out), threads):
         raise ValueError("lm_head: geometry mismatch")
+    return out
+
+
+def kv_store(row) -> np.ndarray:
+    """f32 -> f16 bits, round to nearest even, as KvCache::store_at keeps K and V (model/kv.rs:695-696)."""
+    row = _f32(row).reshape(-1)
+    out = np.empty(row.size, dtype=np.uint16)
+    lib().orc_kv_store(_p(row), row.size, _p(out))
+    return out
+
+
+def attend_one(q_row, kcache, vcache, kv_dim, n_kv_heads, head_dim, group, first, pos, scale) -> np.ndarray:
+    """All heads of one row over cache positions first..=pos (model/attention.rs:403-428, 337-399).
+    kcache / vcache: one layer's [capacity, kv_dim] uint16 (f16 bits)."""
+    q_row = _f32(q_row).reshape(-1)
+    kc = np.ascontiguousarray(kcache, dtype=np.uint16)
+    vc = np.ascontiguousarray(vcache, dtype=np.uint16)
+    out = np.zeros(n_kv_heads * group * head_dim, dtype=np.float32)
+    lib().orc_attend_one(_p(q_row), _p(kc), _p(vc), kv_dim, n_kv_heads, head_dim, group, first, pos, scale, _p(out))
+    return out
+
+
+def attend_head(qh, kcache, vcache, kv_dim, kv_head, head_dim, pos, scale) -> np.ndarray:
+    """The naive one-head formulation (model/attention.rs:430-465)."""
+    qh = _f32(qh).reshape(-1)
+    kc = np.ascontiguousarray(kcache, dtype=np.uint16)
+    vc = np.ascontiguousarray(vcache, dtype=np.uint16)
+    out = np.zeros(head_dim, dtype=np.float32)
+    lib().orc_attend_head(_p(qh), _p(kc), _p(vc), kv_dim, kv_head, head_dim, pos, scale, _p(out))
     return out

@@ -101,6 +101,7 @@ def test_two_gpu_decode_matches_the_unsharded_oracle(ty, m, exchange):
         p.join(timeout=120)
         assert p.exitcode == 0
     print(f"tp2 {exchange} ty={ty} m={m}: chained rel-L2 per seed {['%.1e' % e for e in errs]}")
-    assert np.median(errs) <= 1e-4, errs
+    # (m > 1: wo, down and the head take f32 rows in the reference and two-level int8 rows here)
+    assert np.median(errs) <= (1e-4 if m == 1 else 5e-4), errs
     assert sum(e > 2e-3 for e in errs) <= 1, errs
     assert same and argmax_ok

@@ -426,3 +426,33 @@ def test_cuda_parity_fixture_on_the_oracle(orc):
         want = float(seq_dot(row, x))
         assert abs(got_f32[j] - want) < 1e-3 + 1e-3 * abs(want)
         assert abs(got_q8[j] - want) < q8_act_error_bound(row, x) + 1e-4
+
+
+def test_attend_group_matches_the_naive_reference(orc):
+    """crates/allpaka-model/src/model/attention.rs:569-629: 8 q heads, 2 kv heads, head_dim 16, 33
+    positions from the test's own LCG; the one-pass online softmax against the buffered one."""
+    n_heads, n_kv, hd, positions = 8, 2, 16, 33
+    kv_dim, q_dim, group = n_kv * hd, n_heads * hd, n_heads // n_kv
+    state = 0x123456789ABCDEF0
+
+    def rnd():
+        nonlocal state
+        state = (state * 6364136223846793005 + 1) & 0xFFFFFFFFFFFFFFFF
+        return np.float32(np.float32(state >> 40) / np.float32(1 << 24) * np.float32(2.0) - np.float32(1.0))
+
+    kc = np.zeros((positions, kv_dim), np.uint16)
+    vc = np.zeros((positions, kv_dim), np.uint16)
+    for t in range(positions):
+        k = np.array([rnd() for _ in range(kv_dim)], np.float32)
+        v = np.array([rnd() for _ in range(kv_dim)], np.float32)
+        kc[t], vc[t] = orc.kv_store(k), orc.kv_store(v)
+    q = np.array([rnd() for _ in range(q_dim)], np.float32)
+    scale = np.float32(1.0) / np.sqrt(np.float32(hd))
+    pos = positions - 1
+    got = orc.attend_one(q, kc, vc, kv_dim, n_kv, hd, group, 0, pos, scale)
+    want = np.concatenate([orc.attend_head(q[i * hd:(i + 1) * hd], kc, vc, kv_dim, i // group, hd, pos, scale)
+                           for i in range(n_heads)])
+    assert np.all(np.abs(got - want) < 1e-5 * (1.0 + np.abs(want)))
+    # the cache keeps IEEE halves: the store is the dtype conversion the other known answers pin
+    assert orc.kv_store(np.array([1.0, -2.5, 65504.0, 1e-8, 70000.0], np.float32)).tolist() == \
+        [0x3C00, 0xC100, 0x7BFF, 0x0000, 0x7C00]
