@@ -228,6 +228,8 @@ struct apk_ctx {
     int32_t *dots_dump = nullptr;  // block dots of launch dots_launch
     size_t dots_cap = 0;
     int dots_launch = -1, launch_no = 0;
+    bool prev_mv_exclusive = false;  // the last matvec launched holds every SM to itself (see launch_matvec)
+    int smem_per_sm = 0;
     std::vector<RecMeta> rec_meta;
     bool use_pdl = true;        // ALLPAKA_B200_PDL=0 turns programmatic dependent launch off
     void *comm = nullptr;
@@ -601,6 +603,13 @@ int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool
     const long long U = (long long)W->n_tiles * W->KS;
     const int grid = (int)std::min<long long>(c->n_sm, U);
     if ((U + 1) * grid >= (1LL << 31)) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "matrix too large for 32-bit unit arithmetic");
+    // A launch may defer its dependency wait (xin_late) only behind a matvec that holds every SM
+    // to itself: one CTA per SM, too much shared memory for a second one.  Its own CTAs then start
+    // only where a CTA of that matvec has left, i.e. after that matvec saw everything before it
+    // complete -- the token counter included.  Smaller grids share the GPU with older launches.
+    const bool exclusive = grid == c->n_sm && 2 * (smem + 1024) > c->smem_per_sm;
+    if (p.xin_late && !c->prev_mv_exclusive) p.xin_late = 0;
+    c->prev_mv_exclusive = exclusive;
     CUDA_TRY(launch_ex(c, k, dim3(grid), dim3(MV_THREADS), (size_t)smem, c->use_pdl, (const MvParams)p));
     c->st.launches++;
     return APK_OK;
@@ -824,6 +833,7 @@ int apk_init(apk_ctx **out, int device) {
     c->device = device;
     c->n_sm = prop.multiProcessorCount;
     c->smem_optin = (int)prop.sharedMemPerBlockOptin;
+    c->smem_per_sm = (int)prop.sharedMemPerMultiprocessor;
     CUDA_TRY(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
     CUDA_TRY(cudaEventCreate(&c->ev0));
     CUDA_TRY(cudaEventCreate(&c->ev1));

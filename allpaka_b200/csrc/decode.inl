@@ -317,7 +317,6 @@ struct TokenLaunch {
             XchReduceParams rp{};
             rp.xch = c->xch;
             rp.seq = XchSeq{pending_xch, per_token()};
-            rp.x = xc; rp.ldx = (int)H;
             rp.xout = xn; rp.ldxout = (int)H;
             rp.n = (int)H; rp.m = (int)m;
             rp.err = c->d_err;
@@ -389,6 +388,8 @@ struct TokenLaunch {
             p.epi = EPI_PEERS;
             p.xch = c->xch;
             p.xch_row = (int)H;
+            p.resid = P->x[cur].as<float>();  // rank 0 adds the old rows into its slot
+            p.ldr = (int)H;
             p.xout = XchSeq{n_xch, per_token()};
             pending_xch = n_xch++;
             return launch(W, p, autom, next_W);
@@ -474,6 +475,7 @@ int launch_embed(apk_ctx *c, Plan *P, const uint32_t *token_dev, uint32_t token,
 int enqueue_token(apk_ctx *c, Plan *P, uint32_t m, int argmax, int *n_launches) {
     const uint64_t l0 = c->st.launches;
     c->launch_no = 0;  // launches are numbered within the token (error reports, parity instrumentation)
+    c->prev_mv_exclusive = false;
     TokenLaunch T(c, P, m);
     CUDA_TRY(cudaMemcpyAsync(P->x[0].p, P->xin.p, (size_t)m * P->hidden * 4, cudaMemcpyDeviceToDevice, c->stream));
     for (uint32_t l = 0; l < P->n_layers; ++l) {
@@ -530,8 +532,10 @@ int validate_token_req(apk_ctx *c, const apk_token_req *r) {
     if (r->m == 0 || r->m > APK_MAX_M) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "m = %u is outside 1..8", r->m);
     if (r->attn_core != APK_ATTN_IDENTITY && r->attn_core != APK_ATTN_CAUSAL)
         return decline_decode(c, APK_DECLINE_MISSING_CAPABILITY, "attention core %u is not built into this library", r->attn_core);
-    if (r->attn_core == APK_ATTN_CAUSAL && (!r->kv || (uint64_t)r->pos + r->m > r->kv->capacity))
-        return decline_decode(c, APK_ERR_INVALID_ARG, "no KV cache, or positions %u..%u past its capacity", r->pos, r->pos + r->m - 1);
+    if (r->attn_core == APK_ATTN_CAUSAL && !r->kv) return decline_decode(c, APK_ERR_INVALID_ARG, "attention core without a KV cache");
+    if (r->attn_core == APK_ATTN_CAUSAL && (uint64_t)r->pos + r->m > r->kv->capacity)  // the caller's CPU path grows its own cache
+        return decline_decode(c, APK_DECLINE_INVALID_STATE, "positions %u..%u are past the cache capacity %u", r->pos, r->pos + r->m - 1,
+                              r->kv->capacity);
     const bool by_token = r->use_token && r->embd.w && r->m == 1;
     if ((!r->x && !by_token) || (r->rot_dim && !r->rope)) return decline_decode(c, APK_ERR_INVALID_ARG, "missing input rows or rope table");
     return APK_OK;
@@ -735,9 +739,7 @@ int apk_debug_xch_timeout(apk_ctx *c) {
         CUDA_TRY(cudaMalloc((void **)&b, XCH_BYTES));
         CUDA_TRY(cudaMemsetAsync(b, 0, XCH_BYTES, c->stream));
     }
-    APK_TRY(c->x_dev.ensure(n * sizeof(float)));
     APK_TRY(c->y_dev.ensure(n * sizeof(float)));
-    CUDA_TRY(cudaMemsetAsync(c->x_dev.p, 0, n * sizeof(float), c->stream));
     const uint32_t one = 1u;
     CUDA_TRY(cudaMemcpyAsync(xch_tok(buf[0]), &one, 4, cudaMemcpyHostToDevice, c->stream));
     std::vector<unsigned long long> own(n, 1ull << 32);  // rank 0's words of exchange 1 (parity 1): tag 1, value 0
@@ -749,7 +751,6 @@ int apk_debug_xch_timeout(apk_ctx *c) {
     rp.xch.rank = 0;
     rp.xch.world = 2;
     rp.seq = XchSeq{0, 1};
-    rp.x = c->x_dev.as<float>(); rp.ldx = n;
     rp.xout = c->y_dev.as<float>(); rp.ldxout = n;
     rp.n = n; rp.m = 1;
     rp.err = c->d_err;

@@ -508,12 +508,12 @@ __device__ __forceinline__ void st_relaxed_sys_b64(unsigned long long *p, unsign
 __device__ __forceinline__ void ld_relaxed_sys_v2b64(const unsigned long long *p, unsigned long long &a, unsigned long long &b) {
     asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
-// x[i..i+3] + (slot 0 + slot 1 + ...)[i..i+3] in rank order: the one summation order of an
-// exchange.  Polls (bounded) until the four words of every rank carry tag e; *ok = false when
-// the budget ran out (the sum then holds whatever was there).
-__device__ __forceinline__ float4 xch_gather4(const float *x, float *mine, uint32_t e, int world, size_t off, long long limit,
-                                              bool *ok) {
-    const float4 acc0 = __ldcg(reinterpret_cast<const float4 *>(x));
+// (slot 0 + slot 1 + ...)[i..i+3] in rank order: the one summation order of an exchange (rank 0's
+// slot already holds the residual row plus its partial sums, see EPI_PEERS).  Polls (bounded)
+// until the four words of every rank carry tag e; *ok = false when the budget ran out (the sum
+// then holds whatever was there).  Nothing but tagged words is read, so a caller needs no other
+// ordering with the kernels that produced them.
+__device__ __forceinline__ float4 xch_gather4(float *mine, uint32_t e, int world, size_t off, long long limit, bool *ok) {
     const unsigned long long *s0 = xch_words(mine) + (size_t)(e & 1u) * XCH_MAX_RANKS * XCH_ROW_FLOATS + off;
     float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
     const long long t0 = clock64();
@@ -528,20 +528,21 @@ __device__ __forceinline__ float4 xch_gather4(const float *x, float *mine, uint3
                 break;
             }
         }
-        sum.x = __fadd_rn(sum.x, __uint_as_float((uint32_t)w0)); sum.y = __fadd_rn(sum.y, __uint_as_float((uint32_t)w1));
-        sum.z = __fadd_rn(sum.z, __uint_as_float((uint32_t)w2)); sum.w = __fadd_rn(sum.w, __uint_as_float((uint32_t)w3));
+        const float4 v = make_float4(__uint_as_float((uint32_t)w0), __uint_as_float((uint32_t)w1), __uint_as_float((uint32_t)w2),
+                                     __uint_as_float((uint32_t)w3));
+        if (r == 0) sum = v;
+        else {
+            sum.x = __fadd_rn(sum.x, v.x); sum.y = __fadd_rn(sum.y, v.y);
+            sum.z = __fadd_rn(sum.z, v.z); sum.w = __fadd_rn(sum.w, v.w);
+        }
     }
-    float4 acc;
-    acc.x = __fadd_rn(acc0.x, sum.x); acc.y = __fadd_rn(acc0.y, sum.y);
-    acc.z = __fadd_rn(acc0.z, sum.z); acc.w = __fadd_rn(acc0.w, sum.w);
-    return acc;
+    return sum;
 }
 
 struct XchReduceParams {
     XchPeers xch;
     XchSeq seq;                // which exchange to collect
-    const float *x; int ldx;   // residual stream in  [m][n]
-    float *xout; int ldxout;   // residual stream out [m][n] = x + sum over ranks of the partial vectors
+    float *xout; int ldxout;   // residual stream out [m][n] = sum over ranks of the slots (rank 0's holds the old rows too)
     int n, m;
     int *err;
     int pdl;
@@ -551,7 +552,7 @@ struct XchReduceParams {
 // Stand-alone form of the collecting side (batches of m > 1 rows, whose activations are
 // quantised by a separate pass): grid = ceil(m*n / 1024), 256 threads, four floats per
 // thread.  Waits (bounded) for every rank's tagged words of the exchange and adds them in
-// rank order onto the residual rows.
+// rank order into the new residual rows.
 __global__ void __launch_bounds__(256) xch_reduce_kernel(XchReduceParams p) {
     if (p.pdl) {
         pdl_launch_dependents();
@@ -564,7 +565,7 @@ __global__ void __launch_bounds__(256) xch_reduce_kernel(XchReduceParams p) {
     if (i < total) {
         const int m = (int)(i / p.n), col = (int)(i % p.n);
         bool ok = true;
-        const float4 acc = xch_gather4(p.x + (size_t)m * p.ldx + col, mine, e, p.xch.world, (size_t)m * p.n + col, p.wait_limit, &ok);
+        const float4 acc = xch_gather4(mine, e, p.xch.world, (size_t)m * p.n + col, p.wait_limit, &ok);
         if (!ok) atomicCAS(p.err, 0, ERRW_PEER_TIMEOUT);  // a peer never delivered: record it and finish normally
         *reinterpret_cast<float4 *>(p.xout + (size_t)m * p.ldxout + col) = acc;
     }
@@ -687,7 +688,8 @@ __global__ void repack_q4_k_kernel(RepackParams p) {
 // the Q8 (or two-level) blocks the output projection consumes.
 constexpr int ATT_WARPS = 8;
 constexpr int ATT_MAX_GROUP = 8;       // q heads per kv head handled by one CTA pass
-constexpr int ATT_PART = TILE_ROWS + 2;  // floats per partial: acc[128], running max, denominator
+constexpr int ATT_PART = TILE_ROWS + 4;  // floats per partial: acc[128], running max, denominator, pad (16-byte rows)
+static_assert(ATT_PART % 4 == 0, "partials are moved as float4");
 
 struct AttnParams {
     const float *q; int ldq;           // [m][ldq] roped q heads (head h at column h * 128)
@@ -1070,9 +1072,10 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
     double *dred = reinterpret_cast<double *>(red);
     float v[PRO_CH];
     if (p.xin.index >= 0) {
-        // Tensor parallel: the row is the residual plus the partial sums every rank stored
-        // into this rank's exchange buffer as tagged words.  Poll them (bounded) and add
-        // the slots in rank order; CTA 0 keeps the new residual row.
+        // Tensor parallel: the row is the sum of what every rank stored into this rank's
+        // exchange buffer as tagged words (rank 0: old residual + its partial sums, the others:
+        // their partial sums).  Poll them (bounded) and add the slots in rank order; CTA 0
+        // keeps the new residual row.
         float *mine = p.xch.slots[p.xch.rank];
         const uint32_t e = xch_number(mine, p.xin);
         bool ok = true;
@@ -1081,7 +1084,7 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
             const int el = 4 * tid + PRO_CHUNK * j;
             float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
             if (el < n) {
-                x = xch_gather4(pp.x + el, mine, e, p.xch.world, (size_t)el, p.wait_limit, &ok);
+                x = xch_gather4(mine, e, p.xch.world, (size_t)el, p.wait_limit, &ok);
                 if (pp.xout && blockIdx.x == 0) *reinterpret_cast<float4 *>(pp.xout + el) = x;
             }
             v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
@@ -1257,9 +1260,6 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     // prepared records arrive by bulk copy; a row still to be quantised is read straight into
     // registers by the consumer threads (plain loads return sooner than a copy through shared memory)
     const bool acts_copy = p.pro == PRO_LOAD;
-    // first launch of a token in a tensor-parallel group: advance the token counter that numbers
-    // the exchanges (single writer; later launches read it after this grid has completed)
-    if (p.tok_inc && blockIdx.x == 0 && tid == 0) *xch_tok(p.xch.slots[p.xch.rank]) += 1u;
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) {
             mbar_init(&full[s], 1);
@@ -1540,6 +1540,10 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     // The wait is made up for after the last unit, when it costs nothing.
     const bool late_dep = p.pro == PRO_QUANT && p.xin.index >= 0 && p.xin_late;
     if (p.pdl && !late_dep) pdl_wait();
+    // first launch of a token in a tensor-parallel group: advance the token counter that numbers
+    // the exchanges.  Single writer, after every launch of the previous token has completed
+    // (this launch never defers its wait); later launches read it after this grid has completed.
+    if (p.tok_inc && blockIdx.x == 0 && tid == 0) *xch_tok(p.xch.slots[p.xch.rank]) += 1u;
     if (tl && tid == 0) tl[2] = globaltimer_ns();  // dependency satisfied
     if (tid == 0 && acts_copy) {
         // the activations, as soon as they exist
@@ -2066,7 +2070,9 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw,
             const int m = i / TILE_ROWS, r = i % TILE_ROWS;
             const int row = row0 + r;
             if (row >= p.n_out) continue;
-            const unsigned long long w = ((unsigned long long)e << 32) | (unsigned long long)__float_as_uint(val(m, r));
+            // rank 0 carries the residual rows into the sum (every rank holds the same rows)
+            const float v = (p.resid && p.xch.rank == 0) ? __fadd_rn(__ldcg(p.resid + (size_t)m * p.ldr + row), val(m, r)) : val(m, r);
+            const unsigned long long w = ((unsigned long long)e << 32) | (unsigned long long)__float_as_uint(v);
             for (int k = 0; k < p.xch.world; ++k) {
                 const int dst = (p.xch.rank + k) % p.xch.world;  // start with the local copy, spread the links
                 st_relaxed_sys_b64(xch_words(p.xch.slots[dst]) + slot + (size_t)m * p.xch_row + row, w);

@@ -3,7 +3,8 @@
 The block layouts are the GGUF ones the engine reads from a model file
 (crates/allpaka-dtype/src/lib.rs:93-108; crates/allpaka-gguf/src/dequant.rs:93-126,
 206-231): Q8_0 = ``{f16 d; i8 q[32]}`` (34 B), Q4_K = ``{f16 d; f16 dmin;
-u8 scales[12]; u8 qs[128]}`` (144 B).  No model file is needed: the value
+u8 scales[12]; u8 qs[128]}`` (144 B), Q6_K = ``{u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d}``
+(210 B, dequant.rs:265-296).  No model file is needed: the value
 distributions below are the ones the benchmark configurations state.
 """
 from __future__ import annotations
@@ -12,8 +13,9 @@ import numpy as np
 
 TY_Q8_0 = 8
 TY_Q4_K = 12
+TY_Q6_K = 14
 
-BLOCK = {TY_Q8_0: (32, 34), TY_Q4_K: (256, 144)}
+BLOCK = {TY_Q8_0: (32, 34), TY_Q4_K: (256, 144), TY_Q6_K: (256, 210)}
 
 
 def expected_bytes(ty: int, elements: int) -> int:
@@ -65,11 +67,26 @@ def q4_k_matrix(n_out: int, n_in: int, seed: int, d_sigma: float = 0.002) -> np.
     return out.reshape(-1)
 
 
+def q6_k_matrix(n_out: int, n_in: int, seed: int, d_sigma: float = 0.0005) -> np.ndarray:
+    """6-bit quants uniform (every ql/qh byte uniform), signed 8-bit sub-block scales uniform in
+    [-128,127], f16 d drawn as |N(0,sigma)|."""
+    rng = np.random.default_rng(seed)
+    nsb = n_in // 256
+    out = np.empty((n_out, nsb, 210), dtype=np.uint8)
+    out[:, :, 0:192] = rng.integers(0, 256, size=(n_out, nsb, 192), dtype=np.uint8)
+    out[:, :, 192:208] = rng.integers(-128, 128, size=(n_out, nsb, 16), dtype=np.int8).view(np.uint8)
+    d = np.abs(rng.normal(0.0, d_sigma, size=(n_out, nsb))).astype(np.float16)
+    out[:, :, 208:210] = d.view(np.uint8).reshape(n_out, nsb, 2)
+    return out.reshape(-1)
+
+
 def matrix(ty: int, n_out: int, n_in: int, seed: int) -> np.ndarray:
     if ty == TY_Q8_0:
         return q8_0_matrix(n_out, n_in, seed)
     if ty == TY_Q4_K:
         return q4_k_matrix(n_out, n_in, seed)
+    if ty == TY_Q6_K:
+        return q6_k_matrix(n_out, n_in, seed)
     raise ValueError(f"no generator for ggml type {ty}")
 
 
@@ -117,7 +134,7 @@ def tame_scales(buf: np.ndarray, ty: int, value: int = 0x211F) -> np.ndarray:
     be, bb = BLOCK[ty]
     v = buf.reshape(-1, bb)
     lo, hi = value & 0xFF, value >> 8
-    offs = (0,) if ty == TY_Q8_0 else (0, 2)
+    offs = {TY_Q8_0: (0,), TY_Q4_K: (0, 2), TY_Q6_K: (208,)}[ty]
     for o in offs:
         v[:, o] = lo
         v[:, o + 1] = hi

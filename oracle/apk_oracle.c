@@ -92,6 +92,7 @@ static int block_geom(uint32_t ty, size_t *be, size_t *bb) {
     /* crates/allpaka-dtype/src/lib.rs:79-108 */
     if (ty == ORC_TY_Q8_0) { *be = 32; *bb = 34; return 0; }
     if (ty == ORC_TY_Q4_K) { *be = 256; *bb = 144; return 0; }
+    if (ty == ORC_TY_Q6_K) { *be = 256; *bb = 210; return 0; }
     return -1;
 }
 
@@ -130,12 +131,42 @@ static void dequant_q4_k_block(const uint8_t *b, float *out) {
     }
 }
 
+/* The four 6-bit values that share index l of one 128-element half: ql low/high nibbles of bytes
+ * l and l+32, high bits from successive 2-bit fields of qh[l], each minus 32
+ * (crates/allpaka-gguf/src/dequant.rs:285-289; the same lines in q8_acts.rs:329-333). */
+static inline void q6_k_four(const uint8_t *ql, const uint8_t *qh, int l, int q[4]) {
+    q[0] = (int)(int8_t)((ql[l] & 0xf) | ((qh[l] & 3) << 4)) - 32;
+    q[1] = (int)(int8_t)((ql[l + 32] & 0xf) | (((qh[l] >> 2) & 3) << 4)) - 32;
+    q[2] = (int)(int8_t)((ql[l] >> 4) | (((qh[l] >> 4) & 3) << 4)) - 32;
+    q[3] = (int)(int8_t)((ql[l + 32] >> 4) | (((qh[l] >> 6) & 3) << 4)) - 32;
+}
+
+/* crates/allpaka-gguf/src/dequant.rs:271-296 */
+static void dequant_q6_k_block(const uint8_t *b, float *out) {
+    const uint8_t *scales = b + 192;
+    float d = orc_f16_to_f32(le16(b + 208));
+    for (int half = 0; half < 2; half++) {
+        const uint8_t *ql = b + half * 64, *qh = b + 128 + half * 32;
+        const int8_t *sc = (const int8_t *)scales + half * 8;
+        float *o = out + half * 128;
+        for (int l = 0; l < 32; l++) {
+            int is = l / 16, q[4];
+            q6_k_four(ql, qh, l, q);
+            o[l] = d * (float)sc[is] * (float)q[0];
+            o[32 + l] = d * (float)sc[is + 2] * (float)q[1];
+            o[64 + l] = d * (float)sc[is + 4] * (float)q[2];
+            o[96 + l] = d * (float)sc[is + 6] * (float)q[3];
+        }
+    }
+}
+
 int orc_dequant(uint32_t ty, const uint8_t *bytes, size_t n_bytes, float *out, size_t n) {
     size_t be, bb;
     if (block_geom(ty, &be, &bb) || n % be || n / be * bb != n_bytes) return -1;
     for (size_t i = 0; i < n / be; i++) {
         if (ty == ORC_TY_Q8_0) dequant_q8_0_block(bytes + i * bb, out + i * be);
-        else dequant_q4_k_block(bytes + i * bb, out + i * be);
+        else if (ty == ORC_TY_Q4_K) dequant_q4_k_block(bytes + i * bb, out + i * be);
+        else dequant_q6_k_block(bytes + i * bb, out + i * be);
     }
     return 0;
 }
@@ -226,6 +257,71 @@ float orc_dot_q4_k_i8(const uint8_t *row, size_t n_in, const float *dx, const fl
     return total;
 }
 
+/* The signed 6-bit values of quarter qi (0..3) of one half, in element order. */
+static void q6_k_quarter(const uint8_t *ql, const uint8_t *qh, int qi, int8_t out[32]) {
+    for (int l = 0; l < 32; l++) {
+        int q[4];
+        q6_k_four(ql, qh, l, q);
+        out[l] = (int8_t)q[qi];
+    }
+}
+
+/* crates/allpaka-backend/src/quantmat/q8_acts.rs:307-346 (the non-aarch64 arm 328-334) */
+float orc_dot_q6_k_i8(const uint8_t *row, size_t n_in, const float *dx, const int8_t *q8) {
+    float total = 0.0f;
+    size_t nsb = n_in / 256;
+    for (size_t bi = 0; bi < nsb; bi++) {
+        const uint8_t *block = row + bi * 210;
+        float d = orc_f16_to_f32(le16(block + 208));
+        for (int half = 0; half < 2; half++) {
+            const uint8_t *ql = block + half * 64, *qh = block + 128 + half * 32;
+            const int8_t *sc = (const int8_t *)block + 192 + half * 8;
+            for (int qi = 0; qi < 4; qi++) {
+                int8_t qq[32];
+                q6_k_quarter(ql, qh, qi, qq);
+                size_t blk = bi * 8 + (size_t)half * 4 + (size_t)qi;
+                const int8_t *xq = q8 + blk * 32;
+                float dot0 = (float)orc_dot_i8(qq, xq, 16);
+                float dot1 = (float)orc_dot_i8(qq + 16, xq + 16, 16);
+                float sc0 = (float)sc[2 * qi], sc1 = (float)sc[2 * qi + 1];
+                total += d * dx[blk] * (sc0 * dot0 + sc1 * dot1);
+            }
+        }
+    }
+    return total;
+}
+
+/* crates/allpaka-backend/src/quantmat/dot_f32.rs:252-289 */
+float orc_dot_q6_k(const uint8_t *row, size_t n_in, const float *x) {
+    float total = 0.0f;
+    size_t nsb = n_in / 256;
+    for (size_t bi = 0; bi < nsb; bi++) {
+        const uint8_t *block = row + bi * 210;
+        float d = orc_f16_to_f32(le16(block + 208));
+        const float *xb = x + bi * 256;
+        float blk_sum = 0.0f;
+        for (int half = 0; half < 2; half++) {
+            const uint8_t *ql = block + half * 64, *qh = block + 128 + half * 32;
+            const int8_t *sc = (const int8_t *)block + 192 + half * 8;
+            const float *xh = xb + half * 128;
+            float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int is = 0; is < 2; is++) {
+                for (int l = is * 16; l < is * 16 + 16; l++) {
+                    int q[4];
+                    q6_k_four(ql, qh, l, q);
+                    acc[is] += (float)q[0] * xh[l];
+                    acc[2 + is] += (float)q[1] * xh[l + 32];
+                    acc[4 + is] += (float)q[2] * xh[l + 64];
+                    acc[6 + is] += (float)q[3] * xh[l + 96];
+                }
+            }
+            for (int g = 0; g < 8; g++) blk_sum += (float)sc[g] * acc[g];
+        }
+        total += d * blk_sum;
+    }
+    return total;
+}
+
 /* crates/allpaka-backend/src/quantmat/dot_f32.rs:140-160 (scalar arm 150-156) */
 float orc_dot_q8_0(const uint8_t *row, size_t n_in, const float *x) {
     float total = 0.0f;
@@ -288,6 +384,22 @@ int orc_block_dots(uint32_t ty, const uint8_t *w, size_t n_out, size_t n_in, con
             if (ty == ORC_TY_Q8_0) {
                 for (size_t b = 0; b < nb; b++)
                     o[b] = dot_i8_32((const int8_t *)(row + b * 34 + 2), qi + b * 32);
+            } else if (ty == ORC_TY_Q6_K) {
+                /* per 32-element block the integer the f32 scale multiplies: sc0*dot0 + sc1*dot1
+                 * (q8_acts.rs:338-342; exact in f32 there, |value| < 2^24) */
+                for (size_t sb = 0; sb < n_in / 256; sb++) {
+                    const uint8_t *block = row + sb * 210;
+                    for (int half = 0; half < 2; half++) {
+                        const int8_t *sc = (const int8_t *)block + 192 + half * 8;
+                        for (int qr = 0; qr < 4; qr++) {
+                            int8_t qq[32];
+                            q6_k_quarter(block + half * 64, block + 128 + half * 32, qr, qq);
+                            size_t blk = sb * 8 + (size_t)half * 4 + (size_t)qr;
+                            o[blk] = (int32_t)sc[2 * qr] * orc_dot_i8(qq, qi + blk * 32, 16) +
+                                     (int32_t)sc[2 * qr + 1] * orc_dot_i8(qq + 16, qi + blk * 32 + 16, 16);
+                        }
+                    }
+                }
             } else {
                 for (size_t sb = 0; sb < n_in / 256; sb++) {
                     const uint8_t *qs = row + sb * 144 + 16;
@@ -454,9 +566,12 @@ static inline float row_dot_any(const mm_ctx *c, size_t i, size_t j) {
     if (c->q) {
         if (c->ty == ORC_TY_Q8_0)
             return orc_dot_q8_0_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
+        if (c->ty == ORC_TY_Q6_K)
+            return orc_dot_q6_k_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
         return orc_dot_q4_k_i8(row, c->n_in, c->d + i * nb, c->sum + i * nb, c->q + i * c->n_in);
     }
     const float *xi = c->x + i * c->n_in;
+    if (c->ty == ORC_TY_Q6_K) return orc_dot_q6_k(row, c->n_in, xi);
     return c->ty == ORC_TY_Q8_0 ? orc_dot_q8_0(row, c->n_in, xi) : orc_dot_q4_k(row, c->n_in, xi);
 }
 

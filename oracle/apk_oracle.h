@@ -28,6 +28,7 @@ extern "C" {
 /* GGML type ids (crates/allpaka-dtype/src/lib.rs:61-75). */
 #define ORC_TY_Q8_0 8u
 #define ORC_TY_Q4_K 12u
+#define ORC_TY_Q6_K 14u
 
 /* crates/allpaka-dtype/src/lib.rs:129-201 */
 float orc_f16_to_f32(uint16_t h);
@@ -58,10 +59,14 @@ float orc_dot_q4_k_i8(const uint8_t *row, size_t n_in, const float *d, const flo
                       const int8_t *q);
 float orc_dot_q8_0(const uint8_t *row, size_t n_in, const float *x);
 float orc_dot_q4_k(const uint8_t *row, size_t n_in, const float *x);
+/* q8_acts.rs:307-346 and dot_f32.rs:252-289: one Q6_K row. */
+float orc_dot_q6_k_i8(const uint8_t *row, size_t n_in, const float *d, const int8_t *q);
+float orc_dot_q6_k(const uint8_t *row, size_t n_in, const float *x);
 
 /* The int32 dot of every 32-element block of every row against Q8 acts:
  * dots[(i*n_out + j)*(n_in/32) + b].  For Q4_K block b = 8*superblock +
- * sub-block (lo nibbles = even sub-blocks, q8_acts.rs:288-295). */
+ * sub-block (lo nibbles = even sub-blocks, q8_acts.rs:288-295); for Q6_K the entry is
+ * sc0*dot0 + sc1*dot1 of the block's two 16-element halves (q8_acts.rs:338-342). */
 int orc_block_dots(uint32_t ty, const uint8_t *w, size_t n_out, size_t n_in, const int8_t *q,
                    size_t m, int32_t *dots);
 

@@ -312,19 +312,27 @@ def test_an_expired_device_wait_is_reported_and_the_context_lives_on(orc):
     g.close()
 
 
-@pytest.mark.parametrize("ty,m", [(Q8_0, 1), (Q8_0, 3), (Q4_K, 1)])
-def test_peer_exchange_path_on_one_gpu(orc, monkeypatch, ty, m):
-    """One rank exchanging with itself: wo and down store their rows into the exchange slots and
-    raise the tile flags, the next matvec gathers them in its prologue (m = 1) or the collecting
-    kernel does (m > 1).  Same logits as the ordinary single-GPU path, twice (two tokens: both slot parities)."""
-    hidden, nh, nkv, ffn, vocab = 1024, 8, 2, 2048, 1536
+@pytest.mark.parametrize("ty,m,wide", [(Q8_0, 1, False), (Q8_0, 3, False), (Q4_K, 1, False), (Q8_0, 1, True)])
+def test_peer_exchange_path_on_one_gpu(orc, monkeypatch, ty, m, wide):
+    """One rank exchanging with itself: wo and down store their rows (rank 0: residual included) into
+    the exchange slots as tagged words, the next matvec gathers them in its prologue (m = 1) or the
+    collecting kernel does (m > 1).  Same logits as the ordinary single-GPU path, twice (two tokens).
+    The wide case has matrices that fill every SM, which is what lets a gathering launch start on
+    the tagged words alone and make up for its dependency wait at the end; the narrow ones keep
+    the wait in front."""
+    hidden, nh, nkv, ffn, vocab = (4096, 32, 8, 8192, 24576) if wide else (1024, 8, 2, 2048, 1536)
     outs = []
     for self_xch in ("0", "1"):
         g = fresh_gpu(monkeypatch, ALLPAKA_B200_SELF_XCH=self_xch)
-        req, layers, head, out_norm, x, rope, r = build_token(g, orc, ty, 3, hidden, nh, nkv, ffn, vocab, m, True, 6100)
+        req, layers, head, out_norm, x, rope, r = build_token(g, orc, ty, 2 if wide else 3, hidden, nh, nkv, ffn, vocab, m, True, 6100)
         a = g.decode_token_checked(req)
         b = g.decode_token_checked(req)
         assert np.array_equal(a, b)
+        for _ in range(6 if wide else 0):  # back to back: token counter, both parities of partial buffers and slots
+            assert np.array_equal(g.decode_token_checked(req), a)
+        if wide:  # tokens enqueued back to back with nothing of the host between them
+            g.decode_replay(req, 40)
+            assert np.array_equal(g.decode_token_checked(req), a)
         outs.append(a)
         if self_xch == "1":
             xo = oracle_decode(orc, ty, layers, hidden, nh * 128, nkv * 128, 128, ffn, 1e-6, rope, x, m)

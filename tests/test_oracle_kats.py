@@ -11,7 +11,7 @@ import pytest
 
 from allpaka_b200 import synth
 
-Q8_0, Q4_K = 8, 12
+Q8_0, Q4_K, Q6_K = 8, 12, 14
 
 
 def half_bits(orc, x):
@@ -179,6 +179,51 @@ def q8_act_error_bound(w, x):
     return bound
 
 
+def test_q6_k_reassembles_six_bit_values_from_the_right_bits(orc):
+    """dequant.rs:374-409: one chosen element per quarter, everything else zero."""
+    block = np.zeros(210, dtype=np.uint8)
+    put_f16(orc, block, 208, 1.0)
+    block[192:208] = 1
+    block[0] = 0x05
+    block[128] = 0b0000_0001           # quarter 0, l=0: 5 | 1<<4 = 21 -> -11
+    block[35] = 0x02
+    block[131] = 0b0000_1000           # quarter 1, l=3: 2 | 2<<4 = 34 -> 2
+    block[7] |= 0x90
+    block[135] |= 0b0001_0000          # quarter 2, l=7: 9 | 16 = 25 -> -7
+    block[41] |= 0xF0
+    block[137] |= 0b1100_0000          # quarter 3, l=9: 15 | 48 = 63 -> 31
+    out = orc.dequant(Q6_K, block, 256)
+    assert out[0] == -11.0 and out[32 + 3] == 2.0 and out[64 + 7] == -7.0 and out[96 + 9] == 31.0
+    assert out[1] == -32.0
+    assert np.all(out[128:] == -32.0)
+
+
+def test_q6_k_negative_scales_flip_the_sign(orc):
+    """dequant.rs:412-425"""
+    block = np.zeros(210, dtype=np.uint8)
+    put_f16(orc, block, 208, 0.5)
+    block[192] = np.uint8(np.int8(-2).view(np.uint8))
+    out = orc.dequant(Q6_K, block, 256)
+    assert out[0] == 32.0 and out[16] == 0.0
+
+
+def test_q6_k_block_dots_recombine_to_the_row_dot(orc):
+    """The per-block integers sc0*dot0 + sc1*dot1 are exactly what dot_q6_k_i8 scales
+    (q8_acts.rs:336-343)."""
+    x = synth.normal_f32(512, 15)
+    d, s, q = orc.q8acts(x)
+    w = synth.q6_k_matrix(3, 512, 16)
+    dots = orc.block_dots(Q6_K, w, 3, 512, q)
+    wv = w.reshape(3, 2, 210)
+    for j in range(3):
+        total = np.float32(0.0)
+        for b in range(16):
+            dw = np.float32(wv[j, b // 8, 208:210].view(np.float16)[0])
+            total = np.float32(total + np.float32(np.float32(dw * d[b]) * np.float32(dots[0, j, b])))
+        assert total == np.float32(orc.dot_row(Q6_K, wv[j].reshape(-1), x, q8=True))
+    assert orc.expected_bytes(Q6_K, 512) == 420 and orc.expected_bytes(Q6_K, 300) == 0
+
+
 def test_fused_q4_k_dot_matches_dequant_then_dot(orc):
     """mod.rs:812-838"""
     block = np.zeros(144, dtype=np.uint8)
@@ -234,7 +279,7 @@ def kt_acts():
     return np.array([((i * 7 % 23) - 11.0) * 0.03 for i in range(N_IN)], dtype=np.float32)
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q4_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q4_K, Q6_K])
 def test_float_dot_kernels_match_the_dequantizer(orc, ty):
     """kernel_tests.rs:58-88"""
     x = kt_acts()
@@ -246,7 +291,7 @@ def test_float_dot_kernels_match_the_dequantizer(orc, ty):
     assert abs(got - want) <= 1e-4 * mag + 1e-5
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q4_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q4_K, Q6_K])
 def test_q8_activation_kernels_match_the_dequantizer(orc, ty):
     """kernel_tests.rs:90-121"""
     x = kt_acts()
