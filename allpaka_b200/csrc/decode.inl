@@ -618,14 +618,17 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
             for (uint32_t l = 0; l < n_launch; ++l) {
                 PlanLayer &L = P->L[l];
                 TokenLaunch T(c, P, m);  // fresh state: reads x[0], never flips buffers
-                T.first = false;         // the token counter stays: the words of the token above satisfy every wait
+                T.first = false;         // the token counter stays where the token above left it
                 T.in_token = false;
                 if (uses_xch(c)) {
-                    // as in the real token: Q|K|V, gate/up and the head gather the exchange in front of them
-                    T.n_xch = (int)(2 * l + (kind >= 2 ? 1 : 0));
-                    if (kind == 0 && l > 0) T.pending_xch = (int)(2 * l - 1);
-                    if (kind == 2) T.pending_xch = (int)(2 * l);
-                    if (kind == 4) T.pending_xch = (int)(2 * P->n_layers - 1);
+                    // As in the real token, Q|K|V, gate/up and the head gather an exchange in front of
+                    // them.  The slots keep the tagged words of the token's last two exchanges only,
+                    // so every gathering launch here reads the last one (its words are there on every
+                    // rank, whatever the ranks' relative progress) and the storing launches rewrite
+                    // the last two with their own numbers: no wait of this loop depends on a peer.
+                    const int last = T.per_token() - 1;
+                    T.n_xch = kind == 1 ? last - 1 : last;
+                    if ((kind == 0 && l > 0) || kind == 2 || kind == 4) T.pending_xch = last;
                 } else if (c->world == 1 && c->fuse_norm != 0 && (kind == 0 ? l > 0 : (kind == 2 || kind == 4))) {
                     T.have_sumsq = true;  // left in place by the token above
                 }

@@ -330,6 +330,14 @@ def test_peer_exchange_path_on_one_gpu(orc, monkeypatch, ty, m, wide):
         assert np.array_equal(a, b)
         for _ in range(6 if wide else 0):  # back to back: token counter, both parities of partial buffers and slots
             assert np.array_equal(g.decode_token_checked(req), a)
+        if self_xch == "1":
+            # each kind of launch replayed on its own finds the tagged words it waits for (a wait
+            # that ran out would come back as an error, quickly under this budget)
+            g.debug_set_wait_limit(40_000_000)
+            prof = g.decode_profile(req, reps=2)
+            g.debug_set_wait_limit(0)
+            assert all(v["ms"] > 0 for v in prof.values())
+            assert np.array_equal(g.decode_token_checked(req), a)
         if wide:  # tokens enqueued back to back with nothing of the host between them
             g.decode_replay(req, 40)
             assert np.array_equal(g.decode_token_checked(req), a)
