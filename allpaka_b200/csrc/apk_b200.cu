@@ -61,6 +61,7 @@ bool block_geom(uint32_t ty, uint32_t *be, uint32_t *bb) {
     // crates/allpaka-dtype/src/lib.rs:79-108
     if (ty == APK_TY_Q8_0) { *be = 32; *bb = 34; return true; }
     if (ty == APK_TY_Q4_K) { *be = 256; *bb = 144; return true; }
+    if (ty == APK_TY_Q6_K) { *be = 256; *bb = 210; return true; }
     return false;
 }
 
@@ -272,12 +273,13 @@ MvKernel pick_m(int m) {
 MvKernel pick_kernel(uint32_t ty, int m_eff, bool dump) {
     if (ty == APK_TY_Q8_0) return dump ? pick_m<TY_Q8_0, true>(m_eff) : pick_m<TY_Q8_0, false>(m_eff);
     if (ty == APK_TY_Q4_K) return dump ? pick_m<TY_Q4_K, true>(m_eff) : pick_m<TY_Q4_K, false>(m_eff);
+    if (ty == APK_TY_Q6_K) return dump ? pick_m<TY_Q6_K, true>(m_eff) : pick_m<TY_Q6_K, false>(m_eff);
     return nullptr;
 }
 
 int init_kernel_attrs(apk_ctx *c) {
     static const int ms[] = {1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 14, 16};
-    for (uint32_t ty : {APK_TY_Q8_0, APK_TY_Q4_K})
+    for (uint32_t ty : {APK_TY_Q8_0, APK_TY_Q4_K, APK_TY_Q6_K})
         for (int m : ms)
             for (int dump = 0; dump < 2; ++dump) {
                 MvKernel k = pick_kernel(ty, m, dump != 0);
@@ -287,7 +289,7 @@ int init_kernel_attrs(apk_ctx *c) {
     return APK_OK;
 }
 
-int ke_of(uint32_t ty) { return ty == APK_TY_Q8_0 ? 256 : 512; }
+int ke_of(uint32_t ty) { return ty == APK_TY_Q4_K ? 512 : 256; }
 
 // --------------------------------------------------------------- matrices
 
@@ -328,9 +330,10 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
     m->n_in = n_in;
     m->nb = (int)(n_in / 32);
     m->n_tiles = (int)((n_out + TILE_ROWS - 1) / TILE_ROWS);
-    const int kt = ty == APK_TY_Q8_0 ? Q8_KT : Q4_KT_SB * 8;
+    const int kt = ty == APK_TY_Q4_K ? Q4_KT_SB * 8 : Q8_KT;
     m->KS = (m->nb + kt - 1) / kt;
-    m->tile_bytes = ty == APK_TY_Q8_0 ? (uint32_t)m->nb * Q8_BLOCK_UNIT : (uint32_t)(m->nb / 8) * Q4_SB_UNIT;
+    m->tile_bytes = ty == APK_TY_Q8_0 ? (uint32_t)m->nb * Q8_BLOCK_UNIT
+                                      : (uint32_t)(m->nb / 8) * (ty == APK_TY_Q4_K ? Q4_SB_UNIT : Q6_SB_UNIT);
     m->bytes = (size_t)m->n_tiles * m->tile_bytes;
     CUDA_TRY(cudaMalloc((void **)&m->d, m->bytes));
     CUDA_TRY(cudaMemsetAsync(m->d, 0, m->bytes, c->stream));
@@ -371,8 +374,10 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
             const unsigned blocks = (unsigned)((total + threads - 1) / threads);
             if (ty == APK_TY_Q8_0)
                 repack_q8_0_kernel<<<blocks, threads, 0, c->stream>>>(rp);
-            else
+            else if (ty == APK_TY_Q4_K)
                 repack_q4_k_kernel<<<blocks, threads, 0, c->stream>>>(rp);
+            else
+                repack_q6_k_kernel<<<blocks, threads, 0, c->stream>>>(rp);
             CUDA_TRY(cudaGetLastError());
             c->st.launches++;
             CUDA_TRY(cudaStreamSynchronize(c->stream));  // staging is reused by the next slab
@@ -1164,14 +1169,18 @@ int apk_debug_synth_matrix(apk_ctx *c, void *w, uint32_t ty, uint32_t n_out, uin
     CUDA_TRY(cudaSetDevice(c->device));
     APK_TRY(check_host_matrix(c, "synth", w, ty, n_out, n_in));
     const size_t bytes = host_bytes(ty, n_out, n_in);
-    const size_t n_blocks = bytes / (ty == APK_TY_Q8_0 ? 34 : 144);
+    uint32_t be = 0, bb = 0;
+    block_geom(ty, &be, &bb);
+    const size_t n_blocks = bytes / bb;
     uint8_t *d = nullptr;
     CUDA_TRY(cudaMalloc((void **)&d, bytes));
     const unsigned blocks = (unsigned)((n_blocks + 255) / 256);
     if (ty == APK_TY_Q8_0)
         synth_q8_0_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
-    else
+    else if (ty == APK_TY_Q4_K)
         synth_q4_k_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
+    else
+        synth_q6_k_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
     c->st.launches++;
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess && write_host) e = cudaMemcpyAsync(w, d, bytes, cudaMemcpyDeviceToHost, c->stream);
@@ -1295,3 +1304,4 @@ int apk_dist_init(apk_ctx *c, int rank, int world, const void *unique_id) {
 
 #include "decode.inl"
 #include "noalloc.inl"
+#include "gguf.inl"

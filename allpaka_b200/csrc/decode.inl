@@ -464,7 +464,7 @@ int launch_embed(apk_ctx *c, Plan *P, const uint32_t *token_dev, uint32_t token,
     ep.token = token;
     ep.x = x;
     ep.err = c->d_err;
-    const int threads = E->ty == APK_TY_Q8_0 ? E->nb * 8 : (E->nb / 8) * 32;
+    const int threads = E->ty == APK_TY_Q8_0 ? E->nb * 8 : (E->nb / 8) * (E->ty == APK_TY_Q4_K ? 32 : 16);
     embed_row_kernel<<<(threads + 255) / 256, 256, 0, c->stream>>>(ep);
     CUDA_TRY(cudaGetLastError());
     c->st.launches++;
@@ -609,7 +609,9 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
     CUDA_TRY(cudaGraphLaunch(P->exec[m][r->argmax ? 1 : 0], c->stream));
     APK_TRY(finish(c));
     auto orig_bytes = [](const DevMatrix *W) {
-        return (double)W->n_out * (W->n_in / (W->ty == APK_TY_Q8_0 ? 32 : 256)) * (W->ty == APK_TY_Q8_0 ? 34 : 144);
+        uint32_t be = 32, bb = 34;
+        block_geom(W->ty, &be, &bb);
+        return (double)W->n_out * (W->n_in / be) * bb;
     };
     for (int kind = 0; kind < 5; ++kind) {
         const uint32_t n_launch = kind == 4 ? 1 : P->n_layers;
@@ -654,7 +656,7 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
         const DevMatrix *W = kind == 0 ? L0.qkv : kind == 1 ? L0.wo : kind == 2 ? L0.gateup : kind == 3 ? L0.down : P->head;
         // weights as stored in the GGUF file (padding rows of the tiled stream are not counted)
         double wb = orig_bytes(W);
-        if (kind == 2) wb = 2.0 * (double)P->ffn_l * (H / 32) * (W->ty == APK_TY_Q8_0 ? 34 : 144 / 8.0);
+        if (kind == 2) wb = 2.0 * (double)P->ffn_l * (H / 32) * (W->ty == APK_TY_Q8_0 ? 34 : (W->ty == APK_TY_Q4_K ? 144 : 210) / 8.0);
         const double in_b = (double)m * W->n_in * 4.0;
         const double out_b = kind == 2 ? (double)m * P->ffn_l * 4.0 : (double)m * W->n_out * 4.0;
         bytes[kind] = wb + in_b + out_b;

@@ -2,7 +2,7 @@
 //
 // Data layout in HBM ("tiled stream").  A [n_out, n_in] matrix is cut into
 // tiles of 128 output rows; a tile's K extent is cut into K-steps of 256
-// elements (Q8_0: 8 blocks) or 512 elements (Q4_K: 2 super-blocks).  One
+// elements (Q8_0: 8 blocks; Q6_K: 1 super-block) or 512 elements (Q4_K: 2 super-blocks).  One
 // (tile, K-step) "unit" is ONE contiguous span of at most 36 KiB that a single
 // bulk async copy (cp.async.bulk + mbarrier complete_tx) brings into shared
 // memory.  Inside a unit the bytes sit in the order the tensor-core fragments
@@ -21,6 +21,11 @@
 //        gives the low-nibble sub-block, shifting the high one), 4096 B, then the header
 //        with the 6-bit scales and mins already split out into bytes: {d, dmin} f16 pairs
 //        [g][4 rows], scales [g][half of the sub-blocks][4 rows][4], mins likewise, 640 B
+//   Q6_K unit (one super-block): per row group, the ql bytes as nibble fragments like Q4_K's
+//        (chunk (half, byte group c): low nibbles = quarter c, high = quarter c + 2 of that half),
+//        4096 B; the qh bytes of each half in the same fragment order (quarter qi takes bits
+//        2qi, 2qi+1 of every byte), 2048 B; the sixteen int8 sub-block scales [g][4 rows][16],
+//        512 B; the f16 d [g][4 rows], 64 B.  6720 B = 32 rows x 210 B: nothing is widened.
 //
 // Work split ("stream-K"): the flat unit sequence of the whole matrix is cut
 // into equal contiguous ranges, one per CTA (one CTA per SM), so every SM
@@ -44,7 +49,9 @@ constexpr int Q8_BLOCK_UNIT = 4352;  // 128 rows * 34 B
 constexpr int Q4_SB_RG = 4736;       // one row group of a super-block: 4096 B nibbles + 640 B header
 constexpr int Q4_SB_UNIT = 4 * Q4_SB_RG;  // 128 rows: 18944 B (18432 B of GGUF blocks + split scale bytes)
 constexpr int Q4_KT_SB = 2;          // Q4_K super-blocks per K-step (512 elements)
-__host__ __device__ constexpr int stage_w_bytes(int ty) { return ty == 8 ? 8 * 4352 : 2 * 18944; }  // one full K-step of weights
+constexpr int Q6_SB_RG = 6720;       // one row group of a Q6_K super-block: 4096 B ql + 2048 B qh + 512 B scales + 64 B d
+constexpr int Q6_SB_UNIT = 4 * Q6_SB_RG;  // 128 rows: 26880 B = 128 * 210 B
+__host__ __device__ constexpr int stage_w_bytes(int ty) { return ty == 8 ? 8 * 4352 : (ty == 14 ? 26880 : 2 * 18944); }  // one full K-step of weights
 constexpr int N_CONSUMER_WARPS = 16; // 4 row groups x 4 quarters of a K-step
 constexpr int K_SPLIT = 4;
 constexpr int N_CONSUMERS = N_CONSUMER_WARPS * 32;
@@ -55,6 +62,7 @@ constexpr int MAX_M_EFF = 16;
 constexpr int MAX_STAGES = 8;
 constexpr int TY_Q8_0 = 8;
 constexpr int TY_Q4_K = 12;
+constexpr int TY_Q6_K = 14;
 
 // Error words written by kernels (never a trap): which bounded wait gave up.  The matvec kernel
 // records kind | site << 4 | launch number << 8 (the first one to give up wins): sites 1-3 the
@@ -117,7 +125,7 @@ struct XchSeq {
 //   sum [block][mp] f32
 struct ActLayout {
     uint8_t *base;
-    int ke;        // elements per K-step: 256 (Q8_0 consumer) or 512 (Q4_K consumer)
+    int ke;        // elements per K-step: 256 (Q8_0 or Q6_K consumer) or 512 (Q4_K consumer)
     int m_eff;     // rows in the record (2 per token in two-level mode)
     __host__ __device__ int kt() const { return ke >> 5; }
     __host__ __device__ int mp() const { return (m_eff + 1) & ~1; }
@@ -350,6 +358,40 @@ __device__ __forceinline__ void mma_block_s8_acc(int (&d)[4], const uint4 &a, ui
         "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
         : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+}
+
+// Half of that: 16 rows x 16 k-values x 8 columns, accumulating.  a0/a1 are registers 0, 1
+// (or 2, 3) of the k32 A fragment, b the matching B register.
+__device__ __forceinline__ void mma_half_s8_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(b));
+}
+
+// Q6_K: the signed 6-bit values of quarter qi (0..3) of one half as int8 fragment words:
+// (ql nibble | two qh bits << 4) - 32, per byte (crates/allpaka-backend/src/quantmat/q8_acts.rs:329-333).
+// ql: the chunk of byte group qi & 1; qh: the half's chunk.
+__device__ __forceinline__ uint4 q6_k_unpack(const uint4 &ql, const uint4 &qh, int qi) {
+    const int sh = 2 * qi;
+    uint4 v;
+    if (qi & 2) {
+        v.x = (ql.x >> 4) & 0x0f0f0f0fu; v.y = (ql.y >> 4) & 0x0f0f0f0fu;
+        v.z = (ql.z >> 4) & 0x0f0f0f0fu; v.w = (ql.w >> 4) & 0x0f0f0f0fu;
+    } else {
+        v.x = ql.x & 0x0f0f0f0fu; v.y = ql.y & 0x0f0f0f0fu; v.z = ql.z & 0x0f0f0f0fu; v.w = ql.w & 0x0f0f0f0fu;
+    }
+    v.x = __vsub4(v.x | (((qh.x >> sh) & 0x03030303u) << 4), 0x20202020u);
+    v.y = __vsub4(v.y | (((qh.y >> sh) & 0x03030303u) << 4), 0x20202020u);
+    v.z = __vsub4(v.z | (((qh.z >> sh) & 0x03030303u) << 4), 0x20202020u);
+    v.w = __vsub4(v.w | (((qh.w >> sh) & 0x03030303u) << 4), 0x20202020u);
+    return v;
+}
+// byte i (0..15) of a 16-byte vector as a signed value
+__device__ __forceinline__ int s8_of(const uint4 &v, int i) {
+    const int w = i >> 2;
+    const uint32_t x = w == 0 ? v.x : (w == 1 ? v.y : (w == 2 ? v.z : v.w));
+    return (int)(x << (24 - 8 * (i & 3))) >> 24;
 }
 
 // ----------------------------------------------------- activation quantiser
@@ -676,6 +718,44 @@ __global__ void repack_q4_k_kernel(RepackParams p) {
     }
 }
 
+// One thread per (row, super-block): 210 source bytes -> nibble and high-bit fragments, scales, d.
+__global__ void repack_q6_k_kernel(RepackParams p) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int nsb = p.nb / 8;
+    const size_t total = (size_t)p.src_rows * nsb;
+    if (idx >= total) return;
+    const int sb = (int)(idx % nsb), r = (int)(idx / nsb);
+    const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)sb * 210;
+    const int dr = map_row(p, r);
+    const int tile = dr / TILE_ROWS, rt = dr % TILE_ROWS;
+    int rg, h16, g, upper;
+    frag_pos(rt, rg, h16, g, upper);
+    uint8_t *base = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)sb * Q6_SB_UNIT + (size_t)rg * Q6_SB_RG;
+    auto word = [](const uint8_t *q) {
+        return (uint32_t)q[0] | ((uint32_t)q[1] << 8) | ((uint32_t)q[2] << 16) | ((uint32_t)q[3] << 24);
+    };
+    // ql: chunk (half, c) holds ql[64*half + 32*c .. +31]; word w -> lane column w%4, k-half w/4
+    for (int pr = 0; pr < 4; ++pr) {
+        uint8_t *frag = base + (size_t)((pr * 2 + h16) * 32) * 16;
+        for (int w = 0; w < 8; ++w) {
+            const int lane = g * 4 + (w & 3), reg = 2 * (w >> 2) + upper;
+            *reinterpret_cast<uint32_t *>(frag + lane * 16 + reg * 4) = word(s + pr * 32 + 4 * w);
+        }
+    }
+    // qh: chunk `half` holds qh[32*half .. +31] in the same order
+    for (int half = 0; half < 2; ++half) {
+        uint8_t *frag = base + 4096 + (size_t)((half * 2 + h16) * 32) * 16;
+        for (int w = 0; w < 8; ++w) {
+            const int lane = g * 4 + (w & 3), reg = 2 * (w >> 2) + upper;
+            *reinterpret_cast<uint32_t *>(frag + lane * 16 + reg * 4) = word(s + 128 + half * 32 + 4 * w);
+        }
+    }
+    const int row4 = h16 * 2 + upper;  // which of rows g, g+8, g+16, g+24
+    uint8_t *sc = base + 6144 + (g * 4 + row4) * 16;
+    for (int j = 0; j < 16; ++j) sc[j] = s[192 + j];
+    *reinterpret_cast<uint16_t *>(base + 6656 + (g * 4 + row4) * 2) = (uint16_t)(s[208] | (s[209] << 8));
+}
+
 // ------------------------------------------------------ decode attention over the f16 KV cache
 //
 // What sits between the Q|K|V matvec and the output projection of a decoder layer
@@ -822,6 +902,7 @@ __global__ void __launch_bounds__(TILE_ROWS) attn_combine_kernel(AttnParams p, i
 // The embedding row of a token, dequantised straight out of the tiled stream (the LM head of a
 // model with tied embeddings is the same resident matrix): x[i] = d * q for Q8_0
 // (crates/allpaka-gguf/src/dequant.rs:93-126), d*sc*q - dmin*mn for Q4_K (dequant.rs:211-231),
+// d*sc*(q-32) for Q6_K (dequant.rs:271-296),
 // with the reference's operation order (two roundings, no fused multiply-add).
 struct EmbedParams {
     const uint8_t *W;         // tiled stream of the [vocab, hidden] table
@@ -856,6 +937,29 @@ __global__ void __launch_bounds__(256) embed_row_kernel(EmbedParams p) {
         o.z = __fmul_rn(d, (float)(int8_t)((v >> 16) & 0xffu));
         o.w = __fmul_rn(d, (float)(int8_t)(v >> 24));
         *reinterpret_cast<float4 *>(p.x + b * 32 + 4 * w) = o;
+    } else if (p.ty == TY_Q6_K) {
+        // one thread per (super-block, half, 4-byte word): four values of each of the half's quarters,
+        // x = d * sc * q in that order (dequant.rs:290-293)
+        const int sb = idx >> 4, half = (idx >> 3) & 1, w = idx & 7;
+        if (sb >= p.nb / 8) return;
+        const uint8_t *base = p.W + (size_t)tile * p.tile_bytes + (size_t)sb * Q6_SB_UNIT + (size_t)rg * Q6_SB_RG;
+        const int lane = g * 4 + (w & 3), reg = 2 * (w >> 2) + upper, row4 = h16 * 2 + upper;
+        const uint32_t qh = *reinterpret_cast<const uint32_t *>(base + 4096 + (size_t)((half * 2 + h16) * 32) * 16 + lane * 16 + reg * 4);
+        const float d = __half2float(*reinterpret_cast<const __half *>(base + 6656 + (g * 4 + row4) * 2));
+        const int8_t *sc = reinterpret_cast<const int8_t *>(base + 6144 + (g * 4 + row4) * 16) + half * 8;
+        const int is = w >> 2;  // elements 4w..4w+3 of a quarter lie in its 16-element half `is`
+        float *o = p.x + sb * 256 + half * 128 + 4 * w;
+#pragma unroll
+        for (int qi = 0; qi < 4; ++qi) {
+            const uint32_t ql = *reinterpret_cast<const uint32_t *>(base + (size_t)(((half * 2 + (qi & 1)) * 2 + h16) * 32) * 16 + lane * 16 + reg * 4);
+            const float dsc = __fmul_rn(d, (float)sc[2 * qi + is]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t nib = ((qi & 2) ? (ql >> (8 * k + 4)) : (ql >> (8 * k))) & 0xfu;
+                const int q = (int)(nib | (((qh >> (8 * k + 2 * qi)) & 3u) << 4)) - 32;
+                o[32 * qi + k] = __fmul_rn(dsc, (float)q);
+            }
+        }
     } else {
         // one thread per (super-block, pair of sub-blocks, 4-byte word of nibbles)
         const int sb = idx >> 5, pr = (idx >> 3) & 3, w = idx & 7;
@@ -920,6 +1024,7 @@ __global__ void __launch_bounds__(128) chain_advance_kernel(ChainParams p) {
 // on the device so a multi-gigabyte synthetic model needs no host generation.
 // Q8_0: quants uniform in [-127,127], scale f16(|N(0,0.02)|/127).
 // Q4_K: nibbles, 6-bit scales and mins uniform, d and dmin f16(|N(0,0.002)|).
+// Q6_K: see synth_q6_k_kernel.
 __device__ __forceinline__ uint64_t splitmix64(uint64_t x) {
     x += 0x9E3779B97F4A7C15ull;
     x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
@@ -965,6 +1070,21 @@ __global__ void synth_q4_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) 
         o[4 + i * 4 + 0] = (uint8_t)h; o[4 + i * 4 + 1] = (uint8_t)(h >> 8);
         o[4 + i * 4 + 2] = (uint8_t)(h >> 16); o[4 + i * 4 + 3] = (uint8_t)(h >> 24);
     }
+}
+
+// Q6_K: every ql/qh byte and every int8 sub-block scale uniform, d f16(|N(0,0.0005)|).
+__global__ void synth_q6_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    uint8_t *o = dst + b * 210;
+    const uint64_t base = splitmix64(seed) ^ (b * 0x9E3779B97F4A7C15ull);
+    for (int i = 0; i < 208 / 4; ++i) {
+        const uint32_t h = (uint32_t)splitmix64(base + (uint64_t)i + 1);
+        o[i * 4 + 0] = (uint8_t)h; o[i * 4 + 1] = (uint8_t)(h >> 8);
+        o[i * 4 + 2] = (uint8_t)(h >> 16); o[i * 4 + 3] = (uint8_t)(h >> 24);
+    }
+    const unsigned short d = __half_as_ushort(__float2half_rn(absnormal(splitmix64(base ^ 0x61ull), 0.0005f)));
+    o[208] = (uint8_t)(d & 0xff); o[209] = (uint8_t)(d >> 8);
 }
 
 // ------------------------------------------------------------ the matvec
@@ -1279,7 +1399,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     const uint32_t G = gridDim.x;
     const UnitOrder order(blockIdx.x * U / G, (blockIdx.x + 1) * U / G, (uint32_t)p.KS);
     const int n_total = order.n_total;
-    const int kt = (TY == TY_Q8_0) ? Q8_KT : Q4_KT_SB * 8;  // 32-element blocks per full K-step
+    const int kt = (TY == TY_Q4_K) ? Q4_KT_SB * 8 : Q8_KT;  // 32-element blocks per full K-step
 
     if (warp == N_CONSUMER_WARPS) {
         // ------------------------------------------------ producer (one lane)
@@ -1295,6 +1415,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 if (TY == TY_Q8_0) {
                     wbytes = (uint32_t)kb * Q8_BLOCK_UNIT;
                     woff = (uint32_t)ks * Q8_KT * Q8_BLOCK_UNIT;
+                } else if (TY == TY_Q6_K) {
+                    wbytes = (uint32_t)Q6_SB_UNIT;
+                    woff = (uint32_t)ks * Q6_SB_UNIT;
                 } else {
                     wbytes = (uint32_t)(kb / 8) * Q4_SB_UNIT;
                     woff = (uint32_t)ks * Q4_KT_SB * Q4_SB_UNIT;
@@ -1728,6 +1851,58 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                             if (DUMP) dumpc(d, ks * Q8_KT + cb);
                         }
                     }
+                } else if (TY == TY_Q6_K) {
+                    // One super-block per K-step.  Sub-block scales cover 16 elements, so a block's
+                    // dot is two 16-deep mmas (one per half of the block, each in its own chain) and
+                    // sc0*dot0 + sc1*dot1 is formed in integers: exactly what the reference forms in
+                    // f32 (q8_acts.rs:338-342; |value| < 2^24).
+                    const uint8_t *base = sw + rgc * Q6_SB_RG;
+                    const uint4 scl = *reinterpret_cast<const uint4 *>(base + 6144 + (lg * 4 + 2 * h16c) * 16);      // row lg
+                    const uint4 sch = *reinterpret_cast<const uint4 *>(base + 6144 + (lg * 4 + 2 * h16c + 1) * 16);  // row lg+8
+                    const __half2 dd = *reinterpret_cast<const __half2 *>(base + 6656 + (lg * 4 + 2 * h16c) * 2);
+                    const float dwl = __low2float(dd), dwh = __high2float(dd);
+#pragma unroll
+                    for (int ch = 0; ch < 8 / BPC; ++ch) {
+                        const int xs = ch * BPC + my_blk;
+                        const uint8_t *xb = sa + xs * (32 * M) + my_tok * 16 + 4 * lt;
+                        const uint32_t xb0 = *reinterpret_cast<const uint32_t *>(xb);
+                        const uint32_t xb1 = *reinterpret_cast<const uint32_t *>(xb + 16 * M);
+                        int d[4] = {0, 0, 0, 0}, e[4] = {0, 0, 0, 0};
+#pragma unroll
+                        for (int i = 0; i < BPC; ++i) {
+                            const int blk = ch * BPC + i, half = blk >> 2, qi = blk & 3;
+                            const uint4 ql = *reinterpret_cast<const uint4 *>(base + (((half * 2 + (qi & 1)) * 2 + h16c) * 32 + lane) * 16);
+                            const uint4 qh = *reinterpret_cast<const uint4 *>(base + 4096 + ((half * 2 + h16c) * 32 + lane) * 16);
+                            const uint4 a = q6_k_unpack(ql, qh, qi);
+                            mma_half_s8_acc(d, a.x, a.y, my_blk == i ? xb0 : 0u);
+                            mma_half_s8_acc(e, a.z, a.w, my_blk == i ? xb1 : 0u);
+                        }
+                        int I[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int b = ch * BPC + (2 * lt + (i & 1)) / MP2;
+                            I[i] = (i >> 1) ? s8_of(sch, 2 * b) * d[i] + s8_of(sch, 2 * b + 1) * e[i]
+                                            : s8_of(scl, 2 * b) * d[i] + s8_of(scl, 2 * b + 1) * e[i];
+                        }
+                        if (MP2 > 1 && p.two_level) {
+                            // columns 2lt, 2lt+1 are the two digits of one token of one block, d2 = d1 / 256
+                            const int c = 2 * lt;
+                            const int b = ch * BPC + c / MP2, tok = c % MP2 + 1;
+                            const float dx = ad[b * MP + tok];
+                            cacc[0] = fmaf(__fmul_rn(dwl, dx), (float)(((long long)I[0] << 8) + I[1]), cacc[0]);
+                            cacc[2] = fmaf(__fmul_rn(dwh, dx), (float)(((long long)I[2] << 8) + I[3]), cacc[2]);
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int c = 2 * lt + (i & 1);
+                                const int b = ch * BPC + c / MP2;
+                                const int tok = (c % MP2) < M ? (c % MP2) : M - 1;
+                                // total += d * acts.d[blk] * (sc0*dot0 + sc1*dot1)  (q8_acts.rs:342)
+                                cacc[i] = fmaf(__fmul_rn((i >> 1) ? dwh : dwl, ad[b * MP + tok]), (float)I[i], cacc[i]);
+                            }
+                        }
+                        if (DUMP) dumpc(I, ks * 8 + ch * BPC);
+                    }
                 } else {
 #pragma unroll
                     for (int sbi = 0; sbi < Q4_KT_SB; ++sbi) {
@@ -1851,6 +2026,71 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     block(kq + K_SPLIT);
                 } else {
                     for (int b = kq; b < kb; b += K_SPLIT) block(b);
+                }
+            } else if (TY == TY_Q6_K) {
+                // this warp: quarter kq of both halves of the super-block (blocks kq and kq + 4)
+                const uint8_t *base = sw + rg * Q6_SB_RG;
+                const uint2 ddw = *reinterpret_cast<const uint2 *>(base + 6656 + lg * 8);  // d of rows lg, lg+8, lg+16, lg+24
+                const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&ddw.x));
+                const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&ddw.y));
+                const float dwr[4] = {f01.x, f01.y, f23.x, f23.y};
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int b = half * 4 + kq;
+                    uint4 a[2];
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint4 ql = *reinterpret_cast<const uint4 *>(base + (((half * 2 + (kq & 1)) * 2 + h) * 32 + lane) * 16);
+                        const uint4 qh = *reinterpret_cast<const uint4 *>(base + 4096 + ((half * 2 + h) * 32 + lane) * 16);
+                        a[h] = q6_k_unpack(ql, qh, kq);
+                    }
+                    int s0[4], s1[4];  // the block's two sub-block scales for rows lg, lg+8, lg+16, lg+24
+#pragma unroll
+                    for (int r4 = 0; r4 < 4; ++r4) {
+                        const uint32_t w = *reinterpret_cast<const unsigned short *>(base + 6144 + (lg * 4 + r4) * 16 + 2 * b);
+                        s0[r4] = (int)(w << 24) >> 24;
+                        s1[r4] = (int)(w << 16) >> 24;
+                    }
+                    const uint8_t *xb = sa + b * (32 * M);
+                    const float *xd = ad + b * MP;
+#pragma unroll
+                    for (int j = 0; j < NG; ++j) {
+                        // rows past M are clamped to row M-1: computed, never stored
+                        const int tb = min(8 * j + lg, M - 1);
+                        const int t0 = min(8 * j + 2 * lt, M - 1), t1 = min(8 * j + 2 * lt + 1, M - 1);
+                        const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xb + tb * 16 + 4 * lt);
+                        const uint32_t b1 = *reinterpret_cast<const uint32_t *>(xb + 16 * M + tb * 16 + 4 * lt);
+                        int I[2][4];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            int d[4] = {0, 0, 0, 0}, e[4] = {0, 0, 0, 0};
+                            mma_half_s8_acc(d, a[h].x, a[h].y, b0);
+                            mma_half_s8_acc(e, a[h].z, a[h].w, b1);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) I[h][i] = s0[2 * h + (i >> 1)] * d[i] + s1[2 * h + (i >> 1)] * e[i];
+                        }
+                        const float dx0 = xd[t0], dx1 = xd[t1];
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) {
+                            if (M > 1 && p.two_level) {
+                                // columns 2lt, 2lt+1 are the two digits of one token, d2 = d1 / 256
+#pragma unroll
+                                for (int i = 0; i < 4; i += 2)
+                                    acc[h][j][i] = fmaf(__fmul_rn(dwr[2 * h + (i >> 1)], dx1), (float)(((long long)I[h][i] << 8) + I[h][i + 1]),
+                                                        acc[h][j][i]);
+                            } else {
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    if (M == 1 && (i & 1)) continue;  // a single activation row has no odd column
+                                    acc[h][j][i] = fmaf(__fmul_rn(dwr[2 * h + (i >> 1)], (i & 1) ? dx1 : dx0), (float)I[h][i], acc[h][j][i]);
+                                }
+                            }
+                        }
+                        if (DUMP) {
+                            dump4(I[0], 0, j, ks * 8 + b);
+                            dump4(I[1], 1, j, ks * 8 + b);
+                        }
+                    }
                 }
             } else {
                 // this warp: super-block kq/2 of the K-step, sub-blocks 4*(kq&1) .. +3 (pairs 2*(kq&1), +1)

@@ -25,6 +25,7 @@ LIB_PATH = os.path.join(_HERE, "libapk_b200.so")
 # GGML type ids (crates/allpaka-dtype/src/lib.rs:61-75)
 Q8_0 = 8
 Q4_K = 12
+Q6_K = 14
 
 ACT_Q8, ACT_F32, ACT_AUTO = 0, 1, 2
 ATTN_IDENTITY = 1
@@ -120,6 +121,9 @@ EXPORTS = (
     "apk_debug_token_records", "apk_debug_set_wait_limit", "apk_debug_xch_timeout",
     "apk_bench_ring", "apk_dist_set_exchange", "apk_decode_greedy",
     "apk_kv_create", "apk_kv_destroy", "apk_kv_read", "apk_kv_write", "apk_attend",
+    "apk_gguf_open", "apk_gguf_close", "apk_gguf_n_tensors", "apk_gguf_tensor_at", "apk_gguf_find",
+    "apk_gguf_architecture", "apk_gguf_meta_u32", "apk_gguf_meta_f32", "apk_gguf_meta_str", "apk_gguf_mapping",
+    "apk_model_open", "apk_model_get_info", "apk_model_token_req", "apk_model_attach", "apk_model_close",
 )
 
 _lib = None
@@ -488,21 +492,26 @@ class Gpu:
         :class:`TokenRows` (argmax on and m > 1, as the reference returns for a verify batch).
         With ``want_hidden`` the output-normed rows come along in every form: ``(result, hidden)``."""
         creq, keep = self._token_req(req)
-        vocab = req.output[2]
-        rows = want_hidden or (req.argmax and req.m > 1)
-        hidden = np.empty((req.m, req.hidden), dtype=np.float32) if rows else None
-        if req.argmax:
-            res = np.empty(req.m, dtype=np.uint32)
+        return self.decode_request(creq, want_hidden)
+
+    def decode_request(self, creq: "_TokenReq", want_hidden: bool = False):
+        """``apk_decode_token`` on a C request as it stands (e.g. a model's template with the input,
+        rope rows, cache and position filled in)."""
+        m, argmax = int(creq.m), bool(creq.argmax)
+        rows = want_hidden or (argmax and m > 1)
+        hidden = np.empty((m, int(creq.hidden)), dtype=np.float32) if rows else None
+        if argmax:
+            res = np.empty(m, dtype=np.uint32)
             out = _TokenOut(None, res.ctypes.data, _ptr(hidden))
         else:
-            res = np.empty((req.m, vocab), dtype=np.float32)
+            res = np.empty((m, int(creq.output.n_out)), dtype=np.float32)
             out = _TokenOut(res.ctypes.data, None, _ptr(hidden))
         rc = self._l.apk_decode_token(self._h, C.byref(creq), C.byref(out))
         if rc > 0:
             raise DecodeDecline(rc, self._err())
         if rc < 0:
             raise GpuError(rc, self._err())
-        if req.argmax and req.m > 1:
+        if argmax and m > 1:
             return TokenRows(res, hidden)
         return (res, hidden) if want_hidden else res
 

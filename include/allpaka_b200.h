@@ -52,6 +52,7 @@ extern "C" {
 /* GGML type ids (crates/allpaka-dtype/src/lib.rs:61-75). */
 #define APK_TY_Q8_0 8u
 #define APK_TY_Q4_K 12u
+#define APK_TY_Q6_K 14u
 
 /* How activations meet the integer weights.  The reference picks this by call
  * site, not by dtype (crates/allpaka-backend/src/quantmat/mod.rs):
@@ -387,6 +388,57 @@ void apk_stats(apk_ctx *ctx, apk_stats_t *out);
 /* Human-readable reason for the last non-zero status on this thread
  * (gpu::init_error, stub.rs:51-53; DecodeDecline{stage,reason} gpu/types.rs:247-252). */
 const char *apk_last_error(apk_ctx *ctx);
+
+/* ---- model files ---------------------------------------------------------
+ * GGUF on the host: header, metadata and tensor table parsed out of a read-only mapping of the
+ * file (crates/allpaka-gguf/src/metadata.rs:194-297, tensors.rs:183-217).  Versions >= 2;
+ * general.alignment honoured (default 32); arrays other than short u32 ones are walked over.
+ * Tensor bytes are pointers into the mapping: attach it (apk_gguf_mapping + apk_attach, or
+ * apk_model_attach) and hand them to any entry point above.  No GPU is needed to read a file. */
+typedef struct apk_gguf apk_gguf;
+typedef struct {
+    const char *name;   /* owned by the file handle */
+    uint32_t ty;        /* GGML type id */
+    uint32_t n_dims;
+    uint64_t dims[4];   /* dims[0] is the row length (n_in), dims[1] the rows (n_out) */
+    const void *data;
+    uint64_t n_bytes;   /* 0 for types this library has no block geometry for */
+} apk_gguf_tensor;
+int apk_gguf_open(const char *path, apk_gguf **out);
+void apk_gguf_close(apk_gguf *f);
+uint64_t apk_gguf_n_tensors(const apk_gguf *f);
+int apk_gguf_tensor_at(const apk_gguf *f, uint64_t i, apk_gguf_tensor *out);
+int apk_gguf_find(const apk_gguf *f, const char *name, apk_gguf_tensor *out); /* GgufFile::tensor + data */
+const char *apk_gguf_architecture(const apk_gguf *f);
+/* metadata by full key (GgufFile::meta_u32 / meta_f32 / meta_str, tensors.rs:143-166);
+ * APK_DECLINE_INVALID_STATE / NULL when absent or of another kind */
+int apk_gguf_meta_u32(const apk_gguf *f, const char *key, uint32_t *out);
+int apk_gguf_meta_f32(const apk_gguf *f, const char *key, float *out);
+const char *apk_gguf_meta_str(const apk_gguf *f, const char *key);
+const void *apk_gguf_mapping(const apk_gguf *f, uint64_t *len);
+
+/* The dense-decoder view of a file: Config::from_gguf (crates/allpaka-model/src/config.rs:184-310)
+ * and the tensor binding of Model::load (model/loader.rs:100-260) for attention + dense-FFN blocks.
+ * Every matrix is checked against the shape the graph expects (qmat, loader.rs:558-569); norm
+ * vectors must be F32 (norm_raw, loader.rs:573-580); llama / mistral files get the rows of every
+ * Q and K head reordered for NEOX rotation (neox_order + reorder_head_rows, loader.rs:366-426;
+ * ALLPAKA_ROPE_NORM=1 declines that); mixture-of-experts, projection biases and other block kinds
+ * are declined.  The file handle must outlive the model. */
+typedef struct apk_model apk_model;
+typedef struct {
+    uint32_t n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, rot_dim;
+    float eps, rope_base;
+    int has_qk_norm, neox_reordered, tied;
+} apk_model_info;
+int apk_model_open(apk_gguf *f, apk_model **out);
+const apk_model_info *apk_model_get_info(const apk_model *m);
+/* A request template over the model's tensors (layers, norms, LM head, embedding table, shapes,
+ * causal attention, scale = 1/sqrt(head_dim), m = 1); the caller adds the input (x or token_id),
+ * the rope rows, the cache and the position. */
+int apk_model_token_req(const apk_model *m, apk_token_req *req);
+/* gpu::attach of the file's mapping and of every reordered copy (loader.rs:62-98, 421). */
+int apk_model_attach(apk_ctx *ctx, apk_model *m);
+void apk_model_close(apk_model *m);
 
 /* ---- tensor parallelism over one NVLink domain ----------------------------
  * No counterpart in the reference (its only multi-device scheme is layer
