@@ -161,6 +161,7 @@ namespace {
 
 struct PlanLayer {
     DevMatrix *qkv = nullptr, *wo = nullptr, *gateup = nullptr, *down = nullptr;
+    DevMatrix *v = nullptr;  // V as a matrix of its own when its type differs from Q and K (qkv is then Q | K)
     const float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;  // device
 };
 
@@ -451,12 +452,12 @@ int resolve_plain(apk_ctx *c, const char *what, const void *w, uint32_t ty, uint
 // tensor parallelism this rank's Q heads, then its K heads, then its V heads.
 int resolve_qkv(apk_ctx *c, uint32_t ty, const void *wq, const void *wk, const void *wv, uint32_t hidden,
                 uint32_t n_q, uint32_t n_kv, DevMatrix **out) {
-    MatKey key(KIND_QKV, wq, wk, wv, ty, n_q + 2 * n_kv, hidden, SHARD_ROWS, shard_tag(c, SHARD_ROWS));
+    MatKey key(KIND_QKV, wq, wk, wv, ty, n_q + (wv ? 2 : 1) * n_kv, hidden, SHARD_ROWS, shard_tag(c, SHARD_ROWS));
     auto it = c->mats.find(key);
     if (it != c->mats.end()) { *out = it->second.get(); return APK_OK; }
     APK_TRY(check_host_matrix(c, "attn wq", wq, ty, n_q, hidden));
     APK_TRY(check_host_matrix(c, "attn wk", wk, ty, n_kv, hidden));
-    APK_TRY(check_host_matrix(c, "attn wv", wv, ty, n_kv, hidden));
+    if (wv) APK_TRY(check_host_matrix(c, "attn wv", wv, ty, n_kv, hidden));  // (null: Q | K only, V is a matrix of its own)
     uint32_t sq[4], sk[4];
     APK_TRY(shard_plan(SHARD_ROWS, ty, n_q, hidden, TILE_ROWS, c->rank, c->world, sq));
     APK_TRY(shard_plan(SHARD_ROWS, ty, n_kv, hidden, TILE_ROWS, c->rank, c->world, sk));
@@ -466,8 +467,9 @@ int resolve_qkv(apk_ctx *c, uint32_t ty, const void *wq, const void *wk, const v
         {wk, hidden, sk[0], kl, 0, 1 << 30, 0, (int)ql},
         {wv, hidden, sk[0], kl, 0, 1 << 30, 0, (int)(ql + kl)},
     };
+    if (!wv) segs.pop_back();
     std::unique_ptr<DevMatrix> m;
-    APK_TRY(build_matrix(c, ty, ql + 2 * kl, hidden, segs, &m));
+    APK_TRY(build_matrix(c, ty, ql + (wv ? 2 : 1) * kl, hidden, segs, &m));
     *out = m.get();
     c->mats[key] = std::move(m);
     return APK_OK;

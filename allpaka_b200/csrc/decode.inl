@@ -172,14 +172,18 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
     for (uint32_t l = 0; l < r->n_layers; ++l) {
         const apk_token_layer &tl = r->layers[l];
         PlanLayer &pl = P->L[l];
-        if (tl.wq.ty != tl.wk.ty || tl.wq.ty != tl.wv.ty)
-            return decline_decode(c, APK_DECLINE_UNSUPPORTED_TYPE, "layer %u: wq/wk/wv types differ", l);
+        if (tl.wq.ty != tl.wk.ty) return decline_decode(c, APK_DECLINE_UNSUPPORTED_TYPE, "layer %u: wq/wk types differ", l);
+        // V in a type of its own (the Q4_K_M recipe keeps it in Q6_K): a second matrix and launch
+        const bool own_v = tl.wv.ty != tl.wq.ty;
+        if (own_v && c->world > 1) return decline_decode(c, APK_DECLINE_UNSUPPORTED_TYPE, "layer %u: wv in a type of its own on a sharded context", l);
         if (tl.gate.ty != tl.up.ty) return decline_decode(c, APK_DECLINE_UNSUPPORTED_TYPE, "layer %u: gate/up types differ", l);
         if (tl.wq.n_out != nq || tl.wk.n_out != nkv || tl.wv.n_out != nkv || tl.wo.n_out != H || tl.gate.n_out != ffn ||
             tl.up.n_out != ffn || tl.down.n_out != H)
             return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "layer %u: projection shapes disagree with the request", l);
         int rc;
-        if ((rc = resolve_qkv(c, tl.wq.ty, tl.wq.w, tl.wk.w, tl.wv.w, H, nq, nkv, &pl.qkv))) { c->st.decode_declines++; return rc; }
+        if ((rc = resolve_qkv(c, tl.wq.ty, tl.wq.w, tl.wk.w, own_v ? nullptr : tl.wv.w, H, nq, nkv, &pl.qkv))) { c->st.decode_declines++; return rc; }
+        pl.v = nullptr;
+        if (own_v && (rc = resolve_plain(c, "attn wv", tl.wv.w, tl.wv.ty, nkv, H, SHARD_NONE, &pl.v))) { c->st.decode_declines++; return rc; }
         if ((rc = resolve_plain(c, "attn wo", tl.wo.w, tl.wo.ty, H, nq, SHARD_K, &pl.wo))) { c->st.decode_declines++; return rc; }
         if ((rc = resolve_gateup(c, tl.gate.ty, tl.gate.w, tl.up.w, H, ffn, &pl.gateup, &P->ffn_l))) { c->st.decode_declines++; return rc; }
         if ((rc = resolve_plain(c, "ffn down", tl.down.w, tl.down.ty, H, ffn, SHARD_K, &pl.down))) { c->st.decode_declines++; return rc; }
@@ -341,10 +345,19 @@ struct TokenLaunch {
         return APK_OK;
     }
     int qkv(PlanLayer &L, bool advance = true, uint32_t layer = 0) {
+        if (L.v) {
+            APK_TRY(qkv_part(L, L.qkv, false, layer, 0));
+            return qkv_part(L, L.v, advance, layer, (int)((P->nq_l + P->nkv_l) / TILE_ROWS));
+        }
+        return qkv_part(L, L.qkv, advance, layer, 0);
+    }
+    // W: the Q | K | V stack, or Q | K and then V when V has a type of its own (tile_base: V's first head in the stack)
+    int qkv_part(PlanLayer &L, DevMatrix *W, bool advance, uint32_t layer, int tile_base) {
         MvParams p{};
-        APK_TRY(normed_input(L.qkv, L.attn_norm, q8, &p, advance));
+        APK_TRY(normed_input(W, L.attn_norm, q8, &p, advance));
         p.epi = EPI_QKV_ROPE;
-        p.y = P->qkv.as<float>();
+        p.qkv_tile_base = tile_base;
+        p.y = P->qkv.as<float>() + (size_t)tile_base * TILE_ROWS;
         p.ldy = (int)(P->nq_l + 2 * P->nkv_l);
         p.n_q_tiles = (int)(P->nq_l / TILE_ROWS);
         p.n_k_tiles = (int)(P->nkv_l / TILE_ROWS);
@@ -365,7 +378,7 @@ struct TokenLaunch {
             p.q_next_two_level = autom.two_level;
             p.q_next_need_sum = L.wo->ty == APK_TY_Q4_K;
         }
-        return launch(L.qkv, p, q8, L.wo);
+        return launch(W, p, q8, L.wo);
     }
     // the attention core over the cache: its result, packed, is wo's input
     int attention(PlanLayer &L, uint32_t layer) {
@@ -656,6 +669,7 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
         const DevMatrix *W = kind == 0 ? L0.qkv : kind == 1 ? L0.wo : kind == 2 ? L0.gateup : kind == 3 ? L0.down : P->head;
         // weights as stored in the GGUF file (padding rows of the tiled stream are not counted)
         double wb = orig_bytes(W);
+        if (kind == 0 && L0.v) wb += orig_bytes(L0.v);
         if (kind == 2) wb = 2.0 * (double)P->ffn_l * (H / 32) * (W->ty == APK_TY_Q8_0 ? 34 : (W->ty == APK_TY_Q4_K ? 144 : 210) / 8.0);
         const double in_b = (double)m * W->n_in * 4.0;
         const double out_b = kind == 2 ? (double)m * P->ffn_l * 4.0 : (double)m * W->n_out * 4.0;

@@ -193,6 +193,7 @@ struct MvParams {
     const float *rope; int half;       // [m][half][2] (sin, cos)
     ActLayout q_next;                  // optional: roped Q heads packed as the next matvec's activations
     int q_next_two_level, q_next_need_sum;
+    int qkv_tile_base;  // EPI_QKV_ROPE: stack index of this matrix's first head (n_q_tiles + n_k_tiles for a V matrix of its own)
     __half *kv_k, *kv_v;               // optional: this layer's f16 cache slabs [capacity][kv_dim]; K and V rows go there too
     int kv_dim;                        // (this rank's) kv heads * 128
     const uint32_t *pos_dev; uint32_t pos;  // cache position of row 0: on the device (greedy chain) or with the launch
@@ -1072,7 +1073,7 @@ __global__ void synth_q4_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) 
     }
 }
 
-// Q6_K: every ql/qh byte and every int8 sub-block scale uniform, d f16(|N(0,0.0005)|).
+// Q6_K: every ql/qh byte and every int8 sub-block scale uniform, d f16(|N(0,2.5e-5)|).
 __global__ void synth_q6_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
@@ -1083,7 +1084,7 @@ __global__ void synth_q6_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) 
         o[i * 4 + 0] = (uint8_t)h; o[i * 4 + 1] = (uint8_t)(h >> 8);
         o[i * 4 + 2] = (uint8_t)(h >> 16); o[i * 4 + 3] = (uint8_t)(h >> 24);
     }
-    const unsigned short d = __half_as_ushort(__float2half_rn(absnormal(splitmix64(base ^ 0x61ull), 0.0005f)));
+    const unsigned short d = __half_as_ushort(__float2half_rn(absnormal(splitmix64(base ^ 0x61ull), 2.5e-5f)));
     o[208] = (uint8_t)(d & 0xff); o[209] = (uint8_t)(d >> 8);
 }
 
@@ -2324,8 +2325,9 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw,
     if (p.epi == EPI_QKV_ROPE) {
         // one head per tile (head_dim 128): warp w serves tokens w, w+8, ...
         const int warp = tid >> 5, lane = tid & 31;
-        const float *nw = tile < p.n_q_tiles ? p.q_norm : (tile < p.n_q_tiles + p.n_k_tiles ? p.k_norm : nullptr);
-        const bool rot = tile < p.n_q_tiles + p.n_k_tiles;
+        const int vt = tile + p.qkv_tile_base;  // the head's index in the Q | K | V stack (V may be a matrix, and a launch, of its own)
+        const float *nw = vt < p.n_q_tiles ? p.q_norm : (vt < p.n_q_tiles + p.n_k_tiles ? p.k_norm : nullptr);
+        const bool rot = vt < p.n_q_tiles + p.n_k_tiles;
         for (int m = warp; m < MO; m += (cw.n >> 5)) {
             float v[4];
 #pragma unroll
@@ -2372,17 +2374,17 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw,
                 }
                 const int row = row0 + c;
                 if (row < p.n_out) p.y[(size_t)m * p.ldy + row] = o;
-                if (p.kv_k && tile >= p.n_q_tiles) {
+                if (p.kv_k && vt >= p.n_q_tiles) {
                     // K (roped) and V of this position into the f16 cache, round to nearest even
                     // (KvCache::store_at, crates/allpaka-model/src/kv.rs:682-697)
                     const uint32_t pos = (p.pos_dev ? *p.pos_dev : p.pos) + (uint32_t)m;
-                    const bool is_k = tile < p.n_q_tiles + p.n_k_tiles;
-                    const int col = (tile - p.n_q_tiles - (is_k ? 0 : p.n_k_tiles)) * TILE_ROWS + c;
+                    const bool is_k = vt < p.n_q_tiles + p.n_k_tiles;
+                    const int col = (vt - p.n_q_tiles - (is_k ? 0 : p.n_k_tiles)) * TILE_ROWS + c;
                     (is_k ? p.kv_k : p.kv_v)[(size_t)pos * p.kv_dim + col] = __float2half_rn(o);
                 }
                 v[j] = o;
             }
-            if (p.q_next.base && tile < p.n_q_tiles) {
+            if (p.q_next.base && vt < p.n_q_tiles) {
                 // keep the roped head in shared memory for the packing pass below
                 __syncwarp();
 #pragma unroll
@@ -2391,12 +2393,12 @@ __device__ __forceinline__ void epilogue_tile(const MvParams &p, const Crew &cw,
         }
         // identity attention core: the roped Q head is what the output projection consumes.
         // One warp per (token, 32-element block): the four blocks of a head go in parallel.
-        if (p.q_next.base && tile < p.n_q_tiles) {
+        if (p.q_next.base && vt < p.n_q_tiles) {
             cw.sync();
             for (int w = warp; w < MO * 4; w += (cw.n >> 5)) {
                 const int m = w >> 2, j = w & 3;
                 const float *hs = out + m * TILE_ROWS;
-                quantize_store(p.q_next, p.q_next_two_level, p.q_next_need_sum, m, tile * 4 + j, lane, hs[lane + 32 * j]);
+                quantize_store(p.q_next, p.q_next_two_level, p.q_next_need_sum, m, vt * 4 + j, lane, hs[lane + 32 * j]);
             }
         }
         return;

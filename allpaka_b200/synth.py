@@ -67,9 +67,10 @@ def q4_k_matrix(n_out: int, n_in: int, seed: int, d_sigma: float = 0.002) -> np.
     return out.reshape(-1)
 
 
-def q6_k_matrix(n_out: int, n_in: int, seed: int, d_sigma: float = 0.0005) -> np.ndarray:
+def q6_k_matrix(n_out: int, n_in: int, seed: int, d_sigma: float = 2.5e-5) -> np.ndarray:
     """6-bit quants uniform (every ql/qh byte uniform), signed 8-bit sub-block scales uniform in
-    [-128,127], f16 d drawn as |N(0,sigma)|."""
+    [-128,127], f16 d drawn as |N(0,sigma)|: weights of a few hundredths, like a model's (d of a
+    real file, max|w| / (127 * 32), lies in the f16 subnormal range too)."""
     rng = np.random.default_rng(seed)
     nsb = n_in // 256
     out = np.empty((n_out, nsb, 210), dtype=np.uint8)

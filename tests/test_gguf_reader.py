@@ -13,7 +13,8 @@ from tests.util import Q4_K, Q6_K, Q8_0
 
 
 def tiny_model(arch="qwen3", ty=Q8_0, hidden=256, n_heads=2, n_kv=1, head_dim=128, ffn=512, vocab=300, n_layers=2,
-               qk_norm=True, tied=False, extra_meta=None, drop=(), override=None):
+               qk_norm=True, tied=False, extra_meta=None, drop=(), override=None, ty_of=None):
+    """ty_of: tensor-name suffix -> ggml type, for files that mix types (the rest take ``ty``)."""
     rng = np.random.default_rng(3)
     meta = {"general.architecture": arch, f"{arch}.block_count": n_layers, f"{arch}.embedding_length": hidden,
             f"{arch}.attention.head_count": n_heads, f"{arch}.attention.head_count_kv": n_kv,
@@ -22,25 +23,30 @@ def tiny_model(arch="qwen3", ty=Q8_0, hidden=256, n_heads=2, n_kv=1, head_dim=12
             "tokenizer.ggml.tokens": [f"t{i}" for i in range(vocab)], "tokenizer.ggml.scores": [1, 2, 3]}
     meta.update(extra_meta or {})
     q_dim, kv_dim = n_heads * head_dim, n_kv * head_dim
-    t = [("token_embd.weight", ty, [hidden, vocab], synth.matrix(ty, vocab, hidden, 1))]
+
+    def mat(name, n_out, n_in, seed):
+        t_ = next((v for k, v in (ty_of or {}).items() if name.endswith(k)), ty)
+        return (name, t_, [n_in, n_out], synth.matrix(t_, n_out, n_in, seed))
+
+    t = [mat("token_embd.weight", vocab, hidden, 1)]
     for l in range(n_layers):
         def vec(n, s):
             return (1.0 + 0.1 * rng.standard_normal(n)).astype(np.float32)
         t += [(f"blk.{l}.attn_norm.weight", 0, [hidden], vec(hidden, 0)),
-              (f"blk.{l}.attn_q.weight", ty, [hidden, q_dim], synth.matrix(ty, q_dim, hidden, 10 * l + 2)),
-              (f"blk.{l}.attn_k.weight", ty, [hidden, kv_dim], synth.matrix(ty, kv_dim, hidden, 10 * l + 3)),
-              (f"blk.{l}.attn_v.weight", ty, [hidden, kv_dim], synth.matrix(ty, kv_dim, hidden, 10 * l + 4)),
-              (f"blk.{l}.attn_output.weight", ty, [q_dim, hidden], synth.matrix(ty, hidden, q_dim, 10 * l + 5)),
+              mat(f"blk.{l}.attn_q.weight", q_dim, hidden, 10 * l + 2),
+              mat(f"blk.{l}.attn_k.weight", kv_dim, hidden, 10 * l + 3),
+              mat(f"blk.{l}.attn_v.weight", kv_dim, hidden, 10 * l + 4),
+              mat(f"blk.{l}.attn_output.weight", hidden, q_dim, 10 * l + 5),
               (f"blk.{l}.ffn_norm.weight", 0, [hidden], vec(hidden, 1)),
-              (f"blk.{l}.ffn_gate.weight", ty, [hidden, ffn], synth.matrix(ty, ffn, hidden, 10 * l + 6)),
-              (f"blk.{l}.ffn_up.weight", ty, [hidden, ffn], synth.matrix(ty, ffn, hidden, 10 * l + 7)),
-              (f"blk.{l}.ffn_down.weight", ty, [ffn, hidden], synth.matrix(ty, hidden, ffn, 10 * l + 8))]
+              mat(f"blk.{l}.ffn_gate.weight", ffn, hidden, 10 * l + 6),
+              mat(f"blk.{l}.ffn_up.weight", ffn, hidden, 10 * l + 7),
+              mat(f"blk.{l}.ffn_down.weight", hidden, ffn, 10 * l + 8)]
         if qk_norm:
             t += [(f"blk.{l}.attn_q_norm.weight", 0, [head_dim], vec(head_dim, 2)),
                   (f"blk.{l}.attn_k_norm.weight", 0, [head_dim], vec(head_dim, 3))]
     t.append(("output_norm.weight", 0, [hidden], (1.0 + 0.1 * rng.standard_normal(hidden)).astype(np.float32)))
     if not tied:
-        t.append(("output.weight", ty, [hidden, vocab], synth.matrix(ty, vocab, hidden, 99)))
+        t.append(mat("output.weight", vocab, hidden, 99))
     t = [e for e in t if e[0] not in drop]
     if override:
         t = [override.get(e[0], e) for e in t]

@@ -310,7 +310,7 @@ def test_decode_token_matches_oracle_layer_stack(gpu, orc, ty, m, qk_norm):
     gpu.detach(r.buf)
 
 
-@pytest.mark.parametrize("ty,m", [(Q8_0, 1), (Q8_0, 3), (Q4_K, 1), (Q6_K, 1), (Q6_K, 3)])
+@pytest.mark.parametrize("ty,m", [(Q8_0, 1), (Q8_0, 3), (Q4_K, 1), (Q6_K, 1)])
 def test_decode_token_tiles_shared_by_many_ctas(gpu, orc, ty, m):
     """Shapes whose K dimension spreads one tile over up to eight CTAs (every CTA holds one unit),
     per-head norm on: the cross-CTA hand-off, the residual epilogue and the packed Q for wo."""

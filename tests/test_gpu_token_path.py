@@ -13,7 +13,7 @@ import numpy as np
 import pytest
 
 from allpaka_b200 import synth
-from tests.util import (Q4_K, Q8_0, Region, make_layer, oracle_decode, oracle_logits, rel_l2,
+from tests.util import (Q4_K, Q6_K, Q8_0, Region, make_layer, oracle_decode, oracle_logits, rel_l2,
                         rope_table)
 
 pytestmark = pytest.mark.gpu
@@ -155,7 +155,7 @@ def test_verify_batch_records_are_bit_exact(orc):
     g.close()
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q4_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q4_K, Q6_K])
 def test_block_dots_inside_the_token_are_bit_exact(orc, ty):
     """The int32 block dots of the second layer's Q|K|V launch (its input has been through a whole
     layer of the fused path) against dot_i8 on the oracle's quantisation of the same row."""
@@ -194,7 +194,7 @@ def oracle_trace(orc, ty, layers, hidden, n_q, n_kv, hd, ffn, eps, rope, x, m):
     return rows
 
 
-@pytest.mark.parametrize("ty,m", [(Q8_0, 1), (Q8_0, 4), (Q4_K, 1)])
+@pytest.mark.parametrize("ty,m", [(Q8_0, 1), (Q8_0, 4), (Q4_K, 1), (Q6_K, 1), (Q6_K, 3)])
 def test_every_operator_on_the_gpus_own_rows_over_many_seeds(orc, ty, m):
     """16 input seeds, none picked.  Per operator (attention half, FFN half, head), the oracle is fed
     the row the GPU had at that point and must agree with the GPU's next row to 1e-5.  The chained
@@ -236,13 +236,15 @@ def test_every_operator_on_the_gpus_own_rows_over_many_seeds(orc, ty, m):
                 for t in range(m):
                     _, _, oq = orc.q8acts(orc.rmsnorm_into(trace[k][t], gams[k], 1e-6))
                     if np.any(recs[k]["q"][t] != oq):
-                        assert rel_l2(xs[k][t], trace[k][t]) < 1e-6  # same rows to rounding, different code
+                        # same rows to rounding (m = 1) or to the 16-bit activations of the f32-activation
+                        # matvecs behind them (m > 1), different code
+                        assert rel_l2(xs[k][t], trace[k][t]) < (1e-6 if m == 1 else 1e-4)
                         assert np.max(np.abs(recs[k]["q"][t].astype(int) - oq.astype(int))) == 1
                         explained = True
                 if explained:
                     break
             assert explained, (seed, err)
-    print(f"{'Q8_0' if ty == Q8_0 else 'Q4_K'} m={m}: per-operator worst {worst_op:.2e}; chained over 16 seeds "
+    print(f"{ {Q8_0: 'Q8_0', Q4_K: 'Q4_K', Q6_K: 'Q6_K'}[ty]} m={m}: per-operator worst {worst_op:.2e}; chained over 16 seeds "
           f"median {np.median(chained):.2e} max {np.max(chained):.2e}, {sum(e > 2e-3 for e in chained)} above 2e-3")
     # (an operator here is a whole half-layer: inside the FFN the SwiGLU row is quantised again, and a
     # value that differs in its last bit may round to the neighbouring code: a few 1e-5 at most)
