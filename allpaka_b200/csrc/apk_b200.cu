@@ -230,6 +230,7 @@ struct apk_ctx {
     int32_t *dots_dump = nullptr;  // block dots of launch dots_launch
     size_t dots_cap = 0;
     int dots_launch = -1, launch_no = 0;
+    int tl_alt = 0;              // ALLPAKA_B200_TL_ALT=1: the timeline stamps the closing of each CTA's last tile
     bool prev_mv_exclusive = false;  // the last matvec launched holds every SM to itself (see launch_matvec)
     int smem_per_sm = 0;
     std::vector<RecMeta> rec_meta;
@@ -601,6 +602,7 @@ int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool
         k = pick_kernel(W->ty, mode.m_eff, true);
     }
     p.launch_id = c->launch_no;
+    p.tl_alt = c->tl_alt;
     c->launch_no++;
     const int act_rec = p.act.rec_bytes();
     const int ns = pick_stages(c, (int)W->ty, mode.m_eff, p.pro, W->KS, act_rec);
@@ -857,6 +859,7 @@ int apk_init(apk_ctx **out, int device) {
     if (const char *e = getenv("ALLPAKA_B200_INFLIGHT")) c->inflight = std::max(1, std::min(atoi(e), MAX_STAGES));
     if (const char *e = getenv("ALLPAKA_B200_INFLIGHT_PRE")) c->inflight_pre = std::max(1, std::min(atoi(e), MAX_STAGES));
     if (const char *e = getenv("ALLPAKA_B200_SELF_XCH")) c->self_xch = atoi(e) != 0;
+    if (const char *e = getenv("ALLPAKA_B200_TL_ALT")) c->tl_alt = atoi(e) != 0;
     if (c->self_xch) {
         // one rank exchanging with itself: the peer-store epilogue and the collecting prologue on one GPU
         CUDA_TRY(cudaMalloc((void **)&c->xch_local, XCH_BYTES));

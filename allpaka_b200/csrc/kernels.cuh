@@ -175,7 +175,8 @@ struct MvParams {
     int pdl;            // launched with a programmatic dependency on the previous kernel
     unsigned long long *partials;  // [gridDim.x][2][MAX_M_EFF][128] tagged partial sums (see part_store)
     int *err;           // error word
-    int launch_id;      // number of this launch within its submission (goes into the error word)
+    int launch_id;
+    int tl_alt;     // timeline: stamp the closing of the last tile (1: handed over, 4: crew complete, 7: pieces added) instead of 1 and 4      // number of this launch within its submission (goes into the error word)
     long long wait_limit;  // cycle budget of every bounded wait in this launch
     int32_t *dump;      // optional [m_eff][n_out][nb] int32 block dots
     uint8_t *act_dump;  // optional: CTA 0 copies its resident activation records here (parity instrumentation)
@@ -552,34 +553,61 @@ __device__ __forceinline__ void ld_relaxed_sys_v2b64(const unsigned long long *p
     asm volatile("ld.relaxed.sys.global.v2.b64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
 // (slot 0 + slot 1 + ...)[i..i+3] in rank order: the one summation order of an exchange (rank 0's
-// slot already holds the residual row plus its partial sums, see EPI_PEERS).  Polls (bounded)
-// until the four words of every rank carry tag e; *ok = false when the budget ran out (the sum
-// then holds whatever was there).  Nothing but tagged words is read, so a caller needs no other
+// slot already holds the residual row plus its partial sums, see EPI_PEERS), for NJ groups of
+// four consecutive values per thread (group j at word offset off[j]; live[j] = false: skipped).
+// Polls (bounded) until the words carry tag e; *ok = false when the budget ran out (the sums then
+// hold whatever was there).  Nothing but tagged words is read, so a caller needs no other
 // ordering with the kernels that produced them.
-__device__ __forceinline__ float4 xch_gather4(float *mine, uint32_t e, int world, size_t off, long long limit, bool *ok) {
-    const unsigned long long *s0 = xch_words(mine) + (size_t)(e & 1u) * XCH_MAX_RANKS * XCH_ROW_FLOATS + off;
-    float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+// The loads of XCH_RB ranks and all NJ groups are in flight together: once the words are there,
+// the gather costs world / XCH_RB round trips to L2, not world * NJ.
+constexpr int XCH_RB = 2;
+template <int NJ>
+__device__ __forceinline__ void xch_gather(float *mine, uint32_t e, int world, const size_t (&off)[NJ], const bool (&live)[NJ],
+                                           long long limit, bool *ok, float4 (&sum)[NJ]) {
+    const unsigned long long *s0 = xch_words(mine) + (size_t)(e & 1u) * XCH_MAX_RANKS * XCH_ROW_FLOATS;
     const long long t0 = clock64();
-    for (int r = 0; r < world; ++r) {
-        unsigned long long w0, w1, w2, w3;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) sum[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int r0 = 0; r0 < world; r0 += XCH_RB) {
+        unsigned long long w[XCH_RB][NJ][4];
         for (;;) {
-            ld_relaxed_sys_v2b64(s0 + (size_t)r * XCH_ROW_FLOATS, w0, w1);
-            ld_relaxed_sys_v2b64(s0 + (size_t)r * XCH_ROW_FLOATS + 2, w2, w3);
-            if ((uint32_t)(w0 >> 32) == e && (uint32_t)(w1 >> 32) == e && (uint32_t)(w2 >> 32) == e && (uint32_t)(w3 >> 32) == e) break;
+            bool all = true;
+#pragma unroll
+            for (int rr = 0; rr < XCH_RB; ++rr)
+#pragma unroll
+                for (int j = 0; j < NJ; ++j)
+                    if (r0 + rr < world && live[j]) {
+                        const unsigned long long *src = s0 + (size_t)(r0 + rr) * XCH_ROW_FLOATS + off[j];
+                        ld_relaxed_sys_v2b64(src, w[rr][j][0], w[rr][j][1]);
+                        ld_relaxed_sys_v2b64(src + 2, w[rr][j][2], w[rr][j][3]);
+                    }
+#pragma unroll
+            for (int rr = 0; rr < XCH_RB; ++rr)
+#pragma unroll
+                for (int j = 0; j < NJ; ++j)
+                    if (r0 + rr < world && live[j])
+                        all = all && (uint32_t)(w[rr][j][0] >> 32) == e && (uint32_t)(w[rr][j][1] >> 32) == e &&
+                              (uint32_t)(w[rr][j][2] >> 32) == e && (uint32_t)(w[rr][j][3] >> 32) == e;
+            if (all) break;
             if (clock64() - t0 > limit) {
                 *ok = false;
                 break;
             }
         }
-        const float4 v = make_float4(__uint_as_float((uint32_t)w0), __uint_as_float((uint32_t)w1), __uint_as_float((uint32_t)w2),
-                                     __uint_as_float((uint32_t)w3));
-        if (r == 0) sum = v;
-        else {
-            sum.x = __fadd_rn(sum.x, v.x); sum.y = __fadd_rn(sum.y, v.y);
-            sum.z = __fadd_rn(sum.z, v.z); sum.w = __fadd_rn(sum.w, v.w);
-        }
+#pragma unroll
+        for (int rr = 0; rr < XCH_RB; ++rr)
+#pragma unroll
+            for (int j = 0; j < NJ; ++j)
+                if (r0 + rr < world && live[j]) {
+                    const float4 v = make_float4(__uint_as_float((uint32_t)w[rr][j][0]), __uint_as_float((uint32_t)w[rr][j][1]),
+                                                 __uint_as_float((uint32_t)w[rr][j][2]), __uint_as_float((uint32_t)w[rr][j][3]));
+                    if (r0 + rr == 0) sum[j] = v;
+                    else {
+                        sum[j].x = __fadd_rn(sum[j].x, v.x); sum[j].y = __fadd_rn(sum[j].y, v.y);
+                        sum[j].z = __fadd_rn(sum[j].z, v.z); sum[j].w = __fadd_rn(sum[j].w, v.w);
+                    }
+                }
     }
-    return sum;
 }
 
 struct XchReduceParams {
@@ -608,7 +636,11 @@ __global__ void __launch_bounds__(256) xch_reduce_kernel(XchReduceParams p) {
     if (i < total) {
         const int m = (int)(i / p.n), col = (int)(i % p.n);
         bool ok = true;
-        const float4 acc = xch_gather4(mine, e, p.xch.world, (size_t)m * p.n + col, p.wait_limit, &ok);
+        const size_t off[1] = {(size_t)m * p.n + col};
+        const bool live[1] = {true};
+        float4 accs[1];
+        xch_gather<1>(mine, e, p.xch.world, off, live, p.wait_limit, &ok, accs);
+        const float4 acc = accs[0];
         if (!ok) atomicCAS(p.err, 0, ERRW_PEER_TIMEOUT);  // a peer never delivered: record it and finish normally
         *reinterpret_cast<float4 *>(p.xout + (size_t)m * p.ldxout + col) = acc;
     }
@@ -1200,14 +1232,20 @@ __device__ __forceinline__ void prologue_quant(const MvParams &p, uint8_t *res, 
         float *mine = p.xch.slots[p.xch.rank];
         const uint32_t e = xch_number(mine, p.xin);
         bool ok = true;
+        size_t off[PRO_J];
+        bool live[PRO_J];
+        float4 xs[PRO_J];
+#pragma unroll
+        for (int j = 0; j < PRO_J; ++j) {
+            off[j] = (size_t)(4 * tid + PRO_CHUNK * j);
+            live[j] = 4 * tid + PRO_CHUNK * j < n;
+        }
+        xch_gather<PRO_J>(mine, e, p.xch.world, off, live, p.wait_limit, &ok, xs);
 #pragma unroll
         for (int j = 0; j < PRO_J; ++j) {
             const int el = 4 * tid + PRO_CHUNK * j;
-            float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (el < n) {
-                x = xch_gather4(mine, e, p.xch.world, (size_t)el, p.wait_limit, &ok);
-                if (pp.xout && blockIdx.x == 0) *reinterpret_cast<float4 *>(pp.xout + el) = x;
-            }
+            const float4 x = xs[j];
+            if (el < n && pp.xout && blockIdx.x == 0) *reinterpret_cast<float4 *>(pp.xout + el) = x;
             v[4 * j] = x.x; v[4 * j + 1] = x.y; v[4 * j + 2] = x.z; v[4 * j + 3] = x.w;
         }
         if (!ok) atomicCAS(p.err, 0, ERRW_PEER_TIMEOUT | (p.launch_id << 8));  // goes on with what is there; the host reports the error
@@ -1584,7 +1622,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     if (gave_up) note_timeout(p, ERRW_FINISHER_TIMEOUT, 5);
                     cw.sync();
                 }
-                if (tl && cw.t == 0 && final_tile && p.pro != PRO_QUANT) tl[7] = globaltimer_ns();  // pieces added
+                if (tl && cw.t == 0 && final_tile && (p.pro != PRO_QUANT || p.tl_alt)) tl[7] = globaltimer_ns();  // pieces added
                 epilogue_tile<M>(p, cw, t_cur, fin, use_pre ? pre : nullptr, rope_pre, gam_pre);
             }
     };
@@ -1763,7 +1801,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
             if (lane == 0) note_timeout(p, ERRW_CONSUMER_TIMEOUT, 9);
         }
         if (tl && mine && lane == 0 && (warp & 7) == 0) {
-            if (it == 0) tl[1] = globaltimer_ns();   // first unit landed
+            if (it == 0 && !p.tl_alt) tl[1] = globaltimer_ns();   // first unit landed
             if (it + 1 == n_total) tl[3] = globaltimer_ns();  // last unit landed
         }
         if (mine && !aborted) {
@@ -2246,6 +2284,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
         if (tid == 0) {
             s_flags[0] = t_cur;
             s_flags[1] = (it + 1 == n_total) ? 1 : 0;
+            if (tl && p.tl_alt && it + 1 == n_total) tl[1] = globaltimer_ns();  // (alternative stamps) the last tile handed over
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(red_full);
@@ -2257,6 +2296,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     {
         const Crew cw{N_FINISHERS + tid, N_CREW_ALL, 3};
         cw.sync();
+        if (tl && p.tl_alt && tid == 0) tl[4] = globaltimer_ns();  // (alternative stamps) the closing crew is complete
         close_tile(cw, t_last, true, nullptr);
     }
 }

@@ -48,7 +48,7 @@ if ROOT not in sys.path:
 
 HIDDEN, N_HEADS, N_KV, HEAD_DIM, FFN, VOCAB, N_LAYERS = 5120, 64, 8, 128, 25600, 151936, 64
 EPS, ROPE_BASE = 1e-6, 1e6
-Q8_0, Q4_K = 8, 12
+Q8_0, Q4_K, Q6_K = 8, 12, 14
 FALLBACK_HBM_GBS = 6650.0
 PARITY_LAYERS = 4
 METRIC = "decode tok/s Qwen3-32B-shape Q8_0"
@@ -60,7 +60,7 @@ def q8_bytes(n_out, n_in):
 
 
 def ty_bytes(ty, n_out, n_in):
-    return q8_bytes(n_out, n_in) if ty == Q8_0 else n_out * (n_in // 256) * 144
+    return q8_bytes(n_out, n_in) if ty == Q8_0 else n_out * (n_in // 256) * (144 if ty == Q4_K else 210)
 
 
 def layer_tensors(hidden, nq, nkv, ffn):
@@ -369,6 +369,17 @@ def run_configs(g, peak):
     us = g.bench_ring("matvec", [G.MatvecReq(Q4_K, c[0], n_in, n_out, x, 1) for c in copies], reps=12)
     g.synth_release()
     out["1"] = entry(us, 73850880, par, what="Q4_K 25600x5120 m=1", ring_mb=8 * 73.7)
+    g.detach(keep[1])
+
+    # config 1 in Q6_K (the type the Q4_K_M recipe keeps V, down and the head in): same shape
+    w = synth.q6_k_matrix(n_out, n_in, 1021)
+    assert g.attach(w)
+    par = rel_l2(g.matvec(Q6_K, w, n_in, n_out, x, 1), orc.matmul(Q6_K, w, n_out, n_in, x, 1))
+    g.detach(w)
+    copies, keep = ring([(n_out, n_in)], 6, Q6_K, 72500)
+    us = g.bench_ring("matvec", [G.MatvecReq(Q6_K, c[0], n_in, n_out, x, 1) for c in copies], reps=12)
+    g.synth_release()
+    out["1_q6_k"] = entry(us, ty_bytes(Q6_K, n_out, n_in) + 4 * (n_in + n_out), par, what="Q6_K 25600x5120 m=1", ring_mb=6 * 107.5)
     g.detach(keep[1])
 
     # config 2: RMSNorm -> Q8_0 QKV 10240x5120 -> NeoX RoPE, batch 1 (bf16 x, widened exactly)
