@@ -385,8 +385,10 @@ int apk_model_open(apk_gguf *f, apk_model **out) {
         const uint32_t half = I.rot_dim / 2;
         for (uint32_t nw = 0; nw < I.head_dim; ++nw)
             order.push_back(nw < half ? 2 * nw : (nw < I.rot_dim ? 2 * (nw - half) + 1 : nw));
-    } else if (norm_style && has_qk_norm) {
-        return fail(APK_DECLINE_MISSING_CAPABILITY, "pairwise rotary embedding with per-head norms is outside the decode path");
+    } else if (norm_style) {
+        // the reference then rotates adjacent pairs at run time (per-head norms, or ALLPAKA_ROPE_NORM=1); the kernels here
+        // rotate split halves only
+        return fail(APK_DECLINE_MISSING_CAPABILITY, "pairwise rotary embedding kept in file order is outside the decode path");
     }
     I.neox_reordered = order.empty() ? 0 : 1;
     const uint64_t q_dim = (uint64_t)I.n_heads * I.head_dim, kv_dim = (uint64_t)I.n_kv_heads * I.head_dim;

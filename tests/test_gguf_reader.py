@@ -160,6 +160,28 @@ def test_pairwise_rope_files_get_their_q_and_k_rows_reordered(tmp_path):
         f.close()
 
 
+def test_pairwise_rope_kept_in_file_order_is_declined(tmp_path, monkeypatch):
+    """neox_order returns None for per-head norms or ALLPAKA_ROPE_NORM=1 (loader.rs:366-375): the reference then
+    rotates adjacent pairs at run time, which the kernels here do not."""
+    meta, tensors = tiny_model(arch="llama", qk_norm=False)
+    p = tmp_path / "l.gguf"
+    gguf.write_file(str(p), meta, tensors)
+    f = gguf.GgufFile(str(p))
+    monkeypatch.setenv("ALLPAKA_ROPE_NORM", "1")
+    with pytest.raises(gguf.GgufError) as e:
+        gguf.Model(f)
+    assert "pairwise rotary" in str(e.value) and e.value.rc == 5
+    monkeypatch.delenv("ALLPAKA_ROPE_NORM")
+    gguf.Model(f).close()
+    f.close()
+    meta, tensors = tiny_model(arch="mistral", qk_norm=True)
+    gguf.write_file(str(p), meta, tensors)
+    f = gguf.GgufFile(str(p))
+    with pytest.raises(gguf.GgufError):
+        gguf.Model(f)
+    f.close()
+
+
 def test_what_the_decode_path_cannot_serve_is_declined_by_name(tmp_path):
     def fails(what, **kw):
         meta, tensors = tiny_model(**kw)
