@@ -371,9 +371,11 @@ __device__ __forceinline__ void mma_half_s8_acc(int (&d)[4], uint32_t a0, uint32
         : "r"(a0), "r"(a1), "r"(b));
 }
 
-// Q6_K: the signed 6-bit values of quarter qi (0..3) of one half as int8 fragment words:
-// (ql nibble | two qh bits << 4) - 32, per byte (crates/allpaka-backend/src/quantmat/q8_acts.rs:329-333).
-// ql: the chunk of byte group qi & 1; qh: the half's chunk.
+// Q6_K: the 6-bit values of quarter qi (0..3) of one half as int8 fragment words, (ql nibble | two
+// qh bits << 4) per byte, WITHOUT the -32 of crates/allpaka-backend/src/quantmat/q8_acts.rs:329-333:
+// dot(q - 32, x) = dot(q, x) - 32 * sum(x), and the sums of the activation codes come out of one
+// extra mma against an all-ones fragment (see the consumers), which is cheaper than a byte-wise
+// subtraction per register.  ql: the chunk of byte group qi & 1; qh: the half's chunk.
 __device__ __forceinline__ uint4 q6_k_unpack(const uint4 &ql, const uint4 &qh, int qi) {
     const int sh = 2 * qi;
     uint4 v;
@@ -383,10 +385,10 @@ __device__ __forceinline__ uint4 q6_k_unpack(const uint4 &ql, const uint4 &qh, i
     } else {
         v.x = ql.x & 0x0f0f0f0fu; v.y = ql.y & 0x0f0f0f0fu; v.z = ql.z & 0x0f0f0f0fu; v.w = ql.w & 0x0f0f0f0fu;
     }
-    v.x = __vsub4(v.x | (((qh.x >> sh) & 0x03030303u) << 4), 0x20202020u);
-    v.y = __vsub4(v.y | (((qh.y >> sh) & 0x03030303u) << 4), 0x20202020u);
-    v.z = __vsub4(v.z | (((qh.z >> sh) & 0x03030303u) << 4), 0x20202020u);
-    v.w = __vsub4(v.w | (((qh.w >> sh) & 0x03030303u) << 4), 0x20202020u);
+    v.x |= ((qh.x >> sh) & 0x03030303u) << 4;
+    v.y |= ((qh.y >> sh) & 0x03030303u) << 4;
+    v.z |= ((qh.z >> sh) & 0x03030303u) << 4;
+    v.w |= ((qh.w >> sh) & 0x03030303u) << 4;
     return v;
 }
 // byte i (0..15) of a 16-byte vector as a signed value
@@ -1907,6 +1909,11 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                         const uint32_t xb0 = *reinterpret_cast<const uint32_t *>(xb);
                         const uint32_t xb1 = *reinterpret_cast<const uint32_t *>(xb + 16 * M);
                         int d[4] = {0, 0, 0, 0}, e[4] = {0, 0, 0, 0};
+                        // column c of these two: the sum of the activation codes of the chain's block c / MP2
+                        // (row c % MP2) over its first and second 16 elements, times 32
+                        int sd[4] = {0, 0, 0, 0}, se[4] = {0, 0, 0, 0};
+                        mma_half_s8_acc(sd, 0x20202020u, 0x20202020u, xb0);
+                        mma_half_s8_acc(se, 0x20202020u, 0x20202020u, xb1);
 #pragma unroll
                         for (int i = 0; i < BPC; ++i) {
                             const int blk = ch * BPC + i, half = blk >> 2, qi = blk & 3;
@@ -1920,8 +1927,8 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const int b = ch * BPC + (2 * lt + (i & 1)) / MP2;
-                            I[i] = (i >> 1) ? s8_of(sch, 2 * b) * d[i] + s8_of(sch, 2 * b + 1) * e[i]
-                                            : s8_of(scl, 2 * b) * d[i] + s8_of(scl, 2 * b + 1) * e[i];
+                            I[i] = (i >> 1) ? s8_of(sch, 2 * b) * (d[i] - sd[i]) + s8_of(sch, 2 * b + 1) * (e[i] - se[i])
+                                            : s8_of(scl, 2 * b) * (d[i] - sd[i]) + s8_of(scl, 2 * b + 1) * (e[i] - se[i]);
                         }
                         if (MP2 > 1 && p.two_level) {
                             // columns 2lt, 2lt+1 are the two digits of one token of one block, d2 = d1 / 256
@@ -2100,13 +2107,17 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                         const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xb + tb * 16 + 4 * lt);
                         const uint32_t b1 = *reinterpret_cast<const uint32_t *>(xb + 16 * M + tb * 16 + 4 * lt);
                         int I[2][4];
+                        int sd[4] = {0, 0, 0, 0}, se[4] = {0, 0, 0, 0};  // 32 * the sums of the activation codes, per column
+                        mma_half_s8_acc(sd, 0x20202020u, 0x20202020u, b0);
+                        mma_half_s8_acc(se, 0x20202020u, 0x20202020u, b1);
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
                             int d[4] = {0, 0, 0, 0}, e[4] = {0, 0, 0, 0};
                             mma_half_s8_acc(d, a[h].x, a[h].y, b0);
                             mma_half_s8_acc(e, a[h].z, a[h].w, b1);
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) I[h][i] = s0[2 * h + (i >> 1)] * d[i] + s1[2 * h + (i >> 1)] * e[i];
+                            for (int i = 0; i < 4; ++i)
+                                I[h][i] = s0[2 * h + (i >> 1)] * (d[i] - sd[i]) + s1[2 * h + (i >> 1)] * (e[i] - se[i]);
                         }
                         const float dx0 = xd[t0], dx1 = xd[t1];
 #pragma unroll

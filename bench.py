@@ -663,13 +663,21 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="skip the stand-alone configurations 0-3")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the 4-layer slice")
+    ap.add_argument("--only-configs", action="store_true",
+                    help="run just the stand-alone configurations (one GPU) and print them; small enough to profile")
     ap.add_argument("--tp-exchange", default="p2p", choices=["p2p", "nccl"],
                     help="how the two per-layer reductions cross GPUs: peer-memory stores or NCCL all-reduce")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference":
+    if args.only_configs:
+        if rank == 0:
+            from allpaka_b200 import gpu as G
+
+            peak, peak_kind = measured_peak()
+            print(json.dumps({"configs": run_configs(G.Gpu(local_rank), peak), "peak": peak, "peak_kind": peak_kind}), flush=True)
+    elif args.impl == "reference":
         run_reference(args, rank, world)
     else:
         run_ours(args, rank, world, local_rank)
