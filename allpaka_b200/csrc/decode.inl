@@ -873,6 +873,9 @@ int apk_decode_greedy(apk_ctx *c, const apk_token_req *r, uint32_t n_tokens, con
     if (q.m != 1 || !q.embd.w) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "the greedy chain takes one row and an embedding table");
     if (q.token_id >= q.embd.n_out) return decline_decode(c, APK_ERR_INVALID_ARG, "token %u out of vocabulary %u", q.token_id, q.embd.n_out);
     if (n_tokens > 65536) return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "at most 65536 chained tokens per call");
+    if (q.attn_core == APK_ATTN_CAUSAL && (uint64_t)q.pos + n_tokens > q.kv->capacity)
+        return decline_decode(c, APK_DECLINE_INVALID_STATE, "the chain of %u tokens from position %u runs past the cache capacity %u", n_tokens,
+                              q.pos, q.kv->capacity);
     const uint64_t t0 = now_ns();
     APK_TRY(ensure_graph(c, &q));
     Plan *P = c->plan.get();
@@ -890,8 +893,6 @@ int apk_decode_greedy(apk_ctx *c, const apk_token_req *r, uint32_t n_tokens, con
     float *d_rope = reinterpret_cast<float *>(base + rope_off);
     const uint32_t init[2] = {q.token_id, 0u};
     CUDA_TRY(cudaMemcpyAsync(d_token, init, sizeof init, cudaMemcpyHostToDevice, c->stream));
-    if (q.attn_core == APK_ATTN_CAUSAL && (uint64_t)q.pos + n_tokens > q.kv->capacity)
-        return decline_decode(c, APK_ERR_INVALID_ARG, "the chain runs past the KV cache's capacity");
     CUDA_TRY(cudaMemcpyAsync(P->pos.p, &q.pos, sizeof(uint32_t), cudaMemcpyHostToDevice, c->stream));
     if (row) {
         CUDA_TRY(cudaMemcpyAsync(d_rope, rope, (size_t)n_tokens * row * 4, cudaMemcpyHostToDevice, c->stream));

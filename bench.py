@@ -470,15 +470,28 @@ def run_ours(args, rank, world, local_rank):
 
     # ---- N > 1: the two kinds of reduction must give the same token (before anything is timed)
     tp_check = None
+    exchange = args.tp_exchange
     if world > 1 and want_parity:
         outs = {}
+        g.debug_set_wait_limit(400_000_000)  # ~0.2 s per wait while checking: a broken exchange shows up as an error, not as a stall
         for kind in ("p2p", "nccl"):
             g.dist_set_exchange(kind == "p2p")
-            outs[kind] = g.decode_token_checked(slice1_req)
-        g.dist_set_exchange(args.tp_exchange == "p2p")
-        tp_check = {"layers": 1, "p2p_vs_nccl_rel_l2": rel_l2(outs["p2p"], outs["nccl"]),
-                    "argmax_equal": bool(int(np.argmax(outs["p2p"])) == int(np.argmax(outs["nccl"])))}
-        tp_check["ok"] = bool(tp_check["p2p_vs_nccl_rel_l2"] <= 2e-3 and tp_check["argmax_equal"])
+            try:
+                outs[kind] = g.decode_token_checked(slice1_req)
+            except G.GpuError as e:
+                outs[kind] = None
+                print(f"rank {rank}: {kind} exchange failed on the one-layer slice: {e}", file=sys.stderr, flush=True)
+        g.debug_set_wait_limit(0)
+        both = outs["p2p"] is not None and outs["nccl"] is not None
+        tp_check = {"layers": 1, "p2p_vs_nccl_rel_l2": rel_l2(outs["p2p"], outs["nccl"]) if both else None,
+                    "argmax_equal": bool(int(np.argmax(outs["p2p"])) == int(np.argmax(outs["nccl"]))) if both else None}
+        tp_check["ok"] = bool(both and tp_check["p2p_vs_nccl_rel_l2"] <= 2e-3 and tp_check["argmax_equal"])
+        # every rank must take the same decision: the peer-store exchange is used only if it checked out everywhere
+        bad = int(max_over_ranks([0.0 if (tp_check["ok"] or exchange != "p2p") else 1.0])[0])
+        if bad and outs["nccl"] is not None:
+            exchange = "nccl"
+            tp_check["fallback"] = "the peer-store exchange did not check out; timed with NCCL all-reduce"
+        g.dist_set_exchange(exchange == "p2p")
         g.decode_replay(req, 1)
 
     # ---- device-resident number: rounds of K graph replays, each between one CUDA-event pair
@@ -623,7 +636,7 @@ def run_ours(args, rank, world, local_rank):
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": DTYPE, "data": "synthetic",
-            "config": workload_config(n_layers, world, args.tp_exchange),
+            "config": workload_config(n_layers, world, exchange),
             "timed": {"rounds": int(len(ms_rounds)), "steps_per_round": args.steps, "seconds": float(np.sum(ms_rounds)) / 1e3,
                       "ms_per_step_min": float(np.min(ms_rounds)) / args.steps,
                       "ms_per_step_max": float(np.max(ms_rounds)) / args.steps, "reported": "median round"},

@@ -115,3 +115,48 @@ def test_decoder_layers_with_the_attention_core(orc, ty, m):
     kv.close()
     g.detach(r.buf)
     g.close()
+
+
+def test_greedy_chain_over_the_kv_cache(orc):
+    """decode_greedy_continue with the attention core: each step stores its K/V rows at the next cache
+    position (advanced on the device) and attends over everything before it.  The chain of n steps with
+    one synchronisation gives the ids of n single argmax calls, and leaves the same cache."""
+    from allpaka_b200 import gpu as G
+    from tests.test_gpu_token_ends import build
+
+    g = G.Gpu(0)
+    req, layers, head, embd, out_norm, d, r = build(g, orc, Q8_0, True, 7700)
+    n, pos0, tok0, cap = 6, 3, 41, 16
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(d["hd"])))
+    ropes = rope_table(orc, np.arange(n) + pos0, d["hd"], d["hd"])
+    rng = np.random.default_rng(5)
+    pre_k = f16_rows(orc, rng.standard_normal((pos0, d["nk"])).astype(np.float32))
+    pre_v = f16_rows(orc, rng.standard_normal((pos0, d["nk"])).astype(np.float32))
+    caches = []
+    for _ in range(2):
+        kv = G.KvCache(g, 2, d["nk"], cap)
+        for layer in range(2):
+            kv.write(layer, 0, pre_k, pre_v)   # a prefill handed over from elsewhere
+        caches.append(kv)
+    req.attn_core, req.scale = G.ATTN_CAUSAL, scale
+    req.kv, req.pos, req.token_id = caches[0], pos0, tok0
+    chain = g.decode_greedy(req, n, ropes)
+    assert chain is not None
+    tok, single = tok0, []
+    req.kv, req.argmax = caches[1], True
+    for i in range(n):
+        req.token_id, req.rope, req.pos = tok, ropes[i:i + 1], pos0 + i
+        tok = int(g.decode_token_checked(req)[0])
+        single.append(tok)
+    assert [int(t) for t in chain] == single
+    for layer in range(2):
+        ka, va = caches[0].read(layer, 0, pos0 + n)
+        kb, vb = caches[1].read(layer, 0, pos0 + n)
+        assert np.array_equal(ka, kb) and np.array_equal(va, vb)
+        assert np.array_equal(ka[:pos0], pre_k)
+    req.pos, req.kv = cap - 2, caches[0]
+    assert g.decode_greedy(req, n, ropes) is None and g.last_decline[0] == 6   # would run past the cache
+    for kv in caches:
+        kv.close()
+    g.detach(r.buf)
+    g.close()
