@@ -545,7 +545,7 @@ ActMode resolve_mode(uint32_t act_mode, uint32_t m) {
     return ActMode{f32 ? 1 : 0, (int)(f32 ? 2 * m : m)};
 }
 
-// x [m][n] (f32 or bf16) -> prepared activations for a consumer matrix of type `cty`.
+// x [m][n] (f32) -> prepared activations for a consumer matrix of type `cty`.
 int launch_prep(apk_ctx *c, const float *x, int ldx, const float *add, int ldadd, float *xout,
                 int ldxout, const float *gamma, float eps, float *hout, int ldh, uint32_t n, uint32_t m,
                 uint32_t cty, ActMode mode, void *act_base, const double *sumsq = nullptr) {
@@ -630,7 +630,7 @@ bool want_resident(apk_ctx *c, const DevMatrix *W, int m_eff) {
     return pick_stages(c, (int)W->ty, m_eff, PRO_LOAD, W->KS, L.rec_bytes()) >= 4;
 }
 
-// Activation source for a matvec on x (device, f32 or bf16): at one token the
+// Activation source for a matvec on x (device, f32): at one token the
 // kernel quantises in its own prologue (with the optional RMSNorm); otherwise
 // the separate pass writes records that are then loaded whole or streamed.
 int stage_acts(apk_ctx *c, const DevMatrix *W, const float *x, int ldx, const float *add, int ldadd,

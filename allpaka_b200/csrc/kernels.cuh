@@ -36,7 +36,6 @@
 // the same grid, is bounded).
 #pragma once
 
-#include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -157,7 +156,7 @@ struct PrepParams {
 enum Prologue : int {
     PRO_STREAM = 0,  // prepared records streamed with every unit (any m, any K)
     PRO_LOAD = 1,    // the whole prepared buffer bulk-loaded once into shared memory
-    PRO_QUANT = 2,   // x (f32/bf16) [+ addend] -> optional RMSNorm -> Q8 blocks, computed in the CTA
+    PRO_QUANT = 2,   // x (f32) [+ addend] -> optional RMSNorm -> Q8 blocks, computed in the CTA
 };
 
 struct MvParams {
