@@ -2039,7 +2039,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                         mma_block_s8(d1, a1, b0, b1);
                         const float dx0 = xd[t0];
                         // total += d_w * d_x * dot (q8_acts.rs:93), per (row, token)
-                        if (M > 1 && p.two_level) {
+                        if (M > 8 || (M > 1 && p.two_level)) {
                             // columns 2lt, 2lt+1 are the two digits of one token, d2 = d1 / 256:
                             // merge them as integers, scale once
                             const float dx1 = xd[t1];
@@ -2047,7 +2047,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                             acc[0][j][2] = fmaf(__fmul_rn(f01.y, dx1), (float)((d0[2] << 8) + d0[3]), acc[0][j][2]);
                             acc[1][j][0] = fmaf(__fmul_rn(f23.x, dx1), (float)((d1[0] << 8) + d1[1]), acc[1][j][0]);
                             acc[1][j][2] = fmaf(__fmul_rn(f23.y, dx1), (float)((d1[2] << 8) + d1[3]), acc[1][j][2]);
-                        } else {
+                        } else if constexpr (M <= 8) {
                             acc[0][j][0] = fmaf(__fmul_rn(f01.x, dx0), (float)d0[0], acc[0][j][0]);
                             acc[0][j][2] = fmaf(__fmul_rn(f01.y, dx0), (float)d0[2], acc[0][j][2]);
                             acc[1][j][0] = fmaf(__fmul_rn(f23.x, dx0), (float)d1[0], acc[1][j][0]);
@@ -2121,13 +2121,13 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                         const float dx0 = xd[t0], dx1 = xd[t1];
 #pragma unroll
                         for (int h = 0; h < 2; ++h) {
-                            if (M > 1 && p.two_level) {
+                            if (M > 8 || (M > 1 && p.two_level)) {
                                 // columns 2lt, 2lt+1 are the two digits of one token, d2 = d1 / 256
 #pragma unroll
                                 for (int i = 0; i < 4; i += 2)
                                     acc[h][j][i] = fmaf(__fmul_rn(dwr[2 * h + (i >> 1)], dx1), (float)(((long long)I[h][i] << 8) + I[h][i + 1]),
                                                         acc[h][j][i]);
-                            } else {
+                            } else if constexpr (M <= 8) {
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
                                     if (M == 1 && (i & 1)) continue;  // a single activation row has no odd column
@@ -2194,7 +2194,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                                 mma_block_s8(d1, nib ? hi[1] : lo[1], b0, b1);
                                 const float dx0 = ad[b * MP + t0], dx1 = ad[b * MP + t1];
                                 const float sx0 = as[b * MP + t0], sx1 = as[b * MP + t1];
-                                if (M > 1 && p.two_level) {
+                                // (more than 8 rows only ever are digit pairs: the other form is not compiled for them,
+                                // which halves the live accumulators of the instantiations that used to spill)
+                                if (M > 8 || (M > 1 && p.two_level)) {
                                     // digits merged as integers (d2 = d1 / 256); the min term rides on the first digit's row
 #pragma unroll
                                     for (int i = 0; i < 4; i += 2) {
@@ -2203,7 +2205,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                                         V[0][j][i] = fmaf(mnf[i >> 1], sx0, V[0][j][i]);
                                         V[1][j][i] = fmaf(mnf[2 + (i >> 1)], sx0, V[1][j][i]);
                                     }
-                                } else {
+                                } else if constexpr (M <= 8) {
 #pragma unroll
                                     for (int i = 0; i < 4; ++i) {
                                         if (M == 1 && (i & 1)) continue;  // a single activation row has no odd column

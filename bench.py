@@ -420,6 +420,22 @@ def run_configs(g, peak):
     g.synth_release()
     out["3"] = entry(us, 419205120, par, what="Q8_0 gate/up 25600x5120 + SwiGLU, down 5120x25600, m=6", ring_mb=2 * 417.8)
     g.detach(keep[1])
+
+    # config 3 in Q4_K (verify batch on the other north-star format)
+    gw, uw, dw = (synth.q4_k_matrix(o, i, s) for o, i, s in ((FFN, HIDDEN, 1030), (FFN, HIDDEN, 1031), (HIDDEN, FFN, 1032)))
+    for t in (gw, uw, dw):
+        assert g.attach(t)
+    got = g.ffn_batch([G.FfnReq(Q4_K, gw, Q4_K, uw, Q4_K, dw, HIDDEN, FFN, x, m)])[0]
+    par = rel_l2(got, orc.ffn(Q4_K, gw, Q4_K, uw, Q4_K, dw, HIDDEN, FFN, x, m))
+    for t in (gw, uw, dw):
+        g.detach(t)
+    del gw, uw, dw
+    copies, keep = ring([(FFN, HIDDEN), (FFN, HIDDEN), (HIDDEN, FFN)], 4, Q4_K, 75000)
+    us = g.bench_ring("ffn", [G.FfnReq(Q4_K, c[0], Q4_K, c[1], Q4_K, c[2], HIDDEN, FFN, x, m) for c in copies], reps=12)
+    g.synth_release()
+    nbytes = 3 * ty_bytes(Q4_K, FFN, HIDDEN) + 4 * m * (HIDDEN + HIDDEN)
+    out["3_q4_k"] = entry(us, nbytes, par, what="Q4_K gate/up 25600x5120 + SwiGLU, down 5120x25600, m=6", ring_mb=4 * 221.2)
+    g.detach(keep[1])
     return out
 
 
