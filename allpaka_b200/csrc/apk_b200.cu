@@ -61,6 +61,7 @@ bool block_geom(uint32_t ty, uint32_t *be, uint32_t *bb) {
     // crates/allpaka-dtype/src/lib.rs:79-108
     if (ty == APK_TY_Q8_0) { *be = 32; *bb = 34; return true; }
     if (ty == APK_TY_Q4_K) { *be = 256; *bb = 144; return true; }
+    if (ty == APK_TY_Q5_K) { *be = 256; *bb = 176; return true; }
     if (ty == APK_TY_Q6_K) { *be = 256; *bb = 210; return true; }
     return false;
 }
@@ -275,13 +276,14 @@ MvKernel pick_m(int m) {
 MvKernel pick_kernel(uint32_t ty, int m_eff, bool dump) {
     if (ty == APK_TY_Q8_0) return dump ? pick_m<TY_Q8_0, true>(m_eff) : pick_m<TY_Q8_0, false>(m_eff);
     if (ty == APK_TY_Q4_K) return dump ? pick_m<TY_Q4_K, true>(m_eff) : pick_m<TY_Q4_K, false>(m_eff);
+    if (ty == APK_TY_Q5_K) return dump ? pick_m<TY_Q5_K, true>(m_eff) : pick_m<TY_Q5_K, false>(m_eff);
     if (ty == APK_TY_Q6_K) return dump ? pick_m<TY_Q6_K, true>(m_eff) : pick_m<TY_Q6_K, false>(m_eff);
     return nullptr;
 }
 
 int init_kernel_attrs(apk_ctx *c) {
     static const int ms[] = {1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 14, 16};
-    for (uint32_t ty : {APK_TY_Q8_0, APK_TY_Q4_K, APK_TY_Q6_K})
+    for (uint32_t ty : {APK_TY_Q8_0, APK_TY_Q4_K, APK_TY_Q5_K, APK_TY_Q6_K})
         for (int m : ms)
             for (int dump = 0; dump < 2; ++dump) {
                 MvKernel k = pick_kernel(ty, m, dump != 0);
@@ -291,7 +293,9 @@ int init_kernel_attrs(apk_ctx *c) {
     return APK_OK;
 }
 
-int ke_of(uint32_t ty) { return ty == APK_TY_Q4_K ? 512 : 256; }
+int ke_of(uint32_t ty) { return ty_k45((int)ty) ? 512 : 256; }
+// consumers whose min term multiplies the exact f32 block sums of the activations (q8_acts.rs:257-258, 296-297)
+bool needs_sum(uint32_t ty) { return ty_k45((int)ty); }
 
 // --------------------------------------------------------------- matrices
 
@@ -332,10 +336,10 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
     m->n_in = n_in;
     m->nb = (int)(n_in / 32);
     m->n_tiles = (int)((n_out + TILE_ROWS - 1) / TILE_ROWS);
-    const int kt = ty == APK_TY_Q4_K ? Q4_KT_SB * 8 : Q8_KT;
+    const int kt = ty_k45((int)ty) ? Q4_KT_SB * 8 : Q8_KT;
     m->KS = (m->nb + kt - 1) / kt;
     m->tile_bytes = ty == APK_TY_Q8_0 ? (uint32_t)m->nb * Q8_BLOCK_UNIT
-                                      : (uint32_t)(m->nb / 8) * (ty == APK_TY_Q4_K ? Q4_SB_UNIT : Q6_SB_UNIT);
+                                      : (uint32_t)(m->nb / 8) * (ty == APK_TY_Q4_K ? Q4_SB_UNIT : (ty == APK_TY_Q5_K ? Q5_SB_UNIT : Q6_SB_UNIT));
     m->bytes = (size_t)m->n_tiles * m->tile_bytes;
     CUDA_TRY(cudaMalloc((void **)&m->d, m->bytes));
     CUDA_TRY(cudaMemsetAsync(m->d, 0, m->bytes, c->stream));
@@ -377,7 +381,9 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
             if (ty == APK_TY_Q8_0)
                 repack_q8_0_kernel<<<blocks, threads, 0, c->stream>>>(rp);
             else if (ty == APK_TY_Q4_K)
-                repack_q4_k_kernel<<<blocks, threads, 0, c->stream>>>(rp);
+                repack_q45_k_kernel<false><<<blocks, threads, 0, c->stream>>>(rp);
+            else if (ty == APK_TY_Q5_K)
+                repack_q45_k_kernel<true><<<blocks, threads, 0, c->stream>>>(rp);
             else
                 repack_q6_k_kernel<<<blocks, threads, 0, c->stream>>>(rp);
             CUDA_TRY(cudaGetLastError());
@@ -559,7 +565,7 @@ int launch_prep(apk_ctx *c, const float *x, int ldx, const float *add, int ldadd
     p.n = (int)n; p.m = (int)m;
     p.out = act_layout(act_base, cty, mode.m_eff);
     p.two_level = mode.two_level;
-    p.need_sum = cty == APK_TY_Q4_K;
+    p.need_sum = needs_sum(cty);
     dim3 grid((n / 32 + 7) / 8, m);
     CUDA_TRY(launch_ex(c, prep_acts_kernel, grid, dim3(256), 0, c->use_pdl, p, c->use_pdl ? 1 : 0));
     c->st.launches++;
@@ -649,7 +655,7 @@ int stage_acts(apk_ctx *c, const DevMatrix *W, const float *x, int ldx, const fl
         pp.n = (int)W->n_in; pp.m = (int)m;
         pp.out = p->act;
         pp.two_level = mode.two_level;
-        pp.need_sum = W->ty == APK_TY_Q4_K;
+        pp.need_sum = needs_sum(W->ty);
         return APK_OK;
     }
     APK_TRY(launch_prep(c, x, ldx, add, ldadd, xout, ldxout, gamma, eps, hout, (int)W->n_in, W->n_in, m, W->ty, mode,
@@ -752,7 +758,7 @@ int ffn_enqueue(apk_ctx *c, const FfnOp &op) {
     p.epi = EPI_SWIGLU;
     p.act_next = act_layout(c->act_b.p, op.D->ty, dmode.m_eff);
     p.next_two_level = dmode.two_level;
-    p.next_need_sum = op.D->ty == APK_TY_Q4_K;
+    p.next_need_sum = needs_sum(op.D->ty);
     p.ffn = (int)op.ffn;
     APK_TRY(launch_matvec(c, op.GU, p, q8));
     MvParams pd = mv_store(ActLayout{}, c->y_dev.as<float>(), (int)op.hidden);
@@ -969,7 +975,7 @@ int apk_matvec_batch(apk_ctx *c, const apk_matvec_req *reqs, uint32_t n_reqs, ui
         const apk_matvec_req &r = reqs[i];
         // items that share x share one activation quantisation (quantmat/mod.rs:372-388)
         const bool same = last_x == r.x && last_m == r.m && last_n == r.n_in && ke_of(last_ty) == ke_of(r.ty) &&
-                          (last_ty == APK_TY_Q4_K) == (r.ty == APK_TY_Q4_K);
+                          needs_sum(last_ty) == needs_sum(r.ty);
         if (!same)
             CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, r.x, (size_t)r.m * r.n_in * sizeof(float), cudaMemcpyHostToDevice,
                                      c->stream));
@@ -1184,6 +1190,8 @@ int apk_debug_synth_matrix(apk_ctx *c, void *w, uint32_t ty, uint32_t n_out, uin
         synth_q8_0_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
     else if (ty == APK_TY_Q4_K)
         synth_q4_k_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
+    else if (ty == APK_TY_Q5_K)
+        synth_q5_k_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
     else
         synth_q6_k_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
     c->st.launches++;

@@ -376,7 +376,7 @@ struct TokenLaunch {
             // attention core stand-in (identity): the roped Q slice, packed here, is wo's input
             p.q_next = act_layout(P->act_q.p, L.wo->ty, autom.m_eff);
             p.q_next_two_level = autom.two_level;
-            p.q_next_need_sum = L.wo->ty == APK_TY_Q4_K;
+            p.q_next_need_sum = needs_sum(L.wo->ty);
         }
         return launch(W, p, q8, L.wo);
     }
@@ -385,7 +385,7 @@ struct TokenLaunch {
         const ActLayout next = act_layout(P->act_q.p, L.wo->ty, autom.m_eff);
         return launch_attention(c, P->kv, layer, P->qkv.as<float>(), (int)(P->nq_l + 2 * P->nkv_l), m, P->nq_l / TILE_ROWS,
                                 P->pos.as<uint32_t>(), 0u, P->scale, P->attn_part.as<float>(), P->attn_out.as<float>(),
-                                (int)P->nq_l, &next, autom.two_level, L.wo->ty == APK_TY_Q4_K);
+                                (int)P->nq_l, &next, autom.two_level, needs_sum(L.wo->ty));
     }
     // next_*: the matvec that will read the updated rows through an RMSNorm (null: none)
     int residual(DevMatrix *W, void *records, const DevMatrix *next_W = nullptr, const float *next_gamma = nullptr,
@@ -428,7 +428,7 @@ struct TokenLaunch {
                 p.nq_gamma = next_gamma;
                 p.nq_act = act_layout(P->act_h.p, next_W->ty, next_mode.m_eff);
                 p.nq_two_level = next_mode.two_level;
-                p.nq_need_sum = next_W->ty == APK_TY_Q4_K;
+                p.nq_need_sum = needs_sum(next_W->ty);
                 prenormed_for = next_W;
                 prenormed_m_eff = next_mode.m_eff;
             }
@@ -442,7 +442,7 @@ struct TokenLaunch {
         p.epi = EPI_SWIGLU;
         p.act_next = act_layout(P->act_d.p, L.down->ty, autom.m_eff);
         p.next_two_level = autom.two_level;
-        p.next_need_sum = L.down->ty == APK_TY_Q4_K;
+        p.next_need_sum = needs_sum(L.down->ty);
         p.ffn = (int)P->ffn_l;
         return launch(L.gateup, p, q8, L.down);
     }
@@ -477,7 +477,7 @@ int launch_embed(apk_ctx *c, Plan *P, const uint32_t *token_dev, uint32_t token,
     ep.token = token;
     ep.x = x;
     ep.err = c->d_err;
-    const int threads = E->ty == APK_TY_Q8_0 ? E->nb * 8 : (E->nb / 8) * (E->ty == APK_TY_Q4_K ? 32 : 16);
+    const int threads = E->ty == APK_TY_Q8_0 ? E->nb * 8 : (E->nb / 8) * (ty_k45((int)E->ty) ? 32 : 16);
     embed_row_kernel<<<(threads + 255) / 256, 256, 0, c->stream>>>(ep);
     CUDA_TRY(cudaGetLastError());
     c->st.launches++;
@@ -670,7 +670,11 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
         // weights as stored in the GGUF file (padding rows of the tiled stream are not counted)
         double wb = orig_bytes(W);
         if (kind == 0 && L0.v) wb += orig_bytes(L0.v);
-        if (kind == 2) wb = 2.0 * (double)P->ffn_l * (H / 32) * (W->ty == APK_TY_Q8_0 ? 34 : (W->ty == APK_TY_Q4_K ? 144 : 210) / 8.0);
+        if (kind == 2) {
+            uint32_t be = 32, bb = 34;
+            block_geom(W->ty, &be, &bb);
+            wb = 2.0 * (double)P->ffn_l * (H / be) * bb;
+        }
         const double in_b = (double)m * W->n_in * 4.0;
         const double out_b = kind == 2 ? (double)m * P->ffn_l * 4.0 : (double)m * W->n_out * 4.0;
         bytes[kind] = wb + in_b + out_b;

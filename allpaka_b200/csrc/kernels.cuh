@@ -2,7 +2,7 @@
 //
 // Data layout in HBM ("tiled stream").  A [n_out, n_in] matrix is cut into
 // tiles of 128 output rows; a tile's K extent is cut into K-steps of 256
-// elements (Q8_0: 8 blocks; Q6_K: 1 super-block) or 512 elements (Q4_K: 2 super-blocks).  One
+// elements (Q8_0: 8 blocks; Q6_K: 1 super-block) or 512 elements (Q4_K, Q5_K: 2 super-blocks).  One
 // (tile, K-step) "unit" is ONE contiguous span of at most 36 KiB that a single
 // bulk async copy (cp.async.bulk + mbarrier complete_tx) brings into shared
 // memory.  Inside a unit the bytes sit in the order the tensor-core fragments
@@ -21,6 +21,8 @@
 //        gives the low-nibble sub-block, shifting the high one), 4096 B, then the header
 //        with the 6-bit scales and mins already split out into bytes: {d, dmin} f16 pairs
 //        [g][4 rows], scales [g][half of the sub-blocks][4 rows][4], mins likewise, 640 B
+//   Q5_K: as Q4_K, with the qh bytes (one high bit per element: sub-block j reads bit j) in the
+//        same fragment order between the nibbles and the header, 1024 B per row group
 //   Q6_K unit (one super-block): per row group, the ql bytes as nibble fragments like Q4_K's
 //        (chunk (half, byte group c): low nibbles = quarter c, high = quarter c + 2 of that half),
 //        4096 B; the qh bytes of each half in the same fragment order (quarter qi takes bits
@@ -48,9 +50,17 @@ constexpr int Q8_BLOCK_UNIT = 4352;  // 128 rows * 34 B
 constexpr int Q4_SB_RG = 4736;       // one row group of a super-block: 4096 B nibbles + 640 B header
 constexpr int Q4_SB_UNIT = 4 * Q4_SB_RG;  // 128 rows: 18944 B (18432 B of GGUF blocks + split scale bytes)
 constexpr int Q4_KT_SB = 2;          // Q4_K super-blocks per K-step (512 elements)
+constexpr int Q5_SB_RG = 5760;       // Q5_K: 4096 B nibbles + 1024 B high bits + 640 B header
+constexpr int Q5_SB_UNIT = 4 * Q5_SB_RG;  // 128 rows: 23040 B (22528 B of GGUF blocks + split scale bytes)
 constexpr int Q6_SB_RG = 6720;       // one row group of a Q6_K super-block: 4096 B ql + 2048 B qh + 512 B scales + 64 B d
 constexpr int Q6_SB_UNIT = 4 * Q6_SB_RG;  // 128 rows: 26880 B = 128 * 210 B
-__host__ __device__ constexpr int stage_w_bytes(int ty) { return ty == 8 ? 8 * 4352 : (ty == 14 ? 26880 : 2 * 18944); }  // one full K-step of weights
+__host__ __device__ constexpr int stage_w_bytes(int ty) {  // one full K-step of weights
+    return ty == 8 ? 8 * 4352 : (ty == 14 ? 26880 : (ty == 13 ? 2 * 23040 : 2 * 18944));
+}
+// Q4_K and Q5_K share everything but the fifth bit: row-group size and header offset of a super-block
+__host__ __device__ constexpr bool ty_k45(int ty) { return ty == 12 || ty == 13; }
+__host__ __device__ constexpr int k45_sb_rg(int ty) { return ty == 13 ? Q5_SB_RG : Q4_SB_RG; }
+__host__ __device__ constexpr int k45_hdr(int ty) { return ty == 13 ? 5120 : 4096; }
 constexpr int N_CONSUMER_WARPS = 16; // 4 row groups x 4 quarters of a K-step
 constexpr int K_SPLIT = 4;
 constexpr int N_CONSUMERS = N_CONSUMER_WARPS * 32;
@@ -61,6 +71,7 @@ constexpr int MAX_M_EFF = 16;
 constexpr int MAX_STAGES = 8;
 constexpr int TY_Q8_0 = 8;
 constexpr int TY_Q4_K = 12;
+constexpr int TY_Q5_K = 13;
 constexpr int TY_Q6_K = 14;
 
 // Error words written by kernels (never a trap): which bounded wait gave up.  The matvec kernel
@@ -390,6 +401,15 @@ __device__ __forceinline__ uint4 q6_k_unpack(const uint4 &ql, const uint4 &qh, i
     v.w |= ((qh.w >> sh) & 0x03030303u) << 4;
     return v;
 }
+// Q5_K: the fifth bit of the two sub-blocks of pair pr (low nibbles: bit 2*pr of each qh byte, high
+// nibbles: bit 2*pr + 1) onto the nibble fragments (crates/allpaka-backend/src/quantmat/q8_acts.rs:247-252)
+__device__ __forceinline__ void q5_k_high(uint4 &lo, uint4 &hi, const uint4 &qh, int pr) {
+    const int s = 2 * pr;
+    lo.x |= ((qh.x >> s) & 0x01010101u) << 4; lo.y |= ((qh.y >> s) & 0x01010101u) << 4;
+    lo.z |= ((qh.z >> s) & 0x01010101u) << 4; lo.w |= ((qh.w >> s) & 0x01010101u) << 4;
+    hi.x |= ((qh.x >> (s + 1)) & 0x01010101u) << 4; hi.y |= ((qh.y >> (s + 1)) & 0x01010101u) << 4;
+    hi.z |= ((qh.z >> (s + 1)) & 0x01010101u) << 4; hi.w |= ((qh.w >> (s + 1)) & 0x01010101u) << 4;
+}
 // byte i (0..15) of a 16-byte vector as a signed value
 __device__ __forceinline__ int s8_of(const uint4 &v, int i) {
     const int w = i >> 2;
@@ -704,23 +724,37 @@ __global__ void repack_q8_0_kernel(RepackParams p) {
     *sc = (uint16_t)(s[0] | (s[1] << 8));
 }
 
-// One thread per (row, super-block): 144 source bytes -> nibble fragments + split header.
-__global__ void repack_q4_k_kernel(RepackParams p) {
+// One thread per (row, super-block): 144 (Q4_K) or 176 (Q5_K) source bytes -> nibble fragments
+// [+ high-bit fragments] + split header.
+template <bool K5>
+__global__ void repack_q45_k_kernel(RepackParams p) {
+    constexpr int TY = K5 ? TY_Q5_K : TY_Q4_K;
+    constexpr int SB_RG = k45_sb_rg(TY), SB_UNIT = 4 * SB_RG;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int nsb = p.nb / 8;
     const size_t total = (size_t)p.src_rows * nsb;
     if (idx >= total) return;
     const int sb = (int)(idx % nsb), r = (int)(idx / nsb);
-    const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)sb * 144;
+    const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)sb * (K5 ? 176 : 144);
     const int dr = map_row(p, r);
     const int tile = dr / TILE_ROWS, rt = dr % TILE_ROWS;
     int rg, h16, g, upper;
     frag_pos(rt, rg, h16, g, upper);
     const int ks = sb / Q4_KT_SB, sl = sb % Q4_KT_SB;
-    uint8_t *base = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)ks * Q4_KT_SB * Q4_SB_UNIT +
-                    (size_t)sl * Q4_SB_UNIT + (size_t)rg * Q4_SB_RG;
+    uint8_t *base = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)ks * Q4_KT_SB * SB_UNIT +
+                    (size_t)sl * SB_UNIT + (size_t)rg * SB_RG;
     // nibble bytes: pair pr holds qs[32*pr .. 32*pr+31]; word w of the pair -> lane column w%4, k-half w/4
-    const uint8_t *qs = s + 16;
+    const uint8_t *qs = s + (K5 ? 48 : 16);
+    if (K5) {
+        // high bits: qh[0..31] in the same order (element l of sub-block j reads bit j of qh[l])
+        uint8_t *frag = base + 4096 + (size_t)(h16 * 32) * 16;
+        for (int w = 0; w < 8; ++w) {
+            const uint8_t *q = s + 16 + 4 * w;
+            const uint32_t v = (uint32_t)q[0] | ((uint32_t)q[1] << 8) | ((uint32_t)q[2] << 16) | ((uint32_t)q[3] << 24);
+            const int lane = g * 4 + (w & 3), reg = 2 * (w >> 2) + upper;
+            *reinterpret_cast<uint32_t *>(frag + lane * 16 + reg * 4) = v;
+        }
+    }
 #pragma unroll 4
     for (int pr = 0; pr < 4; ++pr) {
         uint8_t *frag = base + (size_t)((pr * 2 + h16) * 32) * 16;
@@ -732,7 +766,7 @@ __global__ void repack_q4_k_kernel(RepackParams p) {
         }
     }
     // header: {d, dmin} [g][4 rows] | scales [g][j half][4 rows][4] | mins likewise
-    uint8_t *hdr = base + 4096;
+    uint8_t *hdr = base + k45_hdr(TY);
     const int row4 = h16 * 2 + upper;  // which of rows g, g+8, g+16, g+24
     *reinterpret_cast<uint32_t *>(hdr + (g * 4 + row4) * 4) =
         (uint32_t)s[0] | ((uint32_t)s[1] << 8) | ((uint32_t)s[2] << 16) | ((uint32_t)s[3] << 24);
@@ -936,7 +970,7 @@ __global__ void __launch_bounds__(TILE_ROWS) attn_combine_kernel(AttnParams p, i
 // The embedding row of a token, dequantised straight out of the tiled stream (the LM head of a
 // model with tied embeddings is the same resident matrix): x[i] = d * q for Q8_0
 // (crates/allpaka-gguf/src/dequant.rs:93-126), d*sc*q - dmin*mn for Q4_K (dequant.rs:211-231),
-// d*sc*(q-32) for Q6_K (dequant.rs:271-296),
+// the same with the fifth bit for Q5_K (dequant.rs:238-263), d*sc*(q-32) for Q6_K (dequant.rs:271-296),
 // with the reference's operation order (two roundings, no fused multiply-add).
 struct EmbedParams {
     const uint8_t *W;         // tiled stream of the [vocab, hidden] table
@@ -999,12 +1033,16 @@ __global__ void __launch_bounds__(256) embed_row_kernel(EmbedParams p) {
         const int sb = idx >> 5, pr = (idx >> 3) & 3, w = idx & 7;
         if (sb >= p.nb / 8) return;
         const int ks = sb / Q4_KT_SB, sl = sb % Q4_KT_SB;
-        const uint8_t *base = p.W + (size_t)tile * p.tile_bytes + (size_t)ks * Q4_KT_SB * Q4_SB_UNIT + (size_t)sl * Q4_SB_UNIT +
-                              (size_t)rg * Q4_SB_RG;
+        const bool k5 = p.ty == TY_Q5_K;
+        const int sb_rg = k5 ? Q5_SB_RG : Q4_SB_RG, sb_unit = 4 * sb_rg;
+        const uint8_t *base = p.W + (size_t)tile * p.tile_bytes + (size_t)ks * Q4_KT_SB * sb_unit + (size_t)sl * sb_unit +
+                              (size_t)rg * sb_rg;
         const uint8_t *frag = base + (size_t)((pr * 2 + h16) * 32) * 16;
         const int lane = g * 4 + (w & 3), reg = 2 * (w >> 2) + upper;
         const uint32_t v = *reinterpret_cast<const uint32_t *>(frag + lane * 16 + reg * 4);
-        const uint8_t *hdr = base + 4096;
+        // Q5_K: bit 2*pr of qh[l] adds 16 to the low-nibble sub-block's element l, bit 2*pr+1 to the high one's (dequant.rs:253-260)
+        const uint32_t qh = k5 ? *reinterpret_cast<const uint32_t *>(base + 4096 + (size_t)(h16 * 32) * 16 + lane * 16 + reg * 4) : 0u;
+        const uint8_t *hdr = base + (k5 ? 5120 : 4096);
         const int row4 = h16 * 2 + upper;
         const uint32_t dd = *reinterpret_cast<const uint32_t *>(hdr + (g * 4 + row4) * 4);
         const float d = __half2float(__ushort_as_half((unsigned short)(dd & 0xffffu)));
@@ -1019,9 +1057,9 @@ __global__ void __launch_bounds__(256) embed_row_kernel(EmbedParams p) {
         float *o = p.x + sb * 256 + pr * 64 + 4 * w;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-            const uint32_t byte = (v >> (8 * k)) & 0xffu;
-            o[k] = __fsub_rn(__fmul_rn(d_sc1, (float)(byte & 0xfu)), dm1);
-            o[32 + k] = __fsub_rn(__fmul_rn(d_sc2, (float)(byte >> 4)), dm2);
+            const uint32_t byte = (v >> (8 * k)) & 0xffu, hb = (qh >> (8 * k + 2 * pr)) & 3u;
+            o[k] = __fsub_rn(__fmul_rn(d_sc1, (float)((byte & 0xfu) + ((hb & 1u) << 4))), dm1);
+            o[32 + k] = __fsub_rn(__fmul_rn(d_sc2, (float)((byte >> 4) + ((hb >> 1) << 4))), dm2);
         }
     }
 }
@@ -1100,6 +1138,23 @@ __global__ void synth_q4_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) 
     o[0] = (uint8_t)(d & 0xff); o[1] = (uint8_t)(d >> 8);
     o[2] = (uint8_t)(dm & 0xff); o[3] = (uint8_t)(dm >> 8);
     for (int i = 0; i < 140 / 4; ++i) {
+        const uint32_t h = (uint32_t)splitmix64(base + (uint64_t)i + 1);
+        o[4 + i * 4 + 0] = (uint8_t)h; o[4 + i * 4 + 1] = (uint8_t)(h >> 8);
+        o[4 + i * 4 + 2] = (uint8_t)(h >> 16); o[4 + i * 4 + 3] = (uint8_t)(h >> 24);
+    }
+}
+
+// Q5_K: as Q4_K with 32 more uniform bytes (the high bits).
+__global__ void synth_q5_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    uint8_t *o = dst + b * 176;
+    const uint64_t base = splitmix64(seed) ^ (b * 0x9E3779B97F4A7C15ull);
+    const unsigned short d = __half_as_ushort(__float2half_rn(absnormal(splitmix64(base ^ 0x53ull), 0.001f)));
+    const unsigned short dm = __half_as_ushort(__float2half_rn(absnormal(splitmix64(base ^ 0x54ull), 0.001f)));
+    o[0] = (uint8_t)(d & 0xff); o[1] = (uint8_t)(d >> 8);
+    o[2] = (uint8_t)(dm & 0xff); o[3] = (uint8_t)(dm >> 8);
+    for (int i = 0; i < 172 / 4; ++i) {
         const uint32_t h = (uint32_t)splitmix64(base + (uint64_t)i + 1);
         o[4 + i * 4 + 0] = (uint8_t)h; o[4 + i * 4 + 1] = (uint8_t)(h >> 8);
         o[4 + i * 4 + 2] = (uint8_t)(h >> 16); o[4 + i * 4 + 3] = (uint8_t)(h >> 24);
@@ -1439,7 +1494,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
     const uint32_t G = gridDim.x;
     const UnitOrder order(blockIdx.x * U / G, (blockIdx.x + 1) * U / G, (uint32_t)p.KS);
     const int n_total = order.n_total;
-    const int kt = (TY == TY_Q4_K) ? Q4_KT_SB * 8 : Q8_KT;  // 32-element blocks per full K-step
+    const int kt = ty_k45(TY) ? Q4_KT_SB * 8 : Q8_KT;  // 32-element blocks per full K-step
+    constexpr int K45_RG = k45_sb_rg(TY), K45_UNIT = 4 * K45_RG, K45_HDR = k45_hdr(TY);  // (meaningful for Q4_K / Q5_K)
+    constexpr bool K5 = TY == TY_Q5_K;
 
     if (warp == N_CONSUMER_WARPS) {
         // ------------------------------------------------ producer (one lane)
@@ -1459,8 +1516,8 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     wbytes = (uint32_t)Q6_SB_UNIT;
                     woff = (uint32_t)ks * Q6_SB_UNIT;
                 } else {
-                    wbytes = (uint32_t)(kb / 8) * Q4_SB_UNIT;
-                    woff = (uint32_t)ks * Q4_KT_SB * Q4_SB_UNIT;
+                    wbytes = (uint32_t)(kb / 8) * K45_UNIT;
+                    woff = (uint32_t)ks * Q4_KT_SB * K45_UNIT;
                 }
                 mbar_arrive_expect_tx(&full[s], wbytes + (streaming ? (uint32_t)act_rec : 0u));
                 bulk_g2s(stages + (size_t)s * stage_bytes, p.W + (size_t)t * p.tile_bytes + woff, wbytes, &full[s], pol_w);
@@ -1952,8 +2009,11 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
 #pragma unroll
                     for (int sbi = 0; sbi < Q4_KT_SB; ++sbi) {
                         if (sbi * 8 < kb) {
-                            const uint8_t *base = sw + sbi * Q4_SB_UNIT + rgc * Q4_SB_RG;
-                            const uint8_t *hdr = base + 4096;
+                            const uint8_t *base = sw + sbi * K45_UNIT + rgc * K45_RG;
+                            const uint8_t *hdr = base + K45_HDR;
+                            // Q5_K: the fifth bits of this 16-row half, all eight sub-blocks (sub-block j: bit j of every byte)
+                            uint4 qh5 = make_uint4(0u, 0u, 0u, 0u);
+                            if (K5) qh5 = *reinterpret_cast<const uint4 *>(base + 4096 + (h16c * 32 + lane) * 16);
                             // {d, dmin} of rows lg, lg+8 of this half
                             const uint2 dd = *reinterpret_cast<const uint2 *>(hdr + (lg * 4 + 2 * h16c) * 4);
                             float U[4] = {0.0f, 0.0f, 0.0f, 0.0f}, V[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -1968,9 +2028,10 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                                 for (int pi = 0; pi < BPC / 2; ++pi) {  // a byte holds sub-blocks 2*pr (low nibble), 2*pr+1 (high)
                                     const int pr = ch * (BPC / 2) + pi;
                                     const uint4 q = *reinterpret_cast<const uint4 *>(base + ((pr * 2 + h16c) * 32 + lane) * 16);
-                                    const uint4 lo = make_uint4(q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu);
-                                    const uint4 hi = make_uint4((q.x >> 4) & 0x0f0f0f0fu, (q.y >> 4) & 0x0f0f0f0fu,
-                                                                (q.z >> 4) & 0x0f0f0f0fu, (q.w >> 4) & 0x0f0f0f0fu);
+                                    uint4 lo = make_uint4(q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu);
+                                    uint4 hi = make_uint4((q.x >> 4) & 0x0f0f0f0fu, (q.y >> 4) & 0x0f0f0f0fu,
+                                                          (q.z >> 4) & 0x0f0f0f0fu, (q.w >> 4) & 0x0f0f0f0fu);
+                                    if (K5) q5_k_high(lo, hi, qh5, pr);
                                     mma_block_s8_acc(d, lo, my_blk == 2 * pi ? xb0 : 0u, my_blk == 2 * pi ? xb1 : 0u);
                                     mma_block_s8_acc(e, hi, my_blk == 2 * pi + 1 ? xb0 : 0u, my_blk == 2 * pi + 1 ? xb1 : 0u);
                                 }
@@ -2145,8 +2206,8 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 // this warp: super-block kq/2 of the K-step, sub-blocks 4*(kq&1) .. +3 (pairs 2*(kq&1), +1)
                 const int sb = kq >> 1, jh = kq & 1;
                 if (sb * 8 < kb) {
-                    const uint8_t *base = sw + sb * Q4_SB_UNIT + rg * Q4_SB_RG;
-                    const uint8_t *hdr = base + 4096;
+                    const uint8_t *base = sw + sb * K45_UNIT + rg * K45_RG;
+                    const uint8_t *hdr = base + K45_HDR;
                     const uint4 dd = *reinterpret_cast<const uint4 *>(hdr + lg * 16);                   // {d, dmin} of 4 rows
                     const uint4 scw = *reinterpret_cast<const uint4 *>(hdr + 128 + (lg * 2 + jh) * 16);  // 4 scales x 4 rows
                     const uint4 mnw = *reinterpret_cast<const uint4 *>(hdr + 384 + (lg * 2 + jh) * 16);  // 4 mins x 4 rows
@@ -2170,6 +2231,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                             lo[h] = make_uint4(q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu);
                             hi[h] = make_uint4((q.x >> 4) & 0x0f0f0f0fu, (q.y >> 4) & 0x0f0f0f0fu, (q.z >> 4) & 0x0f0f0f0fu,
                                                (q.w >> 4) & 0x0f0f0f0fu);
+                            if (K5) q5_k_high(lo[h], hi[h], *reinterpret_cast<const uint4 *>(base + 4096 + (h * 32 + lane) * 16), pr);
                         }
 #pragma unroll
                         for (int nib = 0; nib < 2; ++nib) {

@@ -106,14 +106,14 @@ extern "C" int apk_matvec_noalloc(apk_ctx *c, const void *w, uint32_t ty, uint32
         pp.n = (int)n_in; pp.m = 1;
         pp.out = p.act;
         pp.two_level = mode.two_level;
-        pp.need_sum = W->ty == APK_TY_Q4_K;
+        pp.need_sum = needs_sum(W->ty);
     } else {
         PrepParams pp{};
         pp.x = x_dev; pp.ldx = (int)n_in;
         pp.n = (int)n_in; pp.m = (int)m;
         pp.out = p.act;
         pp.two_level = mode.two_level;
-        pp.need_sum = W->ty == APK_TY_Q4_K;
+        pp.need_sum = needs_sum(W->ty);
         prep_acts_kernel<<<dim3((n_in / 32 + 7) / 8, m), 256, 0, st>>>(pp, 0);
         CUDA_TRY(cudaGetLastError());
         c->st.launches++;

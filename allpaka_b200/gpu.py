@@ -25,6 +25,7 @@ LIB_PATH = os.path.join(_HERE, "libapk_b200.so")
 # GGML type ids (crates/allpaka-dtype/src/lib.rs:61-75)
 Q8_0 = 8
 Q4_K = 12
+Q5_K = 13
 Q6_K = 14
 
 ACT_Q8, ACT_F32, ACT_AUTO = 0, 1, 2

@@ -13,9 +13,10 @@ import numpy as np
 
 TY_Q8_0 = 8
 TY_Q4_K = 12
+TY_Q5_K = 13
 TY_Q6_K = 14
 
-BLOCK = {TY_Q8_0: (32, 34), TY_Q4_K: (256, 144), TY_Q6_K: (256, 210)}
+BLOCK = {TY_Q8_0: (32, 34), TY_Q4_K: (256, 144), TY_Q5_K: (256, 176), TY_Q6_K: (256, 210)}
 
 
 def expected_bytes(ty: int, elements: int) -> int:
@@ -67,6 +68,23 @@ def q4_k_matrix(n_out: int, n_in: int, seed: int, d_sigma: float = 0.002) -> np.
     return out.reshape(-1)
 
 
+def q5_k_matrix(n_out: int, n_in: int, seed: int, d_sigma: float = 0.001) -> np.ndarray:
+    """Q5_K = ``{f16 d; f16 dmin; u8 scales[12]; u8 qh[32]; u8 qs[128]}`` (176 B, dequant.rs:238-263):
+    5-bit quants, 6-bit scales and mins uniform, d and dmin drawn as |N(0,sigma)|."""
+    rng = np.random.default_rng(seed)
+    nsb = n_in // 256
+    out = np.empty((n_out, nsb, 176), dtype=np.uint8)
+    d = np.abs(rng.normal(0.0, d_sigma, size=(n_out, nsb))).astype(np.float16)
+    dmin = np.abs(rng.normal(0.0, d_sigma, size=(n_out, nsb))).astype(np.float16)
+    sc = rng.integers(0, 64, size=(n_out, nsb, 8), dtype=np.uint8)
+    mn = rng.integers(0, 64, size=(n_out, nsb, 8), dtype=np.uint8)
+    out[:, :, 0:2] = d.view(np.uint8).reshape(n_out, nsb, 2)
+    out[:, :, 2:4] = dmin.view(np.uint8).reshape(n_out, nsb, 2)
+    out[:, :, 4:16] = pack_scales_k4(sc, mn)
+    out[:, :, 16:] = rng.integers(0, 256, size=(n_out, nsb, 160), dtype=np.uint8)
+    return out.reshape(-1)
+
+
 def q6_k_matrix(n_out: int, n_in: int, seed: int, d_sigma: float = 2.5e-5) -> np.ndarray:
     """6-bit quants uniform (every ql/qh byte uniform), signed 8-bit sub-block scales uniform in
     [-128,127], f16 d drawn as |N(0,sigma)|: weights of a few hundredths, like a model's (d of a
@@ -86,6 +104,8 @@ def matrix(ty: int, n_out: int, n_in: int, seed: int) -> np.ndarray:
         return q8_0_matrix(n_out, n_in, seed)
     if ty == TY_Q4_K:
         return q4_k_matrix(n_out, n_in, seed)
+    if ty == TY_Q5_K:
+        return q5_k_matrix(n_out, n_in, seed)
     if ty == TY_Q6_K:
         return q6_k_matrix(n_out, n_in, seed)
     raise ValueError(f"no generator for ggml type {ty}")
@@ -135,7 +155,7 @@ def tame_scales(buf: np.ndarray, ty: int, value: int = 0x211F) -> np.ndarray:
     be, bb = BLOCK[ty]
     v = buf.reshape(-1, bb)
     lo, hi = value & 0xFF, value >> 8
-    offs = {TY_Q8_0: (0,), TY_Q4_K: (0, 2), TY_Q6_K: (208,)}[ty]
+    offs = {TY_Q8_0: (0,), TY_Q4_K: (0, 2), TY_Q5_K: (0, 2), TY_Q6_K: (208,)}[ty]
     for o in offs:
         v[:, o] = lo
         v[:, o + 1] = hi

@@ -92,6 +92,7 @@ static int block_geom(uint32_t ty, size_t *be, size_t *bb) {
     /* crates/allpaka-dtype/src/lib.rs:79-108 */
     if (ty == ORC_TY_Q8_0) { *be = 32; *bb = 34; return 0; }
     if (ty == ORC_TY_Q4_K) { *be = 256; *bb = 144; return 0; }
+    if (ty == ORC_TY_Q5_K) { *be = 256; *bb = 176; return 0; }
     if (ty == ORC_TY_Q6_K) { *be = 256; *bb = 210; return 0; }
     return -1;
 }
@@ -131,6 +132,27 @@ static void dequant_q4_k_block(const uint8_t *b, float *out) {
     }
 }
 
+/* crates/allpaka-gguf/src/dequant.rs:238-263 */
+static void dequant_q5_k_block(const uint8_t *b, float *out) {
+    float d = orc_f16_to_f32(le16(b));
+    float dmin = orc_f16_to_f32(le16(b + 2));
+    const uint8_t *packed = b + 4, *qh = b + 16, *qs = b + 48;
+    for (int pair = 0; pair < 4; pair++) {
+        const uint8_t *q = qs + pair * 32;
+        float sc1, mn1, sc2, mn2;
+        orc_scale_min_k4(pair * 2, packed, &sc1, &mn1);
+        orc_scale_min_k4(pair * 2 + 1, packed, &sc2, &mn2);
+        float d_sc1 = d * sc1, dm1 = dmin * mn1, d_sc2 = d * sc2, dm2 = dmin * mn2;
+        uint8_t bit1 = (uint8_t)(1u << (pair * 2)), bit2 = (uint8_t)(1u << (pair * 2 + 1));
+        int base = pair * 64;
+        for (int l = 0; l < 32; l++) {
+            int hi1 = (qh[l] & bit1) ? 16 : 0, hi2 = (qh[l] & bit2) ? 16 : 0;
+            out[base + l] = d_sc1 * (float)((q[l] & 0xf) + hi1) - dm1;
+            out[base + 32 + l] = d_sc2 * (float)((q[l] >> 4) + hi2) - dm2;
+        }
+    }
+}
+
 /* The four 6-bit values that share index l of one 128-element half: ql low/high nibbles of bytes
  * l and l+32, high bits from successive 2-bit fields of qh[l], each minus 32
  * (crates/allpaka-gguf/src/dequant.rs:285-289; the same lines in q8_acts.rs:329-333). */
@@ -166,6 +188,7 @@ int orc_dequant(uint32_t ty, const uint8_t *bytes, size_t n_bytes, float *out, s
     for (size_t i = 0; i < n / be; i++) {
         if (ty == ORC_TY_Q8_0) dequant_q8_0_block(bytes + i * bb, out + i * be);
         else if (ty == ORC_TY_Q4_K) dequant_q4_k_block(bytes + i * bb, out + i * be);
+        else if (ty == ORC_TY_Q5_K) dequant_q5_k_block(bytes + i * bb, out + i * be);
         else dequant_q6_k_block(bytes + i * bb, out + i * be);
     }
     return 0;
@@ -253,6 +276,74 @@ float orc_dot_q4_k_i8(const uint8_t *row, size_t n_in, const float *dx, const fl
             total += d * sc1 * dot_lo - dmin * mn1 * sum[b_lo];
             total += d * sc2 * dot_hi - dmin * mn2 * sum[b_hi];
         }
+    }
+    return total;
+}
+
+/* The 5-bit values of the two sub-blocks of pair `pair` (q8_acts.rs:247-252). */
+static void q5_k_pair(const uint8_t *q, const uint8_t *qh, int pair, int8_t lo[32], int8_t hi[32]) {
+    for (int l = 0; l < 32; l++) {
+        uint8_t h1 = (uint8_t)(((qh[l] >> (pair * 2)) & 1) << 4), h2 = (uint8_t)(((qh[l] >> (pair * 2 + 1)) & 1) << 4);
+        lo[l] = (int8_t)((q[l] & 0x0f) | h1);
+        hi[l] = (int8_t)((q[l] >> 4) | h2);
+    }
+}
+
+/* crates/allpaka-backend/src/quantmat/q8_acts.rs:223-262 */
+float orc_dot_q5_k_i8(const uint8_t *row, size_t n_in, const float *dx, const float *sum, const int8_t *q8) {
+    float total = 0.0f;
+    size_t nsb = n_in / 256;
+    for (size_t bi = 0; bi < nsb; bi++) {
+        const uint8_t *block = row + bi * 176;
+        float d = orc_f16_to_f32(le16(block));
+        float dmin = orc_f16_to_f32(le16(block + 2));
+        const uint8_t *packed = block + 4, *qh = block + 16, *qs = block + 48;
+        for (int pair = 0; pair < 4; pair++) {
+            float sc1, mn1, sc2, mn2;
+            orc_scale_min_k4(pair * 2, packed, &sc1, &mn1);
+            orc_scale_min_k4(pair * 2 + 1, packed, &sc2, &mn2);
+            int8_t lo[32], hi[32];
+            q5_k_pair(qs + pair * 32, qh, pair, lo, hi);
+            size_t b_lo = bi * 8 + (size_t)pair * 2, b_hi = b_lo + 1;
+            float dot_lo = (float)dot_i8_32(lo, q8 + b_lo * 32) * dx[b_lo];
+            float dot_hi = (float)dot_i8_32(hi, q8 + b_hi * 32) * dx[b_hi];
+            total += d * sc1 * dot_lo - dmin * mn1 * sum[b_lo];
+            total += d * sc2 * dot_hi - dmin * mn2 * sum[b_hi];
+        }
+    }
+    return total;
+}
+
+/* crates/allpaka-backend/src/quantmat/dot_f32.rs:97-135 */
+float orc_dot_q5_k(const uint8_t *row, size_t n_in, const float *x) {
+    float total = 0.0f;
+    size_t nsb = n_in / 256;
+    for (size_t bi = 0; bi < nsb; bi++) {
+        const uint8_t *block = row + bi * 176;
+        float d = orc_f16_to_f32(le16(block));
+        float dmin = orc_f16_to_f32(le16(block + 2));
+        const uint8_t *packed = block + 4, *qh = block + 16, *qs = block + 48;
+        const float *xb = x + bi * 256;
+        float acc_d = 0.0f, acc_m = 0.0f;
+        for (int pair = 0; pair < 4; pair++) {
+            const uint8_t *q = qs + pair * 32;
+            const float *x_lo = xb + pair * 64, *x_hi = xb + pair * 64 + 32;
+            float sc1, mn1, sc2, mn2;
+            orc_scale_min_k4(pair * 2, packed, &sc1, &mn1);
+            orc_scale_min_k4(pair * 2 + 1, packed, &sc2, &mn2);
+            uint8_t bit1 = (uint8_t)(1u << (pair * 2)), bit2 = (uint8_t)(1u << (pair * 2 + 1));
+            float dot_lo = 0.0f, sum_lo = 0.0f, dot_hi = 0.0f, sum_hi = 0.0f;
+            for (int l = 0; l < 32; l++) {
+                int hi1 = (qh[l] & bit1) ? 16 : 0, hi2 = (qh[l] & bit2) ? 16 : 0;
+                dot_lo += (float)((q[l] & 0xf) + hi1) * x_lo[l];
+                sum_lo += x_lo[l];
+                dot_hi += (float)((q[l] >> 4) + hi2) * x_hi[l];
+                sum_hi += x_hi[l];
+            }
+            acc_d += sc1 * dot_lo + sc2 * dot_hi;
+            acc_m += mn1 * sum_lo + mn2 * sum_hi;
+        }
+        total += d * acc_d - dmin * acc_m;
     }
     return total;
 }
@@ -384,6 +475,17 @@ int orc_block_dots(uint32_t ty, const uint8_t *w, size_t n_out, size_t n_in, con
             if (ty == ORC_TY_Q8_0) {
                 for (size_t b = 0; b < nb; b++)
                     o[b] = dot_i8_32((const int8_t *)(row + b * 34 + 2), qi + b * 32);
+            } else if (ty == ORC_TY_Q5_K) {
+                for (size_t sb = 0; sb < n_in / 256; sb++) {
+                    const uint8_t *block = row + sb * 176;
+                    for (int pair = 0; pair < 4; pair++) {
+                        int8_t lo[32], hi[32];
+                        q5_k_pair(block + 48 + pair * 32, block + 16, pair, lo, hi);
+                        size_t b_lo = sb * 8 + (size_t)pair * 2;
+                        o[b_lo] = dot_i8_32(lo, qi + b_lo * 32);
+                        o[b_lo + 1] = dot_i8_32(hi, qi + (b_lo + 1) * 32);
+                    }
+                }
             } else if (ty == ORC_TY_Q6_K) {
                 /* per 32-element block the integer the f32 scale multiplies: sc0*dot0 + sc1*dot1
                  * (q8_acts.rs:338-342; exact in f32 there, |value| < 2^24) */
@@ -568,10 +670,13 @@ static inline float row_dot_any(const mm_ctx *c, size_t i, size_t j) {
             return orc_dot_q8_0_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
         if (c->ty == ORC_TY_Q6_K)
             return orc_dot_q6_k_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
+        if (c->ty == ORC_TY_Q5_K)
+            return orc_dot_q5_k_i8(row, c->n_in, c->d + i * nb, c->sum + i * nb, c->q + i * c->n_in);
         return orc_dot_q4_k_i8(row, c->n_in, c->d + i * nb, c->sum + i * nb, c->q + i * c->n_in);
     }
     const float *xi = c->x + i * c->n_in;
     if (c->ty == ORC_TY_Q6_K) return orc_dot_q6_k(row, c->n_in, xi);
+    if (c->ty == ORC_TY_Q5_K) return orc_dot_q5_k(row, c->n_in, xi);
     return c->ty == ORC_TY_Q8_0 ? orc_dot_q8_0(row, c->n_in, xi) : orc_dot_q4_k(row, c->n_in, xi);
 }
 

@@ -6,7 +6,7 @@ import pytest
 
 from allpaka_b200 import gguf
 from tests.test_gguf_reader import tiny_model
-from tests.util import Q4_K, Q6_K, Q8_0, oracle_logits, rel_l2, rope_table
+from tests.util import Q4_K, Q5_K, Q6_K, Q8_0, oracle_logits, rel_l2, rope_table
 
 pytestmark = pytest.mark.gpu
 
@@ -65,10 +65,11 @@ def oracle_step(orc, f, info, x, pos, kcs, vcs, pairwise):
 
 # the Q4_K_M recipe: V, down and the embedding / head in Q6_K, the rest in Q4_K
 K_M = {"attn_v.weight": Q6_K, "ffn_down.weight": Q6_K, "token_embd.weight": Q6_K, "output.weight": Q6_K}
+# the Q5_K_M recipe: the same tensors in Q6_K, the rest in Q5_K
 
 
 @pytest.mark.parametrize("arch,ty,tied,ty_of", [("qwen3", Q8_0, False, None), ("qwen3", Q4_K, True, None), ("qwen3", Q6_K, True, None),
-                                                 ("llama", Q8_0, False, None), ("qwen3", Q4_K, True, K_M), ("llama", Q4_K, False, K_M)])
+                                                 ("llama", Q8_0, False, None), ("qwen3", Q4_K, True, K_M), ("llama", Q4_K, False, K_M), ("qwen3", Q5_K, True, K_M)])
 def test_tokens_from_a_model_file(orc, tmp_path, arch, ty, tied, ty_of):
     from allpaka_b200 import gpu as G
 

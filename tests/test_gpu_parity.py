@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from allpaka_b200 import synth
-from tests.util import (Q4_K, Q6_K, Q8_0, Region, make_layer, oracle_decode, oracle_logits, rel_l2,
+from tests.util import (Q4_K, Q5_K, Q6_K, Q8_0, Region, make_layer, oracle_decode, oracle_logits, rel_l2,
                         rope_table)
 
 pytestmark = pytest.mark.gpu
@@ -66,6 +66,9 @@ def test_rmsnorm_prologue_feeds_identical_blocks(gpu, orc):
     (Q4_K, 256, 1024, 1),
     (Q4_K, 200, 5120, 2),
     (Q4_K, 64, 256, 8),
+    (Q5_K, 256, 1024, 1),
+    (Q5_K, 200, 5120, 2),
+    (Q5_K, 64, 256, 8),
     (Q6_K, 256, 1024, 1),     # per block: sc0*dot0 + sc1*dot1 of its two 16-element halves
     (Q6_K, 200, 5120, 2),
     (Q6_K, 130, 768, 4),
@@ -83,6 +86,25 @@ def test_int32_block_dots_are_bit_exact(gpu, orc, ty, n_out, n_in, m):
 
 
 # --------------------------------------------------------------------- matvec
+
+@pytest.mark.parametrize("n_out,n_in", [(1, 256), (48, 1024), (130, 768), (513, 5120), (64, 25600), (5120, 5120)])
+@pytest.mark.parametrize("m", [1, 3, 4, 6, 8])
+def test_q5_k_matvec_matches_oracle(gpu, orc, n_out, n_in, m):
+    """dot_q5_k_i8 (q8_acts.rs:223-262) for Q8 activations, dot_q5_k (dot_f32.rs:97-135) for f32 ones."""
+    w = synth.q5_k_matrix(n_out, n_in, 41)
+    r = attach(gpu, w)
+    x = synth.normal_f32((m, n_in), 42 + m)
+    errs = []
+    for mode, omode in ((0, orc.ACT_Q8), (1, orc.ACT_F32), (2, orc.ACT_AUTO)):
+        got = gpu.matvec(Q5_K, r.views[0], n_in, n_out, x, m, mode)
+        want = orc.matmul(Q5_K, w, n_out, n_in, x, m, omode)
+        errs.append(rel_l2(got, want))
+        assert errs[-1] <= TOL, (mode, errs)
+        if mode == 0:
+            assert errs[-1] <= 1e-5
+    print(f"Q5_K {n_out}x{n_in} m={m}: rel-L2 q8 {errs[0]:.1e} f32 {errs[1]:.1e}")
+    gpu.detach(r.buf)
+
 
 @pytest.mark.parametrize("n_out,n_in", [(1, 256), (48, 1024), (130, 768), (513, 5120), (64, 25600), (5120, 5120)])
 @pytest.mark.parametrize("m", [1, 3, 4, 6, 8])
@@ -310,7 +332,7 @@ def test_decode_token_matches_oracle_layer_stack(gpu, orc, ty, m, qk_norm):
     gpu.detach(r.buf)
 
 
-@pytest.mark.parametrize("ty,m", [(Q8_0, 1), (Q8_0, 3), (Q4_K, 1), (Q6_K, 1)])
+@pytest.mark.parametrize("ty,m", [(Q8_0, 1), (Q8_0, 3), (Q4_K, 1), (Q5_K, 1), (Q6_K, 1)])
 def test_decode_token_tiles_shared_by_many_ctas(gpu, orc, ty, m):
     """Shapes whose K dimension spreads one tile over up to eight CTAs (every CTA holds one unit),
     per-head norm on: the cross-CTA hand-off, the residual epilogue and the packed Q for wo."""

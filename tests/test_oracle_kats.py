@@ -11,7 +11,7 @@ import pytest
 
 from allpaka_b200 import synth
 
-Q8_0, Q4_K, Q6_K = 8, 12, 14
+Q8_0, Q4_K, Q5_K, Q6_K = 8, 12, 13, 14
 
 
 def half_bits(orc, x):
@@ -179,6 +179,44 @@ def q8_act_error_bound(w, x):
     return bound
 
 
+def test_q5_k_high_bit_adds_sixteen_for_the_owning_sub_block(orc):
+    """dequant.rs:470-495"""
+    block = np.zeros(176, dtype=np.uint8)
+    put_f16(orc, block, 0, 1.0)
+    put_f16(orc, block, 2, 0.0)
+    block[4:8] = 1          # scales of sub-blocks 0..3
+    block[12:16] = 0x01     # low nibble: scale of sub-blocks 4..7
+    block[16] = 0b0000_1001  # qh[0]: bit 0 -> sub-block 0, bit 3 -> sub-block 3
+    out = orc.dequant(Q5_K, block, 256)
+    assert out[0] == 16.0 and out[1] == 0.0
+    assert out[32] == 0.0                      # bit 1 not set: sub-block 1 unaffected
+    assert out[96] == 16.0 and out[97] == 0.0  # sub-block 3 = pair 1 high nibbles
+    assert orc.expected_bytes(Q5_K, 512) == 352 and orc.expected_bytes(Q5_K, 100) == 0
+
+
+def test_q5_k_block_dots_recombine_to_the_row_dot(orc):
+    """The int32 block dots are what dot_q5_k_i8 scales, the min term rides on the exact block sums
+    (q8_acts.rs:253-258)."""
+    x = synth.normal_f32(512, 25)
+    d, sm, q = orc.q8acts(x)
+    w = synth.q5_k_matrix(3, 512, 26)
+    dots = orc.block_dots(Q5_K, w, 3, 512, q)
+    wv = w.reshape(3, 2, 176)
+    for j in range(3):
+        total = np.float32(0.0)
+        for sb in range(2):
+            dd = np.float32(wv[j, sb, 0:2].view(np.float16)[0])
+            dmin = np.float32(wv[j, sb, 2:4].view(np.float16)[0])
+            for k in range(8):
+                sc, mn = orc.scale_min_k4(k, wv[j, sb, 4:16])
+                b = sb * 8 + k
+                dot = np.float32(np.float32(dots[0, j, b]) * d[b])
+                a = np.float32(np.float32(dd * np.float32(sc)) * dot)
+                m = np.float32(np.float32(dmin * np.float32(mn)) * sm[b])
+                total = np.float32(total + np.float32(a - m))
+        assert total == np.float32(orc.dot_row(Q5_K, wv[j].reshape(-1), x, q8=True))
+
+
 def test_q6_k_reassembles_six_bit_values_from_the_right_bits(orc):
     """dequant.rs:374-409: one chosen element per quarter, everything else zero."""
     block = np.zeros(210, dtype=np.uint8)
@@ -279,7 +317,7 @@ def kt_acts():
     return np.array([((i * 7 % 23) - 11.0) * 0.03 for i in range(N_IN)], dtype=np.float32)
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q4_K, Q6_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q4_K, Q5_K, Q6_K])
 def test_float_dot_kernels_match_the_dequantizer(orc, ty):
     """kernel_tests.rs:58-88"""
     x = kt_acts()
@@ -291,7 +329,7 @@ def test_float_dot_kernels_match_the_dequantizer(orc, ty):
     assert abs(got - want) <= 1e-4 * mag + 1e-5
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q4_K, Q6_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q4_K, Q5_K, Q6_K])
 def test_q8_activation_kernels_match_the_dequantizer(orc, ty):
     """kernel_tests.rs:90-121"""
     x = kt_acts()
