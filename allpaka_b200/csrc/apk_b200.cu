@@ -7,6 +7,7 @@
 // stream described in kernels.cuh.
 #include "../../include/allpaka_b200.h"
 #include "kernels.cuh"
+#include "mv_pick.h"
 
 #include <dlfcn.h>
 
@@ -252,32 +253,11 @@ namespace {
 
 // ------------------------------------------------------------ kernel table
 
-typedef void (*MvKernel)(const MvParams);
-
-template <int TY, bool DUMP>
-MvKernel pick_m(int m) {
-    switch (m) {
-        case 1: return matvec_streamk_kernel<TY, 1, DUMP>;
-        case 2: return matvec_streamk_kernel<TY, 2, DUMP>;
-        case 3: return matvec_streamk_kernel<TY, 3, DUMP>;
-        case 4: return matvec_streamk_kernel<TY, 4, DUMP>;
-        case 5: return matvec_streamk_kernel<TY, 5, DUMP>;
-        case 6: return matvec_streamk_kernel<TY, 6, DUMP>;
-        case 7: return matvec_streamk_kernel<TY, 7, DUMP>;
-        case 8: return matvec_streamk_kernel<TY, 8, DUMP>;
-        case 10: return matvec_streamk_kernel<TY, 10, DUMP>;
-        case 12: return matvec_streamk_kernel<TY, 12, DUMP>;
-        case 14: return matvec_streamk_kernel<TY, 14, DUMP>;
-        case 16: return matvec_streamk_kernel<TY, 16, DUMP>;
-        default: return nullptr;
-    }
-}
-
 MvKernel pick_kernel(uint32_t ty, int m_eff, bool dump) {
-    if (ty == APK_TY_Q8_0) return dump ? pick_m<TY_Q8_0, true>(m_eff) : pick_m<TY_Q8_0, false>(m_eff);
-    if (ty == APK_TY_Q4_K) return dump ? pick_m<TY_Q4_K, true>(m_eff) : pick_m<TY_Q4_K, false>(m_eff);
-    if (ty == APK_TY_Q5_K) return dump ? pick_m<TY_Q5_K, true>(m_eff) : pick_m<TY_Q5_K, false>(m_eff);
-    if (ty == APK_TY_Q6_K) return dump ? pick_m<TY_Q6_K, true>(m_eff) : pick_m<TY_Q6_K, false>(m_eff);
+    if (ty == APK_TY_Q8_0) return mv_pick_q8_0(m_eff, dump);
+    if (ty == APK_TY_Q4_K) return mv_pick_q4_k(m_eff, dump);
+    if (ty == APK_TY_Q5_K) return mv_pick_q5_k(m_eff, dump);
+    if (ty == APK_TY_Q6_K) return mv_pick_q6_k(m_eff, dump);
     return nullptr;
 }
 

@@ -36,6 +36,8 @@
 // publish their partial sums as tagged 64-bit words, it adds them in CTA order
 // (deterministic; no float atomics; its only wait, on CTAs of lower index of
 // the same grid, is bounded).
+// (The kernels that are not templates are `static`: this header is compiled into several
+// translation units, one per weight format for the matvec kernel, which are built side by side.)
 #pragma once
 
 #include <cuda_fp16.h>
@@ -541,7 +543,7 @@ __device__ __forceinline__ double block_rms_scale(const PrepParams &p, int m, do
 }
 
 // grid = (ceil(blocks / 8), m), 256 threads: each warp quantises one block.
-__global__ void __launch_bounds__(256) prep_acts_kernel(PrepParams p, int pdl) {
+static __global__ void __launch_bounds__(256) prep_acts_kernel(PrepParams p, int pdl) {
     __shared__ double red[8];
     if (pdl) {
         pdl_launch_dependents();
@@ -645,7 +647,7 @@ struct XchReduceParams {
 // quantised by a separate pass): grid = ceil(m*n / 1024), 256 threads, four floats per
 // thread.  Waits (bounded) for every rank's tagged words of the exchange and adds them in
 // rank order into the new residual rows.
-__global__ void __launch_bounds__(256) xch_reduce_kernel(XchReduceParams p) {
+static __global__ void __launch_bounds__(256) xch_reduce_kernel(XchReduceParams p) {
     if (p.pdl) {
         pdl_launch_dependents();
         pdl_wait();  // this rank's matvec (and its peer stores) is complete
@@ -699,7 +701,7 @@ __device__ __forceinline__ void frag_pos(int r, int &rg, int &h16, int &g, int &
 }
 
 // One thread per (row, block): 34 unaligned source bytes -> eight fragment words + scale.
-__global__ void repack_q8_0_kernel(RepackParams p) {
+static __global__ void repack_q8_0_kernel(RepackParams p) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t total = (size_t)p.src_rows * p.nb;
     if (idx >= total) return;
@@ -787,7 +789,7 @@ __global__ void repack_q45_k_kernel(RepackParams p) {
 }
 
 // One thread per (row, super-block): 210 source bytes -> nibble and high-bit fragments, scales, d.
-__global__ void repack_q6_k_kernel(RepackParams p) {
+static __global__ void repack_q6_k_kernel(RepackParams p) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int nsb = p.nb / 8;
     const size_t total = (size_t)p.src_rows * nsb;
@@ -854,7 +856,7 @@ struct AttnParams {
 };
 
 // grid (kv heads, splits, m), ATT_WARPS warps.  head_dim is 128.
-__global__ void __launch_bounds__(ATT_WARPS * 32) attn_split_kernel(AttnParams p, int pdl) {
+static __global__ void __launch_bounds__(ATT_WARPS * 32) attn_split_kernel(AttnParams p, int pdl) {
     if (pdl) {
         pdl_launch_dependents();
         pdl_wait();
@@ -944,7 +946,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32) attn_split_kernel(AttnParams p
 
 // grid (q heads, m), 128 threads: merge the splits of one head, normalise (attention.rs:391-398),
 // keep the f32 row and pack the head's four 32-element blocks for the output projection.
-__global__ void __launch_bounds__(TILE_ROWS) attn_combine_kernel(AttnParams p, int pdl) {
+static __global__ void __launch_bounds__(TILE_ROWS) attn_combine_kernel(AttnParams p, int pdl) {
     if (pdl) {
         pdl_launch_dependents();
         pdl_wait();
@@ -982,7 +984,7 @@ struct EmbedParams {
     int *err;
 };
 
-__global__ void __launch_bounds__(256) embed_row_kernel(EmbedParams p) {
+static __global__ void __launch_bounds__(256) embed_row_kernel(EmbedParams p) {
     uint32_t tok = p.token_dev ? *p.token_dev : p.token;
     if (tok >= (uint32_t)p.n_rows) tok = (uint32_t)p.n_rows - 1;  // (the host checks ids it can see; a chained id is an argmax over n_rows)
     const int tile = (int)(tok / TILE_ROWS), rt = (int)(tok % TILE_ROWS);
@@ -1077,7 +1079,7 @@ struct ChainParams {
     int n_steps;
     uint32_t *pos;         // cache position of the next token (advanced here)
 };
-__global__ void __launch_bounds__(128) chain_advance_kernel(ChainParams p) {
+static __global__ void __launch_bounds__(128) chain_advance_kernel(ChainParams p) {
     const uint32_t s = *p.step;
     if (threadIdx.x == 0) {
         p.hist[s] = *p.amax;
@@ -1109,7 +1111,7 @@ __device__ __forceinline__ float absnormal(uint64_t h, float sigma) {
     return fabsf(sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2)) * sigma;
 }
 // one thread per block of the raw row-major GGUF layout
-__global__ void synth_q8_0_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
+static __global__ void synth_q8_0_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
     uint8_t *o = dst + b * 34;
@@ -1128,7 +1130,7 @@ __global__ void synth_q8_0_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) 
         }
     }
 }
-__global__ void synth_q4_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
+static __global__ void synth_q4_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
     uint8_t *o = dst + b * 144;
@@ -1145,7 +1147,7 @@ __global__ void synth_q4_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) 
 }
 
 // Q5_K: as Q4_K with 32 more uniform bytes (the high bits).
-__global__ void synth_q5_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
+static __global__ void synth_q5_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
     uint8_t *o = dst + b * 176;
@@ -1162,7 +1164,7 @@ __global__ void synth_q5_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) 
 }
 
 // Q6_K: every ql/qh byte and every int8 sub-block scale uniform, d f16(|N(0,2.5e-5)|).
-__global__ void synth_q6_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
+static __global__ void synth_q6_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
     const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n_blocks) return;
     uint8_t *o = dst + b * 210;
