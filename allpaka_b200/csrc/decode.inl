@@ -103,9 +103,10 @@ int nccl_allreduce(apk_ctx *c, float *buf, size_t n) {
 
 bool uses_xch(const apk_ctx *c) { return c->p2p_ready && (c->world > 1 || c->self_xch); }
 
-// Position splits of the attention core: fixed per cache (the launch shape is captured), about
-// 256 positions per CTA at full capacity.
-int attn_splits(uint32_t capacity) { return (int)std::max<uint32_t>(1, std::min<uint32_t>(32, (capacity + 255) / 256)); }
+// Position splits of the attention core: fixed per cache (the launch shape is captured), 64 positions
+// per CTA at full capacity up to 128 splits (more CTAs than SMs: the kernel hides its load latency
+// with resident warps).
+int attn_splits(uint32_t capacity) { return (int)std::max<uint32_t>(1, std::min<uint32_t>(128, (capacity + 63) / 64)); }
 
 // q [m][ldq] -> attention over one layer of the cache -> optional f32 rows, optional records for wo.
 int launch_attention(apk_ctx *c, const apk_kv *kv, uint32_t layer, const float *q, int ldq, uint32_t m, uint32_t n_heads_l,
@@ -127,7 +128,15 @@ int launch_attention(apk_ctx *c, const apk_kv *kv, uint32_t layer, const float *
     ap.next_two_level = next_two_level;
     ap.next_need_sum = next_need_sum;
     const int pdl = c->use_pdl ? 1 : 0;
-    CUDA_TRY(launch_ex(c, attn_split_kernel, dim3(ap.n_kv_heads, ap.n_splits, m), dim3(ATT_WARPS * 32), 0, c->use_pdl, ap, pdl));
+    if (c->attn_tc) {
+        if (!c->attn_tc_ready) {
+            CUDA_TRY(cudaFuncSetAttribute((const void *)attn_split_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
+            c->attn_tc_ready = true;
+        }
+        CUDA_TRY(launch_ex(c, attn_split_tc_kernel, dim3(ap.n_kv_heads, ap.n_splits, m), dim3(ATC_WARPS * 32), (size_t)ATC_SMEM, c->use_pdl, ap, pdl));
+    } else {
+        CUDA_TRY(launch_ex(c, attn_split_kernel, dim3(ap.n_kv_heads, ap.n_splits, m), dim3(ATT_WARPS * 32), 0, c->use_pdl, ap, pdl));
+    }
     CUDA_TRY(launch_ex(c, attn_combine_kernel, dim3(n_heads_l, m), dim3(TILE_ROWS), 0, c->use_pdl, ap, pdl));
     c->st.launches += 2;
     return APK_OK;
@@ -1002,6 +1011,40 @@ int apk_attend(apk_ctx *c, const apk_kv *kv, uint32_t layer, const float *q, uin
     CUDA_TRY(cudaMemcpyAsync(out, c->y_dev.p, qn * 4, cudaMemcpyDeviceToHost, c->stream));
     c->st.calls++;
     return finish(c);
+}
+
+// Benchmark helper: apk_attend's launches over every layer of the cache in turn (distinct memory per
+// layer, so a cache larger than L2 is read from HBM), `reps` rounds between one pair of events.
+int apk_bench_attend(apk_ctx *c, const apk_kv *kv, const float *q, uint32_t m, uint32_t n_heads, uint32_t pos, float scale,
+                     uint32_t reps, float *us_per_layer) {
+    if (!c || !kv || !q || !us_per_layer || reps == 0) return fail(APK_ERR_INVALID_ARG, "bench_attend: null argument");
+    std::lock_guard<std::mutex> g(c->mu);
+    CUDA_TRY(cudaSetDevice(c->device));
+    APK_TRY(check_m(m));
+    const uint32_t n_kv = kv->kv_dim / TILE_ROWS;
+    if (c->world != 1 || n_heads == 0 || n_heads % n_kv || (uint64_t)pos + m > kv->capacity)
+        return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "bench_attend: %u heads over %u kv heads, positions to %u", n_heads, n_kv, pos + m - 1);
+    const size_t qn = (size_t)m * n_heads * TILE_ROWS;
+    APK_TRY(c->x_dev.ensure(qn * 4));
+    APK_TRY(c->y_dev.ensure(qn * 4));
+    APK_TRY(c->misc.ensure((size_t)m * n_heads * attn_splits(kv->capacity) * ATT_PART * 4));
+    CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, q, qn * 4, cudaMemcpyHostToDevice, c->stream));
+    auto pass = [&](uint32_t layer) {
+        return launch_attention(c, kv, layer, c->x_dev.as<float>(), (int)(n_heads * TILE_ROWS), m, n_heads, nullptr, pos, scale,
+                                c->misc.as<float>(), c->y_dev.as<float>(), (int)(n_heads * TILE_ROWS), nullptr, 0, 0);
+    };
+    for (uint32_t l = 0; l < kv->n_layers; ++l) APK_TRY(pass(l));
+    APK_TRY(finish(c));
+    CUDA_TRY(cudaEventRecord(c->ev0, c->stream));
+    for (uint32_t r = 0; r < reps; ++r)
+        for (uint32_t l = 0; l < kv->n_layers; ++l) APK_TRY(pass(l));
+    CUDA_TRY(cudaEventRecord(c->ev1, c->stream));
+    APK_TRY(finish(c));
+    float ms = 0.f;
+    CUDA_TRY(cudaEventElapsedTime(&ms, c->ev0, c->ev1));
+    *us_per_layer = ms * 1e3f / (float)(reps * kv->n_layers);
+    c->st.calls++;
+    return APK_OK;
 }
 
 }  // extern "C"

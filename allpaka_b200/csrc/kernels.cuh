@@ -832,10 +832,11 @@ static __global__ void repack_q6_k_kernel(RepackParams p) {
 // (crates/allpaka-model/src/model/attention.rs:337-399): per kv head, its GQA group of q heads
 // attends over cache positions 0..=pos with an online softmax; K and V live in the cache as f16
 // (model/kv.rs), scores and sums are f32.  HBM-bound on the cache bytes and far smaller than the
-// weight stream next to it (2 * positions * kv_dim * 2 B per layer), so plain SIMT: the positions
-// are split over CTAs, a warp walks its share one position at a time (lane = four of the 128
-// head dimensions), the splits are merged by a second small kernel that also packs the result as
-// the Q8 (or two-level) blocks the output projection consumes.
+// weight stream next to it at short contexts (2 * positions * kv_dim * 2 B per layer; as large as a
+// layer's Q|K|V weights from ~13k positions on), plain SIMT in f32 like the reference: the positions
+// are split over CTAs, a warp walks its share four positions at a time, the splits are merged by a
+// second small kernel that also packs the result as the Q8 (or two-level) blocks the output
+// projection consumes.
 constexpr int ATT_WARPS = 8;
 constexpr int ATT_MAX_GROUP = 8;       // q heads per kv head handled by one CTA pass
 constexpr int ATT_PART = TILE_ROWS + 4;  // floats per partial: acc[128], running max, denominator, pad (16-byte rows)
@@ -856,83 +857,311 @@ struct AttnParams {
 };
 
 // grid (kv heads, splits, m), ATT_WARPS warps.  head_dim is 128.
+// A warp serves ATT_HPW q heads of the kv head's group and takes four positions per step: eight
+// lanes per position, 16 head dimensions (two 16-byte loads of K, two of V) per lane, so a score
+// needs three shuffle rounds, the loads of the next step are in flight while this one is reduced,
+// and the running state (max, denominator, 16 x ATT_HPW accumulators) stays in registers.  The
+// warps of a CTA are (pair of heads) x (position slot); the K and V rows a CTA touches are read
+// by its head-pair warps out of L1 after the first.
+constexpr int ATT_HPW = 2;
 static __global__ void __launch_bounds__(ATT_WARPS * 32) attn_split_kernel(AttnParams p, int pdl) {
     if (pdl) {
         pdl_launch_dependents();
         pdl_wait();
     }
-    __shared__ float sm[ATT_WARPS][ATT_MAX_GROUP][ATT_PART];
+    // one state per (warp, position subgroup, head of the warp)
+    __shared__ float sm[ATT_WARPS * 4 * ATT_HPW][ATT_PART];
     const int kvh = blockIdx.x, split = blockIdx.y, row = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int sg = lane >> 3, c = lane & 7;  // position within the step, 16-dimension chunk
     const uint32_t pos = (p.pos_dev ? *p.pos_dev : p.pos) + (uint32_t)row;  // this row sees positions 0..=pos
     const uint32_t n_pos = pos + 1u;
     const uint32_t per = (n_pos + (uint32_t)p.n_splits - 1u) / (uint32_t)p.n_splits;
     const uint32_t t0 = (uint32_t)split * per, t1 = min(n_pos, t0 + per);
     for (int g0 = 0; g0 < p.group; g0 += ATT_MAX_GROUP) {
         const int G = min(ATT_MAX_GROUP, p.group - g0);
-        float4 q[ATT_MAX_GROUP], acc[ATT_MAX_GROUP];
-        float mx[ATT_MAX_GROUP], dn[ATT_MAX_GROUP];
+        const int n_hp = (G + ATT_HPW - 1) / ATT_HPW, n_pp = ATT_WARPS / n_hp;  // head pairs, position slots
+        const int hp = warp % n_hp, pp = warp / n_hp;
+        const bool busy = pp < n_pp;
+        float q[ATT_HPW][16], acc[ATT_HPW][16], mx[ATT_HPW], dn[ATT_HPW];
 #pragma unroll
-        for (int h = 0; h < ATT_MAX_GROUP; ++h) {
-            q[h] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (h < G) q[h] = *reinterpret_cast<const float4 *>(p.q + (size_t)row * p.ldq + (size_t)(kvh * p.group + g0 + h) * TILE_ROWS + 4 * lane);
-            acc[h] = make_float4(0.f, 0.f, 0.f, 0.f);
-            mx[h] = -INFINITY;
-            dn[h] = 0.0f;
+        for (int hh = 0; hh < ATT_HPW; ++hh) {
+            const int h = ATT_HPW * hp + hh;
+            const bool on = busy && h < G;
+            const float *qp = p.q + (size_t)row * p.ldq + (size_t)(kvh * p.group + g0 + (on ? h : 0)) * TILE_ROWS + 16 * c;
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+                const float4 v = on ? *reinterpret_cast<const float4 *>(qp + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                q[hh][i] = v.x; q[hh][i + 1] = v.y; q[hh][i + 2] = v.z; q[hh][i + 3] = v.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[hh][i] = 0.0f;
+            mx[hh] = -INFINITY;
+            dn[hh] = 0.0f;
         }
-        for (uint32_t t = t0 + (uint32_t)warp; t < t1; t += ATT_WARPS) {
-            const uint2 kr = *reinterpret_cast<const uint2 *>(p.kc + (size_t)t * p.kv_dim + (size_t)kvh * TILE_ROWS + 4 * lane);
-            const uint2 vr = *reinterpret_cast<const uint2 *>(p.vc + (size_t)t * p.kv_dim + (size_t)kvh * TILE_ROWS + 4 * lane);
-            const float2 k01 = __half22float2(*reinterpret_cast<const __half2 *>(&kr.x));
-            const float2 k23 = __half22float2(*reinterpret_cast<const __half2 *>(&kr.y));
-            const float2 v01 = __half22float2(*reinterpret_cast<const __half2 *>(&vr.x));
-            const float2 v23 = __half22float2(*reinterpret_cast<const __half2 *>(&vr.y));
+        if (busy) {
+            const size_t col = (size_t)kvh * TILE_ROWS + 16 * c;
+            const uint32_t stride = (uint32_t)n_pp * 4u;
+            // the rows of the next step are requested before this step's are used
+            uint4 kn0, kn1, vn0, vn1;
+            auto fetch = [&](uint32_t tb) {
+                const uint32_t t = tb + (uint32_t)sg;
+                const size_t off = (size_t)(t < t1 ? t : t0) * p.kv_dim + col;
+                kn0 = __ldg(reinterpret_cast<const uint4 *>(p.kc + off));
+                kn1 = __ldg(reinterpret_cast<const uint4 *>(p.kc + off + 8));
+                vn0 = __ldg(reinterpret_cast<const uint4 *>(p.vc + off));
+                vn1 = __ldg(reinterpret_cast<const uint4 *>(p.vc + off + 8));
+            };
+            const uint32_t tb0 = t0 + (uint32_t)pp * 4u;
+            if (tb0 < t1) fetch(tb0);
+            for (uint32_t tb = tb0; tb < t1; tb += stride) {
+                const bool valid = tb + (uint32_t)sg < t1;
+                const uint32_t kw[8] = {kn0.x, kn0.y, kn0.z, kn0.w, kn1.x, kn1.y, kn1.z, kn1.w};
+                const uint32_t vw[8] = {vn0.x, vn0.y, vn0.z, vn0.w, vn1.x, vn1.y, vn1.z, vn1.w};
+                if (tb + stride < t1) fetch(tb + stride);
+                float k[16], v[16];
 #pragma unroll
-            for (int h = 0; h < ATT_MAX_GROUP; ++h) {
-                if (h < G) {
-                    float s = q[h].x * k01.x + q[h].y * k01.y + q[h].z * k23.x + q[h].w * k23.y;
+                for (int i = 0; i < 8; ++i) {
+                    const float2 kf = __half22float2(*reinterpret_cast<const __half2 *>(&kw[i]));
+                    const float2 vf = __half22float2(*reinterpret_cast<const __half2 *>(&vw[i]));
+                    k[2 * i] = kf.x; k[2 * i + 1] = kf.y;
+                    v[2 * i] = vf.x; v[2 * i + 1] = vf.y;
+                }
 #pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+                for (int hh = 0; hh < ATT_HPW; ++hh) {
+                    float s = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) s = fmaf(q[hh][i], k[i], s);
+                    s += __shfl_xor_sync(0xffffffffu, s, 1);
+                    s += __shfl_xor_sync(0xffffffffu, s, 2);
+                    s += __shfl_xor_sync(0xffffffffu, s, 4);
                     s *= p.scale;
-                    if (s > mx[h]) {
-                        if (dn[h] > 0.0f) {
-                            const float r = expf(mx[h] - s);
-                            acc[h].x *= r; acc[h].y *= r; acc[h].z *= r; acc[h].w *= r;
-                            dn[h] *= r;
-                        }
-                        mx[h] = s;
-                    }
-                    const float pr = expf(s - mx[h]);
-                    dn[h] += pr;
-                    acc[h].x += pr * v01.x; acc[h].y += pr * v01.y; acc[h].z += pr * v23.x; acc[h].w += pr * v23.y;
+                    // online softmax without a branch: a maximum that stays gives r = exp(0) = 1 exactly,
+                    // so this is attend_group's update (model/attention.rs:366-388) value for value
+                    const float m_new = valid ? fmaxf(mx[hh], s) : mx[hh];
+                    const float r = mx[hh] == -INFINITY ? 0.0f : expf(mx[hh] - m_new);
+                    const float pr = valid ? expf(s - m_new) : 0.0f;
+                    dn[hh] = fmaf(dn[hh], r, pr);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) acc[hh][i] = fmaf(pr, v[i], acc[hh][i] * r);
+                    mx[hh] = m_new;
                 }
             }
         }
-        // merge the warps' running states, head by head
+        // every (warp, subgroup, head) state into shared memory, then one warp per head merges them
         __syncthreads();
 #pragma unroll
-        for (int h = 0; h < ATT_MAX_GROUP; ++h)
-            if (h < G) {
-                *reinterpret_cast<float4 *>(&sm[warp][h][4 * lane]) = acc[h];
-                if (lane == 0) {
-                    sm[warp][h][TILE_ROWS] = mx[h];
-                    sm[warp][h][TILE_ROWS + 1] = dn[h];
-                }
+        for (int hh = 0; hh < ATT_HPW; ++hh) {
+            float *st = sm[(warp * 4 + sg) * ATT_HPW + hh];
+#pragma unroll
+            for (int i = 0; i < 16; i += 4)
+                *reinterpret_cast<float4 *>(st + 16 * c + i) = make_float4(acc[hh][i], acc[hh][i + 1], acc[hh][i + 2], acc[hh][i + 3]);
+            if (c == 0) {
+                st[TILE_ROWS] = busy ? mx[hh] : -INFINITY;
+                st[TILE_ROWS + 1] = busy ? dn[hh] : 0.0f;
             }
+        }
         __syncthreads();
         for (int h = warp; h < G; h += ATT_WARPS) {
+            const int hp_h = h / ATT_HPW, hh = h % ATT_HPW;
+            float M = -INFINITY;
+            for (int w = hp_h; w < n_hp * n_pp; w += n_hp)
+#pragma unroll
+                for (int s4 = 0; s4 < 4; ++s4) M = fmaxf(M, sm[(w * 4 + s4) * ATT_HPW + hh][TILE_ROWS]);
+            float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+            float d = 0.0f;
+            for (int w = hp_h; w < n_hp * n_pp; w += n_hp)
+#pragma unroll
+                for (int s4 = 0; s4 < 4; ++s4) {
+                    const float *st = sm[(w * 4 + s4) * ATT_HPW + hh];
+                    const float mw = st[TILE_ROWS];
+                    const float r = mw == -INFINITY ? 0.0f : expf(mw - M);
+                    const float4 aw = *reinterpret_cast<const float4 *>(st + 4 * lane);
+                    a.x += r * aw.x; a.y += r * aw.y; a.z += r * aw.z; a.w += r * aw.w;
+                    d += r * st[TILE_ROWS + 1];
+                }
+            float *dst = p.part + (((size_t)row * (p.n_kv_heads * p.group) + (size_t)(kvh * p.group + g0 + h)) * p.n_splits + split) * ATT_PART;
+            *reinterpret_cast<float4 *>(dst + 4 * lane) = a;
+            if (lane == 0) {
+                dst[TILE_ROWS] = M;
+                dst[TILE_ROWS + 1] = d;
+            }
+        }
+        __syncthreads();  // the states are rewritten by the next group of heads
+    }
+}
+
+// The same on tensor cores, for the long contexts where the cache is the larger stream.  K and V
+// are f16 in the cache already; q and the softmax weights are f32, so each is fed as two f16
+// fragments (value = hi + lo, lo = f16(value - hi)): the products are exact in the f32
+// accumulator and the split costs one more mma, which keeps the result at f32 rounding level
+// (the reference computes f32 x f16 in f32).  grid (kv heads, splits, m), ATC_WARPS warps; a warp
+// takes 16 positions per step: cp.async brings their K and V rows (2 x 4 KB) into its own
+// double-buffered stage, ldmatrix (transposed for V) forms the B fragments, S = Q K^T is 8 k-steps
+// x 2 position tiles x {hi, lo}, the online softmax runs on the accumulator fragments (rows =
+// the group's heads, four lanes per row), O += P V is 16 dimension tiles x {hi, lo}.  Rows 8..15 of
+// the 16-row mma stay zero (a GQA group has at most 8 heads per pass).
+constexpr int ATC_WARPS = 4;
+constexpr int ATC_ROW = TILE_ROWS + 8;   // halves per staged row: 272 B, so the eight rows of an ldmatrix hit distinct banks
+constexpr int ATC_STAGE = 2 * 16 * ATC_ROW;  // halves per stage: K tile, then V tile
+constexpr int ATC_SMEM = ATC_WARPS * 2 * ATC_STAGE * 2 + ATC_WARPS * ATT_MAX_GROUP * ATT_PART * 4;
+
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    // rows 8..15 of A (registers a1, a3) are zero
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void split_f16x2(float x, float y, uint32_t &hi, uint32_t &lo) {
+    const __half2 h = __floats2half2_rn(x, y);
+    const float2 hf = __half22float2(h);
+    const __half2 l = __floats2half2_rn(x - hf.x, y - hf.y);
+    hi = *reinterpret_cast<const uint32_t *>(&h);
+    lo = *reinterpret_cast<const uint32_t *>(&l);
+}
+
+static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(AttnParams p, int pdl) {
+    if (pdl) {
+        pdl_launch_dependents();
+        pdl_wait();
+    }
+    extern __shared__ __align__(16) uint8_t att_smem[];
+    __half *stages = reinterpret_cast<__half *>(att_smem);
+    float *merge = reinterpret_cast<float *>(att_smem + ATC_WARPS * 2 * ATC_STAGE * 2);  // [warp][head][ATT_PART]
+    const int kvh = blockIdx.x, split = blockIdx.y, row = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t pos = (p.pos_dev ? *p.pos_dev : p.pos) + (uint32_t)row;
+    const uint32_t n_pos = pos + 1u;
+    const uint32_t per = (n_pos + (uint32_t)p.n_splits - 1u) / (uint32_t)p.n_splits;
+    const uint32_t t0 = (uint32_t)split * per, t1 = min(n_pos, t0 + per);
+    __half *my = stages + (size_t)warp * 2 * ATC_STAGE;
+    const uint32_t my_s = (uint32_t)__cvta_generic_to_shared(my);
+    for (int g0 = 0; g0 < p.group; g0 += ATT_MAX_GROUP) {
+        const int G = min(ATT_MAX_GROUP, p.group - g0);
+        // q of head g as A fragments (hi and lo), eight k-steps of 16 dimensions
+        uint32_t qh[8][2], ql[8][2];
+        {
+            const float *qp = p.q + (size_t)row * p.ldq + (size_t)(kvh * p.group + g0 + (g < G ? g : 0)) * TILE_ROWS;
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                float2 x0 = make_float2(0.f, 0.f), x1 = make_float2(0.f, 0.f);
+                if (g < G) {
+                    x0 = *reinterpret_cast<const float2 *>(qp + 16 * ks + 2 * t);
+                    x1 = *reinterpret_cast<const float2 *>(qp + 16 * ks + 2 * t + 8);
+                }
+                split_f16x2(x0.x, x0.y, qh[ks][0], ql[ks][0]);
+                split_f16x2(x1.x, x1.y, qh[ks][1], ql[ks][1]);
+            }
+        }
+        float o[16][4];
+#pragma unroll
+        for (int nt = 0; nt < 16; ++nt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) o[nt][i] = 0.0f;
+        float mx = -INFINITY, dn = 0.0f;
+        // this warp's 16 positions of step i: t0 + 16 * (warp + ATC_WARPS * i)
+        auto stage_load = [&](uint32_t p0, int st) {
+            // 16 rows x 256 B of K and of V: 512 16-byte chunks, 16 per lane
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const int ch = j * 32 + lane, kvsel = ch >> 8, r = (ch >> 4) & 15, cc = ch & 15;
+                const uint32_t tr = min(p0 + (uint32_t)r, t1 - 1u);  // rows past the end repeat the last one; their scores are masked
+                const __half *src = (kvsel ? p.vc : p.kc) + (size_t)tr * p.kv_dim + (size_t)kvh * TILE_ROWS + 8 * cc;
+                const uint32_t dst = my_s + (uint32_t)((st * ATC_STAGE + kvsel * 16 * ATC_ROW + r * ATC_ROW + 8 * cc) * 2);
+                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        const uint32_t first = t0 + 16u * (uint32_t)warp, stride = 16u * ATC_WARPS;
+        if (first < t1) stage_load(first, 0);
+        int st = 0;
+        for (uint32_t p0 = first; p0 < t1; p0 += stride, st ^= 1) {
+            if (p0 + stride < t1) {
+                stage_load(p0 + stride, st ^ 1);
+                asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else {
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+            }
+            __syncwarp();
+            const uint32_t ks_base = my_s + (uint32_t)(st * ATC_STAGE * 2);
+            const uint32_t vs_base = ks_base + 16 * ATC_ROW * 2;
+            // S = Q K^T for two tiles of 8 positions
+            float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int ks = 0; ks < 8; ++ks) {
+                uint32_t b00, b01, b10, b11;
+                const uint32_t addr = ks_base + (uint32_t)((((lane >> 4) * 8 + (lane & 7)) * ATC_ROW + 16 * ks + ((lane >> 3) & 1) * 8) * 2);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b00), "=r"(b01), "=r"(b10), "=r"(b11) : "r"(addr));
+                mma_f16(s0, qh[ks][0], qh[ks][1], b00, b01);
+                mma_f16(s0, ql[ks][0], ql[ks][1], b00, b01);
+                mma_f16(s1, qh[ks][0], qh[ks][1], b10, b11);
+                mma_f16(s1, ql[ks][0], ql[ks][1], b10, b11);
+            }
+            // online softmax on row g (this lane: positions p0 + 2t, +1 and p0 + 8 + 2t, +1)
+            float sc[4];
+            sc[0] = (p0 + 2 * t < t1) ? s0[0] * p.scale : -INFINITY;
+            sc[1] = (p0 + 2 * t + 1 < t1) ? s0[1] * p.scale : -INFINITY;
+            sc[2] = (p0 + 8 + 2 * t < t1) ? s1[0] * p.scale : -INFINITY;
+            sc[3] = (p0 + 8 + 2 * t + 1 < t1) ? s1[1] * p.scale : -INFINITY;
+            float mt = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+            mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
+            mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
+            const float m_new = fmaxf(mx, mt);  // (position p0 itself is always valid, so m_new is finite)
+            const float r = mx == -INFINITY ? 0.0f : expf(mx - m_new);
+            float pr[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) pr[i] = sc[i] == -INFINITY ? 0.0f : expf(sc[i] - m_new);
+            float ps = (pr[0] + pr[1]) + (pr[2] + pr[3]);
+            ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+            ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+            dn = fmaf(dn, r, ps);
+            mx = m_new;
+            uint32_t ph0, pl0, ph1, pl1;
+            split_f16x2(pr[0], pr[1], ph0, pl0);
+            split_f16x2(pr[2], pr[3], ph1, pl1);
+            // O = O * r + P V, 16 tiles of 8 dimensions
+#pragma unroll
+            for (int nt = 0; nt < 16; nt += 2) {
+                uint32_t b00, b01, b10, b11;
+                const uint32_t addr = vs_base + (uint32_t)(((((lane >> 3) & 1) * 8 + (lane & 7)) * ATC_ROW + (nt + (lane >> 4)) * 8) * 2);
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b00), "=r"(b01), "=r"(b10), "=r"(b11) : "r"(addr));
+                o[nt][0] *= r; o[nt][1] *= r;
+                o[nt + 1][0] *= r; o[nt + 1][1] *= r;
+                mma_f16(o[nt], ph0, ph1, b00, b01);
+                mma_f16(o[nt], pl0, pl1, b00, b01);
+                mma_f16(o[nt + 1], ph0, ph1, b10, b11);
+                mma_f16(o[nt + 1], pl0, pl1, b10, b11);
+            }
+            __syncwarp();  // the stage is refilled two steps from now
+        }
+        // this warp's state for heads 0..G-1, then one warp per head merges the warps
+        __syncthreads();
+        if (g < G) {
+            float *stt = merge + (size_t)(warp * ATT_MAX_GROUP + g) * ATT_PART;
+#pragma unroll
+            for (int nt = 0; nt < 16; ++nt) *reinterpret_cast<float2 *>(stt + nt * 8 + 2 * t) = make_float2(o[nt][0], o[nt][1]);
+            if (t == 0) {
+                stt[TILE_ROWS] = mx;
+                stt[TILE_ROWS + 1] = dn;
+            }
+        }
+        __syncthreads();
+        for (int h = warp; h < G; h += ATC_WARPS) {
             float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, sm[w][h][TILE_ROWS]);
+            for (int w = 0; w < ATC_WARPS; ++w) M = fmaxf(M, merge[(size_t)(w * ATT_MAX_GROUP + h) * ATT_PART + TILE_ROWS]);
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
             float d = 0.0f;
 #pragma unroll
-            for (int w = 0; w < ATT_WARPS; ++w) {
-                const float mw = sm[w][h][TILE_ROWS];
-                const float r = mw == -INFINITY ? 0.0f : expf(mw - M);
-                const float4 aw = *reinterpret_cast<const float4 *>(&sm[w][h][4 * lane]);
-                a.x += r * aw.x; a.y += r * aw.y; a.z += r * aw.z; a.w += r * aw.w;
-                d += r * sm[w][h][TILE_ROWS + 1];
+            for (int w = 0; w < ATC_WARPS; ++w) {
+                const float *stt = merge + (size_t)(w * ATT_MAX_GROUP + h) * ATT_PART;
+                const float mw = stt[TILE_ROWS];
+                const float rr = mw == -INFINITY ? 0.0f : expf(mw - M);
+                const float4 aw = *reinterpret_cast<const float4 *>(stt + 4 * lane);
+                a.x += rr * aw.x; a.y += rr * aw.y; a.z += rr * aw.z; a.w += rr * aw.w;
+                d += rr * stt[TILE_ROWS + 1];
             }
             float *dst = p.part + (((size_t)row * (p.n_kv_heads * p.group) + (size_t)(kvh * p.group + g0 + h)) * p.n_splits + split) * ATT_PART;
             *reinterpret_cast<float4 *>(dst + 4 * lane) = a;
@@ -941,6 +1170,7 @@ static __global__ void __launch_bounds__(ATT_WARPS * 32) attn_split_kernel(AttnP
                 dst[TILE_ROWS + 1] = d;
             }
         }
+        __syncthreads();
     }
 }
 

@@ -121,7 +121,7 @@ EXPORTS = (
     "apk_dist_p2p_export", "apk_dist_p2p_open", "apk_debug_token_timeline",
     "apk_debug_token_records", "apk_debug_set_wait_limit", "apk_debug_xch_timeout",
     "apk_bench_ring", "apk_dist_set_exchange", "apk_decode_greedy",
-    "apk_kv_create", "apk_kv_destroy", "apk_kv_read", "apk_kv_write", "apk_attend",
+    "apk_kv_create", "apk_kv_destroy", "apk_kv_read", "apk_kv_write", "apk_attend", "apk_bench_attend",
     "apk_gguf_open", "apk_gguf_close", "apk_gguf_n_tensors", "apk_gguf_tensor_at", "apk_gguf_find",
     "apk_gguf_architecture", "apk_gguf_meta_u32", "apk_gguf_meta_f32", "apk_gguf_meta_str", "apk_gguf_mapping",
     "apk_model_open", "apk_model_get_info", "apk_model_token_req", "apk_model_attach", "apk_model_close",
@@ -159,6 +159,8 @@ def load_library() -> C.CDLL:
     l.apk_kv_destroy.restype = None
     l.apk_kv_read.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
     l.apk_kv_write.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p]
+    l.apk_bench_attend.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float, C.c_uint32,
+                                   C.POINTER(C.c_float)]
     l.apk_attend.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_float,
                              C.c_void_p]
     l.apk_debug_block_dots.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32,
@@ -544,6 +546,15 @@ class Gpu:
         out = np.empty((m, n_heads * 128), np.float32)
         rc = self._l.apk_attend(self._h, kv._h, layer, q.ctypes.data, m, n_heads, pos, scale, out.ctypes.data)
         return out if self._check(rc) else None
+
+    def bench_attend(self, kv: KvCache, q, m: int, n_heads: int, pos: int, scale: float, reps: int = 10) -> float:
+        """Microseconds per layer of the attention core, launched over every layer of ``kv`` in turn."""
+        q = _f32(q).reshape(-1)
+        us = C.c_float()
+        rc = self._l.apk_bench_attend(self._h, kv._h, q.ctypes.data, m, n_heads, pos, scale, reps, C.byref(us))
+        if rc != 0:
+            raise GpuError(rc, self._err())
+        return float(us.value)
 
     def decode_replay(self, req: TokenReq, iters: int) -> float:
         """Replay the token graph `iters` times on device-resident input; returns GPU ms."""

@@ -436,6 +436,27 @@ def run_configs(g, peak):
     nbytes = 3 * ty_bytes(Q4_K, FFN, HIDDEN) + 4 * m * (HIDDEN + HIDDEN)
     out["3_q4_k"] = entry(us, nbytes, par, what="Q4_K gate/up 25600x5120 + SwiGLU, down 5120x25600, m=6", ring_mb=4 * 221.2)
     g.detach(keep[1])
+    # the decode attention core over the f16 KV cache (64 q heads on 8 kv heads of 128, as the benchmark model):
+    # parity on a short context against the oracle, then timed over a cache larger than L2
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(HEAD_DIM)))
+    kv_dim = N_KV * HEAD_DIM
+    rng = np.random.default_rng(1040)
+    n_small = 700
+    kv = G.KvCache(g, 1, kv_dim, n_small)
+    kk = np.stack([orc.kv_store(r) for r in rng.standard_normal((n_small, kv_dim)).astype(np.float32)])
+    vv = np.stack([orc.kv_store(r) for r in rng.standard_normal((n_small, kv_dim)).astype(np.float32)])
+    kv.write(0, 0, kk, vv)
+    q = rng.standard_normal((1, N_HEADS * HEAD_DIM)).astype(np.float32)
+    par = rel_l2(g.attend(kv, 0, q, 1, N_HEADS, n_small - 1, scale),
+                 orc.attend_one(q[0], kk, vv, kv_dim, N_KV, HEAD_DIM, N_HEADS // N_KV, 0, n_small - 1, scale))
+    kv.close()
+    for n_pos, n_layers_kv in ((4096, 16), (32768, 4)):
+        kv = G.KvCache(g, n_layers_kv, kv_dim, n_pos)
+        us = g.bench_attend(kv, q, 1, N_HEADS, n_pos - 1, scale, reps=10)
+        kv.close()
+        nbytes = 2 * n_pos * kv_dim * 2 + 2 * 4 * N_HEADS * HEAD_DIM
+        out[f"attention_{n_pos}"] = entry(us, nbytes, par, what=f"attention core, {N_HEADS}/{N_KV} heads, {n_pos} positions, m=1",
+                                          ring_mb=n_layers_kv * nbytes / 1e6)
     return out
 
 

@@ -386,6 +386,11 @@ typedef struct {
     uint64_t decode_attempts, decode_successes, decode_declines; /* DecodePathStats, gpu/types.rs:258-285 */
 } apk_stats_t;
 
+/* Benchmark helper: the attention core of apk_attend over every layer of the cache in turn (distinct
+ * memory per layer), `reps` rounds timed with CUDA events; microseconds per layer. */
+int apk_bench_attend(apk_ctx *ctx, const apk_kv *kv, const float *q, uint32_t m, uint32_t n_heads, uint32_t pos, float scale,
+                     uint32_t reps, float *us_per_layer);
+
 void apk_stats(apk_ctx *ctx, apk_stats_t *out);
 
 /* Human-readable reason for the last non-zero status on this thread
