@@ -103,10 +103,16 @@ int nccl_allreduce(apk_ctx *c, float *buf, size_t n) {
 
 bool uses_xch(const apk_ctx *c) { return c->p2p_ready && (c->world > 1 || c->self_xch); }
 
-// Position splits of the attention core: fixed per cache (the launch shape is captured), 64 positions
-// per CTA at full capacity up to 128 splits (more CTAs than SMs: the kernel hides its load latency
-// with resident warps).
-int attn_splits(uint32_t capacity) { return (int)std::max<uint32_t>(1, std::min<uint32_t>(128, (capacity + 63) / 64)); }
+// Position splits of the attention core: fixed per cache (the launch shape is captured).  A split
+// kernel CTA does best with at least 256 positions (four steps per warp: the pipeline fills, the
+// per-CTA prologue and merge amortise), and kv heads x splits should not exceed one wave of two CTAs
+// per SM (measured at 32768 positions: 37 splits 30 us, 43 splits 40 us, 128 splits 43 us).
+int attn_splits(const apk_ctx *c, const apk_kv *kv) {
+    const uint32_t n_kv = std::max<uint32_t>(1, kv->kv_dim / TILE_ROWS);
+    const uint32_t wave = std::max<uint32_t>(1, 2u * (uint32_t)c->n_sm / n_kv);
+    const uint32_t by_len = (kv->capacity + 255) / 256;
+    return (int)std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(wave, by_len), 128));
+}
 
 // q [m][ldq] -> attention over one layer of the cache -> optional f32 rows, optional records for wo.
 int launch_attention(apk_ctx *c, const apk_kv *kv, uint32_t layer, const float *q, int ldq, uint32_t m, uint32_t n_heads_l,
@@ -120,7 +126,7 @@ int launch_attention(apk_ctx *c, const apk_kv *kv, uint32_t layer, const float *
     ap.group = (int)(n_heads_l / (kv->kv_dim / TILE_ROWS));
     ap.pos_dev = pos_dev; ap.pos = pos;
     ap.m = (int)m;
-    ap.n_splits = attn_splits(kv->capacity);
+    ap.n_splits = attn_splits(c, kv);
     ap.scale = scale;
     ap.part = part;
     ap.out = out; ap.ldo = ldo;
@@ -236,7 +242,7 @@ int build_plan(apk_ctx *c, const apk_token_req *r) {
             return decline_decode(c, APK_DECLINE_UNSUPPORTED_SHAPE, "heads do not split over the ranks");
         if (!r->kv || r->kv->n_layers < r->n_layers || r->kv->kv_dim != P->nkv_l)
             return decline_decode(c, APK_ERR_INVALID_ARG, "the KV cache does not fit the request (layers, kv_dim)");
-        APK_TRY(P->attn_part.ensure((size_t)M * (P->nq_l / TILE_ROWS) * attn_splits(r->kv->capacity) * ATT_PART * 4));
+        APK_TRY(P->attn_part.ensure((size_t)M * (P->nq_l / TILE_ROWS) * attn_splits(c, r->kv) * ATT_PART * 4));
         APK_TRY(P->attn_out.ensure((size_t)M * P->nq_l * 4));
     }
     if (uses_xch(c)) {
@@ -1004,7 +1010,7 @@ int apk_attend(apk_ctx *c, const apk_kv *kv, uint32_t layer, const float *q, uin
     const size_t qn = (size_t)m * n_heads * TILE_ROWS;
     APK_TRY(c->x_dev.ensure(qn * 4));
     APK_TRY(c->y_dev.ensure(qn * 4));
-    APK_TRY(c->misc.ensure((size_t)m * n_heads * attn_splits(kv->capacity) * ATT_PART * 4));
+    APK_TRY(c->misc.ensure((size_t)m * n_heads * attn_splits(c, kv) * ATT_PART * 4));
     CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, q, qn * 4, cudaMemcpyHostToDevice, c->stream));
     APK_TRY(launch_attention(c, kv, layer, c->x_dev.as<float>(), (int)(n_heads * TILE_ROWS), m, n_heads, nullptr, pos, scale,
                              c->misc.as<float>(), c->y_dev.as<float>(), (int)(n_heads * TILE_ROWS), nullptr, 0, 0));
@@ -1027,7 +1033,7 @@ int apk_bench_attend(apk_ctx *c, const apk_kv *kv, const float *q, uint32_t m, u
     const size_t qn = (size_t)m * n_heads * TILE_ROWS;
     APK_TRY(c->x_dev.ensure(qn * 4));
     APK_TRY(c->y_dev.ensure(qn * 4));
-    APK_TRY(c->misc.ensure((size_t)m * n_heads * attn_splits(kv->capacity) * ATT_PART * 4));
+    APK_TRY(c->misc.ensure((size_t)m * n_heads * attn_splits(c, kv) * ATT_PART * 4));
     CUDA_TRY(cudaMemcpyAsync(c->x_dev.p, q, qn * 4, cudaMemcpyHostToDevice, c->stream));
     auto pass = [&](uint32_t layer) {
         return launch_attention(c, kv, layer, c->x_dev.as<float>(), (int)(n_heads * TILE_ROWS), m, n_heads, nullptr, pos, scale,

@@ -1004,7 +1004,8 @@ static __global__ void __launch_bounds__(ATT_WARPS * 32) attn_split_kernel(AttnP
 constexpr int ATC_WARPS = 4;
 constexpr int ATC_ROW = TILE_ROWS + 8;   // halves per staged row: 272 B, so the eight rows of an ldmatrix hit distinct banks
 constexpr int ATC_STAGE = 2 * 16 * ATC_ROW;  // halves per stage: K tile, then V tile
-constexpr int ATC_SMEM = ATC_WARPS * 2 * ATC_STAGE * 2 + ATC_WARPS * ATT_MAX_GROUP * ATT_PART * 4;
+constexpr int ATC_SMEM = ATC_WARPS * 2 * ATC_STAGE * 2;  // 68 KB (the merge buffer reuses the stages); two CTAs per SM by registers
+static_assert(ATC_WARPS * ATT_MAX_GROUP * ATT_PART * 4 <= ATC_SMEM, "the merge buffer lives in the stage memory");
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
     // rows 8..15 of A (registers a1, a3) are zero
@@ -1027,7 +1028,7 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
     }
     extern __shared__ __align__(16) uint8_t att_smem[];
     __half *stages = reinterpret_cast<__half *>(att_smem);
-    float *merge = reinterpret_cast<float *>(att_smem + ATC_WARPS * 2 * ATC_STAGE * 2);  // [warp][head][ATT_PART]
+    float *merge = reinterpret_cast<float *>(att_smem);  // [warp][head][ATT_PART], over the stages once every warp is through with them
     const int kvh = blockIdx.x, split = blockIdx.y, row = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const uint32_t pos = (p.pos_dev ? *p.pos_dev : p.pos) + (uint32_t)row;
@@ -1181,17 +1182,29 @@ static __global__ void __launch_bounds__(TILE_ROWS) attn_combine_kernel(AttnPara
         pdl_launch_dependents();
         pdl_wait();
     }
-    const int head = blockIdx.x, row = blockIdx.y, i = threadIdx.x;
+    __shared__ float w[TILE_ROWS];   // weight of each split: exp(its maximum - the common maximum)
+    __shared__ float red[8];
+    const int head = blockIdx.x, row = blockIdx.y, i = threadIdx.x, lane = i & 31, warp = i >> 5;
     const float *src = p.part + ((size_t)row * (p.n_kv_heads * p.group) + head) * p.n_splits * ATT_PART;
-    float M = -INFINITY;
-    for (int s = 0; s < p.n_splits; ++s) M = fmaxf(M, src[(size_t)s * ATT_PART + TILE_ROWS]);
-    float a = 0.0f, d = 0.0f;
-    for (int s = 0; s < p.n_splits; ++s) {
-        const float ms = src[(size_t)s * ATT_PART + TILE_ROWS];
-        const float r = ms == -INFINITY ? 0.0f : expf(ms - M);
-        a += r * src[(size_t)s * ATT_PART + i];
-        d += r * src[(size_t)s * ATT_PART + TILE_ROWS + 1];
-    }
+    // thread s looks at split s (at most 128 splits): common maximum, weights, denominator
+    const float ms = i < p.n_splits ? src[(size_t)i * ATT_PART + TILE_ROWS] : -INFINITY;
+    float M = ms;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if (lane == 0) red[warp] = M;
+    __syncthreads();
+    M = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    const float ws = ms == -INFINITY ? 0.0f : expf(ms - M);
+    w[i] = ws;
+    float d = i < p.n_splits ? ws * src[(size_t)i * ATT_PART + TILE_ROWS + 1] : 0.0f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+    if (lane == 0) red[4 + warp] = d;
+    __syncthreads();
+    d = (red[4] + red[5]) + (red[6] + red[7]);
+    float a = 0.0f;
+#pragma unroll 8
+    for (int s = 0; s < p.n_splits; ++s) a = fmaf(w[s], src[(size_t)s * ATT_PART + i], a);
     const float o = a * (1.0f / fmaxf(d, 1.17549435e-38f));  // denom.max(f32::MIN_POSITIVE)
     if (p.out) p.out[(size_t)row * p.ldo + (size_t)head * TILE_ROWS + i] = o;
     if (p.next.base) quantize_store(p.next, p.next_two_level, p.next_need_sum, row, head * 4 + (i >> 5), i & 31, o);

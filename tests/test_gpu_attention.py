@@ -43,6 +43,34 @@ def test_attention_core_matches_attend_one(orc, n_heads, n_kv, n_pos, m):
     g.close()
 
 
+def test_attention_core_on_cuda_cores_agrees(orc, monkeypatch):
+    """ALLPAKA_B200_ATTN_TC=0 selects the f32 CUDA-core form of the split kernel (the default feeds the tensor
+    cores with hi + lo f16 fragments of q and of the softmax weights): both sit at rounding level of the oracle."""
+    from allpaka_b200 import gpu as G
+
+    outs = []
+    for tc in ("1", "0"):
+        monkeypatch.setenv("ALLPAKA_B200_ATTN_TC", tc)
+        g = G.Gpu(0)
+        n_heads, n_kv, n_pos, hd = 40, 8, 1500, 128
+        kv = G.KvCache(g, 1, n_kv * hd, n_pos)
+        rng = np.random.default_rng(77)
+        k = f16_rows(orc, rng.standard_normal((n_pos, n_kv * hd)).astype(np.float32))
+        v = f16_rows(orc, rng.standard_normal((n_pos, n_kv * hd)).astype(np.float32))
+        kv.write(0, 0, k, v)
+        q = (rng.standard_normal((2, n_heads * hd)) * 3.0).astype(np.float32)
+        scale = float(np.float32(1.0) / np.sqrt(np.float32(hd)))
+        got = g.attend(kv, 0, q, 2, n_heads, n_pos - 2, scale)
+        want = np.stack([orc.attend_one(q[i], k, v, n_kv * hd, n_kv, hd, n_heads // n_kv, 0, n_pos - 2 + i, scale) for i in range(2)])
+        err = rel_l2(got, want)
+        print(f"attention core, tensor cores {tc}: rel-L2 {err:.1e}")
+        assert err <= 2e-5
+        outs.append(got)
+        kv.close()
+        g.close()
+    assert rel_l2(outs[0], outs[1]) <= 2e-5
+
+
 def oracle_token(orc, ty, layers, d, rope, x, m, kcs, vcs, pos, scale):
     """The reference's layer order with the real attention core: K (roped) and V of the m rows go into
     the cache as f16 at pos..pos+m-1, row i attends over 0..=pos+i (model/decode.rs:435-591,
