@@ -12,6 +12,13 @@ from allpaka_b200 import gguf, synth
 from tests.util import Q4_K, Q6_K, Q8_0
 
 
+@pytest.fixture(scope="module", autouse=True)
+def _library():
+    from allpaka_b200 import build
+
+    build.build()  # (no-op when the library is up to date)
+
+
 def tiny_model(arch="qwen3", ty=Q8_0, hidden=256, n_heads=2, n_kv=1, head_dim=128, ffn=512, vocab=300, n_layers=2,
                qk_norm=True, tied=False, extra_meta=None, drop=(), override=None, ty_of=None):
     """ty_of: tensor-name suffix -> ggml type, for files that mix types (the rest take ``ty``)."""
