@@ -136,10 +136,15 @@ int launch_attention(apk_ctx *c, const apk_kv *kv, uint32_t layer, const float *
     const int pdl = c->use_pdl ? 1 : 0;
     if (c->attn_tc) {
         if (!c->attn_tc_ready) {
-            CUDA_TRY(cudaFuncSetAttribute((const void *)attn_split_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
+            CUDA_TRY(cudaFuncSetAttribute((const void *)attn_split_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
+            CUDA_TRY(cudaFuncSetAttribute((const void *)attn_split_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
             c->attn_tc_ready = true;
         }
-        CUDA_TRY(launch_ex(c, attn_split_tc_kernel, dim3(ap.n_kv_heads, ap.n_splits, m), dim3(ATC_WARPS * 32), (size_t)ATC_SMEM, c->use_pdl, ap, pdl));
+        // verify batches: two consecutive rows share one pass over K and V
+        if (m > 1)
+            CUDA_TRY(launch_ex(c, attn_split_tc_kernel<true>, dim3(ap.n_kv_heads, ap.n_splits, (m + 1) / 2), dim3(ATC_WARPS * 32), (size_t)ATC_SMEM, c->use_pdl, ap, pdl));
+        else
+            CUDA_TRY(launch_ex(c, attn_split_tc_kernel<false>, dim3(ap.n_kv_heads, ap.n_splits, 1), dim3(ATC_WARPS * 32), (size_t)ATC_SMEM, c->use_pdl, ap, pdl));
     } else {
         CUDA_TRY(launch_ex(c, attn_split_kernel, dim3(ap.n_kv_heads, ap.n_splits, m), dim3(ATT_WARPS * 32), 0, c->use_pdl, ap, pdl));
     }

@@ -1005,13 +1005,12 @@ constexpr int ATC_WARPS = 4;
 constexpr int ATC_ROW = TILE_ROWS + 8;   // halves per staged row: 272 B, so the eight rows of an ldmatrix hit distinct banks
 constexpr int ATC_STAGE = 2 * 16 * ATC_ROW;  // halves per stage: K tile, then V tile
 constexpr int ATC_SMEM = ATC_WARPS * 2 * ATC_STAGE * 2;  // 68 KB (the merge buffer reuses the stages); two CTAs per SM by registers
-static_assert(ATC_WARPS * ATT_MAX_GROUP * ATT_PART * 4 <= ATC_SMEM, "the merge buffer lives in the stage memory");
+static_assert(ATC_WARPS * 2 * ATT_MAX_GROUP * ATT_PART * 4 <= ATC_SMEM, "the merge buffer lives in the stage memory");
 
-__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
-    // rows 8..15 of A (registers a1, a3) are zero
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%5}, {%7,%8}, {%0,%1,%2,%3};"
+__device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 __device__ __forceinline__ void split_f16x2(float x, float y, uint32_t &hi, uint32_t &lo) {
     const __half2 h = __floats2half2_rn(x, y);
@@ -1021,37 +1020,47 @@ __device__ __forceinline__ void split_f16x2(float x, float y, uint32_t &hi, uint
     lo = *reinterpret_cast<const uint32_t *>(&l);
 }
 
+// PAIR = false: one query row per CTA, rows 8..15 of the mma stay zero (decode).  PAIR = true (verify
+// batches): two consecutive query rows share the K and V stream, the second in rows 8..15 with its own
+// causal limit (one position more) and its own softmax state; grid.z = ceil(m / 2).
+template <bool PAIR>
 static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(AttnParams p, int pdl) {
     if (pdl) {
         pdl_launch_dependents();
         pdl_wait();
     }
+    constexpr int NR = PAIR ? 2 : 1;
     extern __shared__ __align__(16) uint8_t att_smem[];
     __half *stages = reinterpret_cast<__half *>(att_smem);
-    float *merge = reinterpret_cast<float *>(att_smem);  // [warp][head][ATT_PART], over the stages once every warp is through with them
-    const int kvh = blockIdx.x, split = blockIdx.y, row = blockIdx.z;
+    float *merge = reinterpret_cast<float *>(att_smem);  // [warp][row of the pair][head][ATT_PART], over the stages once every warp is through with them
+    const int kvh = blockIdx.x, split = blockIdx.y, row0 = NR * blockIdx.z;
+    const bool has1 = PAIR && row0 + 1 < p.m;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const uint32_t pos = (p.pos_dev ? *p.pos_dev : p.pos) + (uint32_t)row;
-    const uint32_t n_pos = pos + 1u;
+    const uint32_t pos = (p.pos_dev ? *p.pos_dev : p.pos) + (uint32_t)row0;
+    const uint32_t n_pos0 = pos + 1u;                      // row0 sees positions 0..=pos
+    const uint32_t n_pos = n_pos0 + (has1 ? 1u : 0u);      // its partner one more
     const uint32_t per = (n_pos + (uint32_t)p.n_splits - 1u) / (uint32_t)p.n_splits;
     const uint32_t t0 = (uint32_t)split * per, t1 = min(n_pos, t0 + per);
     __half *my = stages + (size_t)warp * 2 * ATC_STAGE;
     const uint32_t my_s = (uint32_t)__cvta_generic_to_shared(my);
     for (int g0 = 0; g0 < p.group; g0 += ATT_MAX_GROUP) {
         const int G = min(ATT_MAX_GROUP, p.group - g0);
-        // q of head g as A fragments (hi and lo), eight k-steps of 16 dimensions
-        uint32_t qh[8][2], ql[8][2];
-        {
-            const float *qp = p.q + (size_t)row * p.ldq + (size_t)(kvh * p.group + g0 + (g < G ? g : 0)) * TILE_ROWS;
+        // q of head g (of each row of the pair) as A fragments, hi and lo, eight k-steps of 16 dimensions
+        uint32_t qh[8][2 * NR], ql[8][2 * NR];
+#pragma unroll
+        for (int rr = 0; rr < NR; ++rr) {
+            const bool on = g < G && (rr == 0 || has1);
+            const float *qp = p.q + (size_t)(row0 + (on ? rr : 0)) * p.ldq + (size_t)(kvh * p.group + g0 + (g < G ? g : 0)) * TILE_ROWS;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 float2 x0 = make_float2(0.f, 0.f), x1 = make_float2(0.f, 0.f);
-                if (g < G) {
+                if (on) {
                     x0 = *reinterpret_cast<const float2 *>(qp + 16 * ks + 2 * t);
                     x1 = *reinterpret_cast<const float2 *>(qp + 16 * ks + 2 * t + 8);
                 }
-                split_f16x2(x0.x, x0.y, qh[ks][0], ql[ks][0]);
-                split_f16x2(x1.x, x1.y, qh[ks][1], ql[ks][1]);
+                // fragment registers: a0 (row g, k 2t..), a1 (row g+8, k 2t..), a2 (row g, k 2t+8..), a3 (row g+8, k 2t+8..)
+                split_f16x2(x0.x, x0.y, qh[ks][rr], ql[ks][rr]);
+                split_f16x2(x1.x, x1.y, qh[ks][NR + rr], ql[ks][NR + rr]);
             }
         }
         float o[16][4];
@@ -1059,7 +1068,12 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
         for (int nt = 0; nt < 16; ++nt)
 #pragma unroll
             for (int i = 0; i < 4; ++i) o[nt][i] = 0.0f;
-        float mx = -INFINITY, dn = 0.0f;
+        float mx[NR], dn[NR];
+#pragma unroll
+        for (int rr = 0; rr < NR; ++rr) {
+            mx[rr] = -INFINITY;
+            dn[rr] = 0.0f;
+        }
         // this warp's 16 positions of step i: t0 + 16 * (warp + ATC_WARPS * i)
         auto stage_load = [&](uint32_t p0, int st) {
             // 16 rows x 256 B of K and of V: 512 16-byte chunks, 16 per lane
@@ -1094,33 +1108,43 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
                 const uint32_t addr = ks_base + (uint32_t)((((lane >> 4) * 8 + (lane & 7)) * ATC_ROW + 16 * ks + ((lane >> 3) & 1) * 8) * 2);
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
                              : "=r"(b00), "=r"(b01), "=r"(b10), "=r"(b11) : "r"(addr));
-                mma_f16(s0, qh[ks][0], qh[ks][1], b00, b01);
-                mma_f16(s0, ql[ks][0], ql[ks][1], b00, b01);
-                mma_f16(s1, qh[ks][0], qh[ks][1], b10, b11);
-                mma_f16(s1, ql[ks][0], ql[ks][1], b10, b11);
+                const uint32_t h1 = PAIR ? qh[ks][1] : 0u, h3 = PAIR ? qh[ks][NR + 1] : 0u;
+                const uint32_t l1 = PAIR ? ql[ks][1] : 0u, l3 = PAIR ? ql[ks][NR + 1] : 0u;
+                mma_f16(s0, qh[ks][0], h1, qh[ks][NR], h3, b00, b01);
+                mma_f16(s0, ql[ks][0], l1, ql[ks][NR], l3, b00, b01);
+                mma_f16(s1, qh[ks][0], h1, qh[ks][NR], h3, b10, b11);
+                mma_f16(s1, ql[ks][0], l1, ql[ks][NR], l3, b10, b11);
             }
-            // online softmax on row g (this lane: positions p0 + 2t, +1 and p0 + 8 + 2t, +1)
-            float sc[4];
-            sc[0] = (p0 + 2 * t < t1) ? s0[0] * p.scale : -INFINITY;
-            sc[1] = (p0 + 2 * t + 1 < t1) ? s0[1] * p.scale : -INFINITY;
-            sc[2] = (p0 + 8 + 2 * t < t1) ? s1[0] * p.scale : -INFINITY;
-            sc[3] = (p0 + 8 + 2 * t + 1 < t1) ? s1[1] * p.scale : -INFINITY;
-            float mt = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
-            mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
-            mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
-            const float m_new = fmaxf(mx, mt);  // (position p0 itself is always valid, so m_new is finite)
-            const float r = mx == -INFINITY ? 0.0f : expf(mx - m_new);
-            float pr[4];
+            // online softmax: fragment row g (and g+8 for the partner); this lane holds positions p0 + 2t, +1 and p0 + 8 + 2t, +1
+            float pr[NR][4], rs[NR];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) pr[i] = sc[i] == -INFINITY ? 0.0f : expf(sc[i] - m_new);
-            float ps = (pr[0] + pr[1]) + (pr[2] + pr[3]);
-            ps += __shfl_xor_sync(0xffffffffu, ps, 1);
-            ps += __shfl_xor_sync(0xffffffffu, ps, 2);
-            dn = fmaf(dn, r, ps);
-            mx = m_new;
-            uint32_t ph0, pl0, ph1, pl1;
-            split_f16x2(pr[0], pr[1], ph0, pl0);
-            split_f16x2(pr[2], pr[3], ph1, pl1);
+            for (int rr = 0; rr < NR; ++rr) {
+                const uint32_t lim = rr == 0 ? min(t1, n_pos0) : t1;  // the first row of a pair stops one position earlier
+                float sc[4];
+                sc[0] = (p0 + 2 * t < lim) ? s0[2 * rr] * p.scale : -INFINITY;
+                sc[1] = (p0 + 2 * t + 1 < lim) ? s0[2 * rr + 1] * p.scale : -INFINITY;
+                sc[2] = (p0 + 8 + 2 * t < lim) ? s1[2 * rr] * p.scale : -INFINITY;
+                sc[3] = (p0 + 8 + 2 * t + 1 < lim) ? s1[2 * rr + 1] * p.scale : -INFINITY;
+                float mt = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+                mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
+                mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
+                const float m_new = fmaxf(mx[rr], mt);
+                // (a row of the pair may have nothing in this step: the last position belongs to the partner alone)
+                rs[rr] = mx[rr] == -INFINITY ? 0.0f : expf(mx[rr] - m_new);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) pr[rr][i] = sc[i] == -INFINITY ? 0.0f : expf(sc[i] - m_new);
+                float ps = (pr[rr][0] + pr[rr][1]) + (pr[rr][2] + pr[rr][3]);
+                ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+                ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+                dn[rr] = fmaf(dn[rr], rs[rr], ps);
+                mx[rr] = m_new;
+            }
+            uint32_t ph[4] = {0u, 0u, 0u, 0u}, pl[4] = {0u, 0u, 0u, 0u};  // A fragment registers a0..a3 of P
+#pragma unroll
+            for (int rr = 0; rr < NR; ++rr) {
+                split_f16x2(pr[rr][0], pr[rr][1], ph[rr], pl[rr]);
+                split_f16x2(pr[rr][2], pr[rr][3], ph[2 + rr], pl[2 + rr]);
+            }
             // O = O * r + P V, 16 tiles of 8 dimensions
 #pragma unroll
             for (int nt = 0; nt < 16; nt += 2) {
@@ -1128,43 +1152,51 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
                 const uint32_t addr = vs_base + (uint32_t)(((((lane >> 3) & 1) * 8 + (lane & 7)) * ATC_ROW + (nt + (lane >> 4)) * 8) * 2);
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                              : "=r"(b00), "=r"(b01), "=r"(b10), "=r"(b11) : "r"(addr));
-                o[nt][0] *= r; o[nt][1] *= r;
-                o[nt + 1][0] *= r; o[nt + 1][1] *= r;
-                mma_f16(o[nt], ph0, ph1, b00, b01);
-                mma_f16(o[nt], pl0, pl1, b00, b01);
-                mma_f16(o[nt + 1], ph0, ph1, b10, b11);
-                mma_f16(o[nt + 1], pl0, pl1, b10, b11);
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    o[nt + u][0] *= rs[0]; o[nt + u][1] *= rs[0];
+                    if (PAIR) { o[nt + u][2] *= rs[NR - 1]; o[nt + u][3] *= rs[NR - 1]; }
+                }
+                mma_f16(o[nt], ph[0], ph[1], ph[2], ph[3], b00, b01);
+                mma_f16(o[nt], pl[0], pl[1], pl[2], pl[3], b00, b01);
+                mma_f16(o[nt + 1], ph[0], ph[1], ph[2], ph[3], b10, b11);
+                mma_f16(o[nt + 1], pl[0], pl[1], pl[2], pl[3], b10, b11);
             }
             __syncwarp();  // the stage is refilled two steps from now
         }
-        // this warp's state for heads 0..G-1, then one warp per head merges the warps
+        // this warp's state for heads 0..G-1 of each row, then one warp per (row, head) merges the warps
         __syncthreads();
         if (g < G) {
-            float *stt = merge + (size_t)(warp * ATT_MAX_GROUP + g) * ATT_PART;
 #pragma unroll
-            for (int nt = 0; nt < 16; ++nt) *reinterpret_cast<float2 *>(stt + nt * 8 + 2 * t) = make_float2(o[nt][0], o[nt][1]);
-            if (t == 0) {
-                stt[TILE_ROWS] = mx;
-                stt[TILE_ROWS + 1] = dn;
+            for (int rr = 0; rr < NR; ++rr) {
+                float *stt = merge + (size_t)((warp * NR + rr) * ATT_MAX_GROUP + g) * ATT_PART;
+#pragma unroll
+                for (int nt = 0; nt < 16; ++nt) *reinterpret_cast<float2 *>(stt + nt * 8 + 2 * t) = make_float2(o[nt][2 * rr], o[nt][2 * rr + 1]);
+                if (t == 0) {
+                    stt[TILE_ROWS] = mx[rr];
+                    stt[TILE_ROWS + 1] = dn[rr];
+                }
             }
         }
         __syncthreads();
-        for (int h = warp; h < G; h += ATC_WARPS) {
+        for (int hr = warp; hr < NR * G; hr += ATC_WARPS) {
+            const int rr = hr / G, h = hr % G;
+            if (rr == 1 && !has1) continue;
             float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < ATC_WARPS; ++w) M = fmaxf(M, merge[(size_t)(w * ATT_MAX_GROUP + h) * ATT_PART + TILE_ROWS]);
+            for (int w = 0; w < ATC_WARPS; ++w) M = fmaxf(M, merge[(size_t)((w * NR + rr) * ATT_MAX_GROUP + h) * ATT_PART + TILE_ROWS]);
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
             float d = 0.0f;
 #pragma unroll
             for (int w = 0; w < ATC_WARPS; ++w) {
-                const float *stt = merge + (size_t)(w * ATT_MAX_GROUP + h) * ATT_PART;
+                const float *stt = merge + (size_t)((w * NR + rr) * ATT_MAX_GROUP + h) * ATT_PART;
                 const float mw = stt[TILE_ROWS];
-                const float rr = mw == -INFINITY ? 0.0f : expf(mw - M);
+                const float wgt = mw == -INFINITY ? 0.0f : expf(mw - M);
                 const float4 aw = *reinterpret_cast<const float4 *>(stt + 4 * lane);
-                a.x += rr * aw.x; a.y += rr * aw.y; a.z += rr * aw.z; a.w += rr * aw.w;
-                d += rr * stt[TILE_ROWS + 1];
+                a.x += wgt * aw.x; a.y += wgt * aw.y; a.z += wgt * aw.z; a.w += wgt * aw.w;
+                d += wgt * stt[TILE_ROWS + 1];
             }
-            float *dst = p.part + (((size_t)row * (p.n_kv_heads * p.group) + (size_t)(kvh * p.group + g0 + h)) * p.n_splits + split) * ATT_PART;
+            float *dst = p.part + (((size_t)(row0 + rr) * (p.n_kv_heads * p.group) + (size_t)(kvh * p.group + g0 + h)) * p.n_splits + split) * ATT_PART;
             *reinterpret_cast<float4 *>(dst + 4 * lane) = a;
             if (lane == 0) {
                 dst[TILE_ROWS] = M;
