@@ -140,9 +140,9 @@ int launch_attention(apk_ctx *c, const apk_kv *kv, uint32_t layer, const float *
             CUDA_TRY(cudaFuncSetAttribute((const void *)attn_split_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
             c->attn_tc_ready = true;
         }
-        // verify batches: two consecutive rows share one pass over K and V
+        // verify batches: 16 / group consecutive rows share one pass over K and V
         if (m > 1)
-            CUDA_TRY(launch_ex(c, attn_split_tc_kernel<true>, dim3(ap.n_kv_heads, ap.n_splits, (m + 1) / 2), dim3(ATC_WARPS * 32), (size_t)ATC_SMEM, c->use_pdl, ap, pdl));
+            CUDA_TRY(launch_ex(c, attn_split_tc_kernel<true>, dim3(ap.n_kv_heads, ap.n_splits, (m + atc_rows(ap.group) - 1) / atc_rows(ap.group)), dim3(ATC_WARPS * 32), (size_t)ATC_SMEM, c->use_pdl, ap, pdl));
         else
             CUDA_TRY(launch_ex(c, attn_split_tc_kernel<false>, dim3(ap.n_kv_heads, ap.n_splits, 1), dim3(ATC_WARPS * 32), (size_t)ATC_SMEM, c->use_pdl, ap, pdl));
     } else {

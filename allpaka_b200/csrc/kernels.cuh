@@ -1005,7 +1005,7 @@ constexpr int ATC_WARPS = 4;
 constexpr int ATC_ROW = TILE_ROWS + 8;   // halves per staged row: 272 B, so the eight rows of an ldmatrix hit distinct banks
 constexpr int ATC_STAGE = 2 * 16 * ATC_ROW;  // halves per stage: K tile, then V tile
 constexpr int ATC_SMEM = ATC_WARPS * 2 * ATC_STAGE * 2;  // 68 KB (the merge buffer reuses the stages); two CTAs per SM by registers
-static_assert(ATC_WARPS * 2 * ATT_MAX_GROUP * ATT_PART * 4 <= ATC_SMEM, "the merge buffer lives in the stage memory");
+static_assert(ATC_WARPS * 16 * ATT_PART * 4 <= ATC_SMEM, "the merge buffer lives in the stage memory");
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -1021,8 +1021,14 @@ __device__ __forceinline__ void split_f16x2(float x, float y, uint32_t &hi, uint
 }
 
 // PAIR = false: one query row per CTA, rows 8..15 of the mma stay zero (decode).  PAIR = true (verify
-// batches): two consecutive query rows share the K and V stream, the second in rows 8..15 with its own
-// causal limit (one position more) and its own softmax state; grid.z = ceil(m / 2).
+// batches): consecutive query rows share the K and V stream.  Each half of the 16 fragment rows holds
+// 8 / Gp query rows of Gp heads (Gp = the group size rounded up to a power of two, at most 8), each
+// row with its own causal limit and softmax state; grid.z = ceil(m / atc_rows(group)).
+// the group size (at most 8 heads per pass) rounded up to a power of two, and the query rows one CTA of
+// the PAIR kernel takes
+__host__ __device__ inline int atc_group_pow2(int group) { return group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8; }
+__host__ __device__ inline int atc_rows(int group) { return 16 / atc_group_pow2(group); }
+
 template <bool PAIR>
 static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(AttnParams p, int pdl) {
     if (pdl) {
@@ -1033,24 +1039,27 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
     extern __shared__ __align__(16) uint8_t att_smem[];
     __half *stages = reinterpret_cast<__half *>(att_smem);
     float *merge = reinterpret_cast<float *>(att_smem);  // [warp][row of the pair][head][ATT_PART], over the stages once every warp is through with them
-    const int kvh = blockIdx.x, split = blockIdx.y, row0 = NR * blockIdx.z;
-    const bool has1 = PAIR && row0 + 1 < p.m;
+    const int Gp = PAIR ? atc_group_pow2(p.group) : 8, RH = 8 / Gp, NRC = NR * RH;  // rows per half, rows per CTA
+    const int kvh = blockIdx.x, split = blockIdx.y, row0 = NRC * blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const uint32_t pos = (p.pos_dev ? *p.pos_dev : p.pos) + (uint32_t)row0;
-    const uint32_t n_pos0 = pos + 1u;                      // row0 sees positions 0..=pos
-    const uint32_t n_pos = n_pos0 + (has1 ? 1u : 0u);      // its partner one more
+    const int hh = g % Gp, sr = g / Gp;                    // this lane's head of the group and row of the half
+    const uint32_t base = p.pos_dev ? *p.pos_dev : p.pos;  // query row r sees positions 0..=base + r
+    const uint32_t n_pos = base + (uint32_t)min(row0 + NRC, p.m);  // what the last row of this CTA sees
     const uint32_t per = (n_pos + (uint32_t)p.n_splits - 1u) / (uint32_t)p.n_splits;
     const uint32_t t0 = (uint32_t)split * per, t1 = min(n_pos, t0 + per);
     __half *my = stages + (size_t)warp * 2 * ATC_STAGE;
     const uint32_t my_s = (uint32_t)__cvta_generic_to_shared(my);
     for (int g0 = 0; g0 < p.group; g0 += ATT_MAX_GROUP) {
         const int G = min(ATT_MAX_GROUP, p.group - g0);
-        // q of head g (of each row of the pair) as A fragments, hi and lo, eight k-steps of 16 dimensions
+        // q of this lane's (row, head) in each half as A fragments, hi and lo, eight k-steps of 16 dimensions
         uint32_t qh[8][2 * NR], ql[8][2 * NR];
+        uint32_t lim[NR];
 #pragma unroll
         for (int rr = 0; rr < NR; ++rr) {
-            const bool on = g < G && (rr == 0 || has1);
-            const float *qp = p.q + (size_t)(row0 + (on ? rr : 0)) * p.ldq + (size_t)(kvh * p.group + g0 + (g < G ? g : 0)) * TILE_ROWS;
+            const int qrow = row0 + rr * RH + sr;
+            const bool on = hh < G && qrow < p.m;
+            lim[rr] = min(t1, base + (uint32_t)qrow + 1u);
+            const float *qp = p.q + (size_t)(on ? qrow : 0) * p.ldq + (size_t)(kvh * p.group + g0 + (on ? hh : 0)) * TILE_ROWS;
 #pragma unroll
             for (int ks = 0; ks < 8; ++ks) {
                 float2 x0 = make_float2(0.f, 0.f), x1 = make_float2(0.f, 0.f);
@@ -1115,21 +1124,20 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
                 mma_f16(s1, qh[ks][0], h1, qh[ks][NR], h3, b10, b11);
                 mma_f16(s1, ql[ks][0], l1, ql[ks][NR], l3, b10, b11);
             }
-            // online softmax: fragment row g (and g+8 for the partner); this lane holds positions p0 + 2t, +1 and p0 + 8 + 2t, +1
+            // online softmax: fragment row g (and g+8 in the other half); this lane holds positions p0 + 2t, +1 and p0 + 8 + 2t, +1
             float pr[NR][4], rs[NR];
 #pragma unroll
             for (int rr = 0; rr < NR; ++rr) {
-                const uint32_t lim = rr == 0 ? min(t1, n_pos0) : t1;  // the first row of a pair stops one position earlier
                 float sc[4];
-                sc[0] = (p0 + 2 * t < lim) ? s0[2 * rr] * p.scale : -INFINITY;
-                sc[1] = (p0 + 2 * t + 1 < lim) ? s0[2 * rr + 1] * p.scale : -INFINITY;
-                sc[2] = (p0 + 8 + 2 * t < lim) ? s1[2 * rr] * p.scale : -INFINITY;
-                sc[3] = (p0 + 8 + 2 * t + 1 < lim) ? s1[2 * rr + 1] * p.scale : -INFINITY;
+                sc[0] = (p0 + 2 * t < lim[rr]) ? s0[2 * rr] * p.scale : -INFINITY;
+                sc[1] = (p0 + 2 * t + 1 < lim[rr]) ? s0[2 * rr + 1] * p.scale : -INFINITY;
+                sc[2] = (p0 + 8 + 2 * t < lim[rr]) ? s1[2 * rr] * p.scale : -INFINITY;
+                sc[3] = (p0 + 8 + 2 * t + 1 < lim[rr]) ? s1[2 * rr + 1] * p.scale : -INFINITY;
                 float mt = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
                 mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 1));
                 mt = fmaxf(mt, __shfl_xor_sync(0xffffffffu, mt, 2));
                 const float m_new = fmaxf(mx[rr], mt);
-                // (a row of the pair may have nothing in this step: the last position belongs to the partner alone)
+                // (a row may have nothing in this step: the last positions belong to later rows alone)
                 rs[rr] = mx[rr] == -INFINITY ? 0.0f : expf(mx[rr] - m_new);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) pr[rr][i] = sc[i] == -INFINITY ? 0.0f : expf(sc[i] - m_new);
@@ -1164,12 +1172,12 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
             }
             __syncwarp();  // the stage is refilled two steps from now
         }
-        // this warp's state for heads 0..G-1 of each row, then one warp per (row, head) merges the warps
+        // this warp's state per fragment row, then one warp per live fragment row merges the warps
         __syncthreads();
-        if (g < G) {
 #pragma unroll
-            for (int rr = 0; rr < NR; ++rr) {
-                float *stt = merge + (size_t)((warp * NR + rr) * ATT_MAX_GROUP + g) * ATT_PART;
+        for (int rr = 0; rr < NR; ++rr) {
+            if (hh < G && row0 + rr * RH + sr < p.m) {
+                float *stt = merge + (size_t)(warp * 8 * NR + rr * 8 + g) * ATT_PART;
 #pragma unroll
                 for (int nt = 0; nt < 16; ++nt) *reinterpret_cast<float2 *>(stt + nt * 8 + 2 * t) = make_float2(o[nt][2 * rr], o[nt][2 * rr + 1]);
                 if (t == 0) {
@@ -1179,24 +1187,24 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
             }
         }
         __syncthreads();
-        for (int hr = warp; hr < NR * G; hr += ATC_WARPS) {
-            const int rr = hr / G, h = hr % G;
-            if (rr == 1 && !has1) continue;
+        for (int fr = warp; fr < 8 * NR; fr += ATC_WARPS) {
+            const int h = (fr & 7) % Gp, qrow = row0 + (fr >> 3) * RH + (fr & 7) / Gp;
+            if (h >= G || qrow >= p.m) continue;
             float M = -INFINITY;
 #pragma unroll
-            for (int w = 0; w < ATC_WARPS; ++w) M = fmaxf(M, merge[(size_t)((w * NR + rr) * ATT_MAX_GROUP + h) * ATT_PART + TILE_ROWS]);
+            for (int w = 0; w < ATC_WARPS; ++w) M = fmaxf(M, merge[(size_t)(w * 8 * NR + fr) * ATT_PART + TILE_ROWS]);
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
             float d = 0.0f;
 #pragma unroll
             for (int w = 0; w < ATC_WARPS; ++w) {
-                const float *stt = merge + (size_t)((w * NR + rr) * ATT_MAX_GROUP + h) * ATT_PART;
+                const float *stt = merge + (size_t)(w * 8 * NR + fr) * ATT_PART;
                 const float mw = stt[TILE_ROWS];
                 const float wgt = mw == -INFINITY ? 0.0f : expf(mw - M);
                 const float4 aw = *reinterpret_cast<const float4 *>(stt + 4 * lane);
                 a.x += wgt * aw.x; a.y += wgt * aw.y; a.z += wgt * aw.z; a.w += wgt * aw.w;
                 d += wgt * stt[TILE_ROWS + 1];
             }
-            float *dst = p.part + (((size_t)(row0 + rr) * (p.n_kv_heads * p.group) + (size_t)(kvh * p.group + g0 + h)) * p.n_splits + split) * ATT_PART;
+            float *dst = p.part + (((size_t)qrow * (p.n_kv_heads * p.group) + (size_t)(kvh * p.group + g0 + h)) * p.n_splits + split) * ATT_PART;
             *reinterpret_cast<float4 *>(dst + 4 * lane) = a;
             if (lane == 0) {
                 dst[TILE_ROWS] = M;

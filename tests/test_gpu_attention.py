@@ -16,7 +16,8 @@ def f16_rows(orc, rows):
 
 
 @pytest.mark.parametrize("n_heads,n_kv,n_pos,m", [(8, 2, 33, 1), (64, 8, 700, 1), (16, 16, 257, 3), (8, 1, 1, 1),
-                                                    (32, 4, 4096, 2)])
+                                                    (32, 4, 4096, 2), (32, 8, 300, 8), (8, 4, 150, 7),
+                                                    (12, 1, 90, 3), (64, 8, 130, 5), (32, 8, 3, 8)])
 def test_attention_core_matches_attend_one(orc, n_heads, n_kv, n_pos, m):
     from allpaka_b200 import gpu as G
 
