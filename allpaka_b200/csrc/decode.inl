@@ -140,10 +140,15 @@ int launch_attention(apk_ctx *c, const apk_kv *kv, uint32_t layer, const float *
             CUDA_TRY(cudaFuncSetAttribute((const void *)attn_split_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM));
             c->attn_tc_ready = true;
         }
-        // verify batches: 16 / group consecutive rows share one pass over K and V
-        if (m > 1)
-            CUDA_TRY(launch_ex(c, attn_split_tc_kernel<true>, dim3(ap.n_kv_heads, ap.n_splits, (m + atc_rows(ap.group) - 1) / atc_rows(ap.group)), dim3(ATC_WARPS * 32), (size_t)ATC_SMEM, c->use_pdl, ap, pdl));
-        else
+        // verify batches: 16 / group consecutive rows share one pass over K and V.  Batches of more rows
+        // than that take several CTAs per (kv head, split): they sit next to each other in the grid, so
+        // that they stream the same K and V rows at the same time and all but one hit in L2, and the
+        // splits shrink to keep the whole grid within one wave.
+        if (m > 1) {
+            const int nz = ((int)m + atc_rows(ap.group) - 1) / atc_rows(ap.group);
+            ap.n_splits = std::min(ap.n_splits, std::max(1, 2 * c->n_sm / (ap.n_kv_heads * nz)));
+            CUDA_TRY(launch_ex(c, attn_split_tc_kernel<true>, dim3(nz, ap.n_kv_heads, ap.n_splits), dim3(ATC_WARPS * 32), (size_t)ATC_SMEM, c->use_pdl, ap, pdl));
+        } else
             CUDA_TRY(launch_ex(c, attn_split_tc_kernel<false>, dim3(ap.n_kv_heads, ap.n_splits, 1), dim3(ATC_WARPS * 32), (size_t)ATC_SMEM, c->use_pdl, ap, pdl));
     } else {
         CUDA_TRY(launch_ex(c, attn_split_kernel, dim3(ap.n_kv_heads, ap.n_splits, m), dim3(ATT_WARPS * 32), 0, c->use_pdl, ap, pdl));

@@ -1023,7 +1023,7 @@ __device__ __forceinline__ void split_f16x2(float x, float y, uint32_t &hi, uint
 // PAIR = false: one query row per CTA, rows 8..15 of the mma stay zero (decode).  PAIR = true (verify
 // batches): consecutive query rows share the K and V stream.  Each half of the 16 fragment rows holds
 // 8 / Gp query rows of Gp heads (Gp = the group size rounded up to a power of two, at most 8), each
-// row with its own causal limit and softmax state; grid.z = ceil(m / atc_rows(group)).
+// row with its own causal limit and softmax state; grid.x = ceil(m / atc_rows(group)).
 // the group size (at most 8 heads per pass) rounded up to a power of two, and the query rows one CTA of
 // the PAIR kernel takes
 __host__ __device__ inline int atc_group_pow2(int group) { return group <= 1 ? 1 : group <= 2 ? 2 : group <= 4 ? 4 : 8; }
@@ -1040,7 +1040,8 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
     __half *stages = reinterpret_cast<__half *>(att_smem);
     float *merge = reinterpret_cast<float *>(att_smem);  // [warp][row of the pair][head][ATT_PART], over the stages once every warp is through with them
     const int Gp = PAIR ? atc_group_pow2(p.group) : 8, RH = 8 / Gp, NRC = NR * RH;  // rows per half, rows per CTA
-    const int kvh = blockIdx.x, split = blockIdx.y, row0 = NRC * blockIdx.z;
+    // grid (kv heads, splits, 1), or for PAIR (row groups, kv heads, splits): the CTAs that walk the same K and V rows are neighbours
+    const int kvh = PAIR ? blockIdx.y : blockIdx.x, split = PAIR ? blockIdx.z : blockIdx.y, row0 = PAIR ? NRC * blockIdx.x : 0;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int hh = g % Gp, sr = g / Gp;                    // this lane's head of the group and row of the half
     const uint32_t base = p.pos_dev ? *p.pos_dev : p.pos;  // query row r sees positions 0..=base + r
