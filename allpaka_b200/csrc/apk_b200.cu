@@ -61,6 +61,7 @@ uint64_t now_ns() {
 bool block_geom(uint32_t ty, uint32_t *be, uint32_t *bb) {
     // crates/allpaka-dtype/src/lib.rs:79-108
     if (ty == APK_TY_Q8_0) { *be = 32; *bb = 34; return true; }
+    if (ty == APK_TY_Q5_0) { *be = 32; *bb = 22; return true; }
     if (ty == APK_TY_Q4_K) { *be = 256; *bb = 144; return true; }
     if (ty == APK_TY_Q5_K) { *be = 256; *bb = 176; return true; }
     if (ty == APK_TY_Q6_K) { *be = 256; *bb = 210; return true; }
@@ -257,6 +258,7 @@ namespace {
 
 MvKernel pick_kernel(uint32_t ty, int m_eff, bool dump) {
     if (ty == APK_TY_Q8_0) return mv_pick_q8_0(m_eff, dump);
+    if (ty == APK_TY_Q5_0) return mv_pick_q5_0(m_eff, dump);
     if (ty == APK_TY_Q4_K) return mv_pick_q4_k(m_eff, dump);
     if (ty == APK_TY_Q5_K) return mv_pick_q5_k(m_eff, dump);
     if (ty == APK_TY_Q6_K) return mv_pick_q6_k(m_eff, dump);
@@ -265,7 +267,7 @@ MvKernel pick_kernel(uint32_t ty, int m_eff, bool dump) {
 
 int init_kernel_attrs(apk_ctx *c) {
     static const int ms[] = {1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 14, 16};
-    for (uint32_t ty : {APK_TY_Q8_0, APK_TY_Q4_K, APK_TY_Q5_K, APK_TY_Q6_K})
+    for (uint32_t ty : {APK_TY_Q8_0, APK_TY_Q5_0, APK_TY_Q4_K, APK_TY_Q5_K, APK_TY_Q6_K})
         for (int m : ms)
             for (int dump = 0; dump < 2; ++dump) {
                 MvKernel k = pick_kernel(ty, m, dump != 0);
@@ -320,7 +322,7 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
     m->n_tiles = (int)((n_out + TILE_ROWS - 1) / TILE_ROWS);
     const int kt = ty_k45((int)ty) ? Q4_KT_SB * 8 : Q8_KT;
     m->KS = (m->nb + kt - 1) / kt;
-    m->tile_bytes = ty == APK_TY_Q8_0 ? (uint32_t)m->nb * Q8_BLOCK_UNIT
+    m->tile_bytes = ty_b32((int)ty) ? (uint32_t)m->nb * (uint32_t)b32_unit((int)ty)
                                       : (uint32_t)(m->nb / 8) * (ty == APK_TY_Q4_K ? Q4_SB_UNIT : (ty == APK_TY_Q5_K ? Q5_SB_UNIT : Q6_SB_UNIT));
     m->bytes = (size_t)m->n_tiles * m->tile_bytes;
     CUDA_TRY(cudaMalloc((void **)&m->d, m->bytes));
@@ -357,11 +359,13 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
             rp.group = s.group;
             rp.stride = s.stride;
             rp.offset = s.offset;
-            const size_t total = ty == APK_TY_Q8_0 ? nr * (size_t)m->nb : nr * (size_t)(m->nb / 8);
+            const size_t total = ty_b32((int)ty) ? nr * (size_t)m->nb : nr * (size_t)(m->nb / 8);
             const int threads = 256;
             const unsigned blocks = (unsigned)((total + threads - 1) / threads);
             if (ty == APK_TY_Q8_0)
                 repack_q8_0_kernel<<<blocks, threads, 0, c->stream>>>(rp);
+            else if (ty == APK_TY_Q5_0)
+                repack_q5_0_kernel<<<blocks, threads, 0, c->stream>>>(rp);
             else if (ty == APK_TY_Q4_K)
                 repack_q45_k_kernel<false><<<blocks, threads, 0, c->stream>>>(rp);
             else if (ty == APK_TY_Q5_K)
@@ -1171,6 +1175,8 @@ int apk_debug_synth_matrix(apk_ctx *c, void *w, uint32_t ty, uint32_t n_out, uin
     const unsigned blocks = (unsigned)((n_blocks + 255) / 256);
     if (ty == APK_TY_Q8_0)
         synth_q8_0_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
+    else if (ty == APK_TY_Q5_0)
+        synth_q5_0_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
     else if (ty == APK_TY_Q4_K)
         synth_q4_k_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
     else if (ty == APK_TY_Q5_K)

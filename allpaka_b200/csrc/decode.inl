@@ -502,7 +502,7 @@ int launch_embed(apk_ctx *c, Plan *P, const uint32_t *token_dev, uint32_t token,
     ep.token = token;
     ep.x = x;
     ep.err = c->d_err;
-    const int threads = E->ty == APK_TY_Q8_0 ? E->nb * 8 : (E->nb / 8) * (ty_k45((int)E->ty) ? 32 : 16);
+    const int threads = ty_b32((int)E->ty) ? E->nb * 8 : (E->nb / 8) * (ty_k45((int)E->ty) ? 32 : 16);
     embed_row_kernel<<<(threads + 255) / 256, 256, 0, c->stream>>>(ep);
     CUDA_TRY(cudaGetLastError());
     c->st.launches++;

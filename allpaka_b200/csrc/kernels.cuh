@@ -56,9 +56,16 @@ constexpr int Q5_SB_RG = 5760;       // Q5_K: 4096 B nibbles + 1024 B high bits 
 constexpr int Q5_SB_UNIT = 4 * Q5_SB_RG;  // 128 rows: 23040 B (22528 B of GGUF blocks + split scale bytes)
 constexpr int Q6_SB_RG = 6720;       // one row group of a Q6_K super-block: 4096 B ql + 2048 B qh + 512 B scales + 64 B d
 constexpr int Q6_SB_UNIT = 4 * Q6_SB_RG;  // 128 rows: 26880 B = 128 * 210 B
+constexpr int Q50_BLOCK_UNIT = 2816; // Q5_0, 128 rows * 22 B: 2048 B nibbles + 512 B fifth bits + 256 B scales
 __host__ __device__ constexpr int stage_w_bytes(int ty) {  // one full K-step of weights
-    return ty == 8 ? 8 * 4352 : (ty == 14 ? 26880 : (ty == 13 ? 2 * 23040 : 2 * 18944));
+    return ty == 8 ? 8 * 4352 : (ty == 6 ? 8 * 2816 : (ty == 14 ? 26880 : (ty == 13 ? 2 * 23040 : 2 * 18944)));
 }
+// Q8_0 and Q5_0: 32-element blocks with one f16 scale, eight blocks per K-step.  Within a K-step of kb
+// blocks the stream holds kb fragment arrays (b32_q_bytes each), for Q5_0 then kb arrays of fifth
+// bits (512 B each), then kb arrays of 128 scales.
+__host__ __device__ constexpr bool ty_b32(int ty) { return ty == 8 || ty == 6; }
+__host__ __device__ constexpr int b32_q_bytes(int ty) { return ty == 6 ? 2048 : 4096; }
+__host__ __device__ constexpr int b32_unit(int ty) { return ty == 6 ? Q50_BLOCK_UNIT : Q8_BLOCK_UNIT; }
 // Q4_K and Q5_K share everything but the fifth bit: row-group size and header offset of a super-block
 __host__ __device__ constexpr bool ty_k45(int ty) { return ty == 12 || ty == 13; }
 __host__ __device__ constexpr int k45_sb_rg(int ty) { return ty == 13 ? Q5_SB_RG : Q4_SB_RG; }
@@ -71,6 +78,7 @@ constexpr int N_FINISHERS = N_FINISH_WARPS * 32;
 constexpr int MV_THREADS = N_CONSUMERS + 32 + N_FINISHERS;  // consumers | producer warp | finisher warps
 constexpr int MAX_M_EFF = 16;
 constexpr int MAX_STAGES = 8;
+constexpr int TY_Q5_0 = 6;
 constexpr int TY_Q8_0 = 8;
 constexpr int TY_Q4_K = 12;
 constexpr int TY_Q5_K = 13;
@@ -419,6 +427,30 @@ __device__ __forceinline__ int s8_of(const uint4 &v, int i) {
     return (int)(x << (24 - 8 * (i & 3))) >> 24;
 }
 
+// Q5_0: q - 16 as int8 is the nibble with 0xF0 on top where the fifth bit is clear.  The repack stores
+// the fifth bits inverted, per lane one byte per fragment row: bits 0..3 for elements 4t..4t+3, bits
+// 4..7 for elements 16+4t..16+4t+3 (crates/allpaka-backend/src/quantmat/q8_acts.rs:115-120).
+__device__ __forceinline__ uint32_t q5_0_top(uint32_t inv4) { return ((inv4 * 0x00204081u) & 0x01010101u) * 0xF0u; }
+__device__ __forceinline__ uint4 q5_0_unpack(const uint2 nib, uint32_t inv) {
+    uint4 a;
+    a.x = (nib.x & 0x0f0f0f0fu) | q5_0_top(inv & 15u);
+    a.y = (nib.y & 0x0f0f0f0fu) | q5_0_top((inv >> 8) & 15u);
+    a.z = ((nib.x >> 4) & 0x0f0f0f0fu) | q5_0_top((inv >> 4) & 15u);
+    a.w = ((nib.y >> 4) & 0x0f0f0f0fu) | q5_0_top((inv >> 12) & 15u);
+    return a;
+}
+// the A fragment of 16 rows (row group rg, half h16) of block b in a staged K-step of kb blocks
+template <int TY>
+__device__ __forceinline__ uint4 b32_frag(const uint8_t *sw, int kb, int b, int rg, int h16, int lane) {
+    if constexpr (TY == TY_Q5_0) {
+        const uint2 nib = *reinterpret_cast<const uint2 *>(sw + b * 2048 + rg * 512 + h16 * 256 + lane * 8);
+        const uint32_t inv = *reinterpret_cast<const uint16_t *>(sw + kb * 2048 + b * 512 + rg * 128 + h16 * 64 + lane * 2);
+        return q5_0_unpack(nib, inv);
+    } else {
+        return *reinterpret_cast<const uint4 *>(sw + b * 4096 + rg * 1024 + h16 * 512 + lane * 16);
+    }
+}
+
 // ----------------------------------------------------- activation quantiser
 //
 // One warp quantises one 32-element block; lane = element.  Arithmetic of
@@ -723,6 +755,35 @@ static __global__ void repack_q8_0_kernel(RepackParams p) {
         *reinterpret_cast<uint32_t *>(frag + lane * 16 + reg * 4) = v;
     }
     uint16_t *sc = reinterpret_cast<uint16_t *>(unit + kb * 4096 + ((bl * 4 + rg) * 8 + g) * 8 + (h16 * 2 + upper) * 2);
+    *sc = (uint16_t)(s[0] | (s[1] << 8));
+}
+
+// Q5_0, one thread per (row, block): 22 source bytes {f16 d, u32 qh, 16 B nibbles} -> four nibble words
+// (byte j = elements j and j + 16, as in the file), the inverted fifth bits of this row's lanes, scale.
+static __global__ void repack_q5_0_kernel(RepackParams p) {
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const size_t total = (size_t)p.src_rows * p.nb;
+    if (idx >= total) return;
+    const int r = (int)(idx / p.nb), b = (int)(idx % p.nb);
+    const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)b * 22;
+    const int dr = map_row(p, r);
+    const int tile = dr / TILE_ROWS, rt = dr % TILE_ROWS;
+    int rg, h16, g, upper;
+    frag_pos(rt, rg, h16, g, upper);
+    const int ks = b / Q8_KT, bl = b % Q8_KT;
+    const int kb = min(Q8_KT, p.nb - ks * Q8_KT);
+    uint8_t *unit = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)ks * Q8_KT * Q50_BLOCK_UNIT;
+    const uint32_t inv = ~((uint32_t)s[2] | ((uint32_t)s[3] << 8) | ((uint32_t)s[4] << 16) | ((uint32_t)s[5] << 24));
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+        const uint32_t v = (uint32_t)s[6 + 4 * w] | ((uint32_t)s[7 + 4 * w] << 8) | ((uint32_t)s[8 + 4 * w] << 16) |
+                           ((uint32_t)s[9 + 4 * w] << 24);
+        const int lane = g * 4 + w;
+        *reinterpret_cast<uint32_t *>(unit + bl * 2048 + rg * 512 + h16 * 256 + lane * 8 + upper * 4) = v;
+        unit[kb * 2048 + bl * 512 + rg * 128 + h16 * 64 + lane * 2 + upper] =
+            (uint8_t)(((inv >> (4 * w)) & 15u) | (((inv >> (16 + 4 * w)) & 15u) << 4));
+    }
+    uint16_t *sc = reinterpret_cast<uint16_t *>(unit + kb * 2560 + ((bl * 4 + rg) * 8 + g) * 8 + (h16 * 2 + upper) * 2);
     *sc = (uint16_t)(s[0] | (s[1] << 8));
 }
 
@@ -1291,6 +1352,28 @@ static __global__ void __launch_bounds__(256) embed_row_kernel(EmbedParams p) {
         o.z = __fmul_rn(d, (float)(int8_t)((v >> 16) & 0xffu));
         o.w = __fmul_rn(d, (float)(int8_t)(v >> 24));
         *reinterpret_cast<float4 *>(p.x + b * 32 + 4 * w) = o;
+    } else if (p.ty == TY_Q5_0) {
+        // one thread per (block, four elements): x = d * (q - 16) (dequant.rs:131-141)
+        const int b = idx >> 3, w = idx & 7;
+        if (b >= p.nb) return;
+        const int ks = b / Q8_KT, bl = b % Q8_KT;
+        const int kb = min(Q8_KT, p.nb - ks * Q8_KT);
+        const uint8_t *unit = p.W + (size_t)tile * p.tile_bytes + (size_t)ks * Q8_KT * Q50_BLOCK_UNIT;
+        const int lane = g * 4 + (w & 3);
+        uint32_t nib = *reinterpret_cast<const uint32_t *>(unit + bl * 2048 + rg * 512 + h16 * 256 + lane * 8 + upper * 4);
+        uint32_t inv = unit[kb * 2048 + bl * 512 + rg * 128 + h16 * 64 + lane * 2 + upper];
+        if (w >= 4) {
+            nib >>= 4;
+            inv >>= 4;
+        }
+        const uint32_t v = (nib & 0x0f0f0f0fu) | q5_0_top(inv & 15u);
+        const float d = __half2float(*reinterpret_cast<const __half *>(unit + kb * 2560 + ((bl * 4 + rg) * 8 + g) * 8 + (h16 * 2 + upper) * 2));
+        float4 o;
+        o.x = __fmul_rn(d, (float)(int8_t)(v & 0xffu));
+        o.y = __fmul_rn(d, (float)(int8_t)((v >> 8) & 0xffu));
+        o.z = __fmul_rn(d, (float)(int8_t)((v >> 16) & 0xffu));
+        o.w = __fmul_rn(d, (float)(int8_t)(v >> 24));
+        *reinterpret_cast<float4 *>(p.x + b * 32 + 4 * w) = o;
     } else if (p.ty == TY_Q6_K) {
         // one thread per (super-block, half, 4-byte word): four values of each of the half's quarters,
         // x = d * sc * q in that order (dequant.rs:290-293)
@@ -1393,6 +1476,23 @@ __device__ __forceinline__ float absnormal(uint64_t h, float sigma) {
     const float u1 = ((float)(uint32_t)(h >> 40) + 1.0f) * (1.0f / 16777217.0f);
     const float u2 = (float)(uint32_t)(h & 0xffffffu) * (1.0f / 16777216.0f);
     return fabsf(sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2)) * sigma;
+}
+// Q5_0: scale |N(0, 0.02)| / 15, uniform fifth bits and nibbles
+static __global__ void synth_q5_0_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    uint8_t *o = dst + b * 22;
+    const uint64_t base = splitmix64(seed) ^ (b * 0x9E3779B97F4A7C15ull);
+    const unsigned short db = __half_as_ushort(__float2half_rn(absnormal(splitmix64(base ^ 0x51ull), 0.02f) / 15.0f));
+    o[0] = (uint8_t)(db & 0xff);
+    o[1] = (uint8_t)(db >> 8);
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        const uint64_t h = splitmix64(base + (uint64_t)i + 1);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (2 + i * 8 + j < 22) o[2 + i * 8 + j] = (uint8_t)(h >> (8 * j));
+    }
 }
 // one thread per block of the raw row-major GGUF layout
 static __global__ void synth_q8_0_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
@@ -1795,9 +1895,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 const int t = (int)(u / p.KS), ks = (int)(u % p.KS);
                 const int kb = min(kt, p.nb - ks * kt);
                 uint32_t wbytes, woff;
-                if (TY == TY_Q8_0) {
-                    wbytes = (uint32_t)kb * Q8_BLOCK_UNIT;
-                    woff = (uint32_t)ks * Q8_KT * Q8_BLOCK_UNIT;
+                if (ty_b32(TY)) {
+                    wbytes = (uint32_t)kb * b32_unit(TY);
+                    woff = (uint32_t)ks * Q8_KT * b32_unit(TY);
                 } else if (TY == TY_Q6_K) {
                     wbytes = (uint32_t)Q6_SB_UNIT;
                     woff = (uint32_t)ks * Q6_SB_UNIT;
@@ -2180,9 +2280,8 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                         if (tok < M && gb < p.nb && row < p.n_out) p.dump[((size_t)tok * p.n_out + row) * p.nb + gb] = d[i];
                     }
                 };
-                if (TY == TY_Q8_0) {
-                    const uint8_t *wa = sw + rgc * 1024 + h16c * 512 + lane * 16;       // + b*4096
-                    const uint8_t *ws = sw + kb * 4096 + (rgc * 8 + lg) * 8 + h16c * 4;  // + b*256: scales of rows lg, lg+8
+                if (ty_b32(TY)) {
+                    const uint8_t *ws = sw + kb * (b32_unit(TY) - 256) + (rgc * 8 + lg) * 8 + h16c * 4;  // + b*256: scales of rows lg, lg+8
 #pragma unroll
                     for (int cb = 0; cb < Q8_KT; cb += BPC) {
                         if (cb < kb) {
@@ -2197,7 +2296,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
 #pragma unroll
                             for (int i = 0; i < BPC; ++i) {
                                 if (cb + i < kb) {
-                                    const uint4 a = *reinterpret_cast<const uint4 *>(wa + (cb + i) * 4096);
+                                    const uint4 a = b32_frag<TY>(sw, kb, cb + i, rgc, h16c, lane);
                                     const uint32_t b0 = my_blk == i ? xb0 : 0u, b1 = my_blk == i ? xb1 : 0u;
                                     if (i & 1) mma_block_s8_acc(e, a, b0, b1);
                                     else mma_block_s8_acc(d, a, b0, b1);
@@ -2359,15 +2458,14 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     }
                 }
             } else
-            if (TY == TY_Q8_0) {
+            if (ty_b32(TY)) {
                 // this warp: blocks kq, kq+4 of the K-step.  Activation rows past M are clamped to
                 // row M-1: their results are computed but never stored, which keeps predicates
                 // out of the loop.
-                const uint8_t *wa = sw + rg * 1024 + lane * 16;           // + b*4096 (+512 for the upper 16 rows)
-                const uint8_t *ws = sw + kb * 4096 + (rg * 8 + lg) * 8;   // + b*256
+                const uint8_t *ws = sw + kb * (b32_unit(TY) - 256) + (rg * 8 + lg) * 8;   // + b*256
                 auto block = [&](int b) {
-                    const uint4 a0 = *reinterpret_cast<const uint4 *>(wa + b * 4096);
-                    const uint4 a1 = *reinterpret_cast<const uint4 *>(wa + b * 4096 + 512);
+                    const uint4 a0 = b32_frag<TY>(sw, kb, b, rg, 0, lane);
+                    const uint4 a1 = b32_frag<TY>(sw, kb, b, rg, 1, lane);
                     const uint2 sc = *reinterpret_cast<const uint2 *>(ws + b * 256);
                     const __half2 s01 = *reinterpret_cast<const __half2 *>(&sc.x);
                     const __half2 s23 = *reinterpret_cast<const __half2 *>(&sc.y);

@@ -25,6 +25,7 @@ LIB_PATH = os.path.join(_HERE, "libapk_b200.so")
 # GGML type ids (crates/allpaka-dtype/src/lib.rs:61-75)
 Q8_0 = 8
 Q4_K = 12
+Q5_0 = 6
 Q5_K = 13
 Q6_K = 14
 

@@ -3,7 +3,7 @@
 The block layouts are the GGUF ones the engine reads from a model file
 (crates/allpaka-dtype/src/lib.rs:93-108; crates/allpaka-gguf/src/dequant.rs:93-126,
 206-231): Q8_0 = ``{f16 d; i8 q[32]}`` (34 B), Q4_K = ``{f16 d; f16 dmin;
-u8 scales[12]; u8 qs[128]}`` (144 B), Q6_K = ``{u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d}``
+u8 scales[12]; u8 qs[128]}`` (144 B), Q5_0 = ``{f16 d; u32 qh; u8 qs[16]}`` (22 B, dequant.rs:128-141), Q6_K = ``{u8 ql[128]; u8 qh[64]; i8 scales[16]; f16 d}``
 (210 B, dequant.rs:265-296).  No model file is needed: the value
 distributions below are the ones the benchmark configurations state.
 """
@@ -11,12 +11,13 @@ from __future__ import annotations
 
 import numpy as np
 
+TY_Q5_0 = 6
 TY_Q8_0 = 8
 TY_Q4_K = 12
 TY_Q5_K = 13
 TY_Q6_K = 14
 
-BLOCK = {TY_Q8_0: (32, 34), TY_Q4_K: (256, 144), TY_Q5_K: (256, 176), TY_Q6_K: (256, 210)}
+BLOCK = {TY_Q8_0: (32, 34), TY_Q5_0: (32, 22), TY_Q4_K: (256, 144), TY_Q5_K: (256, 176), TY_Q6_K: (256, 210)}
 
 
 def expected_bytes(ty: int, elements: int) -> int:
@@ -99,9 +100,22 @@ def q6_k_matrix(n_out: int, n_in: int, seed: int, d_sigma: float = 2.5e-5) -> np
     return out.reshape(-1)
 
 
+def q5_0_matrix(n_out: int, n_in: int, seed: int, scale_sigma: float = 0.02) -> np.ndarray:
+    """5-bit quants uniform in [0,31] (value q - 16), one f16 scale |N(0,sigma)|/15 per block."""
+    rng = np.random.default_rng(seed)
+    nb = n_in // 32
+    out = np.empty((n_out, nb, 22), dtype=np.uint8)
+    d = (np.abs(rng.normal(0.0, scale_sigma, size=(n_out, nb))) / 15.0).astype(np.float16)
+    out[:, :, 0:2] = d.view(np.uint8).reshape(n_out, nb, 2)
+    out[:, :, 2:] = rng.integers(0, 256, size=(n_out, nb, 20), dtype=np.uint8)
+    return out.reshape(-1)
+
+
 def matrix(ty: int, n_out: int, n_in: int, seed: int) -> np.ndarray:
     if ty == TY_Q8_0:
         return q8_0_matrix(n_out, n_in, seed)
+    if ty == TY_Q5_0:
+        return q5_0_matrix(n_out, n_in, seed)
     if ty == TY_Q4_K:
         return q4_k_matrix(n_out, n_in, seed)
     if ty == TY_Q5_K:
@@ -155,7 +169,7 @@ def tame_scales(buf: np.ndarray, ty: int, value: int = 0x211F) -> np.ndarray:
     be, bb = BLOCK[ty]
     v = buf.reshape(-1, bb)
     lo, hi = value & 0xFF, value >> 8
-    offs = {TY_Q8_0: (0,), TY_Q4_K: (0, 2), TY_Q5_K: (0, 2), TY_Q6_K: (208,)}[ty]
+    offs = {TY_Q8_0: (0,), TY_Q5_0: (0,), TY_Q4_K: (0, 2), TY_Q5_K: (0, 2), TY_Q6_K: (208,)}[ty]
     for o in offs:
         v[:, o] = lo
         v[:, o + 1] = hi

@@ -50,6 +50,7 @@ extern "C" {
 #define APK_ERR_OOM (-5)
 
 /* GGML type ids (crates/allpaka-dtype/src/lib.rs:61-75). */
+#define APK_TY_Q5_0 6u
 #define APK_TY_Q8_0 8u
 #define APK_TY_Q4_K 12u
 #define APK_TY_Q5_K 13u

@@ -91,6 +91,7 @@ void orc_scale_min_k4(int j, const uint8_t *p, float *sc, float *mn) {
 static int block_geom(uint32_t ty, size_t *be, size_t *bb) {
     /* crates/allpaka-dtype/src/lib.rs:79-108 */
     if (ty == ORC_TY_Q8_0) { *be = 32; *bb = 34; return 0; }
+    if (ty == ORC_TY_Q5_0) { *be = 32; *bb = 22; return 0; }
     if (ty == ORC_TY_Q4_K) { *be = 256; *bb = 144; return 0; }
     if (ty == ORC_TY_Q5_K) { *be = 256; *bb = 176; return 0; }
     if (ty == ORC_TY_Q6_K) { *be = 256; *bb = 210; return 0; }
@@ -111,6 +112,26 @@ static inline uint16_t le16(const uint8_t *p) { return (uint16_t)(p[0] | (p[1] <
 static void dequant_q8_0_block(const uint8_t *b, float *out) {
     float d = orc_f16_to_f32(le16(b));
     for (int i = 0; i < 32; i++) out[i] = d * (float)(int8_t)b[2 + i];
+}
+
+/* The 32 values q - 16 of a Q5_0 block {f16 d; u32 qh; u8 qs[16]}: element j takes the low nibble of
+ * qs[j] and bit j of qh, element j + 16 the high nibble and bit j + 16
+ * (crates/allpaka-backend/src/quantmat/q8_acts.rs:115-120, dequant.rs:135-138). */
+static void q5_0_values(const uint8_t *b, int8_t out[32]) {
+    uint32_t qh = (uint32_t)b[2] | ((uint32_t)b[3] << 8) | ((uint32_t)b[4] << 16) | ((uint32_t)b[5] << 24);
+    const uint8_t *qs = b + 6;
+    for (int j = 0; j < 16; j++) {
+        out[j] = (int8_t)((int)((qs[j] & 0x0f) | (((qh >> j) & 1u) << 4)) - 16);
+        out[j + 16] = (int8_t)((int)((qs[j] >> 4) | (((qh >> (j + 16)) & 1u) << 4)) - 16);
+    }
+}
+
+/* crates/allpaka-gguf/src/dequant.rs:131-141 */
+static void dequant_q5_0_block(const uint8_t *b, float *out) {
+    float d = orc_f16_to_f32(le16(b));
+    int8_t q[32];
+    q5_0_values(b, q);
+    for (int i = 0; i < 32; i++) out[i] = d * (float)q[i];
 }
 
 /* crates/allpaka-gguf/src/dequant.rs:211-231 */
@@ -187,6 +208,7 @@ int orc_dequant(uint32_t ty, const uint8_t *bytes, size_t n_bytes, float *out, s
     if (block_geom(ty, &be, &bb) || n % be || n / be * bb != n_bytes) return -1;
     for (size_t i = 0; i < n / be; i++) {
         if (ty == ORC_TY_Q8_0) dequant_q8_0_block(bytes + i * bb, out + i * be);
+        else if (ty == ORC_TY_Q5_0) dequant_q5_0_block(bytes + i * bb, out + i * be);
         else if (ty == ORC_TY_Q4_K) dequant_q4_k_block(bytes + i * bb, out + i * be);
         else if (ty == ORC_TY_Q5_K) dequant_q5_k_block(bytes + i * bb, out + i * be);
         else dequant_q6_k_block(bytes + i * bb, out + i * be);
@@ -276,6 +298,35 @@ float orc_dot_q4_k_i8(const uint8_t *row, size_t n_in, const float *dx, const fl
             total += d * sc1 * dot_lo - dmin * mn1 * sum[b_lo];
             total += d * sc2 * dot_hi - dmin * mn2 * sum[b_hi];
         }
+    }
+    return total;
+}
+
+/* crates/allpaka-backend/src/quantmat/q8_acts.rs:100-124 (the not(aarch64) arm): total += d * d_x[b] * dot */
+float orc_dot_q5_0_i8(const uint8_t *row, size_t n_in, const float *dx, const int8_t *q8) {
+    float total = 0.0f;
+    for (size_t bi = 0; bi < n_in / 32; bi++) {
+        const uint8_t *block = row + bi * 22;
+        float d = orc_f16_to_f32(le16(block));
+        int8_t qw[32];
+        q5_0_values(block, qw);
+        total += d * dx[bi] * (float)dot_i8_32(qw, q8 + bi * 32);
+    }
+    return total;
+}
+
+/* crates/allpaka-backend/src/quantmat/dot_f32.rs:39-55: per block s += x0 * xs[j] + x1 * xs[j + 16], total += d * s */
+float orc_dot_q5_0(const uint8_t *row, size_t n_in, const float *x) {
+    float total = 0.0f;
+    for (size_t bi = 0; bi < n_in / 32; bi++) {
+        const uint8_t *block = row + bi * 22;
+        float d = orc_f16_to_f32(le16(block));
+        int8_t q[32];
+        q5_0_values(block, q);
+        const float *xs = x + bi * 32;
+        float s = 0.0f;
+        for (int j = 0; j < 16; j++) s += (float)q[j] * xs[j] + (float)q[j + 16] * xs[j + 16];
+        total += d * s;
     }
     return total;
 }
@@ -475,6 +526,12 @@ int orc_block_dots(uint32_t ty, const uint8_t *w, size_t n_out, size_t n_in, con
             if (ty == ORC_TY_Q8_0) {
                 for (size_t b = 0; b < nb; b++)
                     o[b] = dot_i8_32((const int8_t *)(row + b * 34 + 2), qi + b * 32);
+            } else if (ty == ORC_TY_Q5_0) {
+                for (size_t b = 0; b < nb; b++) {
+                    int8_t qw[32];
+                    q5_0_values(row + b * 22, qw);
+                    o[b] = dot_i8_32(qw, qi + b * 32);
+                }
             } else if (ty == ORC_TY_Q5_K) {
                 for (size_t sb = 0; sb < n_in / 256; sb++) {
                     const uint8_t *block = row + sb * 176;
@@ -668,6 +725,8 @@ static inline float row_dot_any(const mm_ctx *c, size_t i, size_t j) {
     if (c->q) {
         if (c->ty == ORC_TY_Q8_0)
             return orc_dot_q8_0_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
+        if (c->ty == ORC_TY_Q5_0)
+            return orc_dot_q5_0_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
         if (c->ty == ORC_TY_Q6_K)
             return orc_dot_q6_k_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
         if (c->ty == ORC_TY_Q5_K)
@@ -675,6 +734,7 @@ static inline float row_dot_any(const mm_ctx *c, size_t i, size_t j) {
         return orc_dot_q4_k_i8(row, c->n_in, c->d + i * nb, c->sum + i * nb, c->q + i * c->n_in);
     }
     const float *xi = c->x + i * c->n_in;
+    if (c->ty == ORC_TY_Q5_0) return orc_dot_q5_0(row, c->n_in, xi);
     if (c->ty == ORC_TY_Q6_K) return orc_dot_q6_k(row, c->n_in, xi);
     if (c->ty == ORC_TY_Q5_K) return orc_dot_q5_k(row, c->n_in, xi);
     return c->ty == ORC_TY_Q8_0 ? orc_dot_q8_0(row, c->n_in, xi) : orc_dot_q4_k(row, c->n_in, xi);

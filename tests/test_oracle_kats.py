@@ -11,7 +11,7 @@ import pytest
 
 from allpaka_b200 import synth
 
-Q8_0, Q4_K, Q5_K, Q6_K = 8, 12, 13, 14
+Q8_0, Q4_K, Q5_K, Q6_K, Q5_0 = 8, 12, 13, 14, 6
 
 
 def half_bits(orc, x):
@@ -262,6 +262,40 @@ def test_q6_k_block_dots_recombine_to_the_row_dot(orc):
     assert orc.expected_bytes(Q6_K, 512) == 420 and orc.expected_bytes(Q6_K, 300) == 0
 
 
+def test_q5_0_is_scale_times_five_bit_value_minus_16(orc):
+    """dequant.rs:128-141: element j = low nibble of qs[j] with bit j of qh on top, element j + 16 = high
+    nibble with bit j + 16; x = d * (q - 16)."""
+    block = np.zeros(22, dtype=np.uint8)
+    put_f16(orc, block, 0, 0.5)
+    block[6] = 0xA3                      # element 0: 3, element 16: 10
+    block[6 + 15] = 0x0F                 # element 15: 15, element 31: 0
+    block[2] = 0b0000_0001               # bit 0: element 0 -> 3 | 16 = 19
+    block[5] = 0b1000_0000               # bit 31: element 31 -> 0 | 16 = 16
+    out = orc.dequant(Q5_0, block, 32)
+    assert out[0] == 0.5 * 3 and out[16] == 0.5 * (10 - 16) and out[15] == 0.5 * (15 - 16) and out[31] == 0.0
+    assert out[1] == -8.0
+    assert orc.expected_bytes(Q5_0, 64) == 44 and orc.expected_bytes(Q5_0, 48) == 0
+
+
+def test_q5_0_block_dots_recombine_to_the_row_dot(orc):
+    """total += d * d_x[b] * dot (q8_acts.rs:122)."""
+    x = synth.normal_f32(128, 25)
+    d, s, q = orc.q8acts(x)
+    w = synth.q5_0_matrix(3, 128, 26)
+    dots = orc.block_dots(Q5_0, w, 3, 128, q)
+    wv = w.reshape(3, 4, 22)
+    vals = orc.dequant(Q5_0, w, 3 * 128).reshape(3, 4, 32)
+    for j in range(3):
+        total = np.float32(0.0)
+        for b in range(4):
+            dw = np.float32(wv[j, b, 0:2].view(np.float16)[0])
+            if dw > 0:
+                codes = np.rint(vals[j, b] / dw).astype(np.int64)
+                assert dots[0, j, b] == int(np.sum(codes * q[b * 32:(b + 1) * 32].astype(np.int64)))
+            total = np.float32(total + np.float32(np.float32(dw * d[b]) * np.float32(dots[0, j, b])))
+        assert total == np.float32(orc.dot_row(Q5_0, wv[j].reshape(-1), x, q8=True))
+
+
 def test_fused_q4_k_dot_matches_dequant_then_dot(orc):
     """mod.rs:812-838"""
     block = np.zeros(144, dtype=np.uint8)
@@ -317,7 +351,7 @@ def kt_acts():
     return np.array([((i * 7 % 23) - 11.0) * 0.03 for i in range(N_IN)], dtype=np.float32)
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q4_K, Q5_K, Q6_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q4_K, Q5_K, Q6_K])
 def test_float_dot_kernels_match_the_dequantizer(orc, ty):
     """kernel_tests.rs:58-88"""
     x = kt_acts()
@@ -329,7 +363,7 @@ def test_float_dot_kernels_match_the_dequantizer(orc, ty):
     assert abs(got - want) <= 1e-4 * mag + 1e-5
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q4_K, Q5_K, Q6_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q4_K, Q5_K, Q6_K])
 def test_q8_activation_kernels_match_the_dequantizer(orc, ty):
     """kernel_tests.rs:90-121"""
     x = kt_acts()
