@@ -65,8 +65,13 @@ bool block_geom(uint32_t ty, uint32_t *be, uint32_t *bb) {
     if (ty == APK_TY_Q4_K) { *be = 256; *bb = 144; return true; }
     if (ty == APK_TY_Q5_K) { *be = 256; *bb = 176; return true; }
     if (ty == APK_TY_Q6_K) { *be = 256; *bb = 210; return true; }
+    if (ty == APK_TY_Q3_K) { *be = 256; *bb = 110; return true; }
     return false;
 }
+
+// The format a matrix has in device memory: Q3_K is rewritten into the Q6_K stream at load (same
+// sub-block structure and arithmetic, see repack_q6_k_kernel<true>), every other type keeps its own.
+uint32_t stream_ty(uint32_t ty) { return ty == APK_TY_Q3_K ? APK_TY_Q6_K : ty; }
 
 // A device buffer that only ever grows (never while a graph that uses it exists).
 struct DevBuf {
@@ -103,7 +108,8 @@ struct Segment {
 };
 
 struct DevMatrix {
-    uint32_t ty = 0;
+    uint32_t ty = 0;      // format of the device stream (picks the kernel)
+    uint32_t src_ty = 0;  // format of the host bytes it was built from
     uint32_t n_out = 0, n_in = 0;  // of the device matrix (after sharding / fusing)
     int nb = 0, n_tiles = 0, KS = 0;
     uint32_t tile_bytes = 0;
@@ -315,6 +321,9 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
     if (n_in == 0 || n_out == 0 || n_in % be)
         return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "row length %u is not whole %u-element blocks", n_in, be);
     auto m = std::make_unique<DevMatrix>();
+    m->src_ty = ty;
+    const uint32_t src_ty = ty;
+    ty = stream_ty(ty);
     m->ty = ty;
     m->n_out = n_out;
     m->n_in = n_in;
@@ -371,7 +380,7 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
             else if (ty == APK_TY_Q5_K)
                 repack_q45_k_kernel<true><<<blocks, threads, 0, c->stream>>>(rp);
             else
-                repack_q6_k_kernel<<<blocks, threads, 0, c->stream>>>(rp);
+                (src_ty == APK_TY_Q3_K ? repack_q6_k_kernel<true> : repack_q6_k_kernel<false>)<<<blocks, threads, 0, c->stream>>>(rp);
             CUDA_TRY(cudaGetLastError());
             c->st.launches++;
             CUDA_TRY(cudaStreamSynchronize(c->stream));  // staging is reused by the next slab
@@ -1177,6 +1186,8 @@ int apk_debug_synth_matrix(apk_ctx *c, void *w, uint32_t ty, uint32_t n_out, uin
         synth_q8_0_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
     else if (ty == APK_TY_Q5_0)
         synth_q5_0_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
+    else if (ty == APK_TY_Q3_K)
+        synth_q3_k_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
     else if (ty == APK_TY_Q4_K)
         synth_q4_k_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
     else if (ty == APK_TY_Q5_K)

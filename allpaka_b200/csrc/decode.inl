@@ -648,7 +648,7 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
     APK_TRY(finish(c));
     auto orig_bytes = [](const DevMatrix *W) {
         uint32_t be = 32, bb = 34;
-        block_geom(W->ty, &be, &bb);
+        block_geom(W->src_ty, &be, &bb);
         return (double)W->n_out * (W->n_in / be) * bb;
     };
     for (int kind = 0; kind < 5; ++kind) {
@@ -697,7 +697,7 @@ int apk_decode_profile(apk_ctx *c, const apk_token_req *r, uint32_t reps, float 
         if (kind == 0 && L0.v) wb += orig_bytes(L0.v);
         if (kind == 2) {
             uint32_t be = 32, bb = 34;
-            block_geom(W->ty, &be, &bb);
+            block_geom(W->src_ty, &be, &bb);
             wb = 2.0 * (double)P->ffn_l * (H / be) * bb;
         }
         const double in_b = (double)m * W->n_in * 4.0;

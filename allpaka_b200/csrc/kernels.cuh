@@ -80,6 +80,7 @@ constexpr int MAX_M_EFF = 16;
 constexpr int MAX_STAGES = 8;
 constexpr int TY_Q5_0 = 6;
 constexpr int TY_Q8_0 = 8;
+constexpr int TY_Q3_K = 11;  // carried in the Q6_K stream (see repack_q6_k_kernel<true>)
 constexpr int TY_Q4_K = 12;
 constexpr int TY_Q5_K = 13;
 constexpr int TY_Q6_K = 14;
@@ -849,14 +850,49 @@ __global__ void repack_q45_k_kernel(RepackParams p) {
     }
 }
 
+// A Q3_K super-block {u8 hmask[32]; u8 qs[64]; u8 scales[12]; f16 d} rewritten as the Q6_K
+// super-block with the same values.  Both are 16 sub-blocks of 16 elements in natural order with an
+// integer scale each and one f16 d, x = d * sc * q (crates/allpaka-gguf/src/dequant.rs:176-204 and
+// 265-296), and both dots are d * dx * (sc0 * dot0 + sc1 * dot1) per 32-element block
+// (crates/allpaka-backend/src/quantmat/q8_acts.rs:206-210 and 338-342): the signed 3-bit value q
+// becomes the 6-bit code q + 32, the 6-bit scale minus 32 the int8 scale.
+__device__ inline void q3_k_as_q6_k(const uint8_t *s, uint8_t (&o)[210]) {
+    for (int i = 0; i < 192; ++i) o[i] = 0;
+    for (int e = 0; e < 256; ++e) {
+        const int blk = e >> 5, l = e & 31, half = e >> 7, quarter = blk & 3;
+        const int q = ((s[32 + half * 32 + l] >> (2 * quarter)) & 3) - ((s[l] >> blk) & 1 ? 0 : 4);
+        const int code = q + 32;  // 28..35
+        // Q6_K: quarter qr of a half takes the low (qr < 2) or high nibbles of ql[64*half + 32*(qr&1) + l]
+        // and bits 2qr, 2qr+1 of qh[32*half + l]
+        o[half * 64 + (quarter & 1) * 32 + l] |= (uint8_t)((code & 15) << (quarter < 2 ? 0 : 4));
+        o[128 + half * 32 + l] |= (uint8_t)((code >> 4) << (2 * quarter));
+    }
+    const uint8_t *pk = s + 96;
+    for (int i = 0; i < 4; ++i) {  // crates/allpaka-dtype/src/lib.rs:395-404
+        o[192 + i] = (uint8_t)(int8_t)(((pk[i] & 0x0f) | ((pk[8 + i] & 3) << 4)) - 32);
+        o[196 + i] = (uint8_t)(int8_t)(((pk[4 + i] & 0x0f) | (((pk[8 + i] >> 2) & 3) << 4)) - 32);
+        o[200 + i] = (uint8_t)(int8_t)(((pk[i] >> 4) | (((pk[8 + i] >> 4) & 3) << 4)) - 32);
+        o[204 + i] = (uint8_t)(int8_t)(((pk[4 + i] >> 4) | (((pk[8 + i] >> 6) & 3) << 4)) - 32);
+    }
+    o[208] = s[108];
+    o[209] = s[109];
+}
+
 // One thread per (row, super-block): 210 source bytes -> nibble and high-bit fragments, scales, d.
-static __global__ void repack_q6_k_kernel(RepackParams p) {
+// FROM_Q3: the source is Q3_K (110 bytes per super-block), rewritten on the fly.
+template <bool FROM_Q3>
+__global__ void repack_q6_k_kernel(RepackParams p) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int nsb = p.nb / 8;
     const size_t total = (size_t)p.src_rows * nsb;
     if (idx >= total) return;
     const int sb = (int)(idx % nsb), r = (int)(idx / nsb);
-    const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)sb * 210;
+    const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)sb * (FROM_Q3 ? 110 : 210);
+    uint8_t tmp[210];
+    if (FROM_Q3) {
+        q3_k_as_q6_k(s, tmp);
+        s = tmp;
+    }
     const int dr = map_row(p, r);
     const int tile = dr / TILE_ROWS, rt = dr % TILE_ROWS;
     int rg, h16, g, upper;
@@ -1476,6 +1512,21 @@ __device__ __forceinline__ float absnormal(uint64_t h, float sigma) {
     const float u1 = ((float)(uint32_t)(h >> 40) + 1.0f) * (1.0f / 16777217.0f);
     const float u2 = (float)(uint32_t)(h & 0xffffffu) * (1.0f / 16777216.0f);
     return fabsf(sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2)) * sigma;
+}
+// Q3_K: uniform bytes for the masks, quants and packed scales, d ~ |N(0, 1e-4)|
+static __global__ void synth_q3_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    uint8_t *o = dst + b * 110;
+    const uint64_t base = splitmix64(seed) ^ (b * 0x9E3779B97F4A7C15ull);
+    for (int i = 0; i < 14; ++i) {
+        const uint64_t h = splitmix64(base + (uint64_t)i + 1);
+        for (int j = 0; j < 8; ++j)
+            if (i * 8 + j < 108) o[i * 8 + j] = (uint8_t)(h >> (8 * j));
+    }
+    const unsigned short db = __half_as_ushort(__float2half_rn(absnormal(splitmix64(base ^ 0x51ull), 1e-4f)));
+    o[108] = (uint8_t)(db & 0xff);
+    o[109] = (uint8_t)(db >> 8);
 }
 // Q5_0: scale |N(0, 0.02)| / 15, uniform fifth bits and nibbles
 static __global__ void synth_q5_0_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {

@@ -12,12 +12,13 @@ from __future__ import annotations
 import numpy as np
 
 TY_Q5_0 = 6
+TY_Q3_K = 11
 TY_Q8_0 = 8
 TY_Q4_K = 12
 TY_Q5_K = 13
 TY_Q6_K = 14
 
-BLOCK = {TY_Q8_0: (32, 34), TY_Q5_0: (32, 22), TY_Q4_K: (256, 144), TY_Q5_K: (256, 176), TY_Q6_K: (256, 210)}
+BLOCK = {TY_Q8_0: (32, 34), TY_Q5_0: (32, 22), TY_Q3_K: (256, 110), TY_Q4_K: (256, 144), TY_Q5_K: (256, 176), TY_Q6_K: (256, 210)}
 
 
 def expected_bytes(ty: int, elements: int) -> int:
@@ -111,7 +112,22 @@ def q5_0_matrix(n_out: int, n_in: int, seed: int, scale_sigma: float = 0.02) -> 
     return out.reshape(-1)
 
 
+def q3_k_matrix(n_out: int, n_in: int, seed: int, d_sigma: float = 1e-4) -> np.ndarray:
+    """Q3_K = ``{u8 hmask[32]; u8 qs[64]; u8 scales[12]; f16 d}`` (110 B, dequant.rs:176-204): uniform
+    masks, 2-bit quants and packed 6-bit scales, d ~ |N(0, d_sigma)| (value = d * (scale - 32) * q with
+    q in [-4, 3])."""
+    rng = np.random.default_rng(seed)
+    nsb = n_in // 256
+    out = np.empty((n_out, nsb, 110), dtype=np.uint8)
+    out[:, :, 0:108] = rng.integers(0, 256, size=(n_out, nsb, 108), dtype=np.uint8)
+    d = np.abs(rng.normal(0.0, d_sigma, size=(n_out, nsb))).astype(np.float16)
+    out[:, :, 108:110] = d.view(np.uint8).reshape(n_out, nsb, 2)
+    return out.reshape(-1)
+
+
 def matrix(ty: int, n_out: int, n_in: int, seed: int) -> np.ndarray:
+    if ty == TY_Q3_K:
+        return q3_k_matrix(n_out, n_in, seed)
     if ty == TY_Q8_0:
         return q8_0_matrix(n_out, n_in, seed)
     if ty == TY_Q5_0:
@@ -169,7 +185,7 @@ def tame_scales(buf: np.ndarray, ty: int, value: int = 0x211F) -> np.ndarray:
     be, bb = BLOCK[ty]
     v = buf.reshape(-1, bb)
     lo, hi = value & 0xFF, value >> 8
-    offs = {TY_Q8_0: (0,), TY_Q5_0: (0,), TY_Q4_K: (0, 2), TY_Q5_K: (0, 2), TY_Q6_K: (208,)}[ty]
+    offs = {TY_Q8_0: (0,), TY_Q5_0: (0,), TY_Q3_K: (108,), TY_Q4_K: (0, 2), TY_Q5_K: (0, 2), TY_Q6_K: (208,)}[ty]
     for o in offs:
         v[:, o] = lo
         v[:, o + 1] = hi

@@ -48,7 +48,7 @@ if ROOT not in sys.path:
 
 HIDDEN, N_HEADS, N_KV, HEAD_DIM, FFN, VOCAB, N_LAYERS = 5120, 64, 8, 128, 25600, 151936, 64
 EPS, ROPE_BASE = 1e-6, 1e6
-Q8_0, Q4_K, Q6_K = 8, 12, 14
+Q8_0, Q4_K, Q6_K, Q5_0 = 8, 12, 14, 6
 FALLBACK_HBM_GBS = 6650.0
 PARITY_LAYERS = 4
 METRIC = "decode tok/s Qwen3-32B-shape Q8_0"
@@ -60,6 +60,8 @@ def q8_bytes(n_out, n_in):
 
 
 def ty_bytes(ty, n_out, n_in):
+    if ty == Q5_0:
+        return n_out * (n_in // 32) * 22
     return q8_bytes(n_out, n_in) if ty == Q8_0 else n_out * (n_in // 256) * (144 if ty == Q4_K else 210)
 
 
@@ -380,6 +382,17 @@ def run_configs(g, peak):
     us = g.bench_ring("matvec", [G.MatvecReq(Q6_K, c[0], n_in, n_out, x, 1) for c in copies], reps=12)
     g.synth_release()
     out["1_q6_k"] = entry(us, ty_bytes(Q6_K, n_out, n_in) + 4 * (n_in + n_out), par, what="Q6_K 25600x5120 m=1", ring_mb=6 * 107.5)
+    g.detach(keep[1])
+
+    # the same shape in Q5_0 (32-element blocks like Q8_0, nibbles plus a fifth bit)
+    w = synth.q5_0_matrix(n_out, n_in, 1031)
+    assert g.attach(w)
+    par = rel_l2(g.matvec(Q5_0, w, n_in, n_out, x, 1), orc.matmul(Q5_0, w, n_out, n_in, x, 1))
+    g.detach(w)
+    copies, keep = ring([(n_out, n_in)], 7, Q5_0, 73500)
+    us = g.bench_ring("matvec", [G.MatvecReq(Q5_0, c[0], n_in, n_out, x, 1) for c in copies], reps=12)
+    g.synth_release()
+    out["1_q5_0"] = entry(us, ty_bytes(Q5_0, n_out, n_in) + 4 * (n_in + n_out), par, what="Q5_0 25600x5120 m=1", ring_mb=7 * 90.1)
     g.detach(keep[1])
 
     # config 2: RMSNorm -> Q8_0 QKV 10240x5120 -> NeoX RoPE, batch 1 (bf16 x, widened exactly)

@@ -92,6 +92,7 @@ static int block_geom(uint32_t ty, size_t *be, size_t *bb) {
     /* crates/allpaka-dtype/src/lib.rs:79-108 */
     if (ty == ORC_TY_Q8_0) { *be = 32; *bb = 34; return 0; }
     if (ty == ORC_TY_Q5_0) { *be = 32; *bb = 22; return 0; }
+    if (ty == ORC_TY_Q3_K) { *be = 256; *bb = 110; return 0; }
     if (ty == ORC_TY_Q4_K) { *be = 256; *bb = 144; return 0; }
     if (ty == ORC_TY_Q5_K) { *be = 256; *bb = 176; return 0; }
     if (ty == ORC_TY_Q6_K) { *be = 256; *bb = 210; return 0; }
@@ -132,6 +133,41 @@ static void dequant_q5_0_block(const uint8_t *b, float *out) {
     int8_t q[32];
     q5_0_values(b, q);
     for (int i = 0; i < 32; i++) out[i] = d * (float)q[i];
+}
+
+/* Q3_K block {u8 hmask[32]; u8 qs[64]; u8 scales[12]; f16 d}: the 16 six-bit sub-block scales, still
+ * biased by 32 (crates/allpaka-dtype/src/lib.rs:395-404). */
+static void q3_k_scales_raw(const uint8_t *packed, int raw[16]) {
+    for (int i = 0; i < 4; i++) {
+        raw[i] = (packed[i] & 0x0f) | ((packed[8 + i] & 3) << 4);
+        raw[4 + i] = (packed[4 + i] & 0x0f) | (((packed[8 + i] >> 2) & 3) << 4);
+        raw[8 + i] = (packed[i] >> 4) | (((packed[8 + i] >> 4) & 3) << 4);
+        raw[12 + i] = (packed[4 + i] >> 4) | (((packed[8 + i] >> 6) & 3) << 4);
+    }
+}
+
+/* The 32 signed 3-bit values of block blk (0..7) of a super-block: two bits from qs at shift
+ * 2 * (blk % 4), minus 4 where bit blk of hmask is clear (q8_acts.rs:203-205, dequant.rs:193-195). */
+static void q3_k_values(const uint8_t *block, int blk, int8_t out[32]) {
+    const uint8_t *hmask = block, *q = block + 32 + (blk / 4) * 32;
+    int shift = 2 * (blk % 4);
+    uint8_t m = (uint8_t)(1u << blk);
+    for (int l = 0; l < 32; l++) out[l] = (int8_t)(((q[l] >> shift) & 3) - ((hmask[l] & m) ? 0 : 4));
+}
+
+/* crates/allpaka-gguf/src/dequant.rs:176-204 */
+static void dequant_q3_k_block(const uint8_t *b, float *out) {
+    float d_all = orc_f16_to_f32(le16(b + 108));
+    int raw[16];
+    q3_k_scales_raw(b + 96, raw);
+    for (int blk = 0; blk < 8; blk++) {
+        int8_t q[32];
+        q3_k_values(b, blk, q);
+        for (int group = 0; group < 2; group++) {
+            float dl = d_all * (float)(raw[2 * blk + group] - 32);
+            for (int l = 0; l < 16; l++) out[blk * 32 + group * 16 + l] = dl * (float)q[group * 16 + l];
+        }
+    }
 }
 
 /* crates/allpaka-gguf/src/dequant.rs:211-231 */
@@ -209,6 +245,7 @@ int orc_dequant(uint32_t ty, const uint8_t *bytes, size_t n_bytes, float *out, s
     for (size_t i = 0; i < n / be; i++) {
         if (ty == ORC_TY_Q8_0) dequant_q8_0_block(bytes + i * bb, out + i * be);
         else if (ty == ORC_TY_Q5_0) dequant_q5_0_block(bytes + i * bb, out + i * be);
+        else if (ty == ORC_TY_Q3_K) dequant_q3_k_block(bytes + i * bb, out + i * be);
         else if (ty == ORC_TY_Q4_K) dequant_q4_k_block(bytes + i * bb, out + i * be);
         else if (ty == ORC_TY_Q5_K) dequant_q5_k_block(bytes + i * bb, out + i * be);
         else dequant_q6_k_block(bytes + i * bb, out + i * be);
@@ -327,6 +364,53 @@ float orc_dot_q5_0(const uint8_t *row, size_t n_in, const float *x) {
         float s = 0.0f;
         for (int j = 0; j < 16; j++) s += (float)q[j] * xs[j] + (float)q[j + 16] * xs[j + 16];
         total += d * s;
+    }
+    return total;
+}
+
+/* crates/allpaka-backend/src/quantmat/q8_acts.rs:178-218 (the not(aarch64) arm):
+ * total += d_all * dx * (sc0 * dot0 + sc1 * dot1) per 32-element block */
+float orc_dot_q3_k_i8(const uint8_t *row, size_t n_in, const float *dx, const int8_t *q8) {
+    float total = 0.0f;
+    for (size_t bi = 0; bi < n_in / 256; bi++) {
+        const uint8_t *block = row + bi * 110;
+        float d_all = orc_f16_to_f32(le16(block + 108));
+        int raw[16];
+        q3_k_scales_raw(block + 96, raw);
+        for (int b = 0; b < 8; b++) {
+            size_t blk = bi * 8 + (size_t)b;
+            int8_t qw[32];
+            q3_k_values(block, b, qw);
+            float dot0 = (float)orc_dot_i8(qw, q8 + blk * 32, 16);
+            float dot1 = (float)orc_dot_i8(qw + 16, q8 + blk * 32 + 16, 16);
+            float sc0 = (float)(raw[2 * b] - 32), sc1 = (float)(raw[2 * b + 1] - 32);
+            total += d_all * dx[blk] * (sc0 * dot0 + sc1 * dot1);
+        }
+    }
+    return total;
+}
+
+/* crates/allpaka-backend/src/quantmat/dot_f32.rs:58-94: sub-block sums weighted by their scales, one
+ * multiplication by d per super-block */
+float orc_dot_q3_k(const uint8_t *row, size_t n_in, const float *x) {
+    float total = 0.0f;
+    for (size_t bi = 0; bi < n_in / 256; bi++) {
+        const uint8_t *block = row + bi * 110;
+        float d_all = orc_f16_to_f32(le16(block + 108));
+        const float *xb = x + bi * 256;
+        int raw[16];
+        q3_k_scales_raw(block + 96, raw);
+        float blk_sum = 0.0f;
+        for (int b = 0; b < 8; b++) {
+            int8_t q[32];
+            q3_k_values(block, b, q);
+            for (int group = 0; group < 2; group++) {
+                float sub = 0.0f;
+                for (int l = 0; l < 16; l++) sub += (float)q[group * 16 + l] * xb[b * 32 + group * 16 + l];
+                blk_sum += (float)(raw[2 * b + group] - 32) * sub;
+            }
+        }
+        total += d_all * blk_sum;
     }
     return total;
 }
@@ -526,6 +610,21 @@ int orc_block_dots(uint32_t ty, const uint8_t *w, size_t n_out, size_t n_in, con
             if (ty == ORC_TY_Q8_0) {
                 for (size_t b = 0; b < nb; b++)
                     o[b] = dot_i8_32((const int8_t *)(row + b * 34 + 2), qi + b * 32);
+            } else if (ty == ORC_TY_Q3_K) {
+                /* per 32-element block the integer the f32 scales multiply: sc0*dot0 + sc1*dot1
+                 * (q8_acts.rs:206-210; exact in f32 there) */
+                for (size_t sb = 0; sb < n_in / 256; sb++) {
+                    const uint8_t *block = row + sb * 110;
+                    int raw[16];
+                    q3_k_scales_raw(block + 96, raw);
+                    for (int b = 0; b < 8; b++) {
+                        int8_t qw[32];
+                        q3_k_values(block, b, qw);
+                        size_t blk = sb * 8 + (size_t)b;
+                        o[blk] = (int32_t)(raw[2 * b] - 32) * orc_dot_i8(qw, qi + blk * 32, 16) +
+                                 (int32_t)(raw[2 * b + 1] - 32) * orc_dot_i8(qw + 16, qi + blk * 32 + 16, 16);
+                    }
+                }
             } else if (ty == ORC_TY_Q5_0) {
                 for (size_t b = 0; b < nb; b++) {
                     int8_t qw[32];
@@ -727,6 +826,8 @@ static inline float row_dot_any(const mm_ctx *c, size_t i, size_t j) {
             return orc_dot_q8_0_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
         if (c->ty == ORC_TY_Q5_0)
             return orc_dot_q5_0_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
+        if (c->ty == ORC_TY_Q3_K)
+            return orc_dot_q3_k_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
         if (c->ty == ORC_TY_Q6_K)
             return orc_dot_q6_k_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
         if (c->ty == ORC_TY_Q5_K)
@@ -735,6 +836,7 @@ static inline float row_dot_any(const mm_ctx *c, size_t i, size_t j) {
     }
     const float *xi = c->x + i * c->n_in;
     if (c->ty == ORC_TY_Q5_0) return orc_dot_q5_0(row, c->n_in, xi);
+    if (c->ty == ORC_TY_Q3_K) return orc_dot_q3_k(row, c->n_in, xi);
     if (c->ty == ORC_TY_Q6_K) return orc_dot_q6_k(row, c->n_in, xi);
     if (c->ty == ORC_TY_Q5_K) return orc_dot_q5_k(row, c->n_in, xi);
     return c->ty == ORC_TY_Q8_0 ? orc_dot_q8_0(row, c->n_in, xi) : orc_dot_q4_k(row, c->n_in, xi);

@@ -11,7 +11,7 @@ import pytest
 
 from allpaka_b200 import synth
 
-Q8_0, Q4_K, Q5_K, Q6_K, Q5_0 = 8, 12, 13, 14, 6
+Q8_0, Q4_K, Q5_K, Q6_K, Q5_0, Q3_K = 8, 12, 13, 14, 6, 11
 
 
 def half_bits(orc, x):
@@ -296,6 +296,41 @@ def test_q5_0_block_dots_recombine_to_the_row_dot(orc):
         assert total == np.float32(orc.dot_row(Q5_0, wv[j].reshape(-1), x, q8=True))
 
 
+def test_q3_k_values_scales_and_order(orc):
+    """dequant.rs:176-204: x = d * (scale - 32) * q, q = two bits of qs minus 4 where the hmask bit of
+    the block is clear; block blk = 4 * half + shift index, sub-block scale index 2 * blk + group."""
+    block = np.zeros(110, dtype=np.uint8)
+    put_f16(orc, block, 108, 0.25)
+    block[96:108] = 0
+    block[96] = 0x0B | (0x03 << 4)       # raw[0] low nibble 11, raw[8] low nibble 3
+    block[104] = 0b0001_0010             # raw[0] += 2 << 4 = 43, raw[4] += 0, raw[8] += 1 << 4 = 19
+    block[32] = 0b10_01_11_10            # l = 0 of half 0: blocks 0..3 take 2, 3, 1, 2
+    block[0] = 0b0000_0101               # hmask[0]: blocks 0 and 2 keep their value, the others lose 4
+    out = orc.dequant(Q3_K, block, 256)
+    assert out[0] == 0.25 * (43 - 32) * 2             # block 0, group 0: scale raw[0]
+    assert out[32] == 0.25 * (0 - 32) * (3 - 4)       # block 1: raw[2] = 0
+    assert out[64] == 0.25 * (0 - 32) * 1             # block 2: raw[4] = 0
+    assert out[96] == 0.25 * (0 - 32) * (2 - 4)
+    assert out[1] == 0.25 * (43 - 32) * -4 and out[16] == 0.25 * (0 - 32) * -4
+    assert out[128] == 0.25 * (19 - 32) * -4          # block 4, group 0: raw[8]
+    assert orc.expected_bytes(Q3_K, 512) == 220 and orc.expected_bytes(Q3_K, 300) == 0
+
+
+def test_q3_k_block_dots_recombine_to_the_row_dot(orc):
+    """total += d * dx * (sc0 * dot0 + sc1 * dot1) (q8_acts.rs:206-210)."""
+    x = synth.normal_f32(512, 35)
+    d, s, q = orc.q8acts(x)
+    w = synth.q3_k_matrix(3, 512, 36)
+    dots = orc.block_dots(Q3_K, w, 3, 512, q)
+    wv = w.reshape(3, 2, 110)
+    for j in range(3):
+        total = np.float32(0.0)
+        for b in range(16):
+            dw = np.float32(wv[j, b // 8, 108:110].view(np.float16)[0])
+            total = np.float32(total + np.float32(np.float32(dw * d[b]) * np.float32(dots[0, j, b])))
+        assert total == np.float32(orc.dot_row(Q3_K, wv[j].reshape(-1), x, q8=True))
+
+
 def test_fused_q4_k_dot_matches_dequant_then_dot(orc):
     """mod.rs:812-838"""
     block = np.zeros(144, dtype=np.uint8)
@@ -351,7 +386,7 @@ def kt_acts():
     return np.array([((i * 7 % 23) - 11.0) * 0.03 for i in range(N_IN)], dtype=np.float32)
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q4_K, Q5_K, Q6_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q3_K, Q4_K, Q5_K, Q6_K])
 def test_float_dot_kernels_match_the_dequantizer(orc, ty):
     """kernel_tests.rs:58-88"""
     x = kt_acts()
@@ -363,7 +398,7 @@ def test_float_dot_kernels_match_the_dequantizer(orc, ty):
     assert abs(got - want) <= 1e-4 * mag + 1e-5
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q4_K, Q5_K, Q6_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q3_K, Q4_K, Q5_K, Q6_K])
 def test_q8_activation_kernels_match_the_dequantizer(orc, ty):
     """kernel_tests.rs:90-121"""
     x = kt_acts()

@@ -14,7 +14,7 @@ import torch.multiprocessing as mp
 
 from allpaka_b200 import build, gpu, synth
 
-Q8_0, Q4_K, Q5_K, Q6_K = 8, 12, 13, 14
+Q8_0, Q4_K, Q5_K, Q6_K, Q5_0, Q3_K = 8, 12, 13, 14, 6, 11
 
 
 def _free_port():
@@ -110,7 +110,7 @@ def _worker(rank, world, port, ty, out_q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q4_K, Q5_K, Q6_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q3_K, Q4_K, Q5_K, Q6_K])
 def test_two_rank_tensor_parallel_layer_matches_unsharded_oracle(ty):
     build.build()
     from oracle import oracle
@@ -136,6 +136,7 @@ def test_shard_plan_edges():
     build.build()
     assert gpu.shard_plan(gpu.SHARD_ROWS, Q8_0, 8192, 5120, 7, 8, 128) == (7168, 1024, 0, 5120)
     assert gpu.shard_plan(gpu.SHARD_K, Q8_0, 5120, 25600, 3, 8) == (0, 5120, 9600, 3200)
+    assert gpu.shard_plan(gpu.SHARD_K, Q5_0, 5120, 25600, 3, 8) == (0, 5120, 9600, 3200)
     assert gpu.shard_plan(gpu.SHARD_K, Q4_K, 5120, 25600, 0, 8) is None      # 3200 is not whole super-blocks
     assert gpu.shard_plan(gpu.SHARD_K, Q4_K, 5120, 25600, 1, 4) == (0, 5120, 6400, 6400)
     assert gpu.shard_plan(gpu.SHARD_K, Q6_K, 5120, 25600, 0, 8) is None and gpu.shard_plan(gpu.SHARD_K, Q5_K, 5120, 25600, 0, 8) is None
