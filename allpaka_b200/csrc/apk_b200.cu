@@ -241,6 +241,7 @@ struct apk_ctx {
     int dots_launch = -1, launch_no = 0;
     int attn_tc = 1;             // ALLPAKA_B200_ATTN_TC=0: the attention core on CUDA cores instead of tensor cores
     bool attn_tc_ready = false;
+    int attn_min_pos = 256;      // ALLPAKA_B200_ATTN_MIN_POS: fewest cache positions a split of the attention core is sized for
     int tl_alt = 0;              // ALLPAKA_B200_TL_ALT=1: the timeline stamps the closing of each CTA's last tile
     bool prev_mv_exclusive = false;  // the last matvec launched holds every SM to itself (see launch_matvec)
     int smem_per_sm = 0;
@@ -862,6 +863,7 @@ int apk_init(apk_ctx **out, int device) {
     if (const char *e = getenv("ALLPAKA_B200_SELF_XCH")) c->self_xch = atoi(e) != 0;
     if (const char *e = getenv("ALLPAKA_B200_TL_ALT")) c->tl_alt = atoi(e) != 0;
     if (const char *e = getenv("ALLPAKA_B200_ATTN_TC")) c->attn_tc = atoi(e) != 0;
+    if (const char *e = getenv("ALLPAKA_B200_ATTN_MIN_POS")) c->attn_min_pos = std::max(16, std::min(atoi(e), 4096));
     if (c->self_xch) {
         // one rank exchanging with itself: the peer-store epilogue and the collecting prologue on one GPU
         CUDA_TRY(cudaMalloc((void **)&c->xch_local, XCH_BYTES));

@@ -103,15 +103,23 @@ int nccl_allreduce(apk_ctx *c, float *buf, size_t n) {
 
 bool uses_xch(const apk_ctx *c) { return c->p2p_ready && (c->world > 1 || c->self_xch); }
 
-// Position splits of the attention core: fixed per cache (the launch shape is captured).  A split
-// kernel CTA does best with at least 256 positions (four steps per warp: the pipeline fills, the
-// per-CTA prologue and merge amortise), and kv heads x splits should not exceed one wave of two CTAs
-// per SM (measured at 32768 positions: 37 splits 30 us, 43 splits 40 us, 128 splits 43 us).
+// Position splits of the attention core: fixed per cache (the launch shape is captured), and sized
+// in whole steps of a CTA (64 positions) so that the splits come out even.  Long caches: at least 256
+// positions per split (four steps per warp: the pipeline fills, the per-CTA prologue and merge
+// amortise), and kv heads x splits at most one wave of two CTAs per SM (measured at 32768 positions:
+// 37 splits 30 us, 43 splits 40 us, 128 splits 43 us).  Short caches are latency: fewer steps per
+// split while the grid stays within one CTA per SM (measured, 64 q / 8 kv heads: 1024 positions
+// 6.9 us with 16 splits against 11.5 us with 4; 2048 positions 8.1 against 10.7 us with 8; more CTAs
+// than SMs lose again: 4096 positions 11.4 us with 64 splits against 9.9 us with 16).
 int attn_splits(const apk_ctx *c, const apk_kv *kv) {
     const uint32_t n_kv = std::max<uint32_t>(1, kv->kv_dim / TILE_ROWS);
     const uint32_t wave = std::max<uint32_t>(1, 2u * (uint32_t)c->n_sm / n_kv);
-    const uint32_t by_len = (kv->capacity + 255) / 256;
-    return (int)std::max<uint32_t>(1, std::min<uint32_t>(std::min<uint32_t>(wave, by_len), 128));
+    const uint32_t one_per_sm = std::max<uint32_t>(1, (uint32_t)c->n_sm / n_kv);
+    const uint32_t steps = (kv->capacity + 63) / 64;
+    const uint32_t long_steps = std::max<uint32_t>(1, (uint32_t)c->attn_min_pos / 64);
+    uint32_t per = (steps + one_per_sm - 1) / one_per_sm;                        // steps per split, one CTA per SM
+    if (per >= long_steps) per = std::max(long_steps, (steps + wave - 1) / wave);  // two per SM
+    return (int)std::max<uint32_t>(1, std::min<uint32_t>((steps + per - 1) / per, 128));
 }
 
 // q [m][ldq] -> attention over one layer of the cache -> optional f32 rows, optional records for wo.

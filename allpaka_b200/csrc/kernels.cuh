@@ -1101,7 +1101,8 @@ static __global__ void __launch_bounds__(ATT_WARPS * 32) attn_split_kernel(AttnP
 constexpr int ATC_WARPS = 4;
 constexpr int ATC_ROW = TILE_ROWS + 8;   // halves per staged row: 272 B, so the eight rows of an ldmatrix hit distinct banks
 constexpr int ATC_STAGE = 2 * 16 * ATC_ROW;  // halves per stage: K tile, then V tile
-constexpr int ATC_SMEM = ATC_WARPS * 2 * ATC_STAGE * 2;  // 68 KB (the merge buffer reuses the stages); two CTAs per SM by registers
+constexpr int ATC_STAGES = 2;            // per warp: one step of K and V rows in flight while it works on the other (a third stage measured slower: 33.4 against 31.5 us at 32768 positions)
+constexpr int ATC_SMEM = ATC_WARPS * ATC_STAGES * ATC_STAGE * 2;  // 68 KB (the merge buffer reuses the stages); two CTAs per SM by registers
 static_assert(ATC_WARPS * 16 * ATT_PART * 4 <= ATC_SMEM, "the merge buffer lives in the stage memory");
 
 __device__ __forceinline__ void mma_f16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -1143,12 +1144,32 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
     const int hh = g % Gp, sr = g / Gp;                    // this lane's head of the group and row of the half
     const uint32_t base = p.pos_dev ? *p.pos_dev : p.pos;  // query row r sees positions 0..=base + r
     const uint32_t n_pos = base + (uint32_t)min(row0 + NRC, p.m);  // what the last row of this CTA sees
-    const uint32_t per = (n_pos + (uint32_t)p.n_splits - 1u) / (uint32_t)p.n_splits;
+    // positions per split: whole steps of the CTA (16 positions per warp), so that no warp idles through a ragged
+    // last step; the splits this leaves empty publish an empty partial
+    constexpr uint32_t STEP = 16u * ATC_WARPS;
+    const uint32_t per = ((n_pos + (uint32_t)p.n_splits - 1u) / (uint32_t)p.n_splits + STEP - 1u) / STEP * STEP;
     const uint32_t t0 = (uint32_t)split * per, t1 = min(n_pos, t0 + per);
-    __half *my = stages + (size_t)warp * 2 * ATC_STAGE;
+    __half *my = stages + (size_t)warp * ATC_STAGES * ATC_STAGE;
     const uint32_t my_s = (uint32_t)__cvta_generic_to_shared(my);
+    // this warp's 16 positions of step i: t0 + 16 * (warp + ATC_WARPS * i)
+    auto stage_load = [&](uint32_t p0, int st) {
+        // 16 rows x 256 B of K and of V: 512 16-byte chunks, 16 per lane
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            const int ch = j * 32 + lane, kvsel = ch >> 8, r = (ch >> 4) & 15, cc = ch & 15;
+            const uint32_t tr = min(p0 + (uint32_t)r, t1 - 1u);  // rows past the end repeat the last one; their scores are masked
+            const __half *src = (kvsel ? p.vc : p.kc) + (size_t)tr * p.kv_dim + (size_t)kvh * TILE_ROWS + 8 * cc;
+            const uint32_t dst = my_s + (uint32_t)((st * ATC_STAGE + kvsel * 16 * ATC_ROW + r * ATC_ROW + 8 * cc) * 2);
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const uint32_t first = t0 + 16u * (uint32_t)warp, stride = 16u * ATC_WARPS;
     for (int g0 = 0; g0 < p.group; g0 += ATT_MAX_GROUP) {
         const int G = min(ATT_MAX_GROUP, p.group - g0);
+        // the K and V rows of the first two steps are on their way while q is fetched and split
+        if (first < t1) stage_load(first, 0);
+        if (ATC_STAGES > 2 && first + stride < t1) stage_load(first + stride, 1);
         // q of this lane's (row, head) in each half as A fragments, hi and lo, eight k-steps of 16 dimensions
         uint32_t qh[8][2 * NR], ql[8][2 * NR];
         uint32_t lim[NR];
@@ -1181,25 +1202,15 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
             mx[rr] = -INFINITY;
             dn[rr] = 0.0f;
         }
-        // this warp's 16 positions of step i: t0 + 16 * (warp + ATC_WARPS * i)
-        auto stage_load = [&](uint32_t p0, int st) {
-            // 16 rows x 256 B of K and of V: 512 16-byte chunks, 16 per lane
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const int ch = j * 32 + lane, kvsel = ch >> 8, r = (ch >> 4) & 15, cc = ch & 15;
-                const uint32_t tr = min(p0 + (uint32_t)r, t1 - 1u);  // rows past the end repeat the last one; their scores are masked
-                const __half *src = (kvsel ? p.vc : p.kc) + (size_t)tr * p.kv_dim + (size_t)kvh * TILE_ROWS + 8 * cc;
-                const uint32_t dst = my_s + (uint32_t)((st * ATC_STAGE + kvsel * 16 * ATC_ROW + r * ATC_ROW + 8 * cc) * 2);
-                asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
-            }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-        };
-        const uint32_t first = t0 + 16u * (uint32_t)warp, stride = 16u * ATC_WARPS;
-        if (first < t1) stage_load(first, 0);
         int st = 0;
-        for (uint32_t p0 = first; p0 < t1; p0 += stride, st ^= 1) {
-            if (p0 + stride < t1) {
-                stage_load(p0 + stride, st ^ 1);
+        for (uint32_t p0 = first; p0 < t1; p0 += stride, st = st == ATC_STAGES - 1 ? 0 : st + 1) {
+            // ATC_STAGES - 1 steps ahead of this one are in flight; the step fetched now goes to the stage of the step before this one
+            constexpr int AHEAD = ATC_STAGES - 1;
+            if (p0 + AHEAD * stride < t1) {
+                stage_load(p0 + AHEAD * stride, st == 0 ? ATC_STAGES - 1 : st - 1);
+                if (AHEAD == 2) asm volatile("cp.async.wait_group 2;" ::: "memory");
+                else asm volatile("cp.async.wait_group 1;" ::: "memory");
+            } else if (AHEAD == 2 && p0 + stride < t1) {
                 asm volatile("cp.async.wait_group 1;" ::: "memory");
             } else {
                 asm volatile("cp.async.wait_group 0;" ::: "memory");
@@ -1207,20 +1218,35 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
             __syncwarp();
             const uint32_t ks_base = my_s + (uint32_t)(st * ATC_STAGE * 2);
             const uint32_t vs_base = ks_base + 16 * ATC_ROW * 2;
-            // S = Q K^T for two tiles of 8 positions
+            // S = Q K^T for two tiles of 8 positions.  Four accumulator chains (tile x {hi, lo} part of q), so
+            // that consecutive mmas do not wait on each other, and the K fragments of the next k-step are
+            // fetched while this one multiplies.
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-            for (int ks = 0; ks < 8; ++ks) {
-                uint32_t b00, b01, b10, b11;
-                const uint32_t addr = ks_base + (uint32_t)((((lane >> 4) * 8 + (lane & 7)) * ATC_ROW + 16 * ks + ((lane >> 3) & 1) * 8) * 2);
+            {
+                float s0l[4] = {0.f, 0.f, 0.f, 0.f}, s1l[4] = {0.f, 0.f, 0.f, 0.f};
+                uint32_t kb[2][4];
+                const uint32_t addr0 = ks_base + (uint32_t)((((lane >> 4) * 8 + (lane & 7)) * ATC_ROW + ((lane >> 3) & 1) * 8) * 2);
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(b00), "=r"(b01), "=r"(b10), "=r"(b11) : "r"(addr));
-                const uint32_t h1 = PAIR ? qh[ks][1] : 0u, h3 = PAIR ? qh[ks][NR + 1] : 0u;
-                const uint32_t l1 = PAIR ? ql[ks][1] : 0u, l3 = PAIR ? ql[ks][NR + 1] : 0u;
-                mma_f16(s0, qh[ks][0], h1, qh[ks][NR], h3, b00, b01);
-                mma_f16(s0, ql[ks][0], l1, ql[ks][NR], l3, b00, b01);
-                mma_f16(s1, qh[ks][0], h1, qh[ks][NR], h3, b10, b11);
-                mma_f16(s1, ql[ks][0], l1, ql[ks][NR], l3, b10, b11);
+                             : "=r"(kb[0][0]), "=r"(kb[0][1]), "=r"(kb[0][2]), "=r"(kb[0][3]) : "r"(addr0));
+#pragma unroll
+                for (int ks = 0; ks < 8; ++ks) {
+                    if (ks < 7)
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(kb[(ks + 1) & 1][0]), "=r"(kb[(ks + 1) & 1][1]), "=r"(kb[(ks + 1) & 1][2]), "=r"(kb[(ks + 1) & 1][3])
+                                     : "r"(addr0 + 32u * (uint32_t)(ks + 1)));
+                    const uint32_t(&b)[4] = kb[ks & 1];
+                    const uint32_t h1 = PAIR ? qh[ks][1] : 0u, h3 = PAIR ? qh[ks][NR + 1] : 0u;
+                    const uint32_t l1 = PAIR ? ql[ks][1] : 0u, l3 = PAIR ? ql[ks][NR + 1] : 0u;
+                    mma_f16(s0, qh[ks][0], h1, qh[ks][NR], h3, b[0], b[1]);
+                    mma_f16(s1, qh[ks][0], h1, qh[ks][NR], h3, b[2], b[3]);
+                    mma_f16(s0l, ql[ks][0], l1, ql[ks][NR], l3, b[0], b[1]);
+                    mma_f16(s1l, ql[ks][0], l1, ql[ks][NR], l3, b[2], b[3]);
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    s0[i] += s0l[i];
+                    s1[i] += s1l[i];
+                }
             }
             // online softmax: fragment row g (and g+8 in the other half); this lane holds positions p0 + 2t, +1 and p0 + 8 + 2t, +1
             float pr[NR][4], rs[NR];
@@ -1251,22 +1277,31 @@ static __global__ void __launch_bounds__(ATC_WARPS * 32) attn_split_tc_kernel(At
                 split_f16x2(pr[rr][0], pr[rr][1], ph[rr], pl[rr]);
                 split_f16x2(pr[rr][2], pr[rr][3], ph[2 + rr], pl[2 + rr]);
             }
-            // O = O * r + P V, 16 tiles of 8 dimensions
-#pragma unroll
-            for (int nt = 0; nt < 16; nt += 2) {
-                uint32_t b00, b01, b10, b11;
-                const uint32_t addr = vs_base + (uint32_t)(((((lane >> 3) & 1) * 8 + (lane & 7)) * ATC_ROW + (nt + (lane >> 4)) * 8) * 2);
+            // O = O * r + P V, 16 tiles of 8 dimensions; the V fragments of the next pair of tiles are fetched
+            // while this pair multiplies
+            {
+                uint32_t vb[2][4];
+                const uint32_t addr0 = vs_base + (uint32_t)(((((lane >> 3) & 1) * 8 + (lane & 7)) * ATC_ROW + (lane >> 4) * 8) * 2);
                 asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-                             : "=r"(b00), "=r"(b01), "=r"(b10), "=r"(b11) : "r"(addr));
+                             : "=r"(vb[0][0]), "=r"(vb[0][1]), "=r"(vb[0][2]), "=r"(vb[0][3]) : "r"(addr0));
 #pragma unroll
-                for (int u = 0; u < 2; ++u) {
-                    o[nt + u][0] *= rs[0]; o[nt + u][1] *= rs[0];
-                    if (PAIR) { o[nt + u][2] *= rs[NR - 1]; o[nt + u][3] *= rs[NR - 1]; }
+                for (int nt = 0; nt < 16; nt += 2) {
+                    if (nt < 14)
+                        asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(vb[((nt >> 1) + 1) & 1][0]), "=r"(vb[((nt >> 1) + 1) & 1][1]), "=r"(vb[((nt >> 1) + 1) & 1][2]),
+                                       "=r"(vb[((nt >> 1) + 1) & 1][3])
+                                     : "r"(addr0 + 16u * (uint32_t)(nt + 2)));
+                    const uint32_t(&b)[4] = vb[(nt >> 1) & 1];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        o[nt + u][0] *= rs[0]; o[nt + u][1] *= rs[0];
+                        if (PAIR) { o[nt + u][2] *= rs[NR - 1]; o[nt + u][3] *= rs[NR - 1]; }
+                    }
+                    mma_f16(o[nt], ph[0], ph[1], ph[2], ph[3], b[0], b[1]);
+                    mma_f16(o[nt + 1], ph[0], ph[1], ph[2], ph[3], b[2], b[3]);
+                    mma_f16(o[nt], pl[0], pl[1], pl[2], pl[3], b[0], b[1]);
+                    mma_f16(o[nt + 1], pl[0], pl[1], pl[2], pl[3], b[2], b[3]);
                 }
-                mma_f16(o[nt], ph[0], ph[1], ph[2], ph[3], b00, b01);
-                mma_f16(o[nt], pl[0], pl[1], pl[2], pl[3], b00, b01);
-                mma_f16(o[nt + 1], ph[0], ph[1], ph[2], ph[3], b10, b11);
-                mma_f16(o[nt + 1], pl[0], pl[1], pl[2], pl[3], b10, b11);
             }
             __syncwarp();  // the stage is refilled two steps from now
         }

@@ -680,6 +680,13 @@ def run_ours(args, rank, world, local_rank):
         except Exception as e:  # the headline line must not be lost to a side measurement
             configs = {"error": f"{type(e).__name__}: {e}"}
 
+    with_attention = None
+    if rank == 0 and world == 1 and not args.no_configs:
+        try:
+            with_attention = decode_with_attention(g, req, args.steps)
+        except Exception as e:  # a side measurement, like the configs
+            with_attention = {"error": f"{type(e).__name__}: {e}"}
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "tok/s",
@@ -698,6 +705,7 @@ def run_ours(args, rank, world, local_rank):
             "parity": parity,
             "tp_check": tp_check,
             "configs": configs,
+            "decode_with_attention": with_attention,
             "cpu_baseline": cpu,
             "clocks": clocks,
             "setup_s": setup_s,
@@ -712,6 +720,29 @@ def run_ours(args, rank, world, local_rank):
         sys.exit(3)
     if rank == 0 and tp_check is not None and tp_check["p2p_vs_nccl_rel_l2"] > 2e-2:
         sys.exit(3)
+
+
+def decode_with_attention(g, req, steps, positions=4096):
+    """The timed token once more with the decode attention core over an f16 KV cache holding `positions` rows in
+    place of the identity the benchmark configuration names: what a real decoder layer costs.  Same graph replay and
+    event timing as `value`; the cache is all zeros but for the row each replay stores (the work does not depend on
+    the values)."""
+    import dataclasses
+
+    from allpaka_b200 import gpu as G
+
+    kv_dim = N_KV * HEAD_DIM
+    kv = G.KvCache(g, len(req.layers), kv_dim, positions)
+    try:
+        r2 = dataclasses.replace(req, attn_core=G.ATTN_CAUSAL, kv=kv, pos=positions - 1,
+                                 scale=float(np.float32(1.0) / np.sqrt(np.float32(HEAD_DIM))))
+        g.decode_replay(r2, 3)
+        ms = float(np.median([g.decode_replay(r2, steps) for _ in range(5)])) / steps
+    finally:
+        kv.close()
+    kv_bytes = len(req.layers) * 2 * positions * kv_dim * 2
+    return {"positions": positions, "tok_s": 1e3 / ms, "ms_per_step": ms, "kv_bytes_per_step": kv_bytes,
+            "what": "same token, attention core over the f16 KV cache instead of the identity (split + combine kernels per layer)"}
 
 
 def main():
