@@ -13,7 +13,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "build")
 LIB = os.path.join(HERE, "libapk_b200.so")
-SOURCES = ["apk_b200.cu", "mv_q8_0.cu", "mv_q5_0.cu", "mv_q4_k.cu", "mv_q5_k.cu", "mv_q6_k.cu"]
+SOURCES = ["apk_b200.cu", "mv_q8_0.cu", "mv_q5_0.cu", "mv_q2_k.cu", "mv_q4_k.cu", "mv_q5_k.cu", "mv_q6_k.cu"]
 DEPS = SOURCES + ["decode.inl", "noalloc.inl", "gguf.inl", "kernels.cuh", "mv_pick.h",
                   os.path.join("..", "..", "include", "allpaka_b200.h")]
 

@@ -66,6 +66,7 @@ bool block_geom(uint32_t ty, uint32_t *be, uint32_t *bb) {
     if (ty == APK_TY_Q5_K) { *be = 256; *bb = 176; return true; }
     if (ty == APK_TY_Q6_K) { *be = 256; *bb = 210; return true; }
     if (ty == APK_TY_Q3_K) { *be = 256; *bb = 110; return true; }
+    if (ty == APK_TY_Q2_K) { *be = 256; *bb = 84; return true; }
     return false;
 }
 
@@ -269,12 +270,13 @@ MvKernel pick_kernel(uint32_t ty, int m_eff, bool dump) {
     if (ty == APK_TY_Q4_K) return mv_pick_q4_k(m_eff, dump);
     if (ty == APK_TY_Q5_K) return mv_pick_q5_k(m_eff, dump);
     if (ty == APK_TY_Q6_K) return mv_pick_q6_k(m_eff, dump);
+    if (ty == APK_TY_Q2_K) return mv_pick_q2_k(m_eff, dump);
     return nullptr;
 }
 
 int init_kernel_attrs(apk_ctx *c) {
     static const int ms[] = {1, 2, 3, 4, 5, 6, 7, 8, 10, 12, 14, 16};
-    for (uint32_t ty : {APK_TY_Q8_0, APK_TY_Q5_0, APK_TY_Q4_K, APK_TY_Q5_K, APK_TY_Q6_K})
+    for (uint32_t ty : {APK_TY_Q8_0, APK_TY_Q5_0, APK_TY_Q2_K, APK_TY_Q4_K, APK_TY_Q5_K, APK_TY_Q6_K})
         for (int m : ms)
             for (int dump = 0; dump < 2; ++dump) {
                 MvKernel k = pick_kernel(ty, m, dump != 0);
@@ -333,7 +335,7 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
     const int kt = ty_k45((int)ty) ? Q4_KT_SB * 8 : Q8_KT;
     m->KS = (m->nb + kt - 1) / kt;
     m->tile_bytes = ty_b32((int)ty) ? (uint32_t)m->nb * (uint32_t)b32_unit((int)ty)
-                                      : (uint32_t)(m->nb / 8) * (ty == APK_TY_Q4_K ? Q4_SB_UNIT : (ty == APK_TY_Q5_K ? Q5_SB_UNIT : Q6_SB_UNIT));
+                                      : (uint32_t)(m->nb / 8) * (ty == APK_TY_Q4_K ? Q4_SB_UNIT : (ty == APK_TY_Q5_K ? Q5_SB_UNIT : (ty == APK_TY_Q2_K ? Q2_SB_UNIT : Q6_SB_UNIT)));
     m->bytes = (size_t)m->n_tiles * m->tile_bytes;
     CUDA_TRY(cudaMalloc((void **)&m->d, m->bytes));
     CUDA_TRY(cudaMemsetAsync(m->d, 0, m->bytes, c->stream));
@@ -381,7 +383,8 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
             else if (ty == APK_TY_Q5_K)
                 repack_q45_k_kernel<true><<<blocks, threads, 0, c->stream>>>(rp);
             else
-                (src_ty == APK_TY_Q3_K ? repack_q6_k_kernel<true> : repack_q6_k_kernel<false>)<<<blocks, threads, 0, c->stream>>>(rp);
+                (src_ty == APK_TY_Q3_K ? repack_q6_k_kernel<3> : (src_ty == APK_TY_Q2_K ? repack_q6_k_kernel<2> : repack_q6_k_kernel<0>))
+                    <<<blocks, threads, 0, c->stream>>>(rp);
             CUDA_TRY(cudaGetLastError());
             c->st.launches++;
             CUDA_TRY(cudaStreamSynchronize(c->stream));  // staging is reused by the next slab
@@ -1190,6 +1193,8 @@ int apk_debug_synth_matrix(apk_ctx *c, void *w, uint32_t ty, uint32_t n_out, uin
         synth_q5_0_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
     else if (ty == APK_TY_Q3_K)
         synth_q3_k_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
+    else if (ty == APK_TY_Q2_K)
+        synth_q2_k_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
     else if (ty == APK_TY_Q4_K)
         synth_q4_k_kernel<<<blocks, 256, 0, c->stream>>>(d, n_blocks, seed);
     else if (ty == APK_TY_Q5_K)

@@ -56,9 +56,15 @@ constexpr int Q5_SB_RG = 5760;       // Q5_K: 4096 B nibbles + 1024 B high bits 
 constexpr int Q5_SB_UNIT = 4 * Q5_SB_RG;  // 128 rows: 23040 B (22528 B of GGUF blocks + split scale bytes)
 constexpr int Q6_SB_RG = 6720;       // one row group of a Q6_K super-block: 4096 B ql + 2048 B qh + 512 B scales + 64 B d
 constexpr int Q6_SB_UNIT = 4 * Q6_SB_RG;  // 128 rows: 26880 B = 128 * 210 B
+// Q2_K rides on the Q6_K stream (code q + 32, the 4-bit sub-block scales as int8) with its second half appended to
+// each row group: the 4-bit sub-block mins, laid out like the scales, and the f16 dmin, laid out like d.
+constexpr int Q2_SB_RG = Q6_SB_RG + 512 + 64;   // 7296
+constexpr int Q2_SB_UNIT = 4 * Q2_SB_RG;        // 29184
+__host__ __device__ constexpr bool ty_k6(int ty) { return ty == 14 || ty == 10; }
+__host__ __device__ constexpr int k6_sb_rg(int ty) { return ty == 10 ? Q2_SB_RG : Q6_SB_RG; }
 constexpr int Q50_BLOCK_UNIT = 2816; // Q5_0, 128 rows * 22 B: 2048 B nibbles + 512 B fifth bits + 256 B scales
 __host__ __device__ constexpr int stage_w_bytes(int ty) {  // one full K-step of weights
-    return ty == 8 ? 8 * 4352 : (ty == 6 ? 8 * 2816 : (ty == 14 ? 26880 : (ty == 13 ? 2 * 23040 : 2 * 18944)));
+    return ty == 8 ? 8 * 4352 : (ty == 6 ? 8 * 2816 : (ty == 14 ? 26880 : (ty == 10 ? 29184 : (ty == 13 ? 2 * 23040 : 2 * 18944))));
 }
 // Q8_0 and Q5_0: 32-element blocks with one f16 scale, eight blocks per K-step.  Within a K-step of kb
 // blocks the stream holds kb fragment arrays (b32_q_bytes each), for Q5_0 then kb arrays of fifth
@@ -80,6 +86,7 @@ constexpr int MAX_M_EFF = 16;
 constexpr int MAX_STAGES = 8;
 constexpr int TY_Q5_0 = 6;
 constexpr int TY_Q8_0 = 8;
+constexpr int TY_Q2_K = 10;  // the Q6_K stream plus sub-block mins and dmin (see repack_q6_k_kernel<2>)
 constexpr int TY_Q3_K = 11;  // carried in the Q6_K stream (see repack_q6_k_kernel<true>)
 constexpr int TY_Q4_K = 12;
 constexpr int TY_Q5_K = 13;
@@ -878,26 +885,53 @@ __device__ inline void q3_k_as_q6_k(const uint8_t *s, uint8_t (&o)[210]) {
     o[209] = s[109];
 }
 
+// A Q2_K super-block {u8 scales[16]; u8 qs[64]; f16 d; f16 dmin}, x = d * (sc & 15) * q - dmin * (sc >> 4)
+// (crates/allpaka-gguf/src/dequant.rs:150-174): its first term as a Q6_K super-block (code q + 32, scale sc & 15),
+// the 16 mins sc >> 4 and dmin on the side.
+__device__ inline void q2_k_as_q6_k(const uint8_t *s, uint8_t (&o)[210], uint8_t (&mins)[16], uint16_t *dmin) {
+    for (int i = 0; i < 192; ++i) o[i] = 0;
+    for (int e = 0; e < 256; ++e) {
+        const int l = e & 31, half = e >> 7, quarter = (e >> 5) & 3;
+        const int code = ((s[16 + half * 32 + l] >> (2 * quarter)) & 3) + 32;
+        o[half * 64 + (quarter & 1) * 32 + l] |= (uint8_t)((code & 15) << (quarter < 2 ? 0 : 4));
+        o[128 + half * 32 + l] |= (uint8_t)((code >> 4) << (2 * quarter));
+    }
+    for (int i = 0; i < 16; ++i) {
+        o[192 + i] = (uint8_t)(s[i] & 15);
+        mins[i] = (uint8_t)(s[i] >> 4);
+    }
+    o[208] = s[80];
+    o[209] = s[81];
+    *dmin = (uint16_t)(s[82] | (s[83] << 8));
+}
+
 // One thread per (row, super-block): 210 source bytes -> nibble and high-bit fragments, scales, d.
-// FROM_Q3: the source is Q3_K (110 bytes per super-block), rewritten on the fly.
-template <bool FROM_Q3>
+// FROM = 3: the source is Q3_K (110 bytes per super-block), FROM = 2: Q2_K (84 bytes), rewritten on the fly.
+template <int FROM>
 __global__ void repack_q6_k_kernel(RepackParams p) {
+    constexpr bool FROM_Q3 = FROM == 3, FROM_Q2 = FROM == 2;
+    constexpr int RG = FROM_Q2 ? Q2_SB_RG : Q6_SB_RG;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const int nsb = p.nb / 8;
     const size_t total = (size_t)p.src_rows * nsb;
     if (idx >= total) return;
     const int sb = (int)(idx % nsb), r = (int)(idx / nsb);
-    const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)sb * (FROM_Q3 ? 110 : 210);
-    uint8_t tmp[210];
+    const uint8_t *s = p.src + (size_t)r * p.src_row_bytes + (size_t)sb * (FROM_Q3 ? 110 : (FROM_Q2 ? 84 : 210));
+    uint8_t tmp[210], mins[16];
+    uint16_t dmin = 0;
     if (FROM_Q3) {
         q3_k_as_q6_k(s, tmp);
+        s = tmp;
+    }
+    if (FROM_Q2) {
+        q2_k_as_q6_k(s, tmp, mins, &dmin);
         s = tmp;
     }
     const int dr = map_row(p, r);
     const int tile = dr / TILE_ROWS, rt = dr % TILE_ROWS;
     int rg, h16, g, upper;
     frag_pos(rt, rg, h16, g, upper);
-    uint8_t *base = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)sb * Q6_SB_UNIT + (size_t)rg * Q6_SB_RG;
+    uint8_t *base = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)sb * (4 * RG) + (size_t)rg * RG;
     auto word = [](const uint8_t *q) {
         return (uint32_t)q[0] | ((uint32_t)q[1] << 8) | ((uint32_t)q[2] << 16) | ((uint32_t)q[3] << 24);
     };
@@ -921,6 +955,11 @@ __global__ void repack_q6_k_kernel(RepackParams p) {
     uint8_t *sc = base + 6144 + (g * 4 + row4) * 16;
     for (int j = 0; j < 16; ++j) sc[j] = s[192 + j];
     *reinterpret_cast<uint16_t *>(base + 6656 + (g * 4 + row4) * 2) = (uint16_t)(s[208] | (s[209] << 8));
+    if (FROM_Q2) {
+        uint8_t *mn = base + Q6_SB_RG + (g * 4 + row4) * 16;
+        for (int j = 0; j < 16; ++j) mn[j] = mins[j];
+        *reinterpret_cast<uint16_t *>(base + Q6_SB_RG + 512 + (g * 4 + row4) * 2) = dmin;
+    }
 }
 
 // ------------------------------------------------------ decode attention over the f16 KV cache
@@ -1445,27 +1484,32 @@ static __global__ void __launch_bounds__(256) embed_row_kernel(EmbedParams p) {
         o.z = __fmul_rn(d, (float)(int8_t)((v >> 16) & 0xffu));
         o.w = __fmul_rn(d, (float)(int8_t)(v >> 24));
         *reinterpret_cast<float4 *>(p.x + b * 32 + 4 * w) = o;
-    } else if (p.ty == TY_Q6_K) {
+    } else if (ty_k6(p.ty)) {
         // one thread per (super-block, half, 4-byte word): four values of each of the half's quarters,
-        // x = d * sc * q in that order (dequant.rs:290-293)
+        // x = d * sc * q in that order (dequant.rs:290-293); Q2_K: x = d * sc * q - dmin * mn (dequant.rs:163-168)
         const int sb = idx >> 4, half = (idx >> 3) & 1, w = idx & 7;
         if (sb >= p.nb / 8) return;
-        const uint8_t *base = p.W + (size_t)tile * p.tile_bytes + (size_t)sb * Q6_SB_UNIT + (size_t)rg * Q6_SB_RG;
+        const bool k2 = p.ty == TY_Q2_K;
+        const int k6_rg = k2 ? Q2_SB_RG : Q6_SB_RG;
+        const uint8_t *base = p.W + (size_t)tile * p.tile_bytes + (size_t)sb * (4 * k6_rg) + (size_t)rg * k6_rg;
         const int lane = g * 4 + (w & 3), reg = 2 * (w >> 2) + upper, row4 = h16 * 2 + upper;
         const uint32_t qh = *reinterpret_cast<const uint32_t *>(base + 4096 + (size_t)((half * 2 + h16) * 32) * 16 + lane * 16 + reg * 4);
         const float d = __half2float(*reinterpret_cast<const __half *>(base + 6656 + (g * 4 + row4) * 2));
         const int8_t *sc = reinterpret_cast<const int8_t *>(base + 6144 + (g * 4 + row4) * 16) + half * 8;
         const int is = w >> 2;  // elements 4w..4w+3 of a quarter lie in its 16-element half `is`
+        const float dmin = k2 ? __half2float(*reinterpret_cast<const __half *>(base + Q6_SB_RG + 512 + (g * 4 + row4) * 2)) : 0.0f;
+        const uint8_t *mn = base + Q6_SB_RG + (g * 4 + row4) * 16 + half * 8;
         float *o = p.x + sb * 256 + half * 128 + 4 * w;
 #pragma unroll
         for (int qi = 0; qi < 4; ++qi) {
             const uint32_t ql = *reinterpret_cast<const uint32_t *>(base + (size_t)(((half * 2 + (qi & 1)) * 2 + h16) * 32) * 16 + lane * 16 + reg * 4);
             const float dsc = __fmul_rn(d, (float)sc[2 * qi + is]);
+            const float ml = k2 ? __fmul_rn(dmin, (float)mn[2 * qi + is]) : 0.0f;
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const uint32_t nib = ((qi & 2) ? (ql >> (8 * k + 4)) : (ql >> (8 * k))) & 0xfu;
                 const int q = (int)(nib | (((qh >> (8 * k + 2 * qi)) & 3u) << 4)) - 32;
-                o[32 * qi + k] = __fmul_rn(dsc, (float)q);
+                o[32 * qi + k] = k2 ? __fsub_rn(__fmul_rn(dsc, (float)q), ml) : __fmul_rn(dsc, (float)q);
             }
         }
     } else {
@@ -1547,6 +1591,23 @@ __device__ __forceinline__ float absnormal(uint64_t h, float sigma) {
     const float u1 = ((float)(uint32_t)(h >> 40) + 1.0f) * (1.0f / 16777217.0f);
     const float u2 = (float)(uint32_t)(h & 0xffffffu) * (1.0f / 16777216.0f);
     return fabsf(sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2)) * sigma;
+}
+// Q2_K: uniform bytes for the packed scales / mins and the quants, d and dmin ~ |N(0, 4e-4)|
+static __global__ void synth_q2_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
+    const size_t b = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n_blocks) return;
+    uint8_t *o = dst + b * 84;
+    const uint64_t base = splitmix64(seed) ^ (b * 0x9E3779B97F4A7C15ull);
+    for (int i = 0; i < 10; ++i) {
+        const uint64_t h = splitmix64(base + (uint64_t)i + 1);
+        for (int j = 0; j < 8; ++j) o[i * 8 + j] = (uint8_t)(h >> (8 * j));
+    }
+    const unsigned short db = __half_as_ushort(__float2half_rn(absnormal(splitmix64(base ^ 0x51ull), 4e-4f)));
+    const unsigned short mb = __half_as_ushort(__float2half_rn(absnormal(splitmix64(base ^ 0x52ull), 4e-4f)));
+    o[80] = (uint8_t)(db & 0xff);
+    o[81] = (uint8_t)(db >> 8);
+    o[82] = (uint8_t)(mb & 0xff);
+    o[83] = (uint8_t)(mb >> 8);
 }
 // Q3_K: uniform bytes for the masks, quants and packed scales, d ~ |N(0, 1e-4)|
 static __global__ void synth_q3_k_kernel(uint8_t *dst, size_t n_blocks, uint64_t seed) {
@@ -1984,9 +2045,9 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 if (ty_b32(TY)) {
                     wbytes = (uint32_t)kb * b32_unit(TY);
                     woff = (uint32_t)ks * Q8_KT * b32_unit(TY);
-                } else if (TY == TY_Q6_K) {
-                    wbytes = (uint32_t)Q6_SB_UNIT;
-                    woff = (uint32_t)ks * Q6_SB_UNIT;
+                } else if (ty_k6(TY)) {
+                    wbytes = (uint32_t)(4 * k6_sb_rg(TY));
+                    woff = (uint32_t)ks * (uint32_t)(4 * k6_sb_rg(TY));
                 } else {
                     wbytes = (uint32_t)(kb / 8) * K45_UNIT;
                     woff = (uint32_t)ks * Q4_KT_SB * K45_UNIT;
@@ -2419,16 +2480,28 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                             if (DUMP) dumpc(d, ks * Q8_KT + cb);
                         }
                     }
-                } else if (TY == TY_Q6_K) {
+                } else if (ty_k6(TY)) {
                     // One super-block per K-step.  Sub-block scales cover 16 elements, so a block's
                     // dot is two 16-deep mmas (one per half of the block, each in its own chain) and
                     // sc0*dot0 + sc1*dot1 is formed in integers: exactly what the reference forms in
                     // f32 (q8_acts.rs:338-342; |value| < 2^24).
-                    const uint8_t *base = sw + rgc * Q6_SB_RG;
+                    // Q2_K adds its min term: - dmin * dx * (mn0 * sum0 + mn1 * sum1) over the sums of the
+                    // activation codes of the two halves (q8_acts.rs:160-168), which the -32 correction has already.
+                    constexpr bool K2 = TY == TY_Q2_K;
+                    const uint8_t *base = sw + rgc * k6_sb_rg(TY);
                     const uint4 scl = *reinterpret_cast<const uint4 *>(base + 6144 + (lg * 4 + 2 * h16c) * 16);      // row lg
                     const uint4 sch = *reinterpret_cast<const uint4 *>(base + 6144 + (lg * 4 + 2 * h16c + 1) * 16);  // row lg+8
                     const __half2 dd = *reinterpret_cast<const __half2 *>(base + 6656 + (lg * 4 + 2 * h16c) * 2);
                     const float dwl = __low2float(dd), dwh = __high2float(dd);
+                    uint4 mnl = make_uint4(0u, 0u, 0u, 0u), mnh = mnl;
+                    float dml = 0.0f, dmh = 0.0f;
+                    if (K2) {
+                        mnl = *reinterpret_cast<const uint4 *>(base + Q6_SB_RG + (lg * 4 + 2 * h16c) * 16);
+                        mnh = *reinterpret_cast<const uint4 *>(base + Q6_SB_RG + (lg * 4 + 2 * h16c + 1) * 16);
+                        const __half2 dm = *reinterpret_cast<const __half2 *>(base + Q6_SB_RG + 512 + (lg * 4 + 2 * h16c) * 2);
+                        dml = __low2float(dm);
+                        dmh = __high2float(dm);
+                    }
 #pragma unroll
                     for (int ch = 0; ch < 8 / BPC; ++ch) {
                         const int xs = ch * BPC + my_blk;
@@ -2457,6 +2530,15 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                             I[i] = (i >> 1) ? s8_of(sch, 2 * b) * (d[i] - sd[i]) + s8_of(sch, 2 * b + 1) * (e[i] - se[i])
                                             : s8_of(scl, 2 * b) * (d[i] - sd[i]) + s8_of(scl, 2 * b + 1) * (e[i] - se[i]);
                         }
+                        int J[4] = {0, 0, 0, 0};  // Q2_K: mn0 * sum0 + mn1 * sum1 (sd, se are 32 x the sums)
+                        if (K2) {
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const int b = ch * BPC + (2 * lt + (i & 1)) / MP2;
+                                J[i] = (i >> 1) ? s8_of(mnh, 2 * b) * (sd[i] >> 5) + s8_of(mnh, 2 * b + 1) * (se[i] >> 5)
+                                                : s8_of(mnl, 2 * b) * (sd[i] >> 5) + s8_of(mnl, 2 * b + 1) * (se[i] >> 5);
+                            }
+                        }
                         if (MP2 > 1 && p.two_level) {
                             // columns 2lt, 2lt+1 are the two digits of one token of one block, d2 = d1 / 256
                             const int c = 2 * lt;
@@ -2464,6 +2546,10 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                             const float dx = ad[b * MP + tok];
                             cacc[0] = fmaf(__fmul_rn(dwl, dx), (float)(((long long)I[0] << 8) + I[1]), cacc[0]);
                             cacc[2] = fmaf(__fmul_rn(dwh, dx), (float)(((long long)I[2] << 8) + I[3]), cacc[2]);
+                            if (K2) {
+                                cacc[0] = fmaf(-__fmul_rn(dml, dx), (float)((J[0] << 8) + J[1]), cacc[0]);
+                                cacc[2] = fmaf(-__fmul_rn(dmh, dx), (float)((J[2] << 8) + J[3]), cacc[2]);
+                            }
                         } else {
 #pragma unroll
                             for (int i = 0; i < 4; ++i) {
@@ -2472,6 +2558,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                                 const int tok = (c % MP2) < M ? (c % MP2) : M - 1;
                                 // total += d * acts.d[blk] * (sc0*dot0 + sc1*dot1)  (q8_acts.rs:342)
                                 cacc[i] = fmaf(__fmul_rn((i >> 1) ? dwh : dwl, ad[b * MP + tok]), (float)I[i], cacc[i]);
+                                if (K2) cacc[i] = fmaf(-__fmul_rn((i >> 1) ? dmh : dml, ad[b * MP + tok]), (float)J[i], cacc[i]);
                             }
                         }
                         if (DUMP) dumpc(I, ks * 8 + ch * BPC);
@@ -2603,13 +2690,21 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 } else {
                     for (int b = kq; b < kb; b += K_SPLIT) block(b);
                 }
-            } else if (TY == TY_Q6_K) {
+            } else if (ty_k6(TY)) {
                 // this warp: quarter kq of both halves of the super-block (blocks kq and kq + 4)
-                const uint8_t *base = sw + rg * Q6_SB_RG;
+                constexpr bool K2 = TY == TY_Q2_K;
+                const uint8_t *base = sw + rg * k6_sb_rg(TY);
                 const uint2 ddw = *reinterpret_cast<const uint2 *>(base + 6656 + lg * 8);  // d of rows lg, lg+8, lg+16, lg+24
                 const float2 f01 = __half22float2(*reinterpret_cast<const __half2 *>(&ddw.x));
                 const float2 f23 = __half22float2(*reinterpret_cast<const __half2 *>(&ddw.y));
                 const float dwr[4] = {f01.x, f01.y, f23.x, f23.y};
+                float dmr[4] = {0.0f, 0.0f, 0.0f, 0.0f};  // Q2_K: dmin of the same rows
+                if (K2) {
+                    const uint2 dmw = *reinterpret_cast<const uint2 *>(base + Q6_SB_RG + 512 + lg * 8);
+                    const float2 g01 = __half22float2(*reinterpret_cast<const __half2 *>(&dmw.x));
+                    const float2 g23 = __half22float2(*reinterpret_cast<const __half2 *>(&dmw.y));
+                    dmr[0] = g01.x; dmr[1] = g01.y; dmr[2] = g23.x; dmr[3] = g23.y;
+                }
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     const int b = half * 4 + kq;
@@ -2621,11 +2716,17 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                         a[h] = q6_k_unpack(ql, qh, kq);
                     }
                     int s0[4], s1[4];  // the block's two sub-block scales for rows lg, lg+8, lg+16, lg+24
+                    int m0[4] = {0, 0, 0, 0}, m1[4] = {0, 0, 0, 0};  // Q2_K: and its two sub-block mins
 #pragma unroll
                     for (int r4 = 0; r4 < 4; ++r4) {
                         const uint32_t w = *reinterpret_cast<const unsigned short *>(base + 6144 + (lg * 4 + r4) * 16 + 2 * b);
                         s0[r4] = (int)(w << 24) >> 24;
                         s1[r4] = (int)(w << 16) >> 24;
+                        if (K2) {
+                            const uint32_t wm = *reinterpret_cast<const unsigned short *>(base + Q6_SB_RG + (lg * 4 + r4) * 16 + 2 * b);
+                            m0[r4] = (int)(wm & 0xffu);
+                            m1[r4] = (int)(wm >> 8);
+                        }
                     }
                     const uint8_t *xb = sa + b * (32 * M);
                     const float *xd = ad + b * MP;
@@ -2636,7 +2737,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                         const int t0 = min(8 * j + 2 * lt, M - 1), t1 = min(8 * j + 2 * lt + 1, M - 1);
                         const uint32_t b0 = *reinterpret_cast<const uint32_t *>(xb + tb * 16 + 4 * lt);
                         const uint32_t b1 = *reinterpret_cast<const uint32_t *>(xb + 16 * M + tb * 16 + 4 * lt);
-                        int I[2][4];
+                        int I[2][4], J[2][4];
                         int sd[4] = {0, 0, 0, 0}, se[4] = {0, 0, 0, 0};  // 32 * the sums of the activation codes, per column
                         mma_half_s8_acc(sd, 0x20202020u, 0x20202020u, b0);
                         mma_half_s8_acc(se, 0x20202020u, 0x20202020u, b1);
@@ -2646,8 +2747,10 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                             mma_half_s8_acc(d, a[h].x, a[h].y, b0);
                             mma_half_s8_acc(e, a[h].z, a[h].w, b1);
 #pragma unroll
-                            for (int i = 0; i < 4; ++i)
+                            for (int i = 0; i < 4; ++i) {
                                 I[h][i] = s0[2 * h + (i >> 1)] * (d[i] - sd[i]) + s1[2 * h + (i >> 1)] * (e[i] - se[i]);
+                                J[h][i] = K2 ? m0[2 * h + (i >> 1)] * (sd[i] >> 5) + m1[2 * h + (i >> 1)] * (se[i] >> 5) : 0;
+                            }
                         }
                         const float dx0 = xd[t0], dx1 = xd[t1];
 #pragma unroll
@@ -2655,14 +2758,19 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                             if (M > 8 || (M > 1 && p.two_level)) {
                                 // columns 2lt, 2lt+1 are the two digits of one token, d2 = d1 / 256
 #pragma unroll
-                                for (int i = 0; i < 4; i += 2)
+                                for (int i = 0; i < 4; i += 2) {
                                     acc[h][j][i] = fmaf(__fmul_rn(dwr[2 * h + (i >> 1)], dx1), (float)(((long long)I[h][i] << 8) + I[h][i + 1]),
                                                         acc[h][j][i]);
+                                    if (K2)
+                                        acc[h][j][i] = fmaf(-__fmul_rn(dmr[2 * h + (i >> 1)], dx1), (float)((J[h][i] << 8) + J[h][i + 1]), acc[h][j][i]);
+                                }
                             } else if constexpr (M <= 8) {
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
                                     if (M == 1 && (i & 1)) continue;  // a single activation row has no odd column
                                     acc[h][j][i] = fmaf(__fmul_rn(dwr[2 * h + (i >> 1)], (i & 1) ? dx1 : dx0), (float)I[h][i], acc[h][j][i]);
+                                    if (K2)
+                                        acc[h][j][i] = fmaf(-__fmul_rn(dmr[2 * h + (i >> 1)], (i & 1) ? dx1 : dx0), (float)J[h][i], acc[h][j][i]);
                                 }
                             }
                         }

@@ -26,8 +26,9 @@ MvKernel pick_m(int m) {
     }
 }
 
-// defined in mv_q8_0.cu, mv_q5_0.cu, mv_q4_k.cu, mv_q5_k.cu, mv_q6_k.cu
+// defined in mv_q8_0.cu, mv_q5_0.cu, mv_q2_k.cu, mv_q4_k.cu, mv_q5_k.cu, mv_q6_k.cu
 MvKernel mv_pick_q5_0(int m_eff, bool dump);
+MvKernel mv_pick_q2_k(int m_eff, bool dump);
 MvKernel mv_pick_q8_0(int m_eff, bool dump);
 MvKernel mv_pick_q4_k(int m_eff, bool dump);
 MvKernel mv_pick_q5_k(int m_eff, bool dump);

@@ -26,6 +26,7 @@ LIB_PATH = os.path.join(_HERE, "libapk_b200.so")
 Q8_0 = 8
 Q4_K = 12
 Q5_0 = 6
+Q2_K = 10
 Q3_K = 11
 Q5_K = 13
 Q6_K = 14

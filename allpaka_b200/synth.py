@@ -12,13 +12,14 @@ from __future__ import annotations
 import numpy as np
 
 TY_Q5_0 = 6
+TY_Q2_K = 10
 TY_Q3_K = 11
 TY_Q8_0 = 8
 TY_Q4_K = 12
 TY_Q5_K = 13
 TY_Q6_K = 14
 
-BLOCK = {TY_Q8_0: (32, 34), TY_Q5_0: (32, 22), TY_Q3_K: (256, 110), TY_Q4_K: (256, 144), TY_Q5_K: (256, 176), TY_Q6_K: (256, 210)}
+BLOCK = {TY_Q8_0: (32, 34), TY_Q5_0: (32, 22), TY_Q2_K: (256, 84), TY_Q3_K: (256, 110), TY_Q4_K: (256, 144), TY_Q5_K: (256, 176), TY_Q6_K: (256, 210)}
 
 
 def expected_bytes(ty: int, elements: int) -> int:
@@ -125,7 +126,21 @@ def q3_k_matrix(n_out: int, n_in: int, seed: int, d_sigma: float = 1e-4) -> np.n
     return out.reshape(-1)
 
 
+def q2_k_matrix(n_out: int, n_in: int, seed: int, d_sigma: float = 4e-4) -> np.ndarray:
+    """Q2_K = ``{u8 scales[16]; u8 qs[64]; f16 d; f16 dmin}`` (84 B, dequant.rs:143-174): uniform packed
+    4-bit scales / mins and 2-bit quants, d and dmin ~ |N(0, d_sigma)|."""
+    rng = np.random.default_rng(seed)
+    nsb = n_in // 256
+    out = np.empty((n_out, nsb, 84), dtype=np.uint8)
+    out[:, :, 0:80] = rng.integers(0, 256, size=(n_out, nsb, 80), dtype=np.uint8)
+    dd = np.abs(rng.normal(0.0, d_sigma, size=(n_out, nsb, 2))).astype(np.float16)
+    out[:, :, 80:84] = dd.view(np.uint8).reshape(n_out, nsb, 4)
+    return out.reshape(-1)
+
+
 def matrix(ty: int, n_out: int, n_in: int, seed: int) -> np.ndarray:
+    if ty == TY_Q2_K:
+        return q2_k_matrix(n_out, n_in, seed)
     if ty == TY_Q3_K:
         return q3_k_matrix(n_out, n_in, seed)
     if ty == TY_Q8_0:
@@ -185,7 +200,7 @@ def tame_scales(buf: np.ndarray, ty: int, value: int = 0x211F) -> np.ndarray:
     be, bb = BLOCK[ty]
     v = buf.reshape(-1, bb)
     lo, hi = value & 0xFF, value >> 8
-    offs = {TY_Q8_0: (0,), TY_Q5_0: (0,), TY_Q3_K: (108,), TY_Q4_K: (0, 2), TY_Q5_K: (0, 2), TY_Q6_K: (208,)}[ty]
+    offs = {TY_Q8_0: (0,), TY_Q5_0: (0,), TY_Q2_K: (80, 82), TY_Q3_K: (108,), TY_Q4_K: (0, 2), TY_Q5_K: (0, 2), TY_Q6_K: (208,)}[ty]
     for o in offs:
         v[:, o] = lo
         v[:, o + 1] = hi

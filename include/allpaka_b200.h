@@ -52,6 +52,7 @@ extern "C" {
 /* GGML type ids (crates/allpaka-dtype/src/lib.rs:61-75). */
 #define APK_TY_Q5_0 6u
 #define APK_TY_Q8_0 8u
+#define APK_TY_Q2_K 10u
 #define APK_TY_Q3_K 11u
 #define APK_TY_Q4_K 12u
 #define APK_TY_Q5_K 13u

@@ -93,6 +93,7 @@ static int block_geom(uint32_t ty, size_t *be, size_t *bb) {
     if (ty == ORC_TY_Q8_0) { *be = 32; *bb = 34; return 0; }
     if (ty == ORC_TY_Q5_0) { *be = 32; *bb = 22; return 0; }
     if (ty == ORC_TY_Q3_K) { *be = 256; *bb = 110; return 0; }
+    if (ty == ORC_TY_Q2_K) { *be = 256; *bb = 84; return 0; }
     if (ty == ORC_TY_Q4_K) { *be = 256; *bb = 144; return 0; }
     if (ty == ORC_TY_Q5_K) { *be = 256; *bb = 176; return 0; }
     if (ty == ORC_TY_Q6_K) { *be = 256; *bb = 210; return 0; }
@@ -133,6 +134,28 @@ static void dequant_q5_0_block(const uint8_t *b, float *out) {
     int8_t q[32];
     q5_0_values(b, q);
     for (int i = 0; i < 32; i++) out[i] = d * (float)q[i];
+}
+
+/* The 32 two-bit values of block blk (0..7) of a Q2_K super-block {u8 scales[16]; u8 qs[64]; f16 d; f16 dmin}:
+ * qs[32 * (blk / 4) + l] at shift 2 * (blk % 4) (q8_acts.rs:148-152, dequant.rs:158-166). */
+static void q2_k_values(const uint8_t *block, int blk, int8_t out[32]) {
+    const uint8_t *q = block + 16 + (blk / 4) * 32;
+    int shift = 2 * (blk % 4);
+    for (int l = 0; l < 32; l++) out[l] = (int8_t)((q[l] >> shift) & 3);
+}
+
+/* crates/allpaka-gguf/src/dequant.rs:150-174: x = d * (sc & 15) * q - dmin * (sc >> 4) per 16-element sub-block */
+static void dequant_q2_k_block(const uint8_t *b, float *out) {
+    float d = orc_f16_to_f32(le16(b + 80)), dmin = orc_f16_to_f32(le16(b + 82));
+    for (int blk = 0; blk < 8; blk++) {
+        int8_t q[32];
+        q2_k_values(b, blk, q);
+        for (int group = 0; group < 2; group++) {
+            uint8_t sc = b[2 * blk + group];
+            float dl = d * (float)(sc & 0xf), ml = dmin * (float)(sc >> 4);
+            for (int l = 0; l < 16; l++) out[blk * 32 + group * 16 + l] = dl * (float)q[group * 16 + l] - ml;
+        }
+    }
 }
 
 /* Q3_K block {u8 hmask[32]; u8 qs[64]; u8 scales[12]; f16 d}: the 16 six-bit sub-block scales, still
@@ -246,6 +269,7 @@ int orc_dequant(uint32_t ty, const uint8_t *bytes, size_t n_bytes, float *out, s
         if (ty == ORC_TY_Q8_0) dequant_q8_0_block(bytes + i * bb, out + i * be);
         else if (ty == ORC_TY_Q5_0) dequant_q5_0_block(bytes + i * bb, out + i * be);
         else if (ty == ORC_TY_Q3_K) dequant_q3_k_block(bytes + i * bb, out + i * be);
+        else if (ty == ORC_TY_Q2_K) dequant_q2_k_block(bytes + i * bb, out + i * be);
         else if (ty == ORC_TY_Q4_K) dequant_q4_k_block(bytes + i * bb, out + i * be);
         else if (ty == ORC_TY_Q5_K) dequant_q5_k_block(bytes + i * bb, out + i * be);
         else dequant_q6_k_block(bytes + i * bb, out + i * be);
@@ -364,6 +388,62 @@ float orc_dot_q5_0(const uint8_t *row, size_t n_in, const float *x) {
         float s = 0.0f;
         for (int j = 0; j < 16; j++) s += (float)q[j] * xs[j] + (float)q[j + 16] * xs[j + 16];
         total += d * s;
+    }
+    return total;
+}
+
+/* crates/allpaka-backend/src/quantmat/q8_acts.rs:127-174 (the not(aarch64) arm): per 16-element sub-block
+ * total += dl * dotq - ml * sum_x, dotq and sum_x over the activation codes, each times d_x of the block */
+float orc_dot_q2_k_i8(const uint8_t *row, size_t n_in, const float *dx_all, const int8_t *q8) {
+    float total = 0.0f;
+    for (size_t bi = 0; bi < n_in / 256; bi++) {
+        const uint8_t *block = row + bi * 84;
+        float d = orc_f16_to_f32(le16(block + 80)), dmin = orc_f16_to_f32(le16(block + 82));
+        for (int b = 0; b < 8; b++) {
+            size_t blk = bi * 8 + (size_t)b;
+            const int8_t *xq = q8 + blk * 32;
+            float dx = dx_all[blk];
+            int8_t qw[32];
+            q2_k_values(block, b, qw);
+            for (int group = 0; group < 2; group++) {
+                uint8_t sc = block[2 * b + group];
+                float dl = d * (float)(sc & 0xf);
+                float ml = dmin * (float)(sc >> 4);
+                float dotq = (float)orc_dot_i8(qw + group * 16, xq + group * 16, 16) * dx;
+                int32_t s = 0;
+                for (int l = 0; l < 16; l++) s += xq[group * 16 + l];
+                float sum_x = (float)s * dx;
+                total += dl * dotq - ml * sum_x;
+            }
+        }
+    }
+    return total;
+}
+
+/* crates/allpaka-backend/src/quantmat/dot_f32.rs:214-248 */
+float orc_dot_q2_k(const uint8_t *row, size_t n_in, const float *x) {
+    float total = 0.0f;
+    for (size_t bi = 0; bi < n_in / 256; bi++) {
+        const uint8_t *block = row + bi * 84;
+        float d = orc_f16_to_f32(le16(block + 80)), dmin = orc_f16_to_f32(le16(block + 82));
+        const float *xb = x + bi * 256;
+        float acc_d = 0.0f, acc_m = 0.0f;
+        for (int b = 0; b < 8; b++) {
+            int8_t q[32];
+            q2_k_values(block, b, q);
+            for (int group = 0; group < 2; group++) {
+                uint8_t sc = block[2 * b + group];
+                const float *xs = xb + b * 32 + group * 16;
+                float dotq = 0.0f, sum = 0.0f;
+                for (int l = 0; l < 16; l++) {
+                    dotq += (float)q[group * 16 + l] * xs[l];
+                    sum += xs[l];
+                }
+                acc_d += (float)(sc & 0xf) * dotq;
+                acc_m += (float)(sc >> 4) * sum;
+            }
+        }
+        total += d * acc_d - dmin * acc_m;
     }
     return total;
 }
@@ -610,6 +690,19 @@ int orc_block_dots(uint32_t ty, const uint8_t *w, size_t n_out, size_t n_in, con
             if (ty == ORC_TY_Q8_0) {
                 for (size_t b = 0; b < nb; b++)
                     o[b] = dot_i8_32((const int8_t *)(row + b * 34 + 2), qi + b * 32);
+            } else if (ty == ORC_TY_Q2_K) {
+                /* per 32-element block the integer that d * d_x multiplies: sc0*dot0 + sc1*dot1 with the
+                 * 4-bit scales (q8_acts.rs:156-168; the min term is not a dot with the weights) */
+                for (size_t sb = 0; sb < n_in / 256; sb++) {
+                    const uint8_t *block = row + sb * 84;
+                    for (int b = 0; b < 8; b++) {
+                        int8_t qw[32];
+                        q2_k_values(block, b, qw);
+                        size_t blk = sb * 8 + (size_t)b;
+                        o[blk] = (int32_t)(block[2 * b] & 0xf) * orc_dot_i8(qw, qi + blk * 32, 16) +
+                                 (int32_t)(block[2 * b + 1] & 0xf) * orc_dot_i8(qw + 16, qi + blk * 32 + 16, 16);
+                    }
+                }
             } else if (ty == ORC_TY_Q3_K) {
                 /* per 32-element block the integer the f32 scales multiply: sc0*dot0 + sc1*dot1
                  * (q8_acts.rs:206-210; exact in f32 there) */
@@ -828,6 +921,8 @@ static inline float row_dot_any(const mm_ctx *c, size_t i, size_t j) {
             return orc_dot_q5_0_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
         if (c->ty == ORC_TY_Q3_K)
             return orc_dot_q3_k_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
+        if (c->ty == ORC_TY_Q2_K)
+            return orc_dot_q2_k_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
         if (c->ty == ORC_TY_Q6_K)
             return orc_dot_q6_k_i8(row, c->n_in, c->d + i * nb, c->q + i * c->n_in);
         if (c->ty == ORC_TY_Q5_K)
@@ -837,6 +932,7 @@ static inline float row_dot_any(const mm_ctx *c, size_t i, size_t j) {
     const float *xi = c->x + i * c->n_in;
     if (c->ty == ORC_TY_Q5_0) return orc_dot_q5_0(row, c->n_in, xi);
     if (c->ty == ORC_TY_Q3_K) return orc_dot_q3_k(row, c->n_in, xi);
+    if (c->ty == ORC_TY_Q2_K) return orc_dot_q2_k(row, c->n_in, xi);
     if (c->ty == ORC_TY_Q6_K) return orc_dot_q6_k(row, c->n_in, xi);
     if (c->ty == ORC_TY_Q5_K) return orc_dot_q5_k(row, c->n_in, xi);
     return c->ty == ORC_TY_Q8_0 ? orc_dot_q8_0(row, c->n_in, xi) : orc_dot_q4_k(row, c->n_in, xi);

@@ -32,6 +32,7 @@ extern "C" {
 #define ORC_TY_Q6_K 14u
 #define ORC_TY_Q5_0 6u
 #define ORC_TY_Q3_K 11u
+#define ORC_TY_Q2_K 10u
 
 /* crates/allpaka-dtype/src/lib.rs:129-201 */
 float orc_f16_to_f32(uint16_t h);
@@ -68,6 +69,9 @@ float orc_dot_q5_k(const uint8_t *row, size_t n_in, const float *x);
 /* q8_acts.rs:100-124 and dot_f32.rs:39-55: one Q5_0 row. */
 float orc_dot_q5_0_i8(const uint8_t *row, size_t n_in, const float *d, const int8_t *q);
 float orc_dot_q5_0(const uint8_t *row, size_t n_in, const float *x);
+/* q8_acts.rs:127-174 and dot_f32.rs:214-248: one Q2_K row. */
+float orc_dot_q2_k_i8(const uint8_t *row, size_t n_in, const float *d, const int8_t *q);
+float orc_dot_q2_k(const uint8_t *row, size_t n_in, const float *x);
 /* q8_acts.rs:178-218 and dot_f32.rs:58-94: one Q3_K row. */
 float orc_dot_q3_k_i8(const uint8_t *row, size_t n_in, const float *d, const int8_t *q);
 float orc_dot_q3_k(const uint8_t *row, size_t n_in, const float *x);

@@ -18,6 +18,7 @@ _LIB_PATH = os.path.join(_HERE, "libapk_oracle.so")
 
 TY_Q8_0 = 8
 TY_Q5_0 = 6
+TY_Q2_K = 10
 TY_Q3_K = 11
 TY_Q4_K = 12
 TY_Q5_K = 13
@@ -94,7 +95,9 @@ def _declare(l):
     l.orc_dot_q5_0_i8.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
     l.orc_dot_q3_k_i8.restype = C.c_float
     l.orc_dot_q3_k_i8.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
-    for name in ("orc_dot_q8_0", "orc_dot_q5_0", "orc_dot_q3_k", "orc_dot_q4_k", "orc_dot_q5_k", "orc_dot_q6_k"):
+    l.orc_dot_q2_k_i8.restype = C.c_float
+    l.orc_dot_q2_k_i8.argtypes = [C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]
+    for name in ("orc_dot_q8_0", "orc_dot_q5_0", "orc_dot_q3_k", "orc_dot_q2_k", "orc_dot_q4_k", "orc_dot_q5_k", "orc_dot_q6_k"):
         getattr(l, name).restype = C.c_float
         getattr(l, name).argtypes = [C.c_void_p, C.c_size_t, C.c_void_p]
     l.orc_block_dots.restype = C.c_int
@@ -240,10 +243,12 @@ def dot_row(ty: int, row, x, q8: bool) -> float:
             return l.orc_dot_q5_0_i8(_p(row), n_in, _p(d), _p(q))
         if ty == TY_Q3_K:
             return l.orc_dot_q3_k_i8(_p(row), n_in, _p(d), _p(q))
+        if ty == TY_Q2_K:
+            return l.orc_dot_q2_k_i8(_p(row), n_in, _p(d), _p(q))
         if ty == TY_Q5_K:
             return l.orc_dot_q5_k_i8(_p(row), n_in, _p(d), _p(s), _p(q))
         return l.orc_dot_q4_k_i8(_p(row), n_in, _p(d), _p(s), _p(q))
-    fn = {TY_Q8_0: l.orc_dot_q8_0, TY_Q5_0: l.orc_dot_q5_0, TY_Q3_K: l.orc_dot_q3_k, TY_Q4_K: l.orc_dot_q4_k, TY_Q5_K: l.orc_dot_q5_k, TY_Q6_K: l.orc_dot_q6_k}[ty]
+    fn = {TY_Q8_0: l.orc_dot_q8_0, TY_Q5_0: l.orc_dot_q5_0, TY_Q3_K: l.orc_dot_q3_k, TY_Q2_K: l.orc_dot_q2_k, TY_Q4_K: l.orc_dot_q4_k, TY_Q5_K: l.orc_dot_q5_k, TY_Q6_K: l.orc_dot_q6_k}[ty]
     return fn(_p(row), n_in, _p(x))
 
 

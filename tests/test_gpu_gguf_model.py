@@ -6,7 +6,7 @@ import pytest
 
 from allpaka_b200 import gguf
 from tests.test_gguf_reader import tiny_model
-from tests.util import Q3_K, Q4_K, Q5_0, Q5_K, Q6_K, Q8_0, oracle_logits, rel_l2, rope_table
+from tests.util import Q2_K, Q3_K, Q4_K, Q5_0, Q5_K, Q6_K, Q8_0, oracle_logits, rel_l2, rope_table
 
 pytestmark = pytest.mark.gpu
 
@@ -69,7 +69,7 @@ K_M = {"attn_v.weight": Q6_K, "ffn_down.weight": Q6_K, "token_embd.weight": Q6_K
 
 
 @pytest.mark.parametrize("arch,ty,tied,ty_of", [("qwen3", Q8_0, False, None), ("qwen3", Q4_K, True, None), ("qwen3", Q6_K, True, None),
-                                                 ("llama", Q8_0, False, None), ("qwen3", Q4_K, True, K_M), ("llama", Q4_K, False, K_M), ("qwen3", Q5_K, True, K_M), ("qwen3", Q5_0, True, None), ("qwen3", Q3_K, True, None)])
+                                                 ("llama", Q8_0, False, None), ("qwen3", Q4_K, True, K_M), ("llama", Q4_K, False, K_M), ("qwen3", Q5_K, True, K_M), ("qwen3", Q5_0, True, None), ("qwen3", Q3_K, True, None), ("qwen3", Q2_K, True, None)])
 def test_tokens_from_a_model_file(orc, tmp_path, arch, ty, tied, ty_of):
     from allpaka_b200 import gpu as G
 

@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 from allpaka_b200 import synth
-from tests.util import (Q3_K, Q4_K, Q5_0, Q5_K, Q6_K, Q8_0, Region, make_layer, oracle_decode, oracle_logits, rel_l2,
+from tests.util import (Q2_K, Q3_K, Q4_K, Q5_0, Q5_K, Q6_K, Q8_0, Region, make_layer, oracle_decode, oracle_logits, rel_l2,
                         rope_table)
 
 pytestmark = pytest.mark.gpu
@@ -81,6 +81,10 @@ def test_rmsnorm_prologue_feeds_identical_blocks(gpu, orc):
     (Q3_K, 256, 1024, 1),     # carried in the Q6_K stream: sc0*dot0 + sc1*dot1 with the 3-bit values
     (Q3_K, 200, 5120, 2),
     (Q3_K, 64, 256, 8),
+    (Q2_K, 256, 1024, 1),     # the scale-weighted part sc0*dot0 + sc1*dot1; the min term rides on the code sums
+    (Q2_K, 200, 5120, 2),
+    (Q2_K, 130, 768, 4),
+    (Q2_K, 64, 256, 8),
 ])
 def test_int32_block_dots_are_bit_exact(gpu, orc, ty, n_out, n_in, m):
     w = synth.matrix(ty, n_out, n_in, 7)
@@ -111,6 +115,25 @@ def test_q5_k_matvec_matches_oracle(gpu, orc, n_out, n_in, m):
         if mode == 0:
             assert errs[-1] <= 1e-5
     print(f"Q5_K {n_out}x{n_in} m={m}: rel-L2 q8 {errs[0]:.1e} f32 {errs[1]:.1e}")
+    gpu.detach(r.buf)
+
+
+@pytest.mark.parametrize("n_out,n_in", [(1, 256), (48, 1024), (130, 768), (513, 5120), (64, 25600), (5120, 5120)])
+@pytest.mark.parametrize("m", [1, 3, 4, 6, 8])
+def test_q2_k_matvec_matches_oracle(gpu, orc, n_out, n_in, m):
+    """dot_q2_k_i8 (q8_acts.rs:127-174) for Q8 activations, dot_q2_k (dot_f32.rs:214-248) for f32 ones."""
+    w = synth.q2_k_matrix(n_out, n_in, 71)
+    r = attach(gpu, w)
+    x = synth.normal_f32((m, n_in), 72 + m)
+    errs = []
+    for mode, omode in ((0, orc.ACT_Q8), (1, orc.ACT_F32), (2, orc.ACT_AUTO)):
+        got = gpu.matvec(Q2_K, r.views[0], n_in, n_out, x, m, mode)
+        want = orc.matmul(Q2_K, w, n_out, n_in, x, m, omode)
+        errs.append(rel_l2(got, want))
+        assert errs[-1] <= TOL, (mode, errs)
+        if mode == 0:
+            assert errs[-1] <= 1e-5  # integer dots and sums are exact; only the f32 accumulation order differs
+    print(f"Q2_K {n_out}x{n_in} m={m}: rel-L2 q8 {errs[0]:.1e} f32 {errs[1]:.1e}")
     gpu.detach(r.buf)
 
 
@@ -359,7 +382,7 @@ def build_token(gpu, orc, ty, n_layers, hidden, nh, nkv, ffn, vocab, m, qk_norm,
 
 
 @pytest.mark.parametrize("ty,m,qk_norm", [(Q8_0, 1, False), (Q8_0, 1, True), (Q8_0, 4, True), (Q4_K, 1, False),
-                                           (Q4_K, 3, True), (Q5_0, 1, True), (Q5_0, 3, False), (Q3_K, 1, True)])
+                                           (Q4_K, 3, True), (Q5_0, 1, True), (Q5_0, 3, False), (Q3_K, 1, True), (Q2_K, 1, True), (Q2_K, 3, False)])
 def test_decode_token_matches_oracle_layer_stack(gpu, orc, ty, m, qk_norm):
     hidden, nh, nkv, ffn, vocab = 512, 4, 2, 1024, 1000
     req, layers, head, out_norm, x, rope, r = build_token(gpu, orc, ty, 3, hidden, nh, nkv, ffn, vocab, m, qk_norm, 500)

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from allpaka_b200 import synth
-from tests.util import Q3_K, Q4_K, Q5_0, Q5_K, Q6_K, Q8_0, Region, make_layer, oracle_decode, oracle_logits, rel_l2, rope_table
+from tests.util import Q2_K, Q3_K, Q4_K, Q5_0, Q5_K, Q6_K, Q8_0, Region, make_layer, oracle_decode, oracle_logits, rel_l2, rope_table
 
 pytestmark = pytest.mark.gpu
 
@@ -42,7 +42,7 @@ def embed_row(orc, ty, embd, hidden, tok):
     return orc.dequant(ty, embd[tok * rb:(tok + 1) * rb], hidden)
 
 
-@pytest.mark.parametrize("ty,tied", [(Q8_0, True), (Q8_0, False), (Q4_K, True), (Q5_K, True), (Q6_K, True), (Q5_0, True), (Q3_K, True)])
+@pytest.mark.parametrize("ty,tied", [(Q8_0, True), (Q8_0, False), (Q4_K, True), (Q5_K, True), (Q6_K, True), (Q5_0, True), (Q3_K, True), (Q2_K, True)])
 def test_input_row_by_token_id(orc, ty, tied):
     from allpaka_b200 import gpu as G
 

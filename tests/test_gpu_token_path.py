@@ -13,7 +13,7 @@ import numpy as np
 import pytest
 
 from allpaka_b200 import synth
-from tests.util import (Q3_K, Q4_K, Q5_0, Q5_K, Q6_K, Q8_0, Region, make_layer, oracle_decode, oracle_logits, rel_l2,
+from tests.util import (Q2_K, Q3_K, Q4_K, Q5_0, Q5_K, Q6_K, Q8_0, Region, make_layer, oracle_decode, oracle_logits, rel_l2,
                         rope_table)
 
 pytestmark = pytest.mark.gpu
@@ -155,7 +155,7 @@ def test_verify_batch_records_are_bit_exact(orc):
     g.close()
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q3_K, Q4_K, Q5_K, Q6_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K])
 def test_block_dots_inside_the_token_are_bit_exact(orc, ty):
     """The int32 block dots of the second layer's Q|K|V launch (its input has been through a whole
     layer of the fused path) against dot_i8 on the oracle's quantisation of the same row."""
@@ -244,7 +244,7 @@ def test_every_operator_on_the_gpus_own_rows_over_many_seeds(orc, ty, m):
                 if explained:
                     break
             assert explained, (seed, err)
-    print(f"{ {Q8_0: 'Q8_0', Q5_0: 'Q5_0', Q3_K: 'Q3_K', Q4_K: 'Q4_K', Q5_K: 'Q5_K', Q6_K: 'Q6_K'}[ty]} m={m}: per-operator worst {worst_op:.2e}; chained over 16 seeds "
+    print(f"{ {Q8_0: 'Q8_0', Q5_0: 'Q5_0', Q2_K: 'Q2_K', Q3_K: 'Q3_K', Q4_K: 'Q4_K', Q5_K: 'Q5_K', Q6_K: 'Q6_K'}[ty]} m={m}: per-operator worst {worst_op:.2e}; chained over 16 seeds "
           f"median {np.median(chained):.2e} max {np.max(chained):.2e}, {sum(e > 2e-3 for e in chained)} above 2e-3")
     # (an operator here is a whole half-layer: inside the FFN the SwiGLU row is quantised again, and a
     # value that differs in its last bit may round to the neighbouring code: a few 1e-5 at most)

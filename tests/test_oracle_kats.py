@@ -11,7 +11,7 @@ import pytest
 
 from allpaka_b200 import synth
 
-Q8_0, Q4_K, Q5_K, Q6_K, Q5_0, Q3_K = 8, 12, 13, 14, 6, 11
+Q8_0, Q4_K, Q5_K, Q6_K, Q5_0, Q3_K, Q2_K = 8, 12, 13, 14, 6, 11, 10
 
 
 def half_bits(orc, x):
@@ -296,6 +296,55 @@ def test_q5_0_block_dots_recombine_to_the_row_dot(orc):
         assert total == np.float32(orc.dot_row(Q5_0, wv[j].reshape(-1), x, q8=True))
 
 
+def test_q2_k_values_scales_mins_and_order(orc):
+    """dequant.rs:143-174: x = d * (sc & 15) * q - dmin * (sc >> 4); block blk = 4 * half + shift index,
+    sub-block byte 2 * blk + group."""
+    block = np.zeros(84, dtype=np.uint8)
+    put_f16(orc, block, 80, 0.5)
+    put_f16(orc, block, 82, 0.25)
+    block[0] = 0x35                      # sub-block 0: scale 5, min 3
+    block[3] = 0x12                      # sub-block 3 (block 1, group 1): scale 2, min 1
+    block[8] = 0xF0                      # sub-block 8 (block 4 = half 1, shift 0): scale 0, min 15
+    block[16] = 0b11_10_01_10            # l = 0 of half 0: blocks 0..3 take 2, 1, 2, 3
+    block[16 + 16] = 0b00_00_11_00       # l = 16 of half 0: block 1 takes 3
+    out = orc.dequant(Q2_K, block, 256)
+    assert out[0] == 0.5 * 5 * 2 - 0.25 * 3 and out[1] == -0.25 * 3
+    assert out[32] == 0.0                # block 1, group 0: scale and min 0
+    assert out[32 + 16] == 0.5 * 2 * 3 - 0.25 * 1 and out[32 + 17] == -0.25
+    assert out[128] == -0.25 * 15
+    assert orc.expected_bytes(Q2_K, 512) == 168 and orc.expected_bytes(Q2_K, 300) == 0
+
+
+def test_q2_k_block_dots_and_mins_recombine_to_the_row_dot(orc):
+    """total += dl * dotq - ml * sum_x per sub-block, dotq and sum_x over the activation codes
+    (q8_acts.rs:156-170)."""
+    x = synth.normal_f32(512, 45)
+    d, s, q = orc.q8acts(x)
+    w = synth.q2_k_matrix(2, 512, 46)
+    dots = orc.block_dots(Q2_K, w, 2, 512, q)
+    wv = w.reshape(2, 2, 84)
+    for j in range(2):
+        total = np.float32(0.0)
+        for b in range(16):
+            blk = wv[j, b // 8]
+            dw = np.float32(blk[80:82].view(np.float16)[0])
+            dm = np.float32(blk[82:84].view(np.float16)[0])
+            vals = (blk[16 + ((b % 8) // 4) * 32: 16 + ((b % 8) // 4) * 32 + 32] >> (2 * (b % 4))) & 3
+            xq = q[b * 32:(b + 1) * 32].astype(np.int64)
+            want_int = 0
+            for g in range(2):
+                sc = int(blk[2 * (b % 8) + g])
+                dot = int(np.sum(vals[g * 16:(g + 1) * 16].astype(np.int64) * xq[g * 16:(g + 1) * 16]))
+                want_int += (sc & 15) * dot
+                dl = np.float32(dw * np.float32(sc & 15))
+                ml = np.float32(dm * np.float32(sc >> 4))
+                dotq = np.float32(np.float32(dot) * d[b])
+                sum_x = np.float32(np.float32(int(np.sum(xq[g * 16:(g + 1) * 16]))) * d[b])
+                total = np.float32(total + np.float32(np.float32(dl * dotq) - np.float32(ml * sum_x)))
+            assert dots[0, j, b] == want_int
+        assert total == np.float32(orc.dot_row(Q2_K, wv[j].reshape(-1), x, q8=True))
+
+
 def test_q3_k_values_scales_and_order(orc):
     """dequant.rs:176-204: x = d * (scale - 32) * q, q = two bits of qs minus 4 where the hmask bit of
     the block is clear; block blk = 4 * half + shift index, sub-block scale index 2 * blk + group."""
@@ -386,7 +435,7 @@ def kt_acts():
     return np.array([((i * 7 % 23) - 11.0) * 0.03 for i in range(N_IN)], dtype=np.float32)
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q3_K, Q4_K, Q5_K, Q6_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K])
 def test_float_dot_kernels_match_the_dequantizer(orc, ty):
     """kernel_tests.rs:58-88"""
     x = kt_acts()
@@ -398,7 +447,7 @@ def test_float_dot_kernels_match_the_dequantizer(orc, ty):
     assert abs(got - want) <= 1e-4 * mag + 1e-5
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q3_K, Q4_K, Q5_K, Q6_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K])
 def test_q8_activation_kernels_match_the_dequantizer(orc, ty):
     """kernel_tests.rs:90-121"""
     x = kt_acts()

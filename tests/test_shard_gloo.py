@@ -14,7 +14,7 @@ import torch.multiprocessing as mp
 
 from allpaka_b200 import build, gpu, synth
 
-Q8_0, Q4_K, Q5_K, Q6_K, Q5_0, Q3_K = 8, 12, 13, 14, 6, 11
+Q8_0, Q4_K, Q5_K, Q6_K, Q5_0, Q3_K, Q2_K = 8, 12, 13, 14, 6, 11, 10
 
 
 def _free_port():
@@ -110,7 +110,7 @@ def _worker(rank, world, port, ty, out_q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q3_K, Q4_K, Q5_K, Q6_K])
+@pytest.mark.parametrize("ty", [Q8_0, Q5_0, Q2_K, Q3_K, Q4_K, Q5_K, Q6_K])
 def test_two_rank_tensor_parallel_layer_matches_unsharded_oracle(ty):
     build.build()
     from oracle import oracle

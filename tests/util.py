@@ -3,7 +3,7 @@ import numpy as np
 
 from allpaka_b200 import synth
 
-Q8_0, Q4_K, Q5_K, Q6_K, Q5_0, Q3_K = 8, 12, 13, 14, 6, 11
+Q8_0, Q4_K, Q5_K, Q6_K, Q5_0, Q3_K, Q2_K = 8, 12, 13, 14, 6, 11, 10
 
 
 def rel_l2(got, want):
