@@ -252,7 +252,8 @@ int apk_decode_replay(apk_ctx *ctx, const apk_token_req *req, uint32_t iters, fl
  * dots[(i*n_out + j)*(n_in/32) + b], for Q8-activation mode.  For Q4_K and Q5_K
  * block b = 8*superblock + sub-block; for Q6_K and Q3_K the entry is sc0*dot0 + sc1*dot1
  * of the block's two 16-element halves, the integer the reference scales
- * (quantmat/q8_acts.rs:338-342, 206-210); for Q5_0 the dot with the values q - 16. */
+ * (quantmat/q8_acts.rs:338-342, 206-210), for Q2_K the same with its 4-bit scales (its min
+ * term is not a dot with the weights); for Q5_0 the dot with the values q - 16. */
 int apk_debug_block_dots(apk_ctx *ctx, const void *w, uint32_t ty, uint32_t n_in, uint32_t n_out,
                          const float *x, uint32_t m, int32_t *dots);
 
