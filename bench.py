@@ -48,7 +48,7 @@ if ROOT not in sys.path:
 
 HIDDEN, N_HEADS, N_KV, HEAD_DIM, FFN, VOCAB, N_LAYERS = 5120, 64, 8, 128, 25600, 151936, 64
 EPS, ROPE_BASE = 1e-6, 1e6
-Q8_0, Q4_K, Q6_K, Q5_0 = 8, 12, 14, 6
+Q8_0, Q4_K, Q6_K, Q5_0, Q3_K, Q2_K = 8, 12, 14, 6, 11, 10
 FALLBACK_HBM_GBS = 6650.0
 PARITY_LAYERS = 4
 METRIC = "decode tok/s Qwen3-32B-shape Q8_0"
@@ -62,6 +62,8 @@ def q8_bytes(n_out, n_in):
 def ty_bytes(ty, n_out, n_in):
     if ty == Q5_0:
         return n_out * (n_in // 32) * 22
+    if ty in (Q3_K, Q2_K):
+        return n_out * (n_in // 256) * (110 if ty == Q3_K else 84)
     return q8_bytes(n_out, n_in) if ty == Q8_0 else n_out * (n_in // 256) * (144 if ty == Q4_K else 210)
 
 
@@ -394,6 +396,21 @@ def run_configs(g, peak):
     g.synth_release()
     out["1_q5_0"] = entry(us, ty_bytes(Q5_0, n_out, n_in) + 4 * (n_in + n_out), par, what="Q5_0 25600x5120 m=1", ring_mb=7 * 90.1)
     g.detach(keep[1])
+
+    # the same shape in Q3_K and Q2_K: both are held in the Q6_K stream on the device (210 and 228 B per super-block
+    # against 110 and 84 in the file), the fraction is on the file's bytes as everywhere
+    for name, ty, gen, n_copies, seed0 in (("1_q3_k", Q3_K, synth.q3_k_matrix, 10, 74500), ("1_q2_k", Q2_K, synth.q2_k_matrix, 13, 75500)):
+        w = gen(n_out, n_in, seed0 % 1000 + 41)
+        assert g.attach(w)
+        par = rel_l2(g.matvec(ty, w, n_in, n_out, x, 1), orc.matmul(ty, w, n_out, n_in, x, 1))
+        g.detach(w)
+        copies, keep = ring([(n_out, n_in)], n_copies, ty, seed0)
+        us = g.bench_ring("matvec", [G.MatvecReq(ty, c[0], n_in, n_out, x, 1) for c in copies], reps=12)
+        g.synth_release()
+        nb = ty_bytes(ty, n_out, n_in)
+        out[name] = entry(us, nb + 4 * (n_in + n_out), par, what=f"{name[2:].upper()} 25600x5120 m=1",
+                          ring_mb=n_copies * nb / 1e6, device_bytes=n_out * (n_in // 256) * (210 if ty == Q3_K else 228))
+        g.detach(keep[1])
 
     # config 2: RMSNorm -> Q8_0 QKV 10240x5120 -> NeoX RoPE, batch 1 (bf16 x, widened exactly)
     nq, nkv = N_HEADS * HEAD_DIM, N_KV * HEAD_DIM
