@@ -487,6 +487,15 @@ def run_configs(g, peak):
         nbytes = 2 * n_pos * kv_dim * 2 + 2 * 4 * N_HEADS * HEAD_DIM
         out[f"attention_{n_pos}"] = entry(us, nbytes, par, what=f"attention core, {N_HEADS}/{N_KV} heads, {n_pos} positions, m=1",
                                           ring_mb=n_layers_kv * nbytes / 1e6)
+        if n_pos == 32768:
+            # a verify batch of 4 rows at consecutive positions: two rows share each CTA's pass over K and V
+            kv = G.KvCache(g, n_layers_kv, kv_dim, n_pos)
+            q4 = rng.standard_normal((4, N_HEADS * HEAD_DIM)).astype(np.float32)
+            us = g.bench_attend(kv, q4, 4, N_HEADS, n_pos - 4, scale, reps=10)
+            kv.close()
+            nb4 = 2 * n_pos * kv_dim * 2 + 4 * 2 * 4 * N_HEADS * HEAD_DIM
+            out["attention_32768_m4"] = entry(us, nb4, par, what=f"attention core, {N_HEADS}/{N_KV} heads, {n_pos} positions, m=4 (verify)",
+                                              ring_mb=n_layers_kv * nb4 / 1e6)
     return out
 
 
