@@ -115,8 +115,8 @@ enum Epilogue : int {
 };
 
 // One-shot exchange of row-parallel partial sums between the ranks of a
-// tensor-parallel group over peer-mapped memory (plain stores across NVLink; no
-// multicast).  Every rank owns one buffer, laid out
+// tensor-parallel group over peer-mapped memory (plain stores across NVLink, one
+// per peer).  Every rank owns one buffer, laid out
 //   slots [2 parity][XCH_MAX_RANKS][XCH_ROW_FLOATS] 64-bit words | tok u32
 // Exchanges are numbered e = 1, 2, ... for the life of the group (every rank runs the
 // same sequence).  The CTA of rank s that closes a 128-row tile of the row-parallel matvec
