@@ -428,12 +428,6 @@ __device__ __forceinline__ void q5_k_high(uint4 &lo, uint4 &hi, const uint4 &qh,
     hi.x |= ((qh.x >> (s + 1)) & 0x01010101u) << 4; hi.y |= ((qh.y >> (s + 1)) & 0x01010101u) << 4;
     hi.z |= ((qh.z >> (s + 1)) & 0x01010101u) << 4; hi.w |= ((qh.w >> (s + 1)) & 0x01010101u) << 4;
 }
-// byte i (0..15) of a 16-byte vector as a signed value
-__device__ __forceinline__ int s8_of(const uint4 &v, int i) {
-    const int w = i >> 2;
-    const uint32_t x = w == 0 ? v.x : (w == 1 ? v.y : (w == 2 ? v.z : v.w));
-    return (int)(x << (24 - 8 * (i & 3))) >> 24;
-}
 
 // Q5_0: q - 16 as int8 is the nibble with 0xF0 on top where the fifth bit is clear.  The repack stores
 // the fifth bits inverted, per lane one byte per fragment row: bits 0..3 for elements 4t..4t+3, bits
@@ -2489,15 +2483,14 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     // activation codes of the two halves (q8_acts.rs:160-168), which the -32 correction has already.
                     constexpr bool K2 = TY == TY_Q2_K;
                     const uint8_t *base = sw + rgc * k6_sb_rg(TY);
-                    const uint4 scl = *reinterpret_cast<const uint4 *>(base + 6144 + (lg * 4 + 2 * h16c) * 16);      // row lg
-                    const uint4 sch = *reinterpret_cast<const uint4 *>(base + 6144 + (lg * 4 + 2 * h16c + 1) * 16);  // row lg+8
+                    // the 16 sub-block scales of row lg, then of row lg+8: a lane reads the two bytes of the block
+                    // whose dot it holds (a 16-bit load at a lane-dependent offset, no byte selection in registers)
+                    const uint8_t *sc_rows = base + 6144 + (lg * 4 + 2 * h16c) * 16;
+                    const uint8_t *mn_rows = base + Q6_SB_RG + (lg * 4 + 2 * h16c) * 16;  // Q2_K: the mins, same layout
                     const __half2 dd = *reinterpret_cast<const __half2 *>(base + 6656 + (lg * 4 + 2 * h16c) * 2);
                     const float dwl = __low2float(dd), dwh = __high2float(dd);
-                    uint4 mnl = make_uint4(0u, 0u, 0u, 0u), mnh = mnl;
                     float dml = 0.0f, dmh = 0.0f;
                     if (K2) {
-                        mnl = *reinterpret_cast<const uint4 *>(base + Q6_SB_RG + (lg * 4 + 2 * h16c) * 16);
-                        mnh = *reinterpret_cast<const uint4 *>(base + Q6_SB_RG + (lg * 4 + 2 * h16c + 1) * 16);
                         const __half2 dm = *reinterpret_cast<const __half2 *>(base + Q6_SB_RG + 512 + (lg * 4 + 2 * h16c) * 2);
                         dml = __low2float(dm);
                         dmh = __high2float(dm);
@@ -2524,19 +2517,15 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                             mma_half_s8_acc(e, a.z, a.w, my_blk == i ? xb1 : 0u);
                         }
                         int I[4];
+                        int J[4] = {0, 0, 0, 0};  // Q2_K: mn0 * sum0 + mn1 * sum1 (sd, se are 32 x the sums)
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
                             const int b = ch * BPC + (2 * lt + (i & 1)) / MP2;
-                            I[i] = (i >> 1) ? s8_of(sch, 2 * b) * (d[i] - sd[i]) + s8_of(sch, 2 * b + 1) * (e[i] - se[i])
-                                            : s8_of(scl, 2 * b) * (d[i] - sd[i]) + s8_of(scl, 2 * b + 1) * (e[i] - se[i]);
-                        }
-                        int J[4] = {0, 0, 0, 0};  // Q2_K: mn0 * sum0 + mn1 * sum1 (sd, se are 32 x the sums)
-                        if (K2) {
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                const int b = ch * BPC + (2 * lt + (i & 1)) / MP2;
-                                J[i] = (i >> 1) ? s8_of(mnh, 2 * b) * (sd[i] >> 5) + s8_of(mnh, 2 * b + 1) * (se[i] >> 5)
-                                                : s8_of(mnl, 2 * b) * (sd[i] >> 5) + s8_of(mnl, 2 * b + 1) * (se[i] >> 5);
+                            const uint32_t w = *reinterpret_cast<const unsigned short *>(sc_rows + (i >> 1) * 16 + 2 * b);
+                            I[i] = ((int)(w << 24) >> 24) * (d[i] - sd[i]) + ((int)(w << 16) >> 24) * (e[i] - se[i]);
+                            if (K2) {
+                                const uint32_t wm = *reinterpret_cast<const unsigned short *>(mn_rows + (i >> 1) * 16 + 2 * b);
+                                J[i] = (int)(wm & 0xffu) * (sd[i] >> 5) + (int)(wm >> 8) * (se[i] >> 5);
                             }
                         }
                         if (MP2 > 1 && p.two_level) {
