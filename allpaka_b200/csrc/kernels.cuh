@@ -2589,11 +2589,11 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                                     const int c = 2 * lt + (i & 1);
                                     const int sbk = ch * BPC + c / MP2;  // sub-block of the super-block
                                     const int tok = (c % MP2) < M ? (c % MP2) : M - 1;
-                                    // 6-bit scale and min of rows lg, lg+8 (split out at repack): four sub-blocks per word
-                                    const uint2 scw = *reinterpret_cast<const uint2 *>(hdr + 128 + ((lg * 2 + (sbk >> 2)) * 4 + 2 * h16c) * 4);
-                                    const uint2 mnw = *reinterpret_cast<const uint2 *>(hdr + 384 + ((lg * 2 + (sbk >> 2)) * 4 + 2 * h16c) * 4);
-                                    const float sc = (float)((((i >> 1) ? scw.y : scw.x) >> (8 * (sbk & 3))) & 0xffu);
-                                    const float mn = (float)((((i >> 1) ? mnw.y : mnw.x) >> (8 * (sbk & 3))) & 0xffu);
+                                    // 6-bit scale and min of row lg (i < 2) or lg+8 (split out at repack, four sub-blocks per
+                                    // word): one byte load each at the lane's own offset, nothing selected in registers
+                                    const int hoff = ((lg * 2 + (sbk >> 2)) * 4 + 2 * h16c + (i >> 1)) * 4 + (sbk & 3);
+                                    const float sc = (float)hdr[128 + hoff];
+                                    const float mn = (float)hdr[384 + hoff];
                                     const int b = sbi * 8 + sbk;
                                     if (MP2 > 1 && p.two_level) {
                                         // digits merged as integers (d2 = d1 / 256); odd columns carry nothing
