@@ -334,7 +334,8 @@ int build_matrix(apk_ctx *c, uint32_t ty, uint32_t n_out, uint32_t n_in, const s
     m->n_tiles = (int)((n_out + TILE_ROWS - 1) / TILE_ROWS);
     const int kt = ty_k45((int)ty) ? Q4_KT_SB * 8 : Q8_KT;
     m->KS = (m->nb + kt - 1) / kt;
-    m->tile_bytes = ty_b32((int)ty) ? (uint32_t)m->nb * (uint32_t)b32_unit((int)ty)
+    m->tile_bytes = ty_b32((int)ty) ? (uint32_t)(m->nb / Q8_KT) * (uint32_t)b32_step_bytes((int)ty, Q8_KT) +
+                                          (m->nb % Q8_KT ? (uint32_t)b32_step_bytes((int)ty, m->nb % Q8_KT) : 0u)
                                       : (uint32_t)(m->nb / 8) * (ty == APK_TY_Q4_K ? Q4_SB_UNIT : (ty == APK_TY_Q5_K ? Q5_SB_UNIT : (ty == APK_TY_Q2_K ? Q2_SB_UNIT : Q6_SB_UNIT)));
     m->bytes = (size_t)m->n_tiles * m->tile_bytes;
     CUDA_TRY(cudaMalloc((void **)&m->d, m->bytes));

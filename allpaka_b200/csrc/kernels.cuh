@@ -62,16 +62,17 @@ constexpr int Q2_SB_RG = Q6_SB_RG + 512 + 64;   // 7296
 constexpr int Q2_SB_UNIT = 4 * Q2_SB_RG;        // 29184
 __host__ __device__ constexpr bool ty_k6(int ty) { return ty == 14 || ty == 10; }
 __host__ __device__ constexpr int k6_sb_rg(int ty) { return ty == 10 ? Q2_SB_RG : Q6_SB_RG; }
-constexpr int Q50_BLOCK_UNIT = 2816; // Q5_0, 128 rows * 22 B: 2048 B nibbles + 512 B fifth bits + 256 B scales
+constexpr int Q50_BLOCK_UNIT = 2816; // Q5_0, 128 rows * 22 B: 2048 B nibbles + 512 B of the K-step's fifth-bit plane + 256 B scales
 __host__ __device__ constexpr int stage_w_bytes(int ty) {  // one full K-step of weights
     return ty == 8 ? 8 * 4352 : (ty == 6 ? 8 * 2816 : (ty == 14 ? 26880 : (ty == 10 ? 29184 : (ty == 13 ? 2 * 23040 : 2 * 18944))));
 }
-// Q8_0 and Q5_0: 32-element blocks with one f16 scale, eight blocks per K-step.  Within a K-step of kb
-// blocks the stream holds kb fragment arrays (b32_q_bytes each), for Q5_0 then kb arrays of fifth
-// bits (512 B each), then kb arrays of 128 scales.
+// Q8_0 and Q5_0: 32-element blocks with one f16 scale, eight blocks per K-step.  A K-step of kb
+// blocks holds kb fragment arrays (4096 B of int8 for Q8_0, 2048 B of nibbles for Q5_0), for Q5_0
+// then ONE 4096-byte plane of fifth bits (bit j of a byte = block j of the K-step, bytes in
+// fragment order), then kb arrays of 128 scales.
 __host__ __device__ constexpr bool ty_b32(int ty) { return ty == 8 || ty == 6; }
-__host__ __device__ constexpr int b32_q_bytes(int ty) { return ty == 6 ? 2048 : 4096; }
-__host__ __device__ constexpr int b32_unit(int ty) { return ty == 6 ? Q50_BLOCK_UNIT : Q8_BLOCK_UNIT; }
+__host__ __device__ constexpr int b32_step_bytes(int ty, int kb) { return ty == 6 ? kb * 2304 + 4096 : kb * 4352; }
+__host__ __device__ constexpr int b32_scale_off(int ty, int kb) { return ty == 6 ? kb * 2048 + 4096 : kb * 4096; }
 // Q4_K and Q5_K share everything but the fifth bit: row-group size and header offset of a super-block
 __host__ __device__ constexpr bool ty_k45(int ty) { return ty == 12 || ty == 13; }
 __host__ __device__ constexpr int k45_sb_rg(int ty) { return ty == 13 ? Q5_SB_RG : Q4_SB_RG; }
@@ -429,25 +430,27 @@ __device__ __forceinline__ void q5_k_high(uint4 &lo, uint4 &hi, const uint4 &qh,
     hi.z |= ((qh.z >> (s + 1)) & 0x01010101u) << 4; hi.w |= ((qh.w >> (s + 1)) & 0x01010101u) << 4;
 }
 
-// Q5_0: q - 16 as int8 is the nibble with 0xF0 on top where the fifth bit is clear.  The repack stores
-// the fifth bits inverted, per lane one byte per fragment row: bits 0..3 for elements 4t..4t+3, bits
-// 4..7 for elements 16+4t..16+4t+3 (crates/allpaka-backend/src/quantmat/q8_acts.rs:115-120).
-__device__ __forceinline__ uint32_t q5_0_top(uint32_t inv4) { return ((inv4 * 0x00204081u) & 0x01010101u) * 0xF0u; }
-__device__ __forceinline__ uint4 q5_0_unpack(const uint2 nib, uint32_t inv) {
+// Q5_0: the codes q = nibble | fifth bit << 4 (0..31) of block b as an A fragment, WITHOUT the - 16 of
+// crates/allpaka-backend/src/quantmat/q8_acts.rs:115-120: dot(q - 16, x) = dot(q, x) - 16 * sum(x), and the
+// sums of the activation codes come out of one mma against an all-0x10 fragment (see the consumers).
+// nib: the row pair's nibble words (low nibbles = elements 0..15, the first k-half); qh: this lane's
+// bytes of the K-step's fifth-bit plane, bit b of each byte belonging to block b.
+__device__ __forceinline__ uint4 q5_0_unpack(const uint2 nib, const uint4 &qh, int b) {
     uint4 a;
-    a.x = (nib.x & 0x0f0f0f0fu) | q5_0_top(inv & 15u);
-    a.y = (nib.y & 0x0f0f0f0fu) | q5_0_top((inv >> 8) & 15u);
-    a.z = ((nib.x >> 4) & 0x0f0f0f0fu) | q5_0_top((inv >> 4) & 15u);
-    a.w = ((nib.y >> 4) & 0x0f0f0f0fu) | q5_0_top((inv >> 12) & 15u);
+    a.x = (nib.x & 0x0f0f0f0fu) | (((qh.x >> b) & 0x01010101u) << 4);
+    a.y = (nib.y & 0x0f0f0f0fu) | (((qh.y >> b) & 0x01010101u) << 4);
+    a.z = ((nib.x >> 4) & 0x0f0f0f0fu) | (((qh.z >> b) & 0x01010101u) << 4);
+    a.w = ((nib.y >> 4) & 0x0f0f0f0fu) | (((qh.w >> b) & 0x01010101u) << 4);
     return a;
 }
 // the A fragment of 16 rows (row group rg, half h16) of block b in a staged K-step of kb blocks
+// (Q5_0: codes 0..31, see q5_0_unpack)
 template <int TY>
 __device__ __forceinline__ uint4 b32_frag(const uint8_t *sw, int kb, int b, int rg, int h16, int lane) {
     if constexpr (TY == TY_Q5_0) {
         const uint2 nib = *reinterpret_cast<const uint2 *>(sw + b * 2048 + rg * 512 + h16 * 256 + lane * 8);
-        const uint32_t inv = *reinterpret_cast<const uint16_t *>(sw + kb * 2048 + b * 512 + rg * 128 + h16 * 64 + lane * 2);
-        return q5_0_unpack(nib, inv);
+        const uint4 qh = *reinterpret_cast<const uint4 *>(sw + kb * 2048 + ((rg * 2 + h16) * 32 + lane) * 16);
+        return q5_0_unpack(nib, qh, b);
     } else {
         return *reinterpret_cast<const uint4 *>(sw + b * 4096 + rg * 1024 + h16 * 512 + lane * 16);
     }
@@ -761,7 +764,8 @@ static __global__ void repack_q8_0_kernel(RepackParams p) {
 }
 
 // Q5_0, one thread per (row, block): 22 source bytes {f16 d, u32 qh, 16 B nibbles} -> four nibble words
-// (byte j = elements j and j + 16, as in the file), the inverted fifth bits of this row's lanes, scale.
+// (byte j = elements j and j + 16, as in the file), this block's bit in the K-step's fifth-bit plane
+// (eight blocks share each byte, hence the atomic OR into the zero-filled destination), scale.
 static __global__ void repack_q5_0_kernel(RepackParams p) {
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     const size_t total = (size_t)p.src_rows * p.nb;
@@ -774,18 +778,25 @@ static __global__ void repack_q5_0_kernel(RepackParams p) {
     frag_pos(rt, rg, h16, g, upper);
     const int ks = b / Q8_KT, bl = b % Q8_KT;
     const int kb = min(Q8_KT, p.nb - ks * Q8_KT);
-    uint8_t *unit = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)ks * Q8_KT * Q50_BLOCK_UNIT;
-    const uint32_t inv = ~((uint32_t)s[2] | ((uint32_t)s[3] << 8) | ((uint32_t)s[4] << 16) | ((uint32_t)s[5] << 24));
+    uint8_t *unit = p.dst + (size_t)tile * p.dst_tile_bytes + (size_t)ks * b32_step_bytes(TY_Q5_0, Q8_KT);
+    const uint32_t qh = (uint32_t)s[2] | ((uint32_t)s[3] << 8) | ((uint32_t)s[4] << 16) | ((uint32_t)s[5] << 24);
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
         const uint32_t v = (uint32_t)s[6 + 4 * w] | ((uint32_t)s[7 + 4 * w] << 8) | ((uint32_t)s[8 + 4 * w] << 16) |
                            ((uint32_t)s[9 + 4 * w] << 24);
-        const int lane = g * 4 + w;
-        *reinterpret_cast<uint32_t *>(unit + bl * 2048 + rg * 512 + h16 * 256 + lane * 8 + upper * 4) = v;
-        unit[kb * 2048 + bl * 512 + rg * 128 + h16 * 64 + lane * 2 + upper] =
-            (uint8_t)(((inv >> (4 * w)) & 15u) | (((inv >> (16 + 4 * w)) & 15u) << 4));
+        *reinterpret_cast<uint32_t *>(unit + bl * 2048 + rg * 512 + h16 * 256 + (g * 4 + w) * 8 + upper * 4) = v;
     }
-    uint16_t *sc = reinterpret_cast<uint16_t *>(unit + kb * 2560 + ((bl * 4 + rg) * 8 + g) * 8 + (h16 * 2 + upper) * 2);
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {  // k-word w: elements 4w..4w+3, lane column w % 4, fragment register 2 * (w / 4) + upper
+        uint32_t bits = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) bits |= ((qh >> (4 * w + k)) & 1u) << (8 * k + bl);
+        if (bits)
+            atomicOr(reinterpret_cast<unsigned int *>(unit + kb * 2048 + ((rg * 2 + h16) * 32 + g * 4 + (w & 3)) * 16 +
+                                                      (2 * (w >> 2) + upper) * 4),
+                     bits);
+    }
+    uint16_t *sc = reinterpret_cast<uint16_t *>(unit + b32_scale_off(TY_Q5_0, kb) + ((bl * 4 + rg) * 8 + g) * 8 + (h16 * 2 + upper) * 2);
     *sc = (uint16_t)(s[0] | (s[1] << 8));
 }
 
@@ -1462,21 +1473,18 @@ static __global__ void __launch_bounds__(256) embed_row_kernel(EmbedParams p) {
         if (b >= p.nb) return;
         const int ks = b / Q8_KT, bl = b % Q8_KT;
         const int kb = min(Q8_KT, p.nb - ks * Q8_KT);
-        const uint8_t *unit = p.W + (size_t)tile * p.tile_bytes + (size_t)ks * Q8_KT * Q50_BLOCK_UNIT;
-        const int lane = g * 4 + (w & 3);
+        const uint8_t *unit = p.W + (size_t)tile * p.tile_bytes + (size_t)ks * b32_step_bytes(TY_Q5_0, Q8_KT);
+        const int lane = g * 4 + (w & 3), reg = 2 * (w >> 2) + upper;
         uint32_t nib = *reinterpret_cast<const uint32_t *>(unit + bl * 2048 + rg * 512 + h16 * 256 + lane * 8 + upper * 4);
-        uint32_t inv = unit[kb * 2048 + bl * 512 + rg * 128 + h16 * 64 + lane * 2 + upper];
-        if (w >= 4) {
-            nib >>= 4;
-            inv >>= 4;
-        }
-        const uint32_t v = (nib & 0x0f0f0f0fu) | q5_0_top(inv & 15u);
-        const float d = __half2float(*reinterpret_cast<const __half *>(unit + kb * 2560 + ((bl * 4 + rg) * 8 + g) * 8 + (h16 * 2 + upper) * 2));
+        if (w >= 4) nib >>= 4;
+        const uint32_t qh = *reinterpret_cast<const uint32_t *>(unit + kb * 2048 + ((rg * 2 + h16) * 32 + lane) * 16 + reg * 4);
+        const uint32_t v = (nib & 0x0f0f0f0fu) | (((qh >> bl) & 0x01010101u) << 4);
+        const float d = __half2float(*reinterpret_cast<const __half *>(unit + b32_scale_off(TY_Q5_0, kb) + ((bl * 4 + rg) * 8 + g) * 8 + (h16 * 2 + upper) * 2));
         float4 o;
-        o.x = __fmul_rn(d, (float)(int8_t)(v & 0xffu));
-        o.y = __fmul_rn(d, (float)(int8_t)((v >> 8) & 0xffu));
-        o.z = __fmul_rn(d, (float)(int8_t)((v >> 16) & 0xffu));
-        o.w = __fmul_rn(d, (float)(int8_t)(v >> 24));
+        o.x = __fmul_rn(d, (float)((int)(v & 0xffu) - 16));
+        o.y = __fmul_rn(d, (float)((int)((v >> 8) & 0xffu) - 16));
+        o.z = __fmul_rn(d, (float)((int)((v >> 16) & 0xffu) - 16));
+        o.w = __fmul_rn(d, (float)((int)(v >> 24) - 16));
         *reinterpret_cast<float4 *>(p.x + b * 32 + 4 * w) = o;
     } else if (ty_k6(p.ty)) {
         // one thread per (super-block, half, 4-byte word): four values of each of the half's quarters,
@@ -2037,8 +2045,8 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 const int kb = min(kt, p.nb - ks * kt);
                 uint32_t wbytes, woff;
                 if (ty_b32(TY)) {
-                    wbytes = (uint32_t)kb * b32_unit(TY);
-                    woff = (uint32_t)ks * Q8_KT * b32_unit(TY);
+                    wbytes = (uint32_t)b32_step_bytes(TY, kb);
+                    woff = (uint32_t)ks * (uint32_t)b32_step_bytes(TY, Q8_KT);
                 } else if (ty_k6(TY)) {
                     wbytes = (uint32_t)(4 * k6_sb_rg(TY));
                     woff = (uint32_t)ks * (uint32_t)(4 * k6_sb_rg(TY));
@@ -2422,7 +2430,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                     }
                 };
                 if (ty_b32(TY)) {
-                    const uint8_t *ws = sw + kb * (b32_unit(TY) - 256) + (rgc * 8 + lg) * 8 + h16c * 4;  // + b*256: scales of rows lg, lg+8
+                    const uint8_t *ws = sw + b32_scale_off(TY, kb) + (rgc * 8 + lg) * 8 + h16c * 4;  // + b*256: scales of rows lg, lg+8
 #pragma unroll
                     for (int cb = 0; cb < Q8_KT; cb += BPC) {
                         if (cb < kb) {
@@ -2446,6 +2454,13 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                             if (BPC > 1) {
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) d[i] += e[i];
+                            }
+                            if (TY == TY_Q5_0) {
+                                // the codes went in as 0..31: take 16 x the sum of the column's activation codes off
+                                int sd[4] = {0, 0, 0, 0};
+                                mma_block_s8_acc(sd, make_uint4(0x10101010u, 0x10101010u, 0x10101010u, 0x10101010u), xb0, xb1);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) d[i] -= sd[i];
                             }
                             if (MP2 > 1 && p.two_level) {
                                 // columns 2lt, 2lt+1 are the two digits of one token of one block, d2 = d1 / 256:
@@ -2624,7 +2639,7 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                 // this warp: blocks kq, kq+4 of the K-step.  Activation rows past M are clamped to
                 // row M-1: their results are computed but never stored, which keeps predicates
                 // out of the loop.
-                const uint8_t *ws = sw + kb * (b32_unit(TY) - 256) + (rg * 8 + lg) * 8;   // + b*256
+                const uint8_t *ws = sw + b32_scale_off(TY, kb) + (rg * 8 + lg) * 8;   // + b*256
                 auto block = [&](int b) {
                     const uint4 a0 = b32_frag<TY>(sw, kb, b, rg, 0, lane);
                     const uint4 a1 = b32_frag<TY>(sw, kb, b, rg, 1, lane);
@@ -2644,6 +2659,16 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                         int d0[4], d1[4];
                         mma_block_s8(d0, a0, b0, b1);
                         mma_block_s8(d1, a1, b0, b1);
+                        if (TY == TY_Q5_0) {
+                            // the codes went in as 0..31: take 16 x the sum of the column's activation codes off
+                            int sd[4];
+                            mma_block_s8(sd, make_uint4(0x10101010u, 0x10101010u, 0x10101010u, 0x10101010u), b0, b1);
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                d0[i] -= sd[i];
+                                d1[i] -= sd[i];
+                            }
+                        }
                         const float dx0 = xd[t0];
                         // total += d_w * d_x * dot (q8_acts.rs:93), per (row, token)
                         if (M > 8 || (M > 1 && p.two_level)) {
