@@ -214,6 +214,15 @@ struct apk_ctx {
     int n_sm = 0;
     int smem_optin = 0;
     cudaStream_t stream = nullptr;
+    // A V projection with a type of its own runs beside the Q | K launch on a few SMs of its own
+    // (ALLPAKA_B200_FORK_V=0: after it, like every other launch): a second stream forked and joined
+    // with events, which capture turns into two branches of the token graph.
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaStream_t launch_stream = nullptr;  // where launch_ex puts the next kernels (null: stream)
+    int grid_cap = 0;                      // most CTAs the next matvec launches may take (0: no cap)
+    bool no_pdl_once = false;              // the next launch waits for two branches: no programmatic edge
+    int fork_v = 4;                        // CTAs per V tile of that branch (0: no branch); measured 1 / 2 / 4: 168 / 175 / 178 tok/s
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     std::map<std::pair<const uint8_t *, size_t>, int> attached;  // (base,len) -> refcount
     std::map<MatKey, std::unique_ptr<DevMatrix>> mats;
@@ -518,12 +527,13 @@ cudaError_t launch_ex(apk_ctx *c, void (*kernel)(Args...), dim3 grid, dim3 block
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
-    cfg.stream = c->stream;
+    cfg.stream = c->launch_stream ? c->launch_stream : c->stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = pdl && !c->no_pdl_once ? 1 : 0;
+    c->no_pdl_once = false;
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
@@ -616,7 +626,8 @@ int launch_matvec(apk_ctx *c, const DevMatrix *W, MvParams p, ActMode mode, bool
     p.n_stages = ns;
     const int smem = mv_smem_total((int)W->ty, mode.m_eff, p.pro, W->KS, act_rec, ns);
     const long long U = (long long)W->n_tiles * W->KS;
-    const int grid = (int)std::min<long long>(c->n_sm, U);
+    int grid = (int)std::min<long long>(c->n_sm, U);
+    if (c->grid_cap > 0) grid = std::min(grid, c->grid_cap);
     if ((U + 1) * grid >= (1LL << 31)) return fail(APK_DECLINE_UNSUPPORTED_SHAPE, "matrix too large for 32-bit unit arithmetic");
     // A launch may defer its dependency wait (xin_late) only behind a matvec that holds every SM
     // to itself: one CTA per SM, too much shared memory for a second one.  Its own CTAs then start
@@ -850,6 +861,10 @@ int apk_init(apk_ctx **out, int device) {
     c->smem_optin = (int)prop.sharedMemPerBlockOptin;
     c->smem_per_sm = (int)prop.sharedMemPerMultiprocessor;
     CUDA_TRY(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+    CUDA_TRY(cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking));
+    CUDA_TRY(cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming));
+    CUDA_TRY(cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming));
+    if (const char *e = getenv("ALLPAKA_B200_FORK_V")) c->fork_v = std::max(0, std::min(atoi(e), 8));
     CUDA_TRY(cudaEventCreate(&c->ev0));
     CUDA_TRY(cudaEventCreate(&c->ev1));
     CUDA_TRY(cudaMalloc((void **)&c->d_err, sizeof(int)));
@@ -900,6 +915,9 @@ void apk_shutdown(apk_ctx *c) {
     if (c->h_err) cudaFreeHost(c->h_err);
     if (c->ev0) cudaEventDestroy(c->ev0);
     if (c->ev1) cudaEventDestroy(c->ev1);
+    if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+    if (c->ev_join) cudaEventDestroy(c->ev_join);
+    if (c->side) cudaStreamDestroy(c->side);
     if (c->stream) cudaStreamDestroy(c->stream);
     delete c;
 }

@@ -379,8 +379,34 @@ struct TokenLaunch {
     }
     int qkv(PlanLayer &L, bool advance = true, uint32_t layer = 0) {
         if (L.v) {
-            APK_TRY(qkv_part(L, L.qkv, false, layer, 0));
-            return qkv_part(L, L.v, advance, layer, (int)((P->nq_l + P->nkv_l) / TILE_ROWS));
+            const int v_base = (int)((P->nq_l + P->nkv_l) / TILE_ROWS);
+            // One token row on one GPU, nothing pending on the residual stream: V (a few tiles, its row
+            // normalised and quantised inside its own CTAs) runs on SMs of its own beside Q | K instead of
+            // as a whole launch after it.  A few CTAs per V tile, the other SMs for Q | K; the kernel behind
+            // them waits for both branches.
+            // (at most a quarter of the SMs go to V)
+            const int v_ctas = L.v->n_tiles * std::min(c->fork_v, c->n_sm / (4 * std::max(1, L.v->n_tiles)));
+            const bool beside = v_ctas > 0 && c->world == 1 && !uses_xch(c) && m == 1 && !pending_add && pending_xch < 0 &&
+                                P->hidden <= (uint32_t)(N_CONSUMERS * PRO_CH) && want_resident(c, L.v, q8.m_eff);
+            if (!beside) {
+                APK_TRY(qkv_part(L, L.qkv, false, layer, 0));
+                return qkv_part(L, L.v, advance, layer, v_base);
+            }
+            CUDA_TRY(cudaEventRecord(c->ev_fork, c->stream));
+            CUDA_TRY(cudaStreamWaitEvent(c->side, c->ev_fork, 0));
+            c->launch_stream = c->side;
+            c->grid_cap = v_ctas;
+            int rc = qkv_part(L, L.v, false, layer, v_base);
+            c->launch_stream = nullptr;
+            if (rc == APK_OK) rc = cudaEventRecord(c->ev_join, c->side) == cudaSuccess ? APK_OK : fail(APK_ERR_CUDA, "event record on the side branch");
+            c->grid_cap = c->n_sm - v_ctas;
+            if (rc == APK_OK) rc = qkv_part(L, L.qkv, advance, layer, 0);
+            c->grid_cap = 0;
+            // (joined even after an error above, so that a capture in progress can end)
+            const cudaError_t je = cudaStreamWaitEvent(c->stream, c->ev_join, 0);
+            if (rc == APK_OK && je != cudaSuccess) rc = fail(APK_ERR_CUDA, "joining the side branch: %s", cudaGetErrorString(je));
+            c->no_pdl_once = true;
+            return rc;
         }
         return qkv_part(L, L.qkv, advance, layer, 0);
     }

@@ -173,9 +173,15 @@ def anon_region(nbytes):
     return mm, np.frombuffer(mm, dtype=np.uint8)
 
 
-def build_model(g, n_layers, write_host_layers, ty=Q8_0, m=1, head=True):
+def build_model(g, n_layers, write_host_layers, ty=Q8_0, m=1, head=True, ty_of=None):
     """Reserve a host mapping for the whole model, attach it, and fill the
-    tensors from the on-device generator (seeds 2000 + 8*layer + k)."""
+    tensors from the on-device generator (seeds 2000 + 8*layer + k).  `ty_of` maps tensor names
+    ("wv", "down", "head", ...) to a type of their own."""
+    base_ty = ty
+
+    def tty(name):
+        return (ty_of or {}).get(name, base_ty)
+
     from allpaka_b200 import gpu as G
     from allpaka_b200 import synth
 
@@ -187,33 +193,33 @@ def build_model(g, n_layers, write_host_layers, ty=Q8_0, m=1, head=True):
         lo = {}
         for name, n_out, n_in in specs:
             lo[name] = off
-            off += (ty_bytes(ty, n_out, n_in) + 255) // 256 * 256
+            off += (ty_bytes(tty(name), n_out, n_in) + 255) // 256 * 256
         offsets.append(lo)
     head_off = off
-    off += (ty_bytes(ty, vocab, HIDDEN) + 255) // 256 * 256
+    off += (ty_bytes(tty("head"), vocab, HIDDEN) + 255) // 256 * 256
     mm, region = anon_region(off)
     assert g.attach(region)
     layers, host = [], {}
     for l in range(n_layers):
         views = {}
         for k, (name, n_out, n_in) in enumerate(specs):
-            v = region[offsets[l][name]: offsets[l][name] + ty_bytes(ty, n_out, n_in)]
-            g.synth_matrix(v, ty, n_out, n_in, 2000 + 8 * l + k, write_host=(l in write_host_layers))
+            v = region[offsets[l][name]: offsets[l][name] + ty_bytes(tty(name), n_out, n_in)]
+            g.synth_matrix(v, tty(name), n_out, n_in, 2000 + 8 * l + k, write_host=(l in write_host_layers))
             views[name] = v
         an, fn = synth.gamma(HIDDEN, 5000 + 2 * l), synth.gamma(HIDDEN, 5001 + 2 * l)
-        layers.append(G.TokenLayer(an, fn, (ty, views["wq"], nq), (ty, views["wk"], nkv),
-                                   (ty, views["wv"], nkv), (ty, views["wo"], HIDDEN),
-                                   (ty, views["gate"], FFN), (ty, views["up"], FFN),
-                                   (ty, views["down"], HIDDEN)))
+        layers.append(G.TokenLayer(an, fn, (tty("wq"), views["wq"], nq), (tty("wk"), views["wk"], nkv),
+                                   (tty("wv"), views["wv"], nkv), (tty("wo"), views["wo"], HIDDEN),
+                                   (tty("gate"), views["gate"], FFN), (tty("up"), views["up"], FFN),
+                                   (tty("down"), views["down"], HIDDEN)))
         if l in write_host_layers:
             host[l] = dict(views, attn_norm=an, ffn_norm=fn)
-    hd = region[head_off: head_off + ty_bytes(ty, vocab, HIDDEN)]
-    g.synth_matrix(hd, ty, vocab, HIDDEN, 1999, write_host=bool(write_host_layers))
+    hd = region[head_off: head_off + ty_bytes(tty("head"), vocab, HIDDEN)]
+    g.synth_matrix(hd, tty("head"), vocab, HIDDEN, 1999, write_host=bool(write_host_layers))
     out_norm = synth.gamma(HIDDEN, 4999)
     x = synth.normal_f32((m, HIDDEN), 4242)
     pos0 = int(np.random.default_rng(4243).integers(0, 32768 - 8))
     rope = np.concatenate([rope_table(pos0 + i, HEAD_DIM, ROPE_BASE) for i in range(m)])
-    req = G.TokenReq(layers, out_norm, (ty, hd, vocab), x, m, rope, HEAD_DIM, EPS, HIDDEN, HEAD_DIM,
+    req = G.TokenReq(layers, out_norm, (tty("head"), hd, vocab), x, m, rope, HEAD_DIM, EPS, HIDDEN, HEAD_DIM,
                      N_HEADS, N_KV)
     return req, host, hd, out_norm, (mm, region)
 
@@ -713,6 +719,13 @@ def run_ours(args, rank, world, local_rank):
         except Exception as e:  # a side measurement, like the configs
             with_attention = {"error": f"{type(e).__name__}: {e}"}
 
+    k_m = None
+    if rank == 0 and world == 1 and not args.no_configs:
+        try:
+            k_m = decode_k_m(g, n_layers, args.steps, peak)
+        except Exception as e:  # a side measurement, like the configs
+            k_m = {"error": f"{type(e).__name__}: {e}"}
+
     if rank == 0:
         line = {
             "metric": METRIC, "value": value, "unit": "tok/s",
@@ -732,6 +745,7 @@ def run_ours(args, rank, world, local_rank):
             "tp_check": tp_check,
             "configs": configs,
             "decode_with_attention": with_attention,
+            "decode_q4_k_m": k_m,
             "cpu_baseline": cpu,
             "clocks": clocks,
             "setup_s": setup_s,
@@ -746,6 +760,27 @@ def run_ours(args, rank, world, local_rank):
         sys.exit(3)
     if rank == 0 and tp_check is not None and tp_check["p2p_vs_nccl_rel_l2"] > 2e-2:
         sys.exit(3)
+
+
+def decode_k_m(g, n_layers, steps, peak):
+    """The same 64-layer shape in the Q4_K_M recipe of K-quant files (Q4_K, with V, down and the LM head in Q6_K,
+    crates/allpaka-backend/src/gpu/cuda/decode_fused.rs:1733-1742): device-generated weights, graph replay timed
+    like `value`.  The fraction is on the file's bytes."""
+    km = {"wv": Q6_K, "down": Q6_K, "head": Q6_K}
+    req, _, _, _, keep = build_model(g, n_layers, (), ty=Q4_K, ty_of=km)
+    g.decode_replay(req, 1)  # repacks every tensor out of the generator's device copies, captures the token graph
+    g.synth_release()
+    g.decode_replay(req, 3)
+    ms = float(np.median([g.decode_replay(req, steps) for _ in range(5)])) / steps
+    nq, nkv = N_HEADS * HEAD_DIM, N_KV * HEAD_DIM
+    wbytes = n_layers * sum(ty_bytes(km.get(name, Q4_K), o, i) for name, o, i in layer_tensors(HIDDEN, nq, nkv, FFN)) \
+        + ty_bytes(Q6_K, VOCAB, HIDDEN)
+    prof = g.decode_profile(req, reps=3)
+    by_shape = {k: {"us": v["ms"] * 1e3, "frac": v["bytes"] / (v["ms"] * 1e-3) / 1e9 / peak} for k, v in prof.items()}
+    g.detach(keep[1])
+    gbs = wbytes / (ms * 1e-3) / 1e9
+    return {"tok_s": 1e3 / ms, "ms_per_step": ms, "weights_gb": wbytes / 1e9, "hbm_gbs": gbs, "frac": gbs / peak, "by_shape": by_shape,
+            "what": "64 layers + lm_head in the Q4_K_M mix (Q4_K; V, down and head Q6_K), batch 1, identity attention core"}
 
 
 def decode_with_attention(g, req, steps, positions=4096):
