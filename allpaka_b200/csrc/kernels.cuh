@@ -393,6 +393,13 @@ __device__ __forceinline__ void mma_block_s8_acc(int (&d)[4], const uint4 &a, ui
 
 // Half of that: 16 rows x 16 k-values x 8 columns, accumulating.  a0/a1 are registers 0, 1
 // (or 2, 3) of the k32 A fragment, b the matching B register.
+// the same with unsigned A bytes (weights as 0..255) and signed B bytes
+__device__ __forceinline__ void mma_block_u8s8_acc(int (&d)[4], const uint4 &a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a.x), "r"(a.y), "r"(a.z), "r"(a.w), "r"(b0), "r"(b1));
+}
 __device__ __forceinline__ void mma_half_s8_acc(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t b) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
@@ -2591,14 +2598,22 @@ __global__ void __launch_bounds__(MV_THREADS, 1) matvec_streamk_kernel(const MvP
                                     const int pr = ch * (BPC / 2) + pi;
                                     const uint4 q = *reinterpret_cast<const uint4 *>(base + ((pr * 2 + h16c) * 32 + lane) * 16);
                                     uint4 lo = make_uint4(q.x & 0x0f0f0f0fu, q.y & 0x0f0f0f0fu, q.z & 0x0f0f0f0fu, q.w & 0x0f0f0f0fu);
-                                    uint4 hi = make_uint4((q.x >> 4) & 0x0f0f0f0fu, (q.y >> 4) & 0x0f0f0f0fu,
-                                                          (q.z >> 4) & 0x0f0f0f0fu, (q.w >> 4) & 0x0f0f0f0fu);
-                                    if (K5) q5_k_high(lo, hi, qh5, pr);
-                                    mma_block_s8_acc(d, lo, my_blk == 2 * pi ? xb0 : 0u, my_blk == 2 * pi ? xb1 : 0u);
-                                    mma_block_s8_acc(e, hi, my_blk == 2 * pi + 1 ? xb0 : 0u, my_blk == 2 * pi + 1 ? xb1 : 0u);
+                                    if constexpr (K5) {
+                                        uint4 hi = make_uint4((q.x >> 4) & 0x0f0f0f0fu, (q.y >> 4) & 0x0f0f0f0fu,
+                                                              (q.z >> 4) & 0x0f0f0f0fu, (q.w >> 4) & 0x0f0f0f0fu);
+                                        q5_k_high(lo, hi, qh5, pr);
+                                        mma_block_s8_acc(d, lo, my_blk == 2 * pi ? xb0 : 0u, my_blk == 2 * pi ? xb1 : 0u);
+                                        mma_block_s8_acc(e, hi, my_blk == 2 * pi + 1 ? xb0 : 0u, my_blk == 2 * pi + 1 ? xb1 : 0u);
+                                    } else {
+                                        // Q4_K: the high nibbles stay where they are and go in as unsigned bytes 16 * q; the
+                                        // chain's sum is 16 x the dots, exactly, and is shifted back once (below)
+                                        const uint4 hi16 = make_uint4(q.x & 0xf0f0f0f0u, q.y & 0xf0f0f0f0u, q.z & 0xf0f0f0f0u, q.w & 0xf0f0f0f0u);
+                                        mma_block_s8_acc(d, lo, my_blk == 2 * pi ? xb0 : 0u, my_blk == 2 * pi ? xb1 : 0u);
+                                        mma_block_u8s8_acc(e, hi16, my_blk == 2 * pi + 1 ? xb0 : 0u, my_blk == 2 * pi + 1 ? xb1 : 0u);
+                                    }
                                 }
 #pragma unroll
-                                for (int i = 0; i < 4; ++i) d[i] += e[i];
+                                for (int i = 0; i < 4; ++i) d[i] += K5 ? e[i] : (e[i] >> 4);
 #pragma unroll
                                 for (int i = 0; i < 4; ++i) {
                                     const int c = 2 * lt + (i & 1);
