@@ -112,3 +112,39 @@ def test_tokens_from_a_model_file(orc, tmp_path, arch, ty, tied, ty_of):
     model.close()
     g.close()
     f.close()
+
+
+def test_v_beside_qk_gives_the_same_logits(orc, tmp_path, monkeypatch):
+    """In the K_M mix V has a type of its own and, for one token row, runs on SMs of its own beside the Q|K
+    launch (a forked branch of the token graph).  ALLPAKA_B200_FORK_V=0 runs it after Q|K instead: the
+    logits of a short decode must be the same bits either way."""
+    from allpaka_b200 import gpu as G
+
+    meta, tensors = tiny_model(arch="qwen3", ty=Q4_K, hidden=512, n_heads=4, n_kv=2, ffn=1024, vocab=1000, n_layers=3,
+                               qk_norm=True, tied=True, ty_of=K_M)
+    path = tmp_path / "model.gguf"
+    gguf.write_file(str(path), meta, tensors)
+    runs = []
+    for fork in ("0", "4"):
+        monkeypatch.setenv("ALLPAKA_B200_FORK_V", fork)
+        f = gguf.GgufFile(str(path))
+        model = gguf.Model(f)
+        info = model.info
+        g = G.Gpu(0)
+        model.attach(g)
+        kv = G.KvCache(g, info["n_layers"], info["n_kv_heads"] * info["head_dim"], 8)
+        outs = []
+        for pos, tok in enumerate((7, 400, 999, 3)):
+            req = model.request()
+            rope = rope_table(orc, [pos], info["head_dim"], info["rot_dim"], info["rope_base"])
+            req.rope = rope.ctypes.data
+            req.token_id, req.use_token = tok, 1
+            req.kv, req.pos = kv._h, pos
+            outs.append(np.array(g.decode_request(req)))
+        runs.append(outs)
+        kv.close()
+        model.close()
+        g.close()
+        f.close()
+    for a, b in zip(*runs):
+        assert np.array_equal(a, b)
