@@ -221,7 +221,6 @@ struct apk_ctx {
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     cudaStream_t launch_stream = nullptr;  // where launch_ex puts the next kernels (null: stream)
     int grid_cap = 0;                      // most CTAs the next matvec launches may take (0: no cap)
-    bool no_pdl_once = false;              // the next launch waits for two branches: no programmatic edge
     int fork_v = 4;                        // CTAs per V tile of that branch (0: no branch); measured 1 / 2 / 4: 168 / 175 / 178 tok/s
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     std::map<std::pair<const uint8_t *, size_t>, int> attached;  // (base,len) -> refcount
@@ -532,8 +531,7 @@ cudaError_t launch_ex(apk_ctx *c, void (*kernel)(Args...), dim3 grid, dim3 block
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl && !c->no_pdl_once ? 1 : 0;
-    c->no_pdl_once = false;
+    cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 

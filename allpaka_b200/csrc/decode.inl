@@ -383,7 +383,8 @@ struct TokenLaunch {
             // One token row on one GPU, nothing pending on the residual stream: V (a few tiles, its row
             // normalised and quantised inside its own CTAs) runs on SMs of its own beside Q | K instead of
             // as a whole launch after it.  A few CTAs per V tile, the other SMs for Q | K; the kernel behind
-            // them waits for both branches.
+            // them depends on both branches (and keeps its programmatic edge: it may start early and waits
+            // itself, like every other launch of the token).
             // (at most a quarter of the SMs go to V)
             const int v_ctas = L.v->n_tiles * std::min(c->fork_v, c->n_sm / (4 * std::max(1, L.v->n_tiles)));
             const bool beside = v_ctas > 0 && c->world == 1 && !uses_xch(c) && m == 1 && !pending_add && pending_xch < 0 &&
@@ -405,7 +406,6 @@ struct TokenLaunch {
             // (joined even after an error above, so that a capture in progress can end)
             const cudaError_t je = cudaStreamWaitEvent(c->stream, c->ev_join, 0);
             if (rc == APK_OK && je != cudaSuccess) rc = fail(APK_ERR_CUDA, "joining the side branch: %s", cudaGetErrorString(je));
-            c->no_pdl_once = true;
             return rc;
         }
         return qkv_part(L, L.qkv, advance, layer, 0);
